@@ -1,0 +1,133 @@
+"""ctypes bindings for the two native libraries.
+
+``cuda()`` loads ``lib/librmlx_b200_cuda.so`` (every sm_100a kernel, exported as ``extern "C"``
+launchers that take raw device pointers and a stream) and ``host()`` loads
+``lib/librmlx_b200_host.so`` (allocator, block manager and other pure C++ runtime pieces). Missing
+libraries are built on first use when a compiler is present; on a machine with a GPU a missing
+CUDA library is an error, never a silent fallback.
+
+This registry of exported launchers, looked up by name and bound once, is the analogue of the
+reference's KernelRegistry (crates/rmlx-core/src/kernels/mod.rs:95-125) for ahead-of-time
+compiled kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Any, Dict, Optional
+
+import torch
+
+from . import _build
+
+_CODES = {"p": c_void_p, "i": c_int, "f": c_float, "q": c_longlong}
+
+# name -> (argument codes, restype code)
+_CUDA_SIGS: Dict[str, tuple] = {
+    "rmlx_error_string": ("i", "p"),
+    "rmlx_gemv_max_batch": ("", "i"),
+    "rmlx_rms_gemv": ("ippppipfpipiiiiiip", "i"),
+    "rmlx_rms_gate_up_swiglu": ("ippppipfpiiiiip", "i"),
+    "rmlx_swiglu_down": ("ippppipipiiiiip", "i"),
+    "rmlx_moe_router": ("ppipfppppppiiiiip", "i"),
+    "rmlx_topk_route": ("ppppppiiip", "i"),
+    "rmlx_moe_gate_up": ("ippppipfppiiiiiiiip", "i"),
+    "rmlx_moe_down": ("ippppipppipiiiiiiiiip", "i"),
+    "rmlx_flash_decode_gtiles": ("ii", "i"),
+    "rmlx_flash_decode_part_o_elems": ("iiiii", "q"),
+    "rmlx_flash_decode_part_ml_elems": ("iiii", "q"),
+    "rmlx_flash_decode_ticket_elems": ("iii", "q"),
+    "rmlx_flash_decode_paged": ("pppppppppiiiiiiifip", "i"),
+    "rmlx_rope_kv_write": ("pppppppppiiiiiiiip", "i"),
+    "rmlx_rope": ("pppppiiiiip", "i"),
+    "rmlx_embedding": ("pppiiiip", "i"),
+    "rmlx_rms_norm": ("pppppiifip", "i"),
+    "rmlx_argmax": ("ppiiiip", "i"),
+    "rmlx_silu_mul": ("ppqip", "i"),
+    "rmlx_decode_advance": ("pppppiip", "i"),
+    "rmlx_fp8_quant_rows": ("pppiip", "i"),
+    "rmlx_fp8_dequant_rows": ("pppiip", "i"),
+}
+
+_lock = threading.Lock()
+_cuda_lib: Optional[ctypes.CDLL] = None
+_host_lib: Optional[ctypes.CDLL] = None
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+def _bind(lib: ctypes.CDLL, sigs: Dict[str, tuple]) -> None:
+    for name, (args, ret) in sigs.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError:
+            continue  # optional symbol (a source file may be excluded from some builds)
+        fn.argtypes = [_CODES[c] for c in args]
+        fn.restype = _CODES[ret] if ret != "p" else ctypes.c_char_p if name == "rmlx_error_string" else c_void_p
+
+
+def register_cuda_sigs(sigs: Dict[str, tuple]) -> None:
+    """Other modules add their launchers' signatures here before first use."""
+    _CUDA_SIGS.update(sigs)
+    if _cuda_lib is not None:
+        _bind(_cuda_lib, sigs)
+
+
+def cuda() -> ctypes.CDLL:
+    global _cuda_lib
+    if _cuda_lib is None:
+        with _lock:
+            if _cuda_lib is None:
+                if not _build.CUDA_LIB.exists():
+                    _build.build(kinds=("cuda",))
+                lib = ctypes.CDLL(str(_build.CUDA_LIB))
+                _bind(lib, _CUDA_SIGS)
+                _cuda_lib = lib
+    return _cuda_lib
+
+
+def host() -> ctypes.CDLL:
+    global _host_lib
+    if _host_lib is None:
+        with _lock:
+            if _host_lib is None:
+                if not _build.HOST_LIB.exists():
+                    _build.build(kinds=("host",))
+                _host_lib = ctypes.CDLL(str(_build.HOST_LIB))
+    return _host_lib
+
+
+def ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(stream: Optional[torch.cuda.Stream] = None) -> int:
+    return (stream or torch.cuda.current_stream()).cuda_stream
+
+
+_launch_count = 0
+
+
+def launch_count() -> int:
+    """Number of kernel launches issued through ``check`` by this process."""
+    return _launch_count
+
+
+def check(rc: int, what: str) -> None:
+    global _launch_count
+    _launch_count += 1
+    if rc == 0:
+        return
+    if rc == -2:
+        raise NativeError(f"{what}: invalid argument or unsupported shape")
+    msg = cuda().rmlx_error_string(rc)
+    raise NativeError(f"{what}: CUDA error {rc}: {msg.decode() if msg else '?'}")
+
+
+def require_cuda_tensor(*ts: Any) -> None:
+    for t in ts:
+        if t is not None and not (isinstance(t, torch.Tensor) and t.is_cuda):
+            raise NativeError("native kernels need CUDA tensors; use rmlx_b200.reference on CPU")

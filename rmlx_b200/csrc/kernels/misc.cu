@@ -1,0 +1,220 @@
+// Small memory-bound kernels around the hot path: embedding gather, stand-alone RMSNorm (with the
+// residual-add form), greedy arg-max over logits, SwiGLU elementwise, and per-token FP8 (E4M3)
+// quantise/dequantise used by the optional FP8 expert-dispatch payload.
+//
+// Counterparts: crates/rmlx-nn/src/embedding.rs:60, crates/rmlx-core/src/ops/rms_norm.rs:86-807,
+// crates/rmlx-core/src/ops/argreduce.rs, crates/rmlx-core/src/ops/silu.rs,
+// crates/rmlx-core/src/ops/fp8.rs:55-378.
+#include "../common/ptx.cuh"
+#include "../common/launch.cuh"
+#include <cuda_fp8.h>
+
+namespace rb {
+
+__global__ void embedding_kernel(const __nv_bfloat16* __restrict__ table,
+                                 const int* __restrict__ ids, __nv_bfloat16* __restrict__ out,
+                                 int D, int vocab) {
+  pdl_wait();
+  int id = ids[blockIdx.x];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const uint4* src = reinterpret_cast<const uint4*>(table + size_t(id) * D);
+  uint4* dst = reinterpret_cast<uint4*>(out + size_t(blockIdx.x) * D);
+  for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = src[i];
+  pdl_launch_dependents();
+}
+
+// out = rmsnorm(x (+ residual)) * w ; when residual is given, sum_out (may alias x) gets x+residual.
+__global__ void __launch_bounds__(256)
+rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
+                const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ out,
+                __nv_bfloat16* __restrict__ sum_out, int D, float eps) {
+  __shared__ float red[8];
+  __shared__ float s_inv;
+  pdl_wait();
+  const size_t base = size_t(blockIdx.x) * D;
+  float ssq = 0.f;
+  for (int i = threadIdx.x; i < D; i += 256) {
+    float v = __bfloat162float(x[base + i]);
+    if (residual) {
+      v += __bfloat162float(residual[base + i]);
+      v = __bfloat162float(__float2bfloat16_rn(v));
+      if (sum_out) sum_out[base + i] = __float2bfloat16_rn(v);
+    }
+    ssq += v * v;
+  }
+  ssq = warp_sum(ssq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ssq;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+    t = warp_sum(t);
+    if (threadIdx.x == 0) s_inv = rsqrtf(t / float(D) + eps);
+  }
+  __syncthreads();
+  const float inv = s_inv;
+  for (int i = threadIdx.x; i < D; i += 256) {
+    float v = residual ? __bfloat162float(sum_out ? sum_out[base + i]
+                                                  : __float2bfloat16_rn(__bfloat162float(x[base + i]) +
+                                                                        __bfloat162float(residual[base + i])))
+                       : __bfloat162float(x[base + i]);
+    out[base + i] = __float2bfloat16_rn(v * inv * (w ? __bfloat162float(w[i]) : 1.f));
+  }
+  pdl_launch_dependents();
+}
+
+// One block per row: index of the maximum (lowest index on ties).
+__global__ void __launch_bounds__(1024)
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int stride) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  pdl_wait();
+  const float* row = logits + size_t(blockIdx.x) * stride;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += 1024) {
+    const float v = row[i];
+    if (v > best) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    best = sv[threadIdx.x]; bi = si[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+  }
+  pdl_launch_dependents();
+}
+
+// act[t, i] = silu(gu[t, i]) * gu[t, I + i]
+__global__ void silu_mul_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ act,
+                                long long total, int I) {
+  const long long idx = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const long long t = idx / I;
+  const int i = int(idx % I);
+  const float g = __bfloat162float(gu[t * 2 * I + i]), u = __bfloat162float(gu[t * 2 * I + I + i]);
+  const float e = __expf(-fabsf(g));
+  const float sig = g >= 0.f ? 1.f / (1.f + e) : e / (1.f + e);
+  act[idx] = __float2bfloat16_rn(g * sig * u);
+}
+
+// Per-token E4M3 quantisation: scale = max|x| / 448 (crates/rmlx-distributed/src/fp8_exchange.rs:85-160).
+__global__ void __launch_bounds__(256)
+fp8_quant_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_fp8_storage_t* __restrict__ q,
+                      float* __restrict__ scales, int D) {
+  __shared__ float red[8];
+  __shared__ float s_scale;
+  const size_t base = size_t(blockIdx.x) * D;
+  float m = 0.f;
+  for (int i = threadIdx.x; i < D; i += 256) m = fmaxf(m, fabsf(__bfloat162float(x[base + i])));
+  m = warp_max(m);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float t = threadIdx.x < 8 ? red[threadIdx.x] : 0.f;
+    t = warp_max(t);
+    if (threadIdx.x == 0) { s_scale = t > 0.f ? t / 448.f : 1.f; scales[blockIdx.x] = s_scale; }
+  }
+  __syncthreads();
+  const float inv = 1.f / s_scale;
+  for (int i = threadIdx.x; i < D; i += 256)
+    q[base + i] = __nv_cvt_float_to_fp8(__bfloat162float(x[base + i]) * inv, __NV_SATFINITE, __NV_E4M3);
+}
+
+__global__ void fp8_dequant_rows_kernel(const __nv_fp8_storage_t* __restrict__ q,
+                                        const float* __restrict__ scales,
+                                        __nv_bfloat16* __restrict__ out, int D) {
+  const size_t base = size_t(blockIdx.x) * D;
+  const float s = scales[blockIdx.x];
+  for (int i = threadIdx.x; i < D; i += blockDim.x) {
+    const __half_raw h = __nv_cvt_fp8_to_halfraw(q[base + i], __NV_E4M3);
+    out[base + i] = __float2bfloat16_rn(__half2float(*reinterpret_cast<const __half*>(&h)) * s);
+  }
+}
+
+// End of a decode step: the sampled token becomes the next input and the sequence grows by one.
+// Running this inside the captured step keeps the host out of the token loop.
+__global__ void decode_advance_kernel(const int* __restrict__ next, int* __restrict__ tokens,
+                                      int* __restrict__ positions, int* __restrict__ seq_lens,
+                                      const int* __restrict__ active, int B) {
+  pdl_wait();
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b < B && (!active || active[b])) {
+    tokens[b] = next[b];
+    positions[b] += 1;
+    seq_lens[b] += 1;
+  }
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" int rmlx_decode_advance(const int* next, int* tokens, int* positions, int* seq_lens,
+                                   const int* active, int B, int pdl, cudaStream_t st) {
+  if (B < 1) return -2;
+  return launch(decode_advance_kernel, dim3((B + 127) / 128), dim3(128), 0, st, pdl != 0, next,
+                tokens, positions, seq_lens, active, B);
+}
+
+extern "C" const char* rmlx_error_string(int code) {
+  return cudaGetErrorString(static_cast<cudaError_t>(code));
+}
+
+extern "C" int rmlx_embedding(const void* table, const int* ids, void* out, int T, int D, int vocab,
+                              int pdl, cudaStream_t st) {
+  if (T < 1 || D % 8) return -2;
+  return launch(embedding_kernel, dim3(T), dim3(128), 0, st, pdl != 0,
+                static_cast<const __nv_bfloat16*>(table), ids, static_cast<__nv_bfloat16*>(out), D,
+                vocab);
+}
+
+extern "C" int rmlx_rms_norm(const void* x, const void* residual, const void* w, void* out,
+                             void* sum_out, int T, int D, float eps, int pdl, cudaStream_t st) {
+  if (T < 1) return -2;
+  return launch(rms_norm_kernel, dim3(T), dim3(256), 0, st, pdl != 0,
+                static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(residual),
+                static_cast<const __nv_bfloat16*>(w), static_cast<__nv_bfloat16*>(out),
+                static_cast<__nv_bfloat16*>(sum_out), D, eps);
+}
+
+extern "C" int rmlx_argmax(const float* logits, int* out, int B, int V, int stride, int pdl,
+                           cudaStream_t st) {
+  if (B < 1 || V < 1) return -2;
+  return launch(argmax_kernel, dim3(B), dim3(1024), 0, st, pdl != 0, logits, out, V, stride);
+}
+
+extern "C" int rmlx_silu_mul(const void* gate_up, void* act, long long T, int I, cudaStream_t st) {
+  const long long total = T * I;
+  if (total < 1) return -2;
+  silu_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(gate_up), static_cast<__nv_bfloat16*>(act), total, I);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int rmlx_fp8_quant_rows(const void* x, void* q, float* scales, int T, int D,
+                                   cudaStream_t st) {
+  if (T < 1) return -2;
+  fp8_quant_rows_kernel<<<T, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                           static_cast<__nv_fp8_storage_t*>(q), scales, D);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int rmlx_fp8_dequant_rows(const void* q, const float* scales, void* out, int T, int D,
+                                     cudaStream_t st) {
+  if (T < 1) return -2;
+  fp8_dequant_rows_kernel<<<T, 256, 0, st>>>(static_cast<const __nv_fp8_storage_t*>(q), scales,
+                                             static_cast<__nv_bfloat16*>(out), D);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -1,0 +1,222 @@
+"""Paged KV cache: a block manager with copy-on-write reference counts plus the device pools the
+attention kernels read.
+
+API and semantics follow crates/rmlx-nn/src/paged_kv_cache.rs:36-631 (``BlockManager``: free list,
+per-sequence block tables, refcounts, ``fork``; ``PagedKvCache``: ``append``, ``get_keys/values``,
+``trim`` for speculative rollback, ``free_sequence``). Differences that are deliberate: K and V live
+in device pools laid out ``[layer][block, kv_head, page, head_dim]`` so one (block, kv head) page is
+contiguous for the attention kernels; appends are done on the device by the RoPE+KV-write kernel
+(the reference copies each token on the host); and the block table is mirrored in a device int32
+tensor so a captured decode graph sees growth without re-capture.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+import torch
+
+from ..reference import ops as ref
+
+PAGE = 16
+
+
+class OutOfBlocks(RuntimeError):
+    pass
+
+
+class BlockManager:
+    """Fixed pool of KV blocks with a free list, per-sequence block tables and refcounts."""
+
+    def __init__(self, num_blocks: int, block_size: int = PAGE, reserved: int = 0):
+        """``reserved`` leading blocks are never handed out (block 0 serves as the harmless
+        target of idle batch rows in a shape-stable decode graph)."""
+        self.num_blocks = num_blocks
+        self.block_size = block_size
+        self.free: List[int] = list(range(num_blocks - 1, reserved - 1, -1))
+        self.ref = [0] * num_blocks
+        self.tables: Dict[int, List[int]] = {}
+        self.lengths: Dict[int, int] = {}
+
+    # -------------------------------------------------------------- queries
+    def num_free_blocks(self) -> int:
+        return len(self.free)
+
+    def blocks_needed(self, seq_id: int, new_tokens: int) -> int:
+        cur = self.lengths.get(seq_id, 0)
+        have = len(self.tables.get(seq_id, ()))
+        need = (cur + new_tokens + self.block_size - 1) // self.block_size
+        return max(0, need - have)
+
+    def can_allocate(self, seq_id: int, new_tokens: int) -> bool:
+        return self.blocks_needed(seq_id, new_tokens) <= len(self.free)
+
+    def block_table(self, seq_id: int) -> List[int]:
+        return self.tables[seq_id]
+
+    def seq_len(self, seq_id: int) -> int:
+        return self.lengths.get(seq_id, 0)
+
+    # -------------------------------------------------------------- mutation
+    def _take(self) -> int:
+        if not self.free:
+            raise OutOfBlocks("KV block pool exhausted")
+        b = self.free.pop()
+        self.ref[b] = 1
+        return b
+
+    def _drop(self, b: int) -> None:
+        self.ref[b] -= 1
+        if self.ref[b] == 0:
+            self.free.append(b)
+        elif self.ref[b] < 0:
+            raise RuntimeError(f"block {b} freed twice")
+
+    def add_sequence(self, seq_id: int) -> None:
+        if seq_id in self.tables:
+            raise KeyError(f"sequence {seq_id} already exists")
+        self.tables[seq_id] = []
+        self.lengths[seq_id] = 0
+
+    def reserve(self, seq_id: int, new_tokens: int) -> List[tuple]:
+        """Make room for ``new_tokens`` more tokens. Returns the copy-on-write work to do:
+        (src_block, dst_block) pairs for a shared last block that is about to be written."""
+        if seq_id not in self.tables:
+            self.add_sequence(seq_id)
+        if not self.can_allocate(seq_id, new_tokens):
+            raise OutOfBlocks(f"need {self.blocks_needed(seq_id, new_tokens)} blocks, "
+                              f"{len(self.free)} free")
+        copies = []
+        table, cur = self.tables[seq_id], self.lengths[seq_id]
+        if new_tokens > 0 and table and cur % self.block_size != 0:
+            last = table[-1]
+            if self.ref[last] > 1:                       # shared partial block: copy before write
+                nb = self._take()
+                copies.append((last, nb))
+                self._drop(last)
+                table[-1] = nb
+        for _ in range(self.blocks_needed(seq_id, new_tokens)):
+            table.append(self._take())
+        return copies
+
+    def commit(self, seq_id: int, new_tokens: int) -> None:
+        self.lengths[seq_id] += new_tokens
+
+    def fork(self, parent: int, child: int) -> None:
+        """Child shares every block of the parent (copy-on-write)."""
+        if child in self.tables:
+            raise KeyError(f"sequence {child} already exists")
+        self.tables[child] = list(self.tables[parent])
+        self.lengths[child] = self.lengths[parent]
+        for b in self.tables[child]:
+            self.ref[b] += 1
+
+    def trim(self, seq_id: int, num_tokens: int) -> None:
+        """Drop the last ``num_tokens`` tokens (speculative rollback)."""
+        cur = self.lengths[seq_id]
+        new = max(0, cur - num_tokens)
+        keep = (new + self.block_size - 1) // self.block_size
+        table = self.tables[seq_id]
+        while len(table) > keep:
+            self._drop(table.pop())
+        self.lengths[seq_id] = new
+
+    def free_sequence(self, seq_id: int) -> None:
+        for b in self.tables.pop(seq_id, []):
+            self._drop(b)
+        self.lengths.pop(seq_id, None)
+
+
+class PagedKvCache:
+    """Device K/V pools for every layer plus the manager and a device mirror of block tables."""
+
+    def __init__(self, num_blocks: int, num_layers: int, kv_heads: int, head_dim: int,
+                 dtype=torch.bfloat16, device="cpu", max_seqs: int = 64,
+                 max_blocks_per_seq: int = 512, block_size: int = PAGE):
+        self.manager = BlockManager(num_blocks, block_size, reserved=1)
+        self.num_layers, self.kv_heads, self.head_dim = num_layers, kv_heads, head_dim
+        self.block_size = block_size
+        self.k = [torch.zeros(num_blocks, kv_heads, block_size, head_dim, dtype=dtype, device=device)
+                  for _ in range(num_layers)]
+        self.v = [torch.zeros(num_blocks, kv_heads, block_size, head_dim, dtype=dtype, device=device)
+                  for _ in range(num_layers)]
+        self.device = torch.device(device)
+        self.max_blocks_per_seq = max_blocks_per_seq
+        # row r of the device table belongs to the sequence bound to slot r
+        self.block_table = torch.zeros(max_seqs, max_blocks_per_seq, dtype=torch.int32, device=device)
+        self._host_table = torch.zeros(max_seqs, max_blocks_per_seq, dtype=torch.int32,
+                                       pin_memory=self.device.type == "cuda")
+        self.slot_of: Dict[int, int] = {}
+        self._free_slots = list(range(max_seqs - 1, -1, -1))
+
+    # -------------------------------------------------------------- sequences
+    def add_sequence(self, seq_id: int) -> int:
+        self.manager.add_sequence(seq_id)
+        slot = self._free_slots.pop()
+        self.slot_of[seq_id] = slot
+        return slot
+
+    def free_sequence(self, seq_id: int) -> None:
+        self.manager.free_sequence(seq_id)
+        slot = self.slot_of.pop(seq_id)
+        self._host_table[slot].zero_()
+        self._free_slots.append(slot)
+
+    def fork(self, parent: int, child: int) -> int:
+        self.manager.fork(parent, child)
+        slot = self._free_slots.pop()
+        self.slot_of[child] = slot
+        self._sync_slot(child)
+        return slot
+
+    def seq_len(self, seq_id: int) -> int:
+        return self.manager.seq_len(seq_id)
+
+    def _sync_slot(self, seq_id: int) -> None:
+        slot = self.slot_of[seq_id]
+        table = self.manager.block_table(seq_id)
+        if len(table) > self.max_blocks_per_seq:
+            raise OutOfBlocks("sequence exceeds max_blocks_per_seq")
+        row = self._host_table[slot]
+        row[:len(table)] = torch.tensor(table, dtype=torch.int32)
+        self.block_table[slot].copy_(row, non_blocking=True)
+
+    def reserve(self, seq_id: int, new_tokens: int) -> None:
+        """Ensure blocks exist for ``new_tokens`` more tokens (doing any copy-on-write) and push
+        the table row to the device."""
+        before = len(self.manager.tables.get(seq_id, ()))
+        copies = self.manager.reserve(seq_id, new_tokens)
+        for src, dst in copies:
+            for l in range(self.num_layers):
+                self.k[l][dst].copy_(self.k[l][src])
+                self.v[l][dst].copy_(self.v[l][src])
+        if copies or len(self.manager.block_table(seq_id)) != before:
+            self._sync_slot(seq_id)
+
+    def commit(self, seq_id: int, new_tokens: int) -> None:
+        self.manager.commit(seq_id, new_tokens)
+
+    def trim(self, seq_id: int, num_tokens: int) -> None:
+        self.manager.trim(seq_id, num_tokens)
+        self._sync_slot(seq_id)
+
+    # -------------------------------------------------------------- reference-style access
+    def append(self, layer: int, seq_id: int, k: torch.Tensor, v: torch.Tensor, start: int) -> None:
+        """Host-driven append of k, v [n, kv_heads, head_dim] at positions start.. (the reference's
+        form; the native path writes through the RoPE+KV kernel instead)."""
+        table = torch.tensor(self.manager.block_table(seq_id), dtype=torch.int64, device=self.device)
+        bs = self.block_size
+        pos = torch.arange(start, start + k.shape[0], device=self.device)
+        blk, off = table[pos // bs], pos % bs
+        self.k[layer][blk, :, off] = k.to(self.k[layer].dtype)
+        self.v[layer][blk, :, off] = v.to(self.v[layer].dtype)
+
+    def get_keys(self, layer: int, seq_id: int, length: Optional[int] = None) -> torch.Tensor:
+        length = self.manager.seq_len(seq_id) if length is None else length
+        row = torch.tensor(self.manager.block_table(seq_id), dtype=torch.int64, device=self.device)
+        return ref.gather_paged(self.k[layer], row, length)
+
+    def get_values(self, layer: int, seq_id: int, length: Optional[int] = None) -> torch.Tensor:
+        length = self.manager.seq_len(seq_id) if length is None else length
+        row = torch.tensor(self.manager.block_table(seq_id), dtype=torch.int64, device=self.device)
+        return ref.gather_paged(self.v[layer], row, length)

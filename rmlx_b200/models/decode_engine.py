@@ -1,0 +1,215 @@
+"""Cached decode: every buffer, pointer and launch of a decode step is resolved once, the step is
+captured in a CUDA graph, and each new token is one graph replay.
+
+This is the B200 form of the reference's ``CachedDecode`` + fused 7-dispatch layer
+(crates/rmlx-nn/src/transformer.rs:2306-2555,3613-4050) and of its ExecGraph / command-batcher
+machinery (crates/rmlx-metal/src/exec_graph.rs:110-401). Per layer the captured step holds:
+
+  1. RMSNorm + QKV projection            (rms_gemv)
+  2. RoPE(Q,K) + paged KV append         (rope_kv_write)
+  3. paged split-KV flash decode         (flash_decode_paged, merges its splits in-kernel)
+  4. O projection + residual             (rms_gemv)             [tensor parallel: + all-reduce]
+  5. MoE: RMSNorm + router + top-k       (moe_router)
+  6.      expert gate/up + SwiGLU        (moe_gate_up)
+  7.      expert down + weighted combine + residual (moe_down)  [tensor parallel: + all-reduce]
+     or, for dense layers, gate/up + SwiGLU and down + residual.
+
+and after the last layer: final RMSNorm + LM head, arg-max, and the advance kernel that feeds the
+sampled token back as the next input. Consecutive kernels are chained with programmatic dependent
+launch so each one's prologue overlaps its predecessor's tail.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import torch
+
+from .. import _lib
+from ..kv.paged import PagedKvCache
+from ..ops import decode as D
+from .transformer import TransformerModel
+
+
+class CachedDecode:
+    def __init__(self, model: TransformerModel, cache: PagedKvCache, max_batch: int = 1,
+                 use_graph: bool = True, pdl: bool = True, splits: Optional[int] = None,
+                 comm=None, greedy: bool = True):
+        if model.device.type != "cuda":
+            raise _lib.NativeError("CachedDecode runs this package's CUDA kernels; on CPU use "
+                                   "TransformerModel.forward")
+        self.model, self.cache, self.B = model, cache, max_batch
+        self.cfg = cfg = model.cfg
+        self.comm = comm
+        self.pdl = pdl
+        self.use_graph = use_graph
+        self.greedy = greedy
+        dev = model.device
+        B, D_ = max_batch, cfg.hidden_size
+        hq, hkv, hd = model.hq, model.hkv, cfg.head_dim
+        i32 = dict(dtype=torch.int32, device=dev)
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.tokens = torch.zeros(B, **i32)
+        self.positions = torch.zeros(B, **i32)
+        self.seq_lens = torch.zeros(B, **i32)
+        self.active = torch.zeros(B, **i32)
+        self.next_tokens = torch.zeros(B, **i32)
+        self.block_table = torch.zeros(B, cache.max_blocks_per_seq, **i32)
+        self.h = torch.zeros(B, D_, **bf)
+        self.h2 = torch.zeros(B, D_, **bf)
+        self.qkv = torch.zeros(B, (hq + 2 * hkv) * hd, **bf)
+        self.q = torch.zeros(B, hq, hd, **bf)
+        self.attn = torch.zeros(B, hq, hd, **bf)
+        self.vocab_local = model.w.lm_head.n
+        self.logits = torch.zeros(B, cfg.vocab_size, dtype=torch.float32, device=dev)
+        lib = _lib.cuda()
+        gt = lib.rmlx_flash_decode_gtiles(hq, hkv)
+        self.splits = splits or D.default_splits(B, hkv, gt, cfg.max_seq_len)
+        self.fd_scratch = D.FlashDecodeScratch(B, hq, hkv, hd, self.splits, dev)
+        moe = cfg.ff_type.moe
+        if moe is not None:
+            k = moe.num_experts_per_token
+            i_local = max(l.experts_gate_up.n // 2 for l in model.w.layers if l.experts_gate_up is not None)
+            self.idx = torch.zeros(B, k, **i32)
+            self.wts = torch.zeros(B, k, dtype=torch.float32, device=dev)
+            self.act = torch.zeros(B * k, i_local, **bf)
+            self.router_scratch = D.RouterScratch(B, moe.num_experts, dev)
+        dense_i = [l.w_gate_up.n // 2 for l in model.w.layers if l.w_gate_up is not None]
+        if dense_i:
+            self.dense_act = torch.zeros(B, max(dense_i), **bf)
+        self.seq_ids: List[int] = []
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self._launches_per_step = 0
+
+    # ------------------------------------------------------------------ binding
+    def bind(self, seq_ids: Sequence[int], last_tokens: Sequence[int]) -> None:
+        """Attach up to ``max_batch`` cached sequences to the batch rows and load their state."""
+        assert len(seq_ids) <= self.B
+        self.seq_ids = list(seq_ids)
+        n = len(seq_ids)
+        lens = [self.cache.seq_len(s) for s in seq_ids]
+        self.tokens.zero_(); self.positions.zero_(); self.seq_lens.zero_(); self.active.zero_()
+        self.tokens[:n] = torch.tensor(list(last_tokens), dtype=torch.int32)
+        self.positions[:n] = torch.tensor(lens, dtype=torch.int32)
+        self.seq_lens[:n] = torch.tensor([l + 1 for l in lens], dtype=torch.int32)
+        self.active[:n] = 1
+        # inactive rows still run (shape-stable graph): give them a harmless one-token context
+        if n < self.B:
+            self.seq_lens[n:] = 1
+        self.refresh_tables()
+
+    def refresh_tables(self) -> None:
+        for b, s in enumerate(self.seq_ids):
+            self.block_table[b].copy_(self.cache.block_table[self.cache.slot_of[s]])
+
+    def reserve(self, steps: int) -> None:
+        """Allocate KV blocks for the next ``steps`` tokens of every bound sequence."""
+        for s in self.seq_ids:
+            self.cache.reserve(s, steps)
+        self.refresh_tables()
+
+    # ------------------------------------------------------------------ the step
+    def _sum_into(self, partial: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, pdl: bool):
+        """Tensor-parallel reduction of a partial projection plus the residual."""
+        self.comm.allreduce_residual(partial, residual, out, pdl=pdl)
+
+    def _run_step(self) -> None:
+        m, cfg, w = self.model, self.cfg, self.model.w
+        eps, pdl = cfg.rms_norm_eps, self.pdl
+        tp = self.comm is not None and m.layout.world > 1
+        n0 = _lib.launch_count()
+        D.embedding(w.embed, self.tokens, out=self.h, pdl=False)
+        h, h2 = self.h, self.h2
+        for li, lw in enumerate(w.layers):
+            D.rms_gemv(h, lw.wqkv, lw.norm1, eps, out=self.qkv, pdl=pdl)
+            D.rope_kv_write(self.qkv, self.q, self.cache.k[li], self.cache.v[li], self.block_table,
+                            self.positions, m.cos, m.sin, m.hq, m.hkv,
+                            traditional=cfg.rope_traditional, pdl=pdl)
+            D.flash_decode_paged(self.q, self.cache.k[li], self.cache.v[li], self.block_table,
+                                 self.seq_lens, m.scale, self.splits, self.fd_scratch,
+                                 cfg.sliding_window, out=self.attn, pdl=pdl)
+            a2 = self.attn.view(self.B, -1)
+            if tp:
+                self.comm.gemv_allreduce(a2, lw.wo, residual=h, out=h2, pdl=pdl)
+            else:
+                D.rms_gemv(a2, lw.wo, None, eps, residual=h, out=h2, pdl=pdl)
+            if lw.router is not None:
+                moe = cfg.ff_type.moe
+                D.moe_router(h2, lw.router, lw.norm2, eps, moe.num_experts_per_token, lw.expert_bias,
+                             self.router_scratch, self.idx, self.wts, pdl=pdl)
+                D.moe_gate_up(h2, lw.experts_gate_up, lw.norm2, eps, self.idx, out=self.act,
+                              expert_base=lw.expert_base, pdl=pdl)
+                if tp:
+                    self.comm.moe_down_allreduce(self.act, lw.experts_down, self.idx, self.wts,
+                                                 residual=h2, out=h, expert_base=lw.expert_base,
+                                                 pdl=pdl)
+                else:
+                    D.moe_down(self.act, lw.experts_down, self.idx, self.wts, residual=h2, out=h,
+                               expert_base=lw.expert_base, pdl=pdl)
+            else:
+                act = self.dense_act[:, :lw.w_gate_up.n // 2]
+                D.rms_gate_up_swiglu(h2, lw.w_gate_up, lw.norm2, eps, out=act, pdl=pdl)
+                if tp:
+                    self.comm.gemv_allreduce(act, lw.w_down, residual=h2, out=h, pdl=pdl)
+                else:
+                    D.rms_gemv(act, lw.w_down, None, eps, residual=h2, out=h, pdl=pdl)
+        if tp and self.vocab_local != cfg.vocab_size:
+            self.comm.lm_head_allgather(h, w.lm_head, w.final_norm, eps, self.logits, w.vocab_base,
+                                        pdl=pdl)
+        else:
+            D.rms_gemv(h, w.lm_head, w.final_norm, eps, out=self.logits, pdl=pdl)
+        if self.greedy:
+            D.argmax(self.logits, out=self.next_tokens, pdl=pdl)
+            rc = _lib.cuda().rmlx_decode_advance(self.next_tokens.data_ptr(), self.tokens.data_ptr(),
+                                                 self.positions.data_ptr(), self.seq_lens.data_ptr(),
+                                                 self.active.data_ptr(), self.B, int(pdl),
+                                                 _lib.stream_ptr())
+            _lib.check(rc, "decode_advance")
+        self._launches_per_step = _lib.launch_count() - n0
+
+    def capture(self) -> None:
+        """Warm up once eagerly (sets kernel attributes), then capture the step."""
+        saved = [t.clone() for t in (self.tokens, self.positions, self.seq_lens)]
+        s = torch.cuda.Stream(device=self.model.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._run_step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        for t, sv in zip((self.tokens, self.positions, self.seq_lens), saved):
+            t.copy_(sv)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            self._run_step()
+        for t, sv in zip((self.tokens, self.positions, self.seq_lens), saved):
+            t.copy_(sv)
+        torch.cuda.synchronize()
+        self._graph = g
+
+    def step(self) -> torch.Tensor:
+        """Run one decode step for every bound row. Returns the device tensor of sampled tokens
+        (greedy) — reading it is the caller's only synchronisation. KV blocks for the step must
+        have been reserved."""
+        if self.use_graph:
+            if self._graph is None:
+                self.capture()
+            self._graph.replay()
+        else:
+            self._run_step()
+        for s in self.seq_ids:
+            self.cache.commit(s, 1)
+        return self.next_tokens
+
+    @property
+    def launches_per_step(self) -> int:
+        return self._launches_per_step
+
+    # ------------------------------------------------------------------ convenience
+    @torch.no_grad()
+    def generate(self, steps: int) -> torch.Tensor:
+        """Greedy-generate ``steps`` tokens for the bound sequences: [n_seqs, steps] on the host."""
+        self.reserve(steps + 1)
+        out = torch.zeros(len(self.seq_ids), steps, dtype=torch.int64)
+        for i in range(steps):
+            nxt = self.step()
+            out[:, i] = nxt[:len(self.seq_ids)].cpu().long()
+        return out

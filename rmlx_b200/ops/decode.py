@@ -1,0 +1,316 @@
+"""Python entry points for the decode-path kernels (csrc/kernels/decode_gemv.cu, decode_moe.cu,
+flash_decode.cu, rope_kv.cu, misc.cu). Each function validates shapes, allocates the output when
+none is passed, and launches on the current stream; with ``pdl=True`` the launch carries the
+programmatic-dependent-launch attribute so its prologue overlaps the previous kernel's tail.
+
+Batches larger than the kernels' activation-tile limit are processed in chunks.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+
+from .. import _lib
+from .weights import LinearWeight, W_Q4
+
+_MAXB = 4
+
+
+def _wargs(w: LinearWeight):
+    return (w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases))
+
+
+def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = None,
+             eps: float = 1e-6, residual: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None, out_dtype=torch.bfloat16, pdl: bool = False
+             ) -> torch.Tensor:
+    """out[b] = residual[b] + W @ rmsnorm(x[b]; norm_w). norm_w None = no norm; x: [B, K] bf16."""
+    _lib.require_cuda_tensor(x, w.w)
+    assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    b, k = x.shape
+    n = w.n
+    assert k == w.k, f"K mismatch {k} vs {w.k}"
+    if out is None:
+        out = torch.empty(b, n, dtype=out_dtype, device=x.device)
+    lib, st = _lib.cuda(), _lib.stream_ptr()
+    for b0 in range(0, b, _MAXB):
+        bb = min(_MAXB, b - b0)
+        xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
+        rs = None if residual is None else residual[b0:b0 + bb]
+        rc = lib.rmlx_rms_gemv(*_wargs(w), xs.data_ptr(), xs.stride(0), _lib.ptr(norm_w), eps,
+                               _lib.ptr(rs), 0 if rs is None else rs.stride(0), os_.data_ptr(),
+                               os_.stride(0), int(out.dtype == torch.float32), bb, n, k, int(pdl), st)
+        _lib.check(rc, "rms_gemv")
+    return out
+
+
+def rms_gate_up_swiglu(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor], eps: float,
+                       out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
+    """Dense SwiGLU first half: act = silu(Wg xn) * (Wu xn); w holds gate rows then up rows."""
+    _lib.require_cuda_tensor(x, w.w)
+    b, k = x.shape
+    i = w.n // 2
+    if out is None:
+        out = torch.empty(b, i, dtype=torch.bfloat16, device=x.device)
+    lib, st = _lib.cuda(), _lib.stream_ptr()
+    for b0 in range(0, b, _MAXB):
+        bb = min(_MAXB, b - b0)
+        xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
+        rc = lib.rmlx_rms_gate_up_swiglu(*_wargs(w), xs.data_ptr(), xs.stride(0), _lib.ptr(norm_w),
+                                         eps, os_.data_ptr(), os_.stride(0), bb, i, k, int(pdl), st)
+        _lib.check(rc, "rms_gate_up_swiglu")
+    return out
+
+
+def swiglu_down(gate_up: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = None,
+                out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
+    """out = residual + W_down @ (silu(gate) * up) with gate_up = [gate | up] per row."""
+    _lib.require_cuda_tensor(gate_up, w.w)
+    b = gate_up.shape[0]
+    i = gate_up.shape[1] // 2
+    assert i == w.k
+    n = w.n
+    if out is None:
+        out = torch.empty(b, n, dtype=torch.bfloat16, device=gate_up.device)
+    lib, st = _lib.cuda(), _lib.stream_ptr()
+    for b0 in range(0, b, _MAXB):
+        bb = min(_MAXB, b - b0)
+        g, os_ = gate_up[b0:b0 + bb], out[b0:b0 + bb]
+        rs = None if residual is None else residual[b0:b0 + bb]
+        rc = lib.rmlx_swiglu_down(*_wargs(w), g.data_ptr(), g.stride(0), _lib.ptr(rs),
+                                  0 if rs is None else rs.stride(0), os_.data_ptr(), os_.stride(0),
+                                  bb, n, i, int(pdl), st)
+        _lib.check(rc, "swiglu_down")
+    return out
+
+
+class RouterScratch:
+    """Device scratch for the fused router: fp32 logits [B, E] and a zeroed ticket word."""
+
+    def __init__(self, max_batch: int, num_experts: int, device):
+        self.logits = torch.empty(max_batch, num_experts, dtype=torch.float32, device=device)
+        self.ticket = torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def moe_router(x: torch.Tensor, gate_w: torch.Tensor, norm_w: Optional[torch.Tensor], eps: float,
+               top_k: int, expert_bias: Optional[torch.Tensor] = None,
+               scratch: Optional[RouterScratch] = None, idx: Optional[torch.Tensor] = None,
+               wts: Optional[torch.Tensor] = None, counts: Optional[torch.Tensor] = None,
+               pdl: bool = False) -> Tuple[torch.Tensor, torch.Tensor]:
+    """RMSNorm + gate projection + softmax + top-k + renormalise. x [B, K] bf16, gate_w [E, K] bf16.
+    Returns (indices int32 [B, k], weights fp32 [B, k])."""
+    _lib.require_cuda_tensor(x, gate_w)
+    b, k = x.shape
+    e = gate_w.shape[0]
+    scratch = scratch or RouterScratch(b, e, x.device)
+    if idx is None:
+        idx = torch.empty(b, top_k, dtype=torch.int32, device=x.device)
+    if wts is None:
+        wts = torch.empty(b, top_k, dtype=torch.float32, device=x.device)
+    lib, st = _lib.cuda(), _lib.stream_ptr()
+    for b0 in range(0, b, _MAXB):
+        bb = min(_MAXB, b - b0)
+        xs = x[b0:b0 + bb]
+        rc = lib.rmlx_moe_router(gate_w.data_ptr(), xs.data_ptr(), xs.stride(0), _lib.ptr(norm_w),
+                                 eps, _lib.ptr(expert_bias), scratch.logits[b0:].data_ptr(),
+                                 idx[b0:].data_ptr(), wts[b0:].data_ptr(), _lib.ptr(counts),
+                                 scratch.ticket.data_ptr(), bb, e, k, top_k, int(pdl), st)
+        _lib.check(rc, "moe_router")
+    return idx, wts
+
+
+def topk_route(logits: torch.Tensor, top_k: int, expert_bias: Optional[torch.Tensor] = None,
+               want_counts: bool = True):
+    """Selection over precomputed fp32 logits [T, E]. Returns (idx, weights, counts, offsets)."""
+    _lib.require_cuda_tensor(logits)
+    assert logits.dtype == torch.float32 and logits.is_contiguous()
+    t, e = logits.shape
+    idx = torch.empty(t, top_k, dtype=torch.int32, device=logits.device)
+    wts = torch.empty(t, top_k, dtype=torch.float32, device=logits.device)
+    counts = torch.empty(e, dtype=torch.int32, device=logits.device) if want_counts else None
+    offsets = torch.empty(e + 1, dtype=torch.int32, device=logits.device) if want_counts else None
+    rc = _lib.cuda().rmlx_topk_route(logits.data_ptr(), _lib.ptr(expert_bias), idx.data_ptr(),
+                                     wts.data_ptr(), _lib.ptr(counts), _lib.ptr(offsets), t, e, top_k,
+                                     _lib.stream_ptr())
+    _lib.check(rc, "topk_route")
+    return idx, wts, counts, offsets
+
+
+def moe_gate_up(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor], eps: float,
+                idx: torch.Tensor, out: Optional[torch.Tensor] = None, expert_base: int = 0,
+                pdl: bool = False) -> torch.Tensor:
+    """Per (token, slot): act = silu(Wg[e] xn) * (Wu[e] xn). w: stacked [E_local, 2I, K].
+    Slots whose expert is outside [expert_base, expert_base + E_local) are left untouched."""
+    _lib.require_cuda_tensor(x, w.w, idx)
+    b, k = x.shape
+    top_k = idx.shape[1]
+    i = w.n // 2
+    if out is None:
+        out = torch.zeros(b * top_k, i, dtype=torch.bfloat16, device=x.device)
+    rc = _lib.cuda().rmlx_moe_gate_up(*_wargs(w), x.data_ptr(), x.stride(0), _lib.ptr(norm_w), eps,
+                                      idx.data_ptr(), out.data_ptr(), out.stride(0), b, top_k, i, k,
+                                      expert_base, w.experts, int(pdl), _lib.stream_ptr())
+    _lib.check(rc, "moe_gate_up")
+    return out
+
+
+def moe_down(act: torch.Tensor, w: LinearWeight, idx: torch.Tensor, wts: torch.Tensor,
+             residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+             out_dtype=torch.bfloat16, expert_base: int = 0, pdl: bool = False) -> torch.Tensor:
+    """out[b] = residual[b] + sum_slot wts[b,slot] * Wd[e] @ act[b*k+slot]. w: [E_local, N, I]."""
+    _lib.require_cuda_tensor(act, w.w, idx, wts)
+    b, top_k = idx.shape
+    n, i = w.n, w.k
+    if out is None:
+        out = torch.empty(b, n, dtype=out_dtype, device=act.device)
+    rc = _lib.cuda().rmlx_moe_down(*_wargs(w), act.data_ptr(), act.stride(0), idx.data_ptr(),
+                                   wts.data_ptr(), _lib.ptr(residual),
+                                   0 if residual is None else residual.stride(0), out.data_ptr(),
+                                   out.stride(0), int(out.dtype == torch.float32), b, top_k, n, i,
+                                   expert_base, w.experts, int(pdl), _lib.stream_ptr())
+    _lib.check(rc, "moe_down")
+    return out
+
+
+class FlashDecodeScratch:
+    """Split-KV scratch: partial outputs, (max, sum) pairs and the per-tile ticket counters."""
+
+    def __init__(self, batch: int, hq: int, hkv: int, head_dim: int, splits: int, device):
+        lib = _lib.cuda()
+        self.splits = splits
+        self.part_o = torch.empty(lib.rmlx_flash_decode_part_o_elems(batch, hq, hkv, splits, head_dim),
+                                  dtype=torch.float32, device=device)
+        self.part_ml = torch.empty(lib.rmlx_flash_decode_part_ml_elems(batch, hq, hkv, splits),
+                                   dtype=torch.float32, device=device)
+        self.tickets = torch.zeros(lib.rmlx_flash_decode_ticket_elems(batch, hq, hkv),
+                                   dtype=torch.int32, device=device)
+
+
+def default_splits(batch: int, hkv: int, gtiles: int, max_len: int, sm_count: int = 148) -> int:
+    """Enough KV splits to give every SM a block, capped so a split keeps >= 4 pages."""
+    tiles = max(1, batch * hkv * gtiles)
+    want = max(1, (2 * sm_count + tiles - 1) // tiles)
+    cap = max(1, max_len // 64)
+    return int(min(64, want, cap))
+
+
+def flash_decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                       block_table: torch.Tensor, seq_lens: torch.Tensor,
+                       scale: Optional[float] = None, splits: Optional[int] = None,
+                       scratch: Optional[FlashDecodeScratch] = None, window: int = 0,
+                       out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
+    """q [B, Hq, D] bf16; caches [blocks, Hkv, 16, D] bf16; block_table int32 [B, max_blocks];
+    seq_lens int32 [B] (context length including the current token)."""
+    _lib.require_cuda_tensor(q, k_cache, v_cache, block_table, seq_lens)
+    b, hq, d = q.shape
+    hkv, page = k_cache.shape[1], k_cache.shape[2]
+    assert page == 16 and k_cache.shape[3] == d and q.is_contiguous()
+    assert block_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
+    if scale is None:
+        scale = 1.0 / math.sqrt(d)
+    lib = _lib.cuda()
+    if splits is None:
+        splits = scratch.splits if scratch is not None else default_splits(
+            b, hkv, lib.rmlx_flash_decode_gtiles(hq, hkv), block_table.shape[1] * page)
+    if splits > 1 and scratch is None:
+        scratch = FlashDecodeScratch(b, hq, hkv, d, splits, q.device)
+    if out is None:
+        out = torch.empty_like(q)
+    rc = lib.rmlx_flash_decode_paged(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+        seq_lens.data_ptr(), out.data_ptr(),
+        None if scratch is None else scratch.part_o.data_ptr(),
+        None if scratch is None else scratch.part_ml.data_ptr(),
+        None if scratch is None else scratch.tickets.data_ptr(),
+        b, hq, hkv, d, block_table.stride(0), splits, window, scale, int(pdl), _lib.stream_ptr())
+    _lib.check(rc, "flash_decode_paged")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
+                  v_cache: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
+                  cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int,
+                  token_seq: Optional[torch.Tensor] = None, traditional: bool = False,
+                  pdl: bool = False) -> torch.Tensor:
+    """RoPE(Q) -> q_out, RoPE(K) and V -> their page slots. qkv [T, (Hq+2Hkv)*D] bf16."""
+    _lib.require_cuda_tensor(qkv, q_out, k_cache, v_cache, block_table, positions, cos, sin)
+    t = qkv.shape[0]
+    d = k_cache.shape[3]
+    assert qkv.is_contiguous() and qkv.shape[1] == (hq + 2 * hkv) * d
+    assert positions.dtype == torch.int32 and cos.dtype == torch.float32
+    rc = _lib.cuda().rmlx_rope_kv_write(
+        qkv.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), positions.data_ptr(), _lib.ptr(token_seq), cos.data_ptr(),
+        sin.data_ptr(), t, hq, hkv, d, block_table.stride(0), k_cache.shape[2], int(traditional),
+        int(pdl), _lib.stream_ptr())
+    _lib.check(rc, "rope_kv_write")
+    return q_out
+
+
+def rope(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
+         traditional: bool = False, inverse: bool = False) -> torch.Tensor:
+    """x [T, H, D] bf16."""
+    _lib.require_cuda_tensor(x, positions, cos, sin)
+    t, h, d = x.shape
+    out = torch.empty_like(x)
+    rc = _lib.cuda().rmlx_rope(x.data_ptr(), out.data_ptr(), positions.data_ptr(), cos.data_ptr(),
+                               sin.data_ptr(), t, h, d, int(traditional), int(inverse),
+                               _lib.stream_ptr())
+    _lib.check(rc, "rope")
+    return out
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None,
+              pdl: bool = False) -> torch.Tensor:
+    _lib.require_cuda_tensor(table, ids)
+    assert ids.dtype == torch.int32 and table.dtype == torch.bfloat16
+    t = ids.numel()
+    if out is None:
+        out = torch.empty(t, table.shape[1], dtype=torch.bfloat16, device=table.device)
+    rc = _lib.cuda().rmlx_embedding(table.data_ptr(), ids.data_ptr(), out.data_ptr(), t,
+                                    table.shape[1], table.shape[0], int(pdl), _lib.stream_ptr())
+    _lib.check(rc, "embedding")
+    return out
+
+
+def rms_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float,
+             residual: Optional[torch.Tensor] = None, sum_out: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
+    """rmsnorm(x [+ residual]) * w over the last dim; bf16 [T, D]."""
+    _lib.require_cuda_tensor(x)
+    x2 = x.reshape(-1, x.shape[-1])
+    assert x2.is_contiguous() and x2.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty_like(x2)
+    if residual is not None and sum_out is None:
+        sum_out = torch.empty_like(x2)
+    rc = _lib.cuda().rmlx_rms_norm(x2.data_ptr(), _lib.ptr(residual), _lib.ptr(w), out.data_ptr(),
+                                   _lib.ptr(sum_out), x2.shape[0], x2.shape[1], eps, int(pdl),
+                                   _lib.stream_ptr())
+    _lib.check(rc, "rms_norm")
+    return out.view(x.shape)
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, pdl: bool = False
+           ) -> torch.Tensor:
+    _lib.require_cuda_tensor(logits)
+    assert logits.dtype == torch.float32 and logits.dim() == 2
+    if out is None:
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    rc = _lib.cuda().rmlx_argmax(logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1],
+                                 logits.stride(0), int(pdl), _lib.stream_ptr())
+    _lib.check(rc, "argmax")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _lib.require_cuda_tensor(gate_up)
+    t, two_i = gate_up.shape
+    assert gate_up.is_contiguous()
+    if out is None:
+        out = torch.empty(t, two_i // 2, dtype=torch.bfloat16, device=gate_up.device)
+    rc = _lib.cuda().rmlx_silu_mul(gate_up.data_ptr(), out.data_ptr(), t, two_i // 2, _lib.stream_ptr())
+    _lib.check(rc, "silu_mul")
+    return out
