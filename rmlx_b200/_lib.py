@@ -43,7 +43,9 @@ _CUDA_SIGS: Dict[str, tuple] = {
     "rmlx_rope": ("pppppiiiiip", "i"),
     "rmlx_embedding": ("pppiiiip", "i"),
     "rmlx_rms_norm": ("pppppiifip", "i"),
-    "rmlx_argmax": ("ppiiiip", "i"),
+    "rmlx_argmax": ("ppiiippip", "i"),
+    "rmlx_gemm_pick_bn": ("ii", "i"),
+    "rmlx_gemm_bf16": ("ppppiiiiiiipip", "i"),
     "rmlx_silu_mul": ("ppqip", "i"),
     "rmlx_decode_advance": ("pppppiip", "i"),
     "rmlx_fp8_quant_rows": ("pppiip", "i"),

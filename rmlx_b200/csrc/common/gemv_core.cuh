@@ -151,41 +151,54 @@ struct XStage<WQ4> {
 };
 
 // ------------------------------------------------------------------------------------------------
-// Warp dot products. acc[r][b] += dot(row r, activation b) over the whole K, partial per lane
-// (the caller finishes with a warp reduction). smem_b_stride is the byte distance between the
-// staged activations of consecutive b.
+// Warp dot products. A "tile" is the slice of R weight rows that one warp pulls per iteration:
+// two 16-byte loads per lane and row (64 chunks of 8 bf16, or 64 half-groups of 32 nibbles).
+// Loading and multiplying are separate so a kernel can issue the first tile's loads before it
+// stages the activations (and before it waits on the previous kernel): weights do not depend on
+// either. acc[r][b] += dot(row r, activation b), partial per lane; the caller finishes with a warp
+// reduction. smem_b_stride is the byte distance between the staged activations of consecutive b.
 // ------------------------------------------------------------------------------------------------
+template <class Row, int R>
+struct Tile;
+template <int R>
+struct Tile<RowBf16, R> { uint4 w[2][R]; };
+template <int R>
+struct Tile<RowQ4, R> { uint4 w[2][R]; float sc[2][R], bi[2][R]; };
+
+template <int R>
+__device__ __forceinline__ void load_tile(const RowBf16 (&rows)[R], int K, int c0,
+                                          Tile<RowBf16, R>& t) {
+  const int lane = threadIdx.x & 31, nchunk = K >> 3;
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int c = c0 + u * 32 + lane;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      t.w[u][r] = (c < nchunk) ? ldg_stream(rows[r].w + (size_t(c) << 3)) : make_uint4(0, 0, 0, 0);
+  }
+}
+
 template <int R, int B>
-__device__ __forceinline__ void warp_dot(const RowBf16 (&rows)[R], const char* smem,
+__device__ __forceinline__ void fma_tile(const Tile<RowBf16, R>& t, int c0, const char* smem,
                                          size_t smem_b_stride, int K, float (&acc)[R][B]) {
-  const int lane = threadIdx.x & 31;
-  const int nchunk = K >> 3;
-  for (int c0 = 0; c0 < nchunk; c0 += 64) {
-    uint4 w[2][R];
+  const int lane = threadIdx.x & 31, nchunk = K >> 3;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int c = c0 + u * 32 + lane;
+  for (int u = 0; u < 2; ++u) {
+    const int c = c0 + u * 32 + lane;
+    if (c < nchunk) {
 #pragma unroll
-      for (int r = 0; r < R; ++r)
-        w[u][r] = (c < nchunk) ? ldg_stream(rows[r].w + (size_t(c) << 3)) : make_uint4(0, 0, 0, 0);
-    }
+      for (int b = 0; b < B; ++b) {
+        const float4* xs = reinterpret_cast<const float4*>(smem + b * smem_b_stride);
+        const float4 x0 = xs[c], x1 = xs[nchunk + c];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int c = c0 + u * 32 + lane;
-      if (c < nchunk) {
-#pragma unroll
-        for (int b = 0; b < B; ++b) {
-          const float4* xs = reinterpret_cast<const float4*>(smem + b * smem_b_stride);
-          const float4 x0 = xs[c], x1 = xs[nchunk + c];
-#pragma unroll
-          for (int r = 0; r < R; ++r) {
-            float a = acc[r][b];
-            a = fmaf(bf16lo(w[u][r].x), x0.x, a); a = fmaf(bf16hi(w[u][r].x), x0.y, a);
-            a = fmaf(bf16lo(w[u][r].y), x0.z, a); a = fmaf(bf16hi(w[u][r].y), x0.w, a);
-            a = fmaf(bf16lo(w[u][r].z), x1.x, a); a = fmaf(bf16hi(w[u][r].z), x1.y, a);
-            a = fmaf(bf16lo(w[u][r].w), x1.z, a); a = fmaf(bf16hi(w[u][r].w), x1.w, a);
-            acc[r][b] = a;
-          }
+        for (int r = 0; r < R; ++r) {
+          const uint4 w = t.w[u][r];
+          float a = acc[r][b];
+          a = fmaf(bf16lo(w.x), x0.x, a); a = fmaf(bf16hi(w.x), x0.y, a);
+          a = fmaf(bf16lo(w.y), x0.z, a); a = fmaf(bf16hi(w.y), x0.w, a);
+          a = fmaf(bf16lo(w.z), x1.x, a); a = fmaf(bf16hi(w.z), x1.y, a);
+          a = fmaf(bf16lo(w.w), x1.z, a); a = fmaf(bf16hi(w.w), x1.w, a);
+          acc[r][b] = a;
         }
       }
     }
@@ -207,53 +220,78 @@ __device__ __forceinline__ void q4_word_fma(uint32_t w, const uint4& xu, __half2
   a1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), x[3], a1);
 }
 
-template <int R, int B>
-__device__ __forceinline__ void warp_dot(const RowQ4 (&rows)[R], const char* smem,
-                                         size_t smem_b_stride, int K, float (&acc)[R][B]) {
-  const int lane = threadIdx.x & 31;
-  const int nhg = K >> 5;  // half-groups of 32 k = one uint4 of packed weights
-  for (int h0 = 0; h0 < nhg; h0 += 64) {
-    uint4 w[2][R];
-    float sc[2][R], bi[2][R];
+template <int R>
+__device__ __forceinline__ void load_tile(const RowQ4 (&rows)[R], int K, int h0, Tile<RowQ4, R>& t) {
+  const int lane = threadIdx.x & 31, nhg = K >> 5;  // half-groups of 32 k = one uint4
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int hg = h0 + u * 32 + lane;
+  for (int u = 0; u < 2; ++u) {
+    const int hg = h0 + u * 32 + lane;
 #pragma unroll
-      for (int r = 0; r < R; ++r) {
-        if (hg < nhg) {
-          w[u][r] = ldg_stream(rows[r].w + (size_t(hg) << 2));
-          sc[u][r] = __bfloat162float(rows[r].scales[hg >> 1]);
-          bi[u][r] = __bfloat162float(rows[r].biases[hg >> 1]);
-        } else {
-          w[u][r] = make_uint4(0, 0, 0, 0); sc[u][r] = 0.f; bi[u][r] = 0.f;
-        }
+    for (int r = 0; r < R; ++r) {
+      if (hg < nhg) {
+        t.w[u][r] = ldg_stream(rows[r].w + (size_t(hg) << 2));
+        t.sc[u][r] = __bfloat162float(rows[r].scales[hg >> 1]);
+        t.bi[u][r] = __bfloat162float(rows[r].biases[hg >> 1]);
+      } else {
+        t.w[u][r] = make_uint4(0, 0, 0, 0); t.sc[u][r] = 0.f; t.bi[u][r] = 0.f;
       }
     }
+  }
+}
+
+template <int R, int B>
+__device__ __forceinline__ void fma_tile(const Tile<RowQ4, R>& t, int h0, const char* smem,
+                                         size_t smem_b_stride, int K, float (&acc)[R][B]) {
+  const int lane = threadIdx.x & 31, nhg = K >> 5;
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int hg = h0 + u * 32 + lane;
-      if (hg < nhg) {
+  for (int u = 0; u < 2; ++u) {
+    const int hg = h0 + u * 32 + lane;
+    if (hg < nhg) {
 #pragma unroll
-        for (int b = 0; b < B; ++b) {
-          const uint4* xh = reinterpret_cast<const uint4*>(smem + b * smem_b_stride);
-          const float xsum = reinterpret_cast<const float*>(smem + b * smem_b_stride +
-                                                            size_t(K) * 2)[hg];
-          const uint4 x0 = xh[hg], x1 = xh[nhg + hg], x2 = xh[2 * nhg + hg], x3 = xh[3 * nhg + hg];
+      for (int b = 0; b < B; ++b) {
+        const uint4* xh = reinterpret_cast<const uint4*>(smem + b * smem_b_stride);
+        const float xsum = reinterpret_cast<const float*>(smem + b * smem_b_stride +
+                                                          size_t(K) * 2)[hg];
+        const uint4 x0 = xh[hg], x1 = xh[nhg + hg], x2 = xh[2 * nhg + hg], x3 = xh[3 * nhg + hg];
 #pragma unroll
-          for (int r = 0; r < R; ++r) {
-            __half2 a0 = __float2half2_rn(0.f), a1 = a0;
-            q4_word_fma(w[u][r].x, x0, a0, a1);
-            q4_word_fma(w[u][r].y, x1, a0, a1);
-            q4_word_fma(w[u][r].z, x2, a0, a1);
-            q4_word_fma(w[u][r].w, x3, a0, a1);
-            const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
-            const float qx = (f0.x + f0.y) + (f1.x + f1.y);
-            acc[r][b] = fmaf(sc[u][r], qx, fmaf(bi[u][r], xsum, acc[r][b]));
-          }
+        for (int r = 0; r < R; ++r) {
+          __half2 a0 = __float2half2_rn(0.f), a1 = a0;
+          q4_word_fma(t.w[u][r].x, x0, a0, a1);
+          q4_word_fma(t.w[u][r].y, x1, a0, a1);
+          q4_word_fma(t.w[u][r].z, x2, a0, a1);
+          q4_word_fma(t.w[u][r].w, x3, a0, a1);
+          const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
+          const float qx = (f0.x + f0.y) + (f1.x + f1.y);
+          acc[r][b] = fmaf(t.sc[u][r], qx, fmaf(t.bi[u][r], xsum, acc[r][b]));
         }
       }
     }
   }
+}
+
+// Number of loop positions a row spans: chunks (bf16) or half-groups (Q4); a tile covers 64.
+__device__ __forceinline__ int row_units(const RowBf16&, int K) { return K >> 3; }
+__device__ __forceinline__ int row_units(const RowQ4&, int K) { return K >> 5; }
+
+// Whole-row dot product; `first` holds the already-loaded tile at position 0.
+template <int R, int B, class Row>
+__device__ __forceinline__ void warp_dot(const Row (&rows)[R], const char* smem,
+                                         size_t smem_b_stride, int K, float (&acc)[R][B],
+                                         const Tile<Row, R>& first) {
+  const int n = row_units(rows[0], K);
+  fma_tile<R, B>(first, 0, smem, smem_b_stride, K, acc);
+  for (int p = 64; p < n; p += 64) {
+    Tile<Row, R> t;
+    load_tile<R>(rows, K, p, t);
+    fma_tile<R, B>(t, p, smem, smem_b_stride, K, acc);
+  }
+}
+template <int R, int B, class Row>
+__device__ __forceinline__ void warp_dot(const Row (&rows)[R], const char* smem,
+                                         size_t smem_b_stride, int K, float (&acc)[R][B]) {
+  Tile<Row, R> t;
+  load_tile<R>(rows, K, 0, t);
+  warp_dot<R, B, Row>(rows, smem, smem_b_stride, K, acc, t);
 }
 
 // Row accessors for plain [N, K] matrices.

@@ -32,10 +32,16 @@ rms_gemv_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_stride,
   const size_t bstride = (XStage<WT>::bytes(K) + 15) & ~size_t(15);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // Weights do not depend on the previous kernel: pull the first rows toward L2 before waiting.
-  {
-    const int n0 = (blockIdx.x * kGemvWarps + warp) * kRowsPerWarp;
-    if (n0 < N) prefetch_l2(reinterpret_cast<const char*>(W.row(n0).w) + lane * 128);
+  // Weights depend neither on the previous kernel nor on the activations: issue the first tile's
+  // loads now, so their latency overlaps the wait and the staging below.
+  using Row = typename Matrix<WT>::Row;
+  int n0 = (blockIdx.x * kGemvWarps + warp) * kRowsPerWarp;
+  Row rows[kRowsPerWarp];
+  Tile<Row, kRowsPerWarp> t0;
+  if (n0 < N) {
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
+    load_tile<kRowsPerWarp>(rows, K, 0, t0);
   }
   pdl_wait();
 
@@ -47,17 +53,18 @@ rms_gemv_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_stride,
   }
   __syncthreads();
 
-  for (int n0 = (blockIdx.x * kGemvWarps + warp) * kRowsPerWarp; n0 < N;
-       n0 += gridDim.x * kGemvWarps * kRowsPerWarp) {
-    typename Matrix<WT>::Row rows[kRowsPerWarp];
+  for (bool first = true; n0 < N; n0 += gridDim.x * kGemvWarps * kRowsPerWarp, first = false) {
+    if (!first) {
 #pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
+      for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
+      load_tile<kRowsPerWarp>(rows, K, 0, t0);
+    }
     float acc[kRowsPerWarp][B];
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r)
 #pragma unroll
       for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
-    warp_dot<kRowsPerWarp, B>(rows, smem, bstride, K, acc);
+    warp_dot<kRowsPerWarp, B, Row>(rows, smem, bstride, K, acc, t0);
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r)
 #pragma unroll
@@ -88,9 +95,13 @@ rms_gate_up_swiglu_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int
   const int K = W.K;
   const size_t bstride = (XStage<WT>::bytes(K) + 15) & ~size_t(15);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  {
-    const int i0 = blockIdx.x * kGemvWarps + warp;
-    if (i0 < I) prefetch_l2(reinterpret_cast<const char*>(W.row(i0).w) + lane * 128);
+  using Row = typename Matrix<WT>::Row;
+  int i = blockIdx.x * kGemvWarps + warp;
+  Row rows[2];
+  Tile<Row, 2> t0;
+  if (i < I) {
+    rows[0] = W.row(i); rows[1] = W.row(size_t(I) + i);
+    load_tile<2>(rows, K, 0, t0);
   }
   pdl_wait();
 #pragma unroll
@@ -100,12 +111,15 @@ rms_gate_up_swiglu_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int
     if (threadIdx.x == 0) inv_rms[b] = norm_w ? rsqrtf(ssq / float(K) + eps) : 1.f;
   }
   __syncthreads();
-  for (int i = blockIdx.x * kGemvWarps + warp; i < I; i += gridDim.x * kGemvWarps) {
-    typename Matrix<WT>::Row rows[2] = {W.row(i), W.row(size_t(I) + i)};
+  for (bool first = true; i < I; i += gridDim.x * kGemvWarps, first = false) {
+    if (!first) {
+      rows[0] = W.row(i); rows[1] = W.row(size_t(I) + i);
+      load_tile<2>(rows, K, 0, t0);
+    }
     float acc[2][B];
 #pragma unroll
     for (int b = 0; b < B; ++b) acc[0][b] = acc[1][b] = 0.f;
-    warp_dot<2, B>(rows, smem, bstride, K, acc);
+    warp_dot<2, B, Row>(rows, smem, bstride, K, acc, t0);
 #pragma unroll
     for (int b = 0; b < B; ++b) {
       const float g = warp_sum(acc[0][b]) * inv_rms[b];
@@ -127,9 +141,14 @@ swiglu_down_kernel(Matrix<WT> W /*[N, I]*/, const __nv_bfloat16* __restrict__ ga
   const int I = W.K;
   const size_t bstride = (XStage<WT>::bytes(I) + 15) & ~size_t(15);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  {
-    const int n0 = (blockIdx.x * kGemvWarps + warp) * kRowsPerWarp;
-    if (n0 < N) prefetch_l2(reinterpret_cast<const char*>(W.row(n0).w) + lane * 128);
+  using Row = typename Matrix<WT>::Row;
+  int n0 = (blockIdx.x * kGemvWarps + warp) * kRowsPerWarp;
+  Row rows[kRowsPerWarp];
+  Tile<Row, kRowsPerWarp> t0;
+  if (n0 < N) {
+#pragma unroll
+    for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
+    load_tile<kRowsPerWarp>(rows, I, 0, t0);
   }
   pdl_wait();
 #pragma unroll
@@ -147,17 +166,18 @@ swiglu_down_kernel(Matrix<WT> W /*[N, I]*/, const __nv_bfloat16* __restrict__ ga
 #pragma unroll
   for (int b = 0; b < B; ++b) XStage<WT>::finish(smem + b * bstride, I);
   __syncthreads();
-  for (int n0 = (blockIdx.x * kGemvWarps + warp) * kRowsPerWarp; n0 < N;
-       n0 += gridDim.x * kGemvWarps * kRowsPerWarp) {
-    typename Matrix<WT>::Row rows[kRowsPerWarp];
+  for (bool first = true; n0 < N; n0 += gridDim.x * kGemvWarps * kRowsPerWarp, first = false) {
+    if (!first) {
 #pragma unroll
-    for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
+      for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
+      load_tile<kRowsPerWarp>(rows, I, 0, t0);
+    }
     float acc[kRowsPerWarp][B];
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r)
 #pragma unroll
       for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
-    warp_dot<kRowsPerWarp, B>(rows, smem, bstride, I, acc);
+    warp_dot<kRowsPerWarp, B, Row>(rows, smem, bstride, I, acc, t0);
 #pragma unroll
     for (int r = 0; r < kRowsPerWarp; ++r)
 #pragma unroll

@@ -79,31 +79,79 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ gate_w, const __nv_bfloat16*
                   const float* __restrict__ expert_bias, float* __restrict__ logits,
                   int* __restrict__ topk_idx, float* __restrict__ topk_w, int* __restrict__ counts,
                   unsigned int* __restrict__ ticket, int E, int K, int k) {
+  // One block per expert row; the eight warps split K, so every lane has all of its weight bytes
+  // in flight at once (a 4096-wide row is 2 x 16 bytes per lane) and the whole machine takes part.
   extern __shared__ __align__(16) char smem[];
   __shared__ float red[kGemvWarps];
   __shared__ float inv_rms[B];
+  __shared__ float part[kGemvWarps][B];
   __shared__ unsigned int last;
   const size_t bstride = (XStage<WBf16>::bytes(K) + 15) & ~size_t(15);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  pdl_wait();
+  const int nchunk = K >> 3;
+  const int per_warp = (nchunk + kGemvWarps - 1) / kGemvWarps;
+  for (int e = blockIdx.x; e < E; e += gridDim.x) {
+    const __nv_bfloat16* wrow = gate_w + size_t(e) * K;
+    // this warp's slice of the row: chunks [c_lo, c_hi)
+    const int c_lo = warp * per_warp, c_hi = min(nchunk, c_lo + per_warp);
+    uint4 wv[4];
 #pragma unroll
-  for (int b = 0; b < B; ++b) {
-    const float ssq = XStage<WBf16>::stage(smem + b * bstride, x + size_t(b) * x_stride, norm_w, K,
-                                           red, norm_w != nullptr);
-    if (threadIdx.x == 0) inv_rms[b] = norm_w ? rsqrtf(ssq / float(K) + eps) : 1.f;
-  }
-  __syncthreads();
-  for (int e = blockIdx.x * kGemvWarps + warp; e < E; e += gridDim.x * kGemvWarps) {
-    RowBf16 rows[1] = {RowBf16{gate_w + size_t(e) * K}};
-    float acc[1][B];
+    for (int u = 0; u < 4; ++u) {
+      const int c = c_lo + u * 32 + lane;
+      wv[u] = (c < c_hi) ? ldg_stream(wrow + (size_t(c) << 3)) : make_uint4(0, 0, 0, 0);
+    }
+    if (e == blockIdx.x) {
+      pdl_wait();
 #pragma unroll
-    for (int b = 0; b < B; ++b) acc[0][b] = 0.f;
-    warp_dot<1, B>(rows, smem, bstride, K, acc);
+      for (int b = 0; b < B; ++b) {
+        const float ssq = XStage<WBf16>::stage(smem + b * bstride, x + size_t(b) * x_stride, norm_w,
+                                               K, red, norm_w != nullptr);
+        if (threadIdx.x == 0) inv_rms[b] = norm_w ? rsqrtf(ssq / float(K) + eps) : 1.f;
+      }
+      __syncthreads();
+    }
+    float acc[B];
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[b] = 0.f;
+    for (int c0 = c_lo; c0 < c_hi; c0 += 128) {
+      if (c0 != c_lo) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = c0 + u * 32 + lane;
+          wv[u] = (c < c_hi) ? ldg_stream(wrow + (size_t(c) << 3)) : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = c0 + u * 32 + lane;
+        if (c < c_hi) {
+#pragma unroll
+          for (int b = 0; b < B; ++b) {
+            const float4* xs = reinterpret_cast<const float4*>(smem + b * bstride);
+            const float4 x0 = xs[c], x1 = xs[nchunk + c];
+            float a = acc[b];
+            a = fmaf(bf16lo(wv[u].x), x0.x, a); a = fmaf(bf16hi(wv[u].x), x0.y, a);
+            a = fmaf(bf16lo(wv[u].y), x0.z, a); a = fmaf(bf16hi(wv[u].y), x0.w, a);
+            a = fmaf(bf16lo(wv[u].z), x1.x, a); a = fmaf(bf16hi(wv[u].z), x1.y, a);
+            a = fmaf(bf16lo(wv[u].w), x1.z, a); a = fmaf(bf16hi(wv[u].w), x1.w, a);
+            acc[b] = a;
+          }
+        }
+      }
+    }
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      const float v = warp_sum(acc[0][b]);
-      if (lane == b) logits[size_t(b) * E + e] = v * inv_rms[b];
+      const float v = warp_sum(acc[b]);
+      if (lane == 0) part[warp][b] = v;
     }
+    __syncthreads();
+    if (threadIdx.x < B) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < kGemvWarps; ++w) v += part[w][threadIdx.x];
+      logits[size_t(threadIdx.x) * E + e] = v * inv_rms[threadIdx.x];
+    }
+    __syncthreads();
   }
   // Last block to arrive selects the experts for every token of this launch.
   __threadfence();
@@ -194,24 +242,31 @@ moe_gate_up_kernel(ExpertMatrix<WT> W /*rows = 2*I_full: gate then up*/,
   pdl_wait();
   const int e = topk_idx[pair] - expert_base;
   if (e < 0 || e >= experts_local) return;  // expert lives on another rank
+  using Row = typename ExpertMatrix<WT>::Row;
+  constexpr int R = 2 * kGuPairsPerWarp;
+  int i0 = (blockIdx.x * kGemvWarps + warp) * kGuPairsPerWarp;
+  Row rows[R];
+  Tile<Row, R> t0;
+  auto set_rows = [&](int base) {
+#pragma unroll
+    for (int j = 0; j < kGuPairsPerWarp; ++j) {
+      const int i = min(base + j, I - 1);
+      rows[2 * j] = W.row(e, i);
+      rows[2 * j + 1] = W.row(e, size_t(I) + i);
+    }
+  };
+  if (i0 < I) { set_rows(i0); load_tile<R>(rows, K, 0, t0); }  // in flight during the staging
   const float ssq = XStage<WT>::stage(smem, x + size_t(b) * x_stride, norm_w, K, red,
                                       norm_w != nullptr);
   if (threadIdx.x == 0) inv_rms_s = norm_w ? rsqrtf(ssq / float(K) + eps) : 1.f;
   __syncthreads();
   const float inv_rms = inv_rms_s;
-  for (int i0 = (blockIdx.x * kGemvWarps + warp) * kGuPairsPerWarp; i0 < I;
-       i0 += gridDim.x * kGemvWarps * kGuPairsPerWarp) {
-    typename ExpertMatrix<WT>::Row rows[2 * kGuPairsPerWarp];
+  for (bool first = true; i0 < I; i0 += gridDim.x * kGemvWarps * kGuPairsPerWarp, first = false) {
+    if (!first) { set_rows(i0); load_tile<R>(rows, K, 0, t0); }
+    float acc[R][1];
 #pragma unroll
-    for (int j = 0; j < kGuPairsPerWarp; ++j) {
-      const int i = min(i0 + j, I - 1);
-      rows[2 * j] = W.row(e, i);
-      rows[2 * j + 1] = W.row(e, size_t(I) + i);
-    }
-    float acc[2 * kGuPairsPerWarp][1];
-#pragma unroll
-    for (int j = 0; j < 2 * kGuPairsPerWarp; ++j) acc[j][0] = 0.f;
-    warp_dot<2 * kGuPairsPerWarp, 1>(rows, smem, 0, K, acc);
+    for (int j = 0; j < R; ++j) acc[j][0] = 0.f;
+    warp_dot<R, 1, Row>(rows, smem, 0, K, acc, t0);
 #pragma unroll
     for (int j = 0; j < kGuPairsPerWarp; ++j) {
       const float g = warp_sum(acc[2 * j][0]) * inv_rms;
@@ -247,30 +302,60 @@ moe_down_kernel(ExpertMatrix<WT> W /*rows = N, K = I*/, const __nv_bfloat16* __r
     s_w[threadIdx.x] = local ? topk_w[b * top_k + threadIdx.x] : 0.f;
   }
   __syncthreads();
+  using Row = typename ExpertMatrix<WT>::Row;
+  constexpr int R = kRowsPerWarpDown;
+  auto next_local = [&](int s) { while (s < top_k && s_e[s] < 0) ++s; return s; };
+  int n0 = (blockIdx.x * kGemvWarps + warp) * R;
+  const int s_first = next_local(0);
+  Row rows[R];
+  Tile<Row, R> cur;
+  if (n0 < N && s_first < top_k) {  // first slot's weights fly while the activations are staged
+#pragma unroll
+    for (int r = 0; r < R; ++r) rows[r] = W.row(s_e[s_first], min(n0 + r, N - 1));
+    load_tile<R>(rows, I, 0, cur);
+  }
   for (int s = 0; s < top_k; ++s) {
     if (s_e[s] >= 0)
       XStage<WT>::stage(smem + s * bstride, act + size_t(b * top_k + s) * act_stride, nullptr, I,
                         nullptr, false);
   }
   __syncthreads();
-  for (int n0 = (blockIdx.x * kGemvWarps + warp) * kRowsPerWarpDown; n0 < N;
-       n0 += gridDim.x * kGemvWarps * kRowsPerWarpDown) {
-    float tot[kRowsPerWarpDown];
+  const int units = row_units(rows[0], I);
+  for (bool first = true; n0 < N; n0 += gridDim.x * kGemvWarps * R, first = false) {
+    float tot[R];
 #pragma unroll
-    for (int r = 0; r < kRowsPerWarpDown; ++r) tot[r] = 0.f;
-    for (int s = 0; s < top_k; ++s) {
-      const int e = s_e[s];
-      if (e < 0) continue;
-      typename ExpertMatrix<WT>::Row rows[kRowsPerWarpDown];
+    for (int r = 0; r < R; ++r) tot[r] = 0.f;
+    int s = s_first;
+    if (!first && s < top_k) {
 #pragma unroll
-      for (int r = 0; r < kRowsPerWarpDown; ++r) rows[r] = W.row(e, min(n0 + r, N - 1));
-      float acc[kRowsPerWarpDown][1];
+      for (int r = 0; r < R; ++r) rows[r] = W.row(s_e[s], min(n0 + r, N - 1));
+      load_tile<R>(rows, I, 0, cur);
+    }
+    while (s < top_k) {
+      // software pipeline over the slots: the next expert's first tile is requested before the
+      // current one is consumed
+      const int sn = next_local(s + 1);
+      Row rows_n[R];
+      Tile<Row, R> nxt;
+      if (sn < top_k) {
 #pragma unroll
-      for (int r = 0; r < kRowsPerWarpDown; ++r) acc[r][0] = 0.f;
-      warp_dot<kRowsPerWarpDown, 1>(rows, smem + s * bstride, 0, I, acc);
+        for (int r = 0; r < R; ++r) rows_n[r] = W.row(s_e[sn], min(n0 + r, N - 1));
+        load_tile<R>(rows_n, I, 0, nxt);
+      }
+      float acc[R][1];
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r][0] = 0.f;
+      if (units <= 64) fma_tile<R, 1>(cur, 0, smem + s * bstride, 0, I, acc);
+      else warp_dot<R, 1, Row>(rows, smem + s * bstride, 0, I, acc, cur);
       const float w = s_w[s];
 #pragma unroll
-      for (int r = 0; r < kRowsPerWarpDown; ++r) tot[r] = fmaf(w, acc[r][0], tot[r]);
+      for (int r = 0; r < R; ++r) tot[r] = fmaf(w, acc[r][0], tot[r]);
+      if (sn < top_k) {
+        cur = nxt;
+#pragma unroll
+        for (int r = 0; r < R; ++r) rows[r] = rows_n[r];
+      }
+      s = sn;
     }
 #pragma unroll
     for (int r = 0; r < kRowsPerWarpDown; ++r) {
@@ -310,7 +395,7 @@ static int launch_moe_gate_up(const void* w, const void* sc, const void* bi, con
   const size_t smem = (XStage<WT>::bytes(K) + 15) & ~size_t(15);
   auto kern = moe_gate_up_kernel<WT>;
   RB_CHECK(set_max_smem(kern, smem));
-  int gx = (I + kGemvWarps * kGuPairsPerWarp * 2 - 1) / (kGemvWarps * kGuPairsPerWarp * 2);
+  int gx = (I + kGemvWarps * kGuPairsPerWarp - 1) / (kGemvWarps * kGuPairsPerWarp);
   if (gx < 1) gx = 1;
   return launch(kern, dim3(gx, B * top_k), dim3(kGemvThreads), smem, st, pdl != 0,
                 make_expert_matrix<WT>(w, sc, bi, 2 * I, K), static_cast<const __nv_bfloat16*>(x),
@@ -347,7 +432,7 @@ extern "C" int rmlx_moe_router(const void* gate_w, const void* x, int x_stride, 
                                int k, int pdl, cudaStream_t st) {
   if (E > kMaxExperts || k > kMaxTopK || k > E || K % 8 || B < 1 || B > 4) return -2;
   const size_t bstride = (XStage<WBf16>::bytes(K) + 15) & ~size_t(15);
-  int grid = (E + kGemvWarps - 1) / kGemvWarps;
+  int grid = E;
 #define RB_ROUTER(BB)                                                                            \
   {                                                                                              \
     auto kern = moe_router_kernel<BB>;                                                           \

@@ -250,21 +250,45 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
   __syncthreads();
   if (!s_last) return;
   __threadfence();
+  // Per-split weights exp2(m_s - M) / L for the 16 rows go to shared memory first (one parallel
+  // pass over the small (max, sum) table); the big pass over the partial outputs then has no
+  // dependent loads and runs eight splits at a time.
+  float* wgt = reinterpret_cast<float*>(smem);        // [S][16]
+  float* mls = wgt + kFdMaxSplits * 16;               // [S][16][2] copy of the (max, sum) table
+  __syncthreads();
+  for (int i = threadIdx.x; i < p.S * 32; i += kFdThreads) mls[i] = p.part_ml[tile * p.S * 32 + i];
+  __syncthreads();
+  if (threadIdx.x < 16) {
+    const int row = threadIdx.x;
+    float M = -INFINITY;
+    for (int s = 0; s < p.S; ++s) M = fmaxf(M, mls[s * 32 + row * 2]);
+    float L = 0.f;
+    for (int s = 0; s < p.S; ++s) {
+      const float ms = mls[s * 32 + row * 2];
+      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+      wgt[s * 16 + row] = f;
+      L += mls[s * 32 + row * 2 + 1] * f;
+    }
+    const float invL = L > 0.f ? 1.f / L : 0.f;
+    for (int s = 0; s < p.S; ++s) wgt[s * 16 + row] *= invL;
+  }
+  __syncthreads();
+  const float* po = p.part_o + tile * p.S * 16 * HD;
   for (int idx = threadIdx.x; idx < 16 * HD; idx += kFdThreads) {
     const int row = idx / HD, d = idx % HD;
     const int h = gt * 16 + row;
     if (h >= p.G) continue;
-    float M = -INFINITY;
-    for (int s = 0; s < p.S; ++s) M = fmaxf(M, p.part_ml[((tile * p.S + s) * 16 + row) * 2]);
-    float L = 0.f, acc = 0.f;
-    for (int s = 0; s < p.S; ++s) {
-      const float ms = p.part_ml[((tile * p.S + s) * 16 + row) * 2];
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-      L += p.part_ml[((tile * p.S + s) * 16 + row) * 2 + 1] * f;
-      acc += p.part_o[((tile * p.S + s) * 16 + row) * HD + d] * f;
+    float acc = 0.f;
+    int s = 0;
+    for (; s + 8 <= p.S; s += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = po[(size_t(s + j) * 16 + row) * HD + d];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc = fmaf(v[j], wgt[(s + j) * 16 + row], acc);
     }
-    p.out[(size_t(b) * p.Hq + size_t(kvh) * p.G + h) * HD + d] =
-        __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+    for (; s < p.S; ++s) acc = fmaf(po[(size_t(s) * 16 + row) * HD + d], wgt[s * 16 + row], acc);
+    p.out[(size_t(b) * p.Hq + size_t(kvh) * p.G + h) * HD + d] = __float2bfloat16_rn(acc);
   }
   if (threadIdx.x == 0) p.tickets[tile] = 0u;
   pdl_launch_dependents();

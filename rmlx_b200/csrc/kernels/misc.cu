@@ -62,16 +62,20 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
   pdl_launch_dependents();
 }
 
-// One block per row: index of the maximum (lowest index on ties).
+// Index of the row maximum (lowest index on ties). grid = (slices, rows): every block reduces its
+// slice to one 64-bit key (order-preserving float bits, then inverted index), merges it with
+// atomicMax, and the last block of a row decodes the winner and clears the scratch for the next
+// launch. keys[rows] and tickets[rows] must be zero on first use.
 __global__ void __launch_bounds__(1024)
-argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int stride) {
+argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, int stride,
+              unsigned long long* __restrict__ keys, unsigned int* __restrict__ tickets) {
   __shared__ float sv[32];
   __shared__ int si[32];
   pdl_wait();
-  const float* row = logits + size_t(blockIdx.x) * stride;
+  const float* row = logits + size_t(blockIdx.y) * stride;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += 1024) {
+  for (int i = blockIdx.x * 1024 + threadIdx.x; i < V; i += gridDim.x * 1024) {
     const float v = row[i];
     if (v > best) { best = v; bi = i; }
   }
@@ -91,7 +95,20 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, in
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
       if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
     }
-    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+    if (threadIdx.x == 0) {
+      uint32_t u = __float_as_uint(best);
+      u ^= (u >> 31) ? 0xffffffffu : 0x80000000u;          // monotone map float -> uint
+      const unsigned long long key =
+          (static_cast<unsigned long long>(u) << 32) | (0xffffffffu - static_cast<uint32_t>(bi));
+      atomicMax(keys + blockIdx.y, key);
+      __threadfence();
+      if (atomicAdd(tickets + blockIdx.y, 1u) == gridDim.x - 1) {
+        __threadfence();
+        const unsigned long long k = atomicExch(keys + blockIdx.y, 0ull);
+        out[blockIdx.y] = static_cast<int>(0xffffffffu - static_cast<uint32_t>(k & 0xffffffffull));
+        tickets[blockIdx.y] = 0u;
+      }
+    }
   }
   pdl_launch_dependents();
 }
@@ -189,10 +206,14 @@ extern "C" int rmlx_rms_norm(const void* x, const void* residual, const void* w,
                 static_cast<__nv_bfloat16*>(sum_out), D, eps);
 }
 
-extern "C" int rmlx_argmax(const float* logits, int* out, int B, int V, int stride, int pdl,
+extern "C" int rmlx_argmax(const float* logits, int* out, int B, int V, int stride,
+                           unsigned long long* keys, unsigned int* tickets, int pdl,
                            cudaStream_t st) {
-  if (B < 1 || V < 1) return -2;
-  return launch(argmax_kernel, dim3(B), dim3(1024), 0, st, pdl != 0, logits, out, V, stride);
+  if (B < 1 || V < 1 || !keys || !tickets) return -2;
+  int slices = (V + 4095) / 4096;
+  if (slices > 64) slices = 64;
+  return launch(argmax_kernel, dim3(slices, B), dim3(1024), 0, st, pdl != 0, logits, out, V, stride,
+                keys, tickets);
 }
 
 extern "C" int rmlx_silu_mul(const void* gate_up, void* act, long long T, int I, cudaStream_t st) {

@@ -76,6 +76,7 @@ class CachedDecode:
         dense_i = [l.w_gate_up.n // 2 for l in model.w.layers if l.w_gate_up is not None]
         if dense_i:
             self.dense_act = torch.zeros(B, max(dense_i), **bf)
+        self.argmax_scratch = D.ArgmaxScratch(B, dev)
         self.seq_ids: List[int] = []
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._launches_per_step = 0
@@ -158,7 +159,7 @@ class CachedDecode:
         else:
             D.rms_gemv(h, w.lm_head, w.final_norm, eps, out=self.logits, pdl=pdl)
         if self.greedy:
-            D.argmax(self.logits, out=self.next_tokens, pdl=pdl)
+            D.argmax(self.logits, out=self.next_tokens, scratch=self.argmax_scratch, pdl=pdl)
             rc = _lib.cuda().rmlx_decode_advance(self.next_tokens.data_ptr(), self.tokens.data_ptr(),
                                                  self.positions.data_ptr(), self.seq_lens.data_ptr(),
                                                  self.active.data_ptr(), self.B, int(pdl),

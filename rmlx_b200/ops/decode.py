@@ -189,11 +189,11 @@ class FlashDecodeScratch:
 
 
 def default_splits(batch: int, hkv: int, gtiles: int, max_len: int, sm_count: int = 148) -> int:
-    """Enough KV splits to give every SM a block, capped so a split keeps >= 4 pages."""
+    """About one block per SM, capped so a split keeps at least 8 pages (two per warp)."""
     tiles = max(1, batch * hkv * gtiles)
-    want = max(1, (2 * sm_count + tiles - 1) // tiles)
-    cap = max(1, max_len // 64)
-    return int(min(64, want, cap))
+    want = max(1, (sm_count + tiles - 1) // tiles)
+    cap = max(1, max_len // 128)
+    return int(min(32, want, cap))
 
 
 def flash_decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -293,14 +293,24 @@ def rms_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float,
     return out.view(x.shape)
 
 
-def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None, pdl: bool = False
-           ) -> torch.Tensor:
+class ArgmaxScratch:
+    """Zeroed merge keys and tickets for the multi-block arg-max (left zero by every launch)."""
+
+    def __init__(self, rows: int, device):
+        self.keys = torch.zeros(rows, dtype=torch.int64, device=device)
+        self.tickets = torch.zeros(rows, dtype=torch.int32, device=device)
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None,
+           scratch: Optional[ArgmaxScratch] = None, pdl: bool = False) -> torch.Tensor:
     _lib.require_cuda_tensor(logits)
     assert logits.dtype == torch.float32 and logits.dim() == 2
     if out is None:
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    scratch = scratch or ArgmaxScratch(logits.shape[0], logits.device)
     rc = _lib.cuda().rmlx_argmax(logits.data_ptr(), out.data_ptr(), logits.shape[0], logits.shape[1],
-                                 logits.stride(0), int(pdl), _lib.stream_ptr())
+                                 logits.stride(0), scratch.keys.data_ptr(),
+                                 scratch.tickets.data_ptr(), int(pdl), _lib.stream_ptr())
     _lib.check(rc, "argmax")
     return out
 

@@ -49,6 +49,9 @@ def _oracle_from(gpu_weights_model: TransformerModel) -> TransformerModel:
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_decode_matches_oracle(dev, cfg_fn, quant, use_graph):
     cfg = cfg_fn()
+    if quant == "q4" and cfg.ff_type.kind == "gated":
+        # group-64 quantisation needs the FFN width to be a multiple of 64 (688 is not)
+        cfg = cfg.replace(ff_type=FeedForwardType.gated(704))
     sd = random_state_dict(cfg, 0)
     model = TransformerModel(from_state_dict(cfg, sd, device=dev, quant=quant))
     oracle = _oracle_from(model)
