@@ -44,6 +44,13 @@ _CUDA_SIGS: Dict[str, tuple] = {
     "rmlx_embedding": ("pppiiiip", "i"),
     "rmlx_rms_norm": ("pppppiifip", "i"),
     "rmlx_argmax": ("ppiiippip", "i"),
+    "rmlx_qmv_mma_max_batch": ("", "i"),
+    "rmlx_qmv_status": ("", "i"),
+    "rmlx_qmv_mma_supported": ("iii", "i"),
+    "rmlx_moe_down_q4_mma_supported": ("ii", "i"),
+    "rmlx_rms_qmv_mma": ("ppppipfpipiiiiiip", "i"),
+    "rmlx_moe_gate_up_q4_mma": ("ppppipfppiiiiiiiip", "i"),
+    "rmlx_moe_down_q4_mma": ("ppppipppipiiiiiiiiip", "i"),
     "rmlx_gemm_pick_bn": ("ii", "i"),
     "rmlx_gemm_bf16": ("ppppiiiiiiipip", "i"),
     "rmlx_silu_mul": ("ppqip", "i"),

@@ -30,7 +30,8 @@ inline int sm_count() {
 // setting it again is cheap and legal during stream capture (it is not a stream operation).
 template <class Kern>
 inline cudaError_t set_max_smem(Kern kern, size_t bytes) {
-  if (bytes <= 48 * 1024) return cudaSuccess;
+  // the 48 KB default limit counts static shared memory too: opt in well below it
+  if (bytes <= 24 * 1024) return cudaSuccess;
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               static_cast<int>(bytes));
 }
@@ -51,6 +52,7 @@ inline int launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cu
     cfg.numAttrs = 1;
   }
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+  if (e != cudaSuccess) (void)cudaGetLastError();  // do not leave a stale launch error behind
   return static_cast<int>(e);
 }
 

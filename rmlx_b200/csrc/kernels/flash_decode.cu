@@ -66,15 +66,15 @@ struct FdParams {
   float scale_log2;              // softmax scale * log2(e)
 };
 
-template <int HD>
+template <int HD, int NST>
 __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
   constexpr int CH = HD / 8;             // 16-byte chunks per row
   constexpr int KS = HD / 16;            // k-steps of the QK^T product
   constexpr int NT = HD / 8;             // n-tiles of the PV product
   constexpr int PAGE_BYTES = kPage * HD * 2;
   extern __shared__ __align__(128) char smem[];
-  // per warp: 2 stages x (K page, V page); reused afterwards for the cross-warp merge
-  char* wsm = smem + (threadIdx.x >> 5) * (4 * PAGE_BYTES);
+  // per warp: NST stages x (K page, V page); reused afterwards for the cross-warp merge
+  char* wsm = smem + (threadIdx.x >> 5) * (NST * 2 * PAGE_BYTES);
   __shared__ float s_m[kFdWarps][16], s_l[kFdWarps][16];
   __shared__ unsigned int s_last;
 
@@ -133,15 +133,17 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
     }
   };
 
+  // Ring of NST stages per warp: the first NST pages are requested up front, so their DRAM
+  // latencies overlap instead of adding up; a stage is refilled as soon as it has been consumed.
   int pg = pg0 + warp;
-  if (pg < pg1) issue(pg, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int s = 0; s < NST; ++s) {
+    if (pg + s * kFdWarps < pg1) issue(pg + s * kFdWarps, s);
+    cp_async_commit();
+  }
   int stage = 0;
   for (; pg < pg1; pg += kFdWarps) {
-    const int nxt = pg + kFdWarps;
-    if (nxt < pg1) issue(nxt, stage ^ 1);
-    cp_async_commit();
-    cp_async_wait<1>();
+    cp_async_wait<NST - 1>();
     __syncwarp();
     const uint32_t kbase = smem_u32(wsm + stage * 2 * PAGE_BYTES);
     const uint32_t vbase = kbase + PAGE_BYTES;
@@ -197,7 +199,9 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
       mma_bf16_16816(o[j + 1], pa, vb[2], vb[3]);
     }
     __syncwarp();
-    stage ^= 1;
+    if (pg + NST * kFdWarps < pg1) issue(pg + NST * kFdWarps, stage);
+    cp_async_commit();
+    stage = (stage + 1 == NST) ? 0 : stage + 1;
   }
   cp_async_wait<0>();
   // row sums live in the quad: finish them
@@ -273,22 +277,31 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
     for (int s = 0; s < p.S; ++s) wgt[s * 16 + row] *= invL;
   }
   __syncthreads();
-  const float* po = p.part_o + tile * p.S * 16 * HD;
-  for (int idx = threadIdx.x; idx < 16 * HD; idx += kFdThreads) {
-    const int row = idx / HD, d = idx % HD;
+  // Each thread owns four consecutive d of one row at a time and keeps sixteen 16-byte loads in
+  // flight: the partials sit in L2, so the merge is a latency problem, not a bandwidth one.
+  const float4* po4 = reinterpret_cast<const float4*>(p.part_o + tile * p.S * 16 * HD);
+  constexpr int D4 = HD / 4;
+  for (int idx = threadIdx.x; idx < 16 * D4; idx += kFdThreads) {
+    const int row = idx / D4, d4 = idx % D4;
     const int h = gt * 16 + row;
     if (h >= p.G) continue;
-    float acc = 0.f;
-    int s = 0;
-    for (; s + 8 <= p.S; s += 8) {
-      float v[8];
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < p.S; s += 16) {
+      float4 v[16];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = po[(size_t(s + j) * 16 + row) * HD + d];
+      for (int j = 0; j < 16; ++j)
+        v[j] = (s + j < p.S) ? po4[(size_t(s + j) * 16 + row) * D4 + d4] : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) acc = fmaf(v[j], wgt[(s + j) * 16 + row], acc);
+      for (int j = 0; j < 16; ++j) {
+        const float w = (s + j < p.S) ? wgt[(s + j) * 16 + row] : 0.f;
+        acc.x = fmaf(v[j].x, w, acc.x); acc.y = fmaf(v[j].y, w, acc.y);
+        acc.z = fmaf(v[j].z, w, acc.z); acc.w = fmaf(v[j].w, w, acc.w);
+      }
     }
-    for (; s < p.S; ++s) acc = fmaf(po[(size_t(s) * 16 + row) * HD + d], wgt[s * 16 + row], acc);
-    p.out[(size_t(b) * p.Hq + size_t(kvh) * p.G + h) * HD + d] = __float2bfloat16_rn(acc);
+    uint2 o;
+    o.x = pack_bf16(acc.x, acc.y);
+    o.y = pack_bf16(acc.z, acc.w);
+    *reinterpret_cast<uint2*>(p.out + (size_t(b) * p.Hq + size_t(kvh) * p.G + h) * HD + d4 * 4) = o;
   }
   if (threadIdx.x == 0) p.tickets[tile] = 0u;
   pdl_launch_dependents();
@@ -331,16 +344,19 @@ extern "C" int rmlx_flash_decode_paged(const void* q, const void* k_cache, const
   p.gtiles = rmlx_flash_decode_gtiles(Hq, Hkv); p.S = splits; p.window = window;
   p.scale_log2 = scale * 1.4426950408889634f;
   dim3 grid(splits, Hkv * p.gtiles, B);
-  if (HD == 128) {
-    const size_t smem = size_t(kFdWarps) * 4 * kPage * 128 * 2;  // 64 KB >= merge area 32 KB
-    auto kern = flash_decode_kernel<128>;
-    RB_CHECK(set_max_smem(kern, smem));
-    return launch(kern, grid, dim3(kFdThreads), smem, st, pdl != 0, p);
-  } else if (HD == 64) {
-    const size_t smem = size_t(kFdWarps) * 4 * kPage * 64 * 2;   // 32 KB >= merge area 16 KB
-    auto kern = flash_decode_kernel<64>;
-    RB_CHECK(set_max_smem(kern, smem));
-    return launch(kern, grid, dim3(kFdThreads), smem, st, pdl != 0, p);
+  // Few blocks (small batch): deep per-warp ring, one block per SM. Many blocks: shallow ring so
+  // several blocks share an SM. Either way the staging area (>= 32 KB at HD 128, 16 KB at HD 64)
+  // covers the cross-warp merge buffer and the split-merge tables.
+  const bool deep = size_t(splits) * Hkv * p.gtiles * B <= size_t(2 * sm_count());
+#define RB_FD(HD_, NST_)                                                          \
+  {                                                                               \
+    const size_t smem = size_t(kFdWarps) * NST_ * 2 * kPage * HD_ * 2;            \
+    auto kern = flash_decode_kernel<HD_, NST_>;                                   \
+    RB_CHECK(set_max_smem(kern, smem));                                           \
+    return launch(kern, grid, dim3(kFdThreads), smem, st, pdl != 0, p);           \
   }
+  if (HD == 128) { if (deep) RB_FD(128, 4) else RB_FD(128, 2) }
+  if (HD == 64) { if (deep) RB_FD(64, 4) else RB_FD(64, 2) }
+#undef RB_FD
   return -2;
 }

@@ -8,6 +8,7 @@ Batches larger than the kernels' activation-tile limit are processed in chunks.
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -16,6 +17,20 @@ from .. import _lib
 from .weights import LinearWeight, W_Q4
 
 _MAXB = 4
+_Q4_PATH = os.environ.get("RMLX_Q4_PATH", "auto")
+
+
+def q4_path() -> str:
+    """Which Q4 mat-vec implementation runs: 'mma' (bulk-copy-fed tensor-core path), 'scalar'
+    (fp16 FMA path) or 'auto' (per kernel, whichever measured faster on B200: tensor-core path for
+    the expert gate/up projection, scalar path elsewhere)."""
+    return _Q4_PATH
+
+
+def set_q4_path(path: str) -> None:
+    global _Q4_PATH
+    assert path in ("auto", "mma", "scalar")
+    _Q4_PATH = path
 
 
 def _wargs(w: LinearWeight):
@@ -35,6 +50,18 @@ def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = 
     if out is None:
         out = torch.empty(b, n, dtype=out_dtype, device=x.device)
     lib, st = _lib.cuda(), _lib.stream_ptr()
+    if w.kind == W_Q4 and q4_path() == "mma" and lib.rmlx_qmv_mma_supported(k, min(8, b), 16):
+        for b0 in range(0, b, 8):
+            bb = min(8, b - b0)
+            xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
+            rs = None if residual is None else residual[b0:b0 + bb]
+            rc = lib.rmlx_rms_qmv_mma(w.w.data_ptr(), w.scales.data_ptr(), w.biases.data_ptr(),
+                                      xs.data_ptr(), xs.stride(0), _lib.ptr(norm_w), eps,
+                                      _lib.ptr(rs), 0 if rs is None else rs.stride(0),
+                                      os_.data_ptr(), os_.stride(0),
+                                      int(out.dtype == torch.float32), bb, n, k, int(pdl), st)
+            _lib.check(rc, "rms_qmv_mma")
+        return out
     for b0 in range(0, b, _MAXB):
         bb = min(_MAXB, b - b0)
         xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
@@ -149,6 +176,13 @@ def moe_gate_up(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor]
     i = w.n // 2
     if out is None:
         out = torch.zeros(b * top_k, i, dtype=torch.bfloat16, device=x.device)
+    if w.kind == W_Q4 and q4_path() in ("mma", "auto") and _lib.cuda().rmlx_qmv_mma_supported(k, 1, 32):
+        rc = _lib.cuda().rmlx_moe_gate_up_q4_mma(
+            w.w.data_ptr(), w.scales.data_ptr(), w.biases.data_ptr(), x.data_ptr(), x.stride(0),
+            _lib.ptr(norm_w), eps, idx.data_ptr(), out.data_ptr(), out.stride(0), b, top_k, i, k,
+            expert_base, w.experts, int(pdl), _lib.stream_ptr())
+        _lib.check(rc, "moe_gate_up_q4_mma")
+        return out
     rc = _lib.cuda().rmlx_moe_gate_up(*_wargs(w), x.data_ptr(), x.stride(0), _lib.ptr(norm_w), eps,
                                       idx.data_ptr(), out.data_ptr(), out.stride(0), b, top_k, i, k,
                                       expert_base, w.experts, int(pdl), _lib.stream_ptr())
@@ -165,6 +199,15 @@ def moe_down(act: torch.Tensor, w: LinearWeight, idx: torch.Tensor, wts: torch.T
     n, i = w.n, w.k
     if out is None:
         out = torch.empty(b, n, dtype=out_dtype, device=act.device)
+    if w.kind == W_Q4 and q4_path() == "mma" and _lib.cuda().rmlx_moe_down_q4_mma_supported(i, top_k):
+        rc = _lib.cuda().rmlx_moe_down_q4_mma(
+            w.w.data_ptr(), w.scales.data_ptr(), w.biases.data_ptr(), act.data_ptr(), act.stride(0),
+            idx.data_ptr(), wts.data_ptr(), _lib.ptr(residual),
+            0 if residual is None else residual.stride(0), out.data_ptr(), out.stride(0),
+            int(out.dtype == torch.float32), b, top_k, n, i, expert_base, w.experts, int(pdl),
+            _lib.stream_ptr())
+        _lib.check(rc, "moe_down_q4_mma")
+        return out
     rc = _lib.cuda().rmlx_moe_down(*_wargs(w), act.data_ptr(), act.stride(0), idx.data_ptr(),
                                    wts.data_ptr(), _lib.ptr(residual),
                                    0 if residual is None else residual.stride(0), out.data_ptr(),
@@ -193,7 +236,7 @@ def default_splits(batch: int, hkv: int, gtiles: int, max_len: int, sm_count: in
     tiles = max(1, batch * hkv * gtiles)
     want = max(1, (sm_count + tiles - 1) // tiles)
     cap = max(1, max_len // 128)
-    return int(min(32, want, cap))
+    return int(min(16, want, cap))
 
 
 def flash_decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,

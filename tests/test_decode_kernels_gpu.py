@@ -13,6 +13,14 @@ from rmlx_b200.reference import ops as ref
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(autouse=True, params=["mma", "scalar"])
+def q4_path(request):
+    """Every test runs with both Q4 mat-vec implementations."""
+    D.set_q4_path(request.param)
+    yield request.param
+    D.set_q4_path("mma")
+
+
 def _w(n, k, quant, dev, experts=0, seed=0):
     g = torch.Generator().manual_seed(seed)
     shape = (experts, n, k) if experts else (n, k)
@@ -29,7 +37,7 @@ def _close(a, b, atol=2e-2):
 
 
 @pytest.mark.parametrize("quant", [None, "q4"])
-@pytest.mark.parametrize("b,n,k", [(1, 1024, 4096), (3, 72 * 128 // 8, 1024), (4, 130, 512), (6, 256, 2048)])
+@pytest.mark.parametrize("b,n,k", [(1, 1024, 4096), (3, 72 * 128 // 8, 1024), (4, 130, 512), (6, 256, 2048), (8, 20000, 256), (1, 50, 192)])
 def test_rms_gemv(dev, quant, b, n, k):
     torch.manual_seed(1)
     w = _w(n, k, quant, dev)
@@ -105,7 +113,8 @@ def test_topk_route_exact(dev):
 @pytest.mark.parametrize("b", [1, 3])
 def test_moe_gate_up_down(dev, quant, b):
     torch.manual_seed(7)
-    e, d, i, topk = 16, 1024, 320 if quant is None else 384, 4
+    # Q4: 512 takes the bulk-copy tensor-core path (needs a multiple of 512); bf16: any multiple of 8
+    e, d, i, topk = 16, 1024, 320 if quant is None else 512, 4
     wgu = _w(2 * i, d, quant, dev, experts=e, seed=8)
     wdn = _w(d, i, quant, dev, experts=e, seed=9)
     x = torch.randn(b, d, device=dev).to(torch.bfloat16)
