@@ -129,6 +129,17 @@ class LinearWeight:
                             None if self.biases is None else self.biases[lo:hi].contiguous())
 
     @staticmethod
+    def stack(parts: list) -> "LinearWeight":
+        """Stack per-expert [N, K] weights into [E, N, K]."""
+        kind = parts[0].kind
+        assert all(p.kind == kind for p in parts)
+        w = torch.stack([p.w for p in parts], 0).contiguous()
+        if kind == W_BF16:
+            return LinearWeight(kind, w)
+        return LinearWeight(kind, w, torch.stack([p.scales for p in parts], 0).contiguous(),
+                            torch.stack([p.biases for p in parts], 0).contiguous())
+
+    @staticmethod
     def cat_rows(parts: list) -> "LinearWeight":
         """Concatenate along N (merged QKV / gate_up weights, crates/rmlx-nn/src/attention.rs:3590)."""
         kind = parts[0].kind

@@ -1,0 +1,107 @@
+"""Scheduler, sampler, prefix cache and the serving loop on CPU (the logic tests of
+crates/rmlx-nn/src/scheduler.rs, sampler.rs:543-640 and prefix_cache.rs)."""
+import torch
+
+from rmlx_b200.config import SamplerConfig, SchedulerConfig, tiny_dense_config
+from rmlx_b200.kv.paged import BlockManager, OutOfBlocks
+from rmlx_b200.models.transformer import TransformerModel
+from rmlx_b200.models.weights import from_state_dict, random_state_dict
+from rmlx_b200.serve.engine import ServingEngine
+from rmlx_b200.serve.prefix_cache import PrefixCache
+from rmlx_b200.serve.sampler import Sampler
+from rmlx_b200.serve.scheduler import GenerationRequest, Scheduler
+
+
+def test_block_manager_cow_fork_trim():
+    bm = BlockManager(8, 4)
+    bm.reserve(1, 6); bm.commit(1, 6)
+    assert len(bm.block_table(1)) == 2 and bm.num_free_blocks() == 6
+    bm.fork(1, 2)
+    assert bm.block_table(2) == bm.block_table(1)
+    copies = bm.reserve(2, 1)                       # shared partial last block: copy on write
+    assert len(copies) == 1 and copies[0][0] == bm.block_table(1)[1]
+    assert bm.block_table(2)[1] != bm.block_table(1)[1] and bm.block_table(2)[0] == bm.block_table(1)[0]
+    bm.commit(2, 1)
+    bm.trim(2, 3)                                   # 7 -> 4 tokens: second block released
+    assert bm.seq_len(2) == 4 and len(bm.block_table(2)) == 1
+    bm.free_sequence(1); bm.free_sequence(2)
+    assert bm.num_free_blocks() == 8
+    try:
+        bm.reserve(3, 100)
+        assert False
+    except OutOfBlocks:
+        pass
+
+
+def test_scheduler_admission_chunked_prefill_and_eviction():
+    bm = BlockManager(16, 4)
+    s = Scheduler(SchedulerConfig(max_batch_size=2, eos_token_id=99, block_size=4, max_prefill_chunk=8))
+    s.add_request(GenerationRequest(0, list(range(20)), 3))
+    s.add_request(GenerationRequest(1, list(range(5)), 2))
+    s.add_request(GenerationRequest(2, [1, 2, 3], 2))
+    o = s.schedule(bm)
+    assert [m.seq_id for m in o.prefill_seqs] == [0] and o.prefill_chunk_range == (0, 8)
+    assert s.num_active() == 2 and s.num_waiting() == 1
+    o = s.schedule(bm)
+    assert o.prefill_chunk_range == (8, 16) and o.prefill_seqs[0].is_chunked_prefill()
+    o = s.schedule(bm)
+    assert o.prefill_chunk_range == (16, 20)
+    o = s.schedule(bm)                              # seq 1 prefills now, seq 0 decodes
+    assert [m.seq_id for m in o.prefill_seqs] == [1] and [m.seq_id for m in o.decode_seqs] == [0]
+    s.update_sequence(0, bm, 5)
+    o = s.schedule(bm, {0: 99})                     # EOS: evicted, waiting request admitted
+    assert o.evicted_seq_ids == [0] and s.num_waiting() == 0 and 2 in s.active
+
+
+def test_sampler_pipeline_and_speculative():
+    logits = torch.tensor([1.0, 3.0, 2.0, -1.0])
+    assert Sampler().sample_token(logits) == 1
+    s = Sampler(SamplerConfig(temperature=1.0, top_k=2, seed=0))
+    p = s.probabilities(logits)
+    assert p[0] == 0 and p[3] == 0 and abs(float(p.sum()) - 1) < 1e-6
+    s = Sampler(SamplerConfig(temperature=1.0, top_p=0.5, seed=0))
+    p = s.probabilities(logits)
+    assert int((p > 0).sum()) == 1 and p[1] == 1
+    s = Sampler(SamplerConfig(repetition_penalty=2.0))
+    assert s.sample_token(logits, history=[1]) == 2          # 3.0 / 2 < 2.0
+    draws = [Sampler(SamplerConfig(temperature=1.0, seed=i)).sample_token(logits) for i in range(50)]
+    assert set(draws) <= {0, 1, 2, 3} and len(set(draws)) > 1
+    tl = torch.eye(4)[[1, 2, 0, 3]] * 5
+    r = Sampler.greedy_verify([1, 2, 3], tl)
+    assert r.num_accepted == 2 and r.accepted_tokens == [1, 2] and r.correction_token == 0
+    r = Sampler.greedy_verify([1, 2, 0], tl)
+    assert r.num_accepted == 3 and r.correction_token == 3    # bonus token
+    s = Sampler(SamplerConfig(temperature=1.0, seed=1))
+    tp = torch.tensor([[0.0, 1.0, 0.0], [0.5, 0.5, 0.0]])
+    dp = torch.tensor([[0.0, 1.0, 0.0], [0.0, 0.0, 1.0]])
+    r = s.rejection_sample([1, 2], dp, tp)
+    assert r.num_accepted == 1 and r.correction_token in (0, 1)
+
+
+def test_prefix_cache():
+    pc = PrefixCache(block_size=4)
+    toks = list(range(10))
+    assert pc.insert(toks, [7, 8]) == 2               # two full blocks; the ragged tail is not cached
+    assert pc.lookup(toks) == (8, [7, 8])
+    assert pc.lookup([0, 1, 2, 3, 9, 9, 9, 9]) == (4, [7])
+    assert pc.lookup([5, 5, 5, 5]) == (0, [])
+    pc.insert([0, 1, 2, 3, 9, 9, 9, 9], [7, 11])
+    assert len(pc) == 3
+    pc.lookup(toks)                                   # touch the [7, 8] branch
+    assert pc.evict(1) == [11]
+    assert pc.hits >= 2 and pc.misses == 1
+
+
+def test_serving_engine_matches_single_sequence_generation():
+    cfg = tiny_dense_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (5, 19, 9)]
+    eng = ServingEngine(model, num_blocks=24,
+                        scheduler_cfg=SchedulerConfig(max_batch_size=2, max_prefill_chunk=8))
+    ids = [eng.submit(p, 4) for p in prompts]
+    outs = eng.run_until_done()
+    for sid, p in zip(ids, prompts):
+        want = model.generate_greedy(torch.tensor(p), 4)
+        assert outs[sid][:4] == want, (sid, outs[sid], want)
+    assert eng.cache.manager.num_free_blocks() == 23   # everything returned (block 0 is reserved)
