@@ -1,0 +1,132 @@
+"""Expert-parallel dispatch / combine.
+
+Two routing disciplines:
+
+* ``dispatch_with_capacity`` / ``combine_with_layout`` reproduce the reference's semantics
+  (crates/rmlx-distributed/src/moe_exchange.rs:519-581,724-807,1102-1195,2288-2330): expert ``e`` lives
+  on rank ``e // (E / world)``, each expert accepts ``ceil(tokens * k / E * capacity_factor)`` rows
+  per source rank, rows beyond that are dropped (route index -1) and counted as overflow, and the
+  dispatched buffer is laid out ``[local_expert][src_rank * capacity + cursor][hidden]``.
+* ``EpExchange`` is the capacity-free form this framework uses: (token, slot) pairs are sorted by
+  destination expert, per-destination counts are exchanged first, rows travel in one all-to-all,
+  and the receiver gets rows grouped by local expert with prefix offsets (nothing is ever
+  dropped). On GPUs the fused kernels of ``csrc/comm/ep_dispatch.cu`` do the same thing by
+  writing rows straight into the peers' slabs; this class is the library-collective path (NCCL or
+  gloo) and the oracle for it.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import List, Optional, Tuple
+
+import torch
+
+from .group import Group
+
+
+@dataclass
+class DispatchLayout:
+    """What combine needs to undo a dispatch."""
+    order: torch.Tensor            # [T*k] pair index (token*k + slot) in send order
+    send_counts: List[int]         # rows sent to each rank
+    recv_counts: List[int]         # rows received from each rank
+    recv_expert: torch.Tensor      # [R] local expert id of every received row (grouped order)
+    recv_perm: torch.Tensor        # [R] position in arrival order of each grouped row
+    offsets: torch.Tensor          # [E_local + 1] prefix offsets of the grouped rows
+    num_tokens: int
+    top_k: int
+
+
+class EpExchange:
+    def __init__(self, group: Group, num_experts: int):
+        self.group = group
+        self.world, self.rank = group.world_size, group.local_rank
+        if num_experts % self.world:
+            raise ValueError("num_experts must divide by the expert-parallel size")
+        self.E, self.e_local = num_experts, num_experts // self.world
+
+    def dispatch(self, x: torch.Tensor, idx: torch.Tensor) -> Tuple[torch.Tensor, DispatchLayout]:
+        """x [T, D], idx [T, k] (global expert ids). Returns rows grouped by local expert."""
+        t, k = idx.shape
+        flat = idx.reshape(-1).long()
+        order = torch.argsort(flat, stable=True)            # by expert => by destination rank
+        dest = flat[order] // self.e_local
+        send_counts = torch.bincount(dest, minlength=self.world).tolist()
+        rows = x[order // k]
+        meta = (flat[order] % self.e_local).to(torch.int64)
+        recv_counts = self.group.all_to_all(
+            torch.tensor(send_counts, dtype=torch.int64, device=x.device)).tolist() \
+            if self.world > 1 else list(send_counts)
+        got = self.group.all_to_all(rows, send_counts, recv_counts)
+        got_e = self.group.all_to_all(meta, send_counts, recv_counts)
+        perm = torch.argsort(got_e, stable=True)             # group by local expert
+        counts = torch.bincount(got_e, minlength=self.e_local)
+        offsets = torch.zeros(self.e_local + 1, dtype=torch.int64, device=x.device)
+        offsets[1:] = torch.cumsum(counts, 0)
+        layout = DispatchLayout(order, send_counts, recv_counts, got_e[perm], perm, offsets, t, k)
+        return got[perm], layout
+
+    def combine(self, y: torch.Tensor, wts: torch.Tensor, layout: DispatchLayout) -> torch.Tensor:
+        """y: expert outputs for the grouped rows. Returns sum_k w[t,k] * y(t,k) as fp32 [T, D]."""
+        arrival = torch.empty_like(y)
+        arrival[layout.recv_perm] = y                        # back to arrival order
+        back = self.group.all_to_all(arrival, layout.recv_counts, layout.send_counts)
+        out = torch.zeros(layout.num_tokens, y.shape[-1], dtype=torch.float32, device=y.device)
+        pair = layout.order
+        w = wts.reshape(-1)[pair].float()
+        out.index_add_(0, pair // layout.top_k, back.float() * w[:, None])
+        return out
+
+
+# ------------------------------------------------------------------------------------------------
+# Reference-compatible capacity-limited routing (single process view of one rank's send side)
+# ------------------------------------------------------------------------------------------------
+def expert_capacity(num_tokens: int, top_k: int, num_experts: int, capacity_factor: float) -> int:
+    return max(1, math.ceil(num_tokens * top_k / num_experts * capacity_factor))
+
+
+def dispatch_with_capacity(x: torch.Tensor, idx: torch.Tensor, num_experts: int, world: int,
+                           src_rank: int, capacity_factor: float = 1.0):
+    """Returns (buffers, route_indices, overflow): ``buffers[r]`` is what goes to rank r, shaped
+    [E_local, capacity, D] (this source's stripe of the destination layout); ``route_indices``
+    [T, k] holds the slot ``local_expert * world*capacity + src_rank*capacity + cursor`` or -1."""
+    t, k = idx.shape
+    e_local = num_experts // world
+    cap = expert_capacity(t, k, num_experts, capacity_factor)
+    bufs = [torch.zeros(e_local, cap, x.shape[1], dtype=x.dtype) for _ in range(world)]
+    cursors = [0] * num_experts
+    route = torch.full((t, k), -1, dtype=torch.int64)
+    overflow = 0
+    for ti in range(t):
+        for s in range(k):
+            e = int(idx[ti, s])
+            c = cursors[e]
+            if c >= cap:
+                overflow += 1
+                continue
+            cursors[e] = c + 1
+            r, le = e // e_local, e % e_local
+            bufs[r][le, c] = x[ti]
+            route[ti, s] = le * world * cap + src_rank * cap + c
+    return bufs, route, overflow
+
+
+def combine_with_layout(expert_out: List[torch.Tensor], idx: torch.Tensor, wts: torch.Tensor,
+                        route: torch.Tensor, num_experts: int, world: int, src_rank: int,
+                        capacity: int) -> torch.Tensor:
+    """expert_out[r]: [E_local, world*capacity, D] results held by rank r. Dropped pairs add 0."""
+    t, k = idx.shape
+    e_local = num_experts // world
+    d = expert_out[0].shape[-1]
+    out = torch.zeros(t, d, dtype=torch.float32)
+    for ti in range(t):
+        for s in range(k):
+            slot = int(route[ti, s])
+            if slot < 0:
+                continue
+            e = int(idx[ti, s])
+            r = e // e_local
+            le, pos = slot // (world * capacity), slot % (world * capacity)
+            out[ti] += float(wts[ti, s]) * expert_out[r][le, pos].float()
+    return out

@@ -1,0 +1,136 @@
+"""CUDA-graph capture cache and a host-side hazard tracker.
+
+``GraphCache`` keeps one captured graph per key (batch bucket, shapes) with hit/miss counters and
+an LRU bound: the replayable equivalent of the reference's ExecGraph + IcbCache
+(crates/rmlx-metal/src/exec_graph.rs:110-401, crates/rmlx-metal/src/icb.rs:320-420; note that the
+reference's "ICB replay" re-encodes recorded dispatches on the CPU every time, icb.rs:106-168,
+whereas a CUDA graph replays with no per-kernel host work).
+
+``HazardTracker`` is the analogue of ``BarrierTracker`` (crates/rmlx-metal/src/command.rs:130-311):
+given the address ranges an operation reads and writes and the stream it runs on, it reports the
+RAW / WAW / WAR dependencies on operations still in flight on other streams, i.e. where an event
+wait is required. ``serialize=True`` turns every dependency check into "always wait", the switch
+used to bisect suspected races (the reference's ``tracked_hazards`` feature)."""
+from __future__ import annotations
+
+from collections import OrderedDict
+from dataclasses import dataclass, field
+from typing import Callable, Dict, Hashable, List, Optional, Tuple
+
+import torch
+
+
+class GraphCache:
+    def __init__(self, max_entries: int = 64):
+        self.max_entries = max_entries
+        self._g: "OrderedDict[Hashable, object]" = OrderedDict()
+        self.hits = 0
+        self.misses = 0
+        self.captures = 0
+
+    def __len__(self) -> int:
+        return len(self._g)
+
+    def get_or_capture(self, key: Hashable, fn: Callable[[], None], warmup: int = 1):
+        """Returns a replayable object for ``fn`` (a CUDA graph; on CPU, ``fn`` itself)."""
+        g = self._g.get(key)
+        if g is not None:
+            self._g.move_to_end(key)
+            self.hits += 1
+            return g
+        self.misses += 1
+        g = self._capture(fn, warmup)
+        self._g[key] = g
+        if len(self._g) > self.max_entries:
+            self._g.popitem(last=False)
+        return g
+
+    def _capture(self, fn, warmup):
+        self.captures += 1
+        if not torch.cuda.is_available():
+            return _HostReplay(fn)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(warmup):
+                fn()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            fn()
+        return g
+
+    def invalidate(self, key: Optional[Hashable] = None) -> None:
+        if key is None:
+            self._g.clear()
+        else:
+            self._g.pop(key, None)
+
+
+class _HostReplay:
+    def __init__(self, fn):
+        self._fn = fn
+
+    def replay(self):
+        self._fn()
+
+
+def bucket_for(batch: int, buckets=(1, 2, 4, 8, 16, 32, 64)) -> int:
+    """Smallest capture bucket that holds ``batch`` rows."""
+    for b in buckets:
+        if batch <= b:
+            return b
+    raise ValueError(f"batch {batch} exceeds the largest bucket {buckets[-1]}")
+
+
+@dataclass
+class _Op:
+    op_id: int
+    stream: str
+    reads: List[Tuple[int, int]]
+    writes: List[Tuple[int, int]]
+
+
+def _overlap(a: Tuple[int, int], b: Tuple[int, int]) -> bool:
+    return a[0] < b[1] and b[0] < a[1]
+
+
+class HazardTracker:
+    def __init__(self, serialize: bool = False):
+        self.serialize = serialize
+        self._inflight: List[_Op] = []
+        self._next = 0
+
+    def submit(self, stream: str, reads=(), writes=(), temporaries=()) -> List[Tuple[int, str]]:
+        """Register an op; returns [(op_id, kind)] it must wait for, kind in RAW / WAW / WAR.
+        ``temporaries`` are ranges private to the op (exempt from tracking)."""
+        tmp = list(temporaries)
+        rd = [r for r in reads if not any(_overlap(r, t) for t in tmp)]
+        wr = [w for w in writes if not any(_overlap(w, t) for t in tmp)]
+        deps: List[Tuple[int, str]] = []
+        for o in self._inflight:
+            if o.stream == stream and not self.serialize:
+                continue               # same stream: ordered by the stream itself
+            if self.serialize:
+                deps.append((o.op_id, "SERIAL"))
+                continue
+            if any(_overlap(r, w) for r in rd for w in o.writes):
+                deps.append((o.op_id, "RAW"))
+            elif any(_overlap(w, w2) for w in wr for w2 in o.writes):
+                deps.append((o.op_id, "WAW"))
+            elif any(_overlap(w, r) for w in wr for r in o.reads):
+                deps.append((o.op_id, "WAR"))
+        op = _Op(self._next, stream, rd, wr)
+        self._next += 1
+        self._inflight.append(op)
+        return deps
+
+    def retire(self, op_id: int) -> None:
+        self._inflight = [o for o in self._inflight if o.op_id != op_id]
+
+    def retire_stream(self, stream: str) -> None:
+        self._inflight = [o for o in self._inflight if o.stream != stream]
+
+    def in_flight(self) -> int:
+        return len(self._inflight)

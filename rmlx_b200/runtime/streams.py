@@ -1,0 +1,118 @@
+"""Streams, events and fences with bounded host waits.
+
+``GpuEvent`` wraps a CUDA event with a monotonically increasing signal counter; ``cpu_wait`` polls
+``query()`` with spin -> yield -> sleep back-off until a deadline or a cancel flag, and never
+blocks without a bound (crates/rmlx-metal/src/event.rs:15-117). ``GpuFence`` orders two streams
+(crates/rmlx-metal/src/fence.rs:24-130). ``StreamManager`` owns the named streams
+default / compute / copy and the cross-stream synchronisation helpers
+(crates/rmlx-metal/src/stream.rs:56-330). On a machine without a GPU the classes run in a host
+emulation (work is considered complete immediately) so the control logic stays testable.
+"""
+from __future__ import annotations
+
+import threading
+import time
+from typing import Dict, Optional
+
+import torch
+
+STREAM_DEFAULT, STREAM_COMPUTE, STREAM_COPY = "default", "compute", "copy"
+
+
+class WaitTimeout(TimeoutError):
+    pass
+
+
+class WaitCancelled(RuntimeError):
+    pass
+
+
+class GpuEvent:
+    def __init__(self, device=None):
+        self._cuda = torch.cuda.is_available()
+        self._ev = torch.cuda.Event() if self._cuda else None
+        self._signalled = 0      # value the next/last record carries
+        self._cancel = threading.Event()
+        self._host_done = True
+
+    def record(self, stream=None) -> int:
+        self._signalled += 1
+        if self._cuda:
+            self._ev.record(stream or torch.cuda.current_stream())
+        return self._signalled
+
+    def query(self) -> bool:
+        return self._ev.query() if self._cuda else self._host_done
+
+    def cancel(self) -> None:
+        self._cancel.set()
+
+    def cpu_wait(self, timeout_s: float = 5.0) -> None:
+        """Spin briefly, then yield, then sleep; raises WaitTimeout / WaitCancelled."""
+        deadline = time.monotonic() + timeout_s
+        spins = 0
+        while not self.query():
+            if self._cancel.is_set():
+                raise WaitCancelled("event wait cancelled")
+            if time.monotonic() >= deadline:
+                raise WaitTimeout(f"event not signalled within {timeout_s}s")
+            spins += 1
+            if spins < 200:
+                continue
+            time.sleep(0 if spins < 2000 else 0.0002)
+
+    def stream_wait(self, stream) -> None:
+        if self._cuda:
+            stream.wait_event(self._ev)
+
+
+class GpuFence:
+    """Make ``waiter`` stream wait for everything submitted so far on ``signaller``."""
+
+    def __init__(self):
+        self.event = GpuEvent()
+
+    def signal(self, signaller=None) -> int:
+        return self.event.record(signaller)
+
+    def wait(self, waiter) -> None:
+        self.event.stream_wait(waiter)
+
+    def cpu_wait(self, timeout_s: float = 5.0) -> None:
+        self.event.cpu_wait(timeout_s)
+
+
+class StreamManager:
+    def __init__(self, device=None, names=(STREAM_DEFAULT, STREAM_COMPUTE, STREAM_COPY)):
+        self._cuda = torch.cuda.is_available()
+        self.streams: Dict[str, Optional[torch.cuda.Stream]] = {}
+        for n in names:
+            if not self._cuda:
+                self.streams[n] = None
+            elif n == STREAM_DEFAULT:
+                self.streams[n] = torch.cuda.current_stream(device)
+            else:
+                self.streams[n] = torch.cuda.Stream(device)
+
+    def get(self, name: str):
+        return self.streams[name]
+
+    def order(self, before: str, after: str) -> GpuFence:
+        """Everything queued on ``before`` happens before later work on ``after``."""
+        f = GpuFence()
+        f.signal(self.streams[before])
+        if self._cuda:
+            f.wait(self.streams[after])
+        return f
+
+    def compute_to_copy(self) -> GpuFence:
+        return self.order(STREAM_COMPUTE, STREAM_COPY)
+
+    def copy_to_compute(self) -> GpuFence:
+        return self.order(STREAM_COPY, STREAM_COMPUTE)
+
+    def synchronize(self, timeout_s: float = 30.0) -> None:
+        for n, s in self.streams.items():
+            ev = GpuEvent()
+            ev.record(s)
+            ev.cpu_wait(timeout_s)

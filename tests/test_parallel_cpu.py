@@ -1,0 +1,224 @@
+"""Distributed plumbing without GPUs: rank/world resolution, Group collectives and split on gloo
+ranks (one OS process per rank, like the mock-transport tests of
+crates/rmlx-distributed/tests/tree_allreduce_tests.rs:10-121), health monitor with a host-side
+failure, MoE policy hysteresis/cool-down, sparse guard, wire formats, slab ring, EP exchange
+against the single-process oracle (crates/rmlx-distributed/tests/moe_tests.rs)."""
+import os
+import socket
+import time
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from rmlx_b200.config import InitConfig, MoeConfig
+from rmlx_b200.nn.moe import ExpertGroup, MoeLayer, MoeStrategy
+from rmlx_b200.parallel import ep, wire
+from rmlx_b200.parallel.group import DistributedError, Group, ReduceOp
+from rmlx_b200.parallel.health import DictStore, HealthMonitor, HeartbeatConfig, HeartbeatSender, Watchdog
+from rmlx_b200.parallel.init import init, resolve_backend, resolve_rank_world
+from rmlx_b200.parallel.moe_policy import GuardAction, MoeBackend, MoePolicy, SparseGuard
+from rmlx_b200.parallel.slab_ring import SlabRing, SlabRingConfig
+from rmlx_b200.parallel.topology import parse_topo_matrix
+from rmlx_b200.runtime.streams import WaitTimeout
+
+
+def test_rank_resolution_order():
+    assert resolve_rank_world(InitConfig(), {}) == (0, 1, 0)
+    assert resolve_rank_world(InitConfig(), {"RANK": "3", "WORLD_SIZE": "8", "LOCAL_RANK": "3"}) == (3, 8, 3)
+    assert resolve_rank_world(InitConfig(), {"RMLX_RANK": "1", "RMLX_WORLD_SIZE": "2", "RANK": "5",
+                                             "WORLD_SIZE": "9"})[:2] == (1, 2)
+    assert resolve_rank_world(InitConfig(rank=0, world_size=4), {"RANK": "2"})[:2] == (0, 4)
+    assert resolve_rank_world(InitConfig(), {"SLURM_PROCID": "2", "SLURM_NTASKS": "4"})[:2] == (2, 4)
+    with pytest.raises(DistributedError):
+        resolve_rank_world(InitConfig(rank=4, world_size=2), {})
+    assert resolve_backend(InitConfig(backend="gloo"), {}) == "gloo"
+    assert resolve_backend(InitConfig(), {"RMLX_BACKEND": "loopback"}) == "loopback"
+    ctx = init(InitConfig())
+    assert ctx.is_loopback and ctx.world_size == 1
+    g = ctx.group
+    x = torch.arange(4.0)
+    assert torch.equal(g.allreduce(x), x) and torch.equal(g.allgather(x), x)
+    with pytest.raises(DistributedError):
+        g.send(x, 1)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _group_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        g = Group()
+        x = torch.full((4,), float(rank + 1))
+        ok = torch.equal(g.allreduce(x), torch.full((4,), 10.0))
+        ok &= torch.equal(g.allreduce(x, ReduceOp.MAX), torch.full((4,), 4.0))
+        hb = g.allreduce(torch.full((3,), 0.1 * (rank + 1), dtype=torch.bfloat16))
+        ok &= hb.dtype == torch.bfloat16 and abs(float(hb[0]) - 1.0) < 0.02
+        ok &= g.allgather(torch.tensor([rank])).tolist() == [0, 1, 2, 3]
+        ok &= torch.equal(g.reduce_scatter(torch.arange(8.0)), torch.arange(8.0)[2 * rank:2 * rank + 2] * 4)
+        b = torch.tensor([7.0]) if rank == 2 else torch.zeros(1)
+        ok &= float(g.broadcast(b, root=2)) == 7.0
+        a2a = g.all_to_all(torch.arange(4.0) + 10 * rank)
+        ok &= a2a.tolist() == [rank + 10 * r for r in range(4)]
+        var = g.all_to_all(torch.full((rank + 1, 2), float(rank)), [1 if p == 0 else (rank if p == 1 else 0) for p in range(4)][:4]
+                           if False else [rank + 1, 0, 0, 0])
+        ok &= (var.shape[0] == 10) if rank == 0 else (var.shape[0] == 0)
+        peer = rank ^ 1
+        got = g.sendrecv(torch.tensor([float(rank)]), torch.zeros(1), peer)
+        ok &= float(got) == float(peer)
+        sub = g.split(color=rank % 2, key=-rank)          # evens / odds, reversed order
+        ok &= sub.world_size == 2 and sub.ranks == ([2, 0] if rank % 2 == 0 else [3, 1])
+        ok &= float(sub.allreduce(torch.tensor([float(rank)]))) == (2.0 if rank % 2 == 0 else 4.0)
+        g.barrier()
+        # expert-parallel exchange against the single-process oracle
+        torch.manual_seed(0)
+        E, D_, I, T, K = 8, 16, 8, 6, 2
+        gate = [torch.randn(I, D_) * 0.1 for _ in range(E)]
+        up = [torch.randn(I, D_) * 0.1 for _ in range(E)]
+        down = [torch.randn(D_, I) * 0.1 for _ in range(E)]
+        router = torch.randn(E, D_)
+        cfg = MoeConfig(E, K, D_, I)
+        full = MoeLayer(cfg, router, ExpertGroup.from_experts(list(zip(gate, up, down)), dtype=torch.float32),
+                        MoeStrategy.PER_EXPERT)
+        torch.manual_seed(100 + rank)
+        x = torch.randn(T, D_)
+        want = full.forward(x)
+        el = E // world
+        mine = list(zip(gate, up, down))[rank * el:(rank + 1) * el]
+        layer = MoeLayer(cfg, router, ExpertGroup.from_experts(mine, dtype=torch.float32)
+                         ).with_exchange(ep.EpExchange(g, E))
+        got = layer.forward(x)
+        ok &= torch.allclose(got, want, atol=1e-5)
+        grouped = full.with_strategy(MoeStrategy.GROUPED).forward(x)
+        ok &= torch.allclose(grouped, want, atol=1e-5)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_group_collectives_split_and_ep_exchange_on_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_group_worker, args=(r, 4, port, q)) for r in range(4)]
+    [p.start() for p in ps]
+    res = dict(q.get(timeout=120) for _ in range(4))
+    for p in ps:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res == {0: True, 1: True, 2: True, 3: True}
+
+
+def test_health_monitor_detects_a_silent_peer_on_the_host():
+    store = DictStore()
+    now = [0.0]
+    mon = HealthMonitor(store, 0, 3, HeartbeatConfig(1.0, 5.0, 3), clock=lambda: now[0])
+    s1, s2 = HeartbeatSender(store, 1), HeartbeatSender(store, 2)
+    for step in range(5):
+        now[0] += 1.0
+        s1.beat()
+        if step < 1:
+            s2.beat()                       # rank 2 stops after its first beat
+        mon.poll()
+    assert mon.failed_peers() == [2] and not mon.healthy()
+    # the wired form: a watchdog thread flips ok() and calls back; peer 1 never joins
+    failures = []
+    wd = Watchdog(DictStore(), 0, 2, HeartbeatConfig(0.01, 0.2, 3), on_failure=failures.append)
+    wd.start()
+    t0 = time.monotonic()
+    while wd.ok() and time.monotonic() - t0 < 5:
+        time.sleep(0.01)
+    wd.stop()
+    assert not wd.ok() and failures == [[1]]
+
+
+def test_moe_policy_and_sparse_guard():
+    now = [0.0]
+    p = MoePolicy(hysteresis=16, cooldown_s=5.0, cooldown_calls=1000, env={}, clock=lambda: now[0])
+    assert p.select(8) == MoeBackend.LOCAL
+    now[0] += 10
+    assert p.select(70) == MoeBackend.LOCAL           # inside the hysteresis band: no switch
+    assert p.select(400) == MoeBackend.FUSED and p.zone_switches == 1
+    assert p.select(4) == MoeBackend.FUSED            # cool-down holds the choice
+    now[0] += 10
+    assert p.select(4) == MoeBackend.LOCAL and p.zone_switches == 2
+    assert MoePolicy(env={"RMLX_MOE_BACKEND": "nccl"}).select(1) == MoeBackend.NCCL
+    mid = MoePolicy(env={})
+    assert mid.select(200, nbytes=4 << 20) == MoeBackend.FUSED
+    g = SparseGuard(window=10)
+    acts = [g.record_step(1, 10) for _ in range(10)]
+    assert acts[-1] == GuardAction.INCREASE_CAPACITY
+    acts = [g.record_step(9, 10) for _ in range(30)]
+    assert GuardAction.DENSE_FALLBACK in acts
+    acts = [g.record_step(0, 10) for _ in range(400)]
+    assert GuardAction.RESET in acts and g.state == GuardAction.NONE
+
+
+def test_wire_formats():
+    rows = np.arange(24, dtype=np.uint8).reshape(3, 8)
+    buf = wire.pack_v3([0, 2, 1], [5, 0, 65535], rows)
+    assert len(buf) == wire.v3_payload_bytes(3, 8)
+    e, p, r = wire.unpack_v3(buf, 8)
+    assert e == [0, 2, 1] and p == [5, 0, 65535] and np.array_equal(r, rows)
+    assert wire.unpack_v3(wire.pack_v3([], [], np.zeros((0, 8), np.uint8)), 8)[0] == []
+    with pytest.raises(wire.ProtocolError):
+        wire.unpack_v3(buf[:-1], 8)
+    x = torch.randn(5, 64)
+    y = wire.fp8_unpack_tokens(wire.fp8_pack_tokens(x), 5, 64)
+    assert (y - x).abs().max() <= x.abs().max() * 0.07
+    f = wire.crc_frame(b"payload")
+    assert wire.crc_verify(f) == b"payload"
+    with pytest.raises(wire.ProtocolError):
+        wire.crc_verify(b"x" + f[1:])
+
+
+def test_slab_ring_backpressure_and_bounded_waits():
+    ring = SlabRing(SlabRingConfig(depth=2, slab_bytes=64))
+    a = ring.acquire_for_write(); ring.slab(a)[:4] = torch.tensor([1, 2, 3, 4], dtype=torch.uint8)
+    ring.produce(a)
+    b = ring.acquire_for_write(); ring.produce(b)
+    with pytest.raises(WaitTimeout):
+        ring.acquire_for_write(timeout_s=0.01)        # full: consumer has released nothing
+    i = ring.consume(0.1)
+    assert i == a and ring.slab(i)[:4].tolist() == [1, 2, 3, 4]
+    ring.release(i)
+    assert ring.acquire_for_write(0.1) == a
+    ring.release(ring.consume(0.1))
+    with pytest.raises(WaitTimeout):
+        ring.consume(0.01)                            # slot a is being written, nothing ready
+    assert ring.backpressure_events > 0 and ring.produced == 2 and ring.consumed == 2
+
+
+def test_capacity_limited_dispatch_matches_reference_semantics():
+    torch.manual_seed(0)
+    T, K, E, W, D_ = 8, 2, 4, 2, 4
+    x = torch.randn(T, D_)
+    idx = torch.zeros(T, K, dtype=torch.int64); idx[:, 1] = 1      # everyone wants experts 0 and 1
+    wts = torch.full((T, K), 0.5)
+    cap = ep.expert_capacity(T, K, E, 1.0)
+    assert cap == 4
+    bufs, route, overflow = ep.dispatch_with_capacity(x, idx, E, W, src_rank=1, capacity_factor=1.0)
+    assert overflow == 8 and (route[:4] >= 0).all() and (route[4:] == -1).all()
+    assert int(route[0, 0]) == 0 * W * cap + 1 * cap + 0
+    assert torch.equal(bufs[0][0, :4], x[:4]) and bufs[1].abs().sum() == 0
+    outs = [torch.zeros(E // W, W * cap, D_) for _ in range(W)]
+    outs[0][:, cap:2 * cap] = bufs[0] * 2.0                         # identity-ish experts: y = 2x
+    y = ep.combine_with_layout(outs, idx, wts, route, E, W, 1, cap)
+    assert torch.allclose(y[:4], 2.0 * x[:4]) and y[4:].abs().sum() == 0
+
+
+def test_topology_matrix_parser():
+    txt = """\tGPU0\tGPU1\tGPU2\tCPU Affinity
+GPU0\t X \tNV18\tNV18\t0-55
+GPU1\tNV18\t X \tNV18\t0-55
+GPU2\tNV18\tNV18\t X \t56-111
+"""
+    m = parse_topo_matrix(txt)
+    assert m == [["X", "NV18", "NV18"], ["NV18", "X", "NV18"], ["NV18", "NV18", "X"]]
