@@ -360,3 +360,71 @@ extern "C" int rmlx_flash_decode_paged(const void* q, const void* k_cache, const
 #undef RB_FD
   return -2;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Entry point that allocates nothing (declared in flash_decode_noalloc.h). Some users of this
+// library cannot call the CUDA allocator where they run attention: an engine that pre-partitions
+// all device memory, a latency-critical loop that must not block on allocator locks, a plug-in
+// API that passes only inputs and outputs. For them the split-KV scratch lives in this file-scope
+// device array. In host code the array's name is only a host-side handle, not a device address,
+// so the address is looked up once per device with cudaGetSymbolAddress and that pointer is what
+// the kernel receives.
+// ------------------------------------------------------------------------------------------------
+#include "flash_decode_noalloc.h"
+
+namespace {
+constexpr size_t kNaPartO = size_t(RMLX_FD_NOALLOC_MAX_TILES) * RMLX_FD_NOALLOC_MAX_SPLITS * 16 *
+                            RMLX_FD_NOALLOC_MAX_HEAD_DIM;                       // floats
+constexpr size_t kNaPartMl = size_t(RMLX_FD_NOALLOC_MAX_TILES) * RMLX_FD_NOALLOC_MAX_SPLITS * 16 * 2;
+constexpr size_t kNaTickets = RMLX_FD_NOALLOC_MAX_TILES;                        // uint32
+constexpr size_t kNaBytes = (kNaPartO + kNaPartMl) * sizeof(float) + kNaTickets * sizeof(unsigned int);
+
+static __device__ __align__(256) unsigned char g_fd_noalloc_scratch[kNaBytes];
+
+constexpr int kNaMaxDevices = 64;
+void* g_fd_noalloc_ptr[kNaMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" const char* rmlx_flash_decode_noalloc_error(int code) {
+  switch (code) {
+    case RMLX_FD_NOALLOC_TOO_LARGE:
+      return "flash_decode_paged_noalloc: batch*kv_heads*head_tiles > 64, splits > 16 or head_dim > 128 "
+             "exceeds the built-in scratch; use rmlx_flash_decode_paged with caller-provided scratch";
+    case RMLX_FD_NOALLOC_SETUP_FAILED:
+      return "flash_decode_paged_noalloc: could not resolve the device address of the built-in scratch";
+    default:
+      return nullptr;
+  }
+}
+
+extern "C" int rmlx_flash_decode_paged_noalloc(const void* q, const void* k_cache, const void* v_cache,
+                                               const int* block_table, const int* seq_lens, void* out,
+                                               int B, int Hq, int Hkv, int HD, int max_blocks,
+                                               int splits, int window, float scale,
+                                               cudaStream_t stream) {
+  if (B < 1 || Hkv < 1 || Hq < 1 || Hq % Hkv || splits < 1) return -2;
+  const long long tiles = 1LL * B * Hkv * rmlx_flash_decode_gtiles(Hq, Hkv);
+  if (tiles > RMLX_FD_NOALLOC_MAX_TILES || splits > RMLX_FD_NOALLOC_MAX_SPLITS ||
+      HD > RMLX_FD_NOALLOC_MAX_HEAD_DIM)
+    return RMLX_FD_NOALLOC_TOO_LARGE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNaMaxDevices)
+    return RMLX_FD_NOALLOC_SETUP_FAILED;
+  if (g_fd_noalloc_ptr[dev] == nullptr) {
+    // once per device, with that device current; not inside a stream capture
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_fd_noalloc_scratch) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      return RMLX_FD_NOALLOC_SETUP_FAILED;
+    }
+    g_fd_noalloc_ptr[dev] = p;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_fd_noalloc_ptr[dev]);
+  float* part_o = reinterpret_cast<float*>(base);
+  float* part_ml = part_o + kNaPartO;
+  unsigned int* tickets = reinterpret_cast<unsigned int*>(part_ml + kNaPartMl);
+  // the tickets are the only part that must start at zero; the partials are fully rewritten
+  RB_CHECK(cudaMemsetAsync(tickets, 0, kNaTickets * sizeof(unsigned int), stream));
+  return rmlx_flash_decode_paged(q, k_cache, v_cache, block_table, seq_lens, out, part_o, part_ml,
+                                 tickets, B, Hq, Hkv, HD, max_blocks, splits, window, scale, 0, stream);
+}
