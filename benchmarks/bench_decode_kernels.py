@@ -66,6 +66,7 @@ def main():
     ap.add_argument("--iters", type=int, default=50)
     ap.add_argument("--only", default="")
     ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--splits", type=int, default=0, help="KV splits for flash decode (0 = default heuristic)")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     quant = None if args.weights == "bf16" else "q4"
@@ -137,7 +138,7 @@ def main():
     sl = torch.full((B,), ctx, dtype=torch.int32, device=dev)
     q = torch.randn(B, HQ, HD, device=dev).to(torch.bfloat16)
     ao = torch.empty_like(q)
-    splits = D.default_splits(B, HKV, 1, ctx)
+    splits = args.splits or D.default_splits(B, HKV, 1, ctx)
     fsc = D.FlashDecodeScratch(B, HQ, HKV, HD, splits, dev)
     add(f"flash_decode ctx{ctx} splits{splits}",
         [(lambda i=i: D.flash_decode_paged(q, kcs[i], vcs[i], bt, sl, None, splits, fsc, out=ao))

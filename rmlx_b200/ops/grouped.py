@@ -1,0 +1,53 @@
+"""Grouped expert feed-forward for many tokens: rows sorted by expert go through two grouped
+tensor-core GEMMs (gate|up, then down) with SwiGLU in between; ``moe_prefill_ffn`` wraps the whole
+path from router output to combined result (scatter rows -> grouped gate/up -> SwiGLU -> grouped
+down -> routing-weighted combine + residual). The reference's counterpart is
+``ExpertGroup::grouped_forward`` + gather/scatter kernels (crates/rmlx-nn/src/expert_group.rs:308-533,
+crates/rmlx-nn/src/moe.rs:1391-1508)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _lib
+from . import decode as D
+from .quantized import xgemm
+from .weights import LinearWeight, W_Q4
+
+
+def _grouped_ok(w: LinearWeight) -> bool:
+    return w.n % 128 == 0 and (w.kind != W_Q4 or bool(_lib.cuda().rmlx_qgemm_supported(w.k)))
+
+
+def grouped_expert_ffn(x_sorted: torch.Tensor, offsets: torch.Tensor, gate_up: LinearWeight,
+                       down: LinearWeight) -> torch.Tensor:
+    """x_sorted [R, D] bf16 (rows grouped by expert), offsets [E+1] -> [R, D]."""
+    if not (_grouped_ok(gate_up) and _grouped_ok(down)):
+        raise ImportError("shape not covered by the grouped tensor-core kernel")
+    off = offsets.to(torch.int32)
+    gu = xgemm(x_sorted.contiguous(), gate_up, offsets=off)
+    act = D.silu_mul(gu)
+    return xgemm(act, down, offsets=off)
+
+
+def moe_prefill_ffn(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, offsets: torch.Tensor,
+                    gate_up: LinearWeight, down: LinearWeight,
+                    residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, D] bf16, idx/wts [T, k] from the router, offsets [E+1] int32 (device)."""
+    t, d = x.shape
+    k = idx.shape[1]
+    e = gate_up.experts
+    lib, st = _lib.cuda(), _lib.stream_ptr()
+    xs = torch.empty(t * k, d, dtype=torch.bfloat16, device=x.device)
+    row_of_pair = torch.empty(t * k, dtype=torch.int32, device=x.device)
+    cursors = torch.empty(e, dtype=torch.int32, device=x.device)
+    _lib.check(lib.rmlx_moe_scatter_rows(x.data_ptr(), x.stride(0), idx.data_ptr(), offsets.data_ptr(),
+                                         cursors.data_ptr(), xs.data_ptr(), row_of_pair.data_ptr(),
+                                         t, k, d, e, st), "moe_scatter_rows")
+    y = grouped_expert_ffn(xs, offsets, gate_up, down)
+    out = torch.empty(t, d, dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.rmlx_moe_combine(y.data_ptr(), row_of_pair.data_ptr(), wts.data_ptr(),
+                                    _lib.ptr(residual), 0 if residual is None else residual.stride(0),
+                                    out.data_ptr(), out.stride(0), t, k, d, st), "moe_combine")
+    return out
