@@ -93,8 +93,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. `abort_flag` is a CTA-shared word: once any role gives up, the others stop waiting
 // at their next poll instead of each burning the full budget. Returns false on give-up.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
-                                          volatile uint32_t* abort_flag) {
-  for (uint32_t i = 0; i < kMbarPollLimit; ++i) {
+                                          volatile uint32_t* abort_flag,
+                                          uint32_t limit = kMbarPollLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 63u && *abort_flag) return false;
   }

@@ -1,0 +1,533 @@
+// The generalised tcgen05 GEMM kernel (see xgemm_tcgen05.cu for the plain entry points and
+// ../comm/tp_gemm.cu for the tensor-parallel ones). C = A · W^T with
+//   * W bf16 (TMA-fed) or MLX-affine Q4 dequantised inside the main loop by four dequant warps;
+//   * GROUPED: rows of A sorted by expert, tile table derived on the device from offsets[E+1];
+//   * COMM = kCommReduce: this rank holds a K-shard; every finished accumulator tile is stored
+//     straight into the staging slab of the rank that owns the tile (peer stores over NVLink, a
+//     release counter per tile); the owner's epilogue warps sum the world's partials (+ residual)
+//     and store the finished tile into every rank's output — reduce-scatter and all-gather of an
+//     all-reduce, both inside the GEMM kernel, overlapped with the tiles still being multiplied;
+//   * COMM = kCommGather: A is row-sharded over the ranks; the epilogue warps (idle while the first
+//     tiles are multiplied) push this rank's rows into every peer's gathered copy in 8-row chunks
+//     with a counter per 128-row block; the TMA producer starts with the local rows and waits for
+//     a block's counter before its first load of remote rows.
+// Every wait — mbarrier or peer counter — is bounded; a timeout sets the status word and the CTA
+// drains and frees its tensor memory. Peer data is only ever *pushed* (plain stores); loads are
+// always from this GPU's memory.
+#pragma once
+#include <cuda.h>
+#include "../common/ptx.cuh"
+#include "../common/launch.cuh"
+#include "../common/tensormap.cuh"
+
+namespace rb {
+
+constexpr int kXBM = 128;
+constexpr int kXBK = 64;
+constexpr int kXMaxExperts = 256;
+constexpr int kXMaxRanks = 8;
+constexpr int kCommNone = 0, kCommReduce = 1, kCommGather = 2;
+constexpr int kGatherChunkRows = 8;
+
+struct XComm {
+  int rank = 0, world = 1;
+  uint32_t* epoch = nullptr;                 // local: [0] calls completed, [1] exit ticket
+  // reduce
+  __nv_bfloat16* stage[kXMaxRanks] = {};     // rank p's staging slab [world][tiles_owned_max][128*BN]
+  uint32_t* tile_flags[kXMaxRanks] = {};     // rank p's arrival counter per owned tile
+  __nv_bfloat16* out[kXMaxRanks] = {};       // rank p's output matrix [M, ldc]
+  uint32_t* done[kXMaxRanks] = {};           // rank p's count of finished tiles
+  int tiles_owned_max = 0;
+  // gather
+  const __nv_bfloat16* a_shard = nullptr;    // this rank's rows [shard_rows, lda_shard]
+  int lda_shard = 0, shard_rows = 0;
+  __nv_bfloat16* a_full[kXMaxRanks] = {};    // rank p's gathered copy, two parities [2][M][K]
+  uint32_t* ready[kXMaxRanks] = {};          // rank p's counter per 128-row block
+};
+
+template <int BN, bool WQ4>
+struct XSmem {
+  static constexpr int kStages = WQ4 ? 3 : ((BN >= 256) ? 4 : 6);
+  static constexpr int kRawStages = 4;
+  static constexpr int kStageA = kXBM * kXBK * 2;
+  static constexpr int kStageB = BN * kXBK * 2;
+  static constexpr int kStageRaw = BN * 32;          // 64 nibbles per row
+  static constexpr int kScaleSlot = 2 * BN * 16;     // scales + biases for 8 k-blocks
+  static constexpr int kBytes = kStages * (kStageA + kStageB) +
+                                (WQ4 ? kRawStages * kStageRaw + 2 * kScaleSlot : 0) + 1024 + 512 +
+                                (kXMaxExperts + 2) * 8;
+  static constexpr int kThreads = WQ4 ? 320 : 192;
+};
+
+struct XTile {
+  int a_row0;     // first row of the A/C tile
+  int row_end;    // rows >= row_end are not stored
+  int w_row0;     // first row of the W tile (in the stacked weight)
+  int c_col0;     // first output column
+};
+
+// tile id -> coordinates. Plain: column-block major so consecutive CTAs share a W tile; ``rot``
+// rotates the row blocks so that a rank starts with the rows it already holds (gather mode).
+template <int BN, bool GROUPED>
+__device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int tiles_n,
+                                        const int* s_off, const int* s_tprefix, int E, int rot = 0) {
+  XTile t;
+  if (!GROUPED) {
+    int tm = tile % tiles_m + rot;
+    if (tm >= tiles_m) tm -= tiles_m;
+    const int tn = tile / tiles_m;
+    t.a_row0 = tm * kXBM; t.row_end = M; t.w_row0 = tn * BN; t.c_col0 = tn * BN;
+  } else {
+    int e = 0;
+    while (e + 1 < E && s_tprefix[e + 1] <= tile) ++e;
+    while (s_tprefix[e + 1] <= tile) ++e;                 // skips empty experts
+    const int local = tile - s_tprefix[e];
+    const int rows = s_off[e + 1] - s_off[e];
+    const int mt_e = (rows + kXBM - 1) / kXBM;
+    const int nt = local / mt_e, mt = local % mt_e;
+    t.a_row0 = s_off[e] + mt * kXBM; t.row_end = s_off[e + 1];
+    t.w_row0 = e * N + nt * BN; t.c_col0 = nt * BN;
+  }
+  return t;
+}
+
+// Barrier over the four epilogue warps, built on an mbarrier so that it is bounded like every other
+// wait: if a warp left early after a timeout, the rest give up too instead of waiting for it.
+__device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase, volatile uint32_t* abort_flag,
+                                         uint32_t limit) {
+  mbar_arrive(bar);
+  const bool ok = mbar_wait(bar, phase, abort_flag, limit);
+  phase ^= 1u;
+  return ok;
+}
+
+template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM>
+__global__ void __launch_bounds__((XSmem<BN, WQ4>::kThreads), 1)
+xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a2,
+             const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
+             const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16* __restrict__ C,
+             const __nv_bfloat16* __restrict__ residual, const int* __restrict__ offsets, int E, int M,
+             int N, int K, int ldc, int* __restrict__ status, const XComm cm) {
+  static_assert(COMM == kCommNone || !GROUPED, "collective modes are for plain GEMMs");
+  using S = XSmem<BN, WQ4>;
+  constexpr int STAGES = S::kStages, RAW = S::kRawStages;
+  // a role may be waiting, through the pipeline, on a peer that started late: be more patient then
+  constexpr uint32_t LIM = (COMM == kCommNone) ? kMbarPollLimit : (kMbarPollLimit << 4);
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
+  extern __shared__ char smem_raw[];
+  char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  char* sA = smem;
+  char* sB = sA + STAGES * S::kStageA;
+  char* sRaw = sB + STAGES * S::kStageB;
+  char* sScale = sRaw + (WQ4 ? RAW * S::kStageRaw : 0);
+  char* after = sScale + (WQ4 ? 2 * S::kScaleSlot : 0);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(after);
+  uint64_t* full = bars;                        // [STAGES] A (and bf16 B) landed
+  uint64_t* empty = full + STAGES;              // [STAGES] MMAs finished reading the stage
+  uint64_t* bq_full = empty + STAGES;           // [STAGES] dequantised B written (Q4)
+  uint64_t* raw_full = bq_full + STAGES;        // [RAW]
+  uint64_t* raw_empty = raw_full + RAW;         // [RAW]
+  uint64_t* sc_full = raw_empty + RAW;          // [2]
+  uint64_t* sc_empty = sc_full + 2;             // [2]
+  uint64_t* acc_full = sc_empty + 2;            // [2]
+  uint64_t* acc_empty = acc_full + 2;           // [2]
+  uint64_t* epi_mb = acc_empty + 2;             // [1] epilogue-warp barrier (collective modes)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_mb + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  volatile uint32_t* peer_fail = tmem_slot + 2;
+  int* s_off = reinterpret_cast<int*>(after + 512);          // [E+1]
+  int* s_tprefix = s_off + kXMaxExperts + 1;                 // [E+1]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_n = (N + BN - 1) / BN;
+  int tiles_m = (M + kXBM - 1) / kXBM;
+  const int num_kb = (K + kXBK - 1) / kXBK;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < STAGES; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, 1); mbar_init(bq_full + i, 4); }
+    for (int i = 0; i < RAW; ++i) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, 4); }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(sc_full + i, 1); mbar_init(sc_empty + i, 4);
+      mbar_init(acc_full + i, 1); mbar_init(acc_empty + i, 4);
+    }
+    mbar_init(epi_mb, 128);
+    *abort_flag = 0u;
+    *peer_fail = 0u;
+    fence_mbar_init();
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, TMEM_COLS); tmem_relinquish(); }
+  if (GROUPED) {
+    pdl_wait();
+    for (int i = threadIdx.x; i <= E; i += blockDim.x) s_off[i] = offsets[i];
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  if (GROUPED) {
+    if (threadIdx.x == 0) {
+      int acc = 0;
+      for (int e = 0; e < E; ++e) {
+        s_tprefix[e] = acc;
+        acc += ((s_off[e + 1] - s_off[e] + kXBM - 1) / kXBM) * tiles_n;
+      }
+      s_tprefix[E] = acc;
+    }
+    __syncthreads();
+  }
+  const int num_tiles = GROUPED ? s_tprefix[E] : tiles_m * tiles_n;
+  const uint32_t tmem_base = *tmem_slot;
+  // collective modes: calls completed so far on this site; counters only grow, so a call waits
+  // for (epoch+1) x the per-call increment and nothing is ever reset.
+  const uint32_t e1 = (COMM != kCommNone) ? cm.epoch[0] + 1u : 0u;
+  const int rot = (COMM == kCommGather) ? (cm.rank * cm.shard_rows) / kXBM : 0;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      const CUtensorMap* ta = (COMM == kCommGather && (e1 & 1u) == 0u) ? &tmap_a2 : &tmap_a;
+      tma_prefetch_desc(ta);
+      tma_prefetch_desc(&tmap_w);
+      if (!GROUPED) pdl_wait();
+      int stage = 0, rstage = 0, sslot = 0;
+      uint32_t phase = 0, rphase = 0, sphase = 0;
+      bool ok = true;
+      int ready_mb = -1;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const XTile t = x_tile<BN, GROUPED>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
+        if (COMM == kCommGather) {
+          const int mb = t.a_row0 / kXBM;
+          if (mb != ready_mb) {
+            // rows of this block are pushed by their owner (this rank included) in 8-row chunks
+            if (!wait_flag_ge(cm.ready[cm.rank] + mb, e1 * (kXBM / kGatherChunkRows))) {
+              *peer_fail = 1u; *abort_flag = 1u; ok = false; break;
+            }
+            asm volatile("fence.proxy.async;" ::: "memory");   // peer stores -> TMA reads
+            ready_mb = mb;
+          }
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (WQ4) {
+            if ((kb & 7) == 0) {
+              if (!mbar_wait(sc_empty + sslot, sphase ^ 1u, abort_flag, LIM)) { ok = false; break; }
+              mbar_arrive_expect_tx(sc_full + sslot, S::kScaleSlot);
+              tma_load_2d(sScale + sslot * S::kScaleSlot, &tmap_s, sc_full + sslot, kb, t.w_row0);
+              tma_load_2d(sScale + sslot * S::kScaleSlot + BN * 16, &tmap_b, sc_full + sslot, kb, t.w_row0);
+              if (++sslot == 2) { sslot = 0; sphase ^= 1u; }
+            }
+            if (!mbar_wait(raw_empty + rstage, rphase ^ 1u, abort_flag, LIM)) { ok = false; break; }
+            mbar_arrive_expect_tx(raw_full + rstage, S::kStageRaw);
+            tma_load_2d(sRaw + rstage * S::kStageRaw, &tmap_w, raw_full + rstage, kb * 32, t.w_row0);
+            if (++rstage == RAW) { rstage = 0; rphase ^= 1u; }
+          }
+          if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
+          mbar_arrive_expect_tx(full + stage, S::kStageA + (WQ4 ? 0 : S::kStageB));
+          tma_load_2d(sA + stage * S::kStageA, ta, full + stage, kb * kXBK, t.a_row0);
+          if (!WQ4) tma_load_2d(sB + stage * S::kStageB, &tmap_w, full + stage, kb * kXBK, t.w_row0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_bf16_f32(kXBM, BN);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!mbar_wait(acc_empty + acc, acc_phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(full + stage, phase, abort_flag, LIM)) { ok = false; break; }
+          if (WQ4 && !mbar_wait(bq_full + stage, phase, abort_flag, LIM)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint32_t a_addr = smem_u32(sA + stage * S::kStageA);
+          const uint32_t b_addr = smem_u32(sB + stage * S::kStageB);
+#pragma unroll
+          for (int k = 0; k < kXBK / 16; ++k)
+            tc_mma_f16(d_tmem, umma_desc_sw128_kmajor(a_addr + k * 32),
+                       umma_desc_sw128_kmajor(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(empty + stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        tc_commit(acc_full + acc);
+        if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;            // 0..127 over the epilogue warps
+    int acc = 0;
+    uint32_t acc_phase = 0, epi_phase = 0;
+    bool ok = true;
+    if (RESIDUAL && !GROUPED) pdl_wait();
+
+    if (COMM == kCommGather) {
+      // push this rank's rows to every rank's gathered copy (its own included), chunk by chunk
+      const int chunks = cm.shard_rows / kGatherChunkRows;
+      const int vec_per_row = K / 8;
+      const size_t parity_off = ((e1 & 1u) == 0u) ? size_t(M) * K : 0;
+      for (int ch = blockIdx.x; ch < chunks; ch += gridDim.x) {
+        const int r0 = ch * kGatherChunkRows;
+        const int grow0 = cm.rank * cm.shard_rows + r0;
+        for (int pi = 0; pi < cm.world; ++pi) {
+          int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
+          __nv_bfloat16* dstb = cm.a_full[p] + parity_off + size_t(grow0) * K;
+          for (int i = et; i < kGatherChunkRows * vec_per_row; i += 128) {
+            const int r = i / vec_per_row, c = i % vec_per_row;
+            const uint4 v = *reinterpret_cast<const uint4*>(cm.a_shard + size_t(r0 + r) * cm.lda_shard + c * 8);
+            *reinterpret_cast<uint4*>(dstb + size_t(r) * K + c * 8) = v;
+          }
+        }
+        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM)) break;
+        if (et == 0) {
+          __threadfence_system();
+          for (int p = 0; p < cm.world; ++p) red_release_sys_add(cm.ready[p] + grow0 / kXBM, 1u);
+        }
+      }
+    }
+
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const XTile t = x_tile<BN, GROUPED>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
+      if (!mbar_wait(acc_full + acc, acc_phase, abort_flag, LIM)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int row = t.a_row0 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+      if (COMM == kCommReduce) {
+        // partial tile -> the owner's staging slab, laid out so that each warp-wide store is one
+        // contiguous 512-byte run: 16-byte group (c*4+v) of row r sits at ((c*4+v)*128 + r)*16.
+        const int owner = tile % cm.world, slot = tile / cm.world;
+        __nv_bfloat16* sbase = cm.stage[owner] +
+                               (size_t(cm.rank) * cm.tiles_owned_max + slot) * size_t(kXBM * BN);
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = pack_bf16(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+            o.y = pack_bf16(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+            o.z = pack_bf16(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+            o.w = pack_bf16(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+            *reinterpret_cast<uint4*>(sbase + (size_t(c * 4 + v) * kXBM + q * 32 + lane) * 8) = o;
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + acc);
+        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM)) { ok = false; break; }
+        if (et == 0) {
+          __threadfence_system();
+          red_release_sys_add(cm.tile_flags[owner] + slot, 1u);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + c * 32, r);
+          tmem_ld_wait();
+          const int col0 = t.c_col0 + c * 32;
+          if (row < t.row_end && col0 < N) {
+            __nv_bfloat16* dst = C + size_t(row) * ldc + col0;
+            const __nv_bfloat16* res = RESIDUAL ? residual + size_t(row) * ldc + col0 : nullptr;
+            if (col0 + 32 <= N) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float f[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] = __uint_as_float(r[v * 8 + j]);
+                if (RESIDUAL) {
+                  const uint4 rv = *reinterpret_cast<const uint4*>(res + v * 8);
+                  f[0] += bf16lo(rv.x); f[1] += bf16hi(rv.x); f[2] += bf16lo(rv.y); f[3] += bf16hi(rv.y);
+                  f[4] += bf16lo(rv.z); f[5] += bf16hi(rv.z); f[6] += bf16lo(rv.w); f[7] += bf16hi(rv.w);
+                }
+                uint4 o;
+                o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+                o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+                *reinterpret_cast<uint4*>(dst + v * 8) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < N) {
+                  float f = __uint_as_float(r[j]);
+                  if (RESIDUAL) f += __bfloat162float(res[j]);
+                  dst[j] = __float2bfloat16_rn(f);
+                }
+              }
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + acc);
+      }
+      if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
+    }
+
+    if (COMM == kCommReduce) {
+      // owner side: sum the world's partials of each tile this rank owns, add the residual once,
+      // store the finished tile into every rank's output, then count it as done everywhere.
+      constexpr int GROUPS = BN / 8;
+      const int n_owned = (num_tiles - cm.rank + cm.world - 1) / cm.world;
+      for (int j = blockIdx.x; j < n_owned; j += gridDim.x) {
+        if (et == 0 && !wait_flag_ge(cm.tile_flags[cm.rank] + j, e1 * uint32_t(cm.world))) {
+          *peer_fail = 1u; *abort_flag = 1u;
+        }
+        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM) || *abort_flag) break;
+        const int tile = j * cm.world + cm.rank;
+        const XTile t = x_tile<BN, false>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, 0);
+        const __nv_bfloat16* sl = cm.stage[cm.rank] + size_t(j) * size_t(kXBM * BN);
+        const size_t src_stride = size_t(cm.tiles_owned_max) * size_t(kXBM * BN);
+        for (int i = et; i < kXBM * GROUPS; i += 128) {
+          const int g = i % GROUPS, r = i / GROUPS;
+          float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          for (int s = 0; s < cm.world; ++s) {
+            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(sl + s * src_stride + (size_t(g) * kXBM + r) * 8));
+            f[0] += bf16lo(v.x); f[1] += bf16hi(v.x); f[2] += bf16lo(v.y); f[3] += bf16hi(v.y);
+            f[4] += bf16lo(v.z); f[5] += bf16hi(v.z); f[6] += bf16lo(v.w); f[7] += bf16hi(v.w);
+          }
+          const int row = t.a_row0 + r, col = t.c_col0 + g * 8;
+          if (row < M && col < N) {                // N is a multiple of 8 (checked by the launcher)
+            const size_t off = size_t(row) * ldc + col;
+            if (RESIDUAL) {
+              const uint4 rv = *reinterpret_cast<const uint4*>(residual + off);
+              f[0] += bf16lo(rv.x); f[1] += bf16hi(rv.x); f[2] += bf16lo(rv.y); f[3] += bf16hi(rv.y);
+              f[4] += bf16lo(rv.z); f[5] += bf16hi(rv.z); f[6] += bf16lo(rv.w); f[7] += bf16hi(rv.w);
+            }
+            uint4 o;
+            o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+            o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+            for (int pi = 0; pi < cm.world; ++pi) {
+              int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
+              *reinterpret_cast<uint4*>(cm.out[p] + off) = o;
+            }
+          }
+        }
+        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM)) break;
+        if (et == 0) {
+          __threadfence_system();
+          for (int p = 0; p < cm.world; ++p) red_release_sys_add(cm.done[p], 1u);
+        }
+      }
+      // every tile of the result has landed here before this rank's kernel ends
+      if (et == 0 && !*abort_flag) {
+        if (!wait_flag_ge(cm.done[cm.rank], e1 * uint32_t(num_tiles))) { *peer_fail = 1u; *abort_flag = 1u; }
+      }
+    }
+  } else if (WQ4) {
+    // ------------------------------------------------------------------ dequant (warps 6..9)
+    const int dt = threadIdx.x - 192;   // 0..127
+    int stage = 0, rstage = 0, sslot = 0;
+    uint32_t phase = 0, rphase = 0, sphase = 0;
+    bool ok = true;
+    const __nv_bfloat162 k128 = __float2bfloat162_rn(128.f);
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if ((kb & 7) == 0 && !mbar_wait(sc_full + sslot, sphase, abort_flag, LIM)) { ok = false; break; }
+        if (!mbar_wait(raw_full + rstage, rphase, abort_flag, LIM)) { ok = false; break; }
+        if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, LIM)) { ok = false; break; }  // B slot free
+        const char* raw = sRaw + rstage * S::kStageRaw;
+        const __nv_bfloat16* sc = reinterpret_cast<const __nv_bfloat16*>(sScale + sslot * S::kScaleSlot);
+        const __nv_bfloat16* bi = sc + BN * 8;
+        char* bst = sB + stage * S::kStageB;
+#pragma unroll
+        for (int it = 0; it < (BN * 2) / 128; ++it) {
+          const int item = it * 128 + dt;
+          const int r = item % BN, h = item / BN;     // row of the W tile, which half of the 64 k
+          const uint4 wv = *reinterpret_cast<const uint4*>(raw + r * 32 + h * 16);
+          const __nv_bfloat162 s2 = __bfloat162bfloat162(sc[r * 8 + (kb & 7)]);
+          const __nv_bfloat162 b2 = __bfloat162bfloat162(bi[r * 8 + (kb & 7)]);
+          const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t w = words[j];
+            // (128 + q) is exact in bf16: the nibble goes into the low mantissa bits of 128.0
+            uint32_t p04 = (w & 0x000f000fu) | 0x43004300u;            // (k0, k4)
+            uint32_t p15 = ((w >> 4) & 0x000f000fu) | 0x43004300u;     // (k1, k5)
+            uint32_t p26 = ((w >> 8) & 0x000f000fu) | 0x43004300u;     // (k2, k6)
+            uint32_t p37 = ((w >> 12) & 0x000f000fu) | 0x43004300u;    // (k3, k7)
+            __nv_bfloat162 v04 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p04), k128), s2, b2);
+            __nv_bfloat162 v15 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p15), k128), s2, b2);
+            __nv_bfloat162 v26 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p26), k128), s2, b2);
+            __nv_bfloat162 v37 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p37), k128), s2, b2);
+            const uint32_t u04 = *reinterpret_cast<uint32_t*>(&v04), u15 = *reinterpret_cast<uint32_t*>(&v15);
+            const uint32_t u26 = *reinterpret_cast<uint32_t*>(&v26), u37 = *reinterpret_cast<uint32_t*>(&v37);
+            uint4 o;   // natural k order: (k0,k1) (k2,k3) (k4,k5) (k6,k7)
+            o.x = __byte_perm(u04, u15, 0x5410); o.y = __byte_perm(u26, u37, 0x5410);
+            o.z = __byte_perm(u04, u15, 0x7632); o.w = __byte_perm(u26, u37, 0x7632);
+            const int c = h * 4 + j;                   // 16-byte chunk of the 128-byte row
+            *reinterpret_cast<uint4*>(bst + r * 128 + ((c ^ (r & 7)) << 4)) = o;
+          }
+        }
+        fence_proxy_async_smem();     // generic-proxy stores -> visible to the tensor core's reads
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(bq_full + stage);
+          mbar_arrive(raw_empty + rstage);
+          if ((kb & 7) == 7 || kb == num_kb - 1) mbar_arrive(sc_empty + sslot);
+        }
+        if ((kb & 7) == 7 || kb == num_kb - 1) { if (++sslot == 2) { sslot = 0; sphase ^= 1u; } }
+        if (++rstage == RAW) { rstage = 0; rphase ^= 1u; }
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) { tc_fence_after_sync(); tmem_dealloc(tmem_base, TMEM_COLS); }
+  if (threadIdx.x == 0) {
+    if (*abort_flag && status) atomicExch(status, *peer_fail ? kStatusPeerTimeout : kStatusMbarTimeout);
+    if (COMM != kCommNone) {
+      // the last CTA to leave advances the site's epoch for the next call
+      __threadfence();
+      if (atomicAdd(cm.epoch + 1, 1u) == gridDim.x - 1) { cm.epoch[1] = 0u; cm.epoch[0] = e1; }
+    }
+  }
+  pdl_launch_dependents();
+}
+
+template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM = kCommNone>
+static int launch_x(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tw,
+                    const CUtensorMap& ts, const CUtensorMap& tb, void* C, const void* residual,
+                    const int* offsets, int E, int M, int N, int K, int ldc, int* status, int pdl,
+                    cudaStream_t st, const XComm& cm = XComm()) {
+  using S = XSmem<BN, WQ4>;
+  auto kern = xgemm_kernel<BN, WQ4, GROUPED, RESIDUAL, COMM>;
+  RB_CHECK(set_max_smem(kern, S::kBytes));
+  int tiles = ((M + kXBM - 1) / kXBM) * ((N + BN - 1) / BN);
+  if (GROUPED) tiles += E * ((N + BN - 1) / BN);   // upper bound: every group may add a ragged tile
+  const int grid = tiles < sm_count() ? (tiles > 0 ? tiles : 1) : sm_count();
+  return launch(kern, dim3(grid), dim3(S::kThreads), size_t(S::kBytes), st, pdl != 0, ta, ta2, tw, ts, tb,
+                static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(residual), offsets, E,
+                M, N, K, ldc, status, cm);
+}
+
+// Tensor maps of the weight operand (and of its scales/biases for Q4).
+static inline int x_weight_maps(int w_kind, const void* W, const void* scales, const void* biases,
+                                uint64_t rowsW, int K, int bn, CUtensorMap* tw, CUtensorMap* ts,
+                                CUtensorMap* tb) {
+  int rc;
+  if (w_kind == 0) {
+    rc = make_tmap_2d_bf16(tw, W, uint64_t(K), rowsW, uint64_t(K) * 2, kXBK, bn);
+    if (rc) return rc;
+    *ts = *tw; *tb = *tw;
+    return 0;
+  }
+  rc = make_tmap_2d(tw, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, W, uint64_t(K) / 2, rowsW, uint64_t(K) / 2,
+                    32, bn, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  rc = make_tmap_2d(ts, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, scales, uint64_t(K) / 64, rowsW,
+                    uint64_t(K) / 64 * 2, 8, bn, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  return make_tmap_2d(tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, biases, uint64_t(K) / 64, rowsW,
+                      uint64_t(K) / 64 * 2, 8, bn, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+}  // namespace rb
