@@ -50,7 +50,7 @@ extern "C" int rmlx_tp_gemm_allreduce(int w_kind, const void* A, const void* W, 
                                       const void* biases, const void* residual, void* const* stage,
                                       void* const* tile_flags, void* const* out, void* const* done,
                                       void* epoch, int rank, int world, int M, int N, int K, int lda,
-                                      int ldc, int bn, int* status, cudaStream_t st) {
+                                      int ldc, int bn, int* status, void* trace, cudaStream_t st) {
   if (world < 1 || world > kXMaxRanks || rank < 0 || rank >= world) return -2;
   if (M < 1 || N < 8 || N % 8 || ldc % 8 || K < 8 || K % 8 || lda % 8) return -2;
   if (w_kind == 1 && K % 512) return -2;
@@ -64,6 +64,7 @@ extern "C" int rmlx_tp_gemm_allreduce(int w_kind, const void* A, const void* W, 
   XComm cm;
   cm.rank = rank; cm.world = world;
   cm.epoch = static_cast<uint32_t*>(epoch);
+  cm.trace = static_cast<unsigned long long*>(trace);   // optional [grid][8] phase timestamps
   const int tiles = ((M + kXBM - 1) / kXBM) * ((N + bn - 1) / bn);
   cm.tiles_owned_max = (tiles + world - 1) / world;
   for (int p = 0; p < world; ++p) {
@@ -82,7 +83,7 @@ extern "C" int rmlx_tp_allgather_gemm(int w_kind, const void* a_shard, int lda_s
                                       void* const* a_full, void* const* ready, void* epoch,
                                       const void* W, const void* scales, const void* biases, void* C,
                                       const void* residual, int rank, int world, int N, int K,
-                                      int ldc, int bn, int* status, cudaStream_t st) {
+                                      int ldc, int bn, int* status, void* trace, cudaStream_t st) {
   if (world < 1 || world > kXMaxRanks || rank < 0 || rank >= world) return -2;
   if (shard_rows < kXBM || shard_rows % kXBM || lda_shard % 8 || K < 8 || K % 8 || N < 1) return -2;
   if (w_kind == 1 && K % 512) return -2;
@@ -100,6 +101,7 @@ extern "C" int rmlx_tp_allgather_gemm(int w_kind, const void* a_shard, int lda_s
   XComm cm;
   cm.rank = rank; cm.world = world;
   cm.epoch = static_cast<uint32_t*>(epoch);
+  cm.trace = static_cast<unsigned long long*>(trace);   // optional [grid][8] phase timestamps
   cm.a_shard = static_cast<const __nv_bfloat16*>(a_shard);
   cm.lda_shard = lda_shard; cm.shard_rows = shard_rows;
   for (int p = 0; p < world; ++p) {

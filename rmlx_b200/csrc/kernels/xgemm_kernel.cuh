@@ -28,6 +28,7 @@ constexpr int kXMaxExperts = 256;
 constexpr int kXMaxRanks = 8;
 constexpr int kCommNone = 0, kCommReduce = 1, kCommGather = 2;
 constexpr int kGatherChunkRows = 8;
+constexpr int kCommThreads = 160;   // collective modes: four reducer/pusher warps + one signalling warp
 
 struct XComm {
   int rank = 0, world = 1;
@@ -43,6 +44,7 @@ struct XComm {
   int lda_shard = 0, shard_rows = 0;
   __nv_bfloat16* a_full[kXMaxRanks] = {};    // rank p's gathered copy, two parities [2][M][K]
   uint32_t* ready[kXMaxRanks] = {};          // rank p's counter per 128-row block
+  unsigned long long* trace = nullptr;       // optional [grid][8] timestamps (see x_trace)
 };
 
 template <int BN, bool WQ4>
@@ -68,14 +70,16 @@ struct XTile {
 
 // tile id -> coordinates. Plain: column-block major so consecutive CTAs share a W tile; ``rot``
 // rotates the row blocks so that a rank starts with the rows it already holds (gather mode).
-template <int BN, bool GROUPED>
+template <int BN, bool GROUPED, bool ROW_MAJOR = false>
 __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int tiles_n,
                                         const int* s_off, const int* s_tprefix, int E, int rot = 0) {
   XTile t;
   if (!GROUPED) {
-    int tm = tile % tiles_m + rot;
+    // ROW_MAJOR (gather mode): all column tiles of a row block before the next row block, so the
+    // rotation really puts every tile of the local rows first
+    int tm = (ROW_MAJOR ? tile / tiles_n : tile % tiles_m) + rot;
     if (tm >= tiles_m) tm -= tiles_m;
-    const int tn = tile / tiles_m;
+    const int tn = ROW_MAJOR ? tile % tiles_n : tile / tiles_m;
     t.a_row0 = tm * kXBM; t.row_end = M; t.w_row0 = tn * BN; t.c_col0 = tn * BN;
   } else {
     int e = 0;
@@ -91,6 +95,17 @@ __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int
   return t;
 }
 
+// Optional phase trace of the collective modes: slot k of this CTA's row gets the global timer
+// (0 start, 1 last MMA issued, 2 epilogue done, 3 collective warps done, 4 exit).
+template <int COMM>
+__device__ __forceinline__ void x_trace(const XComm& cm, int k) {
+  if (COMM != kCommNone && cm.trace) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    cm.trace[blockIdx.x * 8 + k] = t;
+  }
+}
+
 // Barrier over the four epilogue warps, built on an mbarrier so that it is bounded like every other
 // wait: if a warp left early after a timeout, the rest give up too instead of waiting for it.
 __device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase, volatile uint32_t* abort_flag,
@@ -101,8 +116,61 @@ __device__ __forceinline__ bool epi_sync(uint64_t* bar, uint32_t& phase, volatil
   return ok;
 }
 
+// Owner-side sum of one tile: a warp covers 4 rows x 8 sixteen-byte groups per step (64-byte runs
+// of the staging layout in, 128-byte runs of output rows out) and keeps U steps x W sources of loads
+// in flight. The residual is added once, here.
+template <int BN, bool RESIDUAL, int W, int U>
+__device__ __forceinline__ void x_reduce_tile(const XComm& cm, const __nv_bfloat16* sl, size_t src_stride,
+                                              const XTile& t, int M, int N, int ldc,
+                                              const __nv_bfloat16* residual, int cw, int lane) {
+  constexpr int GB = BN / 64;
+  constexpr int STEPS = (kXBM / 4) * GB;
+  for (int step0 = cw * U; step0 < STEPS; step0 += 4 * U) {
+    uint4 pv[U][W];
+    uint4 rv[U];
+    size_t off[U];
+    bool inb[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int step = step0 + u;
+      const int g = (step % GB) * 8 + (lane & 7), r = (step / GB) * 4 + (lane >> 3);
+#pragma unroll
+      for (int s = 0; s < W; ++s)
+        if (s < cm.world)
+          pv[u][s] = __ldcg(reinterpret_cast<const uint4*>(sl + s * src_stride + (size_t(g) * kXBM + r) * 8));
+      const int row = t.a_row0 + r, col = t.c_col0 + g * 8;
+      inb[u] = row < M && col < N;              // N is a multiple of 8 (checked by the launcher)
+      off[u] = size_t(row) * ldc + col;
+      rv[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (RESIDUAL && inb[u]) rv[u] = *reinterpret_cast<const uint4*>(residual + off[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float f[8] = {bf16lo(rv[u].x), bf16hi(rv[u].x), bf16lo(rv[u].y), bf16hi(rv[u].y),
+                    bf16lo(rv[u].z), bf16hi(rv[u].z), bf16lo(rv[u].w), bf16hi(rv[u].w)};
+#pragma unroll
+      for (int s = 0; s < W; ++s) {
+        if (s < cm.world) {
+          const uint4 v = pv[u][s];
+          f[0] += bf16lo(v.x); f[1] += bf16hi(v.x); f[2] += bf16lo(v.y); f[3] += bf16hi(v.y);
+          f[4] += bf16lo(v.z); f[5] += bf16hi(v.z); f[6] += bf16lo(v.w); f[7] += bf16hi(v.w);
+        }
+      }
+      if (inb[u]) {
+        uint4 o;
+        o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
+        o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
+        for (int pi = 0; pi < cm.world; ++pi) {
+          int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
+          *reinterpret_cast<uint4*>(cm.out[p] + off[u]) = o;
+        }
+      }
+    }
+  }
+}
+
 template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM>
-__global__ void __launch_bounds__((XSmem<BN, WQ4>::kThreads), 1)
+__global__ void __launch_bounds__((XSmem<BN, WQ4>::kThreads + (COMM != kCommNone ? kCommThreads : 0)), 1)
 xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a2,
              const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
              const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16* __restrict__ C,
@@ -113,6 +181,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   constexpr int STAGES = S::kStages, RAW = S::kRawStages;
   // a role may be waiting, through the pipeline, on a peer that started late: be more patient then
   constexpr uint32_t LIM = (COMM == kCommNone) ? kMbarPollLimit : (kMbarPollLimit << 4);
+  constexpr int kCommWarp0 = S::kThreads / 32;          // first of the five collective-mode warps
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
   extern __shared__ char smem_raw[];
   char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -131,8 +200,10 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   uint64_t* sc_empty = sc_full + 2;             // [2]
   uint64_t* acc_full = sc_empty + 2;            // [2]
   uint64_t* acc_empty = acc_full + 2;           // [2]
-  uint64_t* epi_mb = acc_empty + 2;             // [1] epilogue-warp barrier (collective modes)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(epi_mb + 1);
+  uint64_t* sig_full = acc_empty + 2;           // [2] partial tile stored by the epilogue warps
+  uint64_t* sig_free = sig_full + 2;            // [2] its signal has gone out
+  uint64_t* comm_mb = sig_free + 2;             // [1] collective-warp barrier
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(comm_mb + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile uint32_t* peer_fail = tmem_slot + 2;
   int* s_off = reinterpret_cast<int*>(after + 512);          // [E+1]
@@ -150,7 +221,8 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       mbar_init(sc_full + i, 1); mbar_init(sc_empty + i, 4);
       mbar_init(acc_full + i, 1); mbar_init(acc_empty + i, 4);
     }
-    mbar_init(epi_mb, 128);
+    for (int i = 0; i < 2; ++i) { mbar_init(sig_full + i, 128); mbar_init(sig_free + i, 1); }
+    mbar_init(comm_mb, 128);
     *abort_flag = 0u;
     *peer_fail = 0u;
     fence_mbar_init();
@@ -176,6 +248,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   }
   const int num_tiles = GROUPED ? s_tprefix[E] : tiles_m * tiles_n;
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) x_trace<COMM>(cm, 0);
   // collective modes: calls completed so far on this site; counters only grow, so a call waits
   // for (epoch+1) x the per-call increment and nothing is ever reset.
   const uint32_t e1 = (COMM != kCommNone) ? cm.epoch[0] + 1u : 0u;
@@ -193,7 +266,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       bool ok = true;
       int ready_mb = -1;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const XTile t = x_tile<BN, GROUPED>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
+        const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
         if (COMM == kCommGather) {
           const int mb = t.a_row0 / kXBM;
           if (mb != ready_mb) {
@@ -255,43 +328,20 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         tc_commit(acc_full + acc);
         if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
       }
+      x_trace<COMM>(cm, 1);
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;
     const int et = threadIdx.x - 64;            // 0..127 over the epilogue warps
+    (void)et;
     int acc = 0;
-    uint32_t acc_phase = 0, epi_phase = 0;
+    uint32_t acc_phase = 0;
     bool ok = true;
     if (RESIDUAL && !GROUPED) pdl_wait();
 
-    if (COMM == kCommGather) {
-      // push this rank's rows to every rank's gathered copy (its own included), chunk by chunk
-      const int chunks = cm.shard_rows / kGatherChunkRows;
-      const int vec_per_row = K / 8;
-      const size_t parity_off = ((e1 & 1u) == 0u) ? size_t(M) * K : 0;
-      for (int ch = blockIdx.x; ch < chunks; ch += gridDim.x) {
-        const int r0 = ch * kGatherChunkRows;
-        const int grow0 = cm.rank * cm.shard_rows + r0;
-        for (int pi = 0; pi < cm.world; ++pi) {
-          int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
-          __nv_bfloat16* dstb = cm.a_full[p] + parity_off + size_t(grow0) * K;
-          for (int i = et; i < kGatherChunkRows * vec_per_row; i += 128) {
-            const int r = i / vec_per_row, c = i % vec_per_row;
-            const uint4 v = *reinterpret_cast<const uint4*>(cm.a_shard + size_t(r0 + r) * cm.lda_shard + c * 8);
-            *reinterpret_cast<uint4*>(dstb + size_t(r) * K + c * 8) = v;
-          }
-        }
-        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM)) break;
-        if (et == 0) {
-          __threadfence_system();
-          for (int p = 0; p < cm.world; ++p) red_release_sys_add(cm.ready[p] + grow0 / kXBM, 1u);
-        }
-      }
-    }
-
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const XTile t = x_tile<BN, GROUPED>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
+      const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
       if (!mbar_wait(acc_full + acc, acc_phase, abort_flag, LIM)) { ok = false; break; }
       tc_fence_after_sync();
       const int row = t.a_row0 + q * 32 + lane;
@@ -320,11 +370,11 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty + acc);
-        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM)) { ok = false; break; }
-        if (et == 0) {
-          __threadfence_system();
-          red_release_sys_add(cm.tile_flags[owner] + slot, 1u);
-        }
+        // hand the tile to the signalling warp: it makes the stores visible system-wide and bumps
+        // the owner's counter, off this warp's critical path (the slot is free again once the
+        // signal two tiles back has gone out)
+        if (!mbar_wait(sig_free + acc, acc_phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
+        mbar_arrive(sig_full + acc);
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -369,58 +419,96 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       }
       if (++acc == 2) { acc = 0; acc_phase ^= 1u; }
     }
-
-    if (COMM == kCommReduce) {
-      // owner side: sum the world's partials of each tile this rank owns, add the residual once,
-      // store the finished tile into every rank's output, then count it as done everywhere.
-      constexpr int GROUPS = BN / 8;
+    if (et == 0) x_trace<COMM>(cm, 2);
+  } else if (COMM == kCommReduce && warp == kCommWarp0 + 4) {
+    // ------------------------------------------------------------------ signalling warp
+    if (lane == 0) {
+      int acc = 0;
+      uint32_t ph = 0;
+      for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+        if (!mbar_wait(sig_full + acc, ph, abort_flag, LIM)) break;
+        __threadfence_system();
+        red_release_sys_add(cm.tile_flags[tile % cm.world] + tile / cm.world, 1u);
+        mbar_arrive(sig_free + acc);
+        if (++acc == 2) { acc = 0; ph ^= 1u; }
+      }
+    }
+  } else if (COMM != kCommNone && warp >= kCommWarp0 && warp < kCommWarp0 + 4) {
+    // ------------------------------------------------------------------ collective warps (4)
+    const int ct = threadIdx.x - kCommWarp0 * 32;     // 0..127
+    uint32_t cphase = 0;
+    if (COMM == kCommGather) {
+      // push this rank's rows to every rank's gathered copy (its own included), 8 rows at a time,
+      // four 16-byte loads in flight per thread
+      const int chunks = cm.shard_rows / kGatherChunkRows;
+      const int vec_per_row = K / 8;
+      const int vecs = kGatherChunkRows * vec_per_row;
+      const size_t parity_off = ((e1 & 1u) == 0u) ? size_t(M) * K : 0;
+      for (int ch = blockIdx.x; ch < chunks; ch += gridDim.x) {
+        const int r0 = ch * kGatherChunkRows;
+        const int grow0 = cm.rank * cm.shard_rows + r0;
+        for (int i0 = ct; i0 < vecs; i0 += 4 * 128) {
+          uint4 v[4];
+          size_t doff[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 128;
+            if (i < vecs) {
+              const int r = i / vec_per_row, c = i % vec_per_row;
+              v[u] = __ldcs(reinterpret_cast<const uint4*>(cm.a_shard + size_t(r0 + r) * cm.lda_shard + c * 8));
+              doff[u] = parity_off + size_t(grow0 + r) * K + c * 8;
+            }
+          }
+          for (int pi = 0; pi < cm.world; ++pi) {
+            int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (i0 + u * 128 < vecs) *reinterpret_cast<uint4*>(cm.a_full[p] + doff[u]) = v[u];
+          }
+        }
+        if (!epi_sync(comm_mb, cphase, abort_flag, LIM)) break;
+        if (ct == 0) {
+          __threadfence_system();
+          for (int p = 0; p < cm.world; ++p) red_release_sys_add(cm.ready[p] + grow0 / kXBM, 1u);
+        }
+      }
+      if (ct == 0) x_trace<COMM>(cm, 3);
+    } else {
+      // owner side, concurrent with the main loop: sum the world's partials of each tile this rank
+      // owns, add the residual once, store the finished tile into every rank's output, count it as
+      // done everywhere. A warp covers 4 rows x 8 groups per step: 64-byte runs of the staging
+      // layout in, 128-byte runs of output rows out.
+      const int cw = ct >> 5;
       const int n_owned = (num_tiles - cm.rank + cm.world - 1) / cm.world;
+      const size_t src_stride = size_t(cm.tiles_owned_max) * size_t(kXBM * BN);
+      int tiles_done = 0;
       for (int j = blockIdx.x; j < n_owned; j += gridDim.x) {
-        if (et == 0 && !wait_flag_ge(cm.tile_flags[cm.rank] + j, e1 * uint32_t(cm.world))) {
+        if (ct == 0 && !wait_flag_ge(cm.tile_flags[cm.rank] + j, e1 * uint32_t(cm.world), kPeerPollLimit << 2)) {
           *peer_fail = 1u; *abort_flag = 1u;
         }
-        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM) || *abort_flag) break;
+        if (!epi_sync(comm_mb, cphase, abort_flag, LIM) || *abort_flag) break;
         const int tile = j * cm.world + cm.rank;
         const XTile t = x_tile<BN, false>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, 0);
         const __nv_bfloat16* sl = cm.stage[cm.rank] + size_t(j) * size_t(kXBM * BN);
-        const size_t src_stride = size_t(cm.tiles_owned_max) * size_t(kXBM * BN);
-        for (int i = et; i < kXBM * GROUPS; i += 128) {
-          const int g = i % GROUPS, r = i / GROUPS;
-          float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-          for (int s = 0; s < cm.world; ++s) {
-            const uint4 v = __ldcg(reinterpret_cast<const uint4*>(sl + s * src_stride + (size_t(g) * kXBM + r) * 8));
-            f[0] += bf16lo(v.x); f[1] += bf16hi(v.x); f[2] += bf16lo(v.y); f[3] += bf16hi(v.y);
-            f[4] += bf16lo(v.z); f[5] += bf16hi(v.z); f[6] += bf16lo(v.w); f[7] += bf16hi(v.w);
-          }
-          const int row = t.a_row0 + r, col = t.c_col0 + g * 8;
-          if (row < M && col < N) {                // N is a multiple of 8 (checked by the launcher)
-            const size_t off = size_t(row) * ldc + col;
-            if (RESIDUAL) {
-              const uint4 rv = *reinterpret_cast<const uint4*>(residual + off);
-              f[0] += bf16lo(rv.x); f[1] += bf16hi(rv.x); f[2] += bf16lo(rv.y); f[3] += bf16hi(rv.y);
-              f[4] += bf16lo(rv.z); f[5] += bf16hi(rv.z); f[6] += bf16lo(rv.w); f[7] += bf16hi(rv.w);
-            }
-            uint4 o;
-            o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
-            o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
-            for (int pi = 0; pi < cm.world; ++pi) {
-              int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
-              *reinterpret_cast<uint4*>(cm.out[p] + off) = o;
-            }
-          }
-        }
-        if (!epi_sync(epi_mb, epi_phase, abort_flag, LIM)) break;
-        if (et == 0) {
-          __threadfence_system();
-          for (int p = 0; p < cm.world; ++p) red_release_sys_add(cm.done[p], 1u);
-        }
+        if (cm.world <= 2) x_reduce_tile<BN, RESIDUAL, 2, 4>(cm, sl, src_stride, t, M, N, ldc, residual, cw, lane);
+        else if (cm.world <= 4) x_reduce_tile<BN, RESIDUAL, 4, 2>(cm, sl, src_stride, t, M, N, ldc, residual, cw, lane);
+        else x_reduce_tile<BN, RESIDUAL, 8, 1>(cm, sl, src_stride, t, M, N, ldc, residual, cw, lane);
+        ++tiles_done;
       }
+      // one visibility fence and one count per peer for everything this CTA reduced
+      if (epi_sync(comm_mb, cphase, abort_flag, LIM) && ct == 0 && tiles_done > 0) {
+        __threadfence_system();
+        for (int p = 0; p < cm.world; ++p) red_release_sys_add(cm.done[p], uint32_t(tiles_done));
+      }
+      if (ct == 0) x_trace<COMM>(cm, 3);
       // every tile of the result has landed here before this rank's kernel ends
-      if (et == 0 && !*abort_flag) {
-        if (!wait_flag_ge(cm.done[cm.rank], e1 * uint32_t(num_tiles))) { *peer_fail = 1u; *abort_flag = 1u; }
+      if (ct == 0 && !*abort_flag) {
+        if (!wait_flag_ge(cm.done[cm.rank], e1 * uint32_t(num_tiles), kPeerPollLimit << 2)) {
+          *peer_fail = 1u; *abort_flag = 1u;
+        }
       }
     }
-  } else if (WQ4) {
+  } else if (WQ4 && warp < 10) {
     // ------------------------------------------------------------------ dequant (warps 6..9)
     const int dt = threadIdx.x - 192;   // 0..127
     int stage = 0, rstage = 0, sslot = 0;
@@ -483,6 +571,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   __syncthreads();
   if (warp == 1) { tc_fence_after_sync(); tmem_dealloc(tmem_base, TMEM_COLS); }
   if (threadIdx.x == 0) {
+    x_trace<COMM>(cm, 4);
     if (*abort_flag && status) atomicExch(status, *peer_fail ? kStatusPeerTimeout : kStatusMbarTimeout);
     if (COMM != kCommNone) {
       // the last CTA to leave advances the site's epoch for the next call
@@ -504,7 +593,7 @@ static int launch_x(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtenso
   int tiles = ((M + kXBM - 1) / kXBM) * ((N + BN - 1) / BN);
   if (GROUPED) tiles += E * ((N + BN - 1) / BN);   // upper bound: every group may add a ragged tile
   const int grid = tiles < sm_count() ? (tiles > 0 ? tiles : 1) : sm_count();
-  return launch(kern, dim3(grid), dim3(S::kThreads), size_t(S::kBytes), st, pdl != 0, ta, ta2, tw, ts, tb,
+  return launch(kern, dim3(grid), dim3(S::kThreads + (COMM != kCommNone ? kCommThreads : 0)), size_t(S::kBytes), st, pdl != 0, ta, ta2, tw, ts, tb,
                 static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(residual), offsets, E,
                 M, N, K, ldc, status, cm);
 }

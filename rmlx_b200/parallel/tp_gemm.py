@@ -23,8 +23,8 @@ from .comm import SymmetricRegion
 
 _lib.register_cuda_sigs({
     "rmlx_tp_gemm_stage_bytes": ("iiii", "q"),
-    "rmlx_tp_gemm_allreduce": ("ippppppppppiiiiiiiipp", "i"),
-    "rmlx_tp_allgather_gemm": ("ipiippppppppiiiiiipp", "i"),
+    "rmlx_tp_gemm_allreduce": ("ippppppppppiiiiiiiippp", "i"),
+    "rmlx_tp_allgather_gemm": ("ipiippppppppiiiiiippp", "i"),
 })
 
 
@@ -69,6 +69,7 @@ class FusedGemmComm:
         self._out_views = [torch.as_tensor(_RawCuda(self.region.local + o, self.out_bytes), device=self.device)
                            for o in self.off_out]
         self._stage = self.region.peer_array(self.off_stage)
+        self.trace: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ counters per call shape
     def _site(self, key: Tuple, words: int) -> int:
@@ -106,7 +107,7 @@ class FusedGemmComm:
             w.kind, x.data_ptr(), w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases),
             _lib.ptr(residual), self._stage, rg.peer_array(off + 16), rg.peer_array(self.off_out[self._flip]),
             rg.peer_array(off + 8), ctypes.c_void_p(rg.local + off), self.rank, self.world, m, n, k,
-            x.stride(0), n, bn, GemmStatus.get(self.device).data_ptr(), _lib.stream_ptr())
+            x.stride(0), n, bn, GemmStatus.get(self.device).data_ptr(), _lib.ptr(self.trace), _lib.stream_ptr())
         _lib.check(rc, "tp_gemm_allreduce")
         return out
 
@@ -128,9 +129,22 @@ class FusedGemmComm:
             w.kind, x_shard.data_ptr(), x_shard.stride(0), ms, rg.peer_array(self.off_full),
             rg.peer_array(off + 16), ctypes.c_void_p(rg.local + off), w.w.data_ptr(), _lib.ptr(w.scales),
             _lib.ptr(w.biases), out.data_ptr(), _lib.ptr(residual), self.rank, self.world, w.n, k,
-            out.stride(0), bn, GemmStatus.get(self.device).data_ptr(), _lib.stream_ptr())
+            out.stride(0), bn, GemmStatus.get(self.device).data_ptr(), _lib.ptr(self.trace), _lib.stream_ptr())
         _lib.check(rc, "tp_allgather_gemm")
         return out
+
+    def enable_trace(self, on: bool = True) -> None:
+        """Record per-CTA phase timestamps of the next calls (see ``trace_summary``)."""
+        self.trace = torch.zeros(256, 8, dtype=torch.int64, device=self.device) if on else None
+
+    def trace_summary(self) -> Dict[str, float]:
+        """Microseconds from the first CTA's start to the latest CTA's mark, per phase, for the
+        last traced call: last MMA issued, epilogue done, collective warps done, exit."""
+        t = self.trace.cpu()
+        t = t[t[:, 0] > 0]
+        t0 = int(t[:, 0].min())
+        names = ("start_spread", "mma_issued", "epilogue_done", "collective_done", "exit")
+        return {n: (int(t[:, i].max()) - t0) / 1e3 for i, n in enumerate(names)}
 
     def status(self) -> int:
         return int(GemmStatus.get(self.device).item())
