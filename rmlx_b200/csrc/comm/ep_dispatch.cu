@@ -47,6 +47,18 @@ __device__ __forceinline__ void ep_fail(int* status, uint32_t code) {
   if (status) atomicExch(status, int(code));
 }
 
+// One warp copies a row of nvec 16-byte vectors with eight loads in flight per lane.
+__device__ __forceinline__ void ep_copy_row(uint4* __restrict__ dst, const uint4* __restrict__ src,
+                                            int nvec, int lane) {
+  for (int i = lane; i < nvec; i += 256) {
+    uint4 v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) if (i + u * 32 < nvec) v[u] = src[i + u * 32];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) if (i + u * 32 < nvec) dst[i + u * 32] = v[u];
+  }
+}
+
 // -------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kEpThreads)
 ep_dispatch_kernel(EpPeers pp, const __nv_bfloat16* __restrict__ x, int x_stride,
@@ -54,6 +66,8 @@ ep_dispatch_kernel(EpPeers pp, const __nv_bfloat16* __restrict__ x, int x_stride
                    int E, int capacity_rows, int* __restrict__ recv_offsets,
                    int* __restrict__ recv_rows, int* __restrict__ status) {
   __shared__ int s_myoff[kEpMaxExperts];     // where this rank's block of expert e starts (dest slab)
+  __shared__ int s_table[kEpMaxRanks * kEpMaxExperts];   // everyone's counts, row = source rank
+  __shared__ int s_total[kEpMaxExperts];     // pairs per expert over all ranks
   __shared__ int s_ok;
   const int rank = pp.rank, world = pp.world, e_local = E / world;
   uint32_t* ctl = pp.ctl[rank];
@@ -79,23 +93,35 @@ ep_dispatch_kernel(EpPeers pp, const __nv_bfloat16* __restrict__ x, int x_stride
   __syncthreads();
   bool ok = s_ok != 0;
 
-  // 2. block starts. Thread e handles global expert e.
-  const volatile uint32_t* table = ctl + 8 + E;
+  // 2. block starts. The table goes to shared memory in one coalesced pass (it is read many
+  // times); then thread e handles global expert e.
+  int* table = s_table;
+  if (ok) {
+    const volatile uint32_t* gt = ctl + 8 + E;
+    for (int i = threadIdx.x; i < world * E; i += blockDim.x) s_table[i] = int(gt[i]);
+  }
+  __syncthreads();
   if (ok) {
     for (int e = threadIdx.x; e < E; e += blockDim.x) {
-      const int dest = e / e_local, first = dest * e_local;
+      int tot = 0;
+      for (int s = 0; s < world; ++s) tot += table[s * E + e];
+      s_total[e] = tot;
+    }
+  }
+  __syncthreads();
+  if (ok) {
+    for (int e = threadIdx.x; e < E; e += blockDim.x) {
+      const int first = (e / e_local) * e_local;
       int base = 0;
-      for (int e2 = first; e2 < e; ++e2)
-        for (int s = 0; s < world; ++s) base += int(table[s * E + e2]);
+      for (int e2 = first; e2 < e; ++e2) base += s_total[e2];
       int before = 0;
-      for (int s = 0; s < rank; ++s) before += int(table[s * E + e]);
+      for (int s = 0; s < rank; ++s) before += table[s * E + e];
       s_myoff[e] = base + before;
     }
     // every rank sees the same table, so every rank takes the same decision on overflow
     if (threadIdx.x < world) {
       int total = 0;
-      for (int e = threadIdx.x * e_local; e < (threadIdx.x + 1) * e_local; ++e)
-        for (int s = 0; s < world; ++s) total += int(table[s * E + e]);
+      for (int e = threadIdx.x * e_local; e < (threadIdx.x + 1) * e_local; ++e) total += s_total[e];
       if (total > capacity_rows) { s_ok = 0; ep_fail(status, kEpStatusOverflow); }
     }
   }
@@ -105,8 +131,7 @@ ep_dispatch_kernel(EpPeers pp, const __nv_bfloat16* __restrict__ x, int x_stride
     // offsets of this rank's local experts for the grouped GEMM
     if (threadIdx.x <= e_local) {
       int acc = 0;
-      for (int e = rank * e_local; e < rank * e_local + threadIdx.x; ++e)
-        for (int s = 0; s < world; ++s) acc += int(table[s * E + e]);
+      for (int e = rank * e_local; e < rank * e_local + threadIdx.x; ++e) acc += s_total[e];
       recv_offsets[threadIdx.x] = acc;
       if (threadIdx.x == e_local && recv_rows) *recv_rows = acc;
     }
@@ -126,15 +151,8 @@ ep_dispatch_kernel(EpPeers pp, const __nv_bfloat16* __restrict__ x, int x_stride
       e = __shfl_sync(0xffffffffu, e, 0);
       pos = __shfl_sync(0xffffffffu, pos, 0);
       const int dest = e / e_local;
-      const uint4* src = reinterpret_cast<const uint4*>(x + size_t(p / top_k) * x_stride);
-      uint4* dst = reinterpret_cast<uint4*>(pp.slab[dest] + size_t(pos) * D);
-      for (int i = lane; i < D / 8; i += 128) {
-        uint4 v[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) if (i + u * 32 < D / 8) v[u] = src[i + u * 32];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) if (i + u * 32 < D / 8) dst[i + u * 32] = v[u];
-      }
+      ep_copy_row(reinterpret_cast<uint4*>(pp.slab[dest] + size_t(pos) * D),
+                  reinterpret_cast<const uint4*>(x + size_t(p / top_k) * x_stride), D / 8, lane);
       if (lane == 0) pp.meta[dest][pos] = (uint32_t(rank) << 24) | uint32_t(p);
     }
   }
@@ -177,15 +195,8 @@ ep_combine_kernel(EpPeers pp, uint32_t* __restrict__ ctl, const __nv_bfloat16* _
   for (int i = gw; i < rows; i += warps_total) {
     const uint32_t m = pp.meta[rank][i];
     const int src = int(m >> 24), pair = int(m & 0xffffffu);
-    const uint4* s = reinterpret_cast<const uint4*>(y + size_t(i) * D);
-    uint4* d = reinterpret_cast<uint4*>(pp.ret[src] + size_t(pair) * D);
-    for (int j = lane; j < D / 8; j += 128) {
-      uint4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) if (j + u * 32 < D / 8) v[u] = s[j + u * 32];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) if (j + u * 32 < D / 8) d[j + u * 32] = v[u];
-    }
+    ep_copy_row(reinterpret_cast<uint4*>(pp.ret[src] + size_t(pair) * D),
+                reinterpret_cast<const uint4*>(y + size_t(i) * D), D / 8, lane);
   }
   __syncthreads();
   if (threadIdx.x == 0) {

@@ -35,7 +35,7 @@ class FusedEpExchange:
     inbound rows per rank (default: twice the number of local pairs, at least 1024)."""
 
     def __init__(self, max_tokens: int, hidden: int, top_k: int, num_experts: int,
-                 capacity_rows: Optional[int] = None, group=None, device=None, blocks: int = 64):
+                 capacity_rows: Optional[int] = None, group=None, device=None, blocks: int = 128):
         self.group = group
         self.rank = dist.get_rank(group)
         self.world = dist.get_world_size(group)
