@@ -1,15 +1,22 @@
-"""Native prompt processing: the forward over many tokens of one sequence built from this package's
+"""Native many-token forward: prompt processing and large-batch decode built from this package's
 kernels only — RMSNorm, tcgen05 GEMMs (bf16 or Q4 dequantised in the main loop), RoPE + paged KV
-write, paged causal flash attention, and for MoE layers top-k routing, row scatter, two grouped
-tensor-core GEMMs with SwiGLU, and the weighted combine.
+write, paged flash attention (causal prefill kernel or split-KV decode kernel), and for MoE layers
+top-k routing, row scatter, two grouped tensor-core GEMMs with SwiGLU, and the weighted combine.
 
-Counterpart of ``TransformerModel::forward_prefill_graph`` (crates/rmlx-nn/src/transformer.rs:
-4416-4620), which encodes the 9 dispatches of a prefill layer into shared command buffers; here the
-launches go to one stream and the sum over tensor-parallel ranks is injected by the caller.
+``NativePrefill`` is the counterpart of ``TransformerModel::forward_prefill_graph``
+(crates/rmlx-nn/src/transformer.rs:4416-4620), which encodes the 9 dispatches of a prefill layer
+into shared command buffers. ``BatchedDecode`` serves decode batches beyond what the mat-vec
+kernels take (more than 4 rows): one token of each of B sequences per step, every shape static, so
+the whole step is captured in a CUDA graph (the reference's batched decode goes through the same
+GEMM kernels with M = batch, crates/rmlx-nn/src/transformer.rs:4250-4402).
+
+With tensor parallelism the row-parallel projections use the GEMM whose all-reduce runs inside the
+kernel (``parallel.tp_gemm``) when a ``gemm_comm`` is attached to the model; the MoE block's partial
+sums go through the injected ``allreduce``.
 """
 from __future__ import annotations
 
-from typing import Optional
+from typing import List, Optional, Sequence
 
 import torch
 
@@ -29,51 +36,44 @@ def _mm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = Non
     return qmm(x, w, residual=residual)
 
 
-class NativePrefill:
-    """Callable ``(token_ids, cache, seq_id) -> last-token logits [1, vocab_local]`` (fp32)."""
+def _check_model(model) -> None:
+    cfg = model.cfg
+    if cfg.head_dim not in (64, 128):
+        raise ImportError("the native forward covers head_dim 64 and 128")
+    if model.w.embed.dtype != torch.bfloat16:
+        raise ImportError("the native forward needs bf16 activations")
+    for lw in model.w.layers:
+        if lw.experts_gate_up is not None and lw.expert_base != 0:
+            raise ImportError("expert-parallel shards go through the exchange path")
 
-    def __init__(self, model, chunk: int = 8192):
+
+class _Layers:
+    """The per-layer body shared by prefill and batched decode; ``attend`` does RoPE, the KV write
+    and attention for the caller's token layout."""
+
+    def __init__(self, model):
+        _check_model(model)
         self.m = model
-        self.chunk = chunk
-        cfg = model.cfg
-        if cfg.head_dim not in (64, 128):
-            raise ImportError("native prefill covers head_dim 64 and 128")
-        if model.w.embed.dtype != torch.bfloat16:
-            raise ImportError("native prefill needs bf16 activations")
-        for lw in model.w.layers:
-            if lw.experts_gate_up is not None and lw.expert_base != 0:
-                raise ImportError("expert-parallel shards go through the exchange path")
+        self.comm = getattr(model, "gemm_comm", None)
 
-    @torch.no_grad()
-    def __call__(self, token_ids: torch.Tensor, cache: PagedKvCache, seq_id: int) -> torch.Tensor:
-        logits = None
-        for s in range(0, token_ids.numel(), self.chunk):
-            logits = self._chunk(token_ids[s:s + self.chunk], cache, seq_id)
-        return logits
+    def _row_parallel(self, x: torch.Tensor, w: LinearWeight, h: torch.Tensor) -> torch.Tensor:
+        m = self.m
+        if m.layout.world == 1:
+            return _mm(x, w, residual=h)
+        if self.comm is not None:
+            return self.comm.gemm_allreduce(x, w, residual=h.contiguous())
+        return h + m._sum(_mm(x, w))
 
-    def _chunk(self, token_ids, cache, seq_id):
+    def run(self, h: torch.Tensor, attend) -> torch.Tensor:
         m = self.m
         cfg, w = m.cfg, m.w
-        t = token_ids.numel()
-        hd, hq, hkv = cfg.head_dim, m.hq, m.hkv
-        pos0 = cache.seq_len(seq_id)
-        cache.reserve(seq_id, t)
-        row = cache.block_table[cache.slot_of[seq_id]]
-        pos = torch.arange(pos0, pos0 + t, dtype=torch.int32, device=m.device)
-        seq = torch.zeros(t, dtype=torch.int32, device=m.device)
-        h = D.embedding(w.embed, token_ids.to(torch.int32))
-        q = torch.empty(t, hq, hd, dtype=torch.bfloat16, device=m.device)
+        t = h.shape[0]
+        hd, hq = cfg.head_dim, m.hq
         for li, lw in enumerate(w.layers):
             xn = D.rms_norm(h, lw.norm1, cfg.rms_norm_eps)
             qkv = _mm(xn, lw.wqkv)
-            D.rope_kv_write(qkv, q, cache.k[li], cache.v[li], row.view(1, -1), pos, m.cos, m.sin,
-                            hq, hkv, token_seq=seq, traditional=cfg.rope_traditional)
-            attn = flash_prefill_paged(q, cache.k[li], cache.v[li], row, pos0, m.scale,
-                                       cfg.sliding_window or 0)
-            if m.layout.world > 1:
-                h = h + m._sum(_mm(attn.view(t, hq * hd), lw.wo))
-            else:
-                h = _mm(attn.view(t, hq * hd), lw.wo, residual=h)
+            attn = attend(li, qkv)
+            h = self._row_parallel(attn.view(t, hq * hd), lw.wo, h)
             xn = D.rms_norm(h, lw.norm2, cfg.rms_norm_eps)
             if lw.router is not None:
                 moe = cfg.ff_type.moe
@@ -87,18 +87,172 @@ class NativePrefill:
                 h = y if single else h + m._sum(y)
             else:
                 act = D.silu_mul(_mm(xn, lw.w_gate_up))
-                if m.layout.world > 1:
-                    h = h + m._sum(_mm(act, lw.w_down))
-                else:
-                    h = _mm(act, lw.w_down, residual=h)
+                h = self._row_parallel(act, lw.w_down, h)
+        return h
+
+    def logits(self, rows: torch.Tensor) -> torch.Tensor:
+        """Final norm + LM head for a few rows [R, D] -> fp32 [R, vocab] (gathered over TP ranks)."""
+        m = self.m
+        cfg, w = m.cfg, m.w
+        r = rows.shape[0]
+        if r <= 4:
+            out = D.rms_gemv(rows.contiguous(), w.lm_head, w.final_norm, cfg.rms_norm_eps,
+                             out=torch.empty(r, w.lm_head.n, dtype=torch.float32, device=m.device))
+        else:
+            out = _mm(D.rms_norm(rows.contiguous(), w.final_norm, cfg.rms_norm_eps), w.lm_head).float()
+        if m.allgather_logits is not None and m.layout.world > 1 and w.lm_head.n != cfg.vocab_size:
+            out = m.allgather_logits(out)
+        return out
+
+
+class NativePrefill:
+    """Callable ``(token_ids, cache, seq_id) -> last-token logits [1, vocab]`` (fp32)."""
+
+    def __init__(self, model, chunk: int = 8192):
+        self.m = model
+        self.chunk = chunk
+        self.layers = _Layers(model)
+
+    @torch.no_grad()
+    def __call__(self, token_ids: torch.Tensor, cache: PagedKvCache, seq_id: int) -> torch.Tensor:
+        logits = None
+        for s in range(0, token_ids.numel(), self.chunk):
+            logits = self._chunk(token_ids[s:s + self.chunk], cache, seq_id)
+        return logits
+
+    def _chunk(self, token_ids, cache, seq_id):
+        m = self.m
+        cfg = m.cfg
+        t = token_ids.numel()
+        hd, hq, hkv = cfg.head_dim, m.hq, m.hkv
+        pos0 = cache.seq_len(seq_id)
+        cache.reserve(seq_id, t)
+        row = cache.block_table[cache.slot_of[seq_id]]
+        pos = torch.arange(pos0, pos0 + t, dtype=torch.int32, device=m.device)
+        seq = torch.zeros(t, dtype=torch.int32, device=m.device)
+        q = torch.empty(t, hq, hd, dtype=torch.bfloat16, device=m.device)
+
+        def attend(li, qkv):
+            D.rope_kv_write(qkv, q, cache.k[li], cache.v[li], row.view(1, -1), pos, m.cos, m.sin,
+                            hq, hkv, token_seq=seq, traditional=cfg.rope_traditional)
+            return flash_prefill_paged(q, cache.k[li], cache.v[li], row, pos0, m.scale,
+                                       cfg.sliding_window or 0)
+
+        h = self.layers.run(D.embedding(m.w.embed, token_ids.to(torch.int32)), attend)
         cache.commit(seq_id, t)
         GemmStatus.check(m.device)
-        last = h[t - 1:t].contiguous()
-        logits = D.rms_gemv(last, w.lm_head, w.final_norm, cfg.rms_norm_eps,
-                            out=torch.empty(1, w.lm_head.n, dtype=torch.float32, device=m.device))
-        if m.allgather_logits is not None and m.layout.world > 1 and w.lm_head.n != cfg.vocab_size:
-            logits = m.allgather_logits(logits)
-        return logits
+        return self.layers.logits(h[t - 1:t])
+
+
+class BatchedDecode:
+    """One decode step for up to ``max_batch`` sequences through the tensor-core kernels; shapes are
+    static (idle rows point at the reserved page 0), so the step is one CUDA graph."""
+
+    def __init__(self, model, cache: PagedKvCache, max_batch: int, use_graph: bool = True,
+                 splits: Optional[int] = None):
+        self.m, self.cache, self.B = model, cache, max_batch
+        self.layers = _Layers(model)
+        cfg, dev = model.cfg, model.device
+        b = max_batch
+        self.tokens = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.positions = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.seq_lens = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.rows = torch.arange(b, dtype=torch.int32, device=dev)
+        self.live = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.table = torch.zeros(b, cache.max_blocks_per_seq, dtype=torch.int32, device=dev)
+        self.q = torch.empty(b, model.hq, cfg.head_dim, dtype=torch.bfloat16, device=dev)
+        self.next_tokens = torch.zeros(b, dtype=torch.int32, device=dev)
+        self.logits: Optional[torch.Tensor] = None
+        lib = _lib.cuda()
+        self.splits = splits or D.default_splits(b, model.hkv, lib.rmlx_flash_decode_gtiles(model.hq, model.hkv),
+                                                 cache.max_blocks_per_seq * 16)
+        self.fd = D.FlashDecodeScratch(b, model.hq, model.hkv, cfg.head_dim, self.splits, dev)
+        self.argmax_scratch = D.ArgmaxScratch(b, dev)
+        self.seq_ids: List[int] = []
+        self.use_graph = use_graph and model.layout.world == 1
+        self._graph: Optional[torch.cuda.CUDAGraph] = None
+
+    def bind(self, seq_ids: Sequence[int], last_tokens: Sequence[int]) -> None:
+        assert len(seq_ids) <= self.B
+        self.seq_ids = list(seq_ids)
+        n = len(seq_ids)
+        lens = [self.cache.seq_len(s) for s in seq_ids]
+        # idle rows attend to one (zero) key on the reserved page 0 and never advance
+        self.tokens.zero_(); self.positions.zero_(); self.seq_lens.fill_(1); self.live.zero_()
+        self.tokens[:n] = torch.tensor(list(last_tokens), dtype=torch.int32)
+        self.positions[:n] = torch.tensor(lens, dtype=torch.int32)
+        self.seq_lens[:n] = torch.tensor([l + 1 for l in lens], dtype=torch.int32)
+        self.live[:n] = 1
+        self._saved_tokens = self.tokens.clone()
+        self.refresh_tables()
+
+    def refresh_tables(self) -> None:
+        self.table.zero_()
+        for i, s in enumerate(self.seq_ids):
+            self.table[i].copy_(self.cache.block_table[self.cache.slot_of[s]])
+
+    def reserve(self, steps: int) -> None:
+        for s in self.seq_ids:
+            self.cache.reserve(s, steps)
+        self.refresh_tables()
+
+    def _body(self) -> None:
+        m, cfg, cache = self.m, self.m.cfg, self.cache
+
+        def attend(li, qkv):
+            D.rope_kv_write(qkv, self.q, cache.k[li], cache.v[li], self.table, self.positions, m.cos,
+                            m.sin, m.hq, m.hkv, token_seq=self.rows, traditional=cfg.rope_traditional)
+            return D.flash_decode_paged(self.q, cache.k[li], cache.v[li], self.table, self.seq_lens,
+                                        m.scale, self.splits, self.fd, cfg.sliding_window or 0)
+
+        h = self.layers.run(D.embedding(m.w.embed, self.tokens), attend)
+        self.logits = self.layers.logits(h)
+        D.argmax(self.logits, self.next_tokens, self.argmax_scratch)
+        # feed the tokens back and advance the bound rows (idle rows stay at length 0 on page 0)
+        self.tokens.copy_(self.next_tokens * self.live)
+        self.positions.add_(self.live)
+        self.seq_lens.add_(self.live)
+
+    @torch.no_grad()
+    def step(self) -> torch.Tensor:
+        """Run one step for every bound sequence; returns the next-token ids (device, int32)."""
+        if not self.use_graph:
+            self._body()
+        else:
+            if self._graph is None:
+                self._body()                         # warm-up outside capture (lazy initialisations)
+                self._rewind()
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    self._body()
+                self._graph = g
+                self._rewind()                       # capture ran nothing, but keep the invariant explicit
+            self._graph.replay()
+        for s in self.seq_ids:
+            self.cache.commit(s, 1)
+        return self.next_tokens
+
+    def _rewind(self) -> None:
+        """Undo the state advance of a warm-up step (the KV slot it wrote is rewritten by the real one)."""
+        n = len(self.seq_ids)
+        lens = [self.cache.seq_len(s) for s in self.seq_ids]
+        self.positions.zero_(); self.seq_lens.fill_(1)
+        self.positions[:n] = torch.tensor(lens, dtype=torch.int32)
+        self.seq_lens[:n] = torch.tensor([l + 1 for l in lens], dtype=torch.int32)
+        self.tokens.copy_(self._saved_tokens)
+
+    @torch.no_grad()
+    def generate(self, steps: int) -> torch.Tensor:
+        self.reserve(steps + 1)
+        self._saved_tokens = self.tokens.clone()
+        out = torch.zeros(len(self.seq_ids), steps, dtype=torch.int64)
+        for i in range(steps):
+            nxt = self.step()
+            out[:, i] = nxt[:len(self.seq_ids)].cpu().long()
+            self._saved_tokens = self.tokens.clone()
+        GemmStatus.check(self.m.device)
+        return out
 
 
 def enable_native_prefill(model, chunk: int = 8192) -> bool:
