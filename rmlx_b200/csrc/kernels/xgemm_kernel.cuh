@@ -28,6 +28,7 @@ constexpr int kXMaxExperts = 256;
 constexpr int kXMaxRanks = 8;
 constexpr int kCommNone = 0, kCommReduce = 1, kCommGather = 2;
 constexpr int kGatherChunkRows = 8;
+constexpr int kDqWarps = 8;          // dequant warps of the Q4 main loop (two per SM sub-partition)
 constexpr int kCommThreads = 160;   // collective modes: four reducer/pusher warps + one signalling warp
 
 struct XComm {
@@ -58,7 +59,7 @@ struct XSmem {
   static constexpr int kBytes = kStages * (kStageA + kStageB) +
                                 (WQ4 ? kRawStages * kStageRaw + 2 * kScaleSlot : 0) + 1024 + 512 +
                                 (kXMaxExperts + 2) * 8;
-  static constexpr int kThreads = WQ4 ? 320 : 192;
+  static constexpr int kThreads = WQ4 ? 192 + 32 * kDqWarps : 192;
 };
 
 struct XTile {
@@ -215,10 +216,10 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   const int num_kb = (K + kXBK - 1) / kXBK;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, 1); mbar_init(bq_full + i, 4); }
-    for (int i = 0; i < RAW; ++i) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, 4); }
+    for (int i = 0; i < STAGES; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, 1); mbar_init(bq_full + i, kDqWarps); }
+    for (int i = 0; i < RAW; ++i) { mbar_init(raw_full + i, 1); mbar_init(raw_empty + i, kDqWarps); }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(sc_full + i, 1); mbar_init(sc_empty + i, 4);
+      mbar_init(sc_full + i, 1); mbar_init(sc_empty + i, kDqWarps);
       mbar_init(acc_full + i, 1); mbar_init(acc_empty + i, 4);
     }
     for (int i = 0; i < 2; ++i) { mbar_init(sig_full + i, 128); mbar_init(sig_free + i, 1); }
@@ -508,61 +509,83 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         }
       }
     }
-  } else if (WQ4 && warp < 10) {
-    // ------------------------------------------------------------------ dequant (warps 6..9)
-    const int dt = threadIdx.x - 192;   // 0..127
+  } else if (WQ4 && warp < 6 + kDqWarps) {
+    // ------------------------------------------------------------------ dequant (warps 6..13)
+    const int dt = threadIdx.x - 192;   // 0 .. 32*kDqWarps-1
     int stage = 0, rstage = 0, sslot = 0;
     uint32_t phase = 0, rphase = 0, sphase = 0;
     bool ok = true;
+    // Static work split: item = (row of the W tile, which 32-element half of the 64-wide k-block);
+    // consecutive threads take consecutive 16-byte pieces of the packed tile (conflict-free loads),
+    // and a row's 8 group scales/biases stay in registers for 8 k-blocks.
+    constexpr int ITEMS = (BN * 2 + 32 * kDqWarps - 1) / (32 * kDqWarps);
     const __nv_bfloat162 k128 = __float2bfloat162_rn(128.f);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < num_kb; ++kb) {
-        if ((kb & 7) == 0 && !mbar_wait(sc_full + sslot, sphase, abort_flag, LIM)) { ok = false; break; }
-        if (!mbar_wait(raw_full + rstage, rphase, abort_flag, LIM)) { ok = false; break; }
-        if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, LIM)) { ok = false; break; }  // B slot free
-        const char* raw = sRaw + rstage * S::kStageRaw;
-        const __nv_bfloat16* sc = reinterpret_cast<const __nv_bfloat16*>(sScale + sslot * S::kScaleSlot);
-        const __nv_bfloat16* bi = sc + BN * 8;
-        char* bst = sB + stage * S::kStageB;
+      for (int kb8 = 0; kb8 < num_kb && ok; kb8 += 8) {     // K % 512 == 0: whole groups of 8
+        if (!mbar_wait(sc_full + sslot, sphase, abort_flag, LIM)) { ok = false; break; }
+        uint4 sv[ITEMS], bv[ITEMS];
+        const char* scb = sScale + sslot * S::kScaleSlot;
 #pragma unroll
-        for (int it = 0; it < (BN * 2) / 128; ++it) {
-          const int item = it * 128 + dt;
-          const int r = item % BN, h = item / BN;     // row of the W tile, which half of the 64 k
-          const uint4 wv = *reinterpret_cast<const uint4*>(raw + r * 32 + h * 16);
-          const __nv_bfloat162 s2 = __bfloat162bfloat162(sc[r * 8 + (kb & 7)]);
-          const __nv_bfloat162 b2 = __bfloat162bfloat162(bi[r * 8 + (kb & 7)]);
-          const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint32_t w = words[j];
-            // (128 + q) is exact in bf16: the nibble goes into the low mantissa bits of 128.0
-            uint32_t p04 = (w & 0x000f000fu) | 0x43004300u;            // (k0, k4)
-            uint32_t p15 = ((w >> 4) & 0x000f000fu) | 0x43004300u;     // (k1, k5)
-            uint32_t p26 = ((w >> 8) & 0x000f000fu) | 0x43004300u;     // (k2, k6)
-            uint32_t p37 = ((w >> 12) & 0x000f000fu) | 0x43004300u;    // (k3, k7)
-            __nv_bfloat162 v04 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p04), k128), s2, b2);
-            __nv_bfloat162 v15 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p15), k128), s2, b2);
-            __nv_bfloat162 v26 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p26), k128), s2, b2);
-            __nv_bfloat162 v37 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p37), k128), s2, b2);
-            const uint32_t u04 = *reinterpret_cast<uint32_t*>(&v04), u15 = *reinterpret_cast<uint32_t*>(&v15);
-            const uint32_t u26 = *reinterpret_cast<uint32_t*>(&v26), u37 = *reinterpret_cast<uint32_t*>(&v37);
-            uint4 o;   // natural k order: (k0,k1) (k2,k3) (k4,k5) (k6,k7)
-            o.x = __byte_perm(u04, u15, 0x5410); o.y = __byte_perm(u26, u37, 0x5410);
-            o.z = __byte_perm(u04, u15, 0x7632); o.w = __byte_perm(u26, u37, 0x7632);
-            const int c = h * 4 + j;                   // 16-byte chunk of the 128-byte row
-            *reinterpret_cast<uint4*>(bst + r * 128 + ((c ^ (r & 7)) << 4)) = o;
+        for (int it = 0; it < ITEMS; ++it) {
+          const int item = it * (32 * kDqWarps) + dt;
+          if (item < BN * 2) {
+            sv[it] = *reinterpret_cast<const uint4*>(scb + (item >> 1) * 16);
+            bv[it] = *reinterpret_cast<const uint4*>(scb + BN * 16 + (item >> 1) * 16);
           }
         }
-        fence_proxy_async_smem();     // generic-proxy stores -> visible to the tensor core's reads
         __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bq_full + stage);
-          mbar_arrive(raw_empty + rstage);
-          if ((kb & 7) == 7 || kb == num_kb - 1) mbar_arrive(sc_empty + sslot);
+        if (lane == 0) mbar_arrive(sc_empty + sslot);       // the slot can be refilled already
+        if (++sslot == 2) { sslot = 0; sphase ^= 1u; }
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          if (!mbar_wait(raw_full + rstage, rphase, abort_flag, LIM)) { ok = false; break; }
+          if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, LIM)) { ok = false; break; }  // B slot free
+          const char* raw = sRaw + rstage * S::kStageRaw;
+          char* bst = sB + stage * S::kStageB;
+#pragma unroll
+          for (int it = 0; it < ITEMS; ++it) {
+            const int item = it * (32 * kDqWarps) + dt;
+            if (item < BN * 2) {
+              const int r = item >> 1, h = item & 1;
+              const uint4 wv = *reinterpret_cast<const uint4*>(raw + item * 16);
+              const uint32_t sw = (kk >> 1) == 0 ? sv[it].x : (kk >> 1) == 1 ? sv[it].y : (kk >> 1) == 2 ? sv[it].z : sv[it].w;
+              const uint32_t bw = (kk >> 1) == 0 ? bv[it].x : (kk >> 1) == 1 ? bv[it].y : (kk >> 1) == 2 ? bv[it].z : bv[it].w;
+              const uint32_t s2u = __byte_perm(sw, 0u, (kk & 1) ? 0x3232u : 0x1010u);
+              const uint32_t b2u = __byte_perm(bw, 0u, (kk & 1) ? 0x3232u : 0x1010u);
+              const __nv_bfloat162 s2 = *reinterpret_cast<const __nv_bfloat162*>(&s2u);
+              const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&b2u);
+              const uint32_t words[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t w = words[j], w4 = w >> 4;
+                // byte b of the word holds elements 2b (low nibble) and 2b+1 (high nibble): pick the
+                // byte from w and from w>>4 into the two halves, keep the low nibbles, and drop them
+                // into the mantissa of 128.0 (128 + q is exact in bf16)
+                uint32_t p0 = (__byte_perm(w, w4, 0x0400u) & 0x000f000fu) | 0x43004300u;
+                uint32_t p1 = (__byte_perm(w, w4, 0x0501u) & 0x000f000fu) | 0x43004300u;
+                uint32_t p2 = (__byte_perm(w, w4, 0x0602u) & 0x000f000fu) | 0x43004300u;
+                uint32_t p3 = (__byte_perm(w, w4, 0x0703u) & 0x000f000fu) | 0x43004300u;
+                __nv_bfloat162 v0 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p0), k128), s2, b2);
+                __nv_bfloat162 v1 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p1), k128), s2, b2);
+                __nv_bfloat162 v2 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p2), k128), s2, b2);
+                __nv_bfloat162 v3 = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&p3), k128), s2, b2);
+                uint4 o;   // natural k order: (k0,k1) (k2,k3) (k4,k5) (k6,k7)
+                o.x = *reinterpret_cast<uint32_t*>(&v0); o.y = *reinterpret_cast<uint32_t*>(&v1);
+                o.z = *reinterpret_cast<uint32_t*>(&v2); o.w = *reinterpret_cast<uint32_t*>(&v3);
+                const int c = h * 4 + j;                 // 16-byte chunk of the 128-byte row
+                *reinterpret_cast<uint4*>(bst + r * 128 + ((c ^ (r & 7)) << 4)) = o;
+              }
+            }
+          }
+          fence_proxy_async_smem();     // generic-proxy stores -> visible to the tensor core's reads
+          __syncwarp();
+          if (lane == 0) {
+            mbar_arrive(bq_full + stage);
+            mbar_arrive(raw_empty + rstage);
+          }
+          if (++rstage == RAW) { rstage = 0; rphase ^= 1u; }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if ((kb & 7) == 7 || kb == num_kb - 1) { if (++sslot == 2) { sslot = 0; sphase ^= 1u; } }
-        if (++rstage == RAW) { rstage = 0; rphase ^= 1u; }
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
     }
   }

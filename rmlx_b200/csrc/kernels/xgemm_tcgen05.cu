@@ -10,7 +10,7 @@
 //     crates/rmlx-core/src/ops/matmul.rs:8823-8950).
 //
 // Roles per CTA (persistent, one CTA per SM): warp 0 TMA producer, warp 1 MMA issuer (owns TMEM),
-// warps 2-5 epilogue (TMEM -> registers -> bf16 global, + residual), warps 6-9 dequant (Q4 only).
+// warps 2-5 epilogue (TMEM -> registers -> bf16 global, + residual), warps 6-13 dequant (Q4 only).
 // Accumulators are double-buffered in TMEM. All pipeline waits are bounded. The kernel itself is in
 // xgemm_kernel.cuh.
 //
@@ -37,8 +37,12 @@ extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* 
   if (w_kind == 1 && !rmlx_qgemm_supported(K)) return -2;
   const bool grouped = offsets != nullptr;
   if (grouped && (E < 1 || E > kXMaxExperts)) return -2;
-  if (bn == 0) bn = (grouped || w_kind == 1) ? ((N % 256 == 0 && M >= 1024) ? 256 : 128) : 128;
-  if (bn != 128 && bn != 256) return -2;
+  if (bn == 0) {
+    bn = (grouped || w_kind == 1) ? ((N % 256 == 0 && M >= 1024) ? 256 : 128) : 128;
+    // few rows: the work is streaming W, so spread it over more SMs with narrower tiles
+    if (!grouped && ((M + kXBM - 1) / kXBM) * ((N + 127) / 128) < 100) bn = 64;
+  }
+  if (bn != 64 && bn != 128 && bn != 256) return -2;
   if (grouped && N % bn) return -2;
   const uint64_t rowsW = grouped ? uint64_t(E) * N : uint64_t(N);
   CUtensorMap ta, tw, ts, tb;
@@ -52,6 +56,9 @@ extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* 
   if (bn == 256) {
     if (w_kind == 1) { if (grouped) { RB_X(256, true, true); } else { RB_X(256, true, false); } }
     else { if (grouped) { RB_X(256, false, true); } else { RB_X(256, false, false); } }
+  } else if (bn == 64) {
+    if (w_kind == 1) { if (grouped) { RB_X(64, true, true); } else { RB_X(64, true, false); } }
+    else { if (grouped) { RB_X(64, false, true); } else { RB_X(64, false, false); } }
   } else {
     if (w_kind == 1) { if (grouped) { RB_X(128, true, true); } else { RB_X(128, true, false); } }
     else { if (grouped) { RB_X(128, false, true); } else { RB_X(128, false, false); } }

@@ -36,6 +36,20 @@ def _mm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = Non
     return qmm(x, w, residual=residual)
 
 
+_MM_OUT_DTYPE = [True]
+
+
+def _router_logits(xn: torch.Tensor, router: torch.Tensor) -> torch.Tensor:
+    """fp32 router logits from bf16 operands: a plain tensor-core library GEMM with fp32 output when
+    this torch offers it (exact products, fp32 accumulation), else the widened fp32 matmul."""
+    if _MM_OUT_DTYPE[0] and xn.dtype == torch.bfloat16 and router.dtype == torch.bfloat16:
+        try:
+            return torch.mm(xn, router.t(), out_dtype=torch.float32)
+        except (TypeError, RuntimeError):
+            _MM_OUT_DTYPE[0] = False
+    return xn.float() @ router.float().t()
+
+
 def _check_model(model) -> None:
     cfg = model.cfg
     if cfg.head_dim not in (64, 128):
@@ -77,7 +91,7 @@ class _Layers:
             xn = D.rms_norm(h, lw.norm2, cfg.rms_norm_eps)
             if lw.router is not None:
                 moe = cfg.ff_type.moe
-                logits = xn.float() @ lw.router.float().t()
+                logits = _router_logits(xn, lw.router)
                 idx, wts, _, offsets = D.topk_route(logits, moe.num_experts_per_token, lw.expert_bias)
                 single = m.layout.world == 1 and lw.shared_gate_up is None
                 y = moe_prefill_ffn(xn, idx, wts, offsets, lw.experts_gate_up, lw.experts_down,
