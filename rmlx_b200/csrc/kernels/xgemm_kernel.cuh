@@ -73,7 +73,10 @@ struct XTile {
 // rotates the row blocks so that a rank starts with the rows it already holds (gather mode).
 template <int BN, bool GROUPED, bool ROW_MAJOR = false>
 __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int tiles_n,
-                                        const int* s_off, const int* s_tprefix, int E, int rot = 0) {
+                                        const int* s_off, const int* s_tprefix, int E, int rot = 0,
+                                        int half = 0) {
+  // half = 1 (SwiGLU mode): a tile holds BN/2 gate rows and the matching BN/2 up rows of W and
+  // produces BN/2 output columns; w_row0 is the gate row, the up row sits N/2 further.
   XTile t;
   if (!GROUPED) {
     // ROW_MAJOR (gather mode): all column tiles of a row block before the next row block, so the
@@ -81,7 +84,7 @@ __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int
     int tm = (ROW_MAJOR ? tile / tiles_n : tile % tiles_m) + rot;
     if (tm >= tiles_m) tm -= tiles_m;
     const int tn = ROW_MAJOR ? tile % tiles_n : tile / tiles_m;
-    t.a_row0 = tm * kXBM; t.row_end = M; t.w_row0 = tn * BN; t.c_col0 = tn * BN;
+    t.a_row0 = tm * kXBM; t.row_end = M; t.w_row0 = tn * (BN >> half); t.c_col0 = tn * (BN >> half);
   } else {
     int e = 0;
     while (e + 1 < E && s_tprefix[e + 1] <= tile) ++e;
@@ -91,7 +94,7 @@ __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int
     const int mt_e = (rows + kXBM - 1) / kXBM;
     const int nt = local / mt_e, mt = local % mt_e;
     t.a_row0 = s_off[e] + mt * kXBM; t.row_end = s_off[e + 1];
-    t.w_row0 = e * N + nt * BN; t.c_col0 = nt * BN;
+    t.w_row0 = e * N + nt * (BN >> half); t.c_col0 = nt * (BN >> half);
   }
   return t;
 }
@@ -176,7 +179,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
              const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
              const __grid_constant__ CUtensorMap tmap_b, __nv_bfloat16* __restrict__ C,
              const __nv_bfloat16* __restrict__ residual, const int* __restrict__ offsets, int E, int M,
-             int N, int K, int ldc, int* __restrict__ status, const XComm cm) {
+             int N, int K, int ldc, int* __restrict__ status, const XComm cm, int swiglu) {
   static_assert(COMM == kCommNone || !GROUPED, "collective modes are for plain GEMMs");
   using S = XSmem<BN, WQ4>;
   constexpr int STAGES = S::kStages, RAW = S::kRawStages;
@@ -267,7 +270,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       bool ok = true;
       int ready_mb = -1;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
+        const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot, swiglu);
         if (COMM == kCommGather) {
           const int mb = t.a_row0 / kXBM;
           if (mb != ready_mb) {
@@ -284,19 +287,30 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             if ((kb & 7) == 0) {
               if (!mbar_wait(sc_empty + sslot, sphase ^ 1u, abort_flag, LIM)) { ok = false; break; }
               mbar_arrive_expect_tx(sc_full + sslot, S::kScaleSlot);
-              tma_load_2d(sScale + sslot * S::kScaleSlot, &tmap_s, sc_full + sslot, kb, t.w_row0);
-              tma_load_2d(sScale + sslot * S::kScaleSlot + BN * 16, &tmap_b, sc_full + sslot, kb, t.w_row0);
+              char* sd = sScale + sslot * S::kScaleSlot;
+              tma_load_2d(sd, &tmap_s, sc_full + sslot, kb, t.w_row0);
+              tma_load_2d(sd + BN * 16, &tmap_b, sc_full + sslot, kb, t.w_row0);
+              if (swiglu) {     // the maps' boxes are BN/2 rows tall in this mode: second half = up rows
+                tma_load_2d(sd + BN * 8, &tmap_s, sc_full + sslot, kb, t.w_row0 + N / 2);
+                tma_load_2d(sd + BN * 16 + BN * 8, &tmap_b, sc_full + sslot, kb, t.w_row0 + N / 2);
+              }
               if (++sslot == 2) { sslot = 0; sphase ^= 1u; }
             }
             if (!mbar_wait(raw_empty + rstage, rphase ^ 1u, abort_flag, LIM)) { ok = false; break; }
             mbar_arrive_expect_tx(raw_full + rstage, S::kStageRaw);
             tma_load_2d(sRaw + rstage * S::kStageRaw, &tmap_w, raw_full + rstage, kb * 32, t.w_row0);
+            if (swiglu)
+              tma_load_2d(sRaw + rstage * S::kStageRaw + BN * 16, &tmap_w, raw_full + rstage, kb * 32, t.w_row0 + N / 2);
             if (++rstage == RAW) { rstage = 0; rphase ^= 1u; }
           }
           if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
           mbar_arrive_expect_tx(full + stage, S::kStageA + (WQ4 ? 0 : S::kStageB));
           tma_load_2d(sA + stage * S::kStageA, ta, full + stage, kb * kXBK, t.a_row0);
-          if (!WQ4) tma_load_2d(sB + stage * S::kStageB, &tmap_w, full + stage, kb * kXBK, t.w_row0);
+          if (!WQ4) {
+            tma_load_2d(sB + stage * S::kStageB, &tmap_w, full + stage, kb * kXBK, t.w_row0);
+            if (swiglu)
+              tma_load_2d(sB + stage * S::kStageB + BN * 64, &tmap_w, full + stage, kb * kXBK, t.w_row0 + N / 2);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
@@ -342,7 +356,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     if (RESIDUAL && !GROUPED) pdl_wait();
 
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot);
+      const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot, swiglu);
       if (!mbar_wait(acc_full + acc, acc_phase, abort_flag, LIM)) { ok = false; break; }
       tc_fence_after_sync();
       const int row = t.a_row0 + q * 32 + lane;
@@ -376,6 +390,43 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         // signal two tiles back has gone out)
         if (!mbar_wait(sig_free + acc, acc_phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
         mbar_arrive(sig_full + acc);
+      } else if (swiglu) {
+        // accumulator columns [0, BN/2) are the gate, [BN/2, BN) the up projection of the same
+        // output columns: out = silu(gate) * up, straight from tensor memory
+        const int n_out = N / 2;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t rg[32], ru[32];
+          tmem_ld_32x32(t_row + c * 32, rg);
+          tmem_ld_32x32(t_row + BN / 2 + c * 32, ru);
+          tmem_ld_wait();
+          const int col0 = t.c_col0 + c * 32;
+          if (row < t.row_end && col0 < n_out) {
+            __nv_bfloat16* dst = C + size_t(row) * ldc + col0;
+            float f[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float g = __uint_as_float(rg[j]);
+              f[j] = g / (1.f + __expf(-g)) * __uint_as_float(ru[j]);
+            }
+            if (col0 + 32 <= n_out) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 o;
+                o.x = pack_bf16(f[v * 8 + 0], f[v * 8 + 1]); o.y = pack_bf16(f[v * 8 + 2], f[v * 8 + 3]);
+                o.z = pack_bf16(f[v * 8 + 4], f[v * 8 + 5]); o.w = pack_bf16(f[v * 8 + 6], f[v * 8 + 7]);
+                *reinterpret_cast<uint4*>(dst + v * 8) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < n_out) dst[j] = __float2bfloat16_rn(f[j]);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty + acc);
       } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
@@ -609,7 +660,7 @@ template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM = kCommNone>
 static int launch_x(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tw,
                     const CUtensorMap& ts, const CUtensorMap& tb, void* C, const void* residual,
                     const int* offsets, int E, int M, int N, int K, int ldc, int* status, int pdl,
-                    cudaStream_t st, const XComm& cm = XComm()) {
+                    cudaStream_t st, const XComm& cm = XComm(), int swiglu = 0) {
   using S = XSmem<BN, WQ4>;
   auto kern = xgemm_kernel<BN, WQ4, GROUPED, RESIDUAL, COMM>;
   RB_CHECK(set_max_smem(kern, S::kBytes));
@@ -618,7 +669,7 @@ static int launch_x(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtenso
   const int grid = tiles < sm_count() ? (tiles > 0 ? tiles : 1) : sm_count();
   return launch(kern, dim3(grid), dim3(S::kThreads + (COMM != kCommNone ? kCommThreads : 0)), size_t(S::kBytes), st, pdl != 0, ta, ta2, tw, ts, tb,
                 static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(residual), offsets, E,
-                M, N, K, ldc, status, cm);
+                M, N, K, ldc, status, cm, swiglu);
 }
 
 // Tensor maps of the weight operand (and of its scales/biases for Q4).

@@ -29,10 +29,12 @@ extern "C" int rmlx_qgemm_supported(int K) { return K % 512 == 0; }
 //   offsets == nullptr: plain GEMM, rowsW = N.
 //   offsets != nullptr: grouped; A rows are sorted by expert, offsets[E+1] (device, int32),
 //                       rowsW = E*N, N must be a multiple of the tile width.
+//   swiglu != 0: W's N rows (per expert) are [gate; up]; C gets N/2 columns of silu(gate)*up,
+//                computed in the epilogue from the fp32 accumulators (no residual in this mode).
 extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* scales,
                           const void* biases, void* C, const void* residual, const int* offsets,
-                          int E, int M, int N, int K, int lda, int ldc, int bn, int* status, int pdl,
-                          cudaStream_t st) {
+                          int E, int M, int N, int K, int lda, int ldc, int bn, int swiglu,
+                          int* status, int pdl, cudaStream_t st) {
   if (M < 1 || N < 1 || K < 8 || K % 8 || lda % 8) return -2;
   if (w_kind == 1 && !rmlx_qgemm_supported(K)) return -2;
   const bool grouped = offsets != nullptr;
@@ -44,15 +46,16 @@ extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* 
   }
   if (bn != 64 && bn != 128 && bn != 256) return -2;
   if (grouped && N % bn) return -2;
+  if (swiglu && (residual || N % bn)) return -2;
   const uint64_t rowsW = grouped ? uint64_t(E) * N : uint64_t(N);
   CUtensorMap ta, tw, ts, tb;
   int rc = make_tmap_2d_bf16(&ta, A, uint64_t(K), uint64_t(M), uint64_t(lda) * 2, kXBK, kXBM);
   if (rc) return rc;
-  rc = x_weight_maps(w_kind, W, scales, biases, rowsW, K, bn, &tw, &ts, &tb);
+  rc = x_weight_maps(w_kind, W, scales, biases, rowsW, K, swiglu ? bn / 2 : bn, &tw, &ts, &tb);
   if (rc) return rc;
 #define RB_X(BN_, Q_, G_)                                                                          \
   return residual ? launch_x<BN_, Q_, G_, true>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st) \
-                  : launch_x<BN_, Q_, G_, false>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st)
+                  : launch_x<BN_, Q_, G_, false>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st, XComm(), swiglu)
   if (bn == 256) {
     if (w_kind == 1) { if (grouped) { RB_X(256, true, true); } else { RB_X(256, true, false); } }
     else { if (grouped) { RB_X(256, false, true); } else { RB_X(256, false, false); } }

@@ -26,7 +26,7 @@ from ..ops import decode as D
 from ..ops.attention import flash_prefill_paged
 from ..ops.gemm import GemmStatus, gemm_bf16
 from ..ops.grouped import moe_prefill_ffn
-from ..ops.quantized import qmm
+from ..ops.quantized import qmm, xgemm
 from ..ops.weights import LinearWeight, W_BF16
 
 
@@ -34,6 +34,15 @@ def _mm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = Non
     if w.kind == W_BF16:
         return gemm_bf16(x, w.w, residual=residual)
     return qmm(x, w, residual=residual)
+
+
+def _gate_up_act(x: torch.Tensor, w: LinearWeight) -> torch.Tensor:
+    """silu(x W_gate^T) * (x W_up^T) for W = [gate; up]: SwiGLU runs in the GEMM epilogue when the
+    shape allows, else GEMM then the element-wise kernel."""
+    q4_ok = w.kind == W_BF16 or bool(_lib.cuda().rmlx_qgemm_supported(w.k))
+    if w.n % 256 == 0 and w.k % 8 == 0 and q4_ok:
+        return xgemm(x, w, swiglu=True)
+    return D.silu_mul(_mm(x, w))
 
 
 _MM_OUT_DTYPE = [True]
@@ -97,10 +106,10 @@ class _Layers:
                 y = moe_prefill_ffn(xn, idx, wts, offsets, lw.experts_gate_up, lw.experts_down,
                                     residual=h if single else None)
                 if lw.shared_gate_up is not None:
-                    y = y + _mm(D.silu_mul(_mm(xn, lw.shared_gate_up)), lw.shared_down)
+                    y = y + _mm(_gate_up_act(xn, lw.shared_gate_up), lw.shared_down)
                 h = y if single else h + m._sum(y)
             else:
-                act = D.silu_mul(_mm(xn, lw.w_gate_up))
+                act = _gate_up_act(xn, lw.w_gate_up)
                 h = self._row_parallel(act, lw.w_down, h)
         return h
 

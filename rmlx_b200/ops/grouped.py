@@ -26,8 +26,7 @@ def grouped_expert_ffn(x_sorted: torch.Tensor, offsets: torch.Tensor, gate_up: L
     if not (_grouped_ok(gate_up) and _grouped_ok(down)):
         raise ImportError("shape not covered by the grouped tensor-core kernel")
     off = offsets.to(torch.int32)
-    gu = xgemm(x_sorted.contiguous(), gate_up, offsets=off)
-    act = D.silu_mul(gu)
+    act = xgemm(x_sorted.contiguous(), gate_up, offsets=off, swiglu=True)   # SwiGLU in the epilogue
     return xgemm(act, down, offsets=off)
 
 

@@ -16,7 +16,7 @@ from .weights import LinearWeight, W_BF16, W_Q4
 
 _lib.register_cuda_sigs({
     "rmlx_qgemm_supported": ("i", "i"),
-    "rmlx_xgemm": ("ipppppppiiiiiiipip", "i"),
+    "rmlx_xgemm": ("ipppppppiiiiiiiipip", "i"),
     "rmlx_moe_scatter_rows": ("pipppppiiiip", "i"),
     "rmlx_moe_combine": ("ppppipiiiip", "i"),
 })
@@ -24,9 +24,10 @@ _lib.register_cuda_sigs({
 
 def xgemm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = None,
           out: Optional[torch.Tensor] = None, offsets: Optional[torch.Tensor] = None, bn: int = 0,
-          pdl: bool = False) -> torch.Tensor:
+          pdl: bool = False, swiglu: bool = False) -> torch.Tensor:
     """Plain (offsets None) or grouped tensor-core GEMM with bf16 or Q4 weights.
-    Grouped: x rows sorted by expert, ``offsets`` int32 [E+1] on the device, w stacked [E, N, K]."""
+    Grouped: x rows sorted by expert, ``offsets`` int32 [E+1] on the device, w stacked [E, N, K].
+    ``swiglu``: w's rows are [gate; up]; the result has N/2 columns of silu(gate) * up."""
     _lib.require_cuda_tensor(x, w.w)
     assert x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
     m, k = x.shape
@@ -36,10 +37,10 @@ def xgemm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = N
     if offsets is not None:
         assert offsets.dtype == torch.int32 and offsets.numel() == e + 1
     if out is None:
-        out = torch.empty(m, n, dtype=torch.bfloat16, device=x.device)
+        out = torch.empty(m, n // 2 if swiglu else n, dtype=torch.bfloat16, device=x.device)
     rc = _lib.cuda().rmlx_xgemm(w.kind, x.data_ptr(), w.w.data_ptr(), _lib.ptr(w.scales),
                                 _lib.ptr(w.biases), out.data_ptr(), _lib.ptr(residual),
-                                _lib.ptr(offsets), e, m, n, k, x.stride(0), out.stride(0), bn,
+                                _lib.ptr(offsets), e, m, n, k, x.stride(0), out.stride(0), bn, int(swiglu),
                                 GemmStatus.get(x.device).data_ptr(), int(pdl), _lib.stream_ptr())
     _lib.check(rc, "xgemm")
     return out

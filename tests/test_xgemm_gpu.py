@@ -75,3 +75,17 @@ def test_moe_prefill_path_matches_oracle(quant):
     torch.cuda.synchronize(); GemmStatus.check(DEV)
     want = x.float() + ref.moe_ffn(x.float(), idx.long(), wts, gu.dequantized(), dn.dequantized())
     assert _rel(out, want) < 3e-2
+
+
+@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("m,n2,k,bn", [(200, 512, 512, 0), (64, 1024, 1024, 64), (300, 1024, 512, 256)])
+def test_swiglu_epilogue(dev, quant, m, n2, k, bn):
+    """W = [gate; up] with n2 rows in total: the fused epilogue equals silu(x Wg^T) * (x Wu^T)."""
+    torch.manual_seed(3)
+    x = torch.randn(m, k, device=dev).to(torch.bfloat16)
+    w = LinearWeight.from_dense(torch.randn(n2, k) * 0.05, quant, device=dev)
+    got = xgemm(x, w, swiglu=True, bn=bn).float()
+    h = x.float() @ w.dequantized().float().t()
+    want = torch.nn.functional.silu(h[:, :n2 // 2]) * h[:, n2 // 2:]
+    assert got.shape == (m, n2 // 2)
+    assert (got - want).abs().max().item() / want.abs().max().item() < 1.5e-2
