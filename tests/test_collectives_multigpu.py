@@ -1,0 +1,94 @@
+"""Peer-memory collectives on 2+ GPUs against torch.distributed (NCCL) on the same tensors; several
+rounds per operation so that the alternating receive areas and the growing counters recycle."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from rmlx_b200.parallel.collectives import PeerCollectives
+        pc = PeerCollectives(1 << 20, device=dev, blocks=8)
+        bad = []
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        for rnd in range(3):
+            for dtype in (torch.bfloat16, torch.float32):
+                n = 1024 * (rnd + 1)
+                x = torch.randn(world * n, 8, device=dev, generator=g).to(dtype)
+                # all-reduce
+                want = x.clone(); dist.all_reduce(want)
+                got = pc.all_reduce(x)
+                tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+                if not torch.allclose(got.float(), want.float(), rtol=tol, atol=tol):
+                    bad.append(("all_reduce", rnd, str(dtype)))
+                # reduce-scatter
+                want_rs = torch.empty(n, 8, device=dev, dtype=dtype)
+                dist.reduce_scatter_tensor(want_rs, x)
+                if not torch.allclose(pc.reduce_scatter(x).float(), want_rs.float(), rtol=tol, atol=tol):
+                    bad.append(("reduce_scatter", rnd, str(dtype)))
+                # all-gather
+                want_ag = torch.empty(world * n, 8, device=dev, dtype=dtype)
+                dist.all_gather_into_tensor(want_ag, x[:n].contiguous())
+                if not torch.equal(pc.all_gather(x[:n]), want_ag):
+                    bad.append(("all_gather", rnd, str(dtype)))
+                # all-to-all
+                want_a2a = torch.empty_like(x)
+                dist.all_to_all_single(want_a2a, x)
+                if not torch.equal(pc.all_to_all(x), want_a2a):
+                    bad.append(("all_to_all", rnd, str(dtype)))
+                # broadcast from the last rank
+                want_b = x.clone(); dist.broadcast(want_b, world - 1)
+                if not torch.equal(pc.broadcast(x, root=world - 1), want_b):
+                    bad.append(("broadcast", rnd, str(dtype)))
+        torch.cuda.synchronize()
+        status = pc.status()
+        dist.barrier()
+        pc.close()
+        ret.put((rank, bad, status))
+    except Exception as e:      # report instead of leaving the parent to time out
+        import traceback
+        ret.put((rank, f"{e!r}\n{traceback.format_exc()}", -1))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+def test_peer_collectives_match_nccl():
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs two GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        results = [q.get(timeout=90) for _ in range(world)]
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    for rank, bad, status in results:
+        assert not isinstance(bad, str), bad
+        assert status == 0, (rank, status)
+        assert bad == [], (rank, bad)
