@@ -22,7 +22,8 @@ constexpr int kCollThreads = 512;
 enum CollOp { kAllGather = 0, kAllToAll = 1, kReduceScatter = 2, kAllReduce = 3, kBroadcast = 4 };
 
 // control block (uint32): [0] calls completed, [1] exit ticket, [2] phase-1 arrivals (every call),
-// [3] phase-2 arrivals (all-reduce calls only), [4] all-reduce calls completed
+// [3] phase-2 arrivals (all-reduce calls only), [4] all-reduce calls completed, [5],[6] this rank's
+// CTAs counting themselves before the last one publishes
 struct CollPeers {
   char* buf[kCollMaxRanks];       // 2 parities x (recv area [world x chunk_cap] + result area [world x chunk_cap])
   uint32_t* ctl[kCollMaxRanks];
@@ -74,13 +75,20 @@ __device__ __forceinline__ void coll_reduce(char* __restrict__ dst, const char* 
   }
 }
 
-// publish one arrival to every peer and wait for all of them; returns false after the wait budget
+// The CTAs of a rank first count themselves on a local word; the last one publishes a single
+// arrival per peer (so a peer's counter sees ``world`` remote atomics per phase, not world x grid),
+// then everyone waits for all ranks. Returns false after the wait budget.
 __device__ __forceinline__ bool coll_rendezvous(const CollPeers& pp, int word, uint32_t target, int* s_ok,
                                                 int* status) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence_system();
-    for (int p = 0; p < pp.world; ++p) red_release_sys_add(pp.ctl[p] + word, 1u);
+    uint32_t* local = pp.ctl[pp.rank] + word + 3;        // words 5 and 6
+    __threadfence_system();                              // this CTA's stores are visible everywhere
+    if (atomicAdd(local, 1u) == gridDim.x - 1) {
+      *local = 0u;
+      __threadfence_system();
+      for (int p = 0; p < pp.world; ++p) red_release_sys_add(pp.ctl[p] + word, 1u);
+    }
     *s_ok = wait_flag_ge(pp.ctl[pp.rank] + word, target) ? 1 : 0;
     if (!*s_ok && status) atomicExch(status, int(kStatusPeerTimeout));
   }
@@ -110,7 +118,7 @@ coll_kernel(CollPeers pp, int op, int bf16, const char* __restrict__ src, char* 
     else if (op == kBroadcast) { if (rank == root) coll_copy(pp.buf[p] + parity_off, src, chunk, tid, nthreads, false); }
     else coll_copy(recv, src + size_t(p) * chunk, chunk, tid, nthreads, false);
   }
-  bool ok = coll_rendezvous(pp, 2, e1 * uint32_t(world) * gridDim.x, &s_ok, status);
+  bool ok = coll_rendezvous(pp, 2, e1 * uint32_t(world), &s_ok, status);
 
   // phase 2: finish locally
   const char* mine = pp.buf[rank] + parity_off;
@@ -136,7 +144,7 @@ coll_kernel(CollPeers pp, int op, int bf16, const char* __restrict__ src, char* 
           reinterpret_cast<uint4*>(pp.buf[p] + result_off + size_t(rank) * chunk_cap)[i] = v;
         }
       }
-      ok = coll_rendezvous(pp, 3, a1 * uint32_t(world) * gridDim.x, &s_ok, status);
+      ok = coll_rendezvous(pp, 3, a1 * uint32_t(world), &s_ok, status);
       if (ok)
         for (int s = 0; s < world; ++s)
           coll_copy(dst + size_t(s) * chunk, pp.buf[rank] + result_off + size_t(s) * chunk_cap, chunk, tid,
@@ -166,8 +174,8 @@ using namespace rb;
 //   reduce-scatter  src [world*n]     -> dst [n]         (sum over ranks of piece ``rank``)
 //   all-reduce      src [world*n]     -> dst [world*n]   (sum over ranks)
 //   broadcast       src [n] on root   -> dst [n]
-// dtype: 0 raw bytes / fp32 sums, 1 bf16 sums (fp32 accumulation). Every rank must use the same
-// ``blocks``.
+// dtype: 0 raw bytes / fp32 sums, 1 bf16 sums (fp32 accumulation). Ranks may use different
+// ``blocks`` (arrivals are published once per rank).
 extern "C" int rmlx_coll(void* const* buf, void* const* ctl, int rank, int world, int op, int bf16,
                          const void* src, void* dst, unsigned long long chunk,
                          unsigned long long chunk_cap, int root, int blocks, int* status,

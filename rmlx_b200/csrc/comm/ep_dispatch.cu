@@ -33,6 +33,7 @@ constexpr uint32_t kEpStatusOverflow = 0x4f56464cu;   // 'OVFL'
 
 // Layout of a rank's control block (uint32 words), identical on every rank.
 //   [0] epoch  [1] exit ticket  [2] counts-arrived  [3] rows-arrived  [4] returns-arrived
+//   [5] this rank's blocks counting themselves before the last one publishes an arrival
 //   [8 .. 8+E)            cursors (per global expert, this rank's pairs placed so far)
 //   [8+E .. 8+E+world*E)  table of everyone's counts, row = source rank
 struct EpPeers {
@@ -160,9 +161,14 @@ ep_dispatch_kernel(EpPeers pp, const __nv_bfloat16* __restrict__ x, int x_stride
 
   // 4. tell everyone this block is done; wait until every block of every rank is
   if (threadIdx.x == 0) {
+    // blocks count themselves locally; the last one publishes one arrival per peer
     __threadfence_system();
-    for (int p = 0; p < world; ++p) red_release_sys_add(pp.ctl[p] + 3, 1u);
-    if (!wait_flag_ge(ctl + 3, e1 * uint32_t(world) * gridDim.x)) ep_fail(status, kStatusPeerTimeout);
+    if (atomicAdd(ctl + 5, 1u) == gridDim.x - 1) {
+      ctl[5] = 0u;
+      __threadfence_system();
+      for (int p = 0; p < world; ++p) red_release_sys_add(pp.ctl[p] + 3, 1u);
+    }
+    if (!wait_flag_ge(ctl + 3, e1 * uint32_t(world))) ep_fail(status, kStatusPeerTimeout);
     // the last block to leave zeroes the cursors and advances the epoch
     __threadfence();
     if (atomicAdd(ctl + 1, 1u) == gridDim.x - 1) {
@@ -201,10 +207,14 @@ ep_combine_kernel(EpPeers pp, uint32_t* __restrict__ ctl, const __nv_bfloat16* _
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence_system();
-    // the remote control blocks sit at the same offset from each rank's base as the local one
-    const size_t off = size_t(ctl - pp.ctl[rank]);
-    for (int p = 0; p < world; ++p) red_release_sys_add(pp.ctl[p] + off + 4, 1u);
-    s_ok = wait_flag_ge(ctl + 4, e1 * uint32_t(world) * gridDim.x) ? 1 : 0;
+    if (atomicAdd(ctl + 5, 1u) == gridDim.x - 1) {
+      ctl[5] = 0u;
+      __threadfence_system();
+      // the remote control blocks sit at the same offset from each rank's base as the local one
+      const size_t off = size_t(ctl - pp.ctl[rank]);
+      for (int p = 0; p < world; ++p) red_release_sys_add(pp.ctl[p] + off + 4, 1u);
+    }
+    s_ok = wait_flag_ge(ctl + 4, e1 * uint32_t(world)) ? 1 : 0;
     if (!s_ok) ep_fail(status, kStatusPeerTimeout);
   }
   __syncthreads();

@@ -49,8 +49,9 @@ class PeerCollectives:
         bf16 = 1 if src.dtype == torch.bfloat16 else 0
         if op in (REDUCE_SCATTER, ALL_REDUCE) and src.dtype not in (torch.bfloat16, torch.float32):
             raise ValueError("sums are implemented for bf16 and fp32")
+        blocks = max(4, min(self.blocks, chunk_bytes * self.world // 65536))   # small messages: few CTAs
         rc = _lib.cuda().rmlx_coll(self._buf, self._ctl, self.rank, self.world, op, bf16, src.data_ptr(),
-                                   dst.data_ptr(), chunk_bytes, self.cap, root, self.blocks,
+                                   dst.data_ptr(), chunk_bytes, self.cap, root, blocks,
                                    GemmStatus.get(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "coll")
         return dst

@@ -63,6 +63,10 @@ class FusedEpExchange:
         self.recv_offsets = torch.zeros(self.e_local + 1, dtype=torch.int32, device=self.device)
         self.recv_rows = torch.zeros(1, dtype=torch.int32, device=self.device)
 
+    def _blocks_for(self, tokens: int) -> int:
+        """Few blocks for few rows (ranks publish one arrival each, so grids may differ per rank)."""
+        return max(8, min(self.blocks, (tokens * self.k + 15) // 16))
+
     def dispatch(self, x: torch.Tensor, idx: torch.Tensor, counts: torch.Tensor
                  ) -> Tuple[torch.Tensor, torch.Tensor]:
         """x [T, D] bf16, idx [T, k] int32 (global expert ids), counts [E] int32 (the router's).
@@ -73,7 +77,7 @@ class FusedEpExchange:
         rc = _lib.cuda().rmlx_ep_dispatch(
             self._ctl, self._slab, self._meta, self._ret, self.rank, self.world, x.data_ptr(),
             x.stride(0), idx.data_ptr(), counts.data_ptr(), t, k, self.D, self.E, self.capacity,
-            self.recv_offsets.data_ptr(), self.recv_rows.data_ptr(), self.blocks,
+            self.recv_offsets.data_ptr(), self.recv_rows.data_ptr(), self._blocks_for(t),
             GemmStatus.get(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "ep_dispatch")
         return self.slab, self.recv_offsets
@@ -89,7 +93,7 @@ class FusedEpExchange:
             self._ctl, self._slab, self._meta, self._ret, self.rank, self.world,
             ctypes.c_void_p(self.region.local + self.off_ctl2), y.data_ptr(), self.recv_rows.data_ptr(),
             wts.data_ptr(), _lib.ptr(residual), 0 if residual is None else residual.stride(0),
-            out.data_ptr(), out.stride(0), num_tokens, self.k, self.D, self.blocks,
+            out.data_ptr(), out.stride(0), num_tokens, self.k, self.D, self._blocks_for(num_tokens),
             GemmStatus.get(self.device).data_ptr(), _lib.stream_ptr())
         _lib.check(rc, "ep_combine")
         return out
