@@ -5,7 +5,7 @@
 // Weights are streamed with 16-byte no-allocate loads, one contiguous 512-byte span per warp
 // instruction; activations sit in shared memory in a layout that makes every 16-byte shared load
 // conflict-free. Accumulation is fp32 (the 4-bit path accumulates 16 products in fp16 pairs before
-// flushing to fp32).
+// flushing to fp32; its activations are block-scaled per 32 values so that this stays accurate).
 #pragma once
 #include "ptx.cuh"
 
@@ -48,7 +48,51 @@ __device__ __forceinline__ float block_sum_256(float v, float* red) {
 // 4-bit path: fp16, one 16-byte unit per packed word (8 k). Unit (hg, j) for half-group hg = k/32
 // and word j = (k%32)/8 sits at index j*(K/32) + hg. Inside a unit the order is x0,x4,x1,x5,x2,x6,
 // x3,x7 so that half2 p pairs with nibbles p and p+4 of the word, which one mask extracts together.
-// The sum of each half-group (fp32) is kept beside it for the affine bias term.
+// The nibbles are used as they sit in the word, as fp16 *subnormals* (a nibble at bits 0-3 of a
+// half is q * 2^-24, at bits 4-7 it is 16q * 2^-24), so no subtraction of a magic constant is
+// needed. To keep the products in fp16's normal range every half-group of 32 activations is scaled
+// by a power of two S chosen from its own largest magnitude (the largest scaled value lies in
+// [2^14, 2^15)); the halves that meet the bits-4-7 nibbles carry S/16 instead. All of that is
+// exact. Beside the units sit, per half-group, the fp32 sum of the (rounded, unscaled) activations
+// for the affine bias term and the factor 2^24 / S that brings a partial sum back to real units.
+// ------------------------------------------------------------------------------------------------
+// Sources of activation values for the staging routines: fill f[0..7] with chunk c (k = 8c .. 8c+7).
+struct XLoadBf16 {          // x (global, bf16), optionally times a per-channel weight; tracks sum x^2
+  const __nv_bfloat16* x;
+  const __nv_bfloat16* scale_w;
+  float ssq;
+  __device__ __forceinline__ void operator()(int c, float (&f)[8]) {
+    const uint4 v = *reinterpret_cast<const uint4*>(x + (c << 3));
+    f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
+    f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ssq += f[i] * f[i];
+    if (scale_w) {
+      const uint4 s = *reinterpret_cast<const uint4*>(scale_w + (c << 3));
+      f[0] *= bf16lo(s.x); f[1] *= bf16hi(s.x); f[2] *= bf16lo(s.y); f[3] *= bf16hi(s.y);
+      f[4] *= bf16lo(s.z); f[5] *= bf16hi(s.z); f[6] *= bf16lo(s.w); f[7] *= bf16hi(s.w);
+    }
+  }
+};
+struct XLoadSwiglu {        // silu(gate) * up from a [gate | up] row of 2*I bf16
+  const __nv_bfloat16* gu;
+  int I;
+  __device__ __forceinline__ void operator()(int c, float (&f)[8]) {
+    const uint4 gv = *reinterpret_cast<const uint4*>(gu + (c << 3));
+    const uint4 uv = *reinterpret_cast<const uint4*>(gu + I + (c << 3));
+    const float g[8] = {bf16lo(gv.x), bf16hi(gv.x), bf16lo(gv.y), bf16hi(gv.y),
+                        bf16lo(gv.z), bf16hi(gv.z), bf16lo(gv.w), bf16hi(gv.w)};
+    const float u[8] = {bf16lo(uv.x), bf16hi(uv.x), bf16lo(uv.y), bf16hi(uv.y),
+                        bf16lo(uv.z), bf16hi(uv.z), bf16lo(uv.w), bf16hi(uv.w)};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // stable sigmoid: never exponentiates a positive number
+      const float e = __expf(-fabsf(g[i]));
+      const float sig = g[i] >= 0.f ? 1.f / (1.f + e) : e / (1.f + e);
+      f[i] = g[i] * sig * u[i];
+    }
+  }
+};
 // ------------------------------------------------------------------------------------------------
 template <class WT>
 struct XStage;
@@ -57,96 +101,80 @@ template <>
 struct XStage<WBf16> {
   static __host__ __device__ size_t bytes(int K) { return size_t(K) * 4; }
   // x: K bf16 (global), scale_w: K bf16 or nullptr. Returns sum of squares of x (block-wide).
-  static __device__ float stage(char* smem, const __nv_bfloat16* x, const __nv_bfloat16* scale_w,
-                                int K, float* red, bool want_ssq) {
+  // Stage K values produced chunk by chunk by ``load``. Ends with a block barrier.
+  template <class F>
+  static __device__ void stage_with(char* smem, int K, F& load) {
     float4* xs = reinterpret_cast<float4*>(smem);
     const int nchunk = K >> 3;
-    float ssq = 0.f;
     for (int c = threadIdx.x; c < nchunk; c += kGemvThreads) {
-      uint4 v = *reinterpret_cast<const uint4*>(x + (c << 3));
-      float f[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y),
-                    bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ssq += f[i] * f[i];
-      if (scale_w) {
-        uint4 s = *reinterpret_cast<const uint4*>(scale_w + (c << 3));
-        f[0] *= bf16lo(s.x); f[1] *= bf16hi(s.x); f[2] *= bf16lo(s.y); f[3] *= bf16hi(s.y);
-        f[4] *= bf16lo(s.z); f[5] *= bf16hi(s.z); f[6] *= bf16lo(s.w); f[7] *= bf16hi(s.w);
-      }
+      float f[8];
+      load(c, f);
       xs[c] = make_float4(f[0], f[1], f[2], f[3]);
       xs[nchunk + c] = make_float4(f[4], f[5], f[6], f[7]);
     }
-    if (want_ssq) return block_sum_256(ssq, red);
     __syncthreads();
-    return 0.f;
   }
-  // Same, from fp32 values already in registers/global (used by kernels whose prologue computes
-  // the activation, e.g. SwiGLU). Caller synchronises.
-  static __device__ void put(char* smem, int k, int K, float v) {
-    float* xs = reinterpret_cast<float*>(smem);
-    const int c = k >> 3, j = k & 7;
-    xs[((((j >> 2) * (K >> 3)) + c) << 2) + (j & 3)] = v;
+  static __device__ float stage(char* smem, const __nv_bfloat16* x, const __nv_bfloat16* scale_w,
+                                int K, float* red, bool want_ssq) {
+    XLoadBf16 ld{x, scale_w, 0.f};
+    stage_with(smem, K, ld);
+    return want_ssq ? block_sum_256(ld.ssq, red) : 0.f;
   }
-  static __device__ void finish(char*, int) {}
 };
 
 template <>
 struct XStage<WQ4> {
-  // fp16 units + one fp32 sum per half-group.
-  static __host__ __device__ size_t bytes(int K) { return size_t(K) * 2 + size_t(K >> 5) * 4; }
-  static __device__ float* xsum(char* smem, int K) {
-    return reinterpret_cast<float*>(smem + size_t(K) * 2);
+  // fp16 units, then per half-group: fp32 sum of the activations, fp32 factor 2^24 / S.
+  static __host__ __device__ size_t bytes(int K) { return size_t(K) * 2 + size_t(K >> 5) * 8; }
+  static __device__ const float* xsum(const char* smem, int K) {
+    return reinterpret_cast<const float*>(smem + size_t(K) * 2);
+  }
+  // Stage K values produced chunk by chunk by ``load``. Every thread runs every trip of the loop
+  // (the four lanes that share a half-group exchange their maxima and sums by shuffle). Ends with a
+  // block barrier.
+  template <class F>
+  static __device__ void stage_with(char* smem, int K, F& load) {
+    uint4* xh = reinterpret_cast<uint4*>(smem);
+    const int nchunk = K >> 3, nhg = K >> 5;
+    float* xs = reinterpret_cast<float*>(smem + size_t(K) * 2);
+    float* qm = xs + nhg;
+    for (int c0 = 0; c0 < nchunk; c0 += kGemvThreads) {
+      const int c = c0 + threadIdx.x;
+      const bool valid = c < nchunk;               // nchunk is a multiple of 4: groups are all-in or all-out
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (valid) load(c, f);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+      // amax < 2^(ex-126); S = 2^e puts the largest value into [2^14, 2^15). Zero or tiny groups
+      // and infinities are clamped so that S and 2^24 / S stay finite.
+      const int ex = (__float_as_int(amax) >> 23) & 0xff;
+      const int e = max(-60, min(141 - ex, 40));
+      const float S = __int_as_float((127 + e) << 23), S16 = S * 0.0625f;
+      const float inv = __int_as_float((127 - e) << 23);
+      const __half2 p0 = __floats2half2_rn(f[0] * S, f[4] * S), p1 = __floats2half2_rn(f[1] * S16, f[5] * S16);
+      const __half2 p2 = __floats2half2_rn(f[2] * S, f[6] * S), p3 = __floats2half2_rn(f[3] * S16, f[7] * S16);
+      const float2 a = __half22float2(p0), b = __half22float2(p1), cc = __half22float2(p2), d = __half22float2(p3);
+      float sum = ((a.x + a.y) + (cc.x + cc.y)) * inv + ((b.x + b.y) + (d.x + d.y)) * (inv * 16.f);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      if (valid) {
+        uint4 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&p0); o.y = *reinterpret_cast<const uint32_t*>(&p1);
+        o.z = *reinterpret_cast<const uint32_t*>(&p2); o.w = *reinterpret_cast<const uint32_t*>(&p3);
+        xh[(c & 3) * nhg + (c >> 2)] = o;
+        if ((c & 3) == 0) { xs[c >> 2] = sum; qm[c >> 2] = inv * 16777216.f; }
+      }
+    }
+    __syncthreads();
   }
   static __device__ float stage(char* smem, const __nv_bfloat16* x, const __nv_bfloat16* scale_w,
                                 int K, float* red, bool want_ssq) {
-    uint4* xh = reinterpret_cast<uint4*>(smem);
-    const int nchunk = K >> 3, nhg = K >> 5;
-    float ssq = 0.f;
-    for (int c = threadIdx.x; c < nchunk; c += kGemvThreads) {
-      uint4 v = *reinterpret_cast<const uint4*>(x + (c << 3));
-      float f[8] = {bf16lo(v.x), bf16hi(v.x), bf16lo(v.y), bf16hi(v.y),
-                    bf16lo(v.z), bf16hi(v.z), bf16lo(v.w), bf16hi(v.w)};
-#pragma unroll
-      for (int i = 0; i < 8; ++i) ssq += f[i] * f[i];
-      if (scale_w) {
-        uint4 s = *reinterpret_cast<const uint4*>(scale_w + (c << 3));
-        f[0] *= bf16lo(s.x); f[1] *= bf16hi(s.x); f[2] *= bf16lo(s.y); f[3] *= bf16hi(s.y);
-        f[4] *= bf16lo(s.z); f[5] *= bf16hi(s.z); f[6] *= bf16lo(s.w); f[7] *= bf16hi(s.w);
-      }
-      __half2 p0 = __floats2half2_rn(f[0], f[4]), p1 = __floats2half2_rn(f[1], f[5]);
-      __half2 p2 = __floats2half2_rn(f[2], f[6]), p3 = __floats2half2_rn(f[3], f[7]);
-      uint4 o;
-      o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-      o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-      xh[(c & 3) * nhg + (c >> 2)] = o;
-    }
-    float r = 0.f;
-    if (want_ssq) r = block_sum_256(ssq, red); else __syncthreads();
-    finish(smem, K);
-    return r;
-  }
-  static __device__ void put(char* smem, int k, int K, float v) {
-    __half* xh = reinterpret_cast<__half*>(smem);
-    const int hg = k >> 5, j = (k & 31) >> 3, n = k & 7;
-    xh[((j * (K >> 5) + hg) << 3) + ((n & 3) << 1) + (n >> 2)] = __float2half_rn(v);
-  }
-  // Half-group sums from the stored (rounded) values. Ends with a barrier.
-  static __device__ void finish(char* smem, int K) {
-    const uint4* xh = reinterpret_cast<const uint4*>(smem);
-    float* xs = xsum(smem, K);
-    const int nhg = K >> 5;
-    for (int hg = threadIdx.x; hg < nhg; hg += kGemvThreads) {
-      float s = 0.f;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint4 u = xh[j * nhg + hg];
-        const __half2* h = reinterpret_cast<const __half2*>(&u);
-#pragma unroll
-        for (int p = 0; p < 4; ++p) { float2 t = __half22float2(h[p]); s += t.x + t.y; }
-      }
-      xs[hg] = s;
-    }
-    __syncthreads();
+    XLoadBf16 ld{x, scale_w, 0.f};
+    stage_with(smem, K, ld);
+    return want_ssq ? block_sum_256(ld.ssq, red) : 0.f;
   }
 };
 
@@ -205,19 +233,17 @@ __device__ __forceinline__ void fma_tile(const Tile<RowBf16, R>& t, int c0, cons
   }
 }
 
-// One packed word (8 nibbles) times one 16-byte unit of staged fp16 activations.
-// (1024 + q) is built exactly in fp16 by OR-ing the nibble into the mantissa of 1024.0.
+// One packed word (8 nibbles) times one 16-byte unit of staged fp16 activations. The masked
+// nibbles are fp16 subnormals (q or 16q times 2^-24); the activations carry the matching scales.
 __device__ __forceinline__ void q4_word_fma(uint32_t w, const uint4& xu, __half2& a0, __half2& a1) {
-  const __half2 k1024 = __float2half2_rn(1024.f);
   const __half2* x = reinterpret_cast<const __half2*>(&xu);
-  uint32_t t0 = (w & 0x000f000fu) | 0x64006400u;
-  uint32_t t1 = ((w >> 4) & 0x000f000fu) | 0x64006400u;
-  uint32_t t2 = ((w >> 8) & 0x000f000fu) | 0x64006400u;
-  uint32_t t3 = ((w >> 12) & 0x000f000fu) | 0x64006400u;
-  a0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t0), k1024), x[0], a0);
-  a1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t1), k1024), x[1], a1);
-  a0 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t2), k1024), x[2], a0);
-  a1 = __hfma2(__hsub2(*reinterpret_cast<__half2*>(&t3), k1024), x[3], a1);
+  const uint32_t w8 = w >> 8;
+  const uint32_t t0 = w & 0x000f000fu, t1 = w & 0x00f000f0u;       // (k0,k4), 16 x (k1,k5)
+  const uint32_t t2 = w8 & 0x000f000fu, t3 = w8 & 0x00f000f0u;     // (k2,k6), 16 x (k3,k7)
+  a0 = __hfma2(*reinterpret_cast<const __half2*>(&t0), x[0], a0);
+  a1 = __hfma2(*reinterpret_cast<const __half2*>(&t1), x[1], a1);
+  a0 = __hfma2(*reinterpret_cast<const __half2*>(&t2), x[2], a0);
+  a1 = __hfma2(*reinterpret_cast<const __half2*>(&t3), x[3], a1);
 }
 
 template <int R>
@@ -250,8 +276,8 @@ __device__ __forceinline__ void fma_tile(const Tile<RowQ4, R>& t, int h0, const 
 #pragma unroll
       for (int b = 0; b < B; ++b) {
         const uint4* xh = reinterpret_cast<const uint4*>(smem + b * smem_b_stride);
-        const float xsum = reinterpret_cast<const float*>(smem + b * smem_b_stride +
-                                                          size_t(K) * 2)[hg];
+        const float* aux = reinterpret_cast<const float*>(smem + b * smem_b_stride + size_t(K) * 2);
+        const float xsum = aux[hg], qmul = aux[nhg + hg];
         const uint4 x0 = xh[hg], x1 = xh[nhg + hg], x2 = xh[2 * nhg + hg], x3 = xh[3 * nhg + hg];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
@@ -261,7 +287,7 @@ __device__ __forceinline__ void fma_tile(const Tile<RowQ4, R>& t, int h0, const 
           q4_word_fma(t.w[u][r].z, x2, a0, a1);
           q4_word_fma(t.w[u][r].w, x3, a0, a1);
           const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
-          const float qx = (f0.x + f0.y) + (f1.x + f1.y);
+          const float qx = ((f0.x + f0.y) + (f1.x + f1.y)) * qmul;
           acc[r][b] = fmaf(t.sc[u][r], qx, fmaf(t.bi[u][r], xsum, acc[r][b]));
         }
       }

@@ -153,19 +153,9 @@ swiglu_down_kernel(Matrix<WT> W /*[N, I]*/, const __nv_bfloat16* __restrict__ ga
   pdl_wait();
 #pragma unroll
   for (int b = 0; b < B; ++b) {
-    const __nv_bfloat16* gu = gate_up + size_t(b) * gu_stride;
-    for (int k = threadIdx.x; k < I; k += kGemvThreads) {
-      const float g = __bfloat162float(gu[k]), u = __bfloat162float(gu[I + k]);
-      // stable sigmoid: never exponentiates a positive number
-      const float e = __expf(-fabsf(g));
-      const float sig = g >= 0.f ? 1.f / (1.f + e) : e / (1.f + e);
-      XStage<WT>::put(smem + b * bstride, k, I, g * sig * u);
-    }
+    XLoadSwiglu ld{gate_up + size_t(b) * gu_stride, I};
+    XStage<WT>::stage_with(smem + b * bstride, I, ld);
   }
-  __syncthreads();
-#pragma unroll
-  for (int b = 0; b < B; ++b) XStage<WT>::finish(smem + b * bstride, I);
-  __syncthreads();
   for (bool first = true; n0 < N; n0 += gridDim.x * kGemvWarps * kRowsPerWarp, first = false) {
     if (!first) {
 #pragma unroll

@@ -227,7 +227,7 @@ constexpr int kGuPairsPerWarp = 2;  // (gate, up) row pairs in flight per warp
 // grid = (row blocks, token*slot pairs). `i_begin`/`i_count` select a slice of the intermediate
 // dimension (tensor-parallel shards own a slice of every expert).
 template <class WT>
-__global__ void __launch_bounds__(kGemvThreads)
+__global__ void __launch_bounds__(kGemvThreads, 2)
 moe_gate_up_kernel(ExpertMatrix<WT> W /*rows = 2*I_full: gate then up*/,
                    const __nv_bfloat16* __restrict__ x, int x_stride,
                    const __nv_bfloat16* __restrict__ norm_w, float eps,
@@ -282,7 +282,7 @@ moe_gate_up_kernel(ExpertMatrix<WT> W /*rows = 2*I_full: gate then up*/,
 // accumulates over the slots with the routing weight applied per slot. Slots whose expert is not
 // local contribute nothing (the cross-rank sum happens in the caller's all-reduce).
 template <class WT, bool OUT_F32>
-__global__ void __launch_bounds__(kGemvThreads)
+__global__ void __launch_bounds__(kGemvThreads, 2)     // two blocks per SM: keeps more weight loads in flight
 moe_down_kernel(ExpertMatrix<WT> W /*rows = N, K = I*/, const __nv_bfloat16* __restrict__ act,
                 int act_stride, const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
                 const __nv_bfloat16* __restrict__ residual, int res_stride, void* __restrict__ out,

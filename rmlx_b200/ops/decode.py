@@ -22,8 +22,9 @@ _Q4_PATH = os.environ.get("RMLX_Q4_PATH", "auto")
 
 def q4_path() -> str:
     """Which Q4 mat-vec implementation runs: 'mma' (bulk-copy-fed tensor-core path), 'scalar'
-    (fp16 FMA path) or 'auto' (per kernel, whichever measured faster on B200: tensor-core path for
-    the expert gate/up projection, scalar path elsewhere)."""
+    (fp16 FMA path on subnormal-encoded nibbles) or 'auto' (per kernel, whichever measured faster on
+    B200: since the scalar inner loop lost its magic-constant subtraction it wins everywhere, so
+    'auto' is the scalar path; the tensor-core path stays selectable)."""
     return _Q4_PATH
 
 
@@ -176,7 +177,7 @@ def moe_gate_up(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor]
     i = w.n // 2
     if out is None:
         out = torch.zeros(b * top_k, i, dtype=torch.bfloat16, device=x.device)
-    if w.kind == W_Q4 and q4_path() in ("mma", "auto") and _lib.cuda().rmlx_qmv_mma_supported(k, 1, 32):
+    if w.kind == W_Q4 and q4_path() == "mma" and _lib.cuda().rmlx_qmv_mma_supported(k, 1, 32):
         rc = _lib.cuda().rmlx_moe_gate_up_q4_mma(
             w.w.data_ptr(), w.scales.data_ptr(), w.biases.data_ptr(), x.data_ptr(), x.stride(0),
             _lib.ptr(norm_w), eps, idx.data_ptr(), out.data_ptr(), out.stride(0), b, top_k, i, k,
