@@ -222,3 +222,31 @@ GPU2\tNV18\tNV18\t X \t56-111
 """
     m = parse_topo_matrix(txt)
     assert m == [["X", "NV18", "NV18"], ["NV18", "X", "NV18"], ["NV18", "NV18", "X"]]
+
+
+def test_warmup_is_idempotent_and_calibrates():
+    """run_warmup semantics (crates/rmlx-distributed/src/warmup.rs tests): both callables run once,
+    a second call does nothing, the crossover of the two timed paths becomes the thresholds."""
+    from rmlx_b200.parallel.warmup import Warmup, WarmupConfig
+    calls = {"comm": 0, "kern": 0}
+    w = Warmup(WarmupConfig(calibration_sizes=(4, 32, 128, 512), repeats=1))
+    small = lambda n: 10e-6 + n * 1e-6        # latency-optimised path: cheap start, steep slope
+    large = lambda n: 60e-6 + n * 0.1e-6      # bandwidth-optimised path
+    r = w.run(lambda: calls.__setitem__("comm", calls["comm"] + 1),
+              lambda: calls.__setitem__("kern", calls["kern"] + 1), small, large)
+    assert r.ran and calls == {"comm": 1, "kern": 1}
+    assert r.calibration.large_n_min == 128 and r.calibration.small_n_max == 32
+    assert "small_4" in r.timings_us and "large_512" in r.timings_us
+    r2 = w.run(lambda: calls.__setitem__("comm", 99))
+    assert not r2.ran and calls["comm"] == 1 and r2.calibration == r.calibration
+    from rmlx_b200.parallel.moe_policy import MoePolicy
+    p = MoePolicy(env={})
+    p.apply_calibration(r.calibration)
+    assert p.large_n_min == 128
+
+
+def test_nvtx_ranges_are_noops_without_cuda():
+    from rmlx_b200.utils import nvtx
+    with nvtx.range("layer0"):
+        nvtx.mark("x")
+    assert nvtx.enabled() in (False, True)
