@@ -38,9 +38,20 @@ class ServingEngine:
         self._engine = None
         self._bound: List[int] = []
         if model.device.type == "cuda":
+            # prompts through the tensor-core path; decode through the mat-vec engine for small
+            # batches and through the tensor-core path (batch = GEMM rows) for larger ones
+            from .. import _lib
             from ..models.decode_engine import CachedDecode
-            self._engine = CachedDecode(model, self.cache, max_batch=scfg.max_batch_size, comm=comm,
-                                        greedy=True)
+            from ..models.prefill import BatchedDecode, enable_native_prefill
+            enable_native_prefill(model)
+            if scfg.max_batch_size <= int(_lib.cuda().rmlx_gemv_max_batch()):
+                self._engine = CachedDecode(model, self.cache, max_batch=scfg.max_batch_size, comm=comm,
+                                            greedy=True)
+            else:
+                try:
+                    self._engine = BatchedDecode(model, self.cache, max_batch=scfg.max_batch_size)
+                except ImportError:
+                    self._engine = None          # shapes outside the kernels: library-kernel forward
 
     def _on_evict(self, seq_id: int) -> None:
         self.cache.free_sequence(seq_id)
