@@ -123,6 +123,7 @@ gemv_allreduce_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_s
 #pragma unroll
   for (int r = 0; r < kTpRowsPerWarp; ++r) rows[r] = W.row(min(nw + r, N - 1));
   load_tile<kTpRowsPerWarp>(rows, K, 0, t0);
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
 #pragma unroll
   for (int b = 0; b < B; ++b)
@@ -188,6 +189,7 @@ moe_down_allreduce_kernel(ExpertMat<WT> W, const __nv_bfloat16* __restrict__ act
   const int b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   using Row = typename ExpertMat<WT>::Row;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   if (threadIdx.x < top_k) {
     const int e = topk_idx[b * top_k + threadIdx.x] - expert_base;
@@ -243,6 +245,7 @@ __global__ void __launch_bounds__(256)
 allreduce_oneshot_kernel(const float* __restrict__ in, const __nv_bfloat16* __restrict__ residual,
                          void* __restrict__ out, int n, TpPeers P, size_t slot_off, int slot) {
   __shared__ uint32_t s_ok;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const int per = (n + gridDim.x - 1) / gridDim.x;
   const int lo = blockIdx.x * per, hi = min(n, lo + per);
@@ -287,6 +290,7 @@ argmax_allreduce_kernel(const float* __restrict__ logits, int V_local, int strid
   // keys layout per rank: [slot][B][world] u64
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   for (int b = 0; b < B; ++b) {
     const float* row = logits + size_t(b) * stride;

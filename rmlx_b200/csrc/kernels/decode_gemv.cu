@@ -43,6 +43,7 @@ rms_gemv_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_stride,
     for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
     load_tile<kRowsPerWarp>(rows, K, 0, t0);
   }
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
 
 #pragma unroll
@@ -103,6 +104,7 @@ rms_gate_up_swiglu_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int
     rows[0] = W.row(i); rows[1] = W.row(size_t(I) + i);
     load_tile<2>(rows, K, 0, t0);
   }
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
 #pragma unroll
   for (int b = 0; b < B; ++b) {
@@ -150,6 +152,7 @@ swiglu_down_kernel(Matrix<WT> W /*[N, I]*/, const __nv_bfloat16* __restrict__ ga
     for (int r = 0; r < kRowsPerWarp; ++r) rows[r] = W.row(min(n0 + r, N - 1));
     load_tile<kRowsPerWarp>(rows, I, 0, t0);
   }
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
 #pragma unroll
   for (int b = 0; b < B; ++b) {

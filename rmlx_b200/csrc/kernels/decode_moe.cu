@@ -101,6 +101,7 @@ moe_router_kernel(const __nv_bfloat16* __restrict__ gate_w, const __nv_bfloat16*
       wv[u] = (c < c_hi) ? ldg_stream(wrow + (size_t(c) << 3)) : make_uint4(0, 0, 0, 0);
     }
     if (e == blockIdx.x) {
+      pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
       pdl_wait();
 #pragma unroll
       for (int b = 0; b < B; ++b) {
@@ -239,6 +240,7 @@ moe_gate_up_kernel(ExpertMatrix<WT> W /*rows = 2*I_full: gate then up*/,
   const int K = W.K;
   const int pair = blockIdx.y, b = pair / top_k;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const int e = topk_idx[pair] - expert_base;
   if (e < 0 || e >= experts_local) return;  // expert lives on another rank
@@ -294,6 +296,7 @@ moe_down_kernel(ExpertMatrix<WT> W /*rows = N, K = I*/, const __nv_bfloat16* __r
   const size_t bstride = (XStage<WT>::bytes(I) + 15) & ~size_t(15);
   const int b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   if (threadIdx.x < top_k) {
     const int e = topk_idx[b * top_k + threadIdx.x] - expert_base;

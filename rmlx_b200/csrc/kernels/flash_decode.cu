@@ -83,6 +83,7 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
 
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const int len = p.seq_lens[b];
   const int first = (p.window > 0 && len > p.window) ? len - p.window : 0;  // first visible token

@@ -14,6 +14,7 @@ namespace rb {
 __global__ void embedding_kernel(const __nv_bfloat16* __restrict__ table,
                                  const int* __restrict__ ids, __nv_bfloat16* __restrict__ out,
                                  int D, int vocab) {
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   int id = ids[blockIdx.x];
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
@@ -30,6 +31,7 @@ rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
                 __nv_bfloat16* __restrict__ sum_out, int D, float eps) {
   __shared__ float red[8];
   __shared__ float s_inv;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const size_t base = size_t(blockIdx.x) * D;
   float ssq = 0.f;
@@ -71,6 +73,7 @@ argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int V, in
               unsigned long long* __restrict__ keys, unsigned int* __restrict__ tickets) {
   __shared__ float sv[32];
   __shared__ int si[32];
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const float* row = logits + size_t(blockIdx.y) * stride;
   float best = -INFINITY;
@@ -165,6 +168,7 @@ __global__ void fp8_dequant_rows_kernel(const __nv_fp8_storage_t* __restrict__ q
 __global__ void decode_advance_kernel(const int* __restrict__ next, int* __restrict__ tokens,
                                       int* __restrict__ positions, int* __restrict__ seq_lens,
                                       const int* __restrict__ active, int B) {
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const int b = blockIdx.x * blockDim.x + threadIdx.x;
   if (b < B && (!active || active[b])) {

@@ -259,6 +259,7 @@ rms_qmv_mma_kernel(const uint32_t* __restrict__ w, const __nv_bfloat16* __restri
     for (int r = lane; r < ROWS; r += 32)
       wt.issue_row(wimg, ROWS, r, w, scales, biases, size_t(min(row0 + r, N - 1)), &bar);
   }
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
 #pragma unroll
   for (int b = 0; b < NCOLS; ++b)
@@ -323,6 +324,7 @@ moe_gate_up_q4_mma_kernel(const uint32_t* __restrict__ w, const __nv_bfloat16* _
   char* xst = smem + ((wt.bytes(ROWS) + 127) & ~size_t(127));
   const size_t cstride = QStage::col_bytes(K);
   const int i0 = blockIdx.x * 8 * TILES;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();   // the expert index comes from the router kernel
   const int e = topk_idx[pair] - expert_base;
   if (e < 0 || e >= experts_local) return;
@@ -392,6 +394,7 @@ moe_down_q4_mma_kernel(const uint32_t* __restrict__ w, const __nv_bfloat16* __re
   char* xst = smem + img * top_k;
   const size_t cstride = QStage::col_bytes(I);
   const int row0 = blockIdx.x * 16;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   // Every thread reads the (few) routing entries itself: no barrier before the copies go out.
   int my_e[kQMaxTopK];

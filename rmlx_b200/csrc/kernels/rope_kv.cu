@@ -27,6 +27,7 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv,
                                      int traditional) {
   const int tkn = blockIdx.x, head = blockIdx.y, i = threadIdx.x;  // i in [0, HD/2)
   const int half = HD >> 1;
+  pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const int pos = positions[tkn];
   const __nv_bfloat16* src = qkv + (size_t(tkn) * (Hq + 2 * Hkv) + head) * HD;
