@@ -120,62 +120,101 @@ __global__ void __launch_bounds__(kFpThreads) flash_prefill_kernel(FpParams p) {
     __syncthreads();
     const uint32_t kbase = smem_u32(smem + stage * 2 * TILE_BYTES);
     const uint32_t vbase = kbase + TILE_BYTES;
+    // two pages (32 keys) per step: one running-max update and one rescale of the output
+    // accumulators per 32 keys, and no mask arithmetic on steps that lie wholly below the diagonal
+    const int warp_pos_lo = p.pos0 + q0 + warp * 16, warp_pos_hi = warp_pos_lo + 15;
 #pragma unroll 1
-    for (int pg = 0; pg < 4; ++pg) {
-      const int key0 = tile * kFpKvTile + pg * kFpPage;
-      // whole page above the diagonal for every row of this warp, or outside the cached range
-      if (key0 > p.pos0 + q0 + warp * 16 + 15 || key0 >= kv_end) break;
-      if (p.window > 0 && key0 + 15 <= p.pos0 + q0 + warp * 16 - p.window) continue;
-      const uint32_t kpage = kbase + pg * PAGE_BYTES, vpage = vbase + pg * PAGE_BYTES;
-      float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int pp = 0; pp < 2; ++pp) {
+      const int key0 = tile * kFpKvTile + pp * 2 * kFpPage;
+      // whole step above the diagonal for every row of this warp, or outside the cached range
+      if (key0 > warp_pos_hi || key0 >= kv_end) break;
+      if (p.window > 0 && key0 + 31 <= warp_pos_lo - p.window) continue;
+      const bool second = key0 + kFpPage <= warp_pos_hi && key0 + kFpPage < kv_end;   // page 2 has visible keys
+      const bool need_mask = key0 + 31 > warp_pos_lo || p.window > 0;
+      float sv[2][8];
 #pragma unroll
-      for (int ks = 0; ks < KS; ++ks) {
-        const int mi = lane >> 3, r = lane & 7;
-        const int tok = (mi >> 1) * 8 + r, c = 2 * ks + (mi & 1);
-        uint32_t kb[4];
-        fp_ldm4(kb, kpage + tok * (HD * 2) + ((c ^ (tok & 7)) << 4));
-        fp_mma(s0, qa[ks], kb[0], kb[1]);
-        fp_mma(s1, qa[ks], kb[2], kb[3]);
-      }
-      const int kt = key0 + t * 2;
-      const int keys[4] = {kt, kt + 1, kt + 8, kt + 9};
-      float sv[8] = {s0[0], s0[1], s1[0], s1[1], s0[2], s0[3], s1[2], s1[3]};
+      for (int q2 = 0; q2 < 2; ++q2) {
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+        if (q2 == 0 || second) {
+          const uint32_t kpage = kbase + (pp * 2 + q2) * PAGE_BYTES;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        bool oka = keys[i] <= pos_a, okb = keys[i] <= pos_b;
-        if (p.window > 0) { oka = oka && keys[i] > pos_a - p.window; okb = okb && keys[i] > pos_b - p.window; }
-        sv[i] = oka ? sv[i] * p.scale_log2 : -INFINITY;
-        sv[4 + i] = okb ? sv[4 + i] * p.scale_log2 : -INFINITY;
+          for (int ks = 0; ks < KS; ++ks) {
+            const int mi = lane >> 3, r = lane & 7;
+            const int tok = (mi >> 1) * 8 + r, c = 2 * ks + (mi & 1);
+            uint32_t kb[4];
+            fp_ldm4(kb, kpage + tok * (HD * 2) + ((c ^ (tok & 7)) << 4));
+            fp_mma(s0, qa[ks], kb[0], kb[1]);
+            fp_mma(s1, qa[ks], kb[2], kb[3]);
+          }
+        }
+        // row a: keys kt, kt+1, kt+8, kt+9 ; row b: the same keys
+        sv[q2][0] = s0[0]; sv[q2][1] = s0[1]; sv[q2][2] = s1[0]; sv[q2][3] = s1[1];
+        sv[q2][4] = s0[2]; sv[q2][5] = s0[3]; sv[q2][6] = s1[2]; sv[q2][7] = s1[3];
       }
-      float mx0 = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
-      float mx1 = fmaxf(fmaxf(sv[4], sv[5]), fmaxf(sv[6], sv[7]));
+      if (need_mask || !second) {
+#pragma unroll
+        for (int q2 = 0; q2 < 2; ++q2) {
+          const int kt = key0 + q2 * kFpPage + t * 2;
+          const int keys[4] = {kt, kt + 1, kt + 8, kt + 9};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            bool oka = keys[i] <= pos_a && (q2 == 0 || second), okb = keys[i] <= pos_b && (q2 == 0 || second);
+            if (p.window > 0) { oka = oka && keys[i] > pos_a - p.window; okb = okb && keys[i] > pos_b - p.window; }
+            sv[q2][i] = oka ? sv[q2][i] * p.scale_log2 : -INFINITY;
+            sv[q2][4 + i] = okb ? sv[q2][4 + i] * p.scale_log2 : -INFINITY;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sv[q2][i] *= p.scale_log2;
+      }
+      float mx0 = fmaxf(fmaxf(fmaxf(sv[0][0], sv[0][1]), fmaxf(sv[0][2], sv[0][3])),
+                        fmaxf(fmaxf(sv[1][0], sv[1][1]), fmaxf(sv[1][2], sv[1][3])));
+      float mx1 = fmaxf(fmaxf(fmaxf(sv[0][4], sv[0][5]), fmaxf(sv[0][6], sv[0][7])),
+                        fmaxf(fmaxf(sv[1][4], sv[1][5]), fmaxf(sv[1][6], sv[1][7])));
       mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
       mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
       const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
-      // a row may have no visible key in this page (fully masked): keep its state unchanged
+      // a row may have no visible key in this step (fully masked): keep its state unchanged
       const float c0 = (nm0 == -INFINITY) ? 1.f : exp2f(m0 - nm0);
       const float c1 = (nm1 == -INFINITY) ? 1.f : exp2f(m1 - nm1);
       m0 = nm0; m1 = nm1;
-      float pr[8];
+      const float sub0 = (m0 == -INFINITY) ? 0.f : m0, sub1 = (m1 == -INFINITY) ? 0.f : m1;
+      uint32_t pa[2][4];
+      float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        pr[i] = (m0 == -INFINITY) ? 0.f : exp2f(sv[i] - m0);
-        pr[4 + i] = (m1 == -INFINITY) ? 0.f : exp2f(sv[4 + i] - m1);
+      for (int q2 = 0; q2 < 2; ++q2) {
+        float pr[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          pr[i] = exp2f(sv[q2][i] - sub0);            // exp2(-inf) = 0 for masked entries
+          pr[4 + i] = exp2f(sv[q2][4 + i] - sub1);
+        }
+        ps0 += (pr[0] + pr[1]) + (pr[2] + pr[3]);
+        ps1 += (pr[4] + pr[5]) + (pr[6] + pr[7]);
+        pa[q2][0] = pack_bf16(pr[0], pr[1]); pa[q2][1] = pack_bf16(pr[4], pr[5]);
+        pa[q2][2] = pack_bf16(pr[2], pr[3]); pa[q2][3] = pack_bf16(pr[6], pr[7]);
       }
-      l0 = l0 * c0 + (pr[0] + pr[1] + pr[2] + pr[3]);
-      l1 = l1 * c1 + (pr[4] + pr[5] + pr[6] + pr[7]);
-      uint32_t pa[4] = {pack_bf16(pr[0], pr[1]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[2], pr[3]),
-                        pack_bf16(pr[6], pr[7])};
+      l0 = l0 * c0 + ps0;
+      l1 = l1 * c1 + ps1;
 #pragma unroll
       for (int j = 0; j < NT; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
 #pragma unroll
-      for (int j = 0; j < NT; j += 2) {
-        const int mi = lane >> 3, r = lane & 7;
-        const int tok = (mi & 1) * 8 + r, c = j + (mi >> 1);
-        uint32_t vb[4];
-        fp_ldm4t(vb, vpage + tok * (HD * 2) + ((c ^ (tok & 7)) << 4));
-        fp_mma(o[j], pa, vb[0], vb[1]);
-        fp_mma(o[j + 1], pa, vb[2], vb[3]);
+      for (int q2 = 0; q2 < 2; ++q2) {
+        if (q2 == 0 || second) {
+          const uint32_t vpage = vbase + (pp * 2 + q2) * PAGE_BYTES;
+#pragma unroll
+          for (int j = 0; j < NT; j += 2) {
+            const int mi = lane >> 3, r = lane & 7;
+            const int tok = (mi & 1) * 8 + r, c = j + (mi >> 1);
+            uint32_t vb[4];
+            fp_ldm4t(vb, vpage + tok * (HD * 2) + ((c ^ (tok & 7)) << 4));
+            fp_mma(o[j], pa[q2], vb[0], vb[1]);
+            fp_mma(o[j + 1], pa[q2], vb[2], vb[3]);
+          }
+        }
       }
     }
     __syncthreads();          // everyone is done with this stage before it is refilled

@@ -25,28 +25,32 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv,
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t,
                                      int Hq, int Hkv, int HD, int max_blocks, int page,
                                      int traditional) {
-  const int tkn = blockIdx.x, head = blockIdx.y, i = threadIdx.x;  // i in [0, HD/2)
+  const int tkn = blockIdx.x, i = threadIdx.x;  // i in [0, HD/2)
   const int half = HD >> 1;
   pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   const int pos = positions[tkn];
-  const __nv_bfloat16* src = qkv + (size_t(tkn) * (Hq + 2 * Hkv) + head) * HD;
   const int ia = traditional ? 2 * i : i, ib = traditional ? 2 * i + 1 : i + half;
-  float a = __bfloat162float(src[ia]), b = __bfloat162float(src[ib]);
-  __nv_bfloat16* dst;
-  if (head < Hq) {
-    dst = q_out + (size_t(tkn) * Hq + head) * HD;
-  } else {
-    const int seq = token_seq ? token_seq[tkn] : tkn;
-    const int blk = block_table[size_t(seq) * max_blocks + pos / page];
-    const bool is_k = head < Hq + Hkv;
-    const int kvh = is_k ? head - Hq : head - Hq - Hkv;
-    dst = (is_k ? k_cache : v_cache) + ((size_t(blk) * Hkv + kvh) * page + pos % page) * HD;
-    if (!is_k) { dst[ia] = src[ia]; dst[ib] = src[ib]; return; }
-  }
   const float c = cos_t[size_t(pos) * half + i], s = sin_t[size_t(pos) * half + i];
-  dst[ia] = __float2bfloat16_rn(a * c - b * s);
-  dst[ib] = __float2bfloat16_rn(b * c + a * s);
+  // a block takes every gridDim.y-th head of its token (one head each for decode-sized launches,
+  // a strip of heads for prompts, where one block per head would be mostly launch overhead)
+  for (int head = blockIdx.y; head < Hq + 2 * Hkv; head += gridDim.y) {
+    const __nv_bfloat16* src = qkv + (size_t(tkn) * (Hq + 2 * Hkv) + head) * HD;
+    const float a = __bfloat162float(src[ia]), b = __bfloat162float(src[ib]);
+    __nv_bfloat16* dst;
+    if (head < Hq) {
+      dst = q_out + (size_t(tkn) * Hq + head) * HD;
+    } else {
+      const int seq = token_seq ? token_seq[tkn] : tkn;
+      const int blk = block_table[size_t(seq) * max_blocks + pos / page];
+      const bool is_k = head < Hq + Hkv;
+      const int kvh = is_k ? head - Hq : head - Hq - Hkv;
+      dst = (is_k ? k_cache : v_cache) + ((size_t(blk) * Hkv + kvh) * page + pos % page) * HD;
+      if (!is_k) { dst[ia] = src[ia]; dst[ib] = src[ib]; continue; }
+    }
+    dst[ia] = __float2bfloat16_rn(a * c - b * s);
+    dst[ib] = __float2bfloat16_rn(b * c + a * s);
+  }
 }
 
 // Stand-alone RoPE over [T, H, HD] (used by tests and by attention variants that keep their own
@@ -77,7 +81,9 @@ extern "C" int rmlx_rope_kv_write(const void* qkv, void* q_out, void* k_cache, v
                                   int HD, int max_blocks, int page, int traditional, int pdl,
                                   cudaStream_t st) {
   if (T < 1 || HD % 2 || HD / 2 > 1024) return -2;
-  return launch(rope_kv_write_kernel, dim3(T, Hq + 2 * Hkv), dim3(HD / 2), 0, st, pdl != 0,
+  const int H = Hq + 2 * Hkv;
+  const int gy = T >= 128 ? (H + 17) / 18 : H;     // prompts: ~18 heads per block
+  return launch(rope_kv_write_kernel, dim3(T, gy), dim3(HD / 2), 0, st, pdl != 0,
                 static_cast<const __nv_bfloat16*>(qkv), static_cast<__nv_bfloat16*>(q_out),
                 static_cast<__nv_bfloat16*>(k_cache), static_cast<__nv_bfloat16*>(v_cache),
                 block_table, positions, token_seq, cos_t, sin_t, Hq, Hkv, HD, max_blocks, page,
