@@ -1,16 +1,19 @@
 // The generalised tcgen05 GEMM kernel (see xgemm_tcgen05.cu for the plain entry points and
 // ../comm/tp_gemm.cu for the tensor-parallel ones). C = A · W^T with
-//   * W bf16 (TMA-fed) or MLX-affine Q4 dequantised inside the main loop by four dequant warps;
+//   * W bf16 (TMA-fed) or MLX-affine Q4 dequantised inside the main loop by eight dequant warps;
 //   * GROUPED: rows of A sorted by expert, tile table derived on the device from offsets[E+1];
+//   * swiglu: a tile holds BN/2 gate rows and the matching BN/2 up rows of W; the epilogue writes
+//     silu(gate) * up straight from the fp32 accumulators;
 //   * COMM = kCommReduce: this rank holds a K-shard; every finished accumulator tile is stored
-//     straight into the staging slab of the rank that owns the tile (peer stores over NVLink, a
-//     release counter per tile); the owner's epilogue warps sum the world's partials (+ residual)
-//     and store the finished tile into every rank's output — reduce-scatter and all-gather of an
-//     all-reduce, both inside the GEMM kernel, overlapped with the tiles still being multiplied;
-//   * COMM = kCommGather: A is row-sharded over the ranks; the epilogue warps (idle while the first
-//     tiles are multiplied) push this rank's rows into every peer's gathered copy in 8-row chunks
-//     with a counter per 128-row block; the TMA producer starts with the local rows and waits for
-//     a block's counter before its first load of remote rows.
+//     straight into the staging slab of the rank that owns the tile (peer stores over NVLink; a
+//     signalling warp publishes a release counter per tile); four collective warps of the owner
+//     sum the world's partials (+ residual) and store the finished tile into every rank's output —
+//     reduce-scatter and all-gather of an all-reduce, both inside the GEMM kernel, running
+//     alongside the tiles still being multiplied;
+//   * COMM = kCommGather: A is row-sharded over the ranks; the collective warps push this rank's
+//     rows into every peer's gathered copy in 8-row chunks with a counter per 128-row block; the
+//     TMA producer starts with the local rows (row-block-major tile order, rotated by rank) and
+//     waits for a block's counter before its first load of remote rows.
 // Every wait — mbarrier or peer counter — is bounded; a timeout sets the status word and the CTA
 // drains and frees its tensor memory. Peer data is only ever *pushed* (plain stores); loads are
 // always from this GPU's memory.
@@ -48,11 +51,13 @@ struct XComm {
   unsigned long long* trace = nullptr;       // optional [grid][8] timestamps (see x_trace)
 };
 
-template <int BN, bool WQ4>
+// MT = 2: a tile is two stacked 128-row blocks of A against ONE staged block of W, i.e. two
+// accumulators per dequantised operand stage — the dequant warps' work per multiply-add halves.
+template <int BN, bool WQ4, int MT = 1>
 struct XSmem {
-  static constexpr int kStages = WQ4 ? 3 : ((BN >= 256) ? 4 : 6);
+  static constexpr int kStages = MT == 2 ? 3 : (WQ4 ? ((BN >= 256) ? 3 : 5) : ((BN >= 256) ? 4 : 6));
   static constexpr int kRawStages = 4;
-  static constexpr int kStageA = kXBM * kXBK * 2;
+  static constexpr int kStageA = MT * kXBM * kXBK * 2;
   static constexpr int kStageB = BN * kXBK * 2;
   static constexpr int kStageRaw = BN * 32;          // 64 nibbles per row
   static constexpr int kScaleSlot = 2 * BN * 16;     // scales + biases for 8 k-blocks
@@ -71,7 +76,7 @@ struct XTile {
 
 // tile id -> coordinates. Plain: column-block major so consecutive CTAs share a W tile; ``rot``
 // rotates the row blocks so that a rank starts with the rows it already holds (gather mode).
-template <int BN, bool GROUPED, bool ROW_MAJOR = false>
+template <int BN, bool GROUPED, bool ROW_MAJOR = false, int MT = 1>
 __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int tiles_n,
                                         const int* s_off, const int* s_tprefix, int E, int rot = 0,
                                         int half = 0) {
@@ -84,7 +89,7 @@ __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int
     int tm = (ROW_MAJOR ? tile / tiles_n : tile % tiles_m) + rot;
     if (tm >= tiles_m) tm -= tiles_m;
     const int tn = ROW_MAJOR ? tile % tiles_n : tile / tiles_m;
-    t.a_row0 = tm * kXBM; t.row_end = M; t.w_row0 = tn * (BN >> half); t.c_col0 = tn * (BN >> half);
+    t.a_row0 = tm * (kXBM * MT); t.row_end = M; t.w_row0 = tn * (BN >> half); t.c_col0 = tn * (BN >> half);
   } else {
     int e = 0;
     while (e + 1 < E && s_tprefix[e + 1] <= tile) ++e;
@@ -173,7 +178,7 @@ __device__ __forceinline__ void x_reduce_tile(const XComm& cm, const __nv_bfloat
   }
 }
 
-template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM>
+template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM, int MT>
 __global__ void __launch_bounds__((XSmem<BN, WQ4>::kThreads + (COMM != kCommNone ? kCommThreads : 0)), 1)
 xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a2,
              const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ CUtensorMap tmap_s,
@@ -181,12 +186,13 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
              const __nv_bfloat16* __restrict__ residual, const int* __restrict__ offsets, int E, int M,
              int N, int K, int ldc, int* __restrict__ status, const XComm cm, int swiglu) {
   static_assert(COMM == kCommNone || !GROUPED, "collective modes are for plain GEMMs");
-  using S = XSmem<BN, WQ4>;
+  static_assert(MT == 1 || (COMM == kCommNone && !GROUPED && 2 * BN * MT <= 512), "stacked tiles: plain GEMM only");
+  using S = XSmem<BN, WQ4, MT>;
   constexpr int STAGES = S::kStages, RAW = S::kRawStages;
   // a role may be waiting, through the pipeline, on a peer that started late: be more patient then
   constexpr uint32_t LIM = (COMM == kCommNone) ? kMbarPollLimit : (kMbarPollLimit << 4);
   constexpr int kCommWarp0 = S::kThreads / 32;          // first of the five collective-mode warps
-  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;
+  constexpr uint32_t TMEM_COLS = (2 * BN * MT <= 32) ? 32 : 2 * BN * MT;
   extern __shared__ char smem_raw[];
   char* smem = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   char* sA = smem;
@@ -215,7 +221,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_n = (N + BN - 1) / BN;
-  int tiles_m = (M + kXBM - 1) / kXBM;
+  int tiles_m = (M + kXBM * MT - 1) / (kXBM * MT);
   const int num_kb = (K + kXBK - 1) / kXBK;
 
   if (threadIdx.x == 0) {
@@ -270,7 +276,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       bool ok = true;
       int ready_mb = -1;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot, swiglu);
+        const XTile t = x_tile<BN, GROUPED, COMM == kCommGather, MT>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot, swiglu);
         if (COMM == kCommGather) {
           const int mb = t.a_row0 / kXBM;
           if (mb != ready_mb) {
@@ -305,7 +311,10 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           }
           if (!mbar_wait(empty + stage, phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
           mbar_arrive_expect_tx(full + stage, S::kStageA + (WQ4 ? 0 : S::kStageB));
-          tma_load_2d(sA + stage * S::kStageA, ta, full + stage, kb * kXBK, t.a_row0);
+#pragma unroll
+          for (int mh = 0; mh < MT; ++mh)
+            tma_load_2d(sA + stage * S::kStageA + mh * (kXBM * kXBK * 2), ta, full + stage, kb * kXBK,
+                        t.a_row0 + mh * kXBM);
           if (!WQ4) {
             tma_load_2d(sB + stage * S::kStageB, &tmap_w, full + stage, kb * kXBK, t.w_row0);
             if (swiglu)
@@ -325,7 +334,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         if (!mbar_wait(acc_empty + acc, acc_phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t d_tmem = tmem_base + acc * BN;
+        const uint32_t d_tmem = tmem_base + acc * (BN * MT);
         for (int kb = 0; kb < num_kb; ++kb) {
           if (!mbar_wait(full + stage, phase, abort_flag, LIM)) { ok = false; break; }
           if (WQ4 && !mbar_wait(bq_full + stage, phase, abort_flag, LIM)) { ok = false; break; }
@@ -334,8 +343,10 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
           const uint32_t b_addr = smem_u32(sB + stage * S::kStageB);
 #pragma unroll
           for (int k = 0; k < kXBK / 16; ++k)
-            tc_mma_f16(d_tmem, umma_desc_sw128_kmajor(a_addr + k * 32),
-                       umma_desc_sw128_kmajor(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int mh = 0; mh < MT; ++mh)
+              tc_mma_f16(d_tmem + mh * BN, umma_desc_sw128_kmajor(a_addr + mh * (kXBM * kXBK * 2) + k * 32),
+                         umma_desc_sw128_kmajor(b_addr + k * 32), idesc, (kb | k) != 0 ? 1u : 0u);
           tc_commit(empty + stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
@@ -356,11 +367,11 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
     if (RESIDUAL && !GROUPED) pdl_wait();
 
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const XTile t = x_tile<BN, GROUPED, COMM == kCommGather>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot, swiglu);
+      const XTile t = x_tile<BN, GROUPED, COMM == kCommGather, MT>(tile, M, N, tiles_m, tiles_n, s_off, s_tprefix, E, rot, swiglu);
       if (!mbar_wait(acc_full + acc, acc_phase, abort_flag, LIM)) { ok = false; break; }
       tc_fence_after_sync();
-      const int row = t.a_row0 + q * 32 + lane;
-      const uint32_t t_row = tmem_base + acc * BN + (uint32_t(q * 32) << 16);
+      int row = t.a_row0 + q * 32 + lane;
+      uint32_t t_row = tmem_base + acc * (BN * MT) + (uint32_t(q * 32) << 16);
       if (COMM == kCommReduce) {
         // partial tile -> the owner's staging slab, laid out so that each warp-wide store is one
         // contiguous 512-byte run: 16-byte group (c*4+v) of row r sits at ((c*4+v)*128 + r)*16.
@@ -390,7 +401,10 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
         // signal two tiles back has gone out)
         if (!mbar_wait(sig_free + acc, acc_phase ^ 1u, abort_flag, LIM)) { ok = false; break; }
         mbar_arrive(sig_full + acc);
-      } else if (swiglu) {
+      } else {
+#pragma unroll 1
+       for (int mh = 0; mh < MT; ++mh, row += kXBM, t_row += BN) {      // stacked 128-row blocks
+        if (swiglu) {
         // accumulator columns [0, BN/2) are the gate, [BN/2, BN) the up projection of the same
         // output columns: out = silu(gate) * up, straight from tensor memory
         const int n_out = N / 2;
@@ -424,10 +438,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             }
           }
         }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(acc_empty + acc);
-      } else {
+        } else {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -465,6 +476,8 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
             }
           }
         }
+        }
+       }
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty + acc);
@@ -656,15 +669,15 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
   pdl_launch_dependents();
 }
 
-template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM = kCommNone>
+template <int BN, bool WQ4, bool GROUPED, bool RESIDUAL, int COMM = kCommNone, int MT = 1>
 static int launch_x(const CUtensorMap& ta, const CUtensorMap& ta2, const CUtensorMap& tw,
                     const CUtensorMap& ts, const CUtensorMap& tb, void* C, const void* residual,
                     const int* offsets, int E, int M, int N, int K, int ldc, int* status, int pdl,
                     cudaStream_t st, const XComm& cm = XComm(), int swiglu = 0) {
-  using S = XSmem<BN, WQ4>;
-  auto kern = xgemm_kernel<BN, WQ4, GROUPED, RESIDUAL, COMM>;
+  using S = XSmem<BN, WQ4, MT>;
+  auto kern = xgemm_kernel<BN, WQ4, GROUPED, RESIDUAL, COMM, MT>;
   RB_CHECK(set_max_smem(kern, S::kBytes));
-  int tiles = ((M + kXBM - 1) / kXBM) * ((N + BN - 1) / BN);
+  int tiles = ((M + kXBM * MT - 1) / (kXBM * MT)) * ((N + BN - 1) / BN);
   if (GROUPED) tiles += E * ((N + BN - 1) / BN);   // upper bound: every group may add a ragged tile
   const int grid = tiles < sm_count() ? (tiles > 0 ? tiles : 1) : sm_count();
   return launch(kern, dim3(grid), dim3(S::kThreads + (COMM != kCommNone ? kCommThreads : 0)), size_t(S::kBytes), st, pdl != 0, ta, ta2, tw, ts, tb,

@@ -39,8 +39,15 @@ extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* 
   if (w_kind == 1 && !rmlx_qgemm_supported(K)) return -2;
   const bool grouped = offsets != nullptr;
   if (grouped && (E < 1 || E > kXMaxExperts)) return -2;
+  // bn < 0: stacked tiles (two 128-row blocks of A per staged block of W) of width |bn| = 128
+  int mt = 1;
+  if (bn < 0) { mt = 2; bn = -bn; }
+  if (mt == 2 && (bn != 128 || grouped)) return -2;
   if (bn == 0) {
     bn = (grouped || w_kind == 1) ? ((N % 256 == 0 && M >= 1024) ? 256 : 128) : 128;
+    // Q4, many rows: the dequant warps are the limit, so share each dequantised block of W
+    // between two row blocks
+    if (w_kind == 1 && !grouped && ((M + 255) / 256) * ((N + 127) / 128) >= 120) { bn = 128; mt = 2; }
     // few rows: the work is streaming W, so spread it over more SMs with narrower tiles
     if (!grouped && ((M + kXBM - 1) / kXBM) * ((N + 127) / 128) < 100) bn = 64;
   }
@@ -56,6 +63,14 @@ extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* 
 #define RB_X(BN_, Q_, G_)                                                                          \
   return residual ? launch_x<BN_, Q_, G_, true>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st) \
                   : launch_x<BN_, Q_, G_, false>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st, XComm(), swiglu)
+  if (mt == 2) {
+    if (w_kind == 1) {
+      return residual ? launch_x<128, true, false, true, kCommNone, 2>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st)
+                      : launch_x<128, true, false, false, kCommNone, 2>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st, XComm(), swiglu);
+    }
+    return residual ? launch_x<128, false, false, true, kCommNone, 2>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st)
+                    : launch_x<128, false, false, false, kCommNone, 2>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st, XComm(), swiglu);
+  }
   if (bn == 256) {
     if (w_kind == 1) { if (grouped) { RB_X(256, true, true); } else { RB_X(256, true, false); } }
     else { if (grouped) { RB_X(256, false, true); } else { RB_X(256, false, false); } }
