@@ -96,9 +96,9 @@ __device__ __forceinline__ XTile x_tile(int tile, int M, int N, int tiles_m, int
     while (s_tprefix[e + 1] <= tile) ++e;                 // skips empty experts
     const int local = tile - s_tprefix[e];
     const int rows = s_off[e + 1] - s_off[e];
-    const int mt_e = (rows + kXBM - 1) / kXBM;
+    const int mt_e = (rows + kXBM * MT - 1) / (kXBM * MT);
     const int nt = local / mt_e, mt = local % mt_e;
-    t.a_row0 = s_off[e] + mt * kXBM; t.row_end = s_off[e + 1];
+    t.a_row0 = s_off[e] + mt * (kXBM * MT); t.row_end = s_off[e + 1];
     t.w_row0 = e * N + nt * (BN >> half); t.c_col0 = nt * (BN >> half);
   }
   return t;
@@ -186,7 +186,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
              const __nv_bfloat16* __restrict__ residual, const int* __restrict__ offsets, int E, int M,
              int N, int K, int ldc, int* __restrict__ status, const XComm cm, int swiglu) {
   static_assert(COMM == kCommNone || !GROUPED, "collective modes are for plain GEMMs");
-  static_assert(MT == 1 || (COMM == kCommNone && !GROUPED && 2 * BN * MT <= 512), "stacked tiles: plain GEMM only");
+  static_assert(MT == 1 || (COMM == kCommNone && 2 * BN * MT <= 512), "stacked tiles: no collective modes");
   using S = XSmem<BN, WQ4, MT>;
   constexpr int STAGES = S::kStages, RAW = S::kRawStages;
   // a role may be waiting, through the pipeline, on a peer that started late: be more patient then
@@ -250,7 +250,7 @@ xgemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__
       int acc = 0;
       for (int e = 0; e < E; ++e) {
         s_tprefix[e] = acc;
-        acc += ((s_off[e + 1] - s_off[e] + kXBM - 1) / kXBM) * tiles_n;
+        acc += ((s_off[e + 1] - s_off[e] + kXBM * MT - 1) / (kXBM * MT)) * tiles_n;
       }
       s_tprefix[E] = acc;
     }

@@ -42,12 +42,15 @@ extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* 
   // bn < 0: stacked tiles (two 128-row blocks of A per staged block of W) of width |bn| = 128
   int mt = 1;
   if (bn < 0) { mt = 2; bn = -bn; }
-  if (mt == 2 && (bn != 128 || grouped)) return -2;
+  if (mt == 2 && (bn != 128 || (grouped && residual))) return -2;
   if (bn == 0) {
     bn = (grouped || w_kind == 1) ? ((N % 256 == 0 && M >= 1024) ? 256 : 128) : 128;
     // Q4, many rows: the dequant warps are the limit, so share each dequantised block of W
     // between two row blocks
     if (w_kind == 1 && !grouped && ((M + 255) / 256) * ((N + 127) / 128) >= 120) { bn = 128; mt = 2; }
+    // grouped: experts with more than 128 rows share their dequantised blocks too (M is the total
+    // row count; below ~256 rows per expert the wider single-block tile measures faster)
+    if (w_kind == 1 && grouped && !residual && M >= 256 * E && N % 128 == 0) { bn = 128; mt = 2; }
     // few rows: the work is streaming W, so spread it over more SMs with narrower tiles
     if (!grouped && ((M + kXBM - 1) / kXBM) * ((N + 127) / 128) < 100) bn = 64;
   }
@@ -63,6 +66,11 @@ extern "C" int rmlx_xgemm(int w_kind, const void* A, const void* W, const void* 
 #define RB_X(BN_, Q_, G_)                                                                          \
   return residual ? launch_x<BN_, Q_, G_, true>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st) \
                   : launch_x<BN_, Q_, G_, false>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st, XComm(), swiglu)
+  if (mt == 2 && grouped) {
+    if (w_kind == 1)
+      return launch_x<128, true, true, false, kCommNone, 2>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st, XComm(), swiglu);
+    return launch_x<128, false, true, false, kCommNone, 2>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st, XComm(), swiglu);
+  }
   if (mt == 2) {
     if (w_kind == 1) {
       return residual ? launch_x<128, true, false, true, kCommNone, 2>(ta, ta, tw, ts, tb, C, residual, offsets, E, M, N, K, ldc, status, pdl, st)
