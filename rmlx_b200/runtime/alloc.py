@@ -249,3 +249,89 @@ class SymmetricHeap:
 def crc32(data: bytes, seed: int = 0) -> int:
     """IEEE CRC32 (same polynomial as zlib) computed by the native library."""
     return int(_host().rmlx_crc32(data, len(data), seed))
+
+
+class ManagedBuffer:
+    """RAII handle: the allocation goes back to its allocator when the handle is closed or dropped
+    (crates/rmlx-metal/src/managed_buffer.rs:21-115)."""
+
+    def __init__(self, allocator: "CachingAllocator", nbytes: int):
+        self._alloc = allocator
+        self.ptr, self.nbytes = allocator.alloc(nbytes)      # address, usable size
+
+    def close(self) -> None:
+        if self.ptr is not None:
+            self._alloc.free(self.ptr)
+            self.ptr = None
+
+    def __enter__(self) -> "ManagedBuffer":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ResidencyManager:
+    """Book-keeping of which allocations must stay resident (crates/rmlx-alloc/src/residency.rs:
+    54-235). Device memory on a discrete GPU is always resident, so this is the counting form: it
+    tracks the set and its bytes and refuses to exceed a budget."""
+
+    def __init__(self, budget_bytes: Optional[int] = None):
+        self.budget = budget_bytes
+        self._set = {}
+
+    def add(self, key, nbytes: int) -> None:
+        if key in self._set:
+            return
+        if self.budget is not None and self.resident_bytes + nbytes > self.budget:
+            raise AllocError("residency budget exceeded")
+        self._set[key] = int(nbytes)
+
+    def remove(self, key) -> None:
+        self._set.pop(key, None)
+
+    def __contains__(self, key) -> bool:
+        return key in self._set
+
+    @property
+    def resident_bytes(self) -> int:
+        return sum(self._set.values())
+
+    def __len__(self) -> int:
+        return len(self._set)
+
+
+class ForwardArena:
+    """Bump allocator over one pre-allocated tensor, reset once per forward pass
+    (crates/rmlx-core/src/arena.rs:12-55): temporaries of a step cost no allocator calls."""
+
+    def __init__(self, nbytes: int, device="cpu", alignment: int = 256):
+        import torch
+        self._buf = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        self._align = alignment
+        self._top = 0
+        self.peak = 0
+
+    def take(self, shape, dtype):
+        import math
+        import torch
+        n = int(math.prod(shape)) * torch.empty((), dtype=dtype).element_size()
+        start = (self._top + self._align - 1) // self._align * self._align
+        if start + n > self._buf.numel():
+            raise AllocError(f"arena exhausted: need {n} bytes at {start} of {self._buf.numel()}")
+        self._top = start + n
+        self.peak = max(self.peak, self._top)
+        return self._buf[start:start + n].view(dtype).view(*shape)
+
+    def reset(self) -> None:
+        self._top = 0
+
+    @property
+    def used(self) -> int:
+        return self._top

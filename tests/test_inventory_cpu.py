@@ -1,0 +1,127 @@
+"""Smaller components of the inventory: MoE overlap schedules, the layer pipeline, prefill plans and
+scratch pool, convolution wrappers, the dtype table, managed buffers / residency / arena."""
+import pytest
+import torch
+
+from rmlx_b200 import dtypes
+from rmlx_b200.config import FeedForwardType, MoeConfig, TransformerConfig
+from rmlx_b200.models.prefill_plan import PrefillPlan, PrefillPool
+from rmlx_b200.nn.conv import Conv1d, Conv2d
+from rmlx_b200.nn.moe import ExpertGroup, MoeLayer
+from rmlx_b200.nn.moe_pipeline import MoePipeline
+from rmlx_b200.ops.weights import LinearWeight
+from rmlx_b200.parallel.pipeline import LayerPipeline, PipelineConfig, Stage
+from rmlx_b200.runtime.alloc import AllocError, ForwardArena, ResidencyManager
+
+
+def _moe_layer():
+    torch.manual_seed(0)
+    cfg = MoeConfig(num_experts=4, num_experts_per_token=2, hidden_dim=32, intermediate_dim=64)
+    gu = LinearWeight.from_dense(torch.randn(4, 128, 32) * 0.1, None, dtype=torch.float32)
+    dn = LinearWeight.from_dense(torch.randn(4, 32, 64) * 0.1, None, dtype=torch.float32)
+    layer = MoeLayer(cfg, torch.randn(4, 32) * 0.3, ExpertGroup(gu, dn))
+    layer.with_shared_expert(LinearWeight.from_dense(torch.randn(128, 32) * 0.1, None, dtype=torch.float32),
+                             LinearWeight.from_dense(torch.randn(32, 64) * 0.1, None, dtype=torch.float32))
+    return layer
+
+
+def test_moe_overlap_schedules_equal_plain_forward():
+    layer = _moe_layer()
+    x = torch.randn(10, 32)
+    want = layer.forward(x)
+    pipe = MoePipeline(layer)
+    assert torch.allclose(pipe.forward_sbo(x), want, atol=1e-5)
+    assert pipe.stats.shared_tokens == 10 and not pipe.stats.used_side_stream
+    got = pipe.forward_tbo(x, micro_batches=3)
+    assert torch.allclose(got, want, atol=1e-5) and pipe.stats.micro_batches == 3
+    assert layer.shared is not None            # restored after the routed-only pass
+
+
+def test_layer_pipeline_stages_and_stats():
+    p = LayerPipeline(PipelineConfig(num_layers=3), device="cpu")
+    seen = []
+    outs = p.run(lambda l: torch.full((4,), float(l)), lambda l, y: (seen.append(l), y * 2)[1])
+    assert seen == [0, 1, 2] and [float(o[0]) for o in outs] == [0.0, 2.0, 4.0]
+    assert p.stats.layers_run == 3 and all(s == Stage.COMPLETE for s in p.stats.stages)
+    assert 0.0 <= p.stats.overlap_ratio <= 1.0
+    ratio = p.measure_overlap(lambda l: torch.ones(8), lambda l, y: y + 1)
+    assert ratio > 0
+    with pytest.raises(ValueError):
+        PipelineConfig(num_layers=0).validate()
+
+
+def test_prefill_plan_and_pool():
+    moe = MoeConfig(num_experts=8, num_experts_per_token=2, hidden_dim=64, intermediate_dim=128)
+    cfg = TransformerConfig(hidden_size=64, num_heads=4, num_kv_heads=2, head_dim=16, num_layers=2,
+                            vocab_size=100, max_seq_len=128, ff_type=FeedForwardType.moe_(moe)).validate()
+    plan = PrefillPlan(cfg, 32)
+    names = [s.name for s in plan.steps]
+    assert names[:5] == ["attn_norm", "qkv", "rope_kv", "attention", "o_proj"] and "combine" in names
+    qkv = plan.steps[1]
+    assert (qkv.m, qkv.n, qkv.k) == (32, (4 + 4) * 16, 64) and qkv.flops == 2.0 * 32 * 128 * 64
+    assert plan.scratch_bytes >= max(s.out_bytes for s in plan.steps) and plan.flops > 0
+    pool = PrefillPool.for_config(cfg, 64, slots=2)
+    assert pool.plan(32) is pool.plan(32)
+    with pytest.raises(ValueError):
+        pool.plan(256)
+    a, b = pool.acquire(), pool.acquire()
+    assert pool.acquire() is None and a[1].numel() == pool.bytes_per_slot
+    pool.release(a[0])
+    assert pool.available == 1
+    with pytest.raises(ValueError):
+        pool.release(a[0])
+    dense = cfg.replace(ff_type=FeedForwardType.gated(256))
+    assert [s.name for s in PrefillPlan(dense, 8).steps][-2:] == ["gate_up", "down"]
+
+
+def test_conv_wrappers_match_torch():
+    torch.manual_seed(1)
+    x = torch.randn(2, 10, 3)
+    w = torch.randn(5, 3, 3)
+    y = Conv1d(w, torch.zeros(5), padding=1)(x)
+    ref = torch.nn.functional.conv1d(x.transpose(1, 2), w.permute(0, 2, 1), None, padding=1).transpose(1, 2)
+    assert y.shape == (2, 10, 5) and torch.allclose(y, ref, atol=1e-5)
+    x2 = torch.randn(1, 6, 6, 4)
+    w2 = torch.randn(8, 3, 3, 2)
+    y2 = Conv2d(w2, stride=2, padding=1, groups=2)(x2)
+    assert y2.shape == (1, 3, 3, 8)
+
+
+def test_dtype_table():
+    assert dtypes.Q4_0.nbytes(64) == 36 and dtypes.Q8_0.nbytes(32) == 34 and dtypes.Q4_1.nbytes(32) == 20
+    assert dtypes.BF16.nbytes(10) == 20 and not dtypes.BF16.is_quantized and dtypes.Q4_0.is_quantized
+    assert dtypes.from_name("BF16") is dtypes.BF16
+    assert dtypes.Q4_AFFINE_G64.nbytes(4096) == 4096 // 64 * 36          # 4.5 bits per weight
+    with pytest.raises(ValueError):
+        dtypes.Q4_0.nbytes(33)
+    with pytest.raises(ValueError):
+        dtypes.from_name("q3_k")
+
+
+def test_residency_and_arena():
+    r = ResidencyManager(budget_bytes=100)
+    r.add("a", 60)
+    r.add("a", 60)
+    assert len(r) == 1 and r.resident_bytes == 60 and "a" in r
+    with pytest.raises(AllocError):
+        r.add("b", 50)
+    r.remove("a")
+    r.add("b", 50)
+    arena = ForwardArena(4096)
+    t1 = arena.take((4, 8), torch.float32)
+    t2 = arena.take((3,), torch.bfloat16)
+    assert t1.shape == (4, 8) and t2.dtype == torch.bfloat16 and arena.used >= 128 + 6
+    t1.fill_(1.0)
+    assert float(t1.sum()) == 32.0
+    with pytest.raises(AllocError):
+        arena.take((4096,), torch.float32)
+    arena.reset()
+    assert arena.used == 0 and arena.peak > 0
+
+
+def test_managed_buffer_returns_memory():
+    from rmlx_b200.runtime.alloc import CachingAllocator, ManagedBuffer
+    a = CachingAllocator()
+    with ManagedBuffer(a, 4096) as b:
+        assert b.ptr and b.nbytes >= 4096 and a.stats().bytes_in_use >= 4096
+    assert a.stats().bytes_in_use == 0
