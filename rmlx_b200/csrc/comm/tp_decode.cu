@@ -16,9 +16,9 @@
 //
 // Receive-buffer protocol (per rank, in symmetric memory; every rank has the same layout):
 //   recv[slot][src_rank][B*N] fp32, arrive[slot], done[slot]; slot alternates between consecutive
-//   all-reduces. Every block of every rank adds 1 to arrive[slot] of every rank after its stores
-//   (fence + release); reducers wait for world*gridDim.x, and the last reducer to finish zeroes
-//   both counters. A rank can run at most one all-reduce ahead of a peer (finishing one needs the
+//   all-reduces. The blocks of a rank count themselves on a local word after their stores
+//   (fence); the last one adds 1 to arrive[slot] of every rank (release); reducers wait for
+//   ``world`` arrivals, and the last reducer to finish zeroes both counters. A rank can run at most one all-reduce ahead of a peer (finishing one needs the
 //   peer's contribution to it), so two slots suffice. All waits are bounded; a wait that gives up
 //   sets a status word the host reads, and the kernel still terminates.
 //
@@ -36,6 +36,10 @@ constexpr int kTpRowsPerWarp = 2;
 constexpr int kTpRowsPerCta = kGemvWarps * kTpRowsPerWarp;  // 16
 
 __device__ int g_tp_status = 0;
+// This GPU's blocks count themselves here (index = token row * 2 + slot; the last two words serve
+// the stand-alone all-reduce) and only the last one publishes an arrival to the peers, so a peer's
+// counter takes ``world`` remote atomics per all-reduce instead of world x grid.
+__device__ uint32_t g_tp_local[72];
 
 struct TpPeers {
   float* recv[kMaxWorld];        // each rank's receive area (peer-mapped); index = destination rank
@@ -50,7 +54,7 @@ template <int B>
 __device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* vals, int n0, int N,
                                                size_t slot_off, int slot,
                                                const __nv_bfloat16* residual, int res_stride,
-                                               __nv_bfloat16* out, int out_stride) {
+                                               __nv_bfloat16* out, int out_stride, int local_idx) {
   __shared__ uint32_t s_ok;
   const int tid = threadIdx.x;
   // 1. push: thread (b, i) owns one value; 16 consecutive threads write 64 contiguous bytes
@@ -64,7 +68,15 @@ __device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* va
     __threadfence_system();
   }
   __syncthreads();
-  if (tid < P.world) red_release_sys_add(P.ctr[tid] + slot * 2, 1u);
+  if (tid == 0) {
+    uint32_t* local = g_tp_local + local_idx;
+    __threadfence_system();
+    if (atomicAdd(local, 1u) == gridDim.x - 1) {      // last block of this rank: publish once per peer
+      *local = 0u;
+      __threadfence_system();
+      for (int p = 0; p < P.world; ++p) red_release_sys_add(P.ctr[p] + slot * 2, 1u);
+    }
+  }
 
   // 2. the last kReducers blocks of the grid reduce one slice of the output each
   const int ridx = int(blockIdx.x) - (int(gridDim.x) - kReducers);
@@ -73,7 +85,7 @@ __device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* va
   if (my < 0) return;
   uint32_t* ctr = P.ctr[P.rank] + slot * 2;
   if (tid == 0) {
-    const bool ok = wait_flag_ge(ctr, uint32_t(P.world) * gridDim.x);
+    const bool ok = wait_flag_ge(ctr, uint32_t(P.world));
     if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
     s_ok = ok ? 1u : 0u;
   }
@@ -143,7 +155,7 @@ gemv_allreduce_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_s
       if (lane == 0) vals[b * kTpRowsPerCta + warp * kTpRowsPerWarp + r] = v;
     }
   __syncthreads();
-  tp_push_reduce<B>(P, vals, n0, N, slot_off, slot, residual, res_stride, out, out_stride);
+  tp_push_reduce<B>(P, vals, n0, N, slot_off, slot, residual, res_stride, out, out_stride, 64 + slot);
   pdl_launch_dependents();
 }
 
@@ -232,7 +244,7 @@ moe_down_allreduce_kernel(ExpertMat<WT> W, const __nv_bfloat16* __restrict__ act
   for (int p = 0; p < P.world; ++p) Q.ctr[p] = P.ctr[p] + size_t(b) * 2 * slots_total;
   tp_push_reduce<1>(Q, vals, n0, N, slot_off + size_t(b) * slot_stride_y, slot,
                     residual ? residual + size_t(b) * res_stride : nullptr, 0,
-                    out + size_t(b) * out_stride, 0);
+                    out + size_t(b) * out_stride, 0, b * 2 + slot);
   pdl_launch_dependents();
 }
 
@@ -256,10 +268,18 @@ allreduce_oneshot_kernel(const float* __restrict__ in, const __nv_bfloat16* __re
   }
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x < P.world) red_release_sys_add(P.ctr[threadIdx.x] + slot * 2, 1u);
+  if (threadIdx.x == 0) {
+    uint32_t* local = g_tp_local + 70 + slot;
+    __threadfence_system();
+    if (atomicAdd(local, 1u) == gridDim.x - 1) {
+      *local = 0u;
+      __threadfence_system();
+      for (int p = 0; p < P.world; ++p) red_release_sys_add(P.ctr[p] + slot * 2, 1u);
+    }
+  }
   uint32_t* ctr = P.ctr[P.rank] + slot * 2;
   if (threadIdx.x == 0) {
-    const bool ok = wait_flag_ge(ctr, uint32_t(P.world) * gridDim.x);
+    const bool ok = wait_flag_ge(ctr, uint32_t(P.world));
     if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
     s_ok = ok ? 1u : 0u;
   }
