@@ -204,6 +204,14 @@ __device__ __forceinline__ void load_tile(const RowBf16 (&rows)[R], int K, int c
     for (int r = 0; r < R; ++r)
       t.w[u][r] = (c < nchunk) ? ldg_stream(rows[r].w + (size_t(c) << 3)) : make_uint4(0, 0, 0, 0);
   }
+  // pull the next tile of every row (8 lines of 128 bytes each) towards L2 while this one is used
+  if (lane < 8) {
+    const int c = c0 + 64 + lane * 8;
+    if (c < nchunk) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) prefetch_l2(rows[r].w + (size_t(c) << 3));
+    }
+  }
 }
 
 template <int R, int B>
@@ -261,6 +269,14 @@ __device__ __forceinline__ void load_tile(const RowQ4 (&rows)[R], int K, int h0,
       } else {
         t.w[u][r] = make_uint4(0, 0, 0, 0); t.sc[u][r] = 0.f; t.bi[u][r] = 0.f;
       }
+    }
+  }
+  // pull the next tile of every row (8 lines of 128 bytes each) towards L2 while this one is used
+  if (lane < 8) {
+    const int hg = h0 + 64 + lane * 8;
+    if (hg < nhg) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) prefetch_l2(rows[r].w + (size_t(hg) << 2));
     }
   }
 }
