@@ -1,8 +1,8 @@
 // Tensor-parallel decode kernels that fuse the row-parallel projection with its all-reduce over
 // NVLink peer memory: ONE launch computes the local partial product, pushes it into every rank's
-// receive buffer with plain peer stores, signals with a release-add on the peer's arrival counter,
-// and a few "reducer" blocks of the same grid wait (bounded) for all ranks, sum the partials in
-// rank order, add the residual and write the result. No host, no NCCL, no extra launch.
+// receive buffer with plain peer stores that carry their own arrival tag, and every block then
+// collects its own rows from all ranks (bounded waits), sums the partials in rank order, adds the
+// residual and writes the result. No host, no NCCL, no extra launch.
 //
 //   gemv_allreduce        O projection (or dense down projection) + all-reduce + residual
 //   moe_down_allreduce    expert down projection + routing-weighted combine + all-reduce + residual
@@ -15,12 +15,12 @@
 // crates/rmlx-distributed/src/group.rs:348-504, crates/rmlx-nn/src/parallel.rs:619-693).
 //
 // Receive-buffer protocol (per rank, in symmetric memory; every rank has the same layout):
-//   recv[slot][src_rank][B*N] fp32, arrive[slot], done[slot]; slot alternates between consecutive
-//   all-reduces. The blocks of a rank count themselves on a local word after their stores
-//   (fence); the last one adds 1 to arrive[slot] of every rank (release); reducers wait for
-//   ``world`` arrivals, and the last reducer to finish zeroes both counters. A rank can run at most one all-reduce ahead of a peer (finishing one needs the
-//   peer's contribution to it), so two slots suffice. All waits are bounded; a wait that gives up
-//   sets a status word the host reads, and the kernel still terminates.
+//   recv[slot][src_rank][B*N] 8-byte words (fp32 value, 32-bit tag); slot alternates between
+//   consecutive all-reduces. A value and its arrival flag travel in one 8-byte store, so the
+//   exchange costs one NVLink crossing: no fence, no counter, no reducer blocks. A rank can run
+//   at most one all-reduce ahead of a peer (finishing one needs the peer's contribution to it), so
+//   two slots suffice. All waits are bounded; a wait that gives up sets a status word the host
+//   reads, and the kernel still terminates.
 //
 // Remote data is only ever read with plain loads from this GPU's own memory (peers push); nothing
 // here uses TMA on peer memory.
@@ -31,85 +31,76 @@
 namespace rb {
 
 constexpr int kMaxWorld = 8;
-constexpr int kReducers = 4;
 constexpr int kTpRowsPerWarp = 2;
 constexpr int kTpRowsPerCta = kGemvWarps * kTpRowsPerWarp;  // 16
 
 __device__ int g_tp_status = 0;
-// This GPU's blocks count themselves here (index = token row * 2 + slot; the last two words serve
-// the stand-alone all-reduce) and only the last one publishes an arrival to the peers, so a peer's
-// counter takes ``world`` remote atomics per all-reduce instead of world x grid.
-__device__ uint32_t g_tp_local[72];
 
 struct TpPeers {
-  float* recv[kMaxWorld];        // each rank's receive area (peer-mapped); index = destination rank
-  uint32_t* ctr[kMaxWorld];      // each rank's counters: [slot*2 + 0] arrive, [slot*2 + 1] done
+  float* recv[kMaxWorld];        // each rank's receive area of 8-byte (value, tag) words (peer-mapped)
+  uint32_t* ctr[kMaxWorld];      // each rank's counters: [slot*2 + 0] calls completed on the slot, [slot*2 + 1] exit ticket
   int rank, world;
 };
 
-// Push this block's partial values and take part in the reduction.
+// 8-byte (value, tag) words: a peer's store of such a word is a single transaction, so the tag is
+// the arrival flag of its value and no fence or separate counter is needed (the low-latency
+// protocol of collective libraries). Tags are the slot's call number + 1; memory starts zeroed.
+__device__ __forceinline__ void st_ll(uint2* p, float v, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
+}
+__device__ __forceinline__ bool ld_ll(const uint2* p, uint32_t tag, float& v) {
+  for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
+    uint32_t a, b;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(b) : "l"(p) : "memory");
+    if (b == tag) { v = __uint_as_float(a); return true; }
+    if (i > 256) __nanosleep(i > 8192 ? 128 : 20);
+  }
+  v = 0.f;
+  return false;
+}
+
+// Exchange this block's partial values and finish its own rows.
 //   vals: shared memory [B][kTpRowsPerCta] fp32 partial sums for rows n0 .. n0+15
-//   recv layout per rank: slot_off + (src*B + b)*N + n
+//   recv layout per rank (8-byte words): slot_off + (src*B + b)*N + n
+// Thread (b, i) stores its value, tagged, into every peer's receive area, then collects the same
+// element from every peer out of its own receive area and sums in rank order (so every rank gets
+// bit-identical results), adds the residual and writes the output. Blocks never wait for other
+// blocks: the same block index owns the same rows on every rank. ctr[0] is the slot's call count,
+// ctr[1] the exit ticket that advances it (both local).
 template <int B>
 __device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* vals, int n0, int N,
                                                size_t slot_off, int slot,
                                                const __nv_bfloat16* residual, int res_stride,
-                                               __nv_bfloat16* out, int out_stride, int local_idx) {
-  __shared__ uint32_t s_ok;
+                                               __nv_bfloat16* out, int out_stride) {
   const int tid = threadIdx.x;
-  // 1. push: thread (b, i) owns one value; 16 consecutive threads write 64 contiguous bytes
+  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
+  const uint32_t tag = ctr[0] + 1u;
   if (tid < B * kTpRowsPerCta) {
     const int b = tid / kTpRowsPerCta, i = tid % kTpRowsPerCta;
     if (n0 + i < N) {
       const float v = vals[tid];
-      const size_t off = slot_off + (size_t(P.rank) * B + b) * N + n0 + i;
-      for (int p = 0; p < P.world; ++p) P.recv[p][off] = v;
-    }
-    __threadfence_system();
-  }
-  __syncthreads();
-  if (tid == 0) {
-    uint32_t* local = g_tp_local + local_idx;
-    __threadfence_system();
-    if (atomicAdd(local, 1u) == gridDim.x - 1) {      // last block of this rank: publish once per peer
-      *local = 0u;
-      __threadfence_system();
-      for (int p = 0; p < P.world; ++p) red_release_sys_add(P.ctr[p] + slot * 2, 1u);
-    }
-  }
-
-  // 2. the last kReducers blocks of the grid reduce one slice of the output each
-  const int ridx = int(blockIdx.x) - (int(gridDim.x) - kReducers);
-  const int nred = min(kReducers, int(gridDim.x));
-  const int my = (gridDim.x >= kReducers) ? ridx : int(blockIdx.x);
-  if (my < 0) return;
-  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
-  if (tid == 0) {
-    const bool ok = wait_flag_ge(ctr, uint32_t(P.world));
-    if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
-    s_ok = ok ? 1u : 0u;
-  }
-  __syncthreads();
-  const float* mine = P.recv[P.rank] + slot_off;
-  const int per = (N + nred - 1) / nred;
-  const int lo = my * per, hi = min(N, lo + per);
-  for (int idx = lo + tid; idx < hi; idx += blockDim.x) {
-#pragma unroll
-    for (int b = 0; b < B; ++b) {
+      const size_t mine = slot_off + (size_t(P.rank) * B + b) * N + n0 + i;
+      for (int pi = 1; pi < P.world; ++pi) {
+        int p = P.rank + pi; if (p >= P.world) p -= P.world;
+        st_ll(reinterpret_cast<uint2*>(P.recv[p]) + mine, v, tag);
+      }
+      const uint2* rb = reinterpret_cast<const uint2*>(P.recv[P.rank]) + slot_off;
       float s = 0.f;
-      for (int src = 0; src < P.world; ++src) s += __ldcg(mine + (size_t(src) * B + b) * N + idx);
-      if (residual) s += __bfloat162float(residual[size_t(b) * res_stride + idx]);
-      out[size_t(b) * out_stride + idx] = __float2bfloat16_rn(s);
+      bool ok = true;
+      for (int src = 0; src < P.world; ++src) {
+        float u = v;
+        if (src != P.rank) ok = ld_ll(rb + (size_t(src) * B + b) * N + n0 + i, tag, u) && ok;
+        s += u;
+      }
+      if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
+      if (residual) s += __bfloat162float(residual[size_t(b) * res_stride + n0 + i]);
+      out[size_t(b) * out_stride + n0 + i] = __float2bfloat16_rn(s);
     }
   }
   __syncthreads();
   if (tid == 0) {
     __threadfence();
-    if (atomicAdd(ctr + 1, 1u) == uint32_t(nred - 1)) {  // last reducer: ready for the slot's next use
-      ctr[1] = 0u;
-      __threadfence();
-      ctr[0] = 0u;
-    }
+    if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) { ctr[1] = 0u; __threadfence(); ctr[0] = tag; }
   }
 }
 
@@ -155,7 +146,7 @@ gemv_allreduce_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_s
       if (lane == 0) vals[b * kTpRowsPerCta + warp * kTpRowsPerWarp + r] = v;
     }
   __syncthreads();
-  tp_push_reduce<B>(P, vals, n0, N, slot_off, slot, residual, res_stride, out, out_stride, 64 + slot);
+  tp_push_reduce<B>(P, vals, n0, N, slot_off, slot, residual, res_stride, out, out_stride);
   pdl_launch_dependents();
 }
 
@@ -244,7 +235,7 @@ moe_down_allreduce_kernel(ExpertMat<WT> W, const __nv_bfloat16* __restrict__ act
   for (int p = 0; p < P.world; ++p) Q.ctr[p] = P.ctr[p] + size_t(b) * 2 * slots_total;
   tp_push_reduce<1>(Q, vals, n0, N, slot_off + size_t(b) * slot_stride_y, slot,
                     residual ? residual + size_t(b) * res_stride : nullptr, 0,
-                    out + size_t(b) * out_stride, 0, b * 2 + slot);
+                    out + size_t(b) * out_stride, 0);
   pdl_launch_dependents();
 }
 
@@ -256,38 +247,32 @@ template <bool OUT_F32>
 __global__ void __launch_bounds__(256)
 allreduce_oneshot_kernel(const float* __restrict__ in, const __nv_bfloat16* __restrict__ residual,
                          void* __restrict__ out, int n, TpPeers P, size_t slot_off, int slot) {
-  __shared__ uint32_t s_ok;
   pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
+  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
+  const uint32_t tag = ctr[0] + 1u;
   const int per = (n + gridDim.x - 1) / gridDim.x;
   const int lo = blockIdx.x * per, hi = min(n, lo + per);
+  const uint2* rb = reinterpret_cast<const uint2*>(P.recv[P.rank]) + slot_off;
+  // all stores first, so that a thread's several elements cross the link together
   for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
     const float v = in[i];
-    const size_t off = slot_off + size_t(P.rank) * n + i;
-    for (int p = 0; p < P.world; ++p) P.recv[p][off] = v;
-  }
-  __threadfence_system();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    uint32_t* local = g_tp_local + 70 + slot;
-    __threadfence_system();
-    if (atomicAdd(local, 1u) == gridDim.x - 1) {
-      *local = 0u;
-      __threadfence_system();
-      for (int p = 0; p < P.world; ++p) red_release_sys_add(P.ctr[p] + slot * 2, 1u);
+    const size_t mine = slot_off + size_t(P.rank) * n + i;
+    for (int pi = 1; pi < P.world; ++pi) {
+      int p = P.rank + pi; if (p >= P.world) p -= P.world;
+      st_ll(reinterpret_cast<uint2*>(P.recv[p]) + mine, v, tag);
     }
   }
-  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
-  if (threadIdx.x == 0) {
-    const bool ok = wait_flag_ge(ctr, uint32_t(P.world));
-    if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
-    s_ok = ok ? 1u : 0u;
-  }
-  __syncthreads();
-  const float* mine = P.recv[P.rank] + slot_off;
   for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+    const float v = in[i];
     float s = 0.f;
-    for (int src = 0; src < P.world; ++src) s += __ldcg(mine + size_t(src) * n + i);
+    bool ok = true;
+    for (int src = 0; src < P.world; ++src) {
+      float u = v;
+      if (src != P.rank) ok = ld_ll(rb + size_t(src) * n + i, tag, u) && ok;
+      s += u;
+    }
+    if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
     if (residual) s += __bfloat162float(residual[i]);
     if (OUT_F32) reinterpret_cast<float*>(out)[i] = s;
     else reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(s);
@@ -295,7 +280,7 @@ allreduce_oneshot_kernel(const float* __restrict__ in, const __nv_bfloat16* __re
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) { ctr[1] = 0u; __threadfence(); ctr[0] = 0u; }
+    if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) { ctr[1] = 0u; __threadfence(); ctr[0] = tag; }
   }
   pdl_launch_dependents();
 }

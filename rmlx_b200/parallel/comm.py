@@ -100,7 +100,7 @@ class PeerComm:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         w = self.world
         self.slot_floats = w * max_batch * hidden
-        self.recv_bytes = self.SLOTS * self.slot_floats * 4
+        self.recv_bytes = self.SLOTS * self.slot_floats * 8      # 8-byte (value, tag) words
         # counters: per token a block of 2*SLOTS words; then argmax counters; then barrier word
         self.ctr_words = 2 * self.SLOTS * max_batch + 2 * self.SLOTS + 4
         self.ctr_off = self.recv_bytes
