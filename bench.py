@@ -153,8 +153,16 @@ def main():
     for l in range(cfg.num_layers):
         cache.k[l].normal_(0, 1)
         cache.v[l].normal_(0, 1)
-    eng = CachedDecode(model, cache, max_batch=B, use_graph=not args.no_graph, pdl=not args.no_pdl,
-                       comm=comm)
+    if B <= 4:
+        eng = CachedDecode(model, cache, max_batch=B, use_graph=not args.no_graph, pdl=not args.no_pdl,
+                           comm=comm)
+    else:   # more rows than the mat-vec kernels take: the tensor-core decode step
+        from rmlx_b200.models.prefill import BatchedDecode, enable_native_prefill
+        if world > 1:
+            print("bench.py: --batch > 4 runs on one GPU", file=sys.stderr)
+            return 2
+        enable_native_prefill(model)
+        eng = BatchedDecode(model, cache, max_batch=B, use_graph=not args.no_graph)
     eng.bind(list(range(B)), [1] * B)
     eng.reserve(total_steps + 1)
     torch.cuda.synchronize()

@@ -5,8 +5,8 @@ This is the B200 form of the reference's ``CachedDecode`` + fused 7-dispatch lay
 (crates/rmlx-nn/src/transformer.rs:2306-2555,3613-4050) and of its ExecGraph / command-batcher
 machinery (crates/rmlx-metal/src/exec_graph.rs:110-401). Per layer the captured step holds:
 
-  1. RMSNorm + QKV projection            (rms_gemv)
-  2. RoPE(Q,K) + paged KV append         (rope_kv_write)
+  1. RMSNorm + QKV projection  }  one kernel (rms_qkv_rope): the rotation and the page append
+  2. RoPE(Q,K) + paged KV append }  happen in the projection's epilogue
   3. paged split-KV flash decode         (flash_decode_paged, merges its splits in-kernel)
   4. O projection + residual             (rms_gemv)             [tensor parallel: + all-reduce]
   5. MoE: RMSNorm + router + top-k       (moe_router)
@@ -19,6 +19,8 @@ sampled token back as the next input. Consecutive kernels are chained with progr
 launch so each one's prologue overlaps its predecessor's tail.
 """
 from __future__ import annotations
+
+import os
 
 from typing import Callable, List, Optional, Sequence
 
@@ -43,6 +45,8 @@ class CachedDecode:
         self.pdl = pdl
         self.use_graph = use_graph
         self.greedy = greedy
+        # RoPE and the KV append run in the QKV projection's epilogue unless switched off
+        self.fuse_rope = os.environ.get("RMLX_FUSE_ROPE", "1") != "0"
         dev = model.device
         B, D_ = max_batch, cfg.hidden_size
         hq, hkv, hd = model.hq, model.hkv, cfg.head_dim
@@ -121,10 +125,15 @@ class CachedDecode:
         D.embedding(w.embed, self.tokens, out=self.h, pdl=False)
         h, h2 = self.h, self.h2
         for li, lw in enumerate(w.layers):
-            D.rms_gemv(h, lw.wqkv, lw.norm1, eps, out=self.qkv, pdl=pdl)
-            D.rope_kv_write(self.qkv, self.q, self.cache.k[li], self.cache.v[li], self.block_table,
-                            self.positions, m.cos, m.sin, m.hq, m.hkv,
-                            traditional=cfg.rope_traditional, pdl=pdl)
+            if self.fuse_rope:
+                D.rms_qkv_rope(h, lw.wqkv, lw.norm1, eps, self.q, self.cache.k[li], self.cache.v[li],
+                               self.block_table, self.positions, m.cos, m.sin, m.hq, m.hkv,
+                               traditional=cfg.rope_traditional, pdl=pdl)
+            else:
+                D.rms_gemv(h, lw.wqkv, lw.norm1, eps, out=self.qkv, pdl=pdl)
+                D.rope_kv_write(self.qkv, self.q, self.cache.k[li], self.cache.v[li], self.block_table,
+                                self.positions, m.cos, m.sin, m.hq, m.hkv,
+                                traditional=cfg.rope_traditional, pdl=pdl)
             D.flash_decode_paged(self.q, self.cache.k[li], self.cache.v[li], self.block_table,
                                  self.seq_lens, m.scale, self.splits, self.fd_scratch,
                                  cfg.sliding_window, out=self.attn, pdl=pdl)

@@ -192,6 +192,7 @@ class BatchedDecode:
         self.fd = D.FlashDecodeScratch(b, model.hq, model.hkv, cfg.head_dim, self.splits, dev)
         self.argmax_scratch = D.ArgmaxScratch(b, dev)
         self.seq_ids: List[int] = []
+        self.launches_per_step = 0           # launches of this package's kernels in one step
         self.use_graph = use_graph and model.layout.world == 1
         self._graph: Optional[torch.cuda.CUDAGraph] = None
 
@@ -240,10 +241,14 @@ class BatchedDecode:
     def step(self) -> torch.Tensor:
         """Run one step for every bound sequence; returns the next-token ids (device, int32)."""
         if not self.use_graph:
+            n0 = _lib.launch_count()
             self._body()
+            self.launches_per_step = _lib.launch_count() - n0
         else:
             if self._graph is None:
+                n0 = _lib.launch_count()
                 self._body()                         # warm-up outside capture (lazy initialisations)
+                self.launches_per_step = _lib.launch_count() - n0
                 self._rewind()
                 torch.cuda.synchronize()
                 g = torch.cuda.CUDAGraph()

@@ -293,6 +293,33 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
     return q_out
 
 
+_lib.register_cuda_sigs({
+    "rmlx_rms_qkv_rope": ("ippppipfppppppppiiiiiiiiip", "i"),
+})
+
+
+def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor], eps: float,
+                 q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                 block_table: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor,
+                 sin: torch.Tensor, hq: int, hkv: int, row_seq: Optional[torch.Tensor] = None,
+                 traditional: bool = False, pdl: bool = False) -> torch.Tensor:
+    """RMSNorm + merged QKV projection + RoPE(Q, K) + paged K/V append in one kernel (up to 4 rows).
+    x [B, K] bf16; q_out [B, Hq, D]; the new K/V rows go straight to their page slots."""
+    _lib.require_cuda_tensor(x, w.w, q_out, k_cache, v_cache, block_table, positions, cos, sin)
+    b, k = x.shape
+    d = k_cache.shape[3]
+    assert w.n == (hq + 2 * hkv) * d and w.k == k and x.stride(1) == 1 and q_out.is_contiguous()
+    assert positions.dtype == torch.int32 and block_table.dtype == torch.int32 and cos.dtype == torch.float32
+    rc = _lib.cuda().rmlx_rms_qkv_rope(
+        w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), x.data_ptr(), x.stride(0),
+        _lib.ptr(norm_w), eps, q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        block_table.data_ptr(), positions.data_ptr(), _lib.ptr(row_seq), cos.data_ptr(), sin.data_ptr(),
+        b, k, hq, hkv, d, block_table.stride(0), k_cache.shape[2], int(traditional), int(pdl),
+        _lib.stream_ptr())
+    _lib.check(rc, "rms_qkv_rope")
+    return q_out
+
+
 def rope(x: torch.Tensor, positions: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor,
          traditional: bool = False, inverse: bool = False) -> torch.Tensor:
     """x [T, H, D] bf16."""

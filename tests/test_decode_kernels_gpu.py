@@ -232,3 +232,28 @@ def test_small_kernels(dev):
     assert am[0] == int(logits[0].argmax()) and am[1] == 77 and am[2] == 5
     gu = torch.randn(9, 2 * 384, device=dev).to(torch.bfloat16)
     _close(D.silu_mul(gu), ref.swiglu(gu.float()))
+
+
+@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("b,traditional", [(1, False), (3, False), (2, True)])
+def test_rms_qkv_rope_matches_unfused(dev, quant, b, traditional):
+    """The fused projection + RoPE + page append equals the projection kernel followed by the
+    rope/append kernel (up to the bf16 rounding of the un-rotated projection that it skips)."""
+    torch.manual_seed(5)
+    hq, hkv, hd, k = 8, 2, 64, 512
+    w = LinearWeight.from_dense(torch.randn((hq + 2 * hkv) * hd, k) * 0.05, quant, device=dev)
+    nw = (1 + 0.1 * torch.randn(k, device=dev)).to(torch.bfloat16)
+    x = torch.randn(b, k, device=dev).to(torch.bfloat16)
+    cos, sin = ref.rope_tables(hd, 128, 1e4, device=dev)
+    pos = torch.tensor([5, 37, 70][:b], dtype=torch.int32, device=dev)
+    bt = torch.arange(1, 1 + b * 8, dtype=torch.int32, device=dev).view(b, 8)
+    kc1 = torch.zeros(1 + b * 8, hkv, 16, hd, device=dev, dtype=torch.bfloat16)
+    vc1, kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(kc1), torch.zeros_like(kc1)
+    q1 = torch.zeros(b, hq, hd, device=dev, dtype=torch.bfloat16)
+    q2 = torch.zeros_like(q1)
+    D.rms_qkv_rope(x, w, nw, 1e-6, q1, kc1, vc1, bt, pos, cos, sin, hq, hkv, traditional=traditional)
+    qkv = D.rms_gemv(x, w, nw, 1e-6)
+    D.rope_kv_write(qkv, q2, kc2, vc2, bt, pos, cos, sin, hq, hkv, traditional=traditional)
+    for got, want in ((q1, q2), (kc1, kc2), (vc1, vc2)):
+        assert (got.float() - want.float()).abs().max().item() < 3e-2 * max(1.0, want.float().abs().max().item())
+    assert kc1.float().abs().sum() > 0 and vc1.float().abs().sum() > 0
