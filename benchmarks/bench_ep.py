@@ -48,6 +48,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", default="4,32,128,4096")
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--layer", action="store_true", help="also time the whole expert-parallel MoE layer")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "q4"])
     a = ap.parse_args()
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", rank)))
@@ -80,7 +82,41 @@ def main():
         remote = t * k * (world - 1) / world
         floor = 2 * remote * hidden * 2 / 770e3
         rows.append((t, tf, tn, floor, err))
+    # ---- the whole expert-parallel MoE layer: router -> dispatch -> grouped expert FFN -> combine
+    layer_rows = []
+    if a.layer:
+        from rmlx_b200.ops.grouped import grouped_expert_ffn
+        from rmlx_b200.ops.weights import LinearWeight
+        from rmlx_b200.parallel.ep_fused import FusedEpMoe
+        inter, el = 1536, E // world
+        quant = None if a.weights == "bf16" else "q4"
+        gu = LinearWeight.random(2 * inter, hidden, quant, dev, experts=el)
+        dn = LinearWeight.random(hidden, inter, quant, dev, experts=el)
+        router = (torch.randn(E, hidden, device=dev) * 0.05).to(torch.bfloat16)
+        moe = FusedEpMoe(fused, gu, dn)
+        for t in toks:
+            torch.manual_seed(1000 + rank)
+            x = torch.randn(t, hidden, device=dev).to(torch.bfloat16)
+
+            def layer_fused():
+                return moe.forward(x, router, k)
+
+            def layer_lib():
+                logits = torch.mm(x, router.t(), out_dtype=torch.float32)
+                idx, wts, _, _ = D.topk_route(logits, k)
+                got, layout = lib.dispatch(x, idx.long())
+                y = grouped_expert_ffn(got, layout.offsets, gu, dn)
+                return lib.combine(y, wts, layout)
+
+            fa, fb = layer_fused().float(), layer_lib()
+            err = (fa - fb).abs().max().item() / max(fb.abs().max().item(), 1e-6)
+            layer_rows.append((t, timed(layer_fused, a.iters), timed(layer_lib, a.iters), err))
     st = fused.status()
+    if rank == 0 and layer_rows:
+        print(f"# expert-parallel MoE layer end to end (router + exchange + grouped FFN + combine), weights={a.weights}")
+        print(f"{'tokens/rank':>11s} {'fused us':>9s} {'nccl us':>9s} {'speedup':>8s} {'max rel diff':>12s}")
+        for t, tf, tn, err in layer_rows:
+            print(f"{t:11d} {tf:9.1f} {tn:9.1f} {tn / tf:8.2f} {err:12.1e}")
     if rank == 0:
         print(f"# world={world} hidden={hidden} experts={E} top_k={k}; NVLink 770 GB/s/dir; status={st}")
         print(f"{'tokens/rank':>11s} {'fused us':>9s} {'nccl us':>9s} {'speedup':>8s} {'floor us':>9s} {'floor/fused':>11s} {'max rel diff':>12s}")
