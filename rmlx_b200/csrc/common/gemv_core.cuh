@@ -104,15 +104,26 @@ struct XStage<WBf16> {
   // Stage K values produced chunk by chunk by ``load``. Ends with a block barrier.
   template <class F>
   static __device__ void stage_with(char* smem, int K, F& load) {
+    stage_part(smem, K, load, threadIdx.x, kGemvThreads);
+    __syncthreads();
+  }
+  // One warp stages a whole vector by itself (ends with a warp barrier): lets the warps of a block
+  // stage different vectors at the same time.
+  template <class F>
+  static __device__ void stage_warp(char* smem, int K, F& load) {
+    stage_part(smem, K, load, threadIdx.x & 31, 32);
+    __syncwarp();
+  }
+  template <class F>
+  static __device__ void stage_part(char* smem, int K, F& load, int t, int nt) {
     float4* xs = reinterpret_cast<float4*>(smem);
     const int nchunk = K >> 3;
-    for (int c = threadIdx.x; c < nchunk; c += kGemvThreads) {
+    for (int c = t; c < nchunk; c += nt) {
       float f[8];
       load(c, f);
       xs[c] = make_float4(f[0], f[1], f[2], f[3]);
       xs[nchunk + c] = make_float4(f[4], f[5], f[6], f[7]);
     }
-    __syncthreads();
   }
   static __device__ float stage(char* smem, const __nv_bfloat16* x, const __nv_bfloat16* scale_w,
                                 int K, float* red, bool want_ssq) {
@@ -134,12 +145,23 @@ struct XStage<WQ4> {
   // block barrier.
   template <class F>
   static __device__ void stage_with(char* smem, int K, F& load) {
+    stage_part(smem, K, load, threadIdx.x, kGemvThreads);
+    __syncthreads();
+  }
+  // One warp stages a whole vector by itself (ends with a warp barrier).
+  template <class F>
+  static __device__ void stage_warp(char* smem, int K, F& load) {
+    stage_part(smem, K, load, threadIdx.x & 31, 32);
+    __syncwarp();
+  }
+  template <class F>
+  static __device__ void stage_part(char* smem, int K, F& load, int t, int nt) {
     uint4* xh = reinterpret_cast<uint4*>(smem);
     const int nchunk = K >> 3, nhg = K >> 5;
     float* xs = reinterpret_cast<float*>(smem + size_t(K) * 2);
     float* qm = xs + nhg;
-    for (int c0 = 0; c0 < nchunk; c0 += kGemvThreads) {
-      const int c = c0 + threadIdx.x;
+    for (int c0 = 0; c0 < nchunk; c0 += nt) {
+      const int c = c0 + t;
       const bool valid = c < nchunk;               // nchunk is a multiple of 4: groups are all-in or all-out
       float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       if (valid) load(c, f);
@@ -168,7 +190,6 @@ struct XStage<WQ4> {
         if ((c & 3) == 0) { xs[c >> 2] = sum; qm[c >> 2] = inv * 16777216.f; }
       }
     }
-    __syncthreads();
   }
   static __device__ float stage(char* smem, const __nv_bfloat16* x, const __nv_bfloat16* scale_w,
                                 int K, float* red, bool want_ssq) {
