@@ -156,7 +156,8 @@ def main():
     if B <= 4:
         eng = CachedDecode(model, cache, max_batch=B, use_graph=not args.no_graph, pdl=not args.no_pdl,
                            comm=comm)
-    else:   # more rows than the mat-vec kernels take: the tensor-core decode step
+    else:   # more rows than one mat-vec launch takes: the tensor-core decode step (experts are
+            # shared across tokens there; the mat-vec engine would re-read them per token)
         from rmlx_b200.models.prefill import BatchedDecode, enable_native_prefill
         if world > 1:
             print("bench.py: --batch > 4 runs on one GPU", file=sys.stderr)

@@ -310,13 +310,19 @@ def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor
     d = k_cache.shape[3]
     assert w.n == (hq + 2 * hkv) * d and w.k == k and x.stride(1) == 1 and q_out.is_contiguous()
     assert positions.dtype == torch.int32 and block_table.dtype == torch.int32 and cos.dtype == torch.float32
-    rc = _lib.cuda().rmlx_rms_qkv_rope(
-        w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), x.data_ptr(), x.stride(0),
-        _lib.ptr(norm_w), eps, q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
-        block_table.data_ptr(), positions.data_ptr(), _lib.ptr(row_seq), cos.data_ptr(), sin.data_ptr(),
-        b, k, hq, hkv, d, block_table.stride(0), k_cache.shape[2], int(traditional), int(pdl),
-        _lib.stream_ptr())
-    _lib.check(rc, "rms_qkv_rope")
+    for b0 in range(0, b, _MAXB):          # the kernel takes up to four rows per launch
+        bb = min(_MAXB, b - b0)
+        xs, qs = x[b0:b0 + bb], q_out[b0:b0 + bb]
+        # without an explicit map, row r of this launch is sequence b0 + r: shift the table instead
+        bt = block_table if row_seq is not None else block_table[b0:]
+        rs = None if row_seq is None else row_seq[b0:]
+        rc = _lib.cuda().rmlx_rms_qkv_rope(
+            w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(), xs.stride(0),
+            _lib.ptr(norm_w), eps, qs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+            bt.data_ptr(), positions[b0:].data_ptr(), _lib.ptr(rs), cos.data_ptr(), sin.data_ptr(),
+            bb, k, hq, hkv, d, block_table.stride(0), k_cache.shape[2], int(traditional), int(pdl),
+            _lib.stream_ptr())
+        _lib.check(rc, "rms_qkv_rope")
     return q_out
 
 

@@ -118,3 +118,32 @@ def test_batched_decode_rows_independent(dev):
         e1.bind([0], [int(lg[0].argmax())])
         o1 = e1.generate(6)
         assert out[s].tolist() == o1[0].tolist()
+
+
+def test_decode_engine_ten_rows_in_chunks(dev):
+    """More rows than one mat-vec launch takes (10 > 4): every kernel runs in row chunks inside the
+    same captured step; tokens follow the fp32 forward for each sequence."""
+    cfg = tiny_moe_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant="q4"))
+    oracle = _oracle_from(model)
+    g = torch.Generator().manual_seed(4)
+    lens = [3, 9, 17, 5, 12, 7, 20, 4, 6, 11]
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in lens]
+    cache = model.new_cache(40, max_seqs=12)
+    oc = oracle.new_cache(40, max_seqs=12)
+    last = []
+    for s, p in enumerate(prompts):
+        cache.add_sequence(s)
+        oc.add_sequence(s)
+        lg = model.forward(p.to(dev), cache, [s], last_only=True)
+        oracle.forward(p, oc, [s], last_only=True)
+        last.append(int(lg[0].argmax()))
+    eng = CachedDecode(model, cache, max_batch=12, use_graph=True)
+    eng.bind(list(range(10)), last)
+    toks = eng.generate(2)
+    assert toks.shape == (10, 2)
+    got = eng.logits[:10].float().cpu()
+    for feed in (last, toks[:, 0].tolist()):
+        want = torch.cat([oracle.forward(torch.tensor([feed[s]]), oc, [s], last_only=True) for s in range(10)])
+    rel = (got - want).abs().max().item() / want.abs().max().item()
+    assert rel < 5e-2, rel

@@ -132,7 +132,7 @@ def test_serving_engine_large_batch_uses_tensor_core_decode(dev):
     cfg = _moe_cfg()
     model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant="q4"))
     oracle = _oracle_from(model)
-    eng = ServingEngine(model, num_blocks=64, scheduler_cfg=SchedulerConfig(max_batch_size=8, max_prefill_chunk=64))
+    eng = ServingEngine(model, num_blocks=96, scheduler_cfg=SchedulerConfig(max_batch_size=8, max_prefill_chunk=64))
     assert isinstance(eng._engine, BatchedDecode)
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (12, 30, 7, 21, 16, 9)]
