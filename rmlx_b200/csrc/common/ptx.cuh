@@ -203,6 +203,22 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+// The store counterpart: thread i of the warp writes row (lane base + i), columns [col, col+32).
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+        "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]),
+        "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]),
+        "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 
 // Shared-memory matrix descriptor for a K-major bf16 tile stored as rows of 128 bytes (64 bf16)
 // with the 128-byte swizzle, eight-row groups 1024 bytes apart. `smem_addr` is 1024-byte aligned
@@ -217,6 +233,23 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_kmajor(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2u) << 61;                           // layout: 128-byte swizzle
   return d;
 }
+// Descriptor for an MN-major bf16 operand: rows are steps along K (one row = 64 consecutive
+// elements of the M/N dimension = 128 bytes, 128-byte swizzle), eight-row groups 1024 bytes apart,
+// and the next 64 elements of the M/N dimension start `mn_panel_bytes` further on. This is the
+// shape in which a [keys, head_dim] value tile lands when TMA loads it as 64-column panels.
+// Advancing along K by 8 rows adds 1024 bytes to the start address.
+__device__ __forceinline__ uint64_t umma_desc_sw128_mnmajor(uint32_t smem_addr,
+                                                            uint32_t mn_panel_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);        // start address  [0,14)
+  d |= static_cast<uint64_t>((mn_panel_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset
+  d |= static_cast<uint64_t>(1024u >> 4) << 32;                   // stride byte offset [32,46)
+  d |= static_cast<uint64_t>(1u) << 46;                           // descriptor version (sm_100)
+  d |= static_cast<uint64_t>(2u) << 61;                           // layout: 128-byte swizzle
+  return d;
+}
+// Bit 16 of the instruction descriptor: operand B is MN-major instead of K-major.
+constexpr uint32_t kUmmaBMajorMN = 1u << 16;
 // Instruction descriptor for kind::f16 with bf16 A/B (both K-major), fp32 accumulate.
 __host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int m, int n) {
   return (1u << 4)                               // D format: f32

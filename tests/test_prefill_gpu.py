@@ -10,7 +10,8 @@ from rmlx_b200.config import FeedForwardType, MoeConfig, TransformerConfig
 from rmlx_b200.models.prefill import enable_native_prefill
 from rmlx_b200.models.transformer import TransformerModel
 from rmlx_b200.models.weights import from_state_dict, random_state_dict
-from rmlx_b200.ops.attention import flash_prefill_paged
+from rmlx_b200.ops.attention import flash_prefill_paged, prefill_kernel_choice
+from rmlx_b200.ops.gemm import GemmStatus
 from rmlx_b200.reference import ops as ref
 
 from test_decode_engine_gpu import _oracle_from
@@ -18,9 +19,19 @@ from test_decode_engine_gpu import _oracle_from
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("kernel", ["tc", "mma"])
 @pytest.mark.parametrize("hd", [64, 128])
-@pytest.mark.parametrize("t,pos0,window", [(200, 0, 0), (64, 0, 0), (77, 37, 0), (300, 19, 50), (1, 130, 0)])
-def test_flash_prefill_matches_reference(dev, hd, t, pos0, window):
+@pytest.mark.parametrize("t,pos0,window", [(200, 0, 0), (64, 0, 0), (77, 37, 0), (300, 19, 50), (1, 130, 0),
+                                           (640, 100, 0), (1500, 0, 0)])
+def test_flash_prefill_matches_reference(dev, hd, t, pos0, window, kernel, monkeypatch):
+    """Both kernels against fp32 softmax(QK^T)V: the tcgen05 one covers head_dim 128 without a
+    window (several 128-key steps, partial pages, a tile that starts off the diagonal), the
+    mma.sync one everything else and, forced, the same shapes."""
+    monkeypatch.setenv("RMLX_FLASH_PREFILL", kernel)
+    expect = "tc" if (kernel == "tc" and hd == 128 and window == 0) else "mma"
+    assert prefill_kernel_choice(hd, window) == expect
+    if kernel == "tc" and expect == "mma":
+        pytest.skip("shape not covered by the tcgen05 kernel; the mma.sync case runs it")
     torch.manual_seed(0)
     hq, hkv = 8, 2
     total = pos0 + t
@@ -30,14 +41,38 @@ def test_flash_prefill_matches_reference(dev, hd, t, pos0, window):
     perm = (torch.randperm(nblk) + 1).to(torch.int32)             # pages out of order, block 0 unused
     k = torch.randn(total, hkv, hd, device=dev).to(torch.bfloat16)
     v = torch.randn(total, hkv, hd, device=dev).to(torch.bfloat16)
-    for p in range(total):
-        kc[perm[p // 16], :, p % 16] = k[p]
-        vc[perm[p // 16], :, p % 16] = v[p]
+    tok = torch.arange(total, device=dev)
+    kc[perm.to(dev)[tok // 16].long(), :, tok % 16] = k
+    vc[perm.to(dev)[tok // 16].long(), :, tok % 16] = v
     q = torch.randn(t, hq, hd, device=dev).to(torch.bfloat16)
     got = flash_prefill_paged(q, kc, vc, perm.to(dev), pos0, window=window).float()
+    GemmStatus.check(dev)
     want = ref.sdpa(q.float(), k.float(), v.float(), 1.0 / math.sqrt(hd), pos0, window)
     assert torch.isfinite(got).all()
     assert (got - want).abs().max().item() < 2e-2
+
+
+def test_flash_prefill_tc_growing_scores(dev, monkeypatch):
+    """Keys whose scores grow from one 128-key step to the next force the tcgen05 kernel to move its
+    reference maximum and rescale the output accumulator in tensor memory several times per row."""
+    monkeypatch.setenv("RMLX_FLASH_PREFILL", "tc")
+    torch.manual_seed(1)
+    hq, hkv, hd, t = 4, 2, 128, 900
+    nblk = (t + 15) // 16
+    kc = torch.zeros(nblk + 1, hkv, 16, hd, device=dev, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    perm = (torch.randperm(nblk) + 1).to(torch.int32).to(dev)
+    tok = torch.arange(t, device=dev)
+    k = (torch.randn(t, hkv, hd, device=dev) * (1 + 3 * (tok // 128))[:, None, None]).to(torch.bfloat16)
+    v = torch.randn(t, hkv, hd, device=dev).to(torch.bfloat16)
+    kc[perm[tok // 16].long(), :, tok % 16] = k
+    vc[perm[tok // 16].long(), :, tok % 16] = v
+    q = torch.randn(t, hq, hd, device=dev).to(torch.bfloat16)
+    got = flash_prefill_paged(q, kc, vc, perm, 0).float()
+    GemmStatus.check(dev)
+    want = ref.sdpa(q.float(), k.float(), v.float(), 1.0 / math.sqrt(hd), 0, 0)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() < 3e-2
 
 
 def _moe_cfg():
