@@ -52,6 +52,32 @@ def test_flash_prefill_matches_reference(dev, hd, t, pos0, window, kernel, monke
     assert (got - want).abs().max().item() < 2e-2
 
 
+@pytest.mark.parametrize("t,pos0", [(300, 19), (640, 100), (140, 10), (1500, 0), (100, 0)])
+def test_flash_prefill_tc_two_query_tiles_per_cta(dev, t, pos0, monkeypatch):
+    """The two-lane form of the tcgen05 kernel (256 query rows per CTA, K/V tiles shared by the
+    lanes): lanes with different step counts, an idle second lane, pages only the second lane sees."""
+    monkeypatch.setenv("RMLX_FLASH_PREFILL", "tc")
+    monkeypatch.setenv("RMLX_FLASH_PREFILL_LANES", "2")
+    torch.manual_seed(2)
+    hq, hkv, hd = 8, 2, 128
+    total = pos0 + t
+    nblk = (total + 15) // 16
+    kc = torch.zeros(nblk + 2, hkv, 16, hd, device=dev, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    perm = (torch.randperm(nblk) + 1).to(torch.int32).to(dev)
+    tok = torch.arange(total, device=dev)
+    k = torch.randn(total, hkv, hd, device=dev).to(torch.bfloat16)
+    v = torch.randn(total, hkv, hd, device=dev).to(torch.bfloat16)
+    kc[perm[tok // 16].long(), :, tok % 16] = k
+    vc[perm[tok // 16].long(), :, tok % 16] = v
+    q = torch.randn(t, hq, hd, device=dev).to(torch.bfloat16)
+    got = flash_prefill_paged(q, kc, vc, perm, pos0).float()
+    GemmStatus.check(dev)
+    want = ref.sdpa(q.float(), k.float(), v.float(), 1.0 / math.sqrt(hd), pos0, 0)
+    assert torch.isfinite(got).all()
+    assert (got - want).abs().max().item() < 2e-2
+
+
 def test_flash_prefill_tc_growing_scores(dev, monkeypatch):
     """Keys whose scores grow from one 128-key step to the next force the tcgen05 kernel to move its
     reference maximum and rescale the output accumulator in tensor memory several times per row."""
