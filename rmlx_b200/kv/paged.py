@@ -111,6 +111,30 @@ class BlockManager:
         for b in self.tables[child]:
             self.ref[b] += 1
 
+    def adopt(self, seq_id: int, blocks: List[int], num_tokens: int) -> None:
+        """An empty sequence starts from ``blocks`` that already hold the KV of its first
+        ``num_tokens`` tokens (a cached prompt prefix): shared, copy-on-write like ``fork``."""
+        if self.tables.get(seq_id) or self.lengths.get(seq_id, 0):
+            raise ValueError(f"sequence {seq_id} is not empty")
+        if num_tokens > len(blocks) * self.block_size:
+            raise ValueError("more tokens than the blocks hold")
+        for b in blocks:
+            if self.ref[b] <= 0:
+                raise ValueError(f"block {b} is not live")
+            self.ref[b] += 1
+        self.tables[seq_id] = list(blocks)
+        self.lengths[seq_id] = num_tokens
+
+    def retain(self, block: int) -> None:
+        """One more owner of a live block (a prefix cache keeping pages past their sequence)."""
+        if self.ref[block] <= 0:
+            raise ValueError(f"block {block} is not live")
+        self.ref[block] += 1
+
+    def release(self, block: int) -> None:
+        """Give up an ownership taken with ``retain``."""
+        self._drop(block)
+
     def trim(self, seq_id: int, num_tokens: int) -> None:
         """Drop the last ``num_tokens`` tokens (speculative rollback)."""
         cur = self.lengths[seq_id]
@@ -168,6 +192,11 @@ class PagedKvCache:
         self.slot_of[child] = slot
         self._sync_slot(child)
         return slot
+
+    def adopt_prefix(self, seq_id: int, blocks: List[int], num_tokens: int) -> None:
+        """Start an (empty, already added) sequence from cached prefix pages."""
+        self.manager.adopt(seq_id, blocks, num_tokens)
+        self._sync_slot(seq_id)
 
     def seq_len(self, seq_id: int) -> int:
         return self.manager.seq_len(seq_id)

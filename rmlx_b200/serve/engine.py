@@ -26,7 +26,7 @@ class ServingEngine:
         self.model = model
         scfg = scheduler_cfg or SchedulerConfig()
         self.cache = model.new_cache(num_blocks, max_seqs=scfg.max_batch_size)
-        self.sched = Scheduler(scfg, manage_blocks=False, on_admit=self.cache.add_sequence,
+        self.sched = Scheduler(scfg, manage_blocks=False, on_admit=self._on_admit,
                                on_evict=self._on_evict)
         self.sampler = Sampler(sampler_cfg)
         self.greedy = self.sampler.cfg.temperature == 0.0 and self.sampler.cfg.repetition_penalty == 1.0
@@ -35,6 +35,8 @@ class ServingEngine:
         self._ids = itertools.count()
         self._finished: Dict[int, int] = {}
         self.prefix = PrefixCache(self.cache.block_size) if use_prefix_cache else None
+        self._prompts: Dict[int, List[int]] = {}
+        self.prefill_tokens = 0               # prompt tokens actually run (cached prefixes excluded)
         self._engine = None
         self._bound: List[int] = []
         if model.device.type == "cuda":
@@ -53,19 +55,60 @@ class ServingEngine:
                 except ImportError:
                     self._engine = None          # shapes outside the kernels: library-kernel forward
 
+    def _on_admit(self, seq_id: int) -> int:
+        """New sequence; with a prefix cache, start it from the cached pages of the longest
+        block-aligned prefix of its prompt. Returns how many prompt tokens that covers."""
+        self.cache.add_sequence(seq_id)
+        if self.prefix is None:
+            return 0
+        prompt = self._prompts[seq_id]
+        bs = self.cache.block_size
+        _, blocks = self.prefix.lookup(prompt)
+        blocks = blocks[:(len(prompt) - 1) // bs]        # the last prompt token always runs
+        if blocks:
+            self.cache.adopt_prefix(seq_id, blocks, len(blocks) * bs)
+        return len(blocks) * bs
+
     def _on_evict(self, seq_id: int) -> None:
+        prompt = self._prompts.pop(seq_id, None)
+        if self.prefix is not None and prompt is not None:
+            # the finished sequence's full prompt pages stay behind for later requests; the cache
+            # holds its own reference to each page it newly records
+            table = self.cache.manager.block_table(seq_id)
+            done = min(len(prompt), self.cache.seq_len(seq_id))
+            for b in self.prefix.insert_blocks(prompt[:done], table):
+                self.cache.manager.retain(b)
+            for b in self.prefix.take_evicted():
+                self.cache.manager.release(b)
         self.cache.free_sequence(seq_id)
         self._bound = []
+
+    def reclaim(self, num_blocks: int) -> int:
+        """Drop up to ``num_blocks`` least-recently-used prefix pages back to the free pool."""
+        if self.prefix is None:
+            return 0
+        victims = self.prefix.evict(num_blocks)
+        for b in victims:
+            self.cache.manager.release(b)
+        return len(victims)
 
     # ------------------------------------------------------------------ public API
     def submit(self, prompt_tokens: List[int], max_output_len: int) -> int:
         sid = next(self._ids)
+        self._prompts[sid] = [int(t) for t in prompt_tokens]
         self.sched.add_request(GenerationRequest(sid, list(prompt_tokens), max_output_len))
         self.outputs[sid] = []
         return sid
 
     def step(self) -> Dict[int, int]:
         """One scheduler step. Returns the tokens produced in it (seq_id -> token)."""
+        if self.prefix is not None and self.sched.waiting:
+            # cached prefix pages give way to a request that would otherwise wait for blocks
+            req = self.sched.waiting[0]
+            first = min(len(req.prompt_tokens), self.sched.cfg.max_prefill_chunk)
+            short = -(-first // self.cache.block_size) - self.cache.manager.num_free_blocks()
+            if short > 0:
+                self.reclaim(short)
         plan = self.sched.schedule(self.cache.manager, self._finished)
         self._finished = {}
         produced: Dict[int, int] = {}
@@ -74,6 +117,7 @@ class ServingEngine:
             lo, hi = plan.prefill_chunk_range
             chunk = torch.tensor(self.sched.prompt_chunk(meta.seq_id, (lo, hi)), device=dev)
             logits = self.model.prefill(chunk, self.cache, meta.seq_id)
+            self.prefill_tokens += hi - lo
             if hi >= meta.prompt_len:      # prompt complete: its last logits give the first token
                 tok = self.sampler.sample_token(logits[0].float().cpu(), self.outputs[meta.seq_id])
                 produced[meta.seq_id] = tok

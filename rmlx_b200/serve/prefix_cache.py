@@ -33,6 +33,7 @@ class PrefixCache:
         self._num_blocks = 0
         self.hits = 0
         self.misses = 0
+        self._pending_evicted: List[int] = []
 
     def __len__(self) -> int:
         return self._num_blocks
@@ -46,7 +47,12 @@ class PrefixCache:
         """Record that ``blocks[i]`` holds the KV of the i-th full block of ``tokens``. Returns the
         number of blocks newly recorded. Evicts old leaves when over ``max_blocks``; the caller
         releases the returned victims through ``take_evicted``."""
-        node, new = self.root, 0
+        return len(self.insert_blocks(tokens, blocks))
+
+    def insert_blocks(self, tokens: Sequence[int], blocks: Sequence[int]) -> List[int]:
+        """``insert`` that returns the block ids it newly recorded (the ones the caller must keep
+        alive for the cache; chunks already present keep the block they had)."""
+        node, new = self.root, []
         now = next(self._clock)
         for chunk, blk in zip(self._chunks(tokens), blocks):
             nxt = node.children.get(chunk)
@@ -54,12 +60,11 @@ class PrefixCache:
                 nxt = _Node(node, chunk, int(blk))
                 node.children[chunk] = nxt
                 self._num_blocks += 1
-                new += 1
+                new.append(int(blk))
             nxt.last_used = now
             node = nxt
         if self.max_blocks and self._num_blocks > self.max_blocks:
-            self._pending_evicted = getattr(self, "_pending_evicted", []) + \
-                self.evict(self._num_blocks - self.max_blocks)
+            self._pending_evicted += self.evict(self._num_blocks - self.max_blocks)
         return new
 
     def lookup(self, tokens: Sequence[int]) -> Tuple[int, List[int]]:
@@ -99,8 +104,7 @@ class PrefixCache:
         return victims
 
     def take_evicted(self) -> List[int]:
-        v = getattr(self, "_pending_evicted", [])
-        self._pending_evicted = []
+        v, self._pending_evicted = self._pending_evicted, []
         return v
 
     def clear(self) -> List[int]:

@@ -61,7 +61,8 @@ class Scheduler:
                  on_evict=None):
         """``manage_blocks=False``: only check capacity; the caller's forward pass reserves and
         commits KV slots itself. ``on_admit`` / ``on_evict`` replace the default
-        ``add_sequence`` / ``free_sequence`` calls on the block manager."""
+        ``add_sequence`` / ``free_sequence`` calls on the block manager; ``on_admit`` may return the
+        number of leading prompt tokens whose KV it found cached (prefill starts after them)."""
         self.cfg = config.validate()
         self.waiting: Deque[GenerationRequest] = deque()
         self.active: Dict[int, _Active] = {}
@@ -104,11 +105,15 @@ class Scheduler:
             if need > bm.num_free_blocks():
                 break
             self.waiting.popleft()
+            cached = 0
             if self.on_admit is not None:
-                self.on_admit(req.seq_id)
+                cached = self.on_admit(req.seq_id) or 0     # prompt tokens whose KV is already cached
             else:
                 bm.add_sequence(req.seq_id)
-            self.active[req.seq_id] = _Active(list(req.prompt_tokens), req.max_output_len)
+            a = _Active(list(req.prompt_tokens), req.max_output_len)
+            # the last prompt token always runs: its logits give the first generated token
+            a.prefill_progress = max(0, min(int(cached), len(a.prompt) - 1))
+            self.active[req.seq_id] = a
         # 3. one prefill chunk (oldest unfinished prompt first), everyone else decodes
         prefilling = [sid for sid, a in self.active.items() if not a.prefilled]
         if prefilling:

@@ -105,3 +105,72 @@ def test_serving_engine_matches_single_sequence_generation():
         want = model.generate_greedy(torch.tensor(p), 4)
         assert outs[sid][:4] == want, (sid, outs[sid], want)
     assert eng.cache.manager.num_free_blocks() == 23   # everything returned (block 0 is reserved)
+
+
+def test_block_manager_adopt_retain_release():
+    bm = BlockManager(8, 4)
+    bm.reserve(1, 8); bm.commit(1, 8)
+    shared = list(bm.block_table(1))
+    bm.retain(shared[0])                               # a cache keeps the first page
+    bm.add_sequence(2)
+    bm.adopt(2, shared, 8)
+    assert bm.seq_len(2) == 8 and bm.block_table(2) == shared
+    bm.free_sequence(1)
+    assert bm.num_free_blocks() == 6                   # still owned by sequence 2 (and the cache)
+    bm.reserve(2, 1); bm.commit(2, 1)                  # full shared pages: a new page, no copy
+    assert len(bm.block_table(2)) == 3
+    bm.free_sequence(2)
+    assert bm.num_free_blocks() == 7                   # the retained page survives its sequences
+    bm.release(shared[0])
+    assert bm.num_free_blocks() == 8
+    try:
+        bm.retain(shared[0])
+        assert False
+    except ValueError:
+        pass
+
+
+def test_serving_engine_prefix_cache_reuses_prompt_pages():
+    """Requests that share a prompt prefix skip its prefill, produce the same tokens as without the
+    cache, and cached pages are given back when blocks run short or on request."""
+    cfg = tiny_dense_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    g = torch.Generator().manual_seed(5)
+    common = torch.randint(0, cfg.vocab_size, (40,), generator=g).tolist()
+    prompts = [common + torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (3, 7, 0)]
+    scfg = SchedulerConfig(max_batch_size=1, max_prefill_chunk=16)      # one at a time: later ones hit
+
+    plain = ServingEngine(model, num_blocks=24, scheduler_cfg=scfg)
+    ids = [plain.submit(p, 3) for p in prompts]
+    want = plain.run_until_done()
+
+    eng = ServingEngine(model, num_blocks=24, scheduler_cfg=scfg, use_prefix_cache=True)
+    ids2 = [eng.submit(p, 3) for p in prompts]
+    got = eng.run_until_done()
+    for a, b in zip(ids, ids2):
+        assert got[b] == want[a]
+    # 40 common tokens = two full 16-token pages shared by the second and third request; the third
+    # prompt is exactly the common part, so its last page (tokens 32..39) is partial and runs again
+    assert eng.prefix.hits == 2
+    assert eng.prefill_tokens == plain.prefill_tokens - 2 * 32
+    held = len(eng.prefix)
+    assert held >= 2 and eng.cache.manager.num_free_blocks() == 23 - held
+    assert eng.reclaim(100) == held
+    assert eng.cache.manager.num_free_blocks() == 23
+
+
+def test_serving_engine_prefix_cache_gives_way_under_pressure():
+    cfg = tiny_dense_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    g = torch.Generator().manual_seed(6)
+    scfg = SchedulerConfig(max_batch_size=1, max_prefill_chunk=64)
+    eng = ServingEngine(model, num_blocks=6, scheduler_cfg=scfg, use_prefix_cache=True)   # 5 usable pages
+    first = torch.randint(0, cfg.vocab_size, (50,), generator=g).tolist()
+    second = torch.randint(0, cfg.vocab_size, (60,), generator=g).tolist()
+    a = eng.submit(first, 2)
+    eng.run_until_done()
+    assert len(eng.prefix) == 3                         # 48 of the 50 prompt tokens stay cached
+    b = eng.submit(second, 2)                           # needs 4 pages at once: 2 free + cached ones
+    outs = eng.run_until_done()
+    assert outs[b] == model.generate_greedy(torch.tensor(second), 2)
+    assert len(outs[a]) == 2
