@@ -211,6 +211,13 @@ class CachedDecode:
             self.cache.commit(s, 1)
         return self.next_tokens
 
+    def set_next_tokens(self, tokens: Sequence[int]) -> None:
+        """Replace the tokens the last step fed back (its arg-max) with ones chosen by the caller,
+        e.g. sampled from ``logits``; positions and lengths were already advanced by the step."""
+        n = len(self.seq_ids)
+        assert len(tokens) == n
+        self.tokens[:n] = torch.tensor([int(t) for t in tokens], dtype=torch.int32)
+
     @property
     def launches_per_step(self) -> int:
         return self._launches_per_step

@@ -261,6 +261,14 @@ class BatchedDecode:
             self.cache.commit(s, 1)
         return self.next_tokens
 
+    def set_next_tokens(self, tokens: Sequence[int]) -> None:
+        """Replace the tokens the last step fed back (its arg-max) with ones chosen by the caller,
+        e.g. sampled from ``logits``; positions and lengths were already advanced by the step."""
+        n = len(self.seq_ids)
+        assert len(tokens) == n
+        self.tokens[:n] = torch.tensor([int(t) for t in tokens], dtype=torch.int32)
+        self._saved_tokens = self.tokens.clone()
+
     def _rewind(self) -> None:
         """Undo the state advance of a warm-up step (the KV slot it wrote is rewritten by the real one)."""
         n = len(self.seq_ids)

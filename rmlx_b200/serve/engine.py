@@ -143,13 +143,21 @@ class ServingEngine:
     # ------------------------------------------------------------------ decode back-ends
     def _decode(self, ids: List[int]) -> List[int]:
         dev = self.model.device
-        if self._engine is not None and self.greedy:
+        # the device engines compute full-vocabulary logits unless the LM head is sharded
+        on_device = self._engine is not None and (self.greedy or self.model.layout.world == 1)
+        if on_device:
             if ids != self._bound:
                 self._engine.bind(ids, [self.last_token[s] for s in ids])
                 self._bound = list(ids)
             self._engine.reserve(1)
             nxt = self._engine.step()
-            return [int(t) for t in nxt[:len(ids)].cpu()]
+            if self.greedy:
+                return [int(t) for t in nxt[:len(ids)].cpu()]
+            # sampling: the step fed its arg-max back; replace it with the sampled tokens
+            logits = self._engine.logits[:len(ids)].float().cpu()
+            toks = [self.sampler.sample_token(logits[i], self.outputs[s]) for i, s in enumerate(ids)]
+            self._engine.set_next_tokens(toks)
+            return toks
         toks = torch.tensor([self.last_token[s] for s in ids], device=dev)
         logits = self.model.forward(toks, self.cache, ids, last_only=True)
         return [self.sampler.sample_token(logits[i].float().cpu(), self.outputs[s])

@@ -203,3 +203,26 @@ def test_serving_engine_large_batch_uses_tensor_core_decode(dev):
         assert len(out[sid]) == 4
         want = oracle.generate_greedy(torch.tensor(p), 1)
         assert out[sid][0] == want[0]
+
+
+@pytest.mark.parametrize("max_batch", [2, 8])
+def test_serving_engine_samples_through_the_device_engines(dev, max_batch):
+    """A sampler that is not greedy (temperature > 0) but can only pick the most likely token
+    (top_k = 1) must reproduce the greedy run: the step's logits are read back, the sampled token
+    replaces the arg-max the step fed to itself. 2 rows: mat-vec engine; 8 rows: tensor-core engine."""
+    from rmlx_b200.config import SamplerConfig, SchedulerConfig
+    from rmlx_b200.serve.engine import ServingEngine
+    cfg = _moe_cfg()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant="q4"))
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (12, 30, 7)]
+    outs = []
+    for scfg in (SamplerConfig(), SamplerConfig(temperature=0.7, top_k=1, seed=0)):
+        eng = ServingEngine(model, num_blocks=64, sampler_cfg=scfg,
+                            scheduler_cfg=SchedulerConfig(max_batch_size=max_batch, max_prefill_chunk=64))
+        assert eng._engine is not None and eng.greedy == (scfg.temperature == 0.0)
+        ids = [eng.submit(p, 5) for p in prompts]
+        res = eng.run_until_done()
+        outs.append([res[i] for i in ids])
+        GemmStatus.check(dev)
+    assert outs[0] == outs[1]
