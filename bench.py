@@ -125,7 +125,6 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    from rmlx_b200 import _lib
     from rmlx_b200.config import moe_a22b_config
     from rmlx_b200.models.decode_engine import CachedDecode
     from rmlx_b200.models.transformer import TransformerModel

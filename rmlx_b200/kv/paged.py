@@ -11,7 +11,6 @@ tensor so a captured decode graph sees growth without re-capture.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
 import torch

@@ -22,7 +22,7 @@ from __future__ import annotations
 
 import os
 
-from typing import Callable, List, Optional, Sequence
+from typing import List, Optional, Sequence
 
 import torch
 

@@ -7,13 +7,13 @@ routed experts run through ``MoeLayer`` and therefore through this package's gro
 CUDA."""
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import List, Optional
 
 import torch
 
 from ..config import MlaConfig, MoeConfig
-from ..nn.mla import MlaAttention, MlaKvCache, MlaWeights, random_mla_weights
+from ..nn.mla import MlaAttention, MlaKvCache, random_mla_weights
 from ..nn.moe import ExpertGroup, MoeLayer, MoeStrategy
 from ..ops.weights import LinearWeight
 from ..reference import ops as ref

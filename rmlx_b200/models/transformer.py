@@ -20,10 +20,9 @@ from typing import Callable, List, Optional, Sequence
 
 import torch
 
-from ..config import TransformerConfig
 from ..kv.paged import PagedKvCache
 from ..reference import ops as ref
-from .weights import LayerWeights, ModelWeights, ParallelLayout, is_moe_layer
+from .weights import LayerWeights, ModelWeights
 
 
 class TransformerModel:

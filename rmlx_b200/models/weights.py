@@ -12,7 +12,7 @@ crates/rmlx-distributed/src/moe_exchange.rs:578-581). The LM head is split by vo
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional
 
 import torch

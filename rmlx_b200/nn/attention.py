@@ -16,7 +16,7 @@ Sliding-window masks: crates/rmlx-nn/src/sliding_window.rs:25-160.
 from __future__ import annotations
 
 import math
-from typing import List, Optional, Sequence, Tuple
+from typing import List, Sequence
 
 import torch
 

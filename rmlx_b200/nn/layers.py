@@ -8,12 +8,11 @@ GEMM otherwise; Q4 weights go through the Q4 kernels); everywhere else it is pla
 """
 from __future__ import annotations
 
-import math
 from typing import Callable, Dict, Optional
 
 import torch
 
-from ..ops.weights import GROUP, LinearWeight, W_BF16, W_Q4
+from ..ops.weights import LinearWeight, W_BF16
 from ..reference import ops as ref
 
 GEMV_MAX_ROWS = 8

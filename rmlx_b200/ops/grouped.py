@@ -11,7 +11,6 @@ from typing import Optional
 import torch
 
 from .. import _lib
-from . import decode as D
 from .quantized import xgemm
 from .weights import LinearWeight, W_Q4
 

@@ -12,7 +12,7 @@ import torch
 
 from .. import _lib
 from .gemm import GemmStatus, gemm_bf16
-from .weights import LinearWeight, W_BF16, W_Q4
+from .weights import LinearWeight, W_Q4
 
 _lib.register_cuda_sigs({
     "rmlx_qgemm_supported": ("i", "i"),

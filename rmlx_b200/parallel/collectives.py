@@ -8,7 +8,6 @@ Counterpart of the reference's ``Group`` algorithms executed on the CPU over RDM
 """
 from __future__ import annotations
 
-import ctypes
 from typing import Optional
 
 import torch

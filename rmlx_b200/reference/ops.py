@@ -12,7 +12,6 @@ renormalised to sum 1 (crates/rmlx-core/src/ops/topk_route.rs:242-343).
 """
 from __future__ import annotations
 
-import math
 from typing import Optional, Tuple
 
 import torch

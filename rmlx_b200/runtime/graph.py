@@ -14,8 +14,8 @@ used to bisect suspected races (the reference's ``tracked_hazards`` feature)."""
 from __future__ import annotations
 
 from collections import OrderedDict
-from dataclasses import dataclass, field
-from typing import Callable, Dict, Hashable, List, Optional, Tuple
+from dataclasses import dataclass
+from typing import Callable, Hashable, List, Optional, Tuple
 
 import torch
 

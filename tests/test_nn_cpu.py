@@ -14,7 +14,6 @@ from rmlx_b200.nn.lora import LoraConfig, LoraLayer, LoraModel, LoraTrainer, num
 from rmlx_b200.nn.mla import MlaAttention, MlaKvCache, random_mla_weights
 from rmlx_b200.nn.parallel import shard_column, shard_column_segments, shard_row
 from rmlx_b200.ops.weights import LinearWeight
-from rmlx_b200.reference import ops as ref
 
 
 def test_linear_and_quantised_imports():

@@ -5,7 +5,7 @@ import torch
 
 from rmlx_b200.ops import decode as D
 from rmlx_b200.ops.gemm import GemmStatus
-from rmlx_b200.ops.grouped import grouped_expert_ffn, moe_prefill_ffn
+from rmlx_b200.ops.grouped import moe_prefill_ffn
 from rmlx_b200.ops.quantized import qmm, xgemm
 from rmlx_b200.ops.weights import LinearWeight
 from rmlx_b200.reference import ops as ref
