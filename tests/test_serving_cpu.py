@@ -174,3 +174,43 @@ def test_serving_engine_prefix_cache_gives_way_under_pressure():
     outs = eng.run_until_done()
     assert outs[b] == model.generate_greedy(torch.tensor(second), 2)
     assert len(outs[a]) == 2
+
+
+def test_speculative_decoder_reproduces_target_greedy():
+    """Whatever the draft proposes, greedy draft-and-verify yields the target's greedy continuation:
+    a perfect draft (the target itself) is accepted every time, an unrelated one almost never."""
+    from rmlx_b200.serve.speculative import SpeculativeDecoder
+    cfg = tiny_dense_config()
+    target = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    other = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 7), dtype=torch.float32))
+    g = torch.Generator().manual_seed(3)
+    prompt = torch.randint(0, cfg.vocab_size, (21,), generator=g).tolist()
+    want = target.generate_greedy(torch.tensor(prompt), 14)
+
+    same = SpeculativeDecoder(target, target, k=4)
+    assert same.generate(prompt, 14) == want
+    assert same.stats.acceptance_rate == 1.0 and same.stats.rounds == 3      # 1 + 3 * (4 + 1) >= 14
+    assert same.stats.tokens_per_round == 5.0
+
+    for k in (1, 3, 5):
+        spec = SpeculativeDecoder(target, other, k=k)
+        assert spec.generate(prompt, 14) == want, k
+        assert spec.stats.proposed == spec.stats.rounds * k
+        assert spec.stats.acceptance_rate < 1.0
+
+
+def test_speculative_decoder_sampling_runs_and_stops_at_eos():
+    from rmlx_b200.serve.speculative import SpeculativeDecoder
+    cfg = tiny_dense_config()
+    target = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    draft = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 7), dtype=torch.float32))
+    prompt = list(range(1, 12))
+    spec = SpeculativeDecoder(target, draft, k=3, sampler_cfg=SamplerConfig(temperature=0.8, top_k=20, seed=1))
+    out = spec.generate(prompt, 10)
+    assert len(out) == 10 and all(0 <= t < cfg.vocab_size for t in out)
+    # greedy with an end-of-sequence id taken from the known continuation: generation stops on it
+    want = target.generate_greedy(torch.tensor(prompt), 8)
+    eos = want[4]
+    cut = want[:want.index(eos) + 1]
+    spec = SpeculativeDecoder(target, target, k=3, eos_token_id=eos)
+    assert spec.generate(prompt, 8) == cut
