@@ -53,6 +53,15 @@ class BlockManager:
     def block_table(self, seq_id: int) -> List[int]:
         return self.tables[seq_id]
 
+    def has_sequence(self, seq_id: int) -> bool:
+        return seq_id in self.tables
+
+    def num_blocks_of(self, seq_id: int) -> int:
+        return len(self.tables.get(seq_id, ()))
+
+    def ref_count(self, block: int) -> int:
+        return self.ref[block]
+
     def seq_len(self, seq_id: int) -> int:
         return self.lengths.get(seq_id, 0)
 
@@ -150,13 +159,22 @@ class BlockManager:
         self.lengths.pop(seq_id, None)
 
 
+def make_block_manager(num_blocks: int, block_size: int = PAGE, reserved: int = 0):
+    """The block manager of the native host library when it is enabled (the default), else the
+    Python one above; both have the same interface and behaviour."""
+    from ..serve import native
+    if native.enabled():
+        return native.NativeBlockManager(num_blocks, block_size, reserved)
+    return BlockManager(num_blocks, block_size, reserved)
+
+
 class PagedKvCache:
     """Device K/V pools for every layer plus the manager and a device mirror of block tables."""
 
     def __init__(self, num_blocks: int, num_layers: int, kv_heads: int, head_dim: int,
                  dtype=torch.bfloat16, device="cpu", max_seqs: int = 64,
                  max_blocks_per_seq: int = 512, block_size: int = PAGE):
-        self.manager = BlockManager(num_blocks, block_size, reserved=1)
+        self.manager = make_block_manager(num_blocks, block_size, reserved=1)
         self.num_layers, self.kv_heads, self.head_dim = num_layers, kv_heads, head_dim
         self.block_size = block_size
         self.k = [torch.zeros(num_blocks, kv_heads, block_size, head_dim, dtype=dtype, device=device)
@@ -212,7 +230,7 @@ class PagedKvCache:
     def reserve(self, seq_id: int, new_tokens: int) -> None:
         """Ensure blocks exist for ``new_tokens`` more tokens (doing any copy-on-write) and push
         the table row to the device."""
-        before = len(self.manager.tables.get(seq_id, ()))
+        before = self.manager.num_blocks_of(seq_id)
         copies = self.manager.reserve(seq_id, new_tokens)
         for src, dst in copies:
             for l in range(self.num_layers):

@@ -26,7 +26,12 @@ class ServingEngine:
         self.model = model
         scfg = scheduler_cfg or SchedulerConfig()
         self.cache = model.new_cache(num_blocks, max_seqs=scfg.max_batch_size)
-        self.sched = Scheduler(scfg, manage_blocks=False, on_admit=self._on_admit,
+        # scheduler, block manager and prefix cache come from the native host library unless it
+        # is switched off (the cache above made the same choice for its block manager)
+        from . import native
+        self.native = native.enabled()
+        sched_cls = native.NativeScheduler if self.native else Scheduler
+        self.sched = sched_cls(scfg, manage_blocks=False, on_admit=self._on_admit,
                                on_evict=self._on_evict)
         self.sampler = Sampler(sampler_cfg)
         self.greedy = self.sampler.cfg.temperature == 0.0 and self.sampler.cfg.repetition_penalty == 1.0
@@ -34,7 +39,8 @@ class ServingEngine:
         self.last_token: Dict[int, int] = {}
         self._ids = itertools.count()
         self._finished: Dict[int, int] = {}
-        self.prefix = PrefixCache(self.cache.block_size) if use_prefix_cache else None
+        prefix_cls = native.NativePrefixCache if self.native else PrefixCache
+        self.prefix = prefix_cls(self.cache.block_size) if use_prefix_cache else None
         self._prompts: Dict[int, List[int]] = {}
         self.prefill_tokens = 0               # prompt tokens actually run (cached prefixes excluded)
         self._engine = None
@@ -102,10 +108,10 @@ class ServingEngine:
 
     def step(self) -> Dict[int, int]:
         """One scheduler step. Returns the tokens produced in it (seq_id -> token)."""
-        if self.prefix is not None and self.sched.waiting:
+        waiting_len = self.sched.first_waiting_prompt_len() if self.prefix is not None else None
+        if waiting_len is not None:
             # cached prefix pages give way to a request that would otherwise wait for blocks
-            req = self.sched.waiting[0]
-            first = min(len(req.prompt_tokens), self.sched.cfg.max_prefill_chunk)
+            first = min(waiting_len, self.sched.cfg.max_prefill_chunk)
             short = -(-first // self.cache.block_size) - self.cache.manager.num_free_blocks()
             if short > 0:
                 self.reclaim(short)

@@ -1,0 +1,339 @@
+"""The serving core in the native host library (csrc/host/serving.cpp): block manager, prefix cache
+and continuous-batching scheduler behind the interfaces of their Python namesakes
+(``kv.paged.BlockManager``, ``serve.prefix_cache.PrefixCache``, ``serve.scheduler.Scheduler``), which
+remain as the behavioural oracle. The reference implements the three in Rust
+(crates/rmlx-nn/src/paged_kv_cache.rs:36-631, prefix_cache.rs:27-330, scheduler.rs:19-352).
+
+``available()`` is False only when the host library cannot be built or loaded; ``RMLX_NATIVE_SERVING=0``
+makes the serving engine and the paged cache use the Python classes instead.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from collections import deque
+from ctypes import POINTER, c_int, c_int64, c_void_p
+from typing import Deque, Dict, List, Optional, Sequence, Tuple
+
+from .. import _lib
+from ..config import SchedulerConfig
+from ..kv.paged import OutOfBlocks
+from .scheduler import GenerationRequest, SchedulerOutput, SeqMeta
+
+_IP = POINTER(c_int)
+_LP = POINTER(c_int64)
+_bound = False
+
+
+def _host():
+    global _bound
+    lib = _lib.host()
+    if not _bound:
+        sig = {
+            "rmlx_bm_create": (c_void_p, [c_int, c_int, c_int]),
+            "rmlx_bm_destroy": (None, [c_void_p]),
+            "rmlx_bm_num_free": (c_int, [c_void_p]),
+            "rmlx_bm_has": (c_int, [c_void_p, c_int64]),
+            "rmlx_bm_seq_len": (c_int, [c_void_p, c_int64]),
+            "rmlx_bm_blocks_needed": (c_int, [c_void_p, c_int64, c_int]),
+            "rmlx_bm_add_sequence": (c_int, [c_void_p, c_int64]),
+            "rmlx_bm_reserve": (c_int, [c_void_p, c_int64, c_int, _IP, _IP, _IP]),
+            "rmlx_bm_commit": (c_int, [c_void_p, c_int64, c_int]),
+            "rmlx_bm_fork": (c_int, [c_void_p, c_int64, c_int64]),
+            "rmlx_bm_adopt": (c_int, [c_void_p, c_int64, _IP, c_int, c_int]),
+            "rmlx_bm_retain": (c_int, [c_void_p, c_int]),
+            "rmlx_bm_release": (c_int, [c_void_p, c_int]),
+            "rmlx_bm_trim": (c_int, [c_void_p, c_int64, c_int]),
+            "rmlx_bm_free_sequence": (c_int, [c_void_p, c_int64]),
+            "rmlx_bm_ref_count": (c_int, [c_void_p, c_int]),
+            "rmlx_bm_table": (c_int, [c_void_p, c_int64, _IP, c_int]),
+            "rmlx_pc_create": (c_void_p, [c_int, c_int]),
+            "rmlx_pc_destroy": (None, [c_void_p]),
+            "rmlx_pc_len": (c_int, [c_void_p]),
+            "rmlx_pc_hits": (c_int64, [c_void_p]),
+            "rmlx_pc_misses": (c_int64, [c_void_p]),
+            "rmlx_pc_insert": (c_int, [c_void_p, _IP, c_int, _IP, c_int, _IP, c_int]),
+            "rmlx_pc_lookup": (c_int, [c_void_p, _IP, c_int, _IP, c_int]),
+            "rmlx_pc_evict": (c_int, [c_void_p, c_int, _IP, c_int]),
+            "rmlx_pc_take_evicted": (c_int, [c_void_p, _IP, c_int]),
+            "rmlx_sched_create": (c_void_p, [c_int, c_int64, c_int, c_int]),
+            "rmlx_sched_destroy": (None, [c_void_p]),
+            "rmlx_sched_add_request": (c_int, [c_void_p, c_int64, _IP, c_int, c_int]),
+            "rmlx_sched_num_waiting": (c_int, [c_void_p]),
+            "rmlx_sched_num_active": (c_int, [c_void_p]),
+            "rmlx_sched_finish": (c_int, [c_void_p, c_int64, c_int64]),
+            "rmlx_sched_admit_next": (c_int64, [c_void_p, c_void_p]),
+            "rmlx_sched_set_cached": (c_int, [c_void_p, c_int64, c_int]),
+            "rmlx_sched_plan": (c_int, [c_void_p, c_void_p, _LP, _LP, c_int]),
+            "rmlx_sched_update": (c_int, [c_void_p, c_void_p, c_int64]),
+            "rmlx_sched_prompt": (c_int, [c_void_p, c_int64, c_int, c_int, _IP]),
+            "rmlx_sched_info": (c_int, [c_void_p, c_int64, _IP]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _bound = True
+    return lib
+
+
+def available() -> bool:
+    try:
+        _host()
+        return True
+    except Exception:
+        return False
+
+
+def enabled() -> bool:
+    """Native serving core wanted (default) and loadable."""
+    return os.environ.get("RMLX_NATIVE_SERVING", "1") != "0" and available()
+
+
+def _ints(values: Sequence[int]):
+    return (c_int * max(1, len(values)))(*[int(v) for v in values])
+
+
+class NativeBlockManager:
+    """``kv.paged.BlockManager`` backed by the native library."""
+
+    def __init__(self, num_blocks: int, block_size: int = 16, reserved: int = 0):
+        self._lib = _host()
+        self._h = self._lib.rmlx_bm_create(num_blocks, block_size, reserved)
+        if not self._h:
+            raise ValueError("bad block manager arguments")
+        self.num_blocks, self.block_size = num_blocks, block_size
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rmlx_bm_destroy(h)
+
+    # -------------------------------------------------------------- queries
+    def num_free_blocks(self) -> int:
+        return self._lib.rmlx_bm_num_free(self._h)
+
+    def blocks_needed(self, seq_id: int, new_tokens: int) -> int:
+        return self._lib.rmlx_bm_blocks_needed(self._h, seq_id, new_tokens)
+
+    def can_allocate(self, seq_id: int, new_tokens: int) -> bool:
+        return self.blocks_needed(seq_id, new_tokens) <= self.num_free_blocks()
+
+    def has_sequence(self, seq_id: int) -> bool:
+        return bool(self._lib.rmlx_bm_has(self._h, seq_id))
+
+    def num_blocks_of(self, seq_id: int) -> int:
+        return max(0, self._lib.rmlx_bm_table(self._h, seq_id, None, 0))
+
+    def block_table(self, seq_id: int) -> List[int]:
+        n = self._lib.rmlx_bm_table(self._h, seq_id, None, 0)
+        if n < 0:
+            raise KeyError(seq_id)
+        buf = (c_int * max(1, n))()
+        self._lib.rmlx_bm_table(self._h, seq_id, buf, n)
+        return list(buf[:n])
+
+    def seq_len(self, seq_id: int) -> int:
+        return self._lib.rmlx_bm_seq_len(self._h, seq_id)
+
+    def ref_count(self, block: int) -> int:
+        return self._lib.rmlx_bm_ref_count(self._h, block)
+
+    # -------------------------------------------------------------- mutation
+    def add_sequence(self, seq_id: int) -> None:
+        if self._lib.rmlx_bm_add_sequence(self._h, seq_id) != 0:
+            raise KeyError(f"sequence {seq_id} already exists")
+
+    def reserve(self, seq_id: int, new_tokens: int) -> List[tuple]:
+        src, dst, n = c_int(), c_int(), c_int()
+        rc = self._lib.rmlx_bm_reserve(self._h, seq_id, new_tokens, ctypes.byref(src),
+                                       ctypes.byref(dst), ctypes.byref(n))
+        if rc == -3:
+            raise OutOfBlocks(f"need {self.blocks_needed(seq_id, new_tokens)} blocks, "
+                              f"{self.num_free_blocks()} free")
+        if rc != 0:
+            raise ValueError("bad reserve arguments")
+        return [(src.value, dst.value)] if n.value else []
+
+    def commit(self, seq_id: int, new_tokens: int) -> None:
+        if self._lib.rmlx_bm_commit(self._h, seq_id, new_tokens) != 0:
+            raise KeyError(seq_id)
+
+    def fork(self, parent: int, child: int) -> None:
+        if self._lib.rmlx_bm_fork(self._h, parent, child) != 0:
+            raise KeyError(f"sequence {child} already exists or {parent} is unknown")
+
+    def adopt(self, seq_id: int, blocks: List[int], num_tokens: int) -> None:
+        if self._lib.rmlx_bm_adopt(self._h, seq_id, _ints(blocks), len(blocks), num_tokens) != 0:
+            raise ValueError(f"sequence {seq_id} is not empty, or the blocks are not live / too few")
+
+    def retain(self, block: int) -> None:
+        if self._lib.rmlx_bm_retain(self._h, block) != 0:
+            raise ValueError(f"block {block} is not live")
+
+    def release(self, block: int) -> None:
+        if self._lib.rmlx_bm_release(self._h, block) != 0:
+            raise ValueError(f"block {block} is not live")
+
+    def trim(self, seq_id: int, num_tokens: int) -> None:
+        if self._lib.rmlx_bm_trim(self._h, seq_id, num_tokens) != 0:
+            raise KeyError(seq_id)
+
+    def free_sequence(self, seq_id: int) -> None:
+        self._lib.rmlx_bm_free_sequence(self._h, seq_id)
+
+
+class NativePrefixCache:
+    """``serve.prefix_cache.PrefixCache`` backed by the native library."""
+
+    def __init__(self, block_size: int = 16, max_blocks: int = 0):
+        self._lib = _host()
+        self._h = self._lib.rmlx_pc_create(block_size, max_blocks)
+        if not self._h:
+            raise ValueError("bad prefix cache arguments")
+        self.block_size, self.max_blocks = block_size, max_blocks
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rmlx_pc_destroy(h)
+
+    def __len__(self) -> int:
+        return self._lib.rmlx_pc_len(self._h)
+
+    @property
+    def hits(self) -> int:
+        return self._lib.rmlx_pc_hits(self._h)
+
+    @property
+    def misses(self) -> int:
+        return self._lib.rmlx_pc_misses(self._h)
+
+    def insert(self, tokens: Sequence[int], blocks: Sequence[int]) -> int:
+        return len(self.insert_blocks(tokens, blocks))
+
+    def insert_blocks(self, tokens: Sequence[int], blocks: Sequence[int]) -> List[int]:
+        out = (c_int * max(1, len(blocks)))()
+        n = self._lib.rmlx_pc_insert(self._h, _ints(tokens), len(tokens), _ints(blocks), len(blocks),
+                                     out, len(blocks))
+        return list(out[:n])
+
+    def lookup(self, tokens: Sequence[int]) -> Tuple[int, List[int]]:
+        cap = len(tokens) // self.block_size
+        out = (c_int * max(1, cap))()
+        n = self._lib.rmlx_pc_lookup(self._h, _ints(tokens), len(tokens), out, cap)
+        return n * self.block_size, list(out[:n])
+
+    def evict(self, n: int) -> List[int]:
+        n = max(0, min(int(n), len(self)))
+        out = (c_int * max(1, n))()
+        got = self._lib.rmlx_pc_evict(self._h, n, out, n)
+        return list(out[:got])
+
+    def take_evicted(self) -> List[int]:
+        cap = 4096
+        out = (c_int * cap)()
+        victims: List[int] = []
+        while True:
+            got = self._lib.rmlx_pc_take_evicted(self._h, out, cap)
+            victims += list(out[:got])
+            if got < cap:
+                return victims
+
+    def clear(self) -> List[int]:
+        return self.evict(len(self))
+
+
+class NativeScheduler:
+    """``serve.scheduler.Scheduler`` backed by the native library. It plans against a
+    ``NativeBlockManager`` (the two live in the same library and talk directly)."""
+
+    def __init__(self, config: SchedulerConfig, manage_blocks: bool = True, on_admit=None,
+                 on_evict=None):
+        self.cfg = config.validate()
+        self._lib = _host()
+        eos = -1 if self.cfg.eos_token_id is None else int(self.cfg.eos_token_id)
+        self._h = self._lib.rmlx_sched_create(self.cfg.max_batch_size, eos, self.cfg.max_prefill_chunk,
+                                              int(manage_blocks))
+        if not self._h:
+            raise ValueError("bad scheduler configuration")
+        self.manage_blocks = manage_blocks
+        self.on_admit, self.on_evict = on_admit, on_evict
+        self._waiting: Deque[Tuple[int, int]] = deque()       # (seq_id, prompt length) mirror
+        self._decode_buf = (c_int64 * self.cfg.max_batch_size)()
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rmlx_sched_destroy(h)
+
+    # ------------------------------------------------------------------ queueing
+    def add_request(self, req: GenerationRequest) -> None:
+        if not req.prompt_tokens:
+            raise ValueError("empty prompt")
+        rc = self._lib.rmlx_sched_add_request(self._h, req.seq_id, _ints(req.prompt_tokens),
+                                              len(req.prompt_tokens), req.max_output_len)
+        if rc != 0:
+            raise ValueError("request rejected")
+        self._waiting.append((req.seq_id, len(req.prompt_tokens)))
+
+    def num_waiting(self) -> int:
+        return self._lib.rmlx_sched_num_waiting(self._h)
+
+    def num_active(self) -> int:
+        return self._lib.rmlx_sched_num_active(self._h)
+
+    def has_work(self) -> bool:
+        return bool(self.num_waiting() or self.num_active())
+
+    def first_waiting_prompt_len(self) -> Optional[int]:
+        return self._waiting[0][1] if self._waiting else None
+
+    # ------------------------------------------------------------------ one step
+    def schedule(self, bm: NativeBlockManager, finished_tokens: Optional[Dict[int, int]] = None
+                 ) -> SchedulerOutput:
+        out = SchedulerOutput()
+        lib = self._lib
+        for sid, tok in (finished_tokens or {}).items():
+            if lib.rmlx_sched_finish(self._h, sid, -2 if tok is None else int(tok)):
+                if self.on_evict is not None:
+                    self.on_evict(sid)
+                else:
+                    bm.free_sequence(sid)
+                out.evicted_seq_ids.append(sid)
+        while True:
+            sid = lib.rmlx_sched_admit_next(self._h, bm._h)
+            if sid < 0:
+                break
+            self._waiting.popleft()
+            if self.on_admit is not None:
+                cached = self.on_admit(sid) or 0
+                if cached:
+                    lib.rmlx_sched_set_cached(self._h, sid, int(cached))
+            else:
+                bm.add_sequence(sid)
+        prefill = (c_int64 * 3)()
+        n_dec = lib.rmlx_sched_plan(self._h, bm._h, prefill, self._decode_buf, len(self._decode_buf))
+        if prefill[0] >= 0:
+            out.prefill_seqs.append(self._meta(int(prefill[0]), bm))
+            out.prefill_chunk_range = (int(prefill[1]), int(prefill[2]))
+        for i in range(n_dec):
+            out.decode_seqs.append(self._meta(int(self._decode_buf[i]), bm))
+        return out
+
+    def update_sequence(self, seq_id: int, bm: NativeBlockManager, token: int) -> None:
+        if self._lib.rmlx_sched_update(self._h, bm._h, seq_id) != 0:
+            raise KeyError(seq_id)
+
+    def prompt_chunk(self, seq_id: int, rng: Tuple[int, int]) -> List[int]:
+        lo, hi = rng
+        buf = (c_int * max(1, hi - lo))()
+        n = self._lib.rmlx_sched_prompt(self._h, seq_id, lo, hi, buf)
+        if n < 0:
+            raise KeyError(seq_id)
+        return list(buf[:n])
+
+    def _meta(self, sid: int, bm: NativeBlockManager) -> SeqMeta:
+        info = (c_int * 3)()
+        self._lib.rmlx_sched_info(self._h, sid, info)
+        table = bm.block_table(sid) if bm.has_sequence(sid) else []
+        return SeqMeta(sid, int(info[0]), bm.seq_len(sid), table, int(info[1]))

@@ -85,6 +85,9 @@ class Scheduler:
     def has_work(self) -> bool:
         return bool(self.waiting or self.active)
 
+    def first_waiting_prompt_len(self) -> Optional[int]:
+        return len(self.waiting[0].prompt_tokens) if self.waiting else None
+
     # ------------------------------------------------------------------ one step
     def schedule(self, bm: BlockManager, finished_tokens: Optional[Dict[int, int]] = None
                  ) -> SchedulerOutput:
