@@ -125,3 +125,26 @@ def test_managed_buffer_returns_memory():
     with ManagedBuffer(a, 4096) as b:
         assert b.ptr and b.nbytes >= 4096 and a.stats().bytes_in_use >= 4096
     assert a.stats().bytes_in_use == 0
+
+
+def test_ncu_summary_parses_raw_csv():
+    from rmlx_b200.utils.ncu_summary import parse_raw_csv
+    text = "\n".join([
+        "==PROF== banner line that is not CSV",
+        '"ID","Kernel Name","gpu__time_duration.sum","dram__bytes_read.sum",'
+        '"sm__pipe_tensor_cycles_active.avg.pct_of_peak_sustained_active","launch__registers_per_thread",'
+        '"smsp__average_warps_issue_stalled_long_scoreboard_per_issue_active.ratio",'
+        '"smsp__average_warps_issue_stalled_wait_per_issue_active.ratio"',
+        '"","","us","Mbyte","%","register/thread","",""',
+        '"0","void my_kernel<128>(int)","57.95","25.2","36.3","131","2.04","1.65"',
+        '"1","void my_kernel<128>(int)","1,058.40","25.2","n/a","131","0.5","3.25"',
+    ])
+    launches = parse_raw_csv(text)
+    assert len(launches) == 2
+    a, b = launches
+    assert a.kernel.startswith("void my_kernel") and a.number("time") == 57.95
+    assert a.values["tensor pipe active %"] == ("36.3", "%") and a.stalls[0] == (2.04, "long_scoreboard")
+    assert "tensor pipe active %" not in b.values and b.number("time") == 1058.40
+    assert b.stalls[0] == (3.25, "wait")
+    assert "top stalls" in a.render() and "regs/thread: 131" in a.render()
+    assert parse_raw_csv("") == []
