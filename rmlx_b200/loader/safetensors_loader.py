@@ -63,9 +63,20 @@ def read_config(model_dir: str) -> Tuple[TransformerConfig, Optional[QuantConfig
     return cfg, quant
 
 
-def load_tensors(model_dir: str) -> Dict[str, torch.Tensor]:
-    """All tensors of a single-file or sharded checkpoint (CPU)."""
+def _file_loader():
+    """``load_file`` of the native memory-mapped reader when the host library is available
+    (``RMLX_NATIVE_LOADER=0`` opts out), else the one of the ``safetensors`` package."""
+    from . import native_st
+    if os.environ.get("RMLX_NATIVE_LOADER", "1") != "0" and native_st.available():
+        return native_st.load_file
     from safetensors.torch import load_file
+    return load_file
+
+
+def load_tensors(model_dir: str) -> Dict[str, torch.Tensor]:
+    """All tensors of a single-file or sharded checkpoint (CPU). With the native reader they are
+    views of the mapped files: nothing is read until a tensor is converted or copied to a device."""
+    load_file = _file_loader()
     idx = os.path.join(model_dir, "model.safetensors.index.json")
     out: Dict[str, torch.Tensor] = {}
     if os.path.exists(idx):
