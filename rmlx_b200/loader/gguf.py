@@ -115,7 +115,42 @@ def _f16(b: np.ndarray) -> np.ndarray:
     return b.copy().view(np.float16).astype(np.float32)
 
 
+def _native_lib():
+    """The host library with the block dequantisers bound, or None (``RMLX_NATIVE_LOADER=0``, or the
+    library cannot be built or loaded)."""
+    import ctypes
+    import os
+    if os.environ.get("RMLX_NATIVE_LOADER", "1") == "0":
+        return None
+    try:
+        from .. import _lib
+        lib = _lib.host()
+        fn = lib.rmlx_ggml_dequant
+        fn.restype = ctypes.c_int
+        fn.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_uint64, ctypes.c_void_p, ctypes.c_int]
+        return lib
+    except Exception:
+        return None
+
+
 def dequantize(raw: np.ndarray, ggml_type: int) -> np.ndarray:
+    """Blocks of a GGML type to fp32: through the native multi-threaded dequantisers
+    (csrc/host/ggml_dequant.cpp) when available, else ``dequantize_numpy`` (same results)."""
+    lib = _native_lib()
+    if lib is None:
+        return dequantize_numpy(raw, ggml_type)
+    _, be, bb = GGML_TYPES[ggml_type]
+    raw = np.ascontiguousarray(raw, dtype=np.uint8)
+    if raw.size % bb:
+        raise ValueError(f"{raw.size} bytes is not a whole number of {bb}-byte blocks")
+    nblocks = raw.size // bb
+    out = np.empty(nblocks * be, np.float32)
+    if lib.rmlx_ggml_dequant(ggml_type, raw.ctypes.data, nblocks, out.ctypes.data, 0) != 0:
+        raise ValueError(f"no dequantiser for {GGML_TYPES[ggml_type][0]}")
+    return out
+
+
+def dequantize_numpy(raw: np.ndarray, ggml_type: int) -> np.ndarray:
     name, be, bb = GGML_TYPES[ggml_type]
     if name == "F32":
         return raw.view(np.float32).copy()

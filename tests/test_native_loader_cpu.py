@@ -107,3 +107,35 @@ def test_load_tensors_uses_the_native_reader_for_sharded_checkpoints(tmp_path, m
     for n in names:
         assert got[n].dtype == want[n].dtype and got[n].shape == want[n].shape
         assert _same_bytes(got[n], want[n]), n
+
+
+@pytest.mark.parametrize("type_name", ["F32", "F16", "BF16", "Q4_0", "Q4_1", "Q8_0", "Q4_K", "Q6_K"])
+@pytest.mark.parametrize("nblocks", [1, 37, 9000])
+def test_native_ggml_dequantisers_match_numpy_bit_for_bit(type_name, nblocks):
+    """Random block bytes (every scale field a finite fp16, subnormals included) through the native
+    dequantisers and the numpy restatement; 9000 K-quant blocks take the threaded path."""
+    import numpy as np
+    from rmlx_b200.loader import gguf
+    t = gguf._T[type_name]
+    _, be, bb = gguf.GGML_TYPES[t]
+    rng = np.random.default_rng(nblocks)
+    raw = rng.integers(0, 256, size=(nblocks, bb), dtype=np.uint8)
+    scale_fields = {"F16": [0], "Q4_0": [0], "Q4_1": [0, 2], "Q8_0": [0], "Q4_K": [0, 2], "Q6_K": [208]}
+    for off in scale_fields.get(type_name, []):
+        hi = raw[:, off + 1]
+        hi[(hi & 0x7C) == 0x7C] &= 0xBF                  # exponent 31 (inf / nan) -> finite
+    if type_name == "F32":
+        raw = rng.standard_normal(nblocks).astype(np.float32).view(np.uint8).reshape(nblocks, 4)
+    raw = raw.reshape(-1)
+    assert gguf._native_lib() is not None
+    got = gguf.dequantize(raw, t)
+    want = gguf.dequantize_numpy(raw, t)
+    assert got.dtype == np.float32 and got.shape == want.shape == (nblocks * be,)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+def test_ggml_dequantize_rejects_partial_blocks():
+    import numpy as np
+    from rmlx_b200.loader import gguf
+    with pytest.raises(ValueError):
+        gguf.dequantize(np.zeros(17, np.uint8), gguf._T["Q4_0"])
