@@ -113,10 +113,6 @@ class CachedDecode:
         self.refresh_tables()
 
     # ------------------------------------------------------------------ the step
-    def _sum_into(self, partial: torch.Tensor, residual: torch.Tensor, out: torch.Tensor, pdl: bool):
-        """Tensor-parallel reduction of a partial projection plus the residual."""
-        self.comm.allreduce_residual(partial, residual, out, pdl=pdl)
-
     def _run_step(self) -> None:
         m, cfg, w = self.model, self.cfg, self.model.w
         eps, pdl = cfg.rms_norm_eps, self.pdl

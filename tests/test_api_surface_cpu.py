@@ -1,0 +1,148 @@
+"""Small API-surface checks for methods that mirror the reference's public interface but are not on
+any hot path: each is exercised once so that a rename or a broken delegate shows up here."""
+import torch
+
+from rmlx_b200.config import MoeConfig, RotaryConfig, tiny_dense_config
+from rmlx_b200.nn.layers import QuantizedLinear, awq_dequantize, gptq_dequantize
+from rmlx_b200.nn.moe import ExpertGroup, MoeLayer
+from rmlx_b200.parallel.group import Group
+from rmlx_b200.parallel.moe_policy import MoeBackend, MoePolicy
+from rmlx_b200.parallel.topology import GpuInfo, Topology
+from rmlx_b200.parallel.wire import v2_payload_bytes, v3_payload_bytes
+from rmlx_b200.runtime.graph import GraphCache, HazardTracker
+from rmlx_b200.serve.sampler import Sampler
+from rmlx_b200.utils import logging as rlog
+from rmlx_b200.utils import nvtx
+from rmlx_b200.utils.metrics import Counters, TransportMetrics, to_prometheus
+from rmlx_b200.utils.shutdown import ShutdownSignal
+
+
+def test_config_helpers():
+    cfg = tiny_dense_config()
+    assert cfg.q_dim == cfg.num_heads * cfg.head_dim and cfg.kv_dim == cfg.num_kv_heads * cfg.head_dim
+    r = RotaryConfig(head_dim=64, max_seq_len=128)
+    assert (r.base_freq, r.scale, r.traditional) == (10000.0, 1.0, False)
+
+
+def _pack_nibbles(q: torch.Tensor, order) -> torch.Tensor:
+    """[..., 8k] values 0..15 -> int32 [..., k], value order[i] of each group of 8 at bits 4i."""
+    g = q.reshape(*q.shape[:-1], -1, 8).long()
+    word = torch.zeros(g.shape[:-1], dtype=torch.int64)
+    for i, src in enumerate(order):
+        word |= g[..., src] << (4 * i)
+    word = torch.where(word >= 2**31, word - 2**32, word)
+    return word.to(torch.int32)
+
+
+def test_awq_and_gptq_imports_round_trip():
+    g = torch.Generator().manual_seed(0)
+    n_in, n_out, gs = 128, 64, 64
+    q = torch.randint(0, 16, (n_in, n_out), generator=g)
+    z = torch.randint(0, 16, (n_in // gs, n_out), generator=g)
+    s = torch.rand(n_in // gs, n_out, generator=g) * 0.1 + 0.01
+    grp = torch.arange(n_in) // gs
+    want = ((q - z[grp]).float() * s[grp]).t()                       # [out, in]
+    # AutoAWQ: value j of a group of eight sits at nibble position order^-1(j); order 0,2,4,6,1,3,5,7
+    awq_pos = [0, 2, 4, 6, 1, 3, 5, 7]
+    got = awq_dequantize(_pack_nibbles(q, awq_pos), _pack_nibbles(z, awq_pos), s, gs)
+    assert torch.allclose(got, want)
+    lin = QuantizedLinear.from_awq(_pack_nibbles(q, awq_pos), _pack_nibbles(z, awq_pos), s, gs)
+    assert lin.in_features == n_in
+    x = torch.randn(3, n_in, generator=g)
+    assert torch.allclose(lin(x).float(), x @ want.t(), atol=0.35, rtol=0.1)     # re-quantised to Q4
+    # GPTQ: qweight packs eight inputs per word along the input dimension; zeros stored minus one
+    qw = _pack_nibbles(q.t().contiguous(), range(8)).t().contiguous()            # [in/8, out]
+    qz = _pack_nibbles((z - 1) % 16, range(8))                                   # [groups, out/8]
+    got = gptq_dequantize(qw, qz, s)
+    want_g = ((q - (((z - 1) % 16) + 1)[grp]).float() * s[grp]).t()
+    assert torch.allclose(got, want_g)
+    perm = torch.randperm(n_in, generator=g) // gs                               # act-order groups
+    got = gptq_dequantize(qw, qz, s, perm)
+    assert torch.allclose(got, ((q - (((z - 1) % 16) + 1)[perm]).float() * s[perm]).t())
+    assert QuantizedLinear.from_gptq(qw, qz, s).weight.n == n_out
+
+
+def test_moe_expert_bias_builders_and_update():
+    cfg = MoeConfig(num_experts=4, num_experts_per_token=2, hidden_dim=16, intermediate_dim=8)
+    g = torch.Generator().manual_seed(1)
+    experts = [(torch.randn(8, 16, generator=g), torch.randn(8, 16, generator=g), torch.randn(16, 8, generator=g))
+               for _ in range(4)]
+    layer = MoeLayer(cfg, torch.randn(4, 16, generator=g), ExpertGroup.from_experts(experts, dtype=torch.float32))
+    x = torch.randn(12, 16, generator=g)
+    layer.forward(x)
+    before = layer.last_counts.clone()
+    bias = layer.update_expert_bias(lr=0.5)                 # aux-loss-free balancing: starved experts gain
+    assert bias.shape == (4,) and torch.equal(bias.argmax(), before.argmin())
+    same = layer.with_expert_bias(torch.tensor([0.0, 0.0, 0.0, 50.0]))
+    assert same is layer
+    idx, _, counts, _ = layer.route(x)
+    assert (idx == 3).any(dim=1).all() and int(counts[3]) == 12
+
+
+def test_sampler_batch_and_policy_force_and_wire_sizes():
+    s = Sampler()
+    logits = torch.tensor([[0.0, 3.0, 1.0], [5.0, 0.0, 1.0]])
+    assert s.sample_batch(logits) == [1, 0]
+    assert s.sample_batch(logits, [[1], []]) == [1, 0]
+    p = MoePolicy(env={})
+    p.force_backend(MoeBackend.NCCL)
+    assert p.select(1, 16) == MoeBackend.NCCL and p.select(10_000, 1 << 30) == MoeBackend.NCCL
+    p.force_backend(None)
+    assert p.select(1, 16) == MoeBackend.LOCAL
+    assert v2_payload_bytes(8, 64) == 8 * 68 and v3_payload_bytes(3, 64) == 4 + 3 * 68
+
+
+def test_topology_group_metrics_logging_shutdown_nvtx():
+    gpus = [GpuInfo(i, "B200", 180 << 30, 18) for i in range(2)]
+    t = Topology(gpus, [[True, True], [True, True]], [["X", "NV18"], ["NV18", "X"]])
+    assert t.fully_connected() and t.all_nvlink()
+    t.link[0][1] = "SYS"
+    assert not t.all_nvlink()
+    grp = Group.loopback() if hasattr(Group, "loopback") else None
+    if grp is not None:
+        x = torch.arange(4.0)
+        assert grp.allreduce_in_place(x) is x and x.tolist() == [0.0, 1.0, 2.0, 3.0]
+    c = Counters(["peak"])
+    c.set_max("peak", 3); c.set_max("peak", 2)
+    assert c.get("peak") == 3
+    tm = TransportMetrics()
+    name = next(iter(tm.snapshot()))
+    tm.add(name, 5)
+    assert f"rmlx_{name} 5" in to_prometheus("rmlx", tm.snapshot()).replace(".0", "")
+    lines = []
+    old = rlog.get_level()
+    rlog.set_sink(lines.append)
+    rlog.set_level(rlog.LogLevel.DEBUG)
+    rlog.debug("test", "hello", k=1)
+    rlog.set_level(old)
+    rlog.set_sink(print)
+    assert len(lines) == 1 and "hello" in lines[0]
+    sig = ShutdownSignal()
+    assert not sig.is_triggered() and not sig.handle().is_shutdown()
+    sig.trigger()
+    assert sig.is_triggered() and sig.handle().is_shutdown()
+    nvtx.enable(False)
+    assert not nvtx.enabled()
+    with nvtx.range("noop"):
+        nvtx.mark("m")
+    nvtx.enable(True)
+
+
+def test_graph_cache_invalidate_and_hazard_tracker_streams():
+    calls = []
+    cache = GraphCache(max_entries=4)
+    g1 = cache.get_or_capture(("step", 1), lambda: calls.append(1), warmup=0)
+    g1.replay()
+    assert len(cache) == 1 and calls
+    cache.invalidate(("step", 1))
+    assert len(cache) == 0
+    cache.get_or_capture("a", lambda: None, warmup=0); cache.get_or_capture("b", lambda: None, warmup=0)
+    cache.invalidate()
+    assert len(cache) == 0
+    h = HazardTracker()
+    h.submit("compute", writes=[(0, 100)])
+    deps = h.submit("copy", reads=[(50, 60)])
+    assert deps == [(0, "RAW")] and h.in_flight() == 2
+    h.retire_stream("compute")
+    assert h.in_flight() == 1
+    assert h.submit("copy2", reads=[(50, 60)]) == []
