@@ -11,6 +11,9 @@
 // behaviour and serve as the oracle in the tests; the C ABI below is what they are compared with
 // and what the serving engine uses when the host library is present.
 //
+// None of the three classes locks: a serving engine drives them from one thread (the reference's
+// are likewise single-owner `&mut self` types).
+//
 // Return codes: 0 ok, -1 unknown / already existing sequence, -2 bad argument or state,
 // -3 out of blocks. Counts are returned as non-negative ints.
 #include <algorithm>
