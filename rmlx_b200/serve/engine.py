@@ -22,7 +22,9 @@ class ServingEngine:
     def __init__(self, model: TransformerModel, num_blocks: int,
                  scheduler_cfg: Optional[SchedulerConfig] = None,
                  sampler_cfg: Optional[SamplerConfig] = None, comm=None,
-                 use_prefix_cache: bool = False):
+                 use_prefix_cache: bool = False, sample_on_device: bool = False):
+        """``sample_on_device``: run the sampler's tensor ops where the logits are (only the chosen
+        token ids come back) instead of on a host copy of the logits."""
         self.model = model
         scfg = scheduler_cfg or SchedulerConfig()
         self.cache = model.new_cache(num_blocks, max_seqs=scfg.max_batch_size)
@@ -34,6 +36,7 @@ class ServingEngine:
         self.sched = sched_cls(scfg, manage_blocks=False, on_admit=self._on_admit,
                                on_evict=self._on_evict)
         self.sampler = Sampler(sampler_cfg)
+        self.sample_on_device = sample_on_device
         self.greedy = self.sampler.cfg.temperature == 0.0 and self.sampler.cfg.repetition_penalty == 1.0
         self.outputs: Dict[int, List[int]] = {}
         self.last_token: Dict[int, int] = {}
@@ -160,11 +163,14 @@ class ServingEngine:
             if self.greedy:
                 return [int(t) for t in nxt[:len(ids)].cpu()]
             # sampling: the step fed its arg-max back; replace it with the sampled tokens
-            logits = self._engine.logits[:len(ids)].float().cpu()
-            toks = [self.sampler.sample_token(logits[i], self.outputs[s]) for i, s in enumerate(ids)]
+            logits = self._engine.logits[:len(ids)]
+            if not self.sample_on_device:
+                logits = logits.float().cpu()
+            toks = self.sampler.sample_batch(logits, [self.outputs[s] for s in ids])
             self._engine.set_next_tokens(toks)
             return toks
         toks = torch.tensor([self.last_token[s] for s in ids], device=dev)
         logits = self.model.forward(toks, self.cache, ids, last_only=True)
-        return [self.sampler.sample_token(logits[i].float().cpu(), self.outputs[s])
-                for i, s in enumerate(ids)]
+        if not self.sample_on_device:
+            logits = logits.float().cpu()
+        return self.sampler.sample_batch(logits, [self.outputs[s] for s in ids])

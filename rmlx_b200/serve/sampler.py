@@ -30,6 +30,7 @@ class Sampler:
     def __init__(self, config: Optional[SamplerConfig] = None):
         self.cfg = (config or SamplerConfig()).validate()
         self._gen = None
+        self._device_gens = {}
         if self.cfg.seed is not None:
             self._gen = torch.Generator().manual_seed(self.cfg.seed)
 
@@ -73,10 +74,60 @@ class Sampler:
         probs = self.probabilities(logits, history).cpu()
         return int(torch.multinomial(probs, 1, generator=self._gen))
 
+    # ------------------------------------------------------------------ whole batches at once
+    def _generator(self, device: torch.device):
+        """The seeded generator for ``device`` (one per device, derived from ``seed``), or None."""
+        if self.cfg.seed is None:
+            return None
+        if device.type == "cpu":
+            return self._gen
+        g = self._device_gens.get(device)
+        if g is None:
+            g = torch.Generator(device=device).manual_seed(self.cfg.seed)
+            self._device_gens[device] = g
+        return g
+
+    def probabilities_batch(self, logits: torch.Tensor,
+                            histories: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """``probabilities`` for every row of ``logits`` [B, V] in one pass of tensor ops on the
+        device the logits live on (no per-row Python loop, no copy of the logits to the host)."""
+        cfg = self.cfg
+        l = logits.float()
+        if cfg.repetition_penalty != 1.0 and histories is not None and any(len(h) for h in histories):
+            rows, cols = [], []
+            for i, h in enumerate(histories):
+                toks = sorted(set(int(t) for t in h))
+                rows += [i] * len(toks)
+                cols += toks
+            r = torch.tensor(rows, dtype=torch.long, device=l.device)
+            c = torch.tensor(cols, dtype=torch.long, device=l.device)
+            vals = l[r, c]
+            l = l.clone()
+            l[r, c] = torch.where(vals > 0, vals / cfg.repetition_penalty, vals * cfg.repetition_penalty)
+        if cfg.temperature == 0.0:
+            return torch.zeros_like(l).scatter_(1, l.argmax(-1, keepdim=True), 1.0)
+        l = l / cfg.temperature
+        if 0 < cfg.top_k < l.shape[-1]:
+            kth = torch.topk(l, cfg.top_k, dim=-1).values[:, -1:]
+            l = torch.where(l < kth, torch.full_like(l, float("-inf")), l)
+        probs = torch.softmax(l, dim=-1)
+        if cfg.top_p < 1.0:
+            sp, si = torch.sort(probs, dim=-1, descending=True)
+            keep = torch.cumsum(sp, -1) - sp < cfg.top_p      # always keeps the most likely token
+            sp = torch.where(keep, sp, torch.zeros_like(sp))
+            probs = torch.zeros_like(probs).scatter_(1, si, sp)
+            probs = probs / probs.sum(-1, keepdim=True)
+        return probs
+
     def sample_batch(self, logits: torch.Tensor, histories: Optional[Sequence[Sequence[int]]] = None
                      ) -> List[int]:
-        histories = histories or [()] * logits.shape[0]
-        return [self.sample_token(logits[i], histories[i]) for i in range(logits.shape[0])]
+        """One token per row of ``logits`` [B, V]; only the chosen ids leave the logits' device."""
+        if self.cfg.temperature == 0.0:
+            if self.cfg.repetition_penalty == 1.0 or histories is None:
+                return logits.argmax(-1).tolist()
+            return self.probabilities_batch(logits, histories).argmax(-1).tolist()
+        probs = self.probabilities_batch(logits, histories)
+        return torch.multinomial(probs, 1, generator=self._generator(probs.device))[:, 0].tolist()
 
     # ------------------------------------------------------------------ speculative decoding
     @staticmethod

@@ -214,3 +214,32 @@ def test_speculative_decoder_sampling_runs_and_stops_at_eos():
     cut = want[:want.index(eos) + 1]
     spec = SpeculativeDecoder(target, target, k=3, eos_token_id=eos)
     assert spec.generate(prompt, 8) == cut
+
+
+def test_sampler_batch_matches_per_row():
+    g = torch.Generator().manual_seed(4)
+    logits = torch.randn(5, 97, generator=g) * 3
+    hist = [[1, 5, 5, 9], [], [96], [0, 1, 2, 3], [50]]
+    for cfg in (SamplerConfig(), SamplerConfig(repetition_penalty=1.3),
+                SamplerConfig(temperature=0.7), SamplerConfig(temperature=1.2, top_k=10),
+                SamplerConfig(temperature=0.9, top_p=0.8),
+                SamplerConfig(temperature=0.8, top_k=20, top_p=0.6, repetition_penalty=1.2)):
+        s = Sampler(cfg)
+        batch = s.probabilities_batch(logits, hist)
+        rows = torch.stack([s.probabilities(logits[i], hist[i]) for i in range(5)])
+        assert torch.allclose(batch, rows, atol=1e-6), cfg
+        assert torch.allclose(batch.sum(-1), torch.ones(5), atol=1e-5)
+        if cfg.temperature == 0.0:
+            assert s.sample_batch(logits, hist) == [s.sample_token(logits[i], hist[i]) for i in range(5)]
+    # draws follow the distribution: with top_k = 2 only the two best tokens of each row ever appear
+    s = Sampler(SamplerConfig(temperature=1.0, top_k=2, seed=3))
+    best2 = [set(logits[i].topk(2).indices.tolist()) for i in range(5)]
+    seen = [set() for _ in range(5)]
+    for _ in range(40):
+        for i, t in enumerate(s.sample_batch(logits)):
+            assert t in best2[i]
+            seen[i].add(t)
+    assert any(len(v) == 2 for v in seen)
+    # the same seed gives the same draws
+    a, b = Sampler(SamplerConfig(temperature=1.0, seed=11)), Sampler(SamplerConfig(temperature=1.0, seed=11))
+    assert [a.sample_batch(logits) for _ in range(3)] == [b.sample_batch(logits) for _ in range(3)]
