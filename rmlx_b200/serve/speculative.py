@@ -59,7 +59,7 @@ class SpeculativeDecoder:
         if self.greedy:
             return self.sampler.sample_token(logits.cpu(), history), None
         probs = self.sampler.probabilities(logits.cpu(), history)
-        return int(torch.multinomial(probs, 1, generator=self.sampler._gen)), probs
+        return int(torch.multinomial(probs, 1, generator=self.sampler._generator(probs.device))), probs
 
     @torch.no_grad()
     def generate(self, prompt: Sequence[int], max_new_tokens: int) -> List[int]:
