@@ -23,6 +23,8 @@ class GemmStatus:
         if t is None:
             t = torch.zeros(1, dtype=torch.int32, device=device)
             cls._by_device[key] = t
+            from ..runtime.streams import ERRORS
+            ERRORS.register(f"tensor-core kernels, device {key}", t)
         return t
 
     @classmethod

@@ -118,3 +118,82 @@ class Watchdog:
         self._stop.set()
         if self._t:
             self._t.join(timeout=2 * self.cfg.interval_s + 1)
+
+
+class ProgressTracker:
+    """Bulk polling of pending asynchronous operations with an error budget.
+
+    An operation is anything with a non-blocking ``poll() -> bool`` (done or not) that may raise,
+    e.g. ``runtime.streams.GpuEvent.query`` wrapped in a lambda, or a status-word check of a fused
+    kernel. Completed operations leave the pending set; an exception counts as a poll error, and
+    ``max_consecutive_errors`` (5) errors in a row with no success in between raise the health
+    warning flag, which a step loop or the ``Watchdog`` callback can act on. Follows
+    crates/rmlx-distributed/src/progress_tracker.rs:19,38-275 (consecutive-error threshold, bulk
+    poll / wait helpers) with GPU events in place of RDMA completion queues."""
+
+    def __init__(self, max_consecutive_errors: int = 5, clock: Callable[[], float] = time.monotonic):
+        self.max_consecutive_errors = max_consecutive_errors
+        self._clock = clock
+        self._pending: Dict[int, Callable[[], bool]] = {}
+        self._names: Dict[int, str] = {}
+        self._next = 0
+        self._lock = threading.Lock()
+        self.consecutive_errors = 0
+        self.total_errors = 0
+        self.completed = 0
+        self.health_warning = False
+        self.last_error: Optional[str] = None
+
+    def track(self, poll: Callable[[], bool], name: str = "") -> int:
+        """Register a pending operation; returns its id."""
+        with self._lock:
+            oid = self._next
+            self._next += 1
+            self._pending[oid] = poll
+            self._names[oid] = name or f"op{oid}"
+            return oid
+
+    def num_pending(self) -> int:
+        return len(self._pending)
+
+    def poll(self) -> List[int]:
+        """Poll every pending operation once. Returns the ids that completed in this pass."""
+        with self._lock:
+            items = list(self._pending.items())
+        done: List[int] = []
+        for oid, fn in items:
+            try:
+                finished = bool(fn())
+            except Exception as e:                      # noqa: BLE001 - any failure of a poll counts
+                self.total_errors += 1
+                self.consecutive_errors += 1
+                self.last_error = f"{self._names.get(oid, oid)}: {e}"
+                if self.consecutive_errors >= self.max_consecutive_errors:
+                    self.health_warning = True
+                continue
+            self.consecutive_errors = 0
+            if finished:
+                done.append(oid)
+        with self._lock:
+            for oid in done:
+                self._pending.pop(oid, None)
+                self._names.pop(oid, None)
+        self.completed += len(done)
+        return done
+
+    def wait_all(self, timeout_s: float = 5.0, interval_s: float = 0.0005) -> bool:
+        """Poll until nothing is pending, the timeout passes, or the health warning is raised."""
+        deadline = self._clock() + timeout_s
+        while self._pending:
+            self.poll()
+            if not self._pending:
+                break
+            if self.health_warning or self._clock() >= deadline:
+                return False
+            time.sleep(interval_s)
+        return True
+
+    def reset_health(self) -> None:
+        self.consecutive_errors = 0
+        self.health_warning = False
+        self.last_error = None

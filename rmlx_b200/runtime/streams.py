@@ -116,3 +116,61 @@ class StreamManager:
             ev = GpuEvent()
             ev.record(s)
             ev.cpu_wait(timeout_s)
+
+
+class GpuErrorStore:
+    """Collects what kernels report through their status words.
+
+    Kernels of this package never trap: a bounded wait that gives up, or a failed argument check,
+    writes a code into a device word and returns. Components register those words here (a one-element
+    int32 tensor, or a callable returning the code); ``collect()`` reads them all, records every
+    non-zero code with the source's name, clears the words and returns the new records. The
+    counterpart of the reference's per-queue ``GpuErrorStore`` fed by command-buffer completion
+    handlers (crates/rmlx-metal/src/command.rs:325-399)."""
+
+    CODES = {1: "pipeline wait timed out", 2: "peer wait timed out", 3: "bad argument"}
+
+    def __init__(self, max_records: int = 256):
+        self._sources = {}
+        self._records = []
+        self.max_records = max_records
+
+    def register(self, name: str, source) -> None:
+        """``source``: an int32 tensor of one element (device or host), or ``() -> int``."""
+        self._sources[name] = source
+
+    def unregister(self, name: str) -> None:
+        self._sources.pop(name, None)
+
+    def collect(self):
+        """Read and clear every registered word. Returns the list of new (name, code, meaning)."""
+        new = []
+        for name, src in self._sources.items():
+            if callable(src):
+                code = int(src())
+            else:
+                code = int(src.item())
+                if code:
+                    src.zero_()
+            if code:
+                new.append((name, code, self.CODES.get(code, "unknown status")))
+        self._records = (self._records + new)[-self.max_records:]
+        return new
+
+    def records(self):
+        return list(self._records)
+
+    def has_errors(self) -> bool:
+        return bool(self._records)
+
+    def clear(self) -> None:
+        self._records = []
+
+    def raise_if_any(self) -> None:
+        new = self.collect()
+        if new:
+            raise RuntimeError("; ".join(f"{n}: {m} (status {c})" for n, c, m in new))
+
+
+# Process-wide store: components that own a status word register it here when they create it.
+ERRORS = GpuErrorStore()

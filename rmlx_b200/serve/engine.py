@@ -13,6 +13,7 @@ import torch
 
 from ..config import SamplerConfig, SchedulerConfig
 from ..models.transformer import TransformerModel
+from ..utils.metrics import PERF
 from .prefix_cache import PrefixCache
 from .sampler import Sampler
 from .scheduler import GenerationRequest, Scheduler
@@ -161,10 +162,12 @@ class ServingEngine:
             self._engine.reserve(1)
             nxt = self._engine.step()
             if self.greedy:
+                PERF.record_d2h(nxt[:len(ids)])
                 return [int(t) for t in nxt[:len(ids)].cpu()]
             # sampling: the step fed its arg-max back; replace it with the sampled tokens
             logits = self._engine.logits[:len(ids)]
             if not self.sample_on_device:
+                PERF.record_d2h(logits)
                 logits = logits.float().cpu()
             toks = self.sampler.sample_batch(logits, [self.outputs[s] for s in ids])
             self._engine.set_next_tokens(toks)

@@ -67,7 +67,27 @@ class TransportMetrics(Counters):
                           "host_copies", "device_syncs", "fallbacks"])
 
 
+class PerfCounters(Counters):
+    """Process-wide counters of the things that cost a serving loop time outside the kernels: bytes
+    copied between host and device, host-side synchronisations, graph captures and replays, and
+    falls back to a library path. The counterpart of the reference's global zero-copy KPI counters
+    (crates/rmlx-distributed/src/perf_counters.rs:8-220: CPU copies, registrations, GPU syncs,
+    bytes moved, fallbacks)."""
+
+    def __init__(self):
+        super().__init__(["h2d_bytes", "d2h_bytes", "peer_bytes", "host_syncs", "graph_captures",
+                          "graph_replays", "library_fallbacks", "status_errors"])
+
+    def record_d2h(self, tensor) -> None:
+        self.add("d2h_bytes", tensor.numel() * tensor.element_size())
+        self.add("host_syncs")
+
+    def record_h2d(self, tensor) -> None:
+        self.add("h2d_bytes", tensor.numel() * tensor.element_size())
+
+
 GLOBAL = RuntimeMetrics()
+PERF = PerfCounters()
 
 
 def to_prometheus(prefix: str, snapshot: Dict[str, float]) -> str:

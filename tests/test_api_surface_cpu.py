@@ -146,3 +146,68 @@ def test_graph_cache_invalidate_and_hazard_tracker_streams():
     h.retire_stream("compute")
     assert h.in_flight() == 1
     assert h.submit("copy2", reads=[(50, 60)]) == []
+
+
+def test_progress_tracker_error_budget_and_bulk_wait():
+    from rmlx_b200.parallel.health import ProgressTracker
+    pt = ProgressTracker(max_consecutive_errors=4)
+    state = {"a": 2, "b": 0}
+
+    def poll_a():
+        state["a"] -= 1
+        return state["a"] <= 0
+
+    ia, ib = pt.track(poll_a, "a"), pt.track(lambda: True, "b")
+    assert pt.num_pending() == 2
+    assert pt.poll() == [ib] and pt.num_pending() == 1
+    assert pt.wait_all(timeout_s=1.0) and pt.completed == 2 and not pt.health_warning
+
+    def broken():
+        raise OSError("link down")
+
+    pt.track(broken, "c")
+    pt.poll(); pt.poll()
+    assert pt.consecutive_errors == 2 and not pt.health_warning
+    pt.track(lambda: True, "d")
+    pt.poll()                                         # one error, then a success: the run is broken
+    assert pt.consecutive_errors == 0 and not pt.health_warning
+    assert not pt.wait_all(timeout_s=1.0)             # only the broken one is left: four in a row
+    assert pt.health_warning and "link down" in pt.last_error and pt.total_errors >= 5
+    pt.reset_health()
+    assert not pt.health_warning and pt.num_pending() == 1
+
+
+def test_gpu_error_store_collects_and_clears_status_words():
+    from rmlx_b200.runtime.streams import GpuErrorStore
+    store = GpuErrorStore()
+    gemm, peer = torch.zeros(1, dtype=torch.int32), torch.zeros(1, dtype=torch.int32)
+    calls = {"n": 0}
+
+    def tp_status():
+        calls["n"] += 1
+        return 2 if calls["n"] == 2 else 0
+
+    store.register("gemm", gemm); store.register("ep", peer); store.register("tp", tp_status)
+    assert store.collect() == [] and not store.has_errors()
+    gemm[0] = 1
+    got = store.collect()
+    assert ("gemm", 1, "pipeline wait timed out") in got and ("tp", 2, "peer wait timed out") in got
+    assert int(gemm) == 0 and store.has_errors() and len(store.records()) == 2
+    assert store.collect() == []
+    peer[0] = 7
+    try:
+        store.raise_if_any()
+        assert False
+    except RuntimeError as e:
+        assert "ep" in str(e) and "status 7" in str(e)
+    store.clear(); store.unregister("ep")
+    assert not store.has_errors()
+
+
+def test_perf_counters():
+    from rmlx_b200.utils.metrics import PERF, PerfCounters
+    c = PerfCounters()
+    c.record_d2h(torch.zeros(4, 8)); c.record_h2d(torch.zeros(3, dtype=torch.int32)); c.add("graph_replays", 2)
+    snap = c.snapshot()
+    assert snap["d2h_bytes"] == 128 and snap["host_syncs"] == 1 and snap["h2d_bytes"] == 12 and snap["graph_replays"] == 2
+    assert isinstance(PERF, PerfCounters)
