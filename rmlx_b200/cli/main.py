@@ -67,14 +67,46 @@ def launch(cmd: Sequence[str], nproc: int, backend: str = "auto", addr: str = "1
            port: int = 18520, extra_env: Optional[Dict[str, str]] = None, sink=None,
            poll_s: float = 0.05, device_map: Optional[Sequence[int]] = None) -> int:
     """Run ``cmd`` as ``nproc`` ranks. Returns 0 if all succeeded, else 1 after killing the rest."""
-    sink = sink or sys.stdout
-    lock = threading.Lock()
-    procs: List[subprocess.Popen] = []
-    threads = []
+    specs = []
     for r in range(nproc):
         env = dict(os.environ)
         env.update(build_env(r, nproc, backend, addr, port, extra_env, device_map))
-        p = subprocess.Popen(list(cmd), env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+        specs.append((list(cmd), env))
+    return _run_all(specs, sink or sys.stdout, poll_s)
+
+
+def launch_hosts(cmd: Sequence[str], hosts: Sequence[str], per_host: int, backend: str = "nccl",
+                 port: int = 18520, extra_env: Optional[Dict[str, str]] = None, cwd: Optional[str] = None,
+                 sink=None, poll_s: float = 0.05, dry_run: bool = False) -> int:
+    """One rank per GPU on every host, spawned through ssh; the first host is the coordinator.
+    ``dry_run`` prints the ssh command lines instead of running them
+    (crates/rmlx-cli/src/launch.rs:95-120: hosts list, per-rank environment, fail-fast)."""
+    from . import ssh
+    sink = sink or sys.stdout
+    plan = ssh.plan_ranks(hosts, per_host)
+    world = len(plan)
+    addr = hosts[0].split("@")[-1]
+    specs = []
+    for host, rank, slot in plan:
+        env = build_env(rank, world, backend, addr, port, extra_env, device_map=None)
+        env["RMLX_LOCAL_SLOT"] = env["LOCAL_RANK"] = str(slot)
+        specs.append((ssh.ssh_argv(host, cmd, env, cwd), dict(os.environ)))
+    if dry_run:
+        for argv, _ in specs:
+            sink.write(" ".join(ssh.shell_quote(a) for a in argv) + "\n")
+        return 0
+    return _run_all(specs, sink, poll_s)
+
+
+def _run_all(specs, sink, poll_s: float) -> int:
+    """Start every (argv, env), prefix their output with the rank, stop everything at the first
+    non-zero exit. Returns 0 if all succeeded, else 1."""
+    nproc = len(specs)
+    lock = threading.Lock()
+    procs: List[subprocess.Popen] = []
+    threads = []
+    for r, (argv, env) in enumerate(specs):
+        p = subprocess.Popen(argv, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                              text=True, bufsize=1, start_new_session=True)
         procs.append(p)
         t = threading.Thread(target=_pump, args=(r, p.stdout, sink, lock), daemon=True)
@@ -127,6 +159,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     l.add_argument("--coordinator", default="127.0.0.1")
     l.add_argument("--port", type=int, default=18520)
     l.add_argument("--env", action="append", default=[])
+    l.add_argument("--hosts", default="", help="comma-separated [user@]host list: spawn over ssh, --nproc ranks per host")
+    l.add_argument("--cwd", default=None, help="working directory on the remote hosts")
+    l.add_argument("--dry-run", action="store_true", help="with --hosts: print the ssh commands only")
     l.add_argument("command", nargs=argparse.REMAINDER)
     a = ap.parse_args(argv)
     if a.cmd == "config":
@@ -135,6 +170,11 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     cmd = a.command[1:] if a.command and a.command[0] == "--" else a.command
     if not cmd:
         ap.error("launch needs a command after --")
+    if a.hosts:
+        hosts = [h for h in a.hosts.split(",") if h]
+        backend = "nccl" if a.backend == "auto" else resolve_backend(a.backend, True)
+        return launch_hosts(cmd, hosts, a.nproc or 8, backend, a.port, parse_env_args(a.env), a.cwd,
+                            dry_run=a.dry_run)
     import torch
     n = a.nproc or max(1, torch.cuda.device_count())
     backend = resolve_backend(a.backend, torch.cuda.is_available())

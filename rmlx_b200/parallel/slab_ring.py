@@ -81,3 +81,46 @@ class SlabRing:
         assert self.state[i] == self.READING
         self.state[i] = self.FREE
         self.consumed += 1
+
+
+class CreditManager:
+    """Per-(peer, tag) window of receive credits: a sender may only have ``window`` messages of one
+    kind in flight towards one peer, which is what guarantees that the receiver's slots (slabs of a
+    ring, slots of a symmetric receive area) are free when the data lands. The reference pre-posts
+    receive work requests for the same purpose (crates/rmlx-distributed/src/credit_manager.rs); on
+    NVLink the credit is the receiver's slot itself and is returned when the consumer releases it."""
+
+    def __init__(self, window: int = 2):
+        if window < 1:
+            raise ValueError("window must be >= 1")
+        self.window = window
+        self._in_flight = {}
+        self.stalls = 0
+
+    def available(self, peer: int, tag: int) -> int:
+        return self.window - self._in_flight.get((peer, tag), 0)
+
+    def try_acquire(self, peer: int, tag: int) -> bool:
+        k = (peer, tag)
+        if self._in_flight.get(k, 0) >= self.window:
+            self.stalls += 1
+            return False
+        self._in_flight[k] = self._in_flight.get(k, 0) + 1
+        return True
+
+    def acquire(self, peer: int, tag: int, timeout_s: float = 5.0, poll=None, interval_s: float = 0.0005) -> None:
+        """Wait (bounded) for a credit; ``poll`` is called between attempts to make progress on
+        whatever returns credits (e.g. ``ProgressTracker.poll``)."""
+        deadline = time.monotonic() + timeout_s
+        while not self.try_acquire(peer, tag):
+            if time.monotonic() >= deadline:
+                raise WaitTimeout(f"no credit for peer {peer} tag {tag} within {timeout_s} s")
+            if poll is not None:
+                poll()
+            time.sleep(interval_s)
+
+    def release(self, peer: int, tag: int) -> None:
+        k = (peer, tag)
+        if self._in_flight.get(k, 0) <= 0:
+            raise ValueError(f"credit for peer {peer} tag {tag} released twice")
+        self._in_flight[k] -= 1

@@ -99,3 +99,22 @@ def crc_verify(frame: bytes) -> bytes:
     if crc32(payload) != want:
         raise ProtocolError("CRC mismatch")
     return payload
+
+
+# ------------------------------------------------------------------------------------------------
+# Exchange tags: one 64-bit id per in-flight message, so that completions, traces and slot
+# bookkeeping can be matched without a side table. Layout as in the reference's work-request ids
+# (crates/rmlx-rdma/src/exchange_tag.rs): sequence (40 bits) . tag (8) . buffer slot (8) . peer (8).
+# ------------------------------------------------------------------------------------------------
+TAG_DISPATCH, TAG_COMBINE, TAG_ALLREDUCE, TAG_BARRIER = 1, 2, 3, 4
+
+
+def pack_exchange_tag(seq: int, tag: int, slot: int, peer: int) -> int:
+    if not (0 <= seq < 1 << 40 and 0 <= tag < 256 and 0 <= slot < 256 and 0 <= peer < 256):
+        raise ValueError("exchange tag field out of range")
+    return (seq << 24) | (tag << 16) | (slot << 8) | peer
+
+
+def unpack_exchange_tag(word: int):
+    """-> (seq, tag, slot, peer)"""
+    return word >> 24, (word >> 16) & 0xFF, (word >> 8) & 0xFF, word & 0xFF

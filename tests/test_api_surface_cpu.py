@@ -211,3 +211,71 @@ def test_perf_counters():
     snap = c.snapshot()
     assert snap["d2h_bytes"] == 128 and snap["host_syncs"] == 1 and snap["h2d_bytes"] == 12 and snap["graph_replays"] == 2
     assert isinstance(PERF, PerfCounters)
+
+
+def test_ssh_helpers_quote_validate_and_plan():
+    import subprocess
+    import pytest
+    from rmlx_b200.cli import ssh
+    assert ssh.shell_quote("abc-1.2/x") == "abc-1.2/x"
+    assert ssh.shell_quote("it's; rm -rf /") == "'it'\\''s; rm -rf /'"
+    assert ssh.shell_quote("") == "''"
+    for bad in ("-oProxyCommand=evil", "host name", "user@-host", "a;b", "$(x)", ""):
+        with pytest.raises(ValueError):
+            ssh.validate_target(bad)
+    assert ssh.validate_target("user@node-1.cluster") == "user@node-1.cluster"
+    argv = ssh.ssh_argv("node1", ["python", "-c", "print('hi')"], {"RMLX_RANK": "3", "X": "a b"}, cwd="/opt/my app")
+    assert argv[0] == "ssh" and argv[-2] == "node1" and argv[-3] == "--"
+    assert argv[-1] == "cd '/opt/my app' && RMLX_RANK=3 X='a b' python -c 'print('\\''hi'\\'')'"
+    with pytest.raises(ValueError):
+        ssh.remote_command(["x"], {"BAD NAME": "1"})
+
+    def slow(*a, **k):
+        raise subprocess.TimeoutExpired(cmd="ssh", timeout=k.get("timeout"))
+
+    assert ssh.run_remote("node1", ["true"], timeout_s=0.1, runner=slow)[0] == 124
+
+    class R:
+        returncode, stdout, stderr = 0, "ok\n", ""
+
+    assert ssh.run_remote("node1", ["true"], runner=lambda *a, **k: R()) == (0, "ok\n", "")
+    assert ssh.plan_ranks(["a", "b"], 2) == [("a", 0, 0), ("a", 1, 1), ("b", 2, 0), ("b", 3, 1)]
+
+
+def test_exchange_tags_and_credits():
+    import pytest
+    from rmlx_b200.parallel.slab_ring import CreditManager
+    from rmlx_b200.parallel.wire import TAG_COMBINE, pack_exchange_tag, unpack_exchange_tag
+    from rmlx_b200.runtime.streams import WaitTimeout
+    w = pack_exchange_tag((1 << 40) - 1, TAG_COMBINE, 7, 255)
+    assert w < 1 << 64 and unpack_exchange_tag(w) == ((1 << 40) - 1, TAG_COMBINE, 7, 255)
+    with pytest.raises(ValueError):
+        pack_exchange_tag(1 << 40, 0, 0, 0)
+    cm = CreditManager(window=2)
+    assert cm.try_acquire(1, 5) and cm.try_acquire(1, 5) and not cm.try_acquire(1, 5)
+    assert cm.available(1, 5) == 0 and cm.available(2, 5) == 2 and cm.stalls == 1
+    returned = []
+
+    def progress():
+        if not returned:
+            cm.release(1, 5); returned.append(1)
+
+    cm.acquire(1, 5, timeout_s=1.0, poll=progress)          # a credit comes back while waiting
+    with pytest.raises(WaitTimeout):
+        cm.acquire(1, 5, timeout_s=0.02)
+    cm.release(1, 5); cm.release(1, 5)
+    with pytest.raises(ValueError):
+        cm.release(1, 5)
+
+
+def test_cli_multi_host_dry_run_prints_one_ssh_command_per_rank():
+    import io
+    from rmlx_b200.cli.main import launch_hosts
+    out = io.StringIO()
+    rc = launch_hosts(["python", "serve.py"], ["u@n1", "n2"], per_host=2, extra_env={"K": "v w"},
+                      cwd="/srv/app", sink=out, dry_run=True)
+    lines = out.getvalue().strip().splitlines()
+    assert rc == 0 and len(lines) == 4
+    assert lines[0].startswith("ssh ") and " -- u@n1 " in lines[0] and " -- n2 " in lines[3]
+    assert "RMLX_RANK=3" in lines[3] and "RMLX_LOCAL_SLOT=1" in lines[3] and "RMLX_WORLD_SIZE=4" in lines[3]
+    assert "MASTER_ADDR=n1" in lines[2] and "cd /srv/app" in lines[0]
