@@ -1,9 +1,10 @@
 // Block dequantisers for the GGML tensor types found in GGUF checkpoints: F16, BF16, Q4_0, Q4_1,
-// Q8_0, Q4_K and Q6_K to fp32, split over threads by blocks. The arithmetic follows the block
-// layouts of the format (d * q with 4/8-bit quants and fp16 scales for the simple types; 6-bit
-// packed sub-block scales and minima for Q4_K; 6-bit quants with int8 sub-block scales for Q6_K)
-// in the same operation order as the numpy restatement in loader/gguf.py, so the two agree bit for
-// bit and the Python one serves as the oracle.
+// Q5_0, Q5_1, Q8_0, Q2_K, Q3_K, Q4_K, Q5_K and Q6_K to fp32, split over threads by blocks. The
+// arithmetic follows the block layouts of the format (d * q with 4/5/8-bit quants and fp16 scales
+// for the simple types; packed 4- or 6-bit sub-block scales and minima for Q2_K / Q4_K / Q5_K;
+// signed 6-bit sub-block scales for Q3_K; 6-bit quants with int8 sub-block scales for Q6_K) in the
+// same operation order as the numpy restatement in loader/gguf.py, so the two agree bit for bit
+// and the Python one serves as the oracle.
 //
 // Native counterpart of the reference's CPU dequantisation of K-quants and legacy GGML types
 // (crates/rmlx-nn/src/quantized_linear.rs:806 `KQuantConfig::dequantize_to_f32`,
@@ -43,7 +44,8 @@ inline float rd_f16(const uint8_t* p) {
 }
 
 // ggml type ids
-enum : int { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ4_1 = 3, kQ8_0 = 8, kQ4_K = 12, kQ6_K = 14, kBF16 = 30 };
+enum : int { kF32 = 0, kF16 = 1, kQ4_0 = 2, kQ4_1 = 3, kQ5_0 = 6, kQ5_1 = 7, kQ8_0 = 8, kQ2_K = 10,
+              kQ3_K = 11, kQ4_K = 12, kQ5_K = 13, kQ6_K = 14, kBF16 = 30 };
 
 struct TypeInfo { int elems, bytes; };
 bool type_info(int t, TypeInfo* out) {
@@ -53,7 +55,12 @@ bool type_info(int t, TypeInfo* out) {
     case kBF16: *out = {1, 2}; return true;
     case kQ4_0: *out = {32, 18}; return true;
     case kQ4_1: *out = {32, 20}; return true;
+    case kQ5_0: *out = {32, 22}; return true;
+    case kQ5_1: *out = {32, 24}; return true;
     case kQ8_0: *out = {32, 34}; return true;
+    case kQ2_K: *out = {256, 84}; return true;
+    case kQ3_K: *out = {256, 110}; return true;
+    case kQ5_K: *out = {256, 176}; return true;
     case kQ4_K: *out = {256, 144}; return true;
     case kQ6_K: *out = {256, 210}; return true;
     default: return false;
@@ -90,6 +97,94 @@ void block(int type, const uint8_t* b, float* o) {
     case kQ8_0: {
       const float d = rd_f16(b);
       for (int i = 0; i < 32; ++i) o[i] = static_cast<float>(static_cast<int8_t>(b[2 + i])) * d;
+      break;
+    }
+    case kQ5_0:
+    case kQ5_1: {
+      const int off = type == kQ5_0 ? 2 : 4;
+      const float d = rd_f16(b), m = type == kQ5_1 ? rd_f16(b + 2) : 0.f;
+      uint32_t qh;
+      memcpy(&qh, b + off, 4);                 // bit j: fifth bit of value j
+      const uint8_t* qs = b + off + 4;
+      for (int i = 0; i < 16; ++i) {
+        const int lo = (qs[i] & 0xF) | (((qh >> i) & 1u) << 4);
+        const int hi = (qs[i] >> 4) | (((qh >> (i + 16)) & 1u) << 4);
+        if (type == kQ5_0) {
+          o[i] = static_cast<float>(lo - 16) * d;
+          o[16 + i] = static_cast<float>(hi - 16) * d;
+        } else {
+          o[i] = static_cast<float>(lo) * d + m;
+          o[16 + i] = static_cast<float>(hi) * d + m;
+        }
+      }
+      break;
+    }
+    case kQ2_K: {
+      const uint8_t* sc = b;                   // sixteen bytes: 4-bit scale (low) and 4-bit minimum (high)
+      const uint8_t* qs = b + 16;
+      const float d = rd_f16(b + 80), dmin = rd_f16(b + 82);
+      for (int n = 0; n < 2; ++n)
+        for (int j = 0; j < 4; ++j)
+          for (int h = 0; h < 2; ++h) {
+            const uint8_t s = sc[8 * n + 2 * j + h];
+            const float dl = d * static_cast<float>(s & 0xF), ml = dmin * static_cast<float>(s >> 4);
+            float* out = o + 128 * n + 32 * j + 16 * h;
+            const uint8_t* q = qs + 32 * n + 16 * h;
+            for (int i = 0; i < 16; ++i) out[i] = dl * static_cast<float>((q[i] >> (2 * j)) & 3) - ml;
+          }
+      break;
+    }
+    case kQ3_K: {
+      const uint8_t* hm = b;                   // 32 bytes: bit (4n + j) of byte i = high bit of value
+      const uint8_t* qs = b + 32;
+      const uint8_t* sr = b + 96;              // twelve bytes holding sixteen 6-bit scales
+      const float d = rd_f16(b + 108);
+      float scales[16];
+      for (int k = 0; k < 16; ++k) {
+        const int lo = k < 8 ? (sr[k] & 0xF) : (sr[k - 8] >> 4);
+        const int hi = (sr[8 + (k & 3)] >> (2 * (k >> 2))) & 3;
+        scales[k] = static_cast<float>(static_cast<int8_t>(lo | (hi << 4))) - 32.f;
+      }
+      for (int n = 0; n < 2; ++n)
+        for (int j = 0; j < 4; ++j)
+          for (int h = 0; h < 2; ++h) {
+            const float dl = d * scales[8 * n + 2 * j + h];
+            float* out = o + 128 * n + 32 * j + 16 * h;
+            for (int i = 0; i < 16; ++i) {
+              const int idx = 16 * h + i;
+              const int v = static_cast<int>((qs[32 * n + idx] >> (2 * j)) & 3) -
+                            (((hm[idx] >> (4 * n + j)) & 1) ? 0 : 4);
+              out[i] = dl * static_cast<float>(v);
+            }
+          }
+      break;
+    }
+    case kQ5_K: {
+      const float d = rd_f16(b), dmin = rd_f16(b + 2);
+      const uint8_t* s = b + 4;
+      const uint8_t* qh = b + 16;
+      const uint8_t* qs = b + 48;
+      float sc[8], mn[8];
+      for (int j = 0; j < 8; ++j) {
+        if (j < 4) {
+          sc[j] = static_cast<float>(s[j] & 63);
+          mn[j] = static_cast<float>(s[j + 4] & 63);
+        } else {
+          sc[j] = static_cast<float>((s[j + 4] & 0xF) | ((s[j - 4] >> 6) << 4));
+          mn[j] = static_cast<float>((s[j + 4] >> 4) | ((s[j] >> 6) << 4));
+        }
+      }
+      for (int j = 0; j < 4; ++j) {
+        const float d0 = d * sc[2 * j], m0 = dmin * mn[2 * j];
+        const float d1 = d * sc[2 * j + 1], m1 = dmin * mn[2 * j + 1];
+        for (int i = 0; i < 32; ++i) {
+          const uint8_t q = qs[32 * j + i];
+          const int lo = (q & 0xF) + (((qh[i] >> (2 * j)) & 1) << 4);
+          const int hi = (q >> 4) + (((qh[i] >> (2 * j + 1)) & 1) << 4);
+          o[64 * j + i] = d0 * static_cast<float>(lo) - m0;
+          o[64 * j + 32 + i] = d1 * static_cast<float>(hi) - m1;
+        }
+      }
       break;
     }
     case kQ4_K: {

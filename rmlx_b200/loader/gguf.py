@@ -19,8 +19,9 @@ MAGIC = 0x46554747  # "GGUF"
 
 # ggml type id -> (name, block elements, block bytes)
 GGML_TYPES = {
-    0: ("F32", 1, 4), 1: ("F16", 1, 2), 2: ("Q4_0", 32, 18), 3: ("Q4_1", 32, 20), 8: ("Q8_0", 32, 34),
-    12: ("Q4_K", 256, 144), 14: ("Q6_K", 256, 210), 30: ("BF16", 1, 2),
+    0: ("F32", 1, 4), 1: ("F16", 1, 2), 2: ("Q4_0", 32, 18), 3: ("Q4_1", 32, 20), 6: ("Q5_0", 32, 22),
+    7: ("Q5_1", 32, 24), 8: ("Q8_0", 32, 34), 10: ("Q2_K", 256, 84), 11: ("Q3_K", 256, 110),
+    12: ("Q4_K", 256, 144), 13: ("Q5_K", 256, 176), 14: ("Q6_K", 256, 210), 30: ("BF16", 1, 2),
 }
 _T = {v[0]: k for k, v in GGML_TYPES.items()}
 
@@ -172,6 +173,69 @@ def dequantize_numpy(raw: np.ndarray, ggml_type: int) -> np.ndarray:
     if name == "Q8_0":
         d = _f16(blk[:, :2])
         return (blk[:, 2:].view(np.int8).astype(np.float32) * d).reshape(-1)
+    if name in ("Q5_0", "Q5_1"):
+        off = 2 if name == "Q5_0" else 4
+        d = _f16(blk[:, :2])
+        qh = blk[:, off:off + 4].copy().view(np.uint32)                     # [n, 1]: bit j = 5th bit of value j
+        qs = blk[:, off + 4:]
+        bits = ((qh >> np.arange(32, dtype=np.uint32)) & 1).astype(np.uint8)  # [n, 32]
+        q = np.concatenate([qs & 0xF, qs >> 4], 1) | (bits << 4)
+        if name == "Q5_0":
+            return ((q.astype(np.int8) - 16).astype(np.float32) * d).reshape(-1)
+        return (q.astype(np.float32) * d + _f16(blk[:, 2:4])).reshape(-1)
+    if name == "Q2_K":
+        sc, qs = blk[:, :16], blk[:, 16:80]
+        d, dmin = _f16(blk[:, 80:82]), _f16(blk[:, 82:84])
+        out = np.zeros((blk.shape[0], 256), np.float32)
+        for n in range(2):                       # 128 values per half, 32 bytes of quants each
+            q = qs[:, 32 * n:32 * n + 32]
+            for j in range(4):                   # bit pair j of every byte
+                v = (q >> (2 * j)) & 3
+                for h in range(2):               # 16 values per 4-bit scale / 4-bit minimum
+                    s_ = sc[:, 8 * n + 2 * j + h]
+                    dl, ml = d[:, 0] * (s_ & 0xF), dmin[:, 0] * (s_ >> 4)
+                    base = 128 * n + 32 * j + 16 * h
+                    out[:, base:base + 16] = dl[:, None] * v[:, 16 * h:16 * h + 16] - ml[:, None]
+        return out.reshape(-1)
+    if name == "Q3_K":
+        hm, qs, sraw = blk[:, :32], blk[:, 32:96], blk[:, 96:108]
+        d = _f16(blk[:, 108:110])
+        # sixteen 6-bit scales: low 4 bits in bytes 0..7 (two per byte), high 2 bits in bytes 8..11
+        lo = np.concatenate([sraw[:, :8] & 0xF, sraw[:, :8] >> 4], 1)                     # [n, 16]
+        hi = np.concatenate([(sraw[:, 8:12] >> (2 * k)) & 3 for k in range(4)], 1)        # [n, 16]
+        scales = (lo | (hi << 4)).astype(np.int8).astype(np.float32) - 32
+        out = np.zeros((blk.shape[0], 256), np.float32)
+        for n in range(2):
+            q = qs[:, 32 * n:32 * n + 32]
+            for j in range(4):
+                v = ((q >> (2 * j)) & 3).astype(np.int8)
+                m = ((hm >> (4 * n + j)) & 1).astype(np.int8)                              # high bit set: no -4
+                v = v - 4 * (1 - m)
+                for h in range(2):
+                    dl = d[:, 0] * scales[:, 8 * n + 2 * j + h]
+                    base = 128 * n + 32 * j + 16 * h
+                    out[:, base:base + 16] = dl[:, None] * v[:, 16 * h:16 * h + 16]
+        return out.reshape(-1)
+    if name == "Q5_K":
+        d, dmin = _f16(blk[:, 0:2]), _f16(blk[:, 2:4])
+        sc_raw, qh, qs = blk[:, 4:16], blk[:, 16:48], blk[:, 48:176]
+        sc = np.zeros((blk.shape[0], 8), np.float32)
+        mn = np.zeros((blk.shape[0], 8), np.float32)
+        for j in range(8):
+            if j < 4:
+                sc[:, j] = sc_raw[:, j] & 63
+                mn[:, j] = sc_raw[:, j + 4] & 63
+            else:
+                sc[:, j] = (sc_raw[:, j + 4] & 0xF) | ((sc_raw[:, j - 4] >> 6) << 4)
+                mn[:, j] = (sc_raw[:, j + 4] >> 4) | ((sc_raw[:, j] >> 6) << 4)
+        out = np.zeros((blk.shape[0], 256), np.float32)
+        for j in range(4):
+            q = qs[:, 32 * j:32 * j + 32]
+            lo = (q & 0xF) + (((qh >> (2 * j)) & 1) << 4)
+            hi = (q >> 4) + (((qh >> (2 * j + 1)) & 1) << 4)
+            out[:, 64 * j:64 * j + 32] = d * sc[:, [2 * j]] * lo - dmin * mn[:, [2 * j]]
+            out[:, 64 * j + 32:64 * j + 64] = d * sc[:, [2 * j + 1]] * hi - dmin * mn[:, [2 * j + 1]]
+        return out.reshape(-1)
     if name == "Q4_K":
         d, dmin = _f16(blk[:, 0:2]), _f16(blk[:, 2:4])
         sc_raw = blk[:, 4:16].astype(np.uint8)

@@ -109,7 +109,21 @@ def test_load_tensors_uses_the_native_reader_for_sharded_checkpoints(tmp_path, m
         assert _same_bytes(got[n], want[n]), n
 
 
-@pytest.mark.parametrize("type_name", ["F32", "F16", "BF16", "Q4_0", "Q4_1", "Q8_0", "Q4_K", "Q6_K"])
+_SCALE_FIELDS = {"F16": [0], "Q4_0": [0], "Q4_1": [0, 2], "Q5_0": [0], "Q5_1": [0, 2], "Q8_0": [0],
+                 "Q2_K": [80, 82], "Q3_K": [108], "Q4_K": [0, 2], "Q5_K": [0, 2], "Q6_K": [208]}
+
+
+def _random_blocks(rng, nblocks, bb, type_name):
+    import numpy as np
+    raw = rng.integers(0, 256, size=(nblocks, bb), dtype=np.uint8)
+    for off in _SCALE_FIELDS.get(type_name, []):
+        hi = raw[:, off + 1]
+        hi[(hi & 0x7C) == 0x7C] &= 0xBF                  # exponent 31 (inf / nan) -> finite
+    return raw
+
+
+@pytest.mark.parametrize("type_name", ["F32", "F16", "BF16", "Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0",
+                                       "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K"])
 @pytest.mark.parametrize("nblocks", [1, 37, 9000])
 def test_native_ggml_dequantisers_match_numpy_bit_for_bit(type_name, nblocks):
     """Random block bytes (every scale field a finite fp16, subnormals included) through the native
@@ -119,11 +133,7 @@ def test_native_ggml_dequantisers_match_numpy_bit_for_bit(type_name, nblocks):
     t = gguf._T[type_name]
     _, be, bb = gguf.GGML_TYPES[t]
     rng = np.random.default_rng(nblocks)
-    raw = rng.integers(0, 256, size=(nblocks, bb), dtype=np.uint8)
-    scale_fields = {"F16": [0], "Q4_0": [0], "Q4_1": [0, 2], "Q8_0": [0], "Q4_K": [0, 2], "Q6_K": [208]}
-    for off in scale_fields.get(type_name, []):
-        hi = raw[:, off + 1]
-        hi[(hi & 0x7C) == 0x7C] &= 0xBF                  # exponent 31 (inf / nan) -> finite
+    raw = _random_blocks(rng, nblocks, bb, type_name)
     if type_name == "F32":
         raw = rng.standard_normal(nblocks).astype(np.float32).view(np.uint8).reshape(nblocks, 4)
     raw = raw.reshape(-1)
@@ -139,3 +149,30 @@ def test_ggml_dequantize_rejects_partial_blocks():
     from rmlx_b200.loader import gguf
     with pytest.raises(ValueError):
         gguf.dequantize(np.zeros(17, np.uint8), gguf._T["Q4_0"])
+
+
+@pytest.mark.parametrize("type_name", ["Q4_0", "Q4_1", "Q5_0", "Q5_1", "Q8_0", "Q2_K", "Q3_K", "Q4_K", "Q5_K", "Q6_K"])
+def test_ggml_dequantisers_agree_with_the_gguf_package(type_name):
+    """Independent oracle for the block layouts: the ``gguf`` package's own dequantisers on the same
+    random blocks (skipped where that package is not installed)."""
+    import numpy as np
+    gguf_pkg = pytest.importorskip("gguf")
+    from rmlx_b200.loader import gguf
+    t = gguf._T[type_name]
+    _, be, bb = gguf.GGML_TYPES[t]
+    qt = getattr(gguf_pkg.GGMLQuantizationType, type_name)
+    assert tuple(gguf_pkg.GGML_QUANT_SIZES[qt]) == (be, bb)
+    raw = _random_blocks(np.random.default_rng(7), 64, bb, type_name)
+    want = gguf_pkg.quants.dequantize(raw, qt).reshape(-1)
+    for fn in (gguf.dequantize, gguf.dequantize_numpy):
+        got = fn(raw.reshape(-1), t)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), fn.__name__
+
+
+def test_dtype_table_matches_the_gguf_type_table():
+    from rmlx_b200 import dtypes
+    from rmlx_b200.loader import gguf
+    for _, (name, be, bb) in gguf.GGML_TYPES.items():
+        d = dtypes.from_name(name)
+        assert (d.block_elems, d.block_bytes) == (be, bb), name
+    assert dtypes.Q3_K.nbytes(512) == 220 and dtypes.Q5_K.is_quantized
