@@ -95,7 +95,7 @@ def test_dtype_table():
     with pytest.raises(ValueError):
         dtypes.Q4_0.nbytes(33)
     with pytest.raises(ValueError):
-        dtypes.from_name("q3_k")
+        dtypes.from_name("iq2_xxs")
 
 
 def test_residency_and_arena():
