@@ -279,3 +279,29 @@ def test_cli_multi_host_dry_run_prints_one_ssh_command_per_rank():
     assert lines[0].startswith("ssh ") and " -- u@n1 " in lines[0] and " -- n2 " in lines[3]
     assert "RMLX_RANK=3" in lines[3] and "RMLX_LOCAL_SLOT=1" in lines[3] and "RMLX_WORLD_SIZE=4" in lines[3]
     assert "MASTER_ADDR=n1" in lines[2] and "cd /srv/app" in lines[0]
+
+
+def test_ep_runtime_context_stages_and_delivers_with_credits():
+    import pytest
+    from rmlx_b200.parallel.ep_runtime import EpRuntimeContext
+    from rmlx_b200.parallel.slab_ring import CreditManager
+    from rmlx_b200.runtime.streams import WaitTimeout
+    ctx = EpRuntimeContext(rank=0, world=2, credits=CreditManager(window=2))
+    for k in range(2):
+        with ctx.staged(peer=1, tag=1) as buf:
+            buf.tensor[:4] = torch.tensor([k, 1, 2, 3], dtype=torch.uint8)
+    with pytest.raises(WaitTimeout):                      # window of two: the third has to wait
+        with ctx.staged(peer=1, tag=1, timeout_s=0.02):
+            pass
+    assert ctx.delivered(1, 1)[:4].tolist() == [0, 1, 2, 3]
+    ctx.done()
+    with ctx.staged(peer=1, tag=1) as buf:                # the returned credit and slab are reusable
+        buf.tensor[0] = 9
+    assert ctx.delivered(1, 1)[0].item() == 1
+    ctx.done()
+    # a failing producer publishes nothing and leaks neither the slab nor the credit
+    before = (ctx.credits.available(1, 1), ctx.ring.produced)
+    with pytest.raises(RuntimeError):
+        with ctx.staged(peer=1, tag=1):
+            raise RuntimeError("boom")
+    assert (ctx.credits.available(1, 1), ctx.ring.produced) == before and ctx.healthy()
