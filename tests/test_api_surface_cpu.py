@@ -305,3 +305,24 @@ def test_ep_runtime_context_stages_and_delivers_with_credits():
         with ctx.staged(peer=1, tag=1):
             raise RuntimeError("boom")
     assert (ctx.credits.available(1, 1), ctx.ring.produced) == before and ctx.healthy()
+
+
+def test_logical_topology_striping_and_failover():
+    import pytest
+    from rmlx_b200.parallel.topology import LinkFailover, LogicalTopology, stripe_plan
+    assert LogicalTopology.parse(None).peers(2, 4) == [3, 0, 1]
+    assert LogicalTopology.parse("ring").peers(0, 4) == [1, 3] and LogicalTopology.parse("ring").peers(0, 2) == [1]
+    hy = LogicalTopology.parse("hybrid:4")
+    assert hy.peers(5, 8) == [6, 7, 4, 1] and hy.peers(0, 1) == []
+    mat = LogicalTopology.from_env({"RMLX_TOPOLOGY": "[[0,2,1],[2,0,null],[1,1,0]]"})
+    assert mat.peers(0, 3) == [2, 1] and mat.peers(1, 3) == [0]
+    with pytest.raises(ValueError):
+        LogicalTopology.parse("star")
+    assert stripe_plan(1000, 4) == [(0, 0, 1000)]
+    plan = stripe_plan((256 << 10) + 100, 2)
+    assert [p[0] for p in plan] == [0, 1, 0, 1, 0] and plan[-1] == (0, 256 << 10, 100)
+    assert sum(p[2] for p in plan) == (256 << 10) + 100 and stripe_plan(0, 2) == []
+    fo = LinkFailover(lanes=2, fail_after=2, recover_after=2)
+    assert fo.report(1, False) == "active" and fo.report(1, False) == "failed" and fo.usable() == [0]
+    assert fo.report(1, True) == "recovering" and fo.report(1, False) == "failed"
+    assert fo.report(1, True) == "recovering" and fo.report(1, True) == "active" and fo.usable() == [0, 1]
