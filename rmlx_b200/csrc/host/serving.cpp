@@ -335,12 +335,13 @@ class Scheduler {
       if (a.progress >= static_cast<int>(a.prompt.size())) continue;
       const int lo = a.progress;
       const int hi = std::min<int>(static_cast<int>(a.prompt.size()), lo + chunk_);
-      if (bm->blocks_needed(seq, hi - lo) <= bm->num_free()) {
-        if (manage_) {
-          int s, d, n;
-          bm->reserve(seq, hi - lo, &s, &d, &n);
-          bm->commit(seq, hi - lo);
-        }
+      bool room = bm->blocks_needed(seq, hi - lo) <= bm->num_free();
+      if (room && manage_) {
+        int s, d, n;
+        room = bm->reserve(seq, hi - lo, &s, &d, &n) == kOk;   // may still fail on a copy-on-write block
+        if (room) bm->commit(seq, hi - lo);
+      }
+      if (room) {
         a.progress = hi;
         prefill[0] = seq; prefill[1] = lo; prefill[2] = hi;
         chosen = seq;
@@ -354,7 +355,7 @@ class Scheduler {
       if (bm->blocks_needed(seq, 1) > bm->num_free()) continue;   // stalls until blocks free up
       if (manage_) {
         int s, d, n;
-        bm->reserve(seq, 1, &s, &d, &n);
+        if (bm->reserve(seq, 1, &s, &d, &n) != kOk) continue;
       }
       if (n_dec < cap) decode[n_dec++] = seq;
     }
