@@ -21,7 +21,9 @@ def _import_everything():
 def _prototypes():
     """name -> parameter count, from the ``extern "C"`` definitions in the .cu / .cpp sources."""
     out = {}
-    pat = re.compile(r'extern\s+"C"\s+[A-Za-z_][\w\s\*]*?\b(rmlx_\w+)\s*\(')
+    # either prefixed with extern "C", or a definition at the start of a line inside an extern "C" block
+    pat = re.compile(r'(?:extern\s+"C"\s+[A-Za-z_][\w\s\*]*?|^(?:const\s+)?[A-Za-z_]\w*[\s\*]+)\b(rmlx_\w+)\s*\(',
+                     re.MULTILINE)
     for path in list(CSRC.rglob("*.cu")) + list(CSRC.rglob("*.cpp")):
         src = path.read_text()
         for m in pat.finditer(src):
@@ -63,3 +65,40 @@ def test_registered_entry_points_exist_and_match_their_prototypes():
         assert len(args) == len(want), f"{name}: {len(args)} registered arguments, {len(want)} in the prototype"
         got = args.replace("Q", "q").replace("l", "q")
         assert got == want, f"{name}: registered {args!r}, prototype reads {want!r}"
+
+
+def test_host_library_bindings_match_their_prototypes():
+    """The same check for the host library (allocator, serving core, safetensors reader, GGML
+    dequantisers), whose wrappers set ctypes argtypes directly."""
+    import ctypes
+    from rmlx_b200.loader import gguf, native_st
+    from rmlx_b200.runtime import alloc
+    from rmlx_b200.serve import native
+    lib = native._host()
+    native_st._host()
+    alloc._host()
+    assert gguf._native_lib() is not None
+    protos = {n: k for n, k in _prototypes().items()
+              if any(n.startswith(p) for p in ("rmlx_bm_", "rmlx_pc_", "rmlx_sched_", "rmlx_st_", "rmlx_ggml_",
+                                               "rmlx_bfc_", "rmlx_alloc_", "rmlx_crc32"))}
+    assert len(protos) > 60
+
+    def kind(t) -> str:
+        if t in (ctypes.c_void_p, ctypes.c_char_p) or isinstance(t, type) and issubclass(t, ctypes._Pointer):
+            return "p"
+        if t in (ctypes.c_int64, ctypes.c_uint64, ctypes.c_longlong, ctypes.c_ulonglong, ctypes.c_size_t):
+            return "q"
+        if t in (ctypes.c_float,):
+            return "f"
+        return "i"
+
+    checked = 0
+    for name, want in protos.items():
+        assert hasattr(lib, name), name
+        argtypes = getattr(lib, name).argtypes
+        if argtypes is None:
+            continue                                   # exported but not wrapped
+        got = "".join(kind(t) for t in argtypes)
+        assert got == "".join(want), f"{name}: bound as {got!r}, prototype reads {''.join(want)!r}"
+        checked += 1
+    assert checked > 55
