@@ -102,3 +102,17 @@ def test_host_library_bindings_match_their_prototypes():
         assert got == "".join(want), f"{name}: bound as {got!r}, prototype reads {''.join(want)!r}"
         checked += 1
     assert checked > 55
+
+
+def test_prefill_kernel_choice_is_a_host_decision(monkeypatch):
+    """Which attention kernel a prompt gets is decided on the host from head_dim, window and the
+    override variable; no GPU is needed to ask."""
+    from rmlx_b200.ops.attention import prefill_kernel_choice
+    monkeypatch.delenv("RMLX_FLASH_PREFILL", raising=False)
+    assert prefill_kernel_choice(128, 0) == "tc"
+    assert prefill_kernel_choice(64, 0) == "mma" and prefill_kernel_choice(128, 4096) == "mma"
+    monkeypatch.setenv("RMLX_FLASH_PREFILL", "mma")
+    assert prefill_kernel_choice(128, 0) == "mma"
+    lib = _lib.cuda()
+    assert lib.rmlx_qgemm_supported(4096) == 1 and lib.rmlx_qgemm_supported(4096 + 64) == 0
+    assert lib.rmlx_gemm_pick_bn(8192, 4096) in (32, 64, 128, 256)
