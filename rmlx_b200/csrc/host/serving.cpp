@@ -496,6 +496,35 @@ int rmlx_sched_plan(void* h, void* bm, int64_t* prefill, int64_t* decode, int ca
   return SC(h)->plan(BM(bm), prefill, decode, cap);
 }
 int rmlx_sched_update(void* h, void* bm, int64_t seq) { return SC(h)->update(BM(bm), seq); }
+// Bulk forms for the binding: one call per step instead of one per sequence.
+// finish_many: tokens of the previous step for n sequences; writes the ids that ended, returns how many.
+int rmlx_sched_finish_many(void* h, const int64_t* seqs, const int64_t* tokens, int n, int64_t* ended) {
+  int k = 0;
+  for (int i = 0; i < n; ++i)
+    if (SC(h)->finish(seqs[i], tokens[i])) ended[k++] = seqs[i];
+  return k;
+}
+// describe: for n sequence ids writes 4 ints each (prompt length, prefill progress, current length,
+// number of blocks) into meta and the block tables back to back into tables (at most cap entries).
+// Returns the number of table entries written, or -1 if they did not fit; tables may be null.
+int rmlx_sched_describe(void* h, void* bm, const int64_t* seqs, int n, int* meta, int* tables, int cap) {
+  int used = 0;
+  for (int i = 0; i < n; ++i) {
+    int info[3] = {0, 0, 0};
+    SC(h)->info(seqs[i], info);
+    const std::vector<int>* t = BM(bm)->table(seqs[i]);
+    const int nt = t ? static_cast<int>(t->size()) : 0;
+    meta[4 * i] = info[0];
+    meta[4 * i + 1] = info[1];
+    meta[4 * i + 2] = BM(bm)->seq_len(seqs[i]);
+    meta[4 * i + 3] = nt;
+    if (!tables) continue;                       // the caller wants the counters only
+    if (used + nt > cap) return -1;
+    for (int j = 0; j < nt; ++j) tables[used + j] = (*t)[j];
+    used += nt;
+  }
+  return used;
+}
 int rmlx_sched_prompt(void* h, int64_t seq, int lo, int hi, int* out) {
   return SC(h)->prompt(seq, lo, hi, out);
 }

@@ -58,7 +58,7 @@ class _Active:
 
 class Scheduler:
     def __init__(self, config: SchedulerConfig, manage_blocks: bool = True, on_admit=None,
-                 on_evict=None):
+                 on_evict=None, tables_in_meta: bool = True):
         """``manage_blocks=False``: only check capacity; the caller's forward pass reserves and
         commits KV slots itself. ``on_admit`` / ``on_evict`` replace the default
         ``add_sequence`` / ``free_sequence`` calls on the block manager; ``on_admit`` may return the
@@ -69,6 +69,8 @@ class Scheduler:
         self.manage_blocks = manage_blocks
         self.on_admit = on_admit
         self.on_evict = on_evict
+        self.tables_in_meta = tables_in_meta      # False: SeqMeta.block_table stays empty (callers that
+                                                  # read tables from the cache save the copies)
 
     # ------------------------------------------------------------------ queueing
     def add_request(self, req: GenerationRequest) -> None:
@@ -153,8 +155,8 @@ class Scheduler:
     # ------------------------------------------------------------------ internals
     def _meta(self, sid: int, bm: BlockManager) -> SeqMeta:
         a = self.active[sid]
-        return SeqMeta(sid, len(a.prompt), bm.seq_len(sid), list(bm.block_table(sid)),
-                       a.prefill_progress)
+        table = list(bm.block_table(sid)) if self.tables_in_meta else []
+        return SeqMeta(sid, len(a.prompt), bm.seq_len(sid), table, a.prefill_progress)
 
     def _evict(self, sid: int, bm: BlockManager, out: SchedulerOutput) -> None:
         self.active.pop(sid, None)
