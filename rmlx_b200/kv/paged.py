@@ -162,7 +162,7 @@ class BlockManager:
 def make_block_manager(num_blocks: int, block_size: int = PAGE, reserved: int = 0):
     """The block manager of the native host library when it is enabled (the default), else the
     Python one above; both have the same interface and behaviour."""
-    from ..serve import native
+    from . import native
     if native.enabled():
         return native.NativeBlockManager(num_blocks, block_size, reserved)
     return BlockManager(num_blocks, block_size, reserved)
