@@ -140,6 +140,11 @@ def main():
     ao = torch.empty_like(q)
     splits = args.splits or D.default_splits(B, HKV, 1, ctx)
     fsc = D.FlashDecodeScratch(B, HQ, HKV, HD, splits, dev)
+    fcl = D.FlashDecodeScratch(B, HQ, HKV, HD, splits, dev, max_len=ctx)
+    if fcl.clusters > 0:
+        add(f"flash_decode ctx{ctx} clusters {fcl.clusters & 0xff}x{fcl.clusters >> 8}",
+            [(lambda i=i: D.flash_decode_paged(q, kcs[i], vcs[i], bt, sl, None, None, fcl, out=ao))
+             for i in range(ncp)], B * ctx * HKV * HD * 2 * 2)
     add(f"flash_decode ctx{ctx} splits{splits}",
         [(lambda i=i: D.flash_decode_paged(q, kcs[i], vcs[i], bt, sl, None, splits, fsc, out=ao))
          for i in range(ncp)], B * ctx * HKV * HD * 2 * 2)

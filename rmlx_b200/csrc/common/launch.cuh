@@ -36,6 +36,16 @@ inline cudaError_t set_max_smem(Kern kern, size_t bytes) {
                               static_cast<int>(bytes));
 }
 
+// Ask for the largest shared-memory carve-out. The kernels of a decode step are chained with
+// programmatic dependent launch; an SM whose L1 / shared-memory split has to change between two
+// kernels must drain first, which would undo the overlap, so every kernel of the chain asks for
+// the same split.
+template <class Kern>
+inline void prefer_max_shared(Kern kern) {
+  (void)cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared);
+}
+
 template <class... KArgs, class... Args>
 inline int launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
                   bool pdl, Args... args) {
@@ -51,6 +61,7 @@ inline int launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cu
     cfg.attrs = attr;
     cfg.numAttrs = 1;
   }
+  if (pdl) prefer_max_shared(kern);
   cudaError_t e = cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
   if (e != cudaSuccess) (void)cudaGetLastError();  // do not leave a stale launch error behind
   return static_cast<int>(e);

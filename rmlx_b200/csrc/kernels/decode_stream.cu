@@ -1,0 +1,207 @@
+// Launchers of the weight-streaming decode projections (stream_gemv.cuh, stream_problems.cuh) for
+// one GPU. Every entry point returns -2 for shapes the streaming kernel does not take (the caller
+// then uses the per-row kernels of decode_gemv.cu / decode_moe.cu).
+#include "stream_problems.cuh"
+
+namespace rb {
+
+static __device__ int g_sg_status = 0;
+
+static int* sg_status_ptr() {
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_sg_status) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
+}
+
+template <bool Q4, int B, bool F32>
+static int run_dense(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
+                     const void* norm_w, float eps, const void* res, int res_stride, void* out,
+                     int out_stride, int N, int K, int pdl, cudaStream_t st) {
+  SgDense<Q4, B, F32> P;
+  P.W = sg_weights(Q4, w, sc, bi, K);
+  P.N = N; P.K = K;
+  P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
+  P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
+  P.residual = static_cast<const __nv_bfloat16*>(res); P.res_stride = res_stride;
+  P.out = out; P.out_stride = out_stride;
+  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, false, (N + 3) / 4, sm_count(), 1 << 20, sg_x_bytes(Q4, K, B), 0, B);
+  return sg_launch(P, pl, pl.grid, sg_status_ptr(), pdl, st);
+}
+
+template <bool Q4, int B>
+static int run_qkv(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
+                   const void* norm_w, float eps, const SgRopeArgs& a, int K, int pdl, cudaStream_t st) {
+  SgQkvRope<Q4, B> P;
+  P.W = sg_weights(Q4, w, sc, bi, K);
+  P.K = K;
+  P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
+  P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
+  P.a = a;
+  const int quads = (a.Hq + 2 * a.Hkv) * (a.HD / 4);
+  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, !a.traditional, quads, sm_count(), a.HD / 4, sg_x_bytes(Q4, K, B),
+                                 SgQkvRope<Q4, B>::extra_bytes(a.HD, B), B);
+  return sg_launch(P, pl, pl.grid, sg_status_ptr(), pdl, st);
+}
+
+template <bool Q4, int B>
+static int run_gate_up(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
+                       const void* norm_w, float eps, void* act, int act_stride, int I, int K, int pdl,
+                       cudaStream_t st) {
+  SgGateUp<Q4, B> P;
+  P.W = sg_weights(Q4, w, sc, bi, K);
+  P.I = I; P.K = K;
+  P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
+  P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
+  P.act = static_cast<__nv_bfloat16*>(act); P.act_stride = act_stride;
+  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, true, I / 2, sm_count(), 1 << 20, sg_x_bytes(Q4, K, B), 0, B);
+  return sg_launch(P, pl, pl.grid, sg_status_ptr(), pdl, st);
+}
+
+template <bool Q4>
+static int run_moe_gate_up(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
+                           const void* norm_w, float eps, const int* idx, void* act, int act_stride,
+                           int B, int top_k, int I, int K, int expert_base, int experts_local, int pdl,
+                           cudaStream_t st) {
+  SgMoeGateUp<Q4> P;
+  P.W = sg_weights(Q4, w, sc, bi, K);
+  P.I = I; P.K = K;
+  P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
+  P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
+  P.act = static_cast<__nv_bfloat16*>(act); P.act_stride = act_stride;
+  P.R = SgRouting{idx, nullptr, top_k, expert_base, experts_local};
+  P.token = 0; P.packed = 0; P.mask = 0;
+  const int per_token = sm_count() / B > 0 ? sm_count() / B : 1;
+  const int hq = I / 2;
+  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, true, top_k * hq, per_token, hq & -hq, sg_x_bytes(Q4, K, 1), 0, 1);
+  return sg_launch(P, pl, pl.grid * B, sg_status_ptr(), pdl, st);
+}
+
+template <bool Q4, bool F32>
+static int run_moe_down(const void* w, const void* sc, const void* bi, const void* act, int act_stride,
+                        const int* idx, const float* tw, const void* res, int res_stride, void* out,
+                        int out_stride, int B, int top_k, int N, int I, int expert_base,
+                        int experts_local, int pdl, cudaStream_t st) {
+  SgMoeDown<Q4, F32> P;
+  P.W = sg_weights(Q4, w, sc, bi, I);
+  P.N = N; P.I = I;
+  P.act = static_cast<const __nv_bfloat16*>(act); P.act_stride = act_stride;
+  P.R = SgRouting{idx, tw, top_k, expert_base, experts_local};
+  P.token = 0; P.nloc = 0; P.packed = 0;
+  P.residual = static_cast<const __nv_bfloat16*>(res); P.res_stride = res_stride;
+  P.out = out; P.out_stride = out_stride;
+  const int per_token = sm_count() / B > 0 ? sm_count() / B : 1;
+  const SgPlan pl = sg_make_plan(Q4, P.W.units, top_k, false, (N + 3) / 4, per_token, 1 << 20,
+                                 sg_x_bytes(Q4, top_k * I, 1), 64, 1);
+  return sg_launch(P, pl, pl.grid * B, sg_status_ptr(), pdl, st);
+}
+
+}  // namespace rb
+
+using namespace rb;
+
+#define SG_DISPATCH_B(B_, ...)                       \
+  switch (B_) {                                      \
+    case 1: { constexpr int kB = 1; __VA_ARGS__; }   \
+    case 2: { constexpr int kB = 2; __VA_ARGS__; }   \
+    case 3: { constexpr int kB = 3; __VA_ARGS__; }   \
+    case 4: { constexpr int kB = 4; __VA_ARGS__; }   \
+    default: return -2;                              \
+  }
+
+// 0, or the code of a bounded wait that expired in a streaming kernel since the last call.
+extern "C" int rmlx_sg_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_sg_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_sg_status, &zero, sizeof(int));
+  return v;
+}
+
+// Same contract as rmlx_rms_gemv (decode_gemv.cu).
+extern "C" int rmlx_sg_rms_gemv(int w_kind, const void* w, const void* scales, const void* biases,
+                                const void* x, int x_stride, const void* norm_w, float eps,
+                                const void* residual, int res_stride, void* out, int out_stride,
+                                int out_f32, int B, int N, int K, int pdl, cudaStream_t st) {
+  if (B < 1 || N < 1 || w_kind < 0 || w_kind > 1 || !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+    return -2;
+#define SG_ARGS w, scales, biases, x, x_stride, norm_w, eps, residual, res_stride, out, out_stride, N, K, pdl, st
+  if (w_kind == 1) {
+    if (out_f32) { SG_DISPATCH_B(B, return (run_dense<true, kB, true>(SG_ARGS))) }
+    else { SG_DISPATCH_B(B, return (run_dense<true, kB, false>(SG_ARGS))) }
+  } else {
+    if (out_f32) { SG_DISPATCH_B(B, return (run_dense<false, kB, true>(SG_ARGS))) }
+    else { SG_DISPATCH_B(B, return (run_dense<false, kB, false>(SG_ARGS))) }
+  }
+#undef SG_ARGS
+  return -2;
+}
+
+// Same contract as rmlx_rms_qkv_rope (decode_qkv_rope.cu); head_dim must be a multiple of 4.
+extern "C" int rmlx_sg_rms_qkv_rope(int w_kind, const void* w, const void* scales, const void* biases,
+                                    const void* x, int x_stride, const void* norm_w, float eps,
+                                    void* q_out, void* k_cache, void* v_cache, const int* block_table,
+                                    const int* positions, const int* row_seq, const float* cos_t,
+                                    const float* sin_t, int B, int K, int Hq, int Hkv, int HD,
+                                    int max_blocks, int page, int traditional, int pdl,
+                                    cudaStream_t st) {
+  if (B < 1 || HD % 4 || Hq < 1 || Hkv < 1 || w_kind < 0 || w_kind > 1 ||
+      !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+    return -2;
+  SgRopeArgs a{static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
+               static_cast<__nv_bfloat16*>(v_cache), block_table, positions, row_seq, cos_t, sin_t,
+               Hq, Hkv, HD, max_blocks, page, traditional};
+  if (w_kind == 1) { SG_DISPATCH_B(B, return (run_qkv<true, kB>(w, scales, biases, x, x_stride, norm_w, eps, a, K, pdl, st))) }
+  else { SG_DISPATCH_B(B, return (run_qkv<false, kB>(w, scales, biases, x, x_stride, norm_w, eps, a, K, pdl, st))) }
+  return -2;
+}
+
+// Same contract as rmlx_rms_gate_up_swiglu; I must be even.
+extern "C" int rmlx_sg_gate_up(int w_kind, const void* w, const void* scales, const void* biases,
+                               const void* x, int x_stride, const void* norm_w, float eps, void* act,
+                               int act_stride, int B, int I, int K, int pdl, cudaStream_t st) {
+  if (B < 1 || I < 2 || I % 2 || w_kind < 0 || w_kind > 1 || !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+    return -2;
+  if (w_kind == 1) { SG_DISPATCH_B(B, return (run_gate_up<true, kB>(w, scales, biases, x, x_stride, norm_w, eps, act, act_stride, I, K, pdl, st))) }
+  else { SG_DISPATCH_B(B, return (run_gate_up<false, kB>(w, scales, biases, x, x_stride, norm_w, eps, act, act_stride, I, K, pdl, st))) }
+  return -2;
+}
+
+// Same contract as rmlx_moe_gate_up; I must be even, at most 256 local experts.
+extern "C" int rmlx_sg_moe_gate_up(int w_kind, const void* w, const void* scales, const void* biases,
+                                   const void* x, int x_stride, const void* norm_w, float eps,
+                                   const int* topk_idx, void* act, int act_stride, int B, int top_k,
+                                   int I, int K, int expert_base, int experts_local, int pdl,
+                                   cudaStream_t st) {
+  if (B < 1 || top_k < 1 || top_k > kSgMaxTopK || I % 2 || experts_local > 256 || w_kind < 0 ||
+      w_kind > 1 || !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+    return -2;
+  if (w_kind == 1)
+    return run_moe_gate_up<true>(w, scales, biases, x, x_stride, norm_w, eps, topk_idx, act, act_stride,
+                                 B, top_k, I, K, expert_base, experts_local, pdl, st);
+  return run_moe_gate_up<false>(w, scales, biases, x, x_stride, norm_w, eps, topk_idx, act, act_stride, B,
+                                top_k, I, K, expert_base, experts_local, pdl, st);
+}
+
+// Same contract as rmlx_moe_down; at most 256 local experts.
+extern "C" int rmlx_sg_moe_down(int w_kind, const void* w, const void* scales, const void* biases,
+                                const void* act, int act_stride, const int* topk_idx,
+                                const float* topk_w, const void* residual, int res_stride, void* out,
+                                int out_stride, int out_f32, int B, int top_k, int N, int I,
+                                int expert_base, int experts_local, int pdl, cudaStream_t st) {
+  if (B < 1 || top_k < 1 || top_k > kSgMaxTopK || experts_local > 256 || w_kind < 0 || w_kind > 1 ||
+      !sg_weights_ok(w_kind == 1, w, scales, biases, I) || (w_kind == 0 && I % 32))
+    return -2;
+#define SG_DOWN(Q4_, F32_)                                                                         \
+  return run_moe_down<Q4_, F32_>(w, scales, biases, act, act_stride, topk_idx, topk_w, residual,  \
+                                 res_stride, out, out_stride, B, top_k, N, I, expert_base,       \
+                                 experts_local, pdl, st)
+  if (w_kind == 1) { if (out_f32) SG_DOWN(true, true); else SG_DOWN(true, false); }
+  else { if (out_f32) SG_DOWN(false, true); else SG_DOWN(false, false); }
+#undef SG_DOWN
+  return -2;
+}

@@ -68,7 +68,7 @@ class CachedDecode:
         lib = _lib.cuda()
         gt = lib.rmlx_flash_decode_gtiles(hq, hkv)
         self.splits = splits or D.default_splits(B, hkv, gt, cfg.max_seq_len)
-        self.fd_scratch = D.FlashDecodeScratch(B, hq, hkv, hd, self.splits, dev)
+        self.fd_scratch = D.FlashDecodeScratch(B, hq, hkv, hd, self.splits, dev, max_len=cfg.max_seq_len)
         moe = cfg.ff_type.moe
         if moe is not None:
             k = moe.num_experts_per_token

@@ -18,6 +18,34 @@ from .weights import LinearWeight, W_Q4
 
 _MAXB = 4
 _Q4_PATH = os.environ.get("RMLX_Q4_PATH", "auto")
+_STREAM = os.environ.get("RMLX_DECODE_STREAM", "1") != "0"
+
+_lib.register_cuda_sigs({
+    "rmlx_sg_status": ("", "i"),
+    "rmlx_sg_rms_gemv": ("ippppipfpipiiiiiip", "i"),
+    "rmlx_sg_rms_qkv_rope": ("ippppipfppppppppiiiiiiiiip", "i"),
+    "rmlx_sg_gate_up": ("ippppipfpiiiiip", "i"),
+    "rmlx_sg_moe_gate_up": ("ippppipfppiiiiiiiip", "i"),
+    "rmlx_sg_moe_down": ("ippppipppipiiiiiiiiip", "i"),
+})
+
+
+def stream_enabled() -> bool:
+    """Whether the decode projections run on the persistent weight-streaming kernels
+    (csrc/kernels/stream_gemv.cuh: bulk-copy ring, one block per SM). Shapes those kernels do not
+    take, and ``RMLX_DECODE_STREAM=0``, use the one-warp-per-row kernels."""
+    return _STREAM
+
+
+def set_stream(on: bool) -> None:
+    global _STREAM
+    _STREAM = bool(on)
+
+
+def stream_status() -> int:
+    """0, or the code of a bounded wait that expired inside a streaming kernel since the last call."""
+    return int(_lib.cuda().rmlx_sg_status())
+
 
 
 def q4_path() -> str:
@@ -51,6 +79,22 @@ def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = 
     if out is None:
         out = torch.empty(b, n, dtype=out_dtype, device=x.device)
     lib, st = _lib.cuda(), _lib.stream_ptr()
+    if _STREAM:
+        done = True
+        for b0 in range(0, b, _MAXB):
+            bb = min(_MAXB, b - b0)
+            xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
+            rs = None if residual is None else residual[b0:b0 + bb]
+            rc = lib.rmlx_sg_rms_gemv(*_wargs(w), xs.data_ptr(), xs.stride(0), _lib.ptr(norm_w), eps,
+                                      _lib.ptr(rs), 0 if rs is None else rs.stride(0), os_.data_ptr(),
+                                      os_.stride(0), int(out.dtype == torch.float32), bb, n, k,
+                                      int(pdl), st)
+            if rc == -2 and b0 == 0:
+                done = False
+                break
+            _lib.check(rc, "sg_rms_gemv")
+        if done:
+            return out
     if w.kind == W_Q4 and q4_path() == "mma" and lib.rmlx_qmv_mma_supported(k, min(8, b), 16):
         for b0 in range(0, b, 8):
             bb = min(8, b - b0)
@@ -83,6 +127,19 @@ def rms_gate_up_swiglu(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.
     if out is None:
         out = torch.empty(b, i, dtype=torch.bfloat16, device=x.device)
     lib, st = _lib.cuda(), _lib.stream_ptr()
+    if _STREAM:
+        done = True
+        for b0 in range(0, b, _MAXB):
+            bb = min(_MAXB, b - b0)
+            xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
+            rc = lib.rmlx_sg_gate_up(*_wargs(w), xs.data_ptr(), xs.stride(0), _lib.ptr(norm_w), eps,
+                                     os_.data_ptr(), os_.stride(0), bb, i, k, int(pdl), st)
+            if rc == -2 and b0 == 0:
+                done = False
+                break
+            _lib.check(rc, "sg_gate_up")
+        if done:
+            return out
     for b0 in range(0, b, _MAXB):
         bb = min(_MAXB, b - b0)
         xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
@@ -177,6 +234,14 @@ def moe_gate_up(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor]
     i = w.n // 2
     if out is None:
         out = torch.zeros(b * top_k, i, dtype=torch.bfloat16, device=x.device)
+    if _STREAM:
+        rc = _lib.cuda().rmlx_sg_moe_gate_up(*_wargs(w), x.data_ptr(), x.stride(0), _lib.ptr(norm_w),
+                                             eps, idx.data_ptr(), out.data_ptr(), out.stride(0), b,
+                                             top_k, i, k, expert_base, w.experts, int(pdl),
+                                             _lib.stream_ptr())
+        if rc != -2:
+            _lib.check(rc, "sg_moe_gate_up")
+            return out
     if w.kind == W_Q4 and q4_path() == "mma" and _lib.cuda().rmlx_qmv_mma_supported(k, 1, 32):
         rc = _lib.cuda().rmlx_moe_gate_up_q4_mma(
             w.w.data_ptr(), w.scales.data_ptr(), w.biases.data_ptr(), x.data_ptr(), x.stride(0),
@@ -200,6 +265,16 @@ def moe_down(act: torch.Tensor, w: LinearWeight, idx: torch.Tensor, wts: torch.T
     n, i = w.n, w.k
     if out is None:
         out = torch.empty(b, n, dtype=out_dtype, device=act.device)
+    if _STREAM:
+        rc = _lib.cuda().rmlx_sg_moe_down(*_wargs(w), act.data_ptr(), act.stride(0), idx.data_ptr(),
+                                          wts.data_ptr(), _lib.ptr(residual),
+                                          0 if residual is None else residual.stride(0),
+                                          out.data_ptr(), out.stride(0),
+                                          int(out.dtype == torch.float32), b, top_k, n, i,
+                                          expert_base, w.experts, int(pdl), _lib.stream_ptr())
+        if rc != -2:
+            _lib.check(rc, "sg_moe_down")
+            return out
     if w.kind == W_Q4 and q4_path() == "mma" and _lib.cuda().rmlx_moe_down_q4_mma_supported(i, top_k):
         rc = _lib.cuda().rmlx_moe_down_q4_mma(
             w.w.data_ptr(), w.scales.data_ptr(), w.biases.data_ptr(), act.data_ptr(), act.stride(0),
@@ -218,10 +293,25 @@ def moe_down(act: torch.Tensor, w: LinearWeight, idx: torch.Tensor, wts: torch.T
     return out
 
 
-class FlashDecodeScratch:
-    """Split-KV scratch: partial outputs, (max, sum) pairs and the per-tile ticket counters."""
+_lib.register_cuda_sigs({
+    "rmlx_flash_decode_cluster_plan": ("iii", "i"),
+    "rmlx_flash_decode_cluster_part_o_elems": ("iii", "q"),
+    "rmlx_flash_decode_cluster_part_ml_elems": ("ii", "q"),
+    "rmlx_flash_decode_cluster": ("pppppppppiiiiiiifip", "i"),
+})
+_FD_CLUSTER = os.environ.get("RMLX_FLASH_DECODE_CLUSTER", "1") != "0"
 
-    def __init__(self, batch: int, hq: int, hkv: int, head_dim: int, splits: int, device):
+
+class FlashDecodeScratch:
+    """Split-KV scratch: partial outputs, (max, sum) pairs and the per-tile ticket counters.
+
+    With ``max_len`` given, the scratch also plans the cluster kernel (flash_decode_cluster.cu:
+    thread-block clusters merging through distributed shared memory), which takes over when a
+    few sequences have to fill the machine; ``clusters`` is then its plan
+    ((cluster size << 8) | clusters per tile)."""
+
+    def __init__(self, batch: int, hq: int, hkv: int, head_dim: int, splits: int, device,
+                 max_len: Optional[int] = None):
         lib = _lib.cuda()
         self.splits = splits
         self.part_o = torch.empty(lib.rmlx_flash_decode_part_o_elems(batch, hq, hkv, splits, head_dim),
@@ -230,6 +320,19 @@ class FlashDecodeScratch:
                                    dtype=torch.float32, device=device)
         self.tickets = torch.zeros(lib.rmlx_flash_decode_ticket_elems(batch, hq, hkv),
                                    dtype=torch.int32, device=device)
+        self.clusters = 0
+        if max_len is not None and _FD_CLUSTER:
+            tiles = batch * hkv * lib.rmlx_flash_decode_gtiles(hq, hkv)
+            with torch.cuda.device(device):
+                self.clusters = int(lib.rmlx_flash_decode_cluster_plan(tiles, int(max_len), head_dim))
+            if (self.clusters & 0xff) > 1:
+                self.c_part_o = torch.empty(
+                    lib.rmlx_flash_decode_cluster_part_o_elems(tiles, self.clusters & 0xff, head_dim),
+                    dtype=torch.float32, device=device)
+                self.c_part_ml = torch.empty(
+                    lib.rmlx_flash_decode_cluster_part_ml_elems(tiles, self.clusters & 0xff),
+                    dtype=torch.float32, device=device)
+                self.c_tickets = torch.zeros(tiles, dtype=torch.int32, device=device)
 
 
 def default_splits(batch: int, hkv: int, gtiles: int, max_len: int, sm_count: int = 148) -> int:
@@ -262,6 +365,18 @@ def flash_decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         scratch = FlashDecodeScratch(b, hq, hkv, d, splits, q.device)
     if out is None:
         out = torch.empty_like(q)
+    if scratch is not None and scratch.clusters > 0 and (splits is None or splits == scratch.splits):
+        nc = scratch.clusters & 0xff
+        rc = lib.rmlx_flash_decode_cluster(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+            seq_lens.data_ptr(), out.data_ptr(),
+            scratch.c_part_o.data_ptr() if nc > 1 else None,
+            scratch.c_part_ml.data_ptr() if nc > 1 else None,
+            scratch.c_tickets.data_ptr() if nc > 1 else None,
+            b, hq, hkv, d, block_table.stride(0), scratch.clusters, window, scale, int(pdl),
+            _lib.stream_ptr())
+        _lib.check(rc, "flash_decode_cluster")
+        return out
     rc = lib.rmlx_flash_decode_paged(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
         seq_lens.data_ptr(), out.data_ptr(),
@@ -316,6 +431,16 @@ def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor
         # without an explicit map, row r of this launch is sequence b0 + r: shift the table instead
         bt = block_table if row_seq is not None else block_table[b0:]
         rs = None if row_seq is None else row_seq[b0:]
+        fn = _lib.cuda().rmlx_sg_rms_qkv_rope if _STREAM else None
+        if fn is not None:
+            rc = fn(w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
+                    xs.stride(0), _lib.ptr(norm_w), eps, qs.data_ptr(), k_cache.data_ptr(),
+                    v_cache.data_ptr(), bt.data_ptr(), positions[b0:].data_ptr(), _lib.ptr(rs),
+                    cos.data_ptr(), sin.data_ptr(), bb, k, hq, hkv, d, block_table.stride(0),
+                    k_cache.shape[2], int(traditional), int(pdl), _lib.stream_ptr())
+            if rc != -2:
+                _lib.check(rc, "sg_rms_qkv_rope")
+                continue
         rc = _lib.cuda().rmlx_rms_qkv_rope(
             w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(), xs.stride(0),
             _lib.ptr(norm_w), eps, qs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),

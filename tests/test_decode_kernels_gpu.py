@@ -13,12 +13,15 @@ from rmlx_b200.reference import ops as ref
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(autouse=True, params=["mma", "scalar"])
+@pytest.fixture(autouse=True, params=["stream", "mma", "scalar"])
 def q4_path(request):
-    """Every test runs with both Q4 mat-vec implementations."""
-    D.set_q4_path(request.param)
+    """Every test runs on the weight-streaming kernels and on both per-row Q4 implementations."""
+    D.set_stream(request.param == "stream")
+    D.set_q4_path("auto" if request.param == "stream" else request.param)
     yield request.param
-    D.set_q4_path("mma")
+    D.set_q4_path("auto")
+    D.set_stream(True)
+    assert D.stream_status() == 0
 
 
 def _w(n, k, quant, dev, experts=0, seed=0):
@@ -180,6 +183,35 @@ def test_flash_decode_paged(dev, hq, hkv, hd, splits):
     a = D.flash_decode_paged(q, kc, vc, bt, sl, scale, scratch=sc)
     c = D.flash_decode_paged(q, kc, vc, bt, sl, scale, scratch=sc)
     assert torch.equal(a, c)
+
+
+@pytest.mark.parametrize("hq,hkv,hd", [(64, 4, 128), (8, 1, 128), (4, 2, 64), (40, 2, 128)])
+def test_flash_decode_cluster(dev, hq, hkv, hd, q4_path):
+    """The cluster kernel (splits merged through distributed shared memory, then per-cluster
+    partials merged by the last cluster) against the fp32 oracle, on short and long contexts."""
+    if q4_path != "stream":
+        pytest.skip("one run is enough: the kernel does not depend on the mat-vec path")
+    torch.manual_seed(13)
+    scale = 1 / math.sqrt(hd)
+    for lens in ([5000], [1, 333], [2048, 17, 700]):
+        b = len(lens)
+        kc, vc, bt = _paged_setup(dev, b, hkv, hd, lens, seed=3)
+        q = torch.randn(b, hq, hd, device=dev).to(torch.bfloat16)
+        sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+        sc = D.FlashDecodeScratch(b, hq, hkv, hd, 4, dev, max_len=bt.shape[1] * 16)
+        if sc.clusters == 0:
+            continue
+        for window in (0, 100):
+            got = D.flash_decode_paged(q, kc, vc, bt, sl, scale, scratch=sc, window=window)
+            for i, l in enumerate(lens):
+                kk = ref.gather_paged(kc, bt[i].long(), l)
+                vv = ref.gather_paged(vc, bt[i].long(), l)
+                want = ref.sdpa(q[i:i + 1].float(), kk.float(), vv.float(), scale, l - 1, window)
+                _close(got[i:i + 1], want, atol=3e-2)
+        # tickets are left at zero: a second call gives the same bits
+        a = D.flash_decode_paged(q, kc, vc, bt, sl, scale, scratch=sc)
+        c = D.flash_decode_paged(q, kc, vc, bt, sl, scale, scratch=sc)
+        assert torch.equal(a, c)
 
 
 @pytest.mark.parametrize("traditional", [False, True])
