@@ -62,7 +62,9 @@ struct XLoadBf16 {          // x (global, bf16), optionally times a per-channel 
   const __nv_bfloat16* scale_w;
   float ssq;
   __device__ __forceinline__ void operator()(int c, float (&f)[8]) {
-    const uint4 v = *reinterpret_cast<const uint4*>(x + (c << 3));
+    // L2 load: in a kernel that runs several projections back to back, x was written by other
+    // blocks of the same kernel and must not come from this SM's L1
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(x + (c << 3)));
     f[0] = bf16lo(v.x); f[1] = bf16hi(v.x); f[2] = bf16lo(v.y); f[3] = bf16hi(v.y);
     f[4] = bf16lo(v.z); f[5] = bf16hi(v.z); f[6] = bf16lo(v.w); f[7] = bf16hi(v.w);
 #pragma unroll

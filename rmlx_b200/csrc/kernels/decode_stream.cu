@@ -75,7 +75,7 @@ static int run_moe_gate_up(const void* w, const void* sc, const void* bi, const 
   P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
   P.act = static_cast<__nv_bfloat16*>(act); P.act_stride = act_stride;
   P.R = SgRouting{idx, nullptr, top_k, expert_base, experts_local};
-  P.token = 0; P.packed = 0; P.mask = 0;
+  P.token = 0; P.ntok = B; P.packed = 0; P.mask = 0;
   const int per_token = sm_count() / B > 0 ? sm_count() / B : 1;
   const int hq = I / 2;
   const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, true, top_k * hq, per_token, hq & -hq, sg_x_bytes(Q4, K, 1), 0, 1);
@@ -92,7 +92,7 @@ static int run_moe_down(const void* w, const void* sc, const void* bi, const voi
   P.N = N; P.I = I;
   P.act = static_cast<const __nv_bfloat16*>(act); P.act_stride = act_stride;
   P.R = SgRouting{idx, tw, top_k, expert_base, experts_local};
-  P.token = 0; P.nloc = 0; P.packed = 0;
+  P.token = 0; P.ntok = B; P.nloc = 0; P.packed = 0;
   P.residual = static_cast<const __nv_bfloat16*>(res); P.res_stride = res_stride;
   P.out = out; P.out_stride = out_stride;
   const int per_token = sm_count() / B > 0 ? sm_count() / B : 1;

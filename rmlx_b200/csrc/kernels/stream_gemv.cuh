@@ -27,8 +27,8 @@
 // quads with ALL their slices (or, for very long rows, one of KP column parts); its sixteen warps
 // are arranged TR x SQ: TR task rows, SQ warps striding over the slices of a task row. When SQ > 1
 // the warps of a task row hand their partial sums to the row's first warp through shared memory
-// and a per-row mbarrier; that warp adds them in a fixed order (deterministic results) and runs
-// the problem's epilogue. There is no block-wide barrier in the main loop.
+// and a per-row mbarrier (the last warp to hand over signals); that warp adds them in a fixed
+// order (deterministic results) and runs the problem's epilogue. There is no block-wide barrier in the main loop.
 //
 // Scales and biases of the 4-bit format (bf16 per 64 weights: one byte of each per unit) travel
 // through the same ring, one copy per segment. Their rows need not start on 16-byte boundaries, so
@@ -83,7 +83,8 @@ __host__ __device__ inline int sg_part_floats(int ns, int qpt, int B) { return n
 
 __host__ inline size_t sg_smem_bytes(const SgPlan& p, int B) {
   return size_t(p.ns) * p.stage_bytes + p.x_bytes + sg_part_floats(p.ns, p.qpt, B) * 4 +
-         (2 * kSgMaxStages + kSgMaxStages * kSgConsumerWarps) * 8 + kSgMaxStages * kSgMaxSeg * 8 + 256 +
+         (2 * kSgMaxStages + kSgMaxStages * kSgConsumerWarps) * 8 + kSgMaxStages * kSgConsumerWarps * 8 +
+         kSgMaxStages * kSgMaxSeg * 8 + 256 +
          kSgConsumerWarps * 64 + p.extra_bytes + 128;
 }
 
@@ -166,9 +167,17 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
 
 // mbarrier wait that looks at the abort flag first, so a block that has given up once never burns
 // another budget.
-__device__ __forceinline__ bool sg_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortf) {
+// `where` names the waiting site; the first site whose wait expires is kept beside the abort flag
+// and ends up in the status word (bits 8 and up), so a failure can be located from the host.
+__device__ __forceinline__ bool sg_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abortf,
+                                        uint32_t where = 0) {
   if (*abortf) return false;
-  return mbar_wait(bar, parity, abortf);
+  const bool ok = mbar_wait(bar, parity, abortf, 1u << 19);
+  if (!ok) atomicCAS(const_cast<uint32_t*>(abortf) + 1, 0u, where);
+  return ok;
+}
+__device__ __forceinline__ int sg_abort_status(volatile uint32_t* abortf, int code) {
+  return code | int(abortf[1] << 8);
 }
 
 // Sum over the consumer threads. `red` has one float per consumer warp; two consumer barriers.
@@ -252,7 +261,9 @@ struct SgSmem {
   float* part;          // [ns][warps][qpt][4][B]
   uint64_t* full;       // [kSgMaxStages]
   uint64_t* empty;      // [kSgMaxStages]
-  uint64_t* partbar;    // [kSgMaxStages][warps]
+  uint64_t* partbar;    // [kSgMaxStages][warps], one arrival each: the last warp to hand over signals
+  uint32_t* pcnt;       // [kSgMaxStages][warps] hand-overs counted so far, then [kSgMaxStages][warps]
+                        // the parity each hand-over barrier will complete next
   SgSegMeta* meta;      // [kSgMaxStages][kSgMaxSeg]
   volatile uint32_t* abortf;
   float* misc;          // 62 floats: inv_rms[4], red[16], free use
@@ -269,7 +280,8 @@ __device__ __forceinline__ SgSmem sg_carve(char* smem, const SgPlan& pl, int B) 
   s.full = reinterpret_cast<uint64_t*>(s.part + sg_part_floats(pl.ns, pl.qpt, B));
   s.empty = s.full + kSgMaxStages;
   s.partbar = s.empty + kSgMaxStages;
-  s.meta = reinterpret_cast<SgSegMeta*>(s.partbar + kSgMaxStages * kSgConsumerWarps);
+  s.pcnt = reinterpret_cast<uint32_t*>(s.partbar + kSgMaxStages * kSgConsumerWarps);
+  s.meta = reinterpret_cast<SgSegMeta*>(s.pcnt + 2 * kSgMaxStages * kSgConsumerWarps);
   s.abortf = reinterpret_cast<volatile uint32_t*>(s.meta + kSgMaxStages * kSgMaxSeg);
   s.misc = reinterpret_cast<float*>(const_cast<uint32_t*>(s.abortf) + 2);
   s.wscr = s.misc + 62;
@@ -299,93 +311,98 @@ struct SgSegSrc {
 //   void stage_x(SgSmem&, const SgPlan&)                 all consumer threads; ends in a barrier
 //   void epilogue(int quad, float (&v)[4][kB], SgSmem&)  one lane per finished quad
 //   void cta_done(SgSmem&)                               all consumer threads, once
+// Position in the ring; it survives from one problem to the next when several run in one kernel.
+struct SgRingPos {
+  int s;              // slot of the next stage
+  uint32_t round;     // how often the ring has wrapped
+  uint32_t spare;
+  int ns;             // slots
+  int slot_bytes;     // distance between slots
+  uint32_t tag;       // names the running problem in wait-site codes
+};
+
+// Producer side of one problem: issues the bulk copies of this block's stages, in order. Runs in
+// one warp. Returns false when a wait expired.
 template <class P, int LW>
-__global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, int* status) {
-  extern __shared__ char smem_raw[];
-  constexpr int B = P::kB;
-  constexpr int QPT = 32 / LW;
-  SgSmem sm = sg_carve(smem_raw, pl, B);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < pl.ns; ++s) {
-      mbar_init(sm.full + s, 1);
-      mbar_init(sm.empty + s, kSgConsumerWarps);
-      for (int t = 0; t < kSgConsumerWarps; ++t)
-        mbar_init(sm.partbar + s * kSgConsumerWarps + t, pl.SQ > 1 ? pl.SQ - 1 : 1);
-    }
-    *sm.abortf = 0u;
-    fence_mbar_init();
-  }
-  __syncthreads();
-  pdl_launch_dependents();
-  int q0, q1;
-  prob.cta_range(pl, q0, q1);
+__device__ __forceinline__ bool sg_produce(P& prob, const SgPlan& pl, SgSmem& sm, SgRingPos& rp, int q0, int q1) {
+  const int lane = threadIdx.x & 31;
   const int myq = q1 > q0 ? q1 - q0 : 0;
   const int nrb = (myq + pl.QS - 1) / pl.QS;       // row blocks of this block
   const int nst = nrb * pl.KP;
-
-  if (warp == kSgConsumerWarps) {
-    // ------------------------------------------------------------------ producer warp
-    if (P::kWeightsNeedWait) pdl_wait();
-    prob.init(true);
-    const int nseg = pl.pairs ? 2 : prob.nslots();
-    int issued = 0, s = 0, use = 0;                // ring slot and how often it has been used
-    for (int i = 0; i < nst; ++i) {
-      if (use > 0 && !sg_wait(sm.empty + s, (use - 1) & 1, sm.abortf)) break;
-      const int rb = i / pl.KP, kp = i - rb * pl.KP;
-      const int sq0 = q0 + rb * pl.QS, nq = min(pl.QS, q1 - sq0);
-      char* stage = sm.ring + size_t(s) * pl.stage_bytes;
-      uint32_t bytes = 0;
-      if (lane < nseg) {
-        const SgSegSrc src = prob.seg(pl, sq0, nq, lane);
-        SgSegMeta m{0, 0, uint16_t(src.rows), 0};
-        if (src.rows > 0) {
-          char* dst = stage + size_t(lane) * pl.w_seg_bytes;
-          if (pl.KP == 1) {
-            const uint32_t n = uint32_t(src.rows) * uint32_t(pl.units) * 16u;
-            bulk_g2s(dst, src.w, n, sm.full + s);
-            bytes += n;
-          } else {
-            const int u0 = kp * pl.spp * LW;
-            const uint32_t n = uint32_t(min(pl.spp * LW, pl.units - u0)) * 16u;
-            for (int r = 0; r < src.rows; ++r)
-              bulk_g2s(dst + size_t(r) * pl.w_row_bytes, src.w + (size_t(r) * pl.units + u0) * 16, n, sm.full + s);
-            bytes += n * uint32_t(src.rows);
-          }
-          if (P::kQ4) {
-            const uintptr_t a = reinterpret_cast<uintptr_t>(src.sc), b2 = reinterpret_cast<uintptr_t>(src.bi);
-            const uint32_t span = uint32_t(src.rows) * uint32_t(pl.units);
-            const uintptr_t alo = a & ~uintptr_t(15), ahi = (a + span + 15) & ~uintptr_t(15);
-            const uintptr_t blo = b2 & ~uintptr_t(15), bhi = (b2 + span + 15) & ~uintptr_t(15);
-            char* ax = stage + pl.aux_off + size_t(lane) * 2 * pl.aux_seg_bytes;
-            bulk_g2s(ax, reinterpret_cast<const void*>(alo), uint32_t(ahi - alo), sm.full + s);
-            bulk_g2s(ax + pl.aux_seg_bytes, reinterpret_cast<const void*>(blo), uint32_t(bhi - blo), sm.full + s);
-            bytes += uint32_t(ahi - alo) + uint32_t(bhi - blo);
-            m.mis_sc = uint16_t(a & 15u); m.mis_bi = uint16_t(b2 & 15u);
-          }
+  const int nseg = pl.pairs ? 2 : prob.nslots();
+  for (int i = 0; i < nst; ++i) {
+    const int s = rp.s;
+    if (rp.round > 0 && !sg_wait(sm.empty + s, (rp.round - 1) & 1, sm.abortf, rp.tag * 16 + 1)) return false;
+    const int rb = i / pl.KP, kp = i - rb * pl.KP;
+    const int sq0 = q0 + rb * pl.QS, nq = min(pl.QS, q1 - sq0);
+    char* stage = sm.ring + size_t(s) * rp.slot_bytes;
+    uint32_t bytes = 0;
+    if (lane < nseg) {
+      const SgSegSrc src = prob.seg(pl, sq0, nq, lane);
+      SgSegMeta m{0, 0, uint16_t(src.rows), 0};
+      if (src.rows > 0) {
+        char* dst = stage + size_t(lane) * pl.w_seg_bytes;
+        if (pl.KP == 1) {
+          const uint32_t n = uint32_t(src.rows) * uint32_t(pl.units) * 16u;
+          bulk_g2s(dst, src.w, n, sm.full + s);
+          bytes += n;
+        } else {
+          const int u0 = kp * pl.spp * LW;
+          const uint32_t n = uint32_t(min(pl.spp * LW, pl.units - u0)) * 16u;
+          for (int r = 0; r < src.rows; ++r)
+            bulk_g2s(dst + size_t(r) * pl.w_row_bytes, src.w + (size_t(r) * pl.units + u0) * 16, n, sm.full + s);
+          bytes += n * uint32_t(src.rows);
         }
-        sm.meta[s * kSgMaxSeg + lane] = m;
+        if (P::kQ4) {
+          const uintptr_t a = reinterpret_cast<uintptr_t>(src.sc), b2 = reinterpret_cast<uintptr_t>(src.bi);
+          const uint32_t span = uint32_t(src.rows) * uint32_t(pl.units);
+          const uintptr_t alo = a & ~uintptr_t(15), ahi = (a + span + 15) & ~uintptr_t(15);
+          const uintptr_t blo = b2 & ~uintptr_t(15), bhi = (b2 + span + 15) & ~uintptr_t(15);
+          char* ax = stage + pl.aux_off + size_t(lane) * 2 * pl.aux_seg_bytes;
+          bulk_g2s(ax, reinterpret_cast<const void*>(alo), uint32_t(ahi - alo), sm.full + s);
+          bulk_g2s(ax + pl.aux_seg_bytes, reinterpret_cast<const void*>(blo), uint32_t(bhi - blo), sm.full + s);
+          bytes += uint32_t(ahi - alo) + uint32_t(bhi - blo);
+          m.mis_sc = uint16_t(a & 15u); m.mis_bi = uint16_t(b2 & 15u);
+        }
       }
-      bytes = __reduce_add_sync(0xffffffffu, bytes);
-      __syncwarp();
-      if (lane == 0) mbar_arrive_expect_tx(sm.full + s, bytes);
-      issued = i + 1;
-      if (++s == pl.ns) { s = 0; ++use; }
+      sm.meta[s * kSgMaxSeg + lane] = m;
     }
-    // Copies still in flight target this block's shared memory: wait for them before leaving.
-    if (*sm.abortf) {
-      for (int i = max(0, issued - pl.ns); i < issued; ++i)
-        mbar_wait(sm.full + (i % pl.ns), (i / pl.ns) & 1, sm.abortf, 1u << 16);
-      if (lane == 0) atomicExch(status, kStatusMbarTimeout);
-    }
-    return;
+    bytes = __reduce_add_sync(0xffffffffu, bytes);
+    __syncwarp();
+    if (lane == 0) mbar_arrive_expect_tx(sm.full + s, bytes);
+    if (++rp.s == rp.ns) { rp.s = 0; ++rp.round; }
   }
+  return true;
+}
 
-  // -------------------------------------------------------------------- consumer warps
-  pdl_wait();
-  prob.init(false);
+// After a wait has expired: the copies of the last `ns` stages may still be in flight towards this
+// block's shared memory; wait for them (bounded) before the block leaves.
+__device__ __forceinline__ void sg_drain(SgSmem& sm, const SgRingPos& rp) {
+  for (int k = 0; k < rp.ns; ++k) {
+    // slot k was last armed in round rp.round (k < rp.s) or rp.round - 1
+    const int r = int(rp.round) - (k < rp.s ? 0 : 1);
+    if (r >= 0) mbar_wait(sm.full + k, uint32_t(r) & 1u, sm.abortf, 1u << 16);
+  }
+}
+
+// Hand-over barriers and counters of a block: one thread, once, before any use.
+__device__ __forceinline__ void sg_init_handover(SgSmem& sm, int ns) {
+  for (int i = 0; i < ns * kSgConsumerWarps; ++i) {
+    mbar_init(sm.partbar + i, 1);
+    sm.pcnt[i] = 0u;
+    sm.pcnt[kSgMaxStages * kSgConsumerWarps + i] = 0u;
+  }
+}
+
+// Consumer side of one problem: all consumer warps. The activations are already staged.
+template <class P, int LW>
+__device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm, SgRingPos& rp, int q0, int q1) {
+  constexpr int B = P::kB;
+  constexpr int QPT = 32 / LW;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int myq = q1 > q0 ? q1 - q0 : 0;
+  const int nrb = (myq + pl.QS - 1) / pl.QS;
   const int nslots = prob.nslots();
-  prob.stage_x(sm, pl);
   const int tr = warp / pl.SQ, sq = warp - tr * pl.SQ;
   const int sub = lane / LW, l = lane - sub * LW;
   const int xunits = prob.xunits();
@@ -398,9 +415,6 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
   const uint32_t w_lo_off = uint32_t(row_lo) * rowb, w_hi_off = (pl.pairs ? uint32_t(pl.w_seg_bytes) : 0u) + uint32_t(row_hi) * rowb;
   const uint32_t a_lo_off = uint32_t(pl.aux_off) + uint32_t(row_lo) * units;
   const uint32_t a_hi_off = uint32_t(pl.aux_off) + (pl.pairs ? 2u * uint32_t(pl.aux_seg_bytes) : 0u) + uint32_t(row_hi) * units;
-  uint32_t pphase = 0;                              // per ring slot: parity of its next hand-over
-  int s = 0;
-  uint32_t fphase = 0;                              // parity of the ring's current round
 
   for (int rb = 0; rb < nrb; ++rb) {
     float acc[4][B];
@@ -412,10 +426,11 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
     const bool qvalid = sq0 + qi < q1;
     int s_used = 0;
     for (int kp = 0; kp < pl.KP; ++kp) {
+      const int s = rp.s;
       s_used = s;
-      const bool ok = sg_wait(sm.full + s, fphase, sm.abortf);
+      const bool ok = sg_wait(sm.full + s, rp.round & 1u, sm.abortf, rp.tag * 16 + 2);
       if (ok && qvalid) {
-        const char* stage = sm.ring + uint32_t(s) * uint32_t(pl.stage_bytes);
+        const char* stage = sm.ring + uint32_t(s) * uint32_t(rp.slot_bytes);
         const int s_lo = pl.KP == 1 ? 0 : kp * pl.spp, s_hi = pl.KP == 1 ? nsl : min(pl.spl, s_lo + pl.spp);
         // two slices per trip: the second one's shared-memory loads overlap the first one's math
         auto load = [&](int sl, SgTask& t) {
@@ -464,7 +479,7 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
       }
       __syncwarp();
       if (kp + 1 < pl.KP && lane == 0) mbar_arrive(sm.empty + s);   // the last part is released after the hand-over
-      if (++s == pl.ns) { s = 0; fphase ^= 1u; }
+      if (++rp.s == rp.ns) { rp.s = 0; ++rp.round; }
     }
     // ---- lane-group totals, hand-over to the task row's first warp, epilogue
 #pragma unroll
@@ -488,9 +503,24 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
             for (int b = 0; b < B; ++b) pp[r * B + b] = acc[r][b];
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(sm.partbar + sh * kSgConsumerWarps + tr);
+        if (lane == 0) {
+          // the last of the SQ - 1 warps to hand over signals the task row's first warp
+          __threadfence_block();
+          uint32_t* cnt = sm.pcnt + sh * kSgConsumerWarps + tr;
+          if (atomicAdd(cnt, 1u) == uint32_t(pl.SQ - 2)) {
+            *cnt = 0u;
+            __threadfence_block();
+            mbar_arrive(sm.partbar + sh * kSgConsumerWarps + tr);
+          }
+        }
       } else {
-        sg_wait(sm.partbar + sh * kSgConsumerWarps + tr, (pphase >> sh) & 1u, sm.abortf);
+        // the barrier's parity lives in shared memory: which warp owns a task row changes from
+        // one problem to the next
+        uint32_t* ppar = sm.pcnt + kSgMaxStages * kSgConsumerWarps + sh * kSgConsumerWarps + tr;
+        const uint32_t par = *ppar;
+        sg_wait(sm.partbar + sh * kSgConsumerWarps + tr, par & 1u, sm.abortf, rp.tag * 16 + 3);
+        __syncwarp();
+        if (lane == 0) *ppar = par ^ 1u;
         for (int k = 1; k < pl.SQ; ++k) {
           const float* pp = part + (((warp + k) * QPT + sub) * 4) * B;
 #pragma unroll
@@ -499,14 +529,47 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
             for (int b = 0; b < B; ++b) acc[r][b] += pp[r * B + b];
         }
       }
-      pphase ^= 1u << sh;
     }
     if (sq == 0 && qvalid && l == 0) prob.epilogue(sq0 + qi, acc, sm);
     __syncwarp();
     if (lane == 0) mbar_arrive(sm.empty + sh);
   }
+}
+
+template <class P, int LW>
+__global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, int* status) {
+  extern __shared__ char smem_raw[];
+  SgSmem sm = sg_carve(smem_raw, pl, P::kB);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < pl.ns; ++s) {
+      mbar_init(sm.full + s, 1);
+      mbar_init(sm.empty + s, kSgConsumerWarps);
+    }
+    sg_init_handover(sm, pl.ns);
+    sm.abortf[0] = 0u; sm.abortf[1] = 0u;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  int q0, q1;
+  prob.cta_range(pl, q0, q1);
+  SgRingPos rp{0, 0u, 0u, pl.ns, pl.stage_bytes, 0u};
+  if (warp == kSgConsumerWarps) {
+    if (P::kWeightsNeedWait) pdl_wait();
+    prob.init(true);
+    if (!sg_produce<P, LW>(prob, pl, sm, rp, q0, q1)) {
+      sg_drain(sm, rp);
+      if (lane == 0) atomicExch(status, sg_abort_status(sm.abortf, kStatusMbarTimeout));
+    }
+    return;
+  }
+  pdl_wait();
+  prob.init(false);
+  prob.stage_x(sm, pl);
+  sg_consume<P, LW>(prob, pl, sm, rp, q0, q1);
   prob.cta_done(sm);
-  if (*sm.abortf && threadIdx.x == 0) atomicExch(status, kStatusMbarTimeout);
+  if (*sm.abortf && threadIdx.x == 0) atomicExch(status, sg_abort_status(sm.abortf, kStatusMbarTimeout));
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -54,7 +54,7 @@ struct SgDense {
         const int n = quad * 4 + r;
         if (n < N) {
           float o = v[r][b] * inv;
-          if (residual) o += __bfloat162float(residual[size_t(b) * res_stride + n]);
+          if (residual) o += bf16lo(__ldcg(reinterpret_cast<const uint16_t*>(residual + size_t(b) * res_stride + n)));
           if (OUT_F32) static_cast<float*>(out)[size_t(b) * out_stride + n] = o;
           else static_cast<__nv_bfloat16*>(out)[size_t(b) * out_stride + n] = __float2bfloat16_rn(o);
         }
@@ -233,13 +233,14 @@ struct SgMoeGateUp {
   const __nv_bfloat16* norm_w; float eps;
   __nv_bfloat16* act; int act_stride;   // [tokens*top_k, I]
   SgRouting R;
-  int token;
+  int token, ntok;
   unsigned long long packed; uint32_t mask;
 
   __device__ void cta_range(const SgPlan& pl, int& q0, int& q1) {
     token = blockIdx.x / pl.grid;
     const int c = blockIdx.x - token * pl.grid;
     q0 = c * pl.qpc; q1 = min(pl.quads, q0 + pl.qpc);
+    if (token >= ntok) { token = 0; q0 = q1 = 0; }
   }
   __device__ void init(bool) { R.load(token, packed, mask); }
   __device__ int nslots() const { return 1; }
@@ -272,7 +273,7 @@ struct XLoadMoeAct {
   const float* w_of;          // shared memory: virtual slot -> routing weight
   __device__ __forceinline__ void operator()(int c, float (&f)[8]) {
     const int vs = c / cps, cc = c - vs * cps;
-    const uint4 v = *reinterpret_cast<const uint4*>(act + size_t(slot_of[vs]) * act_stride + (cc << 3));
+    const uint4 v = __ldcg(reinterpret_cast<const uint4*>(act + size_t(slot_of[vs]) * act_stride + (cc << 3)));
     const float w = w_of[vs];
     f[0] = bf16lo(v.x) * w; f[1] = bf16hi(v.x) * w; f[2] = bf16lo(v.y) * w; f[3] = bf16hi(v.y) * w;
     f[4] = bf16lo(v.z) * w; f[5] = bf16hi(v.z) * w; f[6] = bf16lo(v.w) * w; f[7] = bf16hi(v.w) * w;
@@ -290,13 +291,14 @@ struct SgMoeDownBase {
   int N, I;
   const __nv_bfloat16* act; int act_stride;   // [tokens*top_k, I]
   SgRouting R;
-  int token, nloc;
+  int token, ntok, nloc;
   unsigned long long packed;                   // local expert of virtual slot v in byte v
 
   __device__ void cta_range(const SgPlan& pl, int& q0, int& q1) {
     token = blockIdx.x / pl.grid;
     const int c = blockIdx.x - token * pl.grid;
     q0 = c * pl.qpc; q1 = min(pl.quads, q0 + pl.qpc);
+    if (token >= ntok) { token = 0; q0 = q1 = 0; }
   }
   __device__ void load_routing() {
     packed = 0ull; nloc = 0;
@@ -345,7 +347,7 @@ struct SgMoeDown : SgMoeDownBase<Q4> {
       const int n = quad * 4 + r;
       if (n < this->N) {
         float o = v[r][0];
-        if (residual) o += __bfloat162float(residual[size_t(b) * res_stride + n]);
+        if (residual) o += bf16lo(__ldcg(reinterpret_cast<const uint16_t*>(residual + size_t(b) * res_stride + n)));
         if (OUT_F32) static_cast<float*>(out)[size_t(b) * out_stride + n] = o;
         else static_cast<__nv_bfloat16*>(out)[size_t(b) * out_stride + n] = __float2bfloat16_rn(o);
       }

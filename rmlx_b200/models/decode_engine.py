@@ -35,7 +35,7 @@ from .transformer import TransformerModel
 class CachedDecode:
     def __init__(self, model: TransformerModel, cache: PagedKvCache, max_batch: int = 1,
                  use_graph: bool = True, pdl: bool = True, splits: Optional[int] = None,
-                 comm=None, greedy: bool = True):
+                 comm=None, greedy: bool = True, step_kernel: Optional[bool] = None):
         if model.device.type != "cuda":
             raise _lib.NativeError("CachedDecode runs this package's CUDA kernels; on CPU use "
                                    "TransformerModel.forward")
@@ -84,6 +84,15 @@ class CachedDecode:
         self.seq_ids: List[int] = []
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._launches_per_step = 0
+        # batch 1 on one GPU: the whole step is one persistent kernel when the model fits it
+        self.step_kernel = None
+        from .step_kernel import DecodeStepKernel
+        if step_kernel is not False and DecodeStepKernel.supported(model, max_batch, comm):
+            sk = DecodeStepKernel(self)
+            if sk.ok:
+                self.step_kernel = sk
+        if step_kernel and self.step_kernel is None:
+            raise _lib.NativeError("the persistent step kernel does not take this model / batch")
 
     # ------------------------------------------------------------------ binding
     def bind(self, seq_ids: Sequence[int], last_tokens: Sequence[int]) -> None:
@@ -118,6 +127,10 @@ class CachedDecode:
         eps, pdl = cfg.rms_norm_eps, self.pdl
         tp = self.comm is not None and m.layout.world > 1
         n0 = _lib.launch_count()
+        if self.step_kernel is not None:
+            self.step_kernel.launch()
+            self._finish_step(pdl=False, n0=n0)
+            return
         D.embedding(w.embed, self.tokens, out=self.h, pdl=False)
         h, h2 = self.h, self.h2
         for li, lw in enumerate(w.layers):
@@ -162,6 +175,13 @@ class CachedDecode:
         # vocabulary-parallel LM head: this rank's logits occupy the first vocab_local columns
         logits = self.logits[:, :self.vocab_local] if sharded_vocab else self.logits
         D.rms_gemv(h, w.lm_head, w.final_norm, eps, out=logits, pdl=pdl)
+        self._finish_step(pdl=pdl, n0=n0, logits=logits, sharded_vocab=sharded_vocab)
+
+    def _finish_step(self, pdl: bool, n0: int, logits=None, sharded_vocab: bool = False) -> None:
+        """Greedy sampling and the advance kernel that feeds the token back."""
+        w = self.model.w
+        if logits is None:
+            logits = self.logits
         if self.greedy:
             if sharded_vocab:
                 self.comm.argmax(logits, w.vocab_base, self.next_tokens, pdl=pdl)

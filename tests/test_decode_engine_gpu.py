@@ -147,3 +147,53 @@ def test_decode_engine_ten_rows_in_chunks(dev):
         want = torch.cat([oracle.forward(torch.tensor([feed[s]]), oc, [s], last_only=True) for s in range(10)])
     rel = (got - want).abs().max().item() / want.abs().max().item()
     assert rel < 5e-2, rel
+
+
+@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("use_graph", [False, True])
+@pytest.mark.parametrize("ctx", [16, 150])
+def test_step_kernel_matches_oracle(dev, quant, use_graph, ctx):
+    """The persistent one-kernel decode step (batch 1, routed-expert layers) against the fp32
+    oracle on the same weights, and against the chain-of-kernels engine."""
+    from rmlx_b200.models.step_kernel import DecodeStepKernel
+    cfg = tiny_moe_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 2), device=dev, quant=quant))
+    oracle = _oracle_from(model)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, cfg.vocab_size, (ctx,), generator=g)
+    steps = 6
+    oc = oracle.new_cache(16, max_seqs=1)
+    oc.add_sequence(0)
+    lg = oracle.forward(prompt, oc, [0], last_only=True)
+    want_logits, toks = [], []
+    tok = int(lg[0].argmax())
+    for _ in range(steps):
+        toks.append(tok)
+        lg = oracle.forward(torch.tensor([tok]), oc, [0], last_only=True)
+        want_logits.append(lg[0].clone())
+        tok = int(lg[0].argmax())
+    engines = []
+    for sk in (True, False):
+        cache = model.new_cache(16, max_seqs=1)
+        cache.add_sequence(0)
+        model.forward(prompt.to(dev), cache, [0], last_only=True)
+        eng = CachedDecode(model, cache, max_batch=1, use_graph=use_graph, step_kernel=sk)
+        assert (eng.step_kernel is not None) == sk
+        eng.bind([0], [toks[0]])
+        eng.reserve(steps + 1)
+        engines.append(eng)
+    for i in range(steps):
+        outs = []
+        for eng in engines:
+            eng.tokens[0] = toks[i]
+            eng.step()
+            torch.cuda.synchronize()
+            outs.append(eng.logits[0].cpu().clone())
+        st = DecodeStepKernel.status()
+        assert st == 0, hex(st)
+        mag = want_logits[i].abs().max().item()
+        for got in outs:
+            err = (got - want_logits[i]).abs().max().item()
+            assert err <= 5e-2 * mag + 2e-2, f"step {i}: err {err} mag {mag}"
+        assert (outs[0] - outs[1]).abs().max().item() <= 3e-2 * mag + 1e-2
+    assert engines[0].cache.seq_len(0) == ctx + steps
