@@ -80,6 +80,7 @@ struct StepParams {
   float* fd_part_ml;                     // [tiles, S, 16, 2]
   float* logits;                         // [V] fp32
   unsigned int* grid_bar;                // zero on entry
+  unsigned long long* trace;             // optional: block 0 stamps the global timer at phase ends [layers][32]
   int* status;
   // shared-memory layout
   int ns, slot_bytes, x_bytes, part_floats, extra_bytes;
@@ -89,41 +90,38 @@ static __device__ int g_step_status = 0;
 
 struct StepSmem {
   SgSmem sm;
-  float* fdbuf;                          // [4][32 lanes][NT*4 + 4] merge buffer of the attention phase
-  volatile uint32_t* go;                 // producer gate: events passed by the consumers
-  int* r_idx;                            // [8] routing result of this token
-  float* r_w;                            // [8]
+  float* fdbuf;                          // attention phase: the Q tile, then the merge buffer
 };
+
+__host__ __device__ inline int step_fdbuf_bytes(int HD) {
+  // merge buffer [4 page slots][2 halves][32 lanes][NT/2 * 4 + 4] floats; the Q tile (16 padded rows) fits in it
+  return 4 * 2 * 32 * (HD / 16 * 4 + 4) * 4;
+}
 
 __device__ __forceinline__ StepSmem step_carve(char* smem, const StepParams& p) {
   StepSmem t;
   char* base = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem) + 127) & ~uintptr_t(127));
   SgSmem& s = t.sm;
-  s.ring = base;
+  s.c = reinterpret_cast<SgCtl*>(base);
+  s.ring = base + sg_ctl_bytes();
   s.xs = s.ring + size_t(p.ns) * p.slot_bytes;
   s.part = reinterpret_cast<float*>(s.xs + p.x_bytes);
-  s.full = reinterpret_cast<uint64_t*>(s.part + p.part_floats);
-  s.empty = s.full + kSgMaxStages;
-  s.partbar = s.empty + kSgMaxStages;
-  s.pcnt = reinterpret_cast<uint32_t*>(s.partbar + kSgMaxStages * kSgConsumerWarps);
-  s.meta = reinterpret_cast<SgSegMeta*>(s.pcnt + 2 * kSgMaxStages * kSgConsumerWarps);
-  s.abortf = reinterpret_cast<volatile uint32_t*>(s.meta + kSgMaxStages * kSgMaxSeg);
-  s.misc = reinterpret_cast<float*>(const_cast<uint32_t*>(s.abortf) + 2);
-  s.wscr = s.misc + 62;
-  s.extra = reinterpret_cast<char*>(s.wscr + kSgConsumerWarps * 16);
-  char* q = s.extra + p.extra_bytes;
-  t.go = reinterpret_cast<volatile uint32_t*>(q);
-  t.r_idx = reinterpret_cast<int*>(q + 16);
-  t.r_w = reinterpret_cast<float*>(q + 48);
-  t.fdbuf = reinterpret_cast<float*>(q + 128);
+  s.extra = reinterpret_cast<char*>(s.part + p.part_floats);
+  t.fdbuf = reinterpret_cast<float*>(s.extra + p.extra_bytes);
   return t;
 }
 
 __host__ inline size_t step_smem_bytes(const StepParams& p, int HD) {
-  return size_t(p.ns) * p.slot_bytes + p.x_bytes + size_t(p.part_floats) * 4 +
-         (2 * kSgMaxStages + kSgMaxStages * kSgConsumerWarps) * 8 + kSgMaxStages * kSgConsumerWarps * 8 +
-         kSgMaxStages * kSgMaxSeg * 8 + 256 +
-         kSgConsumerWarps * 64 + p.extra_bytes + 128 + size_t(4) * 32 * (HD / 8 * 4 + 4) * 4 + 256;
+  return size_t(sg_ctl_bytes()) + size_t(p.ns) * p.slot_bytes + p.x_bytes + size_t(p.part_floats) * 4 +
+         p.extra_bytes + step_fdbuf_bytes(HD) + 256;
+}
+
+__device__ __forceinline__ void step_stamp(const StepParams& p, int layer, int k) {
+  if (p.trace && blockIdx.x == 0 && threadIdx.x == 0) {
+    unsigned long long tm;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(tm));
+    p.trace[layer * 32 + k] = tm;
+  }
 }
 
 // ---- grid barrier: monotonic counter, bounded spin, consumer warps only ------------------------
@@ -133,13 +131,13 @@ __device__ __forceinline__ void step_grid_sync(const StepParams& p, StepSmem& t,
   if (threadIdx.x == 0) {
     __threadfence();
     atomicAdd(p.grid_bar, 1u);
-    if (!*t.sm.abortf) {
+    if (!*t.sm.c->abortf) {
       bool ok = false;
       for (uint32_t i = 0; i < kPeerPollLimit; ++i) {
         if (static_cast<int32_t>(ld_acquire_sys(p.grid_bar) - target) >= 0) { ok = true; break; }
         if (i > 32) __nanosleep(i > 4096 ? 128 : 20);
       }
-      if (!ok) { *t.sm.abortf = 1u; atomicCAS(const_cast<uint32_t*>(t.sm.abortf) + 1, 0u, target & 0xffffu | 0x50000u); }
+      if (!ok) { *t.sm.c->abortf = 1u; atomicCAS(const_cast<uint32_t*>(t.sm.c->abortf) + 1, 0u, target & 0xffffu | 0x50000u); }
     }
     __threadfence();
   }
@@ -151,18 +149,18 @@ __device__ __forceinline__ void step_signal(StepSmem& t) {
   if (threadIdx.x == 0) {
     asm volatile("fence.proxy.async;" ::: "memory");   // our generic writes before the producer's bulk reads
     __threadfence_block();
-    *t.go = *t.go + 1u;
+    t.sm.c->go = t.sm.c->go + 1u;
   }
 }
 __device__ __forceinline__ bool step_wait_go(StepSmem& t, uint32_t want) {
   // the longest budget of all: when something upstream is stuck, that wait should be the one that reports
   for (uint32_t i = 0; i < (kPeerPollLimit << 4); ++i) {
-    if (*t.go >= want) { __threadfence_block(); return true; }
-    if (*t.sm.abortf) return false;
+    if (t.sm.c->go >= want) { __threadfence_block(); return true; }
+    if (*t.sm.c->abortf) return false;
     if (i > 16) __nanosleep(40);
   }
-  *t.sm.abortf = 1u;
-  atomicCAS(const_cast<uint32_t*>(t.sm.abortf) + 1, 0u, want | 0x40000u);
+  *t.sm.c->abortf = 1u;
+  atomicCAS(const_cast<uint32_t*>(t.sm.c->abortf) + 1, 0u, want | 0x40000u);
   return false;
 }
 
@@ -195,7 +193,7 @@ __device__ __forceinline__ bool step_fd_produce(const StepParams& p, const StepL
   const uint32_t page_bytes = uint32_t(kStPage) * p.HD * 2;
   for (int pg = f.pg0; pg < f.pg1; pg += kStFdWarps) {
     const int s = rp.s;
-    if (rp.round > 0 && !sg_wait(t.sm.empty + s, (rp.round - 1) & 1, t.sm.abortf, 0x71)) return false;
+    if (rp.round > 0 && !sg_wait(t.sm.c->empty + s, (rp.round - 1) & 1, t.sm.c->abortf, 0x71)) return false;
     char* stage = t.sm.ring + size_t(s) * rp.slot_bytes;
     uint32_t bytes = 0;
     const int j = lane >> 1, kv = lane & 1;
@@ -203,11 +201,11 @@ __device__ __forceinline__ bool step_fd_produce(const StepParams& p, const StepL
       const int blk = __ldcg(p.block_table + pg + j);
       const char* src = reinterpret_cast<const char*>(kv ? L.v_cache : L.k_cache) +
                         (size_t(blk) * p.Hkv + f.kvh) * page_bytes;
-      bulk_g2s(stage + (size_t(j) * 2 + kv) * page_bytes, src, page_bytes, t.sm.full + s);
+      bulk_g2s(stage + (size_t(j) * 2 + kv) * page_bytes, src, page_bytes, t.sm.c->full + s);
       bytes = page_bytes;
     }
     bytes = __reduce_add_sync(0xffffffffu, bytes);
-    if (lane == 0) mbar_arrive_expect_tx(t.sm.full + s, bytes);
+    if (lane == 0) mbar_arrive_expect_tx(t.sm.c->full + s, bytes);
     if (++rp.s == rp.ns) { rp.s = 0; ++rp.round; }
   }
   return true;
@@ -229,53 +227,54 @@ __device__ __forceinline__ void st_mma(float (&d)[4], const uint32_t (&a)[4], ui
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Consumers: warps 0..7 take one page per stage (online softmax over their pages), then the eight
-// warps' states are merged pairwise through a small buffer and warp 0 writes the split's partial.
-// The pages sit in the ring unswizzled (bulk copies): the ldmatrix bank conflicts are accepted, a
-// warp handles one or two pages per step.
+// Consumers: a KV page of a stage is shared by two warps; both form the 16 x 16 score tile, each
+// accumulates one half of the head dimension (a warp's state then fits the kernel's 96 registers;
+// the query tile stays in shared memory and is re-read per k-step). After the split's pages the
+// eight page slots are merged pairwise through a small buffer and slot 0's warps write the split's
+// partial. The pages sit in the ring unswizzled (bulk copies): the ldmatrix bank conflicts are
+// accepted, a warp handles one or two pages per step.
 template <int HD>
 __device__ __forceinline__ void step_fd_consume(const StepParams& p, StepSmem& t, SgRingPos& rp,
                                                 const FdSplit& f) {
-  constexpr int KS = HD / 16, NT = HD / 8;
+  constexpr int KS = HD / 16, NTH = HD / 16;          // k-steps; n-tiles of this warp's half
   constexpr int PAGE_BYTES = kStPage * HD * 2;
+  constexpr int QROW = HD * 2 + 16;                   // padded row of the Q tile (conflict-free ldmatrix)
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, tq = lane & 3;
+  const int slot = warp >> 1, half = warp & 1;        // page slot of a stage, half of the head dimension
   const int G = p.Hq / p.Hkv;
-  float o[NT][4];
-#pragma unroll
-  for (int j = 0; j < NT; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  uint32_t qa[KS][4];
-  if (warp < kStFdWarps && f.on) {
-    const int h0 = f.gt * 16 + g, h1 = h0 + 8;
-    const __nv_bfloat16* q0 = p.q + (size_t(f.kvh) * G + h0) * HD;
-    const __nv_bfloat16* q1 = p.q + (size_t(f.kvh) * G + h1) * HD;
-    const bool v0 = h0 < G, v1 = h1 < G;
-#pragma unroll
-    for (int ks = 0; ks < KS; ++ks) {
-      const int d = ks * 16 + tq * 2;
-      qa[ks][0] = v0 ? __ldcg(reinterpret_cast<const uint32_t*>(q0 + d)) : 0u;
-      qa[ks][1] = v1 ? __ldcg(reinterpret_cast<const uint32_t*>(q1 + d)) : 0u;
-      qa[ks][2] = v0 ? __ldcg(reinterpret_cast<const uint32_t*>(q0 + d + 8)) : 0u;
-      qa[ks][3] = v1 ? __ldcg(reinterpret_cast<const uint32_t*>(q1 + d + 8)) : 0u;
-    }
+  // ---- Q tile -> shared memory (rows beyond the group are zero)
+  char* qs = reinterpret_cast<char*>(t.fdbuf);
+  for (int i = threadIdx.x; i < 16 * (HD / 8); i += kSgConsumers) {
+    const int row = i / (HD / 8), c = i - row * (HD / 8);
+    const int h = f.gt * 16 + row;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (f.on && h < G) v = __ldcg(reinterpret_cast<const uint4*>(p.q + (size_t(f.kvh) * G + h) * HD) + c);
+    *reinterpret_cast<uint4*>(qs + row * QROW + c * 16) = v;
   }
+  sg_consumer_sync();
+  float o[NTH][4];
+#pragma unroll
+  for (int j = 0; j < NTH; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+  const uint32_t qbase = smem_u32(qs) + (lane & 15) * QROW + (lane >> 4) * 16;
   for (int pg = f.pg0; pg < f.pg1; pg += kStFdWarps) {
     const int s = rp.s;
-    const bool ok = sg_wait(t.sm.full + s, rp.round & 1u, t.sm.abortf, 0x72);
-    const int mypg = pg + warp;
-    if (ok && warp < kStFdWarps && mypg < f.pg1) {
-      const uint32_t kbase = smem_u32(t.sm.ring + size_t(s) * rp.slot_bytes + size_t(warp) * 2 * PAGE_BYTES);
+    const bool ok = sg_wait(t.sm.c->full + s, rp.round & 1u, t.sm.c->abortf, 0x72);
+    const int mypg = pg + slot;
+    if (ok && mypg < f.pg1) {
+      const uint32_t kbase = smem_u32(t.sm.ring + size_t(s) * rp.slot_bytes + size_t(slot) * 2 * PAGE_BYTES);
       const uint32_t vbase = kbase + PAGE_BYTES;
       float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         const int mi = lane >> 3, r = lane & 7;
         const int tok = (mi >> 1) * 8 + r, c = 2 * ks + (mi & 1);
-        uint32_t kb[4];
+        uint32_t qa[4], kb[4];
+        st_ldmatrix_x4(qa, qbase + ks * 32);
         st_ldmatrix_x4(kb, kbase + tok * (HD * 2) + (c << 4));
-        st_mma(s0, qa[ks], kb[0], kb[1]);
-        st_mma(s1, qa[ks], kb[2], kb[3]);
+        st_mma(s0, qa, kb[0], kb[1]);
+        st_mma(s1, qa, kb[2], kb[3]);
       }
       const int tok0 = mypg * kStPage + tq * 2;
       float sv[8] = {s0[0], s0[1], s1[0], s1[1], s0[2], s0[3], s1[2], s1[3]};
@@ -303,11 +302,11 @@ __device__ __forceinline__ void step_fd_consume(const StepParams& p, StepSmem& t
       uint32_t pa[4] = {pack_bf16(pr[0], pr[1]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[2], pr[3]),
                         pack_bf16(pr[6], pr[7])};
 #pragma unroll
-      for (int j = 0; j < NT; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
+      for (int j = 0; j < NTH; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
 #pragma unroll
-      for (int j = 0; j < NT; j += 2) {
+      for (int j = 0; j < NTH; j += 2) {
         const int mi = lane >> 3, r = lane & 7;
-        const int tok = (mi & 1) * 8 + r, c = j + (mi >> 1);
+        const int tok = (mi & 1) * 8 + r, c = half * NTH + j + (mi >> 1);
         uint32_t vb[4];
         st_ldmatrix_x4_trans(vb, vbase + tok * (HD * 2) + (c << 4));
         st_mma(o[j], pa, vb[0], vb[1]);
@@ -315,32 +314,34 @@ __device__ __forceinline__ void step_fd_consume(const StepParams& p, StepSmem& t
       }
     }
     __syncwarp();
-    if (lane == 0) mbar_arrive(t.sm.empty + s);
+    if (lane == 0) mbar_arrive(t.sm.c->empty + s);
     if (++rp.s == rp.ns) { rp.s = 0; ++rp.round; }
   }
   // quad totals of the row sums (the four lanes of a quad hold different key columns)
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  // ---- pairwise merge of warps 0..7: (4..7 -> 0..3), (2,3 -> 0,1), (1 -> 0) ----
-  constexpr int LSTRIDE = NT * 4 + 4;                 // floats per lane in the buffer
+  // ---- pairwise merge of the page slots: (4..7 -> 0..3), (2,3 -> 0,1), (1 -> 0); the Q tile is no
+  //      longer needed, its memory is the merge buffer
+  constexpr int LSTRIDE = NTH * 4 + 4;                // floats per lane in the buffer
+  sg_consumer_sync();
   for (int stride = kStFdWarps / 2; stride >= 1; stride >>= 1) {
-    if (warp >= stride && warp < 2 * stride) {
-      float* b = t.fdbuf + (size_t(warp - stride) * 32 + lane) * LSTRIDE;
+    if (slot >= stride && slot < 2 * stride) {
+      float* b = t.fdbuf + ((size_t(slot - stride) * 2 + half) * 32 + lane) * LSTRIDE;
 #pragma unroll
-      for (int j = 0; j < NT; ++j) *reinterpret_cast<float4*>(b + j * 4) = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
-      *reinterpret_cast<float4*>(b + NT * 4) = make_float4(m0, m1, l0, l1);
+      for (int j = 0; j < NTH; ++j) *reinterpret_cast<float4*>(b + j * 4) = make_float4(o[j][0], o[j][1], o[j][2], o[j][3]);
+      *reinterpret_cast<float4*>(b + NTH * 4) = make_float4(m0, m1, l0, l1);
     }
     sg_consumer_sync();
-    if (warp < stride) {
-      const float* b = t.fdbuf + (size_t(warp) * 32 + lane) * LSTRIDE;
-      const float4 ml = *reinterpret_cast<const float4*>(b + NT * 4);
+    if (slot < stride) {
+      const float* b = t.fdbuf + ((size_t(slot) * 2 + half) * 32 + lane) * LSTRIDE;
+      const float4 ml = *reinterpret_cast<const float4*>(b + NTH * 4);
       const float nm0 = fmaxf(m0, ml.x), nm1 = fmaxf(m1, ml.y);
       const float a0 = m0 == -INFINITY ? 0.f : exp2f(m0 - nm0), a1 = m1 == -INFINITY ? 0.f : exp2f(m1 - nm1);
       const float b0 = ml.x == -INFINITY ? 0.f : exp2f(ml.x - nm0), b1 = ml.y == -INFINITY ? 0.f : exp2f(ml.y - nm1);
       m0 = nm0; m1 = nm1;
       l0 = l0 * a0 + ml.z * b0; l1 = l1 * a1 + ml.w * b1;
 #pragma unroll
-      for (int j = 0; j < NT; ++j) {
+      for (int j = 0; j < NTH; ++j) {
         const float4 v = *reinterpret_cast<const float4*>(b + j * 4);
         o[j][0] = o[j][0] * a0 + v.x * b0; o[j][1] = o[j][1] * a0 + v.y * b0;
         o[j][2] = o[j][2] * a1 + v.z * b1; o[j][3] = o[j][3] * a1 + v.w * b1;
@@ -348,16 +349,16 @@ __device__ __forceinline__ void step_fd_consume(const StepParams& p, StepSmem& t
     }
     sg_consumer_sync();
   }
-  if (warp == 0 && f.on) {
+  if (slot == 0 && f.on) {
     float* po = p.fd_part_o + (size_t(f.tile) * f.S + f.split) * 16 * HD;
     float* pm = p.fd_part_ml + (size_t(f.tile) * f.S + f.split) * 32;
 #pragma unroll
-    for (int j = 0; j < NT; ++j) {
-      const int d = j * 8 + tq * 2;
+    for (int j = 0; j < NTH; ++j) {
+      const int d = (half * NTH + j) * 8 + tq * 2;
       *reinterpret_cast<float2*>(po + g * HD + d) = make_float2(o[j][0], o[j][1]);
       *reinterpret_cast<float2*>(po + (g + 8) * HD + d) = make_float2(o[j][2], o[j][3]);
     }
-    if (tq == 0) { pm[g * 2] = m0; pm[g * 2 + 1] = l0; pm[(g + 8) * 2] = m1; pm[(g + 8) * 2 + 1] = l1; }
+    if (half == 0 && tq == 0) { pm[g * 2] = m0; pm[g * 2 + 1] = l0; pm[(g + 8) * 2] = m1; pm[(g + 8) * 2 + 1] = l1; }
   }
 }
 
@@ -438,8 +439,8 @@ __device__ __forceinline__ void step_topk(const StepParams& p, const StepLayer& 
     if (lane == r) { sel_w = pw; sel_e = best_e; }
   }
   if (lane < p.top_k) {
-    t.r_idx[lane] = sel_e;
-    t.r_w[lane] = sel_w / wsum;
+    t.sm.c->r_idx[lane] = sel_e;
+    t.sm.c->r_w[lane] = sel_w / wsum;
     if (blockIdx.x == 0) { p.topk_idx[lane] = sel_e; p.topk_w[lane] = sel_w / wsum; }
   }
 }
@@ -447,12 +448,13 @@ __device__ __forceinline__ void step_topk(const StepParams& p, const StepLayer& 
 // Runs one streaming problem's consumer side (activations staged first) with the lane width its
 // plan chose.
 template <class P>
-__device__ __forceinline__ void step_consume(P& prob, const SgPlan& pl, StepSmem& t, SgRingPos& rp, uint32_t tag) {
+__device__ __forceinline__ void step_consume(const StepParams& p, int layer, P& prob, const SgPlan& pl, StepSmem& t, SgRingPos& rp, uint32_t tag) {
   rp.tag = tag;
   int q0, q1;
   prob.cta_range(pl, q0, q1);
   prob.init(false);
   prob.stage_x(t.sm, pl);
+  step_stamp(p, layer, 16 + int(tag));
   if (pl.LW == 32) sg_consume<P, 32>(prob, pl, t.sm, rp, q0, q1);
   else if (pl.LW == 16) sg_consume<P, 16>(prob, pl, t.sm, rp, q0, q1);
   else sg_consume<P, 8>(prob, pl, t.sm, rp, q0, q1);
@@ -501,14 +503,14 @@ struct StepProblems {
     GateUp P;
     P.W = L.wgu; P.I = p.I; P.K = p.D; P.x = p.h2; P.x_stride = 0; P.norm_w = L.norm2; P.eps = p.eps;
     P.act = p.act; P.act_stride = p.I;
-    P.R = SgRouting{t.r_idx, t.r_w, p.top_k, L.expert_base, L.experts_local};
+    P.R = SgRouting{t.sm.c->r_idx, t.sm.c->r_w, p.top_k, L.expert_base, L.experts_local};
     P.token = 0; P.ntok = 1; P.packed = 0; P.mask = 0;
     return P;
   }
   static __device__ Down down(const StepParams& p, const StepLayer& L, const StepSmem& t) {
     Down P;
     P.W = L.wdn; P.N = p.D; P.I = p.I; P.act = p.act; P.act_stride = p.I;
-    P.R = SgRouting{t.r_idx, t.r_w, p.top_k, L.expert_base, L.experts_local};
+    P.R = SgRouting{t.sm.c->r_idx, t.sm.c->r_w, p.top_k, L.expert_base, L.experts_local};
     P.token = 0; P.ntok = 1; P.nloc = 0; P.packed = 0;
     P.residual = p.h2; P.res_stride = 0; P.out = p.h; P.out_stride = 0;
     return P;
@@ -529,12 +531,12 @@ __global__ void __launch_bounds__(kSgThreads, 1) decode_step_kernel(StepParams p
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.ns; ++s) {
-      mbar_init(t.sm.full + s, 1);
-      mbar_init(t.sm.empty + s, kSgConsumerWarps);
+      mbar_init(t.sm.c->full + s, 1);
+      mbar_init(t.sm.c->empty + s, kSgConsumerWarps);
     }
     sg_init_handover(t.sm, p.ns);
-    t.sm.abortf[0] = 0u; t.sm.abortf[1] = 0u;
-    *t.go = 0u;
+    t.sm.c->abortf[0] = 0u; t.sm.c->abortf[1] = 0u;
+    t.sm.c->go = 0u;
     fence_mbar_init();
   }
   __syncthreads();
@@ -559,7 +561,7 @@ __global__ void __launch_bounds__(kSgThreads, 1) decode_step_kernel(StepParams p
     if (ok) { auto P = SP::lm_head(p); ok = step_produce(P, p.p_lm, t, rp, 6); }
     if (!ok) {
       sg_drain(t.sm, rp);
-      if (lane == 0) atomicExch(p.status, sg_abort_status(t.sm.abortf, kStatusMbarTimeout));
+      if (lane == 0) atomicExch(p.status, sg_abort_status(t.sm.c->abortf, kStatusMbarTimeout));
     }
     return;
   }
@@ -569,27 +571,42 @@ __global__ void __launch_bounds__(kSgThreads, 1) decode_step_kernel(StepParams p
   for (int l = 0; l < p.num_layers; ++l) {
     const StepLayer& L = p.layers[l];
     const __nv_bfloat16* h_in = l == 0 ? x0 : p.h;
-    { auto P = SP::qkv(p, L, h_in); step_consume(P, L.p_qkv, t, rp, 1); }
+    step_stamp(p, l, 0);
+    { auto P = SP::qkv(p, L, h_in); step_consume(p, l, P, L.p_qkv, t, rp, 1); }
+    step_stamp(p, l, 1);
     step_grid_sync(p, t, bar_target);
     step_signal(t);
+    step_stamp(p, l, 2);
     { const FdSplit f = step_fd_split(p); step_fd_consume<HD>(p, t, rp, f); }
+    step_stamp(p, l, 3);
     step_grid_sync(p, t, bar_target);
+    step_stamp(p, l, 4);
     step_fd_merge(p, t);
     step_grid_sync(p, t, bar_target);
-    { auto P = SP::oproj(p, L, h_in); step_consume(P, L.p_o, t, rp, 2); }
+    step_stamp(p, l, 5);
+    { auto P = SP::oproj(p, L, h_in); step_consume(p, l, P, L.p_o, t, rp, 2); }
+    step_stamp(p, l, 6);
     step_grid_sync(p, t, bar_target);
-    { auto P = SP::router(p, L); step_consume(P, L.p_router, t, rp, 3); }
+    step_stamp(p, l, 7);
+    { auto P = SP::router(p, L); step_consume(p, l, P, L.p_router, t, rp, 3); }
+    step_stamp(p, l, 8);
     step_grid_sync(p, t, bar_target);
+    step_stamp(p, l, 9);
     if (warp == 0) step_topk(p, L, t);
     sg_consumer_sync();
     step_signal(t);
-    { auto P = SP::gate_up(p, L, t); step_consume(P, L.p_gu, t, rp, 4); }
+    step_stamp(p, l, 10);
+    { auto P = SP::gate_up(p, L, t); step_consume(p, l, P, L.p_gu, t, rp, 4); }
+    step_stamp(p, l, 11);
     step_grid_sync(p, t, bar_target);
-    { auto P = SP::down(p, L, t); step_consume(P, L.p_dn, t, rp, 5); }
+    step_stamp(p, l, 12);
+    { auto P = SP::down(p, L, t); step_consume(p, l, P, L.p_dn, t, rp, 5); }
+    step_stamp(p, l, 13);
     step_grid_sync(p, t, bar_target);
+    step_stamp(p, l, 14);
   }
-  { auto P = SP::lm_head(p); step_consume(P, p.p_lm, t, rp, 6); }
-  if (*t.sm.abortf && threadIdx.x == 0) atomicExch(p.status, sg_abort_status(t.sm.abortf, kStatusMbarTimeout));
+  { auto P = SP::lm_head(p); step_consume(p, p.num_layers - 1, P, p.p_lm, t, rp, 6); }
+  if (*t.sm.c->abortf && threadIdx.x == 0) atomicExch(p.status, sg_abort_status(t.sm.c->abortf, kStatusMbarTimeout));
 }
 
 }  // namespace rb
@@ -617,6 +634,7 @@ struct RmlxStepDesc {
   const void *lm, *lm_s, *lm_b;
   void *h, *h2, *q, *attn, *act, *router_logits, *topk_idx, *topk_w, *fd_part_o, *fd_part_ml, *logits;
   void *grid_bar;
+  void *trace;                           // optional [num_layers * 32] u64 phase stamps of block 0
   void *layers_dev;                      // device buffer of num_layers * rmlx_decode_step_layer_bytes()
 };
 
@@ -664,6 +682,7 @@ static int step_fill(const RmlxStepDesc& d, const RmlxStepLayerDesc* ld, StepPar
   p.topk_idx = static_cast<int*>(d.topk_idx); p.topk_w = static_cast<float*>(d.topk_w);
   p.fd_part_o = static_cast<float*>(d.fd_part_o); p.fd_part_ml = static_cast<float*>(d.fd_part_ml);
   p.logits = static_cast<float*>(d.logits); p.grid_bar = static_cast<unsigned int*>(d.grid_bar);
+  p.trace = static_cast<unsigned long long*>(d.trace);
   p.layers = static_cast<const StepLayer*>(d.layers_dev);
 
   int slot = kStFdWarps * 2 * kStPage * d.HD * 2;      // a stage of KV pages

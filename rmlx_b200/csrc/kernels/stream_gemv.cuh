@@ -81,12 +81,7 @@ struct SgPlan {
 
 __host__ __device__ inline int sg_part_floats(int ns, int qpt, int B) { return ns * kSgConsumerWarps * qpt * 4 * B; }
 
-__host__ inline size_t sg_smem_bytes(const SgPlan& p, int B) {
-  return size_t(p.ns) * p.stage_bytes + p.x_bytes + sg_part_floats(p.ns, p.qpt, B) * 4 +
-         (2 * kSgMaxStages + kSgMaxStages * kSgConsumerWarps) * 8 + kSgMaxStages * kSgConsumerWarps * 8 +
-         kSgMaxStages * kSgMaxSeg * 8 + 256 +
-         kSgConsumerWarps * 64 + p.extra_bytes + 128;
-}
+__host__ inline size_t sg_smem_bytes(const SgPlan& p, int B);
 
 // Chooses the task shape and the block partition. `units`: 16-byte weight units per row (per slot);
 // `nslots`: how many such rows are chained along K (1, or top-k for the expert down projection);
@@ -192,11 +187,19 @@ __device__ __forceinline__ float sg_consumer_sum(float v, float* red) {
   return t;
 }
 
-// One task of the 4-bit path: rows w0..w3 (16-byte unit each) against the staged activations.
+// One task of the 4-bit path: rows w0..w3 (16-byte unit each) against the staged activations. The
+// four (scale, bias) pairs are read from the stage only when the dot products are done (they would
+// otherwise sit in eight registers through the whole inner loop): `alo` / `ahi` address the scales
+// of rows 0 / 2, the next row's is `units` bytes on, the biases `bias_off` bytes on.
 template <int B>
-__device__ __forceinline__ void sg_task_q4(const uint4 (&w)[4], const float (&sc)[4], const float (&bi)[4],
-                                           const char* xs, size_t xstride, int NHG, int xunit,
-                                           float (&acc)[4][B]) {
+__device__ __forceinline__ void sg_task_q4(const uint4 (&w)[4], uint32_t alo, uint32_t ahi, uint32_t units,
+                                           uint32_t bias_off, const char* xs, size_t xstride, int NHG,
+                                           int xunit, float (&acc)[4][B]) {
+  auto lds16 = [](uint32_t addr) -> float {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return bf16lo(v);
+  };
 #pragma unroll
   for (int b = 0; b < B; ++b) {
     const uint4* xh = reinterpret_cast<const uint4*>(xs + b * xstride);
@@ -221,9 +224,11 @@ __device__ __forceinline__ void sg_task_q4(const uint4 (&w)[4], const float (&sc
     }
 #pragma unroll
     for (int r = 0; r < 4; ++r) {
+      const uint32_t a = ((r >> 1) ? ahi : alo) + ((r & 1) ? units : 0u);
+      const float sc = lds16(a), bi = lds16(a + bias_off);
       const float2 f0 = __half22float2(a0[r]), f1 = __half22float2(a1[r]);
       const float qx = ((f0.x + f0.y) + (f1.x + f1.y)) * qmul;
-      acc[r][b] = fmaf(sc[r], qx, fmaf(bi[r], xsum, acc[r][b]));
+      acc[r][b] = fmaf(sc, qx, fmaf(bi, xsum, acc[r][b]));
     }
   }
 }
@@ -248,45 +253,55 @@ __device__ __forceinline__ void sg_task_bf16(const uint4 (&w)[4], const char* xs
 }
 
 // One task's operands in registers.
-struct SgTask { uint4 w[4]; float sc[4], bi[4]; int xunit; bool on; };
+struct SgTask { uint4 w[4]; uint32_t alo, ahi; int xunit; bool on; };   // alo/ahi: shared-memory addresses of the scale pairs
 
 // Per stage and segment, posted by the producer: how far the scale / bias spans start past a
 // 16-byte boundary, and how many rows the segment holds (0 = segment absent).
 struct SgSegMeta { uint16_t mis_sc, mis_bi, rows, pad; };
 
-// Shared-memory map of one block.
+// Fixed-layout control block at the start of a block's shared memory. Everything small lives here
+// so that one pointer reaches it (sixteen separate pointers cost thirty-two registers per thread).
+struct SgCtl {
+  uint64_t full[kSgMaxStages];
+  uint64_t empty[kSgMaxStages];
+  uint64_t partbar[kSgMaxStages * kSgConsumerWarps];   // one arrival each: the last warp to hand over signals
+  uint32_t pcnt[kSgMaxStages * kSgConsumerWarps];      // hand-overs counted so far
+  uint32_t ppar[kSgMaxStages * kSgConsumerWarps];      // parity each hand-over barrier completes next
+  SgSegMeta meta[kSgMaxStages * kSgMaxSeg];
+  volatile uint32_t abortf[2];                         // abort flag, first expired wait site
+  volatile uint32_t go;                                // multi-problem kernels: events passed by the consumers
+  uint32_t pad0;
+  float misc[64];                                      // inv_rms[4], red[16], free use
+  int r_idx[8];                                        // multi-problem kernels: routing result
+  float r_w[8];
+};
+
+// Shared-memory map of one block: the control block, then the ring, the staged activations, the
+// partial sums [ns][warps][qpt][4][B] and the problem's own area.
 struct SgSmem {
+  SgCtl* c;
   char* ring;
   char* xs;
-  float* part;          // [ns][warps][qpt][4][B]
-  uint64_t* full;       // [kSgMaxStages]
-  uint64_t* empty;      // [kSgMaxStages]
-  uint64_t* partbar;    // [kSgMaxStages][warps], one arrival each: the last warp to hand over signals
-  uint32_t* pcnt;       // [kSgMaxStages][warps] hand-overs counted so far, then [kSgMaxStages][warps]
-                        // the parity each hand-over barrier will complete next
-  SgSegMeta* meta;      // [kSgMaxStages][kSgMaxSeg]
-  volatile uint32_t* abortf;
-  float* misc;          // 62 floats: inv_rms[4], red[16], free use
-  float* wscr;          // [warps][16] per-warp scratch
+  float* part;
   char* extra;
 };
+
+__host__ __device__ inline int sg_ctl_bytes() { return (int(sizeof(SgCtl)) + 127) & ~127; }
 
 __device__ __forceinline__ SgSmem sg_carve(char* smem, const SgPlan& pl, int B) {
   SgSmem s;
   char* base = reinterpret_cast<char*>((reinterpret_cast<uintptr_t>(smem) + 127) & ~uintptr_t(127));
-  s.ring = base;
+  s.c = reinterpret_cast<SgCtl*>(base);
+  s.ring = base + sg_ctl_bytes();
   s.xs = s.ring + size_t(pl.ns) * pl.stage_bytes;
   s.part = reinterpret_cast<float*>(s.xs + pl.x_bytes);
-  s.full = reinterpret_cast<uint64_t*>(s.part + sg_part_floats(pl.ns, pl.qpt, B));
-  s.empty = s.full + kSgMaxStages;
-  s.partbar = s.empty + kSgMaxStages;
-  s.pcnt = reinterpret_cast<uint32_t*>(s.partbar + kSgMaxStages * kSgConsumerWarps);
-  s.meta = reinterpret_cast<SgSegMeta*>(s.pcnt + 2 * kSgMaxStages * kSgConsumerWarps);
-  s.abortf = reinterpret_cast<volatile uint32_t*>(s.meta + kSgMaxStages * kSgMaxSeg);
-  s.misc = reinterpret_cast<float*>(const_cast<uint32_t*>(s.abortf) + 2);
-  s.wscr = s.misc + 62;
-  s.extra = reinterpret_cast<char*>(s.wscr + kSgConsumerWarps * 16);
+  s.extra = reinterpret_cast<char*>(s.part + sg_part_floats(pl.ns, pl.qpt, B));
   return s;
+}
+
+__host__ inline size_t sg_smem_bytes(const SgPlan& p, int B) {
+  return size_t(sg_ctl_bytes()) + size_t(p.ns) * p.stage_bytes + p.x_bytes +
+         size_t(sg_part_floats(p.ns, p.qpt, B)) * 4 + p.extra_bytes + 256;
 }
 
 // Source of one segment of a stage.
@@ -332,7 +347,7 @@ __device__ __forceinline__ bool sg_produce(P& prob, const SgPlan& pl, SgSmem& sm
   const int nseg = pl.pairs ? 2 : prob.nslots();
   for (int i = 0; i < nst; ++i) {
     const int s = rp.s;
-    if (rp.round > 0 && !sg_wait(sm.empty + s, (rp.round - 1) & 1, sm.abortf, rp.tag * 16 + 1)) return false;
+    if (rp.round > 0 && !sg_wait(sm.c->empty + s, (rp.round - 1) & 1, sm.c->abortf, rp.tag * 16 + 1)) return false;
     const int rb = i / pl.KP, kp = i - rb * pl.KP;
     const int sq0 = q0 + rb * pl.QS, nq = min(pl.QS, q1 - sq0);
     char* stage = sm.ring + size_t(s) * rp.slot_bytes;
@@ -344,13 +359,13 @@ __device__ __forceinline__ bool sg_produce(P& prob, const SgPlan& pl, SgSmem& sm
         char* dst = stage + size_t(lane) * pl.w_seg_bytes;
         if (pl.KP == 1) {
           const uint32_t n = uint32_t(src.rows) * uint32_t(pl.units) * 16u;
-          bulk_g2s(dst, src.w, n, sm.full + s);
+          bulk_g2s(dst, src.w, n, sm.c->full + s);
           bytes += n;
         } else {
           const int u0 = kp * pl.spp * LW;
           const uint32_t n = uint32_t(min(pl.spp * LW, pl.units - u0)) * 16u;
           for (int r = 0; r < src.rows; ++r)
-            bulk_g2s(dst + size_t(r) * pl.w_row_bytes, src.w + (size_t(r) * pl.units + u0) * 16, n, sm.full + s);
+            bulk_g2s(dst + size_t(r) * pl.w_row_bytes, src.w + (size_t(r) * pl.units + u0) * 16, n, sm.c->full + s);
           bytes += n * uint32_t(src.rows);
         }
         if (P::kQ4) {
@@ -359,17 +374,17 @@ __device__ __forceinline__ bool sg_produce(P& prob, const SgPlan& pl, SgSmem& sm
           const uintptr_t alo = a & ~uintptr_t(15), ahi = (a + span + 15) & ~uintptr_t(15);
           const uintptr_t blo = b2 & ~uintptr_t(15), bhi = (b2 + span + 15) & ~uintptr_t(15);
           char* ax = stage + pl.aux_off + size_t(lane) * 2 * pl.aux_seg_bytes;
-          bulk_g2s(ax, reinterpret_cast<const void*>(alo), uint32_t(ahi - alo), sm.full + s);
-          bulk_g2s(ax + pl.aux_seg_bytes, reinterpret_cast<const void*>(blo), uint32_t(bhi - blo), sm.full + s);
+          bulk_g2s(ax, reinterpret_cast<const void*>(alo), uint32_t(ahi - alo), sm.c->full + s);
+          bulk_g2s(ax + pl.aux_seg_bytes, reinterpret_cast<const void*>(blo), uint32_t(bhi - blo), sm.c->full + s);
           bytes += uint32_t(ahi - alo) + uint32_t(bhi - blo);
           m.mis_sc = uint16_t(a & 15u); m.mis_bi = uint16_t(b2 & 15u);
         }
       }
-      sm.meta[s * kSgMaxSeg + lane] = m;
+      sm.c->meta[s * kSgMaxSeg + lane] = m;
     }
     bytes = __reduce_add_sync(0xffffffffu, bytes);
     __syncwarp();
-    if (lane == 0) mbar_arrive_expect_tx(sm.full + s, bytes);
+    if (lane == 0) mbar_arrive_expect_tx(sm.c->full + s, bytes);
     if (++rp.s == rp.ns) { rp.s = 0; ++rp.round; }
   }
   return true;
@@ -381,16 +396,16 @@ __device__ __forceinline__ void sg_drain(SgSmem& sm, const SgRingPos& rp) {
   for (int k = 0; k < rp.ns; ++k) {
     // slot k was last armed in round rp.round (k < rp.s) or rp.round - 1
     const int r = int(rp.round) - (k < rp.s ? 0 : 1);
-    if (r >= 0) mbar_wait(sm.full + k, uint32_t(r) & 1u, sm.abortf, 1u << 16);
+    if (r >= 0) mbar_wait(sm.c->full + k, uint32_t(r) & 1u, sm.c->abortf, 1u << 16);
   }
 }
 
 // Hand-over barriers and counters of a block: one thread, once, before any use.
 __device__ __forceinline__ void sg_init_handover(SgSmem& sm, int ns) {
   for (int i = 0; i < ns * kSgConsumerWarps; ++i) {
-    mbar_init(sm.partbar + i, 1);
-    sm.pcnt[i] = 0u;
-    sm.pcnt[kSgMaxStages * kSgConsumerWarps + i] = 0u;
+    mbar_init(sm.c->partbar + i, 1);
+    sm.c->pcnt[i] = 0u;
+    sm.c->ppar[i] = 0u;
   }
 }
 
@@ -428,7 +443,7 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
     for (int kp = 0; kp < pl.KP; ++kp) {
       const int s = rp.s;
       s_used = s;
-      const bool ok = sg_wait(sm.full + s, rp.round & 1u, sm.abortf, rp.tag * 16 + 2);
+      const bool ok = sg_wait(sm.c->full + s, rp.round & 1u, sm.c->abortf, rp.tag * 16 + 2);
       if (ok && qvalid) {
         const char* stage = sm.ring + uint32_t(s) * uint32_t(rp.slot_bytes);
         const int s_lo = pl.KP == 1 ? 0 : kp * pl.spp, s_hi = pl.KP == 1 ? nsl : min(pl.spl, s_lo + pl.spp);
@@ -437,8 +452,8 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
           int slot = 0, u = sl * LW + l;
           if (P::kMultiSlot) { slot = sl / pl.spl; u = (sl - slot * pl.spl) * LW + l; }
           const int segm = P::kMultiSlot ? slot : 0;
-          const SgSegMeta mlo = sm.meta[s * kSgMaxSeg + segm];
-          const SgSegMeta mhi = pl.pairs ? sm.meta[s * kSgMaxSeg + 1] : mlo;
+          const SgSegMeta mlo = sm.c->meta[s * kSgMaxSeg + segm];
+          const SgSegMeta mhi = pl.pairs ? sm.c->meta[s * kSgMaxSeg + 1] : mlo;
           t.on = u < pl.units && row_lo < mlo.rows;      // a segment that was not fetched has rows == 0
           u = min(u, pl.units - 1);
           const uint32_t ucol = uint32_t(pl.KP == 1 ? u : u - s_lo * LW) * 16u;
@@ -450,15 +465,10 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
           t.xunit = slot * pl.units + u;
           if (P::kQ4) {
             const char* abase = stage + (P::kMultiSlot ? uint32_t(slot) * 2u * uint32_t(pl.aux_seg_bytes) : 0u) + (u & ~1);
-            const char* alo = abase + a_lo_off, *ahi = abase + a_hi_off;
-            t.sc[0] = bf16lo(*reinterpret_cast<const uint16_t*>(alo + mlo.mis_sc));
-            t.sc[1] = bf16lo(*reinterpret_cast<const uint16_t*>(alo + mlo.mis_sc + units));
-            t.sc[2] = bf16lo(*reinterpret_cast<const uint16_t*>(ahi + mhi.mis_sc));
-            t.sc[3] = bf16lo(*reinterpret_cast<const uint16_t*>(ahi + mhi.mis_sc + units));
-            t.bi[0] = bf16lo(*reinterpret_cast<const uint16_t*>(alo + pl.aux_seg_bytes + mlo.mis_bi));
-            t.bi[1] = bf16lo(*reinterpret_cast<const uint16_t*>(alo + pl.aux_seg_bytes + mlo.mis_bi + units));
-            t.bi[2] = bf16lo(*reinterpret_cast<const uint16_t*>(ahi + pl.aux_seg_bytes + mhi.mis_bi));
-            t.bi[3] = bf16lo(*reinterpret_cast<const uint16_t*>(ahi + pl.aux_seg_bytes + mhi.mis_bi + units));
+            // the biases sit aux_seg_bytes after the scales (the launcher checks that both arrays start at
+            // the same remainder modulo 16, so one remainder serves both)
+            t.alo = smem_u32(abase + a_lo_off + mlo.mis_sc);
+            t.ahi = smem_u32(abase + a_hi_off + mhi.mis_sc);
           }
         };
         for (int sl = s_lo + sq; sl < s_hi; sl += 2 * pl.SQ) {
@@ -468,17 +478,17 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
           load(two ? sl + pl.SQ : sl, t1);
           t1.on = t1.on && two;
           if (t0.on) {
-            if (P::kQ4) sg_task_q4<B>(t0.w, t0.sc, t0.bi, sm.xs, xstride, xunits, t0.xunit, acc);
+            if (P::kQ4) sg_task_q4<B>(t0.w, t0.alo, t0.ahi, units, uint32_t(pl.aux_seg_bytes), sm.xs, xstride, xunits, t0.xunit, acc);
             else sg_task_bf16<B>(t0.w, sm.xs, xstride, xunits, t0.xunit, acc);
           }
           if (t1.on) {
-            if (P::kQ4) sg_task_q4<B>(t1.w, t1.sc, t1.bi, sm.xs, xstride, xunits, t1.xunit, acc);
+            if (P::kQ4) sg_task_q4<B>(t1.w, t1.alo, t1.ahi, units, uint32_t(pl.aux_seg_bytes), sm.xs, xstride, xunits, t1.xunit, acc);
             else sg_task_bf16<B>(t1.w, sm.xs, xstride, xunits, t1.xunit, acc);
           }
         }
       }
       __syncwarp();
-      if (kp + 1 < pl.KP && lane == 0) mbar_arrive(sm.empty + s);   // the last part is released after the hand-over
+      if (kp + 1 < pl.KP && lane == 0) mbar_arrive(sm.c->empty + s);   // the last part is released after the hand-over
       if (++rp.s == rp.ns) { rp.s = 0; ++rp.round; }
     }
     // ---- lane-group totals, hand-over to the task row's first warp, epilogue
@@ -506,19 +516,19 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
         if (lane == 0) {
           // the last of the SQ - 1 warps to hand over signals the task row's first warp
           __threadfence_block();
-          uint32_t* cnt = sm.pcnt + sh * kSgConsumerWarps + tr;
+          uint32_t* cnt = sm.c->pcnt + sh * kSgConsumerWarps + tr;
           if (atomicAdd(cnt, 1u) == uint32_t(pl.SQ - 2)) {
             *cnt = 0u;
             __threadfence_block();
-            mbar_arrive(sm.partbar + sh * kSgConsumerWarps + tr);
+            mbar_arrive(sm.c->partbar + sh * kSgConsumerWarps + tr);
           }
         }
       } else {
         // the barrier's parity lives in shared memory: which warp owns a task row changes from
         // one problem to the next
-        uint32_t* ppar = sm.pcnt + kSgMaxStages * kSgConsumerWarps + sh * kSgConsumerWarps + tr;
+        uint32_t* ppar = sm.c->ppar + sh * kSgConsumerWarps + tr;
         const uint32_t par = *ppar;
-        sg_wait(sm.partbar + sh * kSgConsumerWarps + tr, par & 1u, sm.abortf, rp.tag * 16 + 3);
+        sg_wait(sm.c->partbar + sh * kSgConsumerWarps + tr, par & 1u, sm.c->abortf, rp.tag * 16 + 3);
         __syncwarp();
         if (lane == 0) *ppar = par ^ 1u;
         for (int k = 1; k < pl.SQ; ++k) {
@@ -532,7 +542,7 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
     }
     if (sq == 0 && qvalid && l == 0) prob.epilogue(sq0 + qi, acc, sm);
     __syncwarp();
-    if (lane == 0) mbar_arrive(sm.empty + sh);
+    if (lane == 0) mbar_arrive(sm.c->empty + sh);
   }
 }
 
@@ -543,11 +553,11 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
     for (int s = 0; s < pl.ns; ++s) {
-      mbar_init(sm.full + s, 1);
-      mbar_init(sm.empty + s, kSgConsumerWarps);
+      mbar_init(sm.c->full + s, 1);
+      mbar_init(sm.c->empty + s, kSgConsumerWarps);
     }
     sg_init_handover(sm, pl.ns);
-    sm.abortf[0] = 0u; sm.abortf[1] = 0u;
+    sm.c->abortf[0] = 0u; sm.c->abortf[1] = 0u;
     fence_mbar_init();
   }
   __syncthreads();
@@ -560,7 +570,7 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
     prob.init(true);
     if (!sg_produce<P, LW>(prob, pl, sm, rp, q0, q1)) {
       sg_drain(sm, rp);
-      if (lane == 0) atomicExch(status, sg_abort_status(sm.abortf, kStatusMbarTimeout));
+      if (lane == 0) atomicExch(status, sg_abort_status(sm.c->abortf, kStatusMbarTimeout));
     }
     return;
   }
@@ -569,7 +579,7 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
   prob.stage_x(sm, pl);
   sg_consume<P, LW>(prob, pl, sm, rp, q0, q1);
   prob.cta_done(sm);
-  if (*sm.abortf && threadIdx.x == 0) atomicExch(status, sg_abort_status(sm.abortf, kStatusMbarTimeout));
+  if (*sm.c->abortf && threadIdx.x == 0) atomicExch(status, sg_abort_status(sm.c->abortf, kStatusMbarTimeout));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -600,10 +610,10 @@ __device__ __forceinline__ void sg_stage_plain(SgSmem& sm, const __nv_bfloat16* 
     if (Q4) XStage<WQ4>::stage_part(sm.xs + b * xstride, K, ld, tid, kSgConsumers);
     else XStage<WBf16>::stage_part(sm.xs + b * xstride, K, ld, tid, kSgConsumers);
     if (norm_w) {
-      const float ssq = sg_consumer_sum(ld.ssq, sm.misc + 4);
-      if (tid == 0) sm.misc[b] = rsqrtf(ssq / float(K) + eps);
+      const float ssq = sg_consumer_sum(ld.ssq, sm.c->misc + 4);
+      if (tid == 0) sm.c->misc[b] = rsqrtf(ssq / float(K) + eps);
     } else if (tid == 0) {
-      sm.misc[b] = 1.f;
+      sm.c->misc[b] = 1.f;
     }
   }
   sg_consumer_sync();

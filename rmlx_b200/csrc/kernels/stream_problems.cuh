@@ -48,7 +48,7 @@ struct SgDense {
   __device__ void epilogue(int quad, float (&v)[4][B], SgSmem& sm) {
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      const float inv = sm.misc[b];
+      const float inv = sm.c->misc[b];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
         const int n = quad * 4 + r;
@@ -127,7 +127,7 @@ struct SgQkvRope {
     const int half = a.HD >> 1, qph = a.HD >> 2, head = quad / qph, p = quad - head * qph;
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      const float inv = sm.misc[b];
+      const float inv = sm.c->misc[b];
       const float* cs = reinterpret_cast<const float*>(sm.extra + b * (a.HD * 4 + 16));
       const int* pi = reinterpret_cast<const int*>(cs + a.HD);
       const int pos = pi[0];
@@ -197,7 +197,7 @@ struct SgGateUp {
   __device__ void epilogue(int quad, float (&v)[4][B], SgSmem& sm) {
 #pragma unroll
     for (int b = 0; b < B; ++b) {
-      const float inv = sm.misc[b];
+      const float inv = sm.c->misc[b];
       const float a0 = sg_silu_mul(v[0][b] * inv, v[2][b] * inv), a1 = sg_silu_mul(v[1][b] * inv, v[3][b] * inv);
       *reinterpret_cast<uint32_t*>(act + size_t(b) * act_stride + 2 * quad) = pack_bf16(a0, a1);
     }
@@ -257,7 +257,7 @@ struct SgMoeGateUp {
   __device__ void epilogue(int quad, float (&v)[4][1], SgSmem& sm) {
     const int hq = I >> 1, s = quad / hq, i2 = quad - s * hq;
     if (!((mask >> s) & 1u)) return;
-    const float inv = sm.misc[0];
+    const float inv = sm.c->misc[0];
     const float a0 = sg_silu_mul(v[0][0] * inv, v[2][0] * inv), a1 = sg_silu_mul(v[1][0] * inv, v[3][0] * inv);
     *reinterpret_cast<uint32_t*>(act + size_t(token * R.top_k + s) * act_stride + 2 * i2) = pack_bf16(a0, a1);
   }
@@ -368,7 +368,9 @@ inline SgWeights sg_weights(bool q4, const void* w, const void* sc, const void* 
   return W;
 }
 inline bool sg_weights_ok(bool q4, const void* w, const void* sc, const void* bi, int K) {
-  if (q4) return K % 64 == 0 && sg_aligned16(w) && sc && bi && (reinterpret_cast<uintptr_t>(sc) & 1u) == 0;
+  if (q4)
+    return K % 64 == 0 && sg_aligned16(w) && sc && bi && (reinterpret_cast<uintptr_t>(sc) & 1u) == 0 &&
+           ((reinterpret_cast<uintptr_t>(sc) ^ reinterpret_cast<uintptr_t>(bi)) & 15u) == 0;
   return K % 8 == 0 && sg_aligned16(w);
 }
 inline int sg_x_bytes(bool q4, int K, int B) {

@@ -44,7 +44,7 @@ class _StepDesc(ctypes.Structure):
         ("max_blocks", c_int), ("window", c_int), ("traditional", c_int)] + [(n, c_void_p) for n in (
             "tokens", "positions", "seq_lens", "block_table", "cos_t", "sin_t", "embed", "final_norm",
             "lm", "lm_s", "lm_b", "h", "h2", "q", "attn", "act", "router_logits", "topk_idx", "topk_w",
-            "fd_part_o", "fd_part_ml", "logits", "grid_bar", "layers_dev")]
+            "fd_part_o", "fd_part_ml", "logits", "grid_bar", "trace", "layers_dev")]
 
 
 def enabled() -> bool:
@@ -117,6 +117,11 @@ class DecodeStepKernel:
         s.router_logits, s.topk_idx, s.topk_w = self.router_logits.data_ptr(), eng.idx.data_ptr(), eng.wts.data_ptr()
         s.fd_part_o, s.fd_part_ml, s.logits = self.fd_part_o.data_ptr(), self.fd_part_ml.data_ptr(), eng.logits.data_ptr()
         s.grid_bar, s.layers_dev = self.grid_bar.data_ptr(), self.layers_dev.data_ptr()
+        self.trace = None
+        if os.environ.get("RMLX_STEP_TRACE"):
+            # block 0 stamps the global timer at every phase end: [layers, 32] nanoseconds
+            self.trace = torch.zeros(nl, 32, dtype=torch.int64, device=dev)
+            s.trace = self.trace.data_ptr()
         with torch.cuda.device(dev):
             rc = lib.rmlx_decode_step_prepare(ctypes.byref(s), self._layer_descs)
         self.ok = rc == 0
