@@ -15,12 +15,17 @@
 // crates/rmlx-distributed/src/group.rs:348-504, crates/rmlx-nn/src/parallel.rs:619-693).
 //
 // Receive-buffer protocol (per rank, in symmetric memory; every rank has the same layout):
-//   recv[slot][src_rank][B*N] 8-byte words (fp32 value, 32-bit tag); slot alternates between
-//   consecutive all-reduces. A value and its arrival flag travel in one 8-byte store, so the
-//   exchange costs one NVLink crossing: no fence, no counter, no reducer blocks. A rank can run
-//   at most one all-reduce ahead of a peer (finishing one needs the peer's contribution to it), so
-//   two slots suffice. All waits are bounded; a wait that gives up sets a status word the host
-//   reads, and the kernel still terminates.
+//   recv[slot][src_rank][Bmax][N] 8-byte words (fp32 value, 32-bit tag). A value and its arrival
+//   flag travel in one 8-byte store, so the exchange costs one NVLink crossing: no fence, no
+//   counter, no reducer blocks. Tag and slot come from ONE device-side sequence number per
+//   communicator, ctr[0] = all-reduces completed so far (every kind of call advances it: the last
+//   block of a kernel to finish bumps it): tag = seq + 1, slot = seq & 1. Every call kind uses the
+//   same layout of the receive area, so a word left by an earlier call can never carry the tag a
+//   later call waits for. A rank can run at most one all-reduce ahead of a peer (finishing one
+//   needs the peer's contribution to it), so two slots suffice, and because the slot is derived on
+//   the device the alternation holds for any mix of captured and eager calls. All waits are
+//   bounded; a wait that gives up sets a status word the host reads, and the kernel still
+//   terminates.
 //
 // Remote data is only ever read with plain loads from this GPU's own memory (peers push); nothing
 // here uses TMA on peer memory.
@@ -38,13 +43,13 @@ __device__ int g_tp_status = 0;
 
 struct TpPeers {
   float* recv[kMaxWorld];        // each rank's receive area of 8-byte (value, tag) words (peer-mapped)
-  uint32_t* ctr[kMaxWorld];      // each rank's counters: [slot*2 + 0] calls completed on the slot, [slot*2 + 1] exit ticket
-  int rank, world;
+  uint32_t* ctr[kMaxWorld];      // each rank's counters: [0] all-reduces completed, [1] exit ticket of the running one
+  int rank, world, bmax;         // bmax: batch rows the receive area is laid out for
 };
 
 // 8-byte (value, tag) words: a peer's store of such a word is a single transaction, so the tag is
 // the arrival flag of its value and no fence or separate counter is needed (the low-latency
-// protocol of collective libraries). Tags are the slot's call number + 1; memory starts zeroed.
+// protocol of collective libraries). Tags are the sequence number + 1; memory starts zeroed.
 __device__ __forceinline__ void st_ll(uint2* p, float v, uint32_t tag) {
   asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)), "r"(tag) : "memory");
 }
@@ -61,25 +66,29 @@ __device__ __forceinline__ bool ld_ll(const uint2* p, uint32_t tag, float& v) {
 
 // Exchange this block's partial values and finish its own rows.
 //   vals: shared memory [B][kTpRowsPerCta] fp32 partial sums for rows n0 .. n0+15
-//   recv layout per rank (8-byte words): slot_off + (src*B + b)*N + n
+//   recv layout per rank (8-byte words): slot_off + (src*bmax + b)*N + n
 // Thread (b, i) stores its value, tagged, into every peer's receive area, then collects the same
-// element from every peer out of its own receive area and sums in rank order (so every rank gets
-// bit-identical results), adds the residual and writes the output. Blocks never wait for other
-// blocks: the same block index owns the same rows on every rank. ctr[0] is the slot's call count,
-// ctr[1] the exit ticket that advances it (both local).
+// element from every peer out of its own receive area (all peers polled in one loop) and sums in
+// rank order (so every rank gets bit-identical results), adds the residual and writes the output.
+// Blocks never wait for other blocks: the same block index owns the same rows on every rank.
+// ctr[0] is the communicator's sequence number, ctr[1] the exit ticket that advances it (both
+// local).
+// `b0` is the batch row of vals[0] (the expert kernel launches one token per grid row); the
+// counters are read after the kernel's dependency wait, so they reflect every earlier all-reduce.
 template <int B>
 __device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* vals, int n0, int N,
-                                               size_t slot_off, int slot,
-                                               const __nv_bfloat16* residual, int res_stride,
+                                               int b0, const __nv_bfloat16* residual, int res_stride,
                                                __nv_bfloat16* out, int out_stride) {
   const int tid = threadIdx.x;
-  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
-  const uint32_t tag = ctr[0] + 1u;
+  uint32_t* ctr = P.ctr[P.rank];
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(ctr);
+  const uint32_t tag = seq + 1u;
+  const size_t slot_off = size_t(seq & 1u) * P.world * P.bmax * N;
   if (tid < B * kTpRowsPerCta) {
     const int b = tid / kTpRowsPerCta, i = tid % kTpRowsPerCta;
     if (n0 + i < N) {
       const float v = vals[tid];
-      const size_t mine = slot_off + (size_t(P.rank) * B + b) * N + n0 + i;
+      const size_t mine = slot_off + (size_t(P.rank) * P.bmax + b0 + b) * N + n0 + i;
       for (int pi = 1; pi < P.world; ++pi) {
         int p = P.rank + pi; if (p >= P.world) p -= P.world;
         st_ll(reinterpret_cast<uint2*>(P.recv[p]) + mine, v, tag);
@@ -87,11 +96,22 @@ __device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* va
       const uint2* rb = reinterpret_cast<const uint2*>(P.recv[P.rank]) + slot_off;
       float s = 0.f;
       bool ok = true;
-      for (int src = 0; src < P.world; ++src) {
-        float u = v;
-        if (src != P.rank) ok = ld_ll(rb + (size_t(src) * B + b) * N + n0 + i, tag, u) && ok;
-        s += u;
+      // all peers' words are polled together: one NVLink latency, not world - 1
+      float u[kMaxWorld];
+      uint32_t pending = 0;
+      for (int src = 0; src < P.world; ++src) { u[src] = v; if (src != P.rank) pending |= 1u << src; }
+      for (uint32_t it = 0; pending && it < kPeerPollLimit; ++it) {
+        for (int src = 0; src < P.world; ++src) {
+          if (!((pending >> src) & 1u)) continue;
+          uint32_t a, t2;
+          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(t2)
+                       : "l"(rb + (size_t(src) * P.bmax + b0 + b) * N + n0 + i) : "memory");
+          if (t2 == tag) { u[src] = __uint_as_float(a); pending &= ~(1u << src); }
+        }
+        if (pending && it > 256) __nanosleep(it > 8192 ? 128 : 20);
       }
+      if (pending) { ok = false; for (int src = 0; src < P.world; ++src) if ((pending >> src) & 1u) u[src] = 0.f; }
+      for (int src = 0; src < P.world; ++src) s += u[src];
       if (!ok) atomicExch(&g_tp_status, kStatusPeerTimeout);
       if (residual) s += __bfloat162float(residual[size_t(b) * res_stride + n0 + i]);
       out[size_t(b) * out_stride + n0 + i] = __float2bfloat16_rn(s);
@@ -100,7 +120,7 @@ __device__ __forceinline__ void tp_push_reduce(const TpPeers& P, const float* va
   __syncthreads();
   if (tid == 0) {
     __threadfence();
-    if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) { ctr[1] = 0u; __threadfence(); ctr[0] = tag; }
+    if (atomicAdd(ctr + 1, 1u) == gridDim.x * gridDim.y - 1) { ctr[1] = 0u; __threadfence(); *reinterpret_cast<volatile uint32_t*>(ctr) = tag; }
   }
 }
 
@@ -111,8 +131,7 @@ template <class WT, int B>
 __global__ void __launch_bounds__(kGemvThreads)
 gemv_allreduce_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_stride,
                       const __nv_bfloat16* __restrict__ residual, int res_stride,
-                      __nv_bfloat16* __restrict__ out, int out_stride, int N, TpPeers P,
-                      size_t slot_off, int slot) {
+                      __nv_bfloat16* __restrict__ out, int out_stride, int N, TpPeers P) {
   extern __shared__ __align__(16) char smem[];
   __shared__ float vals[B * kTpRowsPerCta];
   const int K = W.K;
@@ -146,7 +165,7 @@ gemv_allreduce_kernel(Matrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_s
       if (lane == 0) vals[b * kTpRowsPerCta + warp * kTpRowsPerWarp + r] = v;
     }
   __syncthreads();
-  tp_push_reduce<B>(P, vals, n0, N, slot_off, slot, residual, res_stride, out, out_stride);
+  tp_push_reduce<B>(P, vals, n0, N, 0, residual, res_stride, out, out_stride);
   pdl_launch_dependents();
 }
 
@@ -173,16 +192,15 @@ struct ExpertMat<WQ4> {
 
 constexpr int kTpMaxTopK = 8;
 
-// One token (B = 1) per launch row; the batch is the grid's y dimension, and each y has its own
-// receive area and counters (slot_off / counter index advance with y).
+// One token (B = 1) per launch row; the batch is the grid's y dimension. All rows share the
+// communicator's sequence number (the last block of the whole grid bumps it).
 template <class WT>
 __global__ void __launch_bounds__(kGemvThreads)
 moe_down_allreduce_kernel(ExpertMat<WT> W, const __nv_bfloat16* __restrict__ act, int act_stride,
                           const int* __restrict__ topk_idx, const float* __restrict__ topk_w,
                           const __nv_bfloat16* __restrict__ residual, int res_stride,
                           __nv_bfloat16* __restrict__ out, int out_stride, int N, int top_k,
-                          int expert_base, int experts_local, TpPeers P, size_t slot_off,
-                          size_t slot_stride_y, int slot, int slots_total) {
+                          int expert_base, int experts_local, TpPeers P) {
   extern __shared__ __align__(16) char smem[];
   __shared__ int s_e[kTpMaxTopK];
   __shared__ float s_w[kTpMaxTopK];
@@ -230,11 +248,7 @@ moe_down_allreduce_kernel(ExpertMat<WT> W, const __nv_bfloat16* __restrict__ act
     if (lane == 0) vals[warp * kTpRowsPerWarp + r] = v;
   }
   __syncthreads();
-  // per-token receive area and counters
-  TpPeers Q = P;
-  for (int p = 0; p < P.world; ++p) Q.ctr[p] = P.ctr[p] + size_t(b) * 2 * slots_total;
-  tp_push_reduce<1>(Q, vals, n0, N, slot_off + size_t(b) * slot_stride_y, slot,
-                    residual ? residual + size_t(b) * res_stride : nullptr, 0,
+  tp_push_reduce<1>(P, vals, n0, N, b, residual ? residual + size_t(b) * res_stride : nullptr, 0,
                     out + size_t(b) * out_stride, 0);
   pdl_launch_dependents();
 }
@@ -246,11 +260,13 @@ moe_down_allreduce_kernel(ExpertMat<WT> W, const __nv_bfloat16* __restrict__ act
 template <bool OUT_F32>
 __global__ void __launch_bounds__(256)
 allreduce_oneshot_kernel(const float* __restrict__ in, const __nv_bfloat16* __restrict__ residual,
-                         void* __restrict__ out, int n, TpPeers P, size_t slot_off, int slot) {
+                         void* __restrict__ out, int n, TpPeers P, size_t slot_floats) {
   pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
-  uint32_t* ctr = P.ctr[P.rank] + slot * 2;
-  const uint32_t tag = ctr[0] + 1u;
+  uint32_t* ctr = P.ctr[P.rank];
+  const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(ctr);
+  const uint32_t tag = seq + 1u;
+  const size_t slot_off = size_t(seq & 1u) * slot_floats;
   const int per = (n + gridDim.x - 1) / gridDim.x;
   const int lo = blockIdx.x * per, hi = min(n, lo + per);
   const uint2* rb = reinterpret_cast<const uint2*>(P.recv[P.rank]) + slot_off;
@@ -280,7 +296,7 @@ allreduce_oneshot_kernel(const float* __restrict__ in, const __nv_bfloat16* __re
   __syncthreads();
   if (threadIdx.x == 0) {
     __threadfence();
-    if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) { ctr[1] = 0u; __threadfence(); ctr[0] = tag; }
+    if (atomicAdd(ctr + 1, 1u) == gridDim.x - 1) { ctr[1] = 0u; __threadfence(); *reinterpret_cast<volatile uint32_t*>(ctr) = tag; }
   }
   pdl_launch_dependents();
 }
@@ -376,13 +392,13 @@ Matrix<WQ4> mk_matrix<WQ4>(const void* w, const void* s, const void* b, int K) {
                      static_cast<const __nv_bfloat16*>(b), K};
 }
 
-static TpPeers make_peers(void* const* recv, void* const* ctr, int rank, int world) {
+static TpPeers make_peers(void* const* recv, void* const* ctr, int rank, int world, int bmax = 1) {
   TpPeers P;
   for (int i = 0; i < kMaxWorld; ++i) {
     P.recv[i] = i < world ? static_cast<float*>(recv[i]) : nullptr;
     P.ctr[i] = i < world ? static_cast<uint32_t*>(ctr[i]) : nullptr;
   }
-  P.rank = rank; P.world = world;
+  P.rank = rank; P.world = world; P.bmax = bmax;
   return P;
 }
 
@@ -398,17 +414,18 @@ extern "C" int rmlx_tp_status() {
 }
 
 // recv / ctr: host arrays of `world` device pointers (peer-mapped bases, index = rank).
-// slot_off: float offset of this call's receive area inside every rank's recv buffer;
-// slot: which counter pair to use (alternate between consecutive all-reduces).
+// bmax: batch rows the receive area is laid out for (2 slots x world x bmax x N words); the slot
+// and the tag are derived on the device from the communicator's sequence number.
 extern "C" int rmlx_tp_gemv_allreduce(int w_kind, const void* w, const void* scales,
                                       const void* biases, const void* x, int x_stride,
                                       const void* residual, int res_stride, void* out,
                                       int out_stride, int B, int N, int K, void* const* recv,
-                                      void* const* ctr, int rank, int world, long long slot_off,
-                                      int slot, int pdl, cudaStream_t st) {
-  if (K % 8 || (w_kind == 1 && K % 64) || B < 1 || B > 4 || N < 1 || world < 1 || world > kMaxWorld)
+                                      void* const* ctr, int rank, int world, int bmax, int pdl,
+                                      cudaStream_t st) {
+  if (K % 8 || (w_kind == 1 && K % 64) || B < 1 || B > 4 || B > bmax || N < 1 || world < 1 ||
+      world > kMaxWorld)
     return -2;
-  const TpPeers P = make_peers(recv, ctr, rank, world);
+  const TpPeers P = make_peers(recv, ctr, rank, world, bmax);
   const int grid = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
 #define RB_TPG(WT, BB)                                                                            \
   {                                                                                               \
@@ -418,7 +435,7 @@ extern "C" int rmlx_tp_gemv_allreduce(int w_kind, const void* w, const void* sca
     return launch(kern, dim3(grid), dim3(kGemvThreads), smem, st, pdl != 0,                       \
                   mk_matrix<WT>(w, scales, biases, K), static_cast<const __nv_bfloat16*>(x),      \
                   x_stride, static_cast<const __nv_bfloat16*>(residual), res_stride,              \
-                  static_cast<__nv_bfloat16*>(out), out_stride, N, P, size_t(slot_off), slot);    \
+                  static_cast<__nv_bfloat16*>(out), out_stride, N, P);                         \
   }
 #define RB_TPG_B(WT)                                            \
   switch (B) {                                                  \
@@ -431,21 +448,18 @@ extern "C" int rmlx_tp_gemv_allreduce(int w_kind, const void* w, const void* sca
   return -2;
 }
 
-// slot_stride_y: float distance between consecutive tokens' receive areas; each token also uses
-// its own counter block of 2*slots_total words.
 extern "C" int rmlx_tp_moe_down_allreduce(int w_kind, const void* w, const void* scales,
                                           const void* biases, const void* act, int act_stride,
                                           const int* topk_idx, const float* topk_w,
                                           const void* residual, int res_stride, void* out,
                                           int out_stride, int B, int top_k, int N, int I,
                                           int expert_base, int experts_local, void* const* recv,
-                                          void* const* ctr, int rank, int world, long long slot_off,
-                                          long long slot_stride_y, int slot, int slots_total,
-                                          int pdl, cudaStream_t st) {
-  if (I % 8 || (w_kind == 1 && I % 64) || B < 1 || top_k < 1 || top_k > kTpMaxTopK || world < 1 ||
-      world > kMaxWorld)
+                                          void* const* ctr, int rank, int world, int bmax, int pdl,
+                                          cudaStream_t st) {
+  if (I % 8 || (w_kind == 1 && I % 64) || B < 1 || B > bmax || top_k < 1 || top_k > kTpMaxTopK ||
+      world < 1 || world > kMaxWorld)
     return -2;
-  const TpPeers P = make_peers(recv, ctr, rank, world);
+  const TpPeers P = make_peers(recv, ctr, rank, world, bmax);
   const int gx = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
 #define RB_TPD(WT, MK)                                                                            \
   {                                                                                               \
@@ -456,7 +470,7 @@ extern "C" int rmlx_tp_moe_down_allreduce(int w_kind, const void* w, const void*
                   static_cast<const __nv_bfloat16*>(act), act_stride, topk_idx, topk_w,           \
                   static_cast<const __nv_bfloat16*>(residual), res_stride,                        \
                   static_cast<__nv_bfloat16*>(out), out_stride, N, top_k, expert_base,            \
-                  experts_local, P, size_t(slot_off), size_t(slot_stride_y), slot, slots_total);  \
+                  experts_local, P);                                                              \
   }
   if (w_kind == 0)
     RB_TPD(WBf16, (ExpertMat<WBf16>{static_cast<const __nv_bfloat16*>(w), N, I}))
@@ -468,18 +482,19 @@ extern "C" int rmlx_tp_moe_down_allreduce(int w_kind, const void* w, const void*
   return -2;
 }
 
+// slot_floats: words of one slot of the receive area (world x bmax x N); n <= bmax x N.
 extern "C" int rmlx_tp_allreduce(const float* in, const void* residual, void* out, int out_f32,
                                  int n, void* const* recv, void* const* ctr, int rank, int world,
-                                 long long slot_off, int slot, int pdl, cudaStream_t st) {
-  if (n < 1 || world < 1 || world > kMaxWorld) return -2;
+                                 long long slot_floats, int pdl, cudaStream_t st) {
+  if (n < 1 || world < 1 || world > kMaxWorld || 1LL * world * n > slot_floats) return -2;
   const TpPeers P = make_peers(recv, ctr, rank, world);
   int grid = (n + 2047) / 2048;
   if (grid > 32) grid = 32;
   if (out_f32)
     return launch(allreduce_oneshot_kernel<true>, dim3(grid), dim3(256), 0, st, pdl != 0, in,
-                  static_cast<const __nv_bfloat16*>(residual), out, n, P, size_t(slot_off), slot);
+                  static_cast<const __nv_bfloat16*>(residual), out, n, P, size_t(slot_floats));
   return launch(allreduce_oneshot_kernel<false>, dim3(grid), dim3(256), 0, st, pdl != 0, in,
-                static_cast<const __nv_bfloat16*>(residual), out, n, P, size_t(slot_off), slot);
+                static_cast<const __nv_bfloat16*>(residual), out, n, P, size_t(slot_floats));
 }
 
 // keys_peer_dev: DEVICE array of `world` pointers to each rank's key area.

@@ -87,7 +87,7 @@ class CachedDecode:
         # batch 1 on one GPU: the whole step is one persistent kernel when the model fits it
         self.step_kernel = None
         from .step_kernel import DecodeStepKernel
-        if step_kernel is not False and DecodeStepKernel.supported(model, max_batch, comm):
+        if step_kernel is not False and DecodeStepKernel.supported(model, max_batch, comm, force=bool(step_kernel)):
             sk = DecodeStepKernel(self)
             if sk.ok:
                 self.step_kernel = sk

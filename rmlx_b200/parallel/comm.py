@@ -25,9 +25,9 @@ from ..ops.weights import LinearWeight
 
 _lib.register_cuda_sigs({
     "rmlx_tp_status": ("", "i"),
-    "rmlx_tp_gemv_allreduce": ("ippppipipiiiippiiqiip", "i"),
-    "rmlx_tp_moe_down_allreduce": ("ippppipppipiiiiiiippiiqqiiip", "i"),
-    "rmlx_tp_allreduce": ("pppiippiiqiip", "i"),
+    "rmlx_tp_gemv_allreduce": ("ippppipipiiiippiiiip", "i"),
+    "rmlx_tp_moe_down_allreduce": ("ippppipppipiiiiiiippiiiip", "i"),
+    "rmlx_tp_allreduce": ("pppiippiiqip", "i"),
     "rmlx_tp_argmax": ("piiiippppiiiip", "i"),
     "rmlx_tp_barrier": ("ppiiiip", "i"),
     "rmlx_symm_malloc": ("pq", "i"),
@@ -87,7 +87,12 @@ class SymmetricRegion:
 
 
 class PeerComm:
-    """Fused projection + all-reduce over peer memory for decode batches of up to ``max_batch``."""
+    """Fused projection + all-reduce over peer memory for decode batches of up to ``max_batch``.
+
+    Every all-reduce, whatever its kind, takes its arrival tag and its receive slot from one
+    sequence number kept on the device (the last block of a call advances it), so captured and
+    eager calls can be mixed freely and consecutive calls always alternate slots; the host keeps no
+    slot state."""
 
     kind = "fused"
     SLOTS = 2
@@ -101,29 +106,25 @@ class PeerComm:
         w = self.world
         self.slot_floats = w * max_batch * hidden
         self.recv_bytes = self.SLOTS * self.slot_floats * 8      # 8-byte (value, tag) words
-        # counters: per token a block of 2*SLOTS words; then argmax counters; then barrier word
-        self.ctr_words = 2 * self.SLOTS * max_batch + 2 * self.SLOTS + 4
+        # counters: [0] all-reduces completed, [1] exit ticket; then arg-max counters; then barrier word
         self.ctr_off = self.recv_bytes
-        self.key_off = (self.ctr_off + self.ctr_words * 4 + 255) // 256 * 256
+        self.ctr_argmax_off = self.ctr_off + 16
+        self.ctr_barrier_off = self.ctr_argmax_off + 2 * self.SLOTS * 4
+        self.key_off = (self.ctr_barrier_off + 16 + 255) // 256 * 256
         self.key_bytes = self.SLOTS * max_batch * w * 8
         total = self.key_off + self.key_bytes
         self.region = SymmetricRegion(total, group)
         self._recv = self.region.peer_array(0)
         self._ctr = self.region.peer_array(self.ctr_off)
-        self._ctr_argmax = self.region.peer_array(self.ctr_off + 2 * self.SLOTS * max_batch * 4)
-        self._ctr_barrier = self.region.peer_array(self.ctr_off + (2 * self.SLOTS * max_batch + 2 * self.SLOTS) * 4)
+        self._ctr_argmax = self.region.peer_array(self.ctr_argmax_off)
+        self._ctr_barrier = self.region.peer_array(self.ctr_barrier_off)
         keys = [self.region.ptrs[r] + self.key_off for r in range(w)]
         self._keys_dev = torch.tensor(keys, dtype=torch.int64, device=self.device)
-        self._n = 0           # collective calls issued (slot alternates)
+        self._n = 0           # collective calls issued (statistics only)
         self._n_argmax = 0
         self._barrier_epoch = 0
 
     # ------------------------------------------------------------------
-    def _slot(self) -> int:
-        s = self._n % self.SLOTS
-        self._n += 1
-        return s
-
     def calls_issued(self) -> int:
         return self._n
 
@@ -135,14 +136,14 @@ class PeerComm:
         lib, st = _lib.cuda(), _lib.stream_ptr()
         for b0 in range(0, b, 4):
             bb = min(4, b - b0)
-            s = self._slot()
+            self._n += 1
             xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
             rs = None if residual is None else residual[b0:b0 + bb]
             rc = lib.rmlx_tp_gemv_allreduce(
                 w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
                 xs.stride(0), _lib.ptr(rs), 0 if rs is None else rs.stride(0), os_.data_ptr(),
                 os_.stride(0), bb, self.N, k, self._recv, self._ctr, self.rank, self.world,
-                s * self.slot_floats, s, int(pdl), st)
+                self.B, int(pdl), st)
             _lib.check(rc, "tp_gemv_allreduce")
         return out
 
@@ -151,13 +152,13 @@ class PeerComm:
                            expert_base: int = 0, pdl: bool = False) -> torch.Tensor:
         b, top_k = idx.shape
         assert b <= self.B and w.n == self.N
-        s = self._slot()
+        self._n += 1
         rc = _lib.cuda().rmlx_tp_moe_down_allreduce(
             w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), act.data_ptr(),
             act.stride(0), idx.data_ptr(), wts.data_ptr(), _lib.ptr(residual),
             0 if residual is None else residual.stride(0), out.data_ptr(), out.stride(0), b, top_k,
             self.N, w.k, expert_base, w.experts, self._recv, self._ctr, self.rank, self.world,
-            s * self.slot_floats, self.world * self.N, s, self.SLOTS, int(pdl), _lib.stream_ptr())
+            self.B, int(pdl), _lib.stream_ptr())
         _lib.check(rc, "tp_moe_down_allreduce")
         return out
 
@@ -167,10 +168,10 @@ class PeerComm:
         assert x.dtype == torch.float32 and x.is_contiguous() and x.numel() <= self.B * self.N
         if out is None:
             out = torch.empty_like(x)
-        s = self._slot()
+        self._n += 1
         rc = _lib.cuda().rmlx_tp_allreduce(x.data_ptr(), _lib.ptr(residual), out.data_ptr(),
                                            int(out.dtype == torch.float32), x.numel(), self._recv,
-                                           self._ctr, self.rank, self.world, s * self.slot_floats, s,
+                                           self._ctr, self.rank, self.world, self.slot_floats,
                                            int(pdl), _lib.stream_ptr())
         _lib.check(rc, "tp_allreduce")
         return out
