@@ -1,15 +1,11 @@
+#!/usr/bin/env python
 """Short text summaries of Nsight Compute reports: per captured launch the duration, DRAM traffic and
 throughput, tensor-pipe and special-function-pipe activity, occupancy, registers, and the warp stall
-reasons that dominate. The files under ``profiles/`` are made from this output.
-
-This is the counterpart of the reference's per-dispatch GPU counters (CounterHeap / GPU start-end
-timestamps, crates/rmlx-metal/src/capture.rs and the ``gpu_profile_bench`` family): there the
-framework samples counters itself, here the profiler's report is the source of truth and this module
-only condenses it.
+reasons that dominate. A report condenser for the benchmark scripts beside it, not a capture API.
 
     ncu --set full --clock-control none -k regex:<kernel> -c 3 -o report <command>
-    python -m rmlx_b200.utils.ncu_summary report.ncu-rep        # needs `ncu` on PATH, no GPU
-    ncu -i report.ncu-rep --page raw --csv | python -m rmlx_b200.utils.ncu_summary -
+    python benchmarks/ncu_summary.py report.ncu-rep        # needs `ncu` on PATH, no GPU
+    ncu -i report.ncu-rep --page raw --csv | python benchmarks/ncu_summary.py -
 """
 from __future__ import annotations
 

@@ -122,6 +122,10 @@ extern "C" int rmlx_sg_status() {
   return v;
 }
 
+// Test hook for the bounded-wait path: block 0 of the NEXT streaming launch never sends stage
+// `stage`; its consumers' wait expires, the block aborts cleanly and rmlx_sg_status() reports it.
+extern "C" void rmlx_sg_debug_drop_stage(int stage) { sg_debug_drop() = stage; }
+
 // Same contract as rmlx_rms_gemv (decode_gemv.cu).
 extern "C" int rmlx_sg_rms_gemv(int w_kind, const void* w, const void* scales, const void* biases,
                                 const void* x, int x_stride, const void* norm_w, float eps,

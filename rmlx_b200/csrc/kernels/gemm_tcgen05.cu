@@ -35,12 +35,15 @@ struct GemmSmem {
   static constexpr int kBytes = kStages * (kStageA + kStageB) + 1024 /*align slack*/ + 256 /*barriers*/;
 };
 
-template <int BN, bool RESIDUAL>
+// OUT_F32: the accumulator is stored as fp32 (C is then float*, ldc counts floats): router logits
+// and other results that must not be rounded to bf16.
+template <int BN, bool RESIDUAL, bool OUT_F32 = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
                          const __grid_constant__ CUtensorMap tmap_w,
-                         __nv_bfloat16* __restrict__ C, const __nv_bfloat16* __restrict__ residual,
+                         void* __restrict__ Cv, const __nv_bfloat16* __restrict__ residual,
                          int M, int N, int K, int ldc, int* __restrict__ status) {
+  __nv_bfloat16* C = static_cast<__nv_bfloat16*>(Cv);
   using S = GemmSmem<BN>;
   constexpr int STAGES = S::kStages;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : 2 * BN;  // power of two: BN in {32,..,256}
@@ -148,7 +151,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = tn * BN + c * 32;
-        if (row < M && col0 < N) {
+        if (OUT_F32) {
+          if (row < M && col0 < N) {
+            float* dstf = static_cast<float*>(Cv) + size_t(row) * ldc + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < N) dstf[j] = __uint_as_float(r[j]);
+          }
+        } else if (row < M && col0 < N) {
           __nv_bfloat16* dst = C + size_t(row) * ldc + col0;
           const __nv_bfloat16* res = RESIDUAL ? residual + size_t(row) * ldc + col0 : nullptr;
           if (col0 + 32 <= N) {
@@ -197,17 +207,16 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a,
   pdl_launch_dependents();
 }
 
-template <int BN, bool RESIDUAL>
+template <int BN, bool RESIDUAL, bool OUT_F32 = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tw, void* C, const void* residual,
                        int M, int N, int K, int ldc, int* status, int pdl, cudaStream_t st) {
-  auto kern = gemm_bf16_tcgen05_kernel<BN, RESIDUAL>;
+  auto kern = gemm_bf16_tcgen05_kernel<BN, RESIDUAL, OUT_F32>;
   constexpr size_t smem = GemmSmem<BN>::kBytes;
   RB_CHECK(set_max_smem(kern, smem));
   const int tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
   const int grid = tiles < sm_count() ? tiles : sm_count();
-  return launch(kern, dim3(grid), dim3(kGemmThreads), smem, st, pdl != 0, ta, tw,
-                static_cast<__nv_bfloat16*>(C), static_cast<const __nv_bfloat16*>(residual), M, N, K,
-                ldc, status);
+  return launch(kern, dim3(grid), dim3(kGemmThreads), smem, st, pdl != 0, ta, tw, C,
+                static_cast<const __nv_bfloat16*>(residual), M, N, K, ldc, status);
 }
 
 }  // namespace rb
@@ -253,4 +262,19 @@ extern "C" int rmlx_gemm_bf16(const void* A, const void* W, void* C, const void*
     default: return -2;
   }
 #undef RB_GEMM
+}
+
+// The same product with an fp32 result: C[M,N] float, row stride ldc floats. No residual.
+extern "C" int rmlx_gemm_bf16_f32(const void* A, const void* W, void* C, int M, int N, int K, int lda,
+                                  int ldw, int ldc, int* status, int pdl, cudaStream_t st) {
+  if (M < 1 || N < 1 || K < 8 || K % 8 || lda % 8 || ldw % 8) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(W)) & 15) return -2;
+  const int bn = rmlx_gemm_pick_bn(M, N) >= 128 ? 128 : 64;
+  CUtensorMap ta, tw;
+  int rc = make_tmap_2d_bf16(&ta, A, uint64_t(K), uint64_t(M), uint64_t(lda) * 2, kBK, kBM);
+  if (rc) return rc;
+  rc = make_tmap_2d_bf16(&tw, W, uint64_t(K), uint64_t(N), uint64_t(ldw) * 2, kBK, bn);
+  if (rc) return rc;
+  if (bn == 128) return launch_gemm<128, false, true>(ta, tw, C, nullptr, M, N, K, ldc, status, pdl, st);
+  return launch_gemm<64, false, true>(ta, tw, C, nullptr, M, N, K, ldc, status, pdl, st);
 }

@@ -77,6 +77,7 @@ struct SgPlan {
   int x_bytes;       // staged activations (all vectors)
   int extra_bytes;   // problem-specific shared memory
   int grid;          // blocks (per token for the per-token problems); 0 = shape not supported
+  int drop_stage;    // test hook: block 0's producer withholds this stage (-1: none)
 };
 
 __host__ __device__ inline int sg_part_floats(int ns, int qpt, int B) { return ns * kSgConsumerWarps * qpt * 4 * B; }
@@ -143,6 +144,7 @@ __host__ inline SgPlan sg_make_plan(bool q4, int units, int nslots, bool pairs, 
     p.ns = ns;
   }
   p.grid = (quads + qpc - 1) / qpc;
+  p.drop_stage = -1;
   (void)B;
   return p;
 }
@@ -348,6 +350,11 @@ __device__ __forceinline__ bool sg_produce(P& prob, const SgPlan& pl, SgSmem& sm
   for (int i = 0; i < nst; ++i) {
     const int s = rp.s;
     if (rp.round > 0 && !sg_wait(sm.c->empty + s, (rp.round - 1) & 1, sm.c->abortf, rp.tag * 16 + 1)) return false;
+    if (i == pl.drop_stage && blockIdx.x == 0) {
+      // test hook (a message that is never sent): the consumers' wait for this stage runs out
+      if (++rp.s == rp.ns) { rp.s = 0; ++rp.round; }
+      continue;
+    }
     const int rb = i / pl.KP, kp = i - rb * pl.KP;
     const int sq0 = q0 + rb * pl.QS, nq = min(pl.QS, q1 - sq0);
     char* stage = sm.ring + size_t(s) * rp.slot_bytes;
@@ -594,6 +601,9 @@ struct SgWeights {
     return SgSegSrc{w + n * size_t(units) * 16, sc + n * size_t(units), bi + n * size_t(units), count};
   }
 };
+
+// Test hook: the next launch withholds one stage in block 0 (see SgPlan::drop_stage).
+__host__ inline int& sg_debug_drop() { static int v = -1; return v; }
 
 __host__ inline bool sg_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

@@ -379,8 +379,11 @@ inline int sg_x_bytes(bool q4, int K, int B) {
 }
 
 template <class P>
-inline int sg_launch(const P& prob, const SgPlan& pl, int grid, int* status, int pdl, cudaStream_t st) {
-  if (pl.grid < 1) return -2;
+inline int sg_launch(const P& prob, const SgPlan& plan, int grid, int* status, int pdl, cudaStream_t st) {
+  if (plan.grid < 1) return -2;
+  SgPlan pl = plan;
+  pl.drop_stage = sg_debug_drop();
+  sg_debug_drop() = -1;
   const size_t smem = sg_smem_bytes(pl, P::kB);
   if (smem > 200 * 1024) return -2;
 #define SG_LAUNCH_LW(LW_)                                                                         \

@@ -45,17 +45,12 @@ def _gate_up_act(x: torch.Tensor, w: LinearWeight) -> torch.Tensor:
     return D.silu_mul(_mm(x, w))
 
 
-_MM_OUT_DTYPE = [True]
-
-
 def _router_logits(xn: torch.Tensor, router: torch.Tensor) -> torch.Tensor:
-    """fp32 router logits from bf16 operands: a plain tensor-core library GEMM with fp32 output when
-    this torch offers it (exact products, fp32 accumulation), else the widened fp32 matmul."""
-    if _MM_OUT_DTYPE[0] and xn.dtype == torch.bfloat16 and router.dtype == torch.bfloat16:
-        try:
-            return torch.mm(xn, router.t(), out_dtype=torch.float32)
-        except (TypeError, RuntimeError):
-            _MM_OUT_DTYPE[0] = False
+    """fp32 router logits from bf16 operands on this package's tensor-core GEMM, the accumulator
+    stored unrounded (a bf16 result would create ties between experts)."""
+    if xn.dtype == torch.bfloat16 and router.dtype == torch.bfloat16 and xn.shape[1] % 8 == 0:
+        from ..ops.gemm import gemm_bf16_f32
+        return gemm_bf16_f32(xn.contiguous(), router)
     return xn.float() @ router.float().t()
 
 

@@ -155,9 +155,16 @@ class TransformerModel:
         """Run a prompt (or a chunk of one) for ``seq_id``, filling its KV pages. Returns the
         logits of the last token, ``[1, vocab]``. On CUDA this takes the native tensor-core path
         when it is available for the model's weights, else the library-kernel forward."""
-        native = getattr(self, "_native_prefill", None)
-        if native is not None and token_ids.is_cuda:
-            return native(token_ids, cache, seq_id)
+        if token_ids.is_cuda:
+            if not hasattr(self, "_native_prefill"):
+                # first prompt on a GPU: attach the tensor-core path when the model's shapes and
+                # layout are covered (single rank, head_dim 64 / 128, bf16 activations)
+                self._native_prefill = None
+                if self.layout.world == 1:
+                    from .prefill import enable_native_prefill
+                    enable_native_prefill(self)
+            if self._native_prefill is not None:
+                return self._native_prefill(token_ids, cache, seq_id)
         return self.forward(token_ids, cache, [seq_id], last_only=True)
 
     # ------------------------------------------------------------------ greedy generation (oracle)

@@ -22,6 +22,7 @@ _STREAM = os.environ.get("RMLX_DECODE_STREAM", "1") != "0"
 
 _lib.register_cuda_sigs({
     "rmlx_sg_status": ("", "i"),
+    "rmlx_sg_debug_drop_stage": ("i", "i"),
     "rmlx_sg_rms_gemv": ("ippppipfpipiiiiiip", "i"),
     "rmlx_sg_rms_qkv_rope": ("ippppipfppppppppiiiiiiiiip", "i"),
     "rmlx_sg_gate_up": ("ippppipfpiiiiip", "i"),

@@ -55,3 +55,26 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, residual: Optional[torch.Tensor]
                                     GemmStatus.get(x.device).data_ptr(), int(pdl), _lib.stream_ptr())
     _lib.check(rc, "gemm_bf16")
     return out
+
+
+_lib.register_cuda_sigs({"rmlx_gemm_bf16_f32": ("pppiiiiiipip", "i")})
+
+
+def gemm_bf16_f32(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+                  pdl: bool = False) -> torch.Tensor:
+    """x [M, K] bf16, w [N, K] bf16 -> [M, N] fp32: the tensor-memory accumulator stored unrounded
+    (router logits, where a bf16 result would create ties)."""
+    _lib.require_cuda_tensor(x, w)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.dim() == 2 and w.dim() == 2 and x.stride(1) == 1 and w.stride(1) == 1
+    m, k = x.shape
+    n = w.shape[0]
+    assert w.shape[1] == k
+    if out is None:
+        out = torch.empty(m, n, dtype=torch.float32, device=x.device)
+    assert out.stride(1) == 1 and out.dtype == torch.float32
+    rc = _lib.cuda().rmlx_gemm_bf16_f32(x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k,
+                                        x.stride(0), w.stride(0), out.stride(0),
+                                        GemmStatus.get(x.device).data_ptr(), int(pdl), _lib.stream_ptr())
+    _lib.check(rc, "gemm_bf16_f32")
+    return out

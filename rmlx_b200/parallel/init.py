@@ -99,3 +99,30 @@ def init(cfg: Optional[InitConfig] = None) -> DistributedContext:
 def shutdown() -> None:
     if dist.is_available() and dist.is_initialized():
         dist.destroy_process_group()
+
+
+def rejoin(store, old_rank: int, survivors, backend: str = "gloo", generation: int = 1,
+           timeout_s: float = 30.0):
+    """Teardown + re-rendezvous after a rank has left between steps: the reference has no elastic
+    re-ranking (a dead peer ends the job); recovery here is to destroy the process group and form a
+    new, smaller one from the ranks that are still alive.
+
+    ``survivors`` is the sorted list of old ranks that continue (every survivor passes the same
+    list, learned on the host from the store or the heartbeat monitor before the next launch).
+    The new rank is the position in that list. ``store`` is any ``torch.distributed`` store all
+    survivors can reach (the job's TCPStore); keys are prefixed with the generation so several
+    recoveries do not collide. Returns the new ``DistributedContext``."""
+    survivors = sorted(int(r) for r in survivors)
+    if old_rank not in survivors:
+        raise DistributedError(f"rank {old_rank} is not among the survivors {survivors}")
+    if dist.is_initialized():
+        dist.destroy_process_group()
+    new_rank, new_world = survivors.index(old_rank), len(survivors)
+    if new_world == 1:
+        return loopback_context()
+    pstore = dist.PrefixStore(f"rmlx_gen{generation}", store)
+    dist.init_process_group(backend, store=pstore, rank=new_rank, world_size=new_world,
+                            timeout=datetime.timedelta(seconds=timeout_s))
+    rlog.info("rmlx.distributed", "process group re-formed", rank=new_rank, world=new_world,
+              generation=generation)
+    return DistributedContext(Group(), new_rank, new_world, new_rank, backend)

@@ -128,7 +128,13 @@ def test_managed_buffer_returns_memory():
 
 
 def test_ncu_summary_parses_raw_csv():
-    from rmlx_b200.utils.ncu_summary import parse_raw_csv
+    import importlib.util
+    import os
+    spec = importlib.util.spec_from_file_location(
+        "ncu_summary", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "ncu_summary.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    parse_raw_csv = mod.parse_raw_csv
     text = "\n".join([
         "==PROF== banner line that is not CSV",
         '"ID","Kernel Name","gpu__time_duration.sum","dram__bytes_read.sum",'

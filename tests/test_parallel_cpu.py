@@ -250,3 +250,56 @@ def test_nvtx_ranges_are_noops_without_cuda():
     with nvtx.range("layer0"):
         nvtx.mark("x")
     assert nvtx.enabled() in (False, True)
+
+
+def _leaver_worker(rank, world, port, q):
+    """Three gloo ranks run all-reduce 'steps'; rank 2 leaves between steps (announced on the
+    store, nothing in flight); the others learn of it on the host before their next launch, tear the
+    group down, re-form a two-rank group and carry on."""
+    import datetime
+    from rmlx_b200.parallel.init import rejoin
+    store = dist.TCPStore("127.0.0.1", port, world, rank == 0, timeout=datetime.timedelta(seconds=60),
+                          wait_for_workers=False)
+    dist.init_process_group("gloo", store=dist.PrefixStore("gen0", store), rank=rank, world_size=world,
+                            timeout=datetime.timedelta(seconds=60))
+    try:
+        sums = []
+        for step in range(3):
+            t = torch.tensor([float(rank + 1)])
+            dist.all_reduce(t)
+            sums.append(t.item())
+        if rank == 2:
+            store.set("left/2", b"1")        # between steps, no collective in flight
+            dist.destroy_process_group()
+            q.put((rank, sums, None))
+            return
+        store.wait(["left/2"], datetime.timedelta(seconds=30))   # host-side notice before the next launch
+        ctx = rejoin(store, rank, [0, 1], backend="gloo", generation=1)
+        after = []
+        for step in range(3):
+            t = torch.tensor([float(rank + 1)])
+            dist.all_reduce(t)
+            after.append(t.item())
+        q.put((rank, sums, (ctx.rank, ctx.world_size, after)))
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def test_rank_leaves_between_steps_and_the_rest_re_rendezvous():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_leaver_worker, args=(r, 3, port, q)) for r in range(3)]
+    [p.start() for p in ps]
+    res = {}
+    for _ in range(3):
+        r, sums, after = q.get(timeout=120)
+        res[r] = (sums, after)
+    for p in ps:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for r in range(3):
+        assert res[r][0] == [6.0, 6.0, 6.0]
+    assert res[2][1] is None
+    assert res[0][1] == (0, 2, [3.0, 3.0, 3.0]) and res[1][1] == (1, 2, [3.0, 3.0, 3.0])
