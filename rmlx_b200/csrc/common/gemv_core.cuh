@@ -16,6 +16,7 @@ constexpr int kGemvWarps = kGemvThreads / 32;
 
 struct WBf16 {};  // weights: bf16 [N, K] row-major
 struct WQ4 {};    // weights: uint32 [N, K/8], scales/biases bf16 [N, K/64]
+struct WQ8 {};    // weights: uint32 [N, K/4] (bytes), scales/biases bf16 [N, K/64]
 
 // One weight row as seen by a dot product.
 struct RowBf16 {
@@ -200,6 +201,59 @@ struct XStage<WQ4> {
     return want_ssq ? block_sum_256(ld.ssq, red) : 0.f;
   }
 };
+
+// 8-bit affine weights (w = s*q + b, q an unsigned byte, four per word): the bytes are used in
+// place as fp16 subnormals exactly like the nibbles above (a byte at bits 0-7 of a half is
+// q * 2^-24), two masks per word: t0 = w & 0x00ff00ff pairs bytes (0, 2), t1 = (w >> 8) & 0x00ff00ff
+// pairs bytes (1, 3). A unit is 16 weights (one uint4); its activations are two 16-byte pieces,
+// piece h at index h*(K/16) + unit, holding (x0,x2),(x1,x3) of words 2h and 2h+1. Every 16
+// activations carry their own power-of-two scale; beside the pieces sit, per unit, the fp32 sum of
+// the activations and the factor 2^24 / S.
+template <>
+struct XStage<WQ8> {
+  static __host__ __device__ size_t bytes(int K) { return size_t(K) * 2 + size_t(K >> 4) * 8; }
+  template <class F>
+  static __device__ void stage_part(char* smem, int K, F& load, int t, int nt) {
+    uint4* xh = reinterpret_cast<uint4*>(smem);
+    const int nchunk = K >> 3, nu = K >> 4;
+    float* xs = reinterpret_cast<float*>(smem + size_t(K) * 2);
+    float* qm = xs + nu;
+    for (int c0 = 0; c0 < nchunk; c0 += nt) {
+      const int c = c0 + t;
+      const bool valid = c < nchunk;               // nchunk is even: the two lanes of a unit are all-in or all-out
+      float f[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (valid) load(c, f);
+      float amax = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+      amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+      const int ex = (__float_as_int(amax) >> 23) & 0xff;
+      const int e = max(-60, min(141 - ex, 40));
+      const float S = __int_as_float((127 + e) << 23);
+      const float inv = __int_as_float((127 - e) << 23);
+      const __half2 p0 = __floats2half2_rn(f[0] * S, f[2] * S), p1 = __floats2half2_rn(f[1] * S, f[3] * S);
+      const __half2 p2 = __floats2half2_rn(f[4] * S, f[6] * S), p3 = __floats2half2_rn(f[5] * S, f[7] * S);
+      const float2 a = __half22float2(p0), b = __half22float2(p1), cc = __half22float2(p2), d = __half22float2(p3);
+      float sum = ((a.x + a.y) + (b.x + b.y) + (cc.x + cc.y) + (d.x + d.y)) * inv;
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      if (valid) {
+        uint4 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&p0); o.y = *reinterpret_cast<const uint32_t*>(&p1);
+        o.z = *reinterpret_cast<const uint32_t*>(&p2); o.w = *reinterpret_cast<const uint32_t*>(&p3);
+        xh[(c & 1) * nu + (c >> 1)] = o;
+        if ((c & 1) == 0) { xs[c >> 1] = sum; qm[c >> 1] = inv * 16777216.f; }
+      }
+    }
+  }
+};
+
+// One packed word (4 bytes) times the matching half of a 16-byte activation piece.
+__device__ __forceinline__ void q8_word_fma(uint32_t w, const __half2& x02, const __half2& x13,
+                                            __half2& a0, __half2& a1) {
+  const uint32_t t0 = w & 0x00ff00ffu, t1 = (w >> 8) & 0x00ff00ffu;
+  a0 = __hfma2(*reinterpret_cast<const __half2*>(&t0), x02, a0);
+  a1 = __hfma2(*reinterpret_cast<const __half2*>(&t1), x13, a1);
+}
 
 // ------------------------------------------------------------------------------------------------
 // Warp dot products. A "tile" is the slice of R weight rows that one warp pulls per iteration:

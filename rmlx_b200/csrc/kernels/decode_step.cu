@@ -54,7 +54,7 @@ struct StepParams {
   const StepLayer* layers;
   int num_layers;
   int D, Hq, Hkv, HD, I, E, top_k, V;
-  int q4;                                // projections are 4-bit (the router is always bf16)
+  int q4;                                // weight kind of the projections: 0 bf16, 1 Q4, 2 Q8 (the router is bf16)
   float eps, scale_log2;
   int max_blocks, window, traditional;
   const int* tokens;                     // [1]
@@ -470,14 +470,14 @@ __device__ __forceinline__ bool step_produce(P& prob, const SgPlan& pl, StepSmem
   return sg_produce<P, 8>(prob, pl, t.sm, rp, q0, q1);
 }
 
-template <bool Q4>
+template <int WK>
 struct StepProblems {
-  using Qkv = SgQkvRope<Q4, 1>;
-  using Oproj = SgDense<Q4, 1, false>;
-  using Router = SgDense<false, 1, true>;
-  using GateUp = SgMoeGateUp<Q4>;
-  using Down = SgMoeDown<Q4, false>;
-  using LmHead = SgDense<Q4, 1, true>;
+  using Qkv = SgQkvRope<WK, 1>;
+  using Oproj = SgDense<WK, 1, false>;
+  using Router = SgDense<0, 1, true>;
+  using GateUp = SgMoeGateUp<WK>;
+  using Down = SgMoeDown<WK, false>;
+  using LmHead = SgDense<WK, 1, true>;
 
   static __device__ Qkv qkv(const StepParams& p, const StepLayer& L, const __nv_bfloat16* x) {
     Qkv P;
@@ -494,7 +494,7 @@ struct StepProblems {
   }
   static __device__ Router router(const StepParams& p, const StepLayer& L) {
     Router P;
-    P.W = SgWeights{reinterpret_cast<const char*>(L.router), nullptr, nullptr, p.D >> 3};
+    P.W = SgWeights{reinterpret_cast<const char*>(L.router), nullptr, nullptr, p.D >> 3, 0};
     P.N = p.E; P.K = p.D; P.x = p.h2; P.x_stride = 0; P.norm_w = L.norm2; P.eps = p.eps;
     P.residual = nullptr; P.res_stride = 0; P.out = p.router_logits; P.out_stride = 0;
     return P;
@@ -523,10 +523,10 @@ struct StepProblems {
   }
 };
 
-template <bool Q4, int HD>
+template <int WK, int HD>
 __global__ void __launch_bounds__(kSgThreads, 1) decode_step_kernel(StepParams p) {
   extern __shared__ char smem_raw[];
-  using SP = StepProblems<Q4>;
+  using SP = StepProblems<WK>;
   StepSmem t = step_carve(smem_raw, p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -662,7 +662,8 @@ extern "C" int rmlx_decode_step_status() {
 
 static int step_fill(const RmlxStepDesc& d, const RmlxStepLayerDesc* ld, StepParams& p,
                      StepLayer* host_layers, int grid) {
-  const bool q4 = d.q4 != 0;
+  const int q4 = d.q4;               // weight kind
+  if (q4 < 0 || q4 > 2) return -2;
   if (d.HD != 64 && d.HD != 128) return -2;
   if (d.E > kStMaxExperts || d.top_k > kSgMaxTopK || d.I % 2 || d.Hq % d.Hkv) return -2;
   const int G = d.Hq / d.Hkv, tiles = d.Hkv * ((G + 15) / 16);
@@ -701,7 +702,7 @@ static int step_fill(const RmlxStepDesc& d, const RmlxStepLayerDesc* ld, StepPar
     StepLayer& L = host_layers[l];
     if (!sg_weights_ok(q4, s.wqkv, s.wqkv_s, s.wqkv_b, d.D) || !sg_weights_ok(q4, s.wo, s.wo_s, s.wo_b, Kq) ||
         !sg_weights_ok(q4, s.wgu, s.wgu_s, s.wgu_b, d.D) || !sg_weights_ok(q4, s.wdn, s.wdn_s, s.wdn_b, d.I) ||
-        !sg_aligned16(s.router) || d.D % 64 || (!q4 && d.I % 32) || s.experts_local > 256)
+        !sg_aligned16(s.router) || d.D % 64 || (q4 == 0 && d.I % 32) || s.experts_local > 256)
       return -2;
     L.wqkv = sg_weights(q4, s.wqkv, s.wqkv_s, s.wqkv_b, d.D);
     L.wo = sg_weights(q4, s.wo, s.wo_s, s.wo_b, Kq);
@@ -713,9 +714,9 @@ static int step_fill(const RmlxStepDesc& d, const RmlxStepLayerDesc* ld, StepPar
     L.k_cache = static_cast<__nv_bfloat16*>(s.k_cache); L.v_cache = static_cast<__nv_bfloat16*>(s.v_cache);
     L.expert_base = s.expert_base; L.experts_local = s.experts_local;
     L.p_qkv = sg_make_plan(q4, L.wqkv.units, 1, !d.traditional, (d.Hq + 2 * d.Hkv) * (d.HD / 4), grid,
-                           d.HD / 4, sg_x_bytes(q4, d.D, 1), SgQkvRope<true, 1>::extra_bytes(d.HD, 1), 1);
+                           d.HD / 4, sg_x_bytes(q4, d.D, 1), SgQkvRope<1, 1>::extra_bytes(d.HD, 1), 1);
     L.p_o = sg_make_plan(q4, L.wo.units, 1, false, (d.D + 3) / 4, grid, 1 << 20, sg_x_bytes(q4, Kq, 1), 0, 1);
-    L.p_router = sg_make_plan(false, d.D >> 3, 1, false, (d.E + 3) / 4, grid, 1 << 20, sg_x_bytes(false, d.D, 1), 0, 1);
+    L.p_router = sg_make_plan(0, d.D >> 3, 1, false, (d.E + 3) / 4, grid, 1 << 20, sg_x_bytes(0, d.D, 1), 0, 1);
     L.p_gu = sg_make_plan(q4, L.wgu.units, 1, true, d.top_k * hq2, grid, hq2 & -hq2, sg_x_bytes(q4, d.D, 1), 0, 1);
     L.p_dn = sg_make_plan(q4, L.wdn.units, d.top_k, false, (d.D + 3) / 4, grid, 1 << 20,
                           sg_x_bytes(q4, d.top_k * d.I, 1), 64, 1);
@@ -780,10 +781,12 @@ extern "C" int rmlx_decode_step_launch(const void* desc, const void* layer_descs
     if (e != cudaSuccess) (void)cudaGetLastError();                                                \
     return static_cast<int>(e);                                                                    \
   }
-  if (d.q4 && d.HD == 128) RB_STEP(true, 128)
-  if (d.q4 && d.HD == 64) RB_STEP(true, 64)
-  if (!d.q4 && d.HD == 128) RB_STEP(false, 128)
-  if (!d.q4 && d.HD == 64) RB_STEP(false, 64)
+  if (d.q4 == 1 && d.HD == 128) RB_STEP(1, 128)
+  if (d.q4 == 1 && d.HD == 64) RB_STEP(1, 64)
+  if (d.q4 == 2 && d.HD == 128) RB_STEP(2, 128)
+  if (d.q4 == 2 && d.HD == 64) RB_STEP(2, 64)
+  if (d.q4 == 0 && d.HD == 128) RB_STEP(0, 128)
+  if (d.q4 == 0 && d.HD == 64) RB_STEP(0, 64)
 #undef RB_STEP
   return -2;
 }

@@ -7,6 +7,9 @@ namespace rb {
 
 static __device__ int g_sg_status = 0;
 
+// Set by the entry points for the launch they are about to make: scales / biases are fp16.
+static thread_local int t_scale_f16 = 0;
+
 static int* sg_status_ptr() {
   static int* cached[64] = {nullptr};
   int dev = 0;
@@ -19,57 +22,57 @@ static int* sg_status_ptr() {
   return cached[dev];
 }
 
-template <bool Q4, int B, bool F32>
+template <int WK, int B, bool F32>
 static int run_dense(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
                      const void* norm_w, float eps, const void* res, int res_stride, void* out,
                      int out_stride, int N, int K, int pdl, cudaStream_t st) {
-  SgDense<Q4, B, F32> P;
-  P.W = sg_weights(Q4, w, sc, bi, K);
+  SgDense<WK, B, F32> P;
+  P.W = sg_weights(WK, w, sc, bi, K);
   P.N = N; P.K = K;
   P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
   P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
   P.residual = static_cast<const __nv_bfloat16*>(res); P.res_stride = res_stride;
   P.out = out; P.out_stride = out_stride;
-  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, false, (N + 3) / 4, sm_count(), 1 << 20, sg_x_bytes(Q4, K, B), 0, B);
+  const SgPlan pl = sg_make_plan(WK | (t_scale_f16 << 8), P.W.units, 1, false, (N + 3) / 4, sm_count(), 1 << 20, sg_x_bytes(WK, K, B), 0, B);
   return sg_launch(P, pl, pl.grid, sg_status_ptr(), pdl, st);
 }
 
-template <bool Q4, int B>
+template <int WK, int B>
 static int run_qkv(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
                    const void* norm_w, float eps, const SgRopeArgs& a, int K, int pdl, cudaStream_t st) {
-  SgQkvRope<Q4, B> P;
-  P.W = sg_weights(Q4, w, sc, bi, K);
+  SgQkvRope<WK, B> P;
+  P.W = sg_weights(WK, w, sc, bi, K);
   P.K = K;
   P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
   P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
   P.a = a;
   const int quads = (a.Hq + 2 * a.Hkv) * (a.HD / 4);
-  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, !a.traditional, quads, sm_count(), a.HD / 4, sg_x_bytes(Q4, K, B),
-                                 SgQkvRope<Q4, B>::extra_bytes(a.HD, B), B);
+  const SgPlan pl = sg_make_plan(WK | (t_scale_f16 << 8), P.W.units, 1, !a.traditional, quads, sm_count(), a.HD / 4, sg_x_bytes(WK, K, B),
+                                 SgQkvRope<WK, B>::extra_bytes(a.HD, B), B);
   return sg_launch(P, pl, pl.grid, sg_status_ptr(), pdl, st);
 }
 
-template <bool Q4, int B>
+template <int WK, int B>
 static int run_gate_up(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
                        const void* norm_w, float eps, void* act, int act_stride, int I, int K, int pdl,
                        cudaStream_t st) {
-  SgGateUp<Q4, B> P;
-  P.W = sg_weights(Q4, w, sc, bi, K);
+  SgGateUp<WK, B> P;
+  P.W = sg_weights(WK, w, sc, bi, K);
   P.I = I; P.K = K;
   P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
   P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
   P.act = static_cast<__nv_bfloat16*>(act); P.act_stride = act_stride;
-  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, true, I / 2, sm_count(), 1 << 20, sg_x_bytes(Q4, K, B), 0, B);
+  const SgPlan pl = sg_make_plan(WK | (t_scale_f16 << 8), P.W.units, 1, true, I / 2, sm_count(), 1 << 20, sg_x_bytes(WK, K, B), 0, B);
   return sg_launch(P, pl, pl.grid, sg_status_ptr(), pdl, st);
 }
 
-template <bool Q4>
+template <int WK>
 static int run_moe_gate_up(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
                            const void* norm_w, float eps, const int* idx, void* act, int act_stride,
                            int B, int top_k, int I, int K, int expert_base, int experts_local, int pdl,
                            cudaStream_t st) {
-  SgMoeGateUp<Q4> P;
-  P.W = sg_weights(Q4, w, sc, bi, K);
+  SgMoeGateUp<WK> P;
+  P.W = sg_weights(WK, w, sc, bi, K);
   P.I = I; P.K = K;
   P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
   P.norm_w = static_cast<const __nv_bfloat16*>(norm_w); P.eps = eps;
@@ -78,17 +81,17 @@ static int run_moe_gate_up(const void* w, const void* sc, const void* bi, const 
   P.token = 0; P.ntok = B; P.packed = 0; P.mask = 0;
   const int per_token = sm_count() / B > 0 ? sm_count() / B : 1;
   const int hq = I / 2;
-  const SgPlan pl = sg_make_plan(Q4, P.W.units, 1, true, top_k * hq, per_token, hq & -hq, sg_x_bytes(Q4, K, 1), 0, 1);
+  const SgPlan pl = sg_make_plan(WK | (t_scale_f16 << 8), P.W.units, 1, true, top_k * hq, per_token, hq & -hq, sg_x_bytes(WK, K, 1), 0, 1);
   return sg_launch(P, pl, pl.grid * B, sg_status_ptr(), pdl, st);
 }
 
-template <bool Q4, bool F32>
+template <int WK, bool F32>
 static int run_moe_down(const void* w, const void* sc, const void* bi, const void* act, int act_stride,
                         const int* idx, const float* tw, const void* res, int res_stride, void* out,
                         int out_stride, int B, int top_k, int N, int I, int expert_base,
                         int experts_local, int pdl, cudaStream_t st) {
-  SgMoeDown<Q4, F32> P;
-  P.W = sg_weights(Q4, w, sc, bi, I);
+  SgMoeDown<WK, F32> P;
+  P.W = sg_weights(WK, w, sc, bi, I);
   P.N = N; P.I = I;
   P.act = static_cast<const __nv_bfloat16*>(act); P.act_stride = act_stride;
   P.R = SgRouting{idx, tw, top_k, expert_base, experts_local};
@@ -96,8 +99,8 @@ static int run_moe_down(const void* w, const void* sc, const void* bi, const voi
   P.residual = static_cast<const __nv_bfloat16*>(res); P.res_stride = res_stride;
   P.out = out; P.out_stride = out_stride;
   const int per_token = sm_count() / B > 0 ? sm_count() / B : 1;
-  const SgPlan pl = sg_make_plan(Q4, P.W.units, top_k, false, (N + 3) / 4, per_token, 1 << 20,
-                                 sg_x_bytes(Q4, top_k * I, 1), 64, 1);
+  const SgPlan pl = sg_make_plan(WK | (t_scale_f16 << 8), P.W.units, top_k, false, (N + 3) / 4, per_token, 1 << 20,
+                                 sg_x_bytes(WK, top_k * I, 1), 64, 1);
   return sg_launch(P, pl, pl.grid * B, sg_status_ptr(), pdl, st);
 }
 
@@ -131,16 +134,18 @@ extern "C" int rmlx_sg_rms_gemv(int w_kind, const void* w, const void* scales, c
                                 const void* x, int x_stride, const void* norm_w, float eps,
                                 const void* residual, int res_stride, void* out, int out_stride,
                                 int out_f32, int B, int N, int K, int pdl, cudaStream_t st) {
-  if (B < 1 || N < 1 || w_kind < 0 || w_kind > 1 || !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+  t_scale_f16 = (w_kind >> 8) & 1;   // bit 8: fp16 scales and biases
+  w_kind &= 0xff;
+  if (B < 1 || N < 1 || w_kind < 0 || w_kind > 2 || !sg_weights_ok(w_kind, w, scales, biases, K))
     return -2;
 #define SG_ARGS w, scales, biases, x, x_stride, norm_w, eps, residual, res_stride, out, out_stride, N, K, pdl, st
-  if (w_kind == 1) {
-    if (out_f32) { SG_DISPATCH_B(B, return (run_dense<true, kB, true>(SG_ARGS))) }
-    else { SG_DISPATCH_B(B, return (run_dense<true, kB, false>(SG_ARGS))) }
-  } else {
-    if (out_f32) { SG_DISPATCH_B(B, return (run_dense<false, kB, true>(SG_ARGS))) }
-    else { SG_DISPATCH_B(B, return (run_dense<false, kB, false>(SG_ARGS))) }
+#define SG_KIND(KIND_)                                                                  \
+  if (w_kind == KIND_) {                                                                \
+    if (out_f32) { SG_DISPATCH_B(B, return (run_dense<KIND_, kB, true>(SG_ARGS))) }     \
+    else { SG_DISPATCH_B(B, return (run_dense<KIND_, kB, false>(SG_ARGS))) }            \
   }
+  SG_KIND(0) SG_KIND(1) SG_KIND(2)
+#undef SG_KIND
 #undef SG_ARGS
   return -2;
 }
@@ -153,14 +158,17 @@ extern "C" int rmlx_sg_rms_qkv_rope(int w_kind, const void* w, const void* scale
                                     const float* sin_t, int B, int K, int Hq, int Hkv, int HD,
                                     int max_blocks, int page, int traditional, int pdl,
                                     cudaStream_t st) {
-  if (B < 1 || HD % 4 || Hq < 1 || Hkv < 1 || w_kind < 0 || w_kind > 1 ||
-      !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+  t_scale_f16 = (w_kind >> 8) & 1;   // bit 8: fp16 scales and biases
+  w_kind &= 0xff;
+  if (B < 1 || HD % 4 || Hq < 1 || Hkv < 1 || w_kind < 0 || w_kind > 2 ||
+      !sg_weights_ok(w_kind, w, scales, biases, K))
     return -2;
   SgRopeArgs a{static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_cache),
                static_cast<__nv_bfloat16*>(v_cache), block_table, positions, row_seq, cos_t, sin_t,
                Hq, Hkv, HD, max_blocks, page, traditional};
-  if (w_kind == 1) { SG_DISPATCH_B(B, return (run_qkv<true, kB>(w, scales, biases, x, x_stride, norm_w, eps, a, K, pdl, st))) }
-  else { SG_DISPATCH_B(B, return (run_qkv<false, kB>(w, scales, biases, x, x_stride, norm_w, eps, a, K, pdl, st))) }
+  if (w_kind == 1) { SG_DISPATCH_B(B, return (run_qkv<1, kB>(w, scales, biases, x, x_stride, norm_w, eps, a, K, pdl, st))) }
+  else if (w_kind == 2) { SG_DISPATCH_B(B, return (run_qkv<2, kB>(w, scales, biases, x, x_stride, norm_w, eps, a, K, pdl, st))) }
+  else { SG_DISPATCH_B(B, return (run_qkv<0, kB>(w, scales, biases, x, x_stride, norm_w, eps, a, K, pdl, st))) }
   return -2;
 }
 
@@ -168,10 +176,13 @@ extern "C" int rmlx_sg_rms_qkv_rope(int w_kind, const void* w, const void* scale
 extern "C" int rmlx_sg_gate_up(int w_kind, const void* w, const void* scales, const void* biases,
                                const void* x, int x_stride, const void* norm_w, float eps, void* act,
                                int act_stride, int B, int I, int K, int pdl, cudaStream_t st) {
-  if (B < 1 || I < 2 || I % 2 || w_kind < 0 || w_kind > 1 || !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+  t_scale_f16 = (w_kind >> 8) & 1;   // bit 8: fp16 scales and biases
+  w_kind &= 0xff;
+  if (B < 1 || I < 2 || I % 2 || w_kind < 0 || w_kind > 2 || !sg_weights_ok(w_kind, w, scales, biases, K))
     return -2;
-  if (w_kind == 1) { SG_DISPATCH_B(B, return (run_gate_up<true, kB>(w, scales, biases, x, x_stride, norm_w, eps, act, act_stride, I, K, pdl, st))) }
-  else { SG_DISPATCH_B(B, return (run_gate_up<false, kB>(w, scales, biases, x, x_stride, norm_w, eps, act, act_stride, I, K, pdl, st))) }
+  if (w_kind == 1) { SG_DISPATCH_B(B, return (run_gate_up<1, kB>(w, scales, biases, x, x_stride, norm_w, eps, act, act_stride, I, K, pdl, st))) }
+  else if (w_kind == 2) { SG_DISPATCH_B(B, return (run_gate_up<2, kB>(w, scales, biases, x, x_stride, norm_w, eps, act, act_stride, I, K, pdl, st))) }
+  else { SG_DISPATCH_B(B, return (run_gate_up<0, kB>(w, scales, biases, x, x_stride, norm_w, eps, act, act_stride, I, K, pdl, st))) }
   return -2;
 }
 
@@ -181,14 +192,18 @@ extern "C" int rmlx_sg_moe_gate_up(int w_kind, const void* w, const void* scales
                                    const int* topk_idx, void* act, int act_stride, int B, int top_k,
                                    int I, int K, int expert_base, int experts_local, int pdl,
                                    cudaStream_t st) {
+  t_scale_f16 = (w_kind >> 8) & 1;   // bit 8: fp16 scales and biases
+  w_kind &= 0xff;
   if (B < 1 || top_k < 1 || top_k > kSgMaxTopK || I % 2 || experts_local > 256 || w_kind < 0 ||
-      w_kind > 1 || !sg_weights_ok(w_kind == 1, w, scales, biases, K))
+      w_kind > 2 || !sg_weights_ok(w_kind, w, scales, biases, K))
     return -2;
-  if (w_kind == 1)
-    return run_moe_gate_up<true>(w, scales, biases, x, x_stride, norm_w, eps, topk_idx, act, act_stride,
-                                 B, top_k, I, K, expert_base, experts_local, pdl, st);
-  return run_moe_gate_up<false>(w, scales, biases, x, x_stride, norm_w, eps, topk_idx, act, act_stride, B,
-                                top_k, I, K, expert_base, experts_local, pdl, st);
+#define SG_MGU(KIND_)                                                                                   \
+  if (w_kind == KIND_)                                                                                  \
+    return run_moe_gate_up<KIND_>(w, scales, biases, x, x_stride, norm_w, eps, topk_idx, act, act_stride, \
+                                  B, top_k, I, K, expert_base, experts_local, pdl, st);
+  SG_MGU(0) SG_MGU(1) SG_MGU(2)
+#undef SG_MGU
+  return -2;
 }
 
 // Same contract as rmlx_moe_down; at most 256 local experts.
@@ -197,15 +212,18 @@ extern "C" int rmlx_sg_moe_down(int w_kind, const void* w, const void* scales, c
                                 const float* topk_w, const void* residual, int res_stride, void* out,
                                 int out_stride, int out_f32, int B, int top_k, int N, int I,
                                 int expert_base, int experts_local, int pdl, cudaStream_t st) {
-  if (B < 1 || top_k < 1 || top_k > kSgMaxTopK || experts_local > 256 || w_kind < 0 || w_kind > 1 ||
-      !sg_weights_ok(w_kind == 1, w, scales, biases, I) || (w_kind == 0 && I % 32))
+  t_scale_f16 = (w_kind >> 8) & 1;   // bit 8: fp16 scales and biases
+  w_kind &= 0xff;
+  if (B < 1 || top_k < 1 || top_k > kSgMaxTopK || experts_local > 256 || w_kind < 0 || w_kind > 2 ||
+      !sg_weights_ok(w_kind, w, scales, biases, I) || (w_kind == 0 && I % 32))
     return -2;
 #define SG_DOWN(Q4_, F32_)                                                                         \
   return run_moe_down<Q4_, F32_>(w, scales, biases, act, act_stride, topk_idx, topk_w, residual,  \
                                  res_stride, out, out_stride, B, top_k, N, I, expert_base,       \
                                  experts_local, pdl, st)
-  if (w_kind == 1) { if (out_f32) SG_DOWN(true, true); else SG_DOWN(true, false); }
-  else { if (out_f32) SG_DOWN(false, true); else SG_DOWN(false, false); }
+  if (w_kind == 1) { if (out_f32) SG_DOWN(1, true); else SG_DOWN(1, false); }
+  else if (w_kind == 2) { if (out_f32) SG_DOWN(2, true); else SG_DOWN(2, false); }
+  else { if (out_f32) SG_DOWN(0, true); else SG_DOWN(0, false); }
 #undef SG_DOWN
   return -2;
 }

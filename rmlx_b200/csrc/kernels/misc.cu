@@ -228,6 +228,51 @@ extern "C" int rmlx_silu_mul(const void* gate_up, void* act, long long T, int I,
   return static_cast<int>(cudaGetLastError());
 }
 
+// Affine group-64 dequantisation to bf16: w = scale * q + bias, q packed little-endian in 32-bit
+// words (4 or 8 bits per value). One thread per packed word. The prompt path expands 8-bit weights
+// this way before its bf16 tensor-core GEMM (the 4-bit weights are expanded inside the GEMM).
+// Reference: dequantize rows of affine_qmm (crates/rmlx-core/src/ops/quantized.rs:2755).
+template <int BITS, bool SF16>
+__global__ void __launch_bounds__(256)
+dequant_affine_kernel(const uint32_t* __restrict__ w, const uint16_t* __restrict__ scales,
+                      const uint16_t* __restrict__ biases, __nv_bfloat16* __restrict__ out,
+                      long long words, int K) {
+  constexpr int PER = 32 / BITS;
+  const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+  if (i >= words) return;
+  const int wpr = K / PER;                       // words per row
+  const long long row = i / wpr;
+  const int col = int(i - row * wpr) * PER;
+  const long long g = row * (K / 64) + col / 64;
+  const float sc = SF16 ? __half2float(__ushort_as_half(scales[g])) : bf16lo(scales[g]);
+  const float bi = SF16 ? __half2float(__ushort_as_half(biases[g])) : bf16lo(biases[g]);
+  const uint32_t v = w[i];
+  __nv_bfloat16* o = out + row * K + col;
+#pragma unroll
+  for (int j = 0; j < PER; j += 2) {
+    const float a = float((v >> (j * BITS)) & ((1u << BITS) - 1u)) * sc + bi;
+    const float b = float((v >> ((j + 1) * BITS)) & ((1u << BITS) - 1u)) * sc + bi;
+    *reinterpret_cast<uint32_t*>(o + j) = pack_bf16(a, b);
+  }
+}
+
+// w: packed words of `rows` x K values (bits 4 or 8), scales / biases [rows, K/64] in bf16 or
+// (scale_f16) fp16, out bf16.
+extern "C" int rmlx_dequant_affine(const void* w, const void* scales, const void* biases, void* out,
+                                   long long rows, int K, int bits, int scale_f16, cudaStream_t st) {
+  if (rows < 1 || K % 64 || (bits != 4 && bits != 8)) return -2;
+  const long long words = rows * (K / (32 / bits));
+  const unsigned grid = unsigned((words + 255) / 256);
+#define RB_DQ(BITS_, SF_)                                                                         \
+  dequant_affine_kernel<BITS_, SF_><<<grid, 256, 0, st>>>(                                        \
+      static_cast<const uint32_t*>(w), static_cast<const uint16_t*>(scales),                      \
+      static_cast<const uint16_t*>(biases), static_cast<__nv_bfloat16*>(out), words, K)
+  if (bits == 4) { if (scale_f16) RB_DQ(4, true); else RB_DQ(4, false); }
+  else { if (scale_f16) RB_DQ(8, true); else RB_DQ(8, false); }
+#undef RB_DQ
+  return static_cast<int>(cudaGetLastError());
+}
+
 extern "C" int rmlx_fp8_quant_rows(const void* x, void* q, float* scales, int T, int D,
                                    cudaStream_t st) {
   if (T < 1) return -2;

@@ -78,6 +78,8 @@ struct SgPlan {
   int extra_bytes;   // problem-specific shared memory
   int grid;          // blocks (per token for the per-token problems); 0 = shape not supported
   int drop_stage;    // test hook: block 0's producer withholds this stage (-1: none)
+  int srow;          // quantised weights: bytes of scales (and of biases) per row
+  int scale_f16;     // scales and biases are fp16 (MLX checkpoints in half precision), else bf16
 };
 
 __host__ __device__ inline int sg_part_floats(int ns, int qpt, int B) { return ns * kSgConsumerWarps * qpt * 4 * B; }
@@ -89,9 +91,13 @@ __host__ inline size_t sg_smem_bytes(const SgPlan& p, int B);
 // `pairs`: quads are two row pairs from two segments; `quads`: quads to spread over at most
 // `max_ctas` blocks; `qs_cap`: upper bound on quads per stage (a stage must not straddle a head or
 // an expert). Returns grid == 0 when the shape does not fit.
-__host__ inline SgPlan sg_make_plan(bool q4, int units, int nslots, bool pairs, int quads, int max_ctas,
+// `kind`: 0 bf16 weights, 1 4-bit affine, 2 8-bit affine (group 64, bf16 scale and bias).
+__host__ inline SgPlan sg_make_plan(int kind, int units, int nslots, bool pairs, int quads, int max_ctas,
                                     int qs_cap, int x_bytes, int extra_bytes, int B) {
   SgPlan p{};
+  const int base_kind = kind & 0xff;    // bit 8 of `kind`: fp16 scales and biases
+  const bool q4 = base_kind != 0;       // quantised: scales and biases travel with the weights
+  p.srow = base_kind == 1 ? units : base_kind == 2 ? units / 2 : 0;
   int best_lw = 32, best_pad = 1 << 30;
   const int lws[3] = {32, 16, 8};
   for (int i = 0; i < 3; ++i) {
@@ -128,7 +134,7 @@ __host__ inline SgPlan sg_make_plan(bool q4, int units, int nslots, bool pairs, 
   p.seg_rows = (pairs ? 2 : 4) * p.QS;
   p.w_row_bytes = (p.KP == 1 ? units : p.spp * p.LW) * 16;
   p.w_seg_bytes = p.seg_rows * p.w_row_bytes;
-  p.aux_seg_bytes = q4 ? ((p.seg_rows * units + 32 + 15) & ~15) : 0;
+  p.aux_seg_bytes = q4 ? ((p.seg_rows * p.srow + 32 + 15) & ~15) : 0;
   p.aux_off = (p.nseg * p.w_seg_bytes + 127) & ~127;
   p.stage_bytes = (p.aux_off + 2 * p.nseg * p.aux_seg_bytes + 127) & ~127;
   p.x_bytes = (x_bytes + 127) & ~127;
@@ -145,6 +151,7 @@ __host__ inline SgPlan sg_make_plan(bool q4, int units, int nslots, bool pairs, 
   }
   p.grid = (quads + qpc - 1) / qpc;
   p.drop_stage = -1;
+  p.scale_f16 = kind >> 8 & 1;
   (void)B;
   return p;
 }
@@ -195,12 +202,12 @@ __device__ __forceinline__ float sg_consumer_sum(float v, float* red) {
 // of rows 0 / 2, the next row's is `units` bytes on, the biases `bias_off` bytes on.
 template <int B>
 __device__ __forceinline__ void sg_task_q4(const uint4 (&w)[4], uint32_t alo, uint32_t ahi, uint32_t units,
-                                           uint32_t bias_off, const char* xs, size_t xstride, int NHG,
-                                           int xunit, float (&acc)[4][B]) {
-  auto lds16 = [](uint32_t addr) -> float {
+                                           uint32_t bias_off, bool sf16, const char* xs, size_t xstride,
+                                           int NHG, int xunit, float (&acc)[4][B]) {
+  auto lds16 = [sf16](uint32_t addr) -> float {
     uint16_t v;
     asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
-    return bf16lo(v);
+    return sf16 ? __half2float(__ushort_as_half(v)) : bf16lo(v);
   };
 #pragma unroll
   for (int b = 0; b < B; ++b) {
@@ -229,6 +236,40 @@ __device__ __forceinline__ void sg_task_q4(const uint4 (&w)[4], uint32_t alo, ui
       const uint32_t a = ((r >> 1) ? ahi : alo) + ((r & 1) ? units : 0u);
       const float sc = lds16(a), bi = lds16(a + bias_off);
       const float2 f0 = __half22float2(a0[r]), f1 = __half22float2(a1[r]);
+      const float qx = ((f0.x + f0.y) + (f1.x + f1.y)) * qmul;
+      acc[r][b] = fmaf(sc, qx, fmaf(bi, xsum, acc[r][b]));
+    }
+  }
+}
+
+// One task of the 8-bit path: rows w0..w3 (16 weights each) against the staged activations.
+template <int B>
+__device__ __forceinline__ void sg_task_q8(const uint4 (&w)[4], uint32_t alo, uint32_t ahi, uint32_t srow,
+                                           uint32_t bias_off, bool sf16, const char* xs, size_t xstride,
+                                           int NU, int xunit, float (&acc)[4][B]) {
+  auto lds16 = [sf16](uint32_t addr) -> float {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=h"(v) : "r"(addr));
+    return sf16 ? __half2float(__ushort_as_half(v)) : bf16lo(v);
+  };
+#pragma unroll
+  for (int b = 0; b < B; ++b) {
+    const uint4* xh = reinterpret_cast<const uint4*>(xs + b * xstride);
+    const float* aux = reinterpret_cast<const float*>(xs + b * xstride + size_t(NU) * 32);
+    const float xsum = aux[xunit], qmul = aux[NU + xunit];
+    const uint4 x0 = xh[xunit], x1 = xh[NU + xunit];
+    const __half2* h0 = reinterpret_cast<const __half2*>(&x0);
+    const __half2* h1 = reinterpret_cast<const __half2*>(&x1);
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      __half2 a0 = __float2half2_rn(0.f), a1 = a0;
+      q8_word_fma(w[r].x, h0[0], h0[1], a0, a1);
+      q8_word_fma(w[r].y, h0[2], h0[3], a0, a1);
+      q8_word_fma(w[r].z, h1[0], h1[1], a0, a1);
+      q8_word_fma(w[r].w, h1[2], h1[3], a0, a1);
+      const uint32_t a = ((r >> 1) ? ahi : alo) + ((r & 1) ? srow : 0u);
+      const float sc = lds16(a), bi = lds16(a + bias_off);
+      const float2 f0 = __half22float2(a0), f1 = __half22float2(a1);
       const float qx = ((f0.x + f0.y) + (f1.x + f1.y)) * qmul;
       acc[r][b] = fmaf(sc, qx, fmaf(bi, xsum, acc[r][b]));
     }
@@ -315,7 +356,8 @@ struct SgSegSrc {
 };
 
 // A problem P provides:
-//   static constexpr bool kQ4; static constexpr int kB; static constexpr bool kWeightsNeedWait;
+//   static constexpr int kKind (0 bf16, 1 Q4, 2 Q8); static constexpr int kB;
+//   static constexpr bool kWeightsNeedWait;
 //   static constexpr bool kMultiSlot                     rows chained along K over several segments
 //   void cta_range(const SgPlan&, int& q0, int& q1)      this block's quads
 //   void init(bool producer)                             every thread; consumers call it after
@@ -375,9 +417,9 @@ __device__ __forceinline__ bool sg_produce(P& prob, const SgPlan& pl, SgSmem& sm
             bulk_g2s(dst + size_t(r) * pl.w_row_bytes, src.w + (size_t(r) * pl.units + u0) * 16, n, sm.c->full + s);
           bytes += n * uint32_t(src.rows);
         }
-        if (P::kQ4) {
+        if (P::kKind != 0) {
           const uintptr_t a = reinterpret_cast<uintptr_t>(src.sc), b2 = reinterpret_cast<uintptr_t>(src.bi);
-          const uint32_t span = uint32_t(src.rows) * uint32_t(pl.units);
+          const uint32_t span = uint32_t(src.rows) * uint32_t(pl.srow);
           const uintptr_t alo = a & ~uintptr_t(15), ahi = (a + span + 15) & ~uintptr_t(15);
           const uintptr_t blo = b2 & ~uintptr_t(15), bhi = (b2 + span + 15) & ~uintptr_t(15);
           char* ax = stage + pl.aux_off + size_t(lane) * 2 * pl.aux_seg_bytes;
@@ -428,12 +470,13 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
   const int tr = warp / pl.SQ, sq = warp - tr * pl.SQ;
   const int sub = lane / LW, l = lane - sub * LW;
   const int xunits = prob.xunits();
-  const size_t xstride = P::kQ4 ? (size_t(xunits) * 72 + 15) & ~size_t(15) : size_t(xunits) * 32;
+  const size_t xstride = P::kKind == 1 ? (size_t(xunits) * 72 + 15) & ~size_t(15)
+                         : P::kKind == 2 ? size_t(xunits) * 40 : size_t(xunits) * 32;
   const int qi = tr * QPT + sub;                    // this lane group's quad inside a stage
   const int nsl = pl.spl * nslots;                  // slices per output row (all slots)
   // rows of the quad inside a stage: pairs come from segments 0 and 1, consecutive rows from one
   const int row_lo = pl.pairs ? 2 * qi : 4 * qi, row_hi = pl.pairs ? 2 * qi : 4 * qi + 2;
-  const uint32_t rowb = uint32_t(pl.w_row_bytes), units = uint32_t(pl.units);
+  const uint32_t rowb = uint32_t(pl.w_row_bytes), units = uint32_t(pl.srow);   // `units`: bytes between rows' scales
   const uint32_t w_lo_off = uint32_t(row_lo) * rowb, w_hi_off = (pl.pairs ? uint32_t(pl.w_seg_bytes) : 0u) + uint32_t(row_hi) * rowb;
   const uint32_t a_lo_off = uint32_t(pl.aux_off) + uint32_t(row_lo) * units;
   const uint32_t a_hi_off = uint32_t(pl.aux_off) + (pl.pairs ? 2u * uint32_t(pl.aux_seg_bytes) : 0u) + uint32_t(row_hi) * units;
@@ -470,8 +513,9 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
           t.w[2] = *reinterpret_cast<const uint4*>(sbase + w_hi_off + ucol);
           t.w[3] = *reinterpret_cast<const uint4*>(sbase + w_hi_off + rowb + ucol);
           t.xunit = slot * pl.units + u;
-          if (P::kQ4) {
-            const char* abase = stage + (P::kMultiSlot ? uint32_t(slot) * 2u * uint32_t(pl.aux_seg_bytes) : 0u) + (u & ~1);
+          if (P::kKind != 0) {
+            const char* abase = stage + (P::kMultiSlot ? uint32_t(slot) * 2u * uint32_t(pl.aux_seg_bytes) : 0u) +
+                                (P::kKind == 1 ? (u & ~1) : ((u >> 2) << 1));
             // the biases sit aux_seg_bytes after the scales (the launcher checks that both arrays start at
             // the same remainder modulo 16, so one remainder serves both)
             t.alo = smem_u32(abase + a_lo_off + mlo.mis_sc);
@@ -485,11 +529,13 @@ __device__ __forceinline__ void sg_consume(P& prob, const SgPlan& pl, SgSmem& sm
           load(two ? sl + pl.SQ : sl, t1);
           t1.on = t1.on && two;
           if (t0.on) {
-            if (P::kQ4) sg_task_q4<B>(t0.w, t0.alo, t0.ahi, units, uint32_t(pl.aux_seg_bytes), sm.xs, xstride, xunits, t0.xunit, acc);
+            if (P::kKind == 1) sg_task_q4<B>(t0.w, t0.alo, t0.ahi, units, uint32_t(pl.aux_seg_bytes), pl.scale_f16 != 0, sm.xs, xstride, xunits, t0.xunit, acc);
+            else if (P::kKind == 2) sg_task_q8<B>(t0.w, t0.alo, t0.ahi, units, uint32_t(pl.aux_seg_bytes), pl.scale_f16 != 0, sm.xs, xstride, xunits, t0.xunit, acc);
             else sg_task_bf16<B>(t0.w, sm.xs, xstride, xunits, t0.xunit, acc);
           }
           if (t1.on) {
-            if (P::kQ4) sg_task_q4<B>(t1.w, t1.alo, t1.ahi, units, uint32_t(pl.aux_seg_bytes), sm.xs, xstride, xunits, t1.xunit, acc);
+            if (P::kKind == 1) sg_task_q4<B>(t1.w, t1.alo, t1.ahi, units, uint32_t(pl.aux_seg_bytes), pl.scale_f16 != 0, sm.xs, xstride, xunits, t1.xunit, acc);
+            else if (P::kKind == 2) sg_task_q8<B>(t1.w, t1.alo, t1.ahi, units, uint32_t(pl.aux_seg_bytes), pl.scale_f16 != 0, sm.xs, xstride, xunits, t1.xunit, acc);
             else sg_task_bf16<B>(t1.w, sm.xs, xstride, xunits, t1.xunit, acc);
           }
         }
@@ -594,11 +640,12 @@ __global__ void __launch_bounds__(kSgThreads, 1) sg_kernel(P prob, SgPlan pl, in
 // ------------------------------------------------------------------------------------------------
 struct SgWeights {
   const char* w;    // rows of units*16 bytes
-  const char* sc;   // Q4: rows of `units` bytes (bf16 per 2 units); else unused
+  const char* sc;   // quantised: rows of `srow` bytes (one bf16 per 64 weights); else unused
   const char* bi;
   int units;
+  int srow;
   __device__ __forceinline__ SgSegSrc rows(size_t n, int count) const {
-    return SgSegSrc{w + n * size_t(units) * 16, sc + n * size_t(units), bi + n * size_t(units), count};
+    return SgSegSrc{w + n * size_t(units) * 16, sc + n * size_t(srow), bi + n * size_t(srow), count};
   }
 };
 
@@ -609,15 +656,17 @@ __host__ inline bool sg_aligned16(const void* p) { return (reinterpret_cast<uint
 
 // Activation staging for up to B vectors of K values: x (bf16, global) times an optional
 // per-channel norm weight; writes inv_rms[b] to misc[b] (1 when there is no norm).
-template <bool Q4, int B>
+template <int WK, int B>
 __device__ __forceinline__ void sg_stage_plain(SgSmem& sm, const __nv_bfloat16* x, int x_stride,
                                                const __nv_bfloat16* norm_w, float eps, int K) {
   const int tid = threadIdx.x;
-  const size_t xstride = Q4 ? (size_t(K >> 5) * 72 + 15) & ~size_t(15) : size_t(K >> 3) * 32;
+  const size_t xstride = WK == 1 ? (size_t(K >> 5) * 72 + 15) & ~size_t(15)
+                         : WK == 2 ? size_t(K >> 4) * 40 : size_t(K >> 3) * 32;
 #pragma unroll
   for (int b = 0; b < B; ++b) {
     XLoadBf16 ld{x + size_t(b) * x_stride, norm_w, 0.f};
-    if (Q4) XStage<WQ4>::stage_part(sm.xs + b * xstride, K, ld, tid, kSgConsumers);
+    if (WK == 1) XStage<WQ4>::stage_part(sm.xs + b * xstride, K, ld, tid, kSgConsumers);
+    else if (WK == 2) XStage<WQ8>::stage_part(sm.xs + b * xstride, K, ld, tid, kSgConsumers);
     else XStage<WBf16>::stage_part(sm.xs + b * xstride, K, ld, tid, kSgConsumers);
     if (norm_w) {
       const float ssq = sg_consumer_sum(ld.ssq, sm.c->misc + 4);

@@ -22,9 +22,9 @@ constexpr int kSgMaxTopK = 8;
 __device__ __forceinline__ float sg_silu_mul(float g, float u) { return g / (1.f + __expf(-g)) * u; }
 
 // ------------------------------------------------------------------------------------------------
-template <bool Q4, int B, bool OUT_F32>
+template <int WK, int B, bool OUT_F32>
 struct SgDense {
-  static constexpr bool kQ4 = Q4;
+  static constexpr int kKind = WK;
   static constexpr int kB = B;
   static constexpr bool kWeightsNeedWait = false;
   static constexpr bool kMultiSlot = false;
@@ -40,11 +40,11 @@ struct SgDense {
   }
   __device__ void init(bool) {}
   __device__ int nslots() const { return 1; }
-  __device__ int xunits() const { return Q4 ? K >> 5 : K >> 3; }
+  __device__ int xunits() const { return WK == 1 ? K >> 5 : WK == 2 ? K >> 4 : K >> 3; }
   __device__ SgSegSrc seg(const SgPlan&, int sq0, int nq, int) const {
     return W.rows(size_t(sq0) * 4, min(4 * nq, N - 4 * sq0));
   }
-  __device__ void stage_x(SgSmem& sm, const SgPlan&) { sg_stage_plain<Q4, B>(sm, x, x_stride, norm_w, eps, K); }
+  __device__ void stage_x(SgSmem& sm, const SgPlan&) { sg_stage_plain<WK, B>(sm, x, x_stride, norm_w, eps, K); }
   __device__ void epilogue(int quad, float (&v)[4][B], SgSmem& sm) {
 #pragma unroll
     for (int b = 0; b < B; ++b) {
@@ -80,9 +80,9 @@ struct SgRopeArgs {
 // A quad is the two rotation pairs (2p, 2p+1) of one head: rows {2p, 2p+1, HD/2+2p, HD/2+2p+1}
 // (or four consecutive rows in the interleaved "traditional" layout), so the rotation happens on
 // the fp32 dot products and the un-rotated projection never reaches memory.
-template <bool Q4, int B>
+template <int WK, int B>
 struct SgQkvRope {
-  static constexpr bool kQ4 = Q4;
+  static constexpr int kKind = WK;
   static constexpr int kB = B;
   static constexpr bool kWeightsNeedWait = false;
   static constexpr bool kMultiSlot = false;
@@ -97,7 +97,7 @@ struct SgQkvRope {
   }
   __device__ void init(bool) {}
   __device__ int nslots() const { return 1; }
-  __device__ int xunits() const { return Q4 ? K >> 5 : K >> 3; }
+  __device__ int xunits() const { return WK == 1 ? K >> 5 : WK == 2 ? K >> 4 : K >> 3; }
   __device__ SgSegSrc seg(const SgPlan&, int sq0, int nq, int g) const {
     if (a.traditional) return W.rows(size_t(sq0) * 4, 4 * nq);
     const int qph = a.HD >> 2, head = sq0 / qph, p0 = sq0 - head * qph;
@@ -121,7 +121,7 @@ struct SgQkvRope {
         pi[1] = a.block_table[size_t(seq) * a.max_blocks + pos / a.page];
       }
     }
-    sg_stage_plain<Q4, B>(sm, x, x_stride, norm_w, eps, K);
+    sg_stage_plain<WK, B>(sm, x, x_stride, norm_w, eps, K);
   }
   __device__ void epilogue(int quad, float (&v)[4][B], SgSmem& sm) {
     const int half = a.HD >> 1, qph = a.HD >> 2, head = quad / qph, p = quad - head * qph;
@@ -172,9 +172,9 @@ struct SgQkvRope {
 // ------------------------------------------------------------------------------------------------
 // Dense SwiGLU first half: W holds the gate rows [0, I) then the up rows [I, 2I); a quad is
 // {gate 2q, gate 2q+1, up 2q, up 2q+1}.
-template <bool Q4, int B>
+template <int WK, int B>
 struct SgGateUp {
-  static constexpr bool kQ4 = Q4;
+  static constexpr int kKind = WK;
   static constexpr int kB = B;
   static constexpr bool kWeightsNeedWait = false;
   static constexpr bool kMultiSlot = false;
@@ -189,11 +189,11 @@ struct SgGateUp {
   }
   __device__ void init(bool) {}
   __device__ int nslots() const { return 1; }
-  __device__ int xunits() const { return Q4 ? K >> 5 : K >> 3; }
+  __device__ int xunits() const { return WK == 1 ? K >> 5 : WK == 2 ? K >> 4 : K >> 3; }
   __device__ SgSegSrc seg(const SgPlan&, int sq0, int nq, int g) const {
     return W.rows(size_t(g ? I : 0) + 2 * size_t(sq0), 2 * nq);
   }
-  __device__ void stage_x(SgSmem& sm, const SgPlan&) { sg_stage_plain<Q4, B>(sm, x, x_stride, norm_w, eps, K); }
+  __device__ void stage_x(SgSmem& sm, const SgPlan&) { sg_stage_plain<WK, B>(sm, x, x_stride, norm_w, eps, K); }
   __device__ void epilogue(int quad, float (&v)[4][B], SgSmem& sm) {
 #pragma unroll
     for (int b = 0; b < B; ++b) {
@@ -221,9 +221,9 @@ struct SgRouting {
   }
 };
 
-template <bool Q4>
+template <int WK>
 struct SgMoeGateUp {
-  static constexpr bool kQ4 = Q4;
+  static constexpr int kKind = WK;
   static constexpr int kB = 1;
   static constexpr bool kWeightsNeedWait = true;
   static constexpr bool kMultiSlot = false;
@@ -244,7 +244,7 @@ struct SgMoeGateUp {
   }
   __device__ void init(bool) { R.load(token, packed, mask); }
   __device__ int nslots() const { return 1; }
-  __device__ int xunits() const { return Q4 ? K >> 5 : K >> 3; }
+  __device__ int xunits() const { return WK == 1 ? K >> 5 : WK == 2 ? K >> 4 : K >> 3; }
   __device__ SgSegSrc seg(const SgPlan&, int sq0, int nq, int g) const {
     const int hq = I >> 1, s = sq0 / hq, i2 = sq0 - s * hq;
     if (!((mask >> s) & 1u)) return SgSegSrc{nullptr, nullptr, nullptr, 0};
@@ -252,7 +252,7 @@ struct SgMoeGateUp {
     return W.rows(size_t(e) * 2 * I + (g ? I : 0) + 2 * size_t(i2), 2 * nq);
   }
   __device__ void stage_x(SgSmem& sm, const SgPlan&) {
-    sg_stage_plain<Q4, 1>(sm, x + size_t(token) * x_stride, 0, norm_w, eps, K);
+    sg_stage_plain<WK, 1>(sm, x + size_t(token) * x_stride, 0, norm_w, eps, K);
   }
   __device__ void epilogue(int quad, float (&v)[4][1], SgSmem& sm) {
     const int hq = I >> 1, s = quad / hq, i2 = quad - s * hq;
@@ -281,9 +281,9 @@ struct XLoadMoeAct {
 };
 
 // Shared by the single-GPU and the tensor-parallel form of the expert down projection.
-template <bool Q4>
+template <int WK>
 struct SgMoeDownBase {
-  static constexpr bool kQ4 = Q4;
+  static constexpr int kKind = WK;
   static constexpr int kB = 1;
   static constexpr bool kWeightsNeedWait = true;
   static constexpr bool kMultiSlot = true;
@@ -308,7 +308,7 @@ struct SgMoeDownBase {
     }
   }
   __device__ int nslots() const { return nloc; }
-  __device__ int xunits() const { return nloc * (Q4 ? I >> 5 : I >> 3); }
+  __device__ int xunits() const { return nloc * (WK == 1 ? I >> 5 : WK == 2 ? I >> 4 : I >> 3); }
   __device__ SgSegSrc seg(const SgPlan&, int sq0, int nq, int g) const {
     const int e = int((packed >> (8 * g)) & 0xffull);
     return W.rows(size_t(e) * N + 4 * size_t(sq0), min(4 * nq, N - 4 * sq0));
@@ -327,15 +327,16 @@ struct SgMoeDownBase {
     sg_consumer_sync();
     if (nloc > 0) {
       XLoadMoeAct ld{act + size_t(token) * R.top_k * act_stride, act_stride, I >> 3, slot_of, w_of};
-      if (Q4) XStage<WQ4>::stage_part(sm.xs, nloc * I, ld, threadIdx.x, kSgConsumers);
+      if (WK == 1) XStage<WQ4>::stage_part(sm.xs, nloc * I, ld, threadIdx.x, kSgConsumers);
+      else if (WK == 2) XStage<WQ8>::stage_part(sm.xs, nloc * I, ld, threadIdx.x, kSgConsumers);
       else XStage<WBf16>::stage_part(sm.xs, nloc * I, ld, threadIdx.x, kSgConsumers);
     }
     sg_consumer_sync();
   }
 };
 
-template <bool Q4, bool OUT_F32>
-struct SgMoeDown : SgMoeDownBase<Q4> {
+template <int WK, bool OUT_F32>
+struct SgMoeDown : SgMoeDownBase<WK> {
   const __nv_bfloat16* residual; int res_stride;
   void* out; int out_stride;
   __device__ void init(bool) { this->load_routing(); }
@@ -359,22 +360,24 @@ struct SgMoeDown : SgMoeDownBase<Q4> {
 // ------------------------------------------------------------------------------------------------
 // Host-side helpers shared by the launchers.
 // ------------------------------------------------------------------------------------------------
-inline SgWeights sg_weights(bool q4, const void* w, const void* sc, const void* bi, int K) {
+inline SgWeights sg_weights(int kind, const void* w, const void* sc, const void* bi, int K) {
   SgWeights W;
   W.w = static_cast<const char*>(w);
   W.sc = static_cast<const char*>(sc);
   W.bi = static_cast<const char*>(bi);
-  W.units = q4 ? K >> 5 : K >> 3;
+  W.units = kind == 1 ? K >> 5 : kind == 2 ? K >> 4 : K >> 3;
+  W.srow = kind != 0 ? K >> 5 : 0;        // one bf16 per 64 weights
   return W;
 }
-inline bool sg_weights_ok(bool q4, const void* w, const void* sc, const void* bi, int K) {
-  if (q4)
+inline bool sg_weights_ok(int kind, const void* w, const void* sc, const void* bi, int K) {
+  if (kind != 0)
     return K % 64 == 0 && sg_aligned16(w) && sc && bi && (reinterpret_cast<uintptr_t>(sc) & 1u) == 0 &&
            ((reinterpret_cast<uintptr_t>(sc) ^ reinterpret_cast<uintptr_t>(bi)) & 15u) == 0;
   return K % 8 == 0 && sg_aligned16(w);
 }
-inline int sg_x_bytes(bool q4, int K, int B) {
-  const size_t one = q4 ? (size_t(K >> 5) * 72 + 15) & ~size_t(15) : size_t(K >> 3) * 32;
+inline int sg_x_bytes(int kind, int K, int B) {
+  const size_t one = kind == 1 ? (size_t(K >> 5) * 72 + 15) & ~size_t(15)
+                     : kind == 2 ? size_t(K >> 4) * 40 : size_t(K >> 3) * 32;
   return int(one * B);
 }
 

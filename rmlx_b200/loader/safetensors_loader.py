@@ -23,7 +23,7 @@ import torch
 
 from ..config import FeedForwardType, MoeConfig, QuantConfig, TransformerConfig
 from ..models.weights import LayerWeights, ModelWeights, ParallelLayout, _split, is_moe_layer
-from ..ops.weights import GROUP, LinearWeight, W_BF16, W_Q4
+from ..ops.weights import GROUP, LinearWeight, W_BF16, W_Q4, W_Q8
 
 
 def hf_name_to_internal(name: str) -> str:
@@ -108,17 +108,26 @@ class _Source:
     def __init__(self, tensors, quant: Optional[QuantConfig], dtype):
         self.t, self.q, self.dtype = tensors, quant, dtype
         self.triplets = set(detect_triplets(tensors))
-        if self.triplets and (quant is None or quant.bits != 4 or quant.group_size != GROUP):
-            raise ValueError("quantised checkpoint: only bits=4, group_size=64 is supported by the "
-                             "kernels (config.json 'quantization' block missing or different)")
+        if self.triplets and (quant is None or quant.bits not in (4, 8) or quant.group_size != GROUP):
+            raise ValueError("quantised checkpoint: bits 4 or 8 with group_size 64 is what the kernels "
+                             "support (config.json 'quantization' block missing or different)")
 
     def linear(self, prefix: str) -> LinearWeight:
         if prefix in self.triplets:
             w = self.t[prefix + ".weight"]
             if w.dtype == torch.uint32:
                 w = w.view(torch.int32)
-            return LinearWeight(W_Q4, w.contiguous(), self.t[prefix + ".scales"].to(torch.bfloat16),
-                                self.t[prefix + ".biases"].to(torch.bfloat16))
+            sc, bi = self.t[prefix + ".scales"], self.t[prefix + ".biases"]
+            # bits from the shapes (a checkpoint may mix widths): words per row * 32 / (groups * 64)
+            bits = w.shape[-1] * 32 // (sc.shape[-1] * GROUP)
+            if bits not in (4, 8):
+                raise ValueError(f"{prefix}: {bits}-bit weights are not supported (4 or 8)")
+            # scales and biases stay at checkpoint precision: fp16 is kept as fp16 (casting it to
+            # bf16 would drop three mantissa bits of every group's scale and bias); wider types
+            # go to bf16
+            if sc.dtype != torch.float16:
+                sc, bi = sc.to(torch.bfloat16), bi.to(torch.bfloat16)
+            return LinearWeight(W_Q4 if bits == 4 else W_Q8, w.contiguous(), sc.contiguous(), bi.contiguous())
         return LinearWeight(W_BF16, self.t[prefix + ".weight"].to(self.dtype))
 
     def vec(self, name: str) -> torch.Tensor:

@@ -27,7 +27,7 @@ from ..ops.attention import flash_prefill_paged
 from ..ops.gemm import GemmStatus, gemm_bf16
 from ..ops.grouped import moe_prefill_ffn
 from ..ops.quantized import qmm, xgemm
-from ..ops.weights import LinearWeight, W_BF16
+from ..ops.weights import LinearWeight, W_BF16, W_Q4
 
 
 def _mm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -39,7 +39,8 @@ def _mm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = Non
 def _gate_up_act(x: torch.Tensor, w: LinearWeight) -> torch.Tensor:
     """silu(x W_gate^T) * (x W_up^T) for W = [gate; up]: SwiGLU runs in the GEMM epilogue when the
     shape allows, else GEMM then the element-wise kernel."""
-    q4_ok = w.kind == W_BF16 or bool(_lib.cuda().rmlx_qgemm_supported(w.k))
+    q4_ok = w.kind == W_BF16 or (w.kind == W_Q4 and not w.scales_f16 and
+                                 bool(_lib.cuda().rmlx_qgemm_supported(w.k)))
     if w.n % 256 == 0 and w.k % 8 == 0 and q4_ok:
         return xgemm(x, w, swiglu=True)
     return D.silu_mul(_mm(x, w))

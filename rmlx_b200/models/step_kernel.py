@@ -16,7 +16,6 @@ from ctypes import c_float, c_int, c_void_p
 import torch
 
 from .. import _lib
-from ..ops.weights import W_Q4
 
 _lib.register_cuda_sigs({
     "rmlx_decode_step_layer_bytes": ("", "i"),
@@ -108,7 +107,7 @@ class DecodeStepKernel:
         s = self._desc = _StepDesc()
         s.num_layers, s.D, s.Hq, s.Hkv, s.HD = nl, cfg.hidden_size, hq, hkv, hd
         s.I, s.E, s.top_k = w.layers[0].experts_gate_up.n // 2, moe.num_experts, moe.num_experts_per_token
-        s.V, s.q4 = w.lm_head.n, int(w.lm_head.kind == W_Q4)
+        s.V, s.q4 = w.lm_head.n, int(w.lm_head.kind)      # weight kind: 0 bf16, 1 Q4, 2 Q8
         s.eps, s.scale = cfg.rms_norm_eps, m.scale
         s.max_blocks, s.window = eng.block_table.stride(0), int(cfg.sliding_window or 0)
         s.traditional = int(cfg.rope_traditional)

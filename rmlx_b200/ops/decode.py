@@ -64,7 +64,7 @@ def set_q4_path(path: str) -> None:
 
 
 def _wargs(w: LinearWeight):
-    return (w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases))
+    return (w.kernel_kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases))
 
 
 def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = None,
@@ -434,7 +434,7 @@ def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor
         rs = None if row_seq is None else row_seq[b0:]
         fn = _lib.cuda().rmlx_sg_rms_qkv_rope if _STREAM else None
         if fn is not None:
-            rc = fn(w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
+            rc = fn(w.kernel_kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
                     xs.stride(0), _lib.ptr(norm_w), eps, qs.data_ptr(), k_cache.data_ptr(),
                     v_cache.data_ptr(), bt.data_ptr(), positions[b0:].data_ptr(), _lib.ptr(rs),
                     cos.data_ptr(), sin.data_ptr(), bb, k, hq, hkv, d, block_table.stride(0),
@@ -443,7 +443,7 @@ def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor
                 _lib.check(rc, "sg_rms_qkv_rope")
                 continue
         rc = _lib.cuda().rmlx_rms_qkv_rope(
-            w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(), xs.stride(0),
+            w.kernel_kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(), xs.stride(0),
             _lib.ptr(norm_w), eps, qs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
             bt.data_ptr(), positions[b0:].data_ptr(), _lib.ptr(rs), cos.data_ptr(), sin.data_ptr(),
             bb, k, hq, hkv, d, block_table.stride(0), k_cache.shape[2], int(traditional), int(pdl),

@@ -12,7 +12,7 @@ import torch
 
 from .. import _lib
 from .quantized import xgemm
-from .weights import LinearWeight, W_Q4
+from .weights import LinearWeight, W_BF16, W_Q4, W_Q8
 
 
 def _grouped_ok(w: LinearWeight) -> bool:
@@ -22,6 +22,10 @@ def _grouped_ok(w: LinearWeight) -> bool:
 def grouped_expert_ffn(x_sorted: torch.Tensor, offsets: torch.Tensor, gate_up: LinearWeight,
                        down: LinearWeight) -> torch.Tensor:
     """x_sorted [R, D] bf16 (rows grouped by expert), offsets [E+1] -> [R, D]."""
+    if gate_up.kind == W_Q8 or gate_up.scales_f16:   # expanded to bf16 for the grouped tensor-core GEMM
+        gate_up = LinearWeight(W_BF16, gate_up.dense_bf16())
+    if down.kind == W_Q8 or down.scales_f16:
+        down = LinearWeight(W_BF16, down.dense_bf16())
     if not (_grouped_ok(gate_up) and _grouped_ok(down)):
         raise ImportError("shape not covered by the grouped tensor-core kernel")
     off = offsets.to(torch.int32)

@@ -48,8 +48,11 @@ def xgemm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = N
 
 def qmm(x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = None,
         out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
-    assert w.kind == W_Q4
-    if _lib.cuda().rmlx_qgemm_supported(w.k):
+    """x @ W^T for affine-quantised W: 4-bit weights are expanded inside the tensor-core GEMM's main
+    loop; 8-bit weights, weights with fp16 scales and 4-bit shapes the fused kernel does not take are
+    expanded to bf16 by the
+    dequantisation kernel first and go through the bf16 tensor-core GEMM."""
+    assert w.kind != 0
+    if w.kind == W_Q4 and not w.scales_f16 and _lib.cuda().rmlx_qgemm_supported(w.k):
         return xgemm(x, w, residual, out, pdl=pdl)
-    dense = w.dequantized().to(torch.bfloat16)
-    return gemm_bf16(x, dense, residual=residual, out=out, pdl=pdl)
+    return gemm_bf16(x, w.dense_bf16(), residual=residual, out=out, pdl=pdl)

@@ -1,8 +1,10 @@
 """Weight containers shared by the kernels, the reference path and the loaders.
 
-``LinearWeight`` is one [N, K] projection stored either as bf16 or in the MLX affine 4-bit layout
-(packed ``uint32`` ``[N, K/8]`` viewed as int32, bf16 ``scales``/``biases`` ``[N, K/64]``), the
-checkpoint triplet of crates/rmlx-nn/src/safetensors_loader.rs:420-552. A leading expert dimension
+``LinearWeight`` is one [N, K] projection stored either as bf16 or in the MLX affine 4-bit or 8-bit
+layout (packed ``uint32`` ``[N, K/8]`` or ``[N, K/4]`` viewed as int32, bf16 ``scales``/``biases``
+``[N, K/64]``), the checkpoint triplet of crates/rmlx-nn/src/safetensors_loader.rs:420-552; the
+8-bit kernels follow affine_qmv_fast_q8 / affine_qmm_q8
+(crates/rmlx-core/src/ops/quantized.rs:620,2755). A leading expert dimension
 turns it into a stacked expert weight ``[E, N, K]`` (crates/rmlx-nn/src/expert_group.rs:41-57).
 Row and column slicing implement the tensor-parallel shards of
 crates/rmlx-nn/src/parallel.rs:888-1130 (quantised shards re-slice packed words, scales and biases
@@ -19,30 +21,33 @@ from ..reference import ops as ref
 
 W_BF16 = 0
 W_Q4 = 1
+W_Q8 = 2
 GROUP = 64
+_BITS = {W_Q4: 4, W_Q8: 8}
 
 
 @dataclass
 class LinearWeight:
     kind: int
     w: torch.Tensor                       # bf16/fp32 [.., N, K]  or int32 [.., N, K/8]
-    scales: Optional[torch.Tensor] = None # bf16 [.., N, K/64]
+    scales: Optional[torch.Tensor] = None # bf16 (or fp16) [.., N, K/64]
     biases: Optional[torch.Tensor] = None
 
     # ---------------------------------------------------------------- construction
     @staticmethod
     def from_dense(w: torch.Tensor, quant: Optional[str] = None, dtype=torch.bfloat16,
                    device=None) -> "LinearWeight":
-        """w: fp32 [.., N, K]. quant: None | 'q4'."""
+        """w: fp32 [.., N, K]. quant: None | 'q4' | 'q8'."""
         device = device or w.device
         if quant in (None, "bf16", "none"):
             return LinearWeight(W_BF16, w.to(dtype).to(device).contiguous())
-        if quant != "q4":
+        if quant not in ("q4", "q8"):
             raise ValueError(f"unsupported quantisation {quant}")
+        bits = 4 if quant == "q4" else 8
         lead = w.shape[:-2]
         n, k = w.shape[-2:]
-        p, s, b = ref.quantize_affine(w.reshape(-1, k), 4, GROUP)
-        return LinearWeight(W_Q4, p.view(*lead, n, k // 8).to(device).contiguous(),
+        p, s, b = ref.quantize_affine(w.reshape(-1, k), bits, GROUP)
+        return LinearWeight(W_Q4 if bits == 4 else W_Q8, p.view(*lead, n, k * bits // 32).to(device).contiguous(),
                             s.view(*lead, n, k // GROUP).to(device).contiguous(),
                             b.view(*lead, n, k // GROUP).to(device).contiguous())
 
@@ -60,16 +65,18 @@ class LinearWeight:
             for r in range(0, flat.shape[0], step):
                 flat[r:r + step].normal_(0.0, std, generator=generator)
             return LinearWeight(W_BF16, w)
-        words = torch.empty(*lead, n, k // 8, dtype=torch.int32, device=device)
+        bits = 8 if quant == "q8" else 4
+        words = torch.empty(*lead, n, k * bits // 32, dtype=torch.int32, device=device)
         flat = words.view(-1)
         step = 1 << 28
         for r in range(0, flat.numel(), step):
             flat[r:r + step].random_(-(2 ** 31), 2 ** 31 - 1, generator=generator)
-        scales = torch.full((*lead, n, k // GROUP), 6.0 * std / 15.0, dtype=torch.bfloat16,
+        levels = float((1 << bits) - 1)
+        scales = torch.full((*lead, n, k // GROUP), 6.0 * std / levels, dtype=torch.bfloat16,
                             device=device)
         scales.mul_(torch.empty_like(scales).uniform_(0.75, 1.25, generator=generator))
-        biases = (-7.5 * scales.float()).to(torch.bfloat16)
-        return LinearWeight(W_Q4, words, scales, biases)
+        biases = (-0.5 * levels * scales.float()).to(torch.bfloat16)
+        return LinearWeight(W_Q4 if bits == 4 else W_Q8, words, scales, biases)
 
     # ---------------------------------------------------------------- shape
     @property
@@ -78,7 +85,7 @@ class LinearWeight:
 
     @property
     def k(self) -> int:
-        return self.w.shape[-1] * (8 if self.kind == W_Q4 else 1)
+        return self.w.shape[-1] * (8 if self.kind == W_Q4 else 4 if self.kind == W_Q8 else 1)
 
     @property
     def experts(self) -> int:
@@ -99,7 +106,40 @@ class LinearWeight:
         """fp32 [.., N, K] as the kernels see it (bf16-rounded or s*q+b)."""
         if self.kind == W_BF16:
             return self.w.float()
-        return ref.dequantize_affine(self.w, self.scales, self.biases, 4, GROUP)
+        return ref.dequantize_affine(self.w, self.scales, self.biases, _BITS[self.kind], GROUP)
+
+    @property
+    def scales_f16(self) -> bool:
+        """Scales and biases are kept in fp16, the precision of half-precision MLX checkpoints (the
+        decode kernels and the dequantisation kernel read either; bf16 is the default)."""
+        return self.scales is not None and self.scales.dtype == torch.float16
+
+    @property
+    def kernel_kind(self) -> int:
+        """Weight kind as the native launchers take it: bit 8 flags fp16 scales and biases."""
+        return self.kind | (0x100 if self.scales_f16 else 0)
+
+    @property
+    def bits(self) -> int:
+        """Bits per stored weight (16 for bf16)."""
+        return _BITS.get(self.kind, 16)
+
+    def dense_bf16(self) -> torch.Tensor:
+        """bf16 [.., N, K] on the weight's device: the tensor itself, or (CUDA) the packed weights
+        expanded by the dequantisation kernel (csrc/kernels/misc.cu)."""
+        if self.kind == W_BF16:
+            return self.w
+        if not self.w.is_cuda:
+            return self.dequantized().to(torch.bfloat16)
+        from .. import _lib
+        _lib.register_cuda_sigs({"rmlx_dequant_affine": ("ppppqiiip", "i")})
+        out = torch.empty(*self.w.shape[:-1], self.k, dtype=torch.bfloat16, device=self.w.device)
+        rows = self.w.numel() // self.w.shape[-1]
+        rc = _lib.cuda().rmlx_dequant_affine(self.w.data_ptr(), self.scales.data_ptr(),
+                                             self.biases.data_ptr(), out.data_ptr(), rows, self.k,
+                                             self.bits, int(self.scales_f16), _lib.stream_ptr())
+        _lib.check(rc, "dequant_affine")
+        return out
 
     def to(self, device) -> "LinearWeight":
         return LinearWeight(self.kind, self.w.to(device),
@@ -118,8 +158,9 @@ class LinearWeight:
         if self.kind == W_BF16:
             return LinearWeight(W_BF16, self.w[..., lo:hi].contiguous())
         if lo % GROUP or hi % GROUP:
-            raise ValueError("Q4 column shards must fall on 64-element group boundaries")
-        return LinearWeight(W_Q4, self.w[..., lo // 8:hi // 8].contiguous(),
+            raise ValueError("quantised column shards must fall on 64-element group boundaries")
+        per = 32 // _BITS[self.kind]
+        return LinearWeight(self.kind, self.w[..., lo // per:hi // per].contiguous(),
                             self.scales[..., lo // GROUP:hi // GROUP].contiguous(),
                             self.biases[..., lo // GROUP:hi // GROUP].contiguous())
 

@@ -45,11 +45,11 @@ def _oracle_from(gpu_weights_model: TransformerModel) -> TransformerModel:
 
 
 @pytest.mark.parametrize("cfg_fn", [tiny_dense_config, tiny_moe_config])
-@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("quant", [None, "q4", "q8"])
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_decode_matches_oracle(dev, cfg_fn, quant, use_graph):
     cfg = cfg_fn()
-    if quant == "q4" and cfg.ff_type.kind == "gated":
+    if quant in ("q4", "q8") and cfg.ff_type.kind == "gated":
         # group-64 quantisation needs the FFN width to be a multiple of 64 (688 is not)
         cfg = cfg.replace(ff_type=FeedForwardType.gated(704))
     sd = random_state_dict(cfg, 0)
@@ -149,7 +149,7 @@ def test_decode_engine_ten_rows_in_chunks(dev):
     assert rel < 5e-2, rel
 
 
-@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("quant", [None, "q4", "q8"])
 @pytest.mark.parametrize("use_graph", [False, True])
 @pytest.mark.parametrize("ctx", [16, 150])
 def test_step_kernel_matches_oracle(dev, quant, use_graph, ctx):

@@ -45,9 +45,11 @@ def _close(a, b, atol=2e-2, fro=None):
     assert rel <= fro, f"relative Frobenius error {rel} > {fro}"
 
 
-@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("quant", [None, "q4", "q8"])
 @pytest.mark.parametrize("b,n,k", [(1, 1024, 4096), (3, 72 * 128 // 8, 1024), (4, 130, 512), (6, 256, 2048), (8, 20000, 256), (1, 50, 192)])
-def test_rms_gemv(dev, quant, b, n, k):
+def test_rms_gemv(dev, quant, b, n, k, q4_path):
+    if quant == "q8" and q4_path != "stream":
+        pytest.skip("8-bit weights run on the streaming kernels")
     torch.manual_seed(1)
     w = _w(n, k, quant, dev)
     x = torch.randn(b, k, device=dev).to(torch.bfloat16)
@@ -64,8 +66,10 @@ def test_rms_gemv(dev, quant, b, n, k):
     _close(got, want)
 
 
-@pytest.mark.parametrize("quant", [None, "q4"])
-def test_dense_swiglu_pair(dev, quant):
+@pytest.mark.parametrize("quant", [None, "q4", "q8"])
+def test_dense_swiglu_pair(dev, quant, q4_path):
+    if quant == "q8" and q4_path != "stream":
+        pytest.skip("8-bit weights run on the streaming kernels")
     torch.manual_seed(2)
     b, k, i = 2, 1024, 704
     wgu = _w(2 * i, k, quant, dev, seed=3)
@@ -77,6 +81,8 @@ def test_dense_swiglu_pair(dev, quant):
     want_act = ref.swiglu(gu)
     _close(act, want_act)
     # reference-style second half: raw gate_up in, silu*up fused into the staging
+    if quant == "q8":
+        return          # the raw-gate_up form below is a per-row kernel (bf16 / 4-bit)
     gu_bf = gu.to(torch.bfloat16)
     out = D.swiglu_down(gu_bf, wdn, residual=x)
     want = ref.swiglu(gu_bf.float()) @ wdn.dequantized().t() + x.float()
@@ -118,9 +124,11 @@ def test_topk_route_exact(dev):
     assert idx.cpu().tolist() == [[0, 1, 2, 3]] * 2
 
 
-@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("quant", [None, "q4", "q8"])
 @pytest.mark.parametrize("b", [1, 3])
-def test_moe_gate_up_down(dev, quant, b):
+def test_moe_gate_up_down(dev, quant, b, q4_path):
+    if quant == "q8" and q4_path != "stream":
+        pytest.skip("8-bit weights run on the streaming kernels")
     torch.manual_seed(7)
     # Q4: 512 takes the bulk-copy tensor-core path (needs a multiple of 512); bf16: any multiple of 8
     e, d, i, topk = 16, 1024, 320 if quant is None else 512, 4
@@ -150,7 +158,7 @@ def test_moe_gate_up_down(dev, quant, b):
         for t in range(b)])
     # fp32 result: the 4-bit path adds 16 products in fp16 pairs before widening (2^-11 per add),
     # so its floor is ~1.2e-3, not the 1e-3 of an fp32-accumulated product
-    _close(out_hi, want_hi, fro=2e-3 if quant == "q4" else None)
+    _close(out_hi, want_hi, fro=2e-3 if quant in ("q4", "q8") else None)
 
 
 def _paged_setup(dev, b, hkv, hd, lens, seed=0):
@@ -274,9 +282,11 @@ def test_small_kernels(dev):
     _close(D.silu_mul(gu), ref.swiglu(gu.float()))
 
 
-@pytest.mark.parametrize("quant", [None, "q4"])
+@pytest.mark.parametrize("quant", [None, "q4", "q8"])
 @pytest.mark.parametrize("b,traditional", [(1, False), (3, False), (2, True)])
-def test_rms_qkv_rope_matches_unfused(dev, quant, b, traditional):
+def test_rms_qkv_rope_matches_unfused(dev, quant, b, traditional, q4_path):
+    if quant == "q8" and q4_path != "stream":
+        pytest.skip("8-bit weights run on the streaming kernels")
     """The fused projection + RoPE + page append equals the projection kernel followed by the
     rope/append kernel (up to the bf16 rounding of the un-rotated projection that it skips)."""
     torch.manual_seed(5)
@@ -297,3 +307,23 @@ def test_rms_qkv_rope_matches_unfused(dev, quant, b, traditional):
     for got, want in ((q1, q2), (kc1, kc2), (vc1, vc2)):
         assert (got.float() - want.float()).abs().max().item() < 3e-2 * max(1.0, want.float().abs().max().item())
     assert kc1.float().abs().sum() > 0 and vc1.float().abs().sum() > 0
+
+
+@pytest.mark.parametrize("quant", ["q4", "q8"])
+def test_fp16_scales_and_dequant_kernel(dev, quant, q4_path):
+    """Scales and biases kept in fp16 (half-precision MLX checkpoints): the streaming mat-vec and the
+    dequantisation kernel read them unrounded, so both match the fp32 dequantisation of the triplet."""
+    if q4_path != "stream":
+        pytest.skip("fp16 scales are read by the streaming kernels")
+    torch.manual_seed(21)
+    n, k, b = 512, 1024, 2
+    w = _w(n, k, quant, dev)
+    w16 = LinearWeight(w.kind, w.w, (w.scales.float() * 1.0009765625).to(torch.float16),
+                       (w.biases.float() * 1.0009765625).to(torch.float16))
+    assert w16.scales_f16
+    wd = w16.dequantized()
+    x = torch.randn(b, k, device=dev).to(torch.bfloat16)
+    _close(D.rms_gemv(x, w16, out_dtype=torch.float32), x.float() @ wd.t(), fro=2e-3)
+    dense = w16.dense_bf16()
+    assert dense.dtype == torch.bfloat16 and torch.equal(dense.float(), wd.to(torch.bfloat16).float())
+    assert torch.equal(w.dense_bf16().float(), w.dequantized().to(torch.bfloat16).float())

@@ -133,6 +133,8 @@ def test_ncu_summary_parses_raw_csv():
     spec = importlib.util.spec_from_file_location(
         "ncu_summary", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "ncu_summary.py"))
     mod = importlib.util.module_from_spec(spec)
+    import sys
+    sys.modules["ncu_summary"] = mod        # dataclasses look their module up by name
     spec.loader.exec_module(mod)
     parse_raw_csv = mod.parse_raw_csv
     text = "\n".join([

@@ -133,3 +133,41 @@ def test_affine_quantisation_oracle():
     word = int(p[0, 0]) & 0xFFFFFFFF
     q0 = round(float((w[0, 0] - b[0, 0].float()) / s[0, 0].float()))
     assert (word & 0xF) == max(0, min(15, q0))
+
+
+def test_q8_triplets_and_fp16_scales_keep_checkpoint_precision(tmp_path):
+    """An 8-bit group-64 checkpoint loads as the 8-bit weight kind (bits inferred from the shapes),
+    and fp16 scales / biases stay fp16: the dequantised weights equal the fp32 dequantisation of the
+    stored triplet exactly, which a cast to bf16 would not give."""
+    import torch
+    from safetensors.torch import save_file
+    from rmlx_b200.config import QuantConfig
+    from rmlx_b200.loader.safetensors_loader import _Source
+    from rmlx_b200.ops.weights import W_Q4, W_Q8
+    from rmlx_b200.reference import ops as ref
+    torch.manual_seed(0)
+    w = torch.randn(32, 128) * 0.05
+    tensors = {}
+    for name, bits in (("a", 4), ("b", 8)):
+        p, s, b = ref.quantize_affine(w, bits, 64)
+        # an MLX checkpoint in half precision: scales and biases are fp16 with full fp16 mantissas
+        s16 = (s.float() * 1.0009765625).to(torch.float16)
+        b16 = (b.float() * 1.0009765625).to(torch.float16)
+        tensors[f"{name}.weight"], tensors[f"{name}.scales"], tensors[f"{name}.biases"] = p, s16, b16
+    src = _Source(tensors, QuantConfig(4, 64), torch.bfloat16)
+    la, lb = src.linear("a"), src.linear("b")
+    assert la.kind == W_Q4 and lb.kind == W_Q8 and la.k == 128 and lb.k == 128
+    for lw, name, bits in ((la, "a", 4), (lb, "b", 8)):
+        assert lw.scales.dtype == torch.float16 and lw.scales_f16 and lw.kernel_kind == lw.kind | 0x100
+        want = ref.dequantize_affine(tensors[f"{name}.weight"], tensors[f"{name}.scales"].float(),
+                                     tensors[f"{name}.biases"].float(), bits, 64)
+        assert torch.equal(lw.dequantized(), want)
+        lossy = ref.dequantize_affine(tensors[f"{name}.weight"], tensors[f"{name}.scales"].to(torch.bfloat16),
+                                      tensors[f"{name}.biases"].to(torch.bfloat16), bits, 64)
+        assert not torch.equal(lossy, want)          # what the cast to bf16 used to lose
+    # 8-bit quantisation is ~16x finer than 4-bit
+    e4 = (la.dequantized() - w).abs().max().item()
+    e8 = (lb.dequantized() - w).abs().max().item()
+    assert e8 < e4 / 8
+    # column shards re-slice the packed words of either width
+    assert lb.cols(64, 128).k == 64 and torch.equal(lb.cols(64, 128).dequantized(), lb.dequantized()[:, 64:])
