@@ -4,8 +4,11 @@
 // collects its own rows from all ranks (bounded waits), sums the partials in rank order, adds the
 // residual and writes the result. No host, no NCCL, no extra launch.
 //
-//   gemv_allreduce        O projection (or dense down projection) + all-reduce + residual
-//   moe_down_allreduce    expert down projection + routing-weighted combine + all-reduce + residual
+//   SgDenseTp             O projection (or dense down projection) + all-reduce + residual, on the
+//   SgMoeDownTp           weight-streaming mat-vec (stream_gemv.cuh): expert down projection +
+//                         routing-weighted combine + all-reduce + residual
+//   gemv_allreduce        the same two on the per-row kernels (shapes the streaming kernel does
+//   moe_down_allreduce    not take)
 //   argmax_allreduce      vocabulary-parallel greedy sampling: local arg-max, 8-byte key exchange
 //   allreduce_oneshot     stand-alone one-shot all-reduce of a small fp32 vector (+ residual)
 //   barrier               epoch barrier on the peers' flag words
@@ -32,6 +35,7 @@
 #include <cstring>
 #include "../common/gemv_core.cuh"
 #include "../common/launch.cuh"
+#include "../kernels/stream_problems.cuh"
 
 namespace rb {
 
@@ -380,6 +384,185 @@ __global__ void barrier_kernel(TpPeers P, int word, uint32_t epoch) {
   }
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// The same two fused kernels on the weight-streaming mat-vec. A finished quad (four consecutive
+// output rows) is pushed at once, as two 16-byte stores of two (value, tag) words per rank, this
+// rank's own receive area included; when the block has pushed all of its quads its consumer
+// threads collect the block's rows from every rank, so the wait for the peers overlaps the rest of
+// the block's own weight stream.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void st_ll2(uint2* p, float v0, float v1, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(v0)),
+               "r"(tag), "r"(__float_as_uint(v1)), "r"(tag) : "memory");
+}
+
+struct SgTpTail {
+  TpPeers P;
+  const __nv_bfloat16* residual; int res_stride;
+  __nv_bfloat16* out; int out_stride;
+  int N;                          // multiple of 4
+  uint32_t tag; size_t slot_off;  // of the running all-reduce (begin())
+  int q0, q1;                     // this block's quads
+
+  __device__ __forceinline__ void begin() {
+    const uint32_t seq = *reinterpret_cast<volatile uint32_t*>(P.ctr[P.rank]);
+    tag = seq + 1u;
+    slot_off = size_t(seq & 1u) * P.world * P.bmax * N;
+  }
+  // one lane per quad; v: the quad's four partial sums for B batch rows starting at row b0
+  template <int B>
+  __device__ __forceinline__ void push(int quad, const float (&v)[4][B], int b0) const {
+    const int n = quad * 4;
+    if (n >= N) return;
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const size_t idx = slot_off + (size_t(P.rank) * P.bmax + b0 + b) * N + n;
+      for (int pi = 0; pi < P.world; ++pi) {
+        int p = P.rank + pi; if (p >= P.world) p -= P.world;
+        uint2* d = reinterpret_cast<uint2*>(P.recv[p]) + idx;
+        st_ll2(d, v[0][b], v[1][b], tag);
+        st_ll2(d + 2, v[2][b], v[3][b], tag);
+      }
+    }
+  }
+  // all consumer threads, once per block, after its last push
+  template <int B>
+  __device__ __forceinline__ void finish(int b0) const {
+    const int r0 = q0 * 4, rows = max(min(q1 * 4, N) - r0, 0);
+    const uint2* rb = reinterpret_cast<const uint2*>(P.recv[P.rank]) + slot_off;
+    for (int e = threadIdx.x; e < rows * B; e += kSgConsumers) {
+      const int b = e / rows, n = r0 + e - b * rows;
+      float u[kMaxWorld];
+      uint32_t pending = (1u << P.world) - 1u;
+#pragma unroll
+      for (int src = 0; src < kMaxWorld; ++src) u[src] = 0.f;
+      for (uint32_t it = 0; pending && it < kPeerPollLimit; ++it) {
+#pragma unroll
+        for (int src = 0; src < kMaxWorld; ++src) {
+          if (!((pending >> src) & 1u)) continue;
+          uint32_t a, t2;
+          asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(a), "=r"(t2)
+                       : "l"(rb + (size_t(src) * P.bmax + b0 + b) * N + n) : "memory");
+          if (t2 == tag) { u[src] = __uint_as_float(a); pending &= ~(1u << src); }
+        }
+        if (pending && it > 256) __nanosleep(it > 8192 ? 128 : 20);
+      }
+      if (pending) atomicExch(&g_tp_status, kStatusPeerTimeout);
+      float s = 0.f;
+#pragma unroll
+      for (int src = 0; src < kMaxWorld; ++src) s += u[src];   // rank order: bit-identical on every rank
+      if (residual) s += bf16lo(__ldcg(reinterpret_cast<const uint16_t*>(residual + size_t(b) * res_stride + n)));
+      out[size_t(b) * out_stride + n] = __float2bfloat16_rn(s);
+    }
+    sg_consumer_sync();
+    if (threadIdx.x == 0) {
+      uint32_t* ctr = P.ctr[P.rank];
+      __threadfence();
+      if (atomicAdd(ctr + 1, 1u) == gridDim.x * gridDim.y - 1) { ctr[1] = 0u; __threadfence(); *reinterpret_cast<volatile uint32_t*>(ctr) = tag; }
+    }
+  }
+};
+
+template <int WK, int B>
+struct SgDenseTp : SgDense<WK, B, false> {
+  SgTpTail T;
+  __device__ void cta_range(const SgPlan& pl, int& q0, int& q1) {
+    SgDense<WK, B, false>::cta_range(pl, q0, q1);
+    T.q0 = q0; T.q1 = q1;
+  }
+  __device__ void init(bool producer) { if (!producer) T.begin(); }
+  __device__ void epilogue(int quad, float (&v)[4][B], SgSmem& sm) {
+#pragma unroll
+    for (int b = 0; b < B; ++b) {
+      const float inv = sm.c->misc[b];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) v[r][b] *= inv;
+    }
+    T.template push<B>(quad, v, 0);
+  }
+  __device__ void cta_done(SgSmem&) { T.template finish<B>(0); }
+};
+
+// One token per grid partition (B = 1); `residual` / `out` of the tail point at the token's row.
+template <int WK>
+struct SgMoeDownTp : SgMoeDownBase<WK> {
+  SgTpTail T;
+  __device__ void cta_range(const SgPlan& pl, int& q0, int& q1) {
+    SgMoeDownBase<WK>::cta_range(pl, q0, q1);
+    T.q0 = q0; T.q1 = q1;
+  }
+  __device__ void init(bool producer) {
+    this->load_routing();
+    if (!producer) {
+      T.begin();
+      if (T.residual) T.residual += size_t(this->token) * T.res_stride;
+      T.out += size_t(this->token) * T.out_stride;
+    }
+  }
+  __device__ void stage_x(SgSmem& sm, const SgPlan&) { this->stage_moe_x(sm); }
+  __device__ void epilogue(int quad, float (&v)[4][1], SgSmem&) { T.template push<1>(quad, v, this->token); }
+  __device__ void cta_done(SgSmem&) { T.template finish<1>(this->token); }
+};
+
+static bool& tp_stream_on() { static bool v = true; return v; }
+static long long& tp_stream_launches() { static long long v = 0; return v; }
+
+static int* tp_status_ptr() {
+  static int* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  if (!cached[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_tp_status) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+    cached[dev] = static_cast<int*>(p);
+  }
+  return cached[dev];
+}
+
+static SgTpTail make_tail(const TpPeers& P, const void* residual, int res_stride, void* out,
+                          int out_stride, int N) {
+  SgTpTail T;
+  T.P = P;
+  T.residual = static_cast<const __nv_bfloat16*>(residual); T.res_stride = res_stride;
+  T.out = static_cast<__nv_bfloat16*>(out); T.out_stride = out_stride;
+  T.N = N; T.tag = 0u; T.slot_off = 0; T.q0 = T.q1 = 0;
+  return T;
+}
+
+template <int WK, int B>
+static int run_dense_tp(int kind_bits, const void* w, const void* sc, const void* bi, const void* x,
+                        int x_stride, const SgTpTail& T, int N, int K, int pdl, cudaStream_t st) {
+  SgDenseTp<WK, B> P;
+  P.W = sg_weights(WK, w, sc, bi, K);
+  P.N = N; P.K = K;
+  P.x = static_cast<const __nv_bfloat16*>(x); P.x_stride = x_stride;
+  P.norm_w = nullptr; P.eps = 0.f;
+  P.residual = nullptr; P.res_stride = 0; P.out = nullptr; P.out_stride = 0;
+  P.T = T;
+  const SgPlan pl = sg_make_plan(kind_bits, P.W.units, 1, false, N / 4, sm_count(), 1 << 20,
+                                 sg_x_bytes(WK, K, B), 0, B);
+  return sg_launch(P, pl, pl.grid, tp_status_ptr(), pdl, st);
+}
+
+template <int WK>
+static int run_moe_down_tp(int kind_bits, const void* w, const void* sc, const void* bi,
+                           const void* act, int act_stride, const int* topk_idx,
+                           const float* topk_w, const SgTpTail& T, int B, int top_k, int N, int I,
+                           int expert_base, int experts_local, int pdl, cudaStream_t st) {
+  SgMoeDownTp<WK> P;
+  P.W = sg_weights(WK, w, sc, bi, I);
+  P.N = N; P.I = I;
+  P.act = static_cast<const __nv_bfloat16*>(act); P.act_stride = act_stride;
+  P.R = SgRouting{topk_idx, topk_w, top_k, expert_base, experts_local};
+  P.token = 0; P.ntok = B; P.nloc = 0; P.packed = 0ull;
+  P.T = T;
+  const int per_token = sm_count() / B > 0 ? sm_count() / B : 1;
+  const SgPlan pl = sg_make_plan(kind_bits, P.W.units, top_k, false, N / 4, per_token, 1 << 20,
+                                 sg_x_bytes(WK, top_k * I, 1), 64, 1);
+  return sg_launch(P, pl, pl.grid * B, tp_status_ptr(), pdl, st);
+}
+
 template <class WT>
 static Matrix<WT> mk_matrix(const void* w, const void* s, const void* b, int K);
 template <>
@@ -406,6 +589,12 @@ static TpPeers make_peers(void* const* recv, void* const* ctr, int rank, int wor
 
 using namespace rb;
 
+// The fused projections take the weight-streaming kernel when the shape fits (default), else the
+// per-row kernels; off: always the per-row kernels.
+extern "C" int rmlx_tp_set_stream(int on) { tp_stream_on() = on != 0; return 0; }
+// Launches (captures included) of this process that took the weight-streaming form.
+extern "C" long long rmlx_tp_stream_launches() { return tp_stream_launches(); }
+
 extern "C" int rmlx_tp_status() {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_tp_status, sizeof(int)) != cudaSuccess) return -1;
@@ -422,10 +611,28 @@ extern "C" int rmlx_tp_gemv_allreduce(int w_kind, const void* w, const void* sca
                                       int out_stride, int B, int N, int K, void* const* recv,
                                       void* const* ctr, int rank, int world, int bmax, int pdl,
                                       cudaStream_t st) {
-  if (K % 8 || (w_kind == 1 && K % 64) || B < 1 || B > 4 || B > bmax || N < 1 || world < 1 ||
+  const int kind_bits = w_kind;      // bit 8: fp16 scales and biases (streaming kernel only)
+  w_kind &= 0xff;
+  if (K % 8 || (w_kind != 0 && K % 64) || B < 1 || B > 4 || B > bmax || N < 1 || world < 1 ||
       world > kMaxWorld)
     return -2;
   const TpPeers P = make_peers(recv, ctr, rank, world, bmax);
+  if (tp_stream_on() && N % 4 == 0 && w_kind >= 0 && w_kind <= 2 &&
+      sg_weights_ok(w_kind, w, scales, biases, K)) {
+    const SgTpTail T = make_tail(P, residual, res_stride, out, out_stride, N);
+    int rc = -2;
+#define RB_TPS(KIND_)                                                                              \
+    if (w_kind == KIND_) switch (B) {                                                                \
+      case 1: rc = run_dense_tp<KIND_, 1>(kind_bits, w, scales, biases, x, x_stride, T, N, K, pdl, st); break; \
+      case 2: rc = run_dense_tp<KIND_, 2>(kind_bits, w, scales, biases, x, x_stride, T, N, K, pdl, st); break; \
+      case 3: rc = run_dense_tp<KIND_, 3>(kind_bits, w, scales, biases, x, x_stride, T, N, K, pdl, st); break; \
+      default: rc = run_dense_tp<KIND_, 4>(kind_bits, w, scales, biases, x, x_stride, T, N, K, pdl, st); break; \
+    }
+    RB_TPS(0) RB_TPS(1) RB_TPS(2)
+#undef RB_TPS
+    if (rc != -2) { tp_stream_launches() += rc == 0; return rc; }
+  }
+  if (kind_bits & 0x100) return -2;
   const int grid = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
 #define RB_TPG(WT, BB)                                                                            \
   {                                                                                               \
@@ -456,10 +663,25 @@ extern "C" int rmlx_tp_moe_down_allreduce(int w_kind, const void* w, const void*
                                           int expert_base, int experts_local, void* const* recv,
                                           void* const* ctr, int rank, int world, int bmax, int pdl,
                                           cudaStream_t st) {
-  if (I % 8 || (w_kind == 1 && I % 64) || B < 1 || B > bmax || top_k < 1 || top_k > kTpMaxTopK ||
+  const int kind_bits = w_kind;      // bit 8: fp16 scales and biases (streaming kernel only)
+  w_kind &= 0xff;
+  if (I % 8 || (w_kind != 0 && I % 64) || B < 1 || B > bmax || top_k < 1 || top_k > kTpMaxTopK ||
       world < 1 || world > kMaxWorld)
     return -2;
   const TpPeers P = make_peers(recv, ctr, rank, world, bmax);
+  if (tp_stream_on() && N % 4 == 0 && w_kind >= 0 && w_kind <= 2 && experts_local <= 256 &&
+      sg_weights_ok(w_kind, w, scales, biases, I) && !(w_kind == 0 && I % 32)) {
+    const SgTpTail T = make_tail(P, residual, res_stride, out, out_stride, N);
+    int rc = -2;
+#define RB_TPS(KIND_)                                                                              \
+    if (w_kind == KIND_)                                                                           \
+      rc = run_moe_down_tp<KIND_>(kind_bits, w, scales, biases, act, act_stride, topk_idx, topk_w, \
+                                  T, B, top_k, N, I, expert_base, experts_local, pdl, st);
+    RB_TPS(0) RB_TPS(1) RB_TPS(2)
+#undef RB_TPS
+    if (rc != -2) { tp_stream_launches() += rc == 0; return rc; }
+  }
+  if (kind_bits & 0x100) return -2;
   const int gx = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
 #define RB_TPD(WT, MK)                                                                            \
   {                                                                                               \

@@ -13,6 +13,8 @@ with rendezvous over TCP (crates/rmlx-distributed/src/init.rs:397-417). Here ren
 """
 from __future__ import annotations
 
+import os
+
 import ctypes
 from typing import List, Optional
 
@@ -25,6 +27,8 @@ from ..ops.weights import LinearWeight
 
 _lib.register_cuda_sigs({
     "rmlx_tp_status": ("", "i"),
+    "rmlx_tp_set_stream": ("i", "i"),
+    "rmlx_tp_stream_launches": ("", "q"),
     "rmlx_tp_gemv_allreduce": ("ippppipipiiiippiiiip", "i"),
     "rmlx_tp_moe_down_allreduce": ("ippppipppipiiiiiiippiiiip", "i"),
     "rmlx_tp_allreduce": ("pppiippiiqip", "i"),
@@ -122,6 +126,9 @@ class PeerComm:
         self._keys_dev = torch.tensor(keys, dtype=torch.int64, device=self.device)
         self._n = 0           # collective calls issued (statistics only)
         self._n_argmax = 0
+        # RMLX_TP_STREAM=0: the fused projections use the per-row kernels instead of the
+        # weight-streaming ones (both speak the same receive-area protocol)
+        _lib.cuda().rmlx_tp_set_stream(int(os.environ.get("RMLX_TP_STREAM", "1") != "0"))
         self._barrier_epoch = 0
 
     # ------------------------------------------------------------------
@@ -140,7 +147,7 @@ class PeerComm:
             xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]
             rs = None if residual is None else residual[b0:b0 + bb]
             rc = lib.rmlx_tp_gemv_allreduce(
-                w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
+                w.kernel_kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
                 xs.stride(0), _lib.ptr(rs), 0 if rs is None else rs.stride(0), os_.data_ptr(),
                 os_.stride(0), bb, self.N, k, self._recv, self._ctr, self.rank, self.world,
                 self.B, int(pdl), st)
@@ -154,7 +161,7 @@ class PeerComm:
         assert b <= self.B and w.n == self.N
         self._n += 1
         rc = _lib.cuda().rmlx_tp_moe_down_allreduce(
-            w.kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), act.data_ptr(),
+            w.kernel_kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), act.data_ptr(),
             act.stride(0), idx.data_ptr(), wts.data_ptr(), _lib.ptr(residual),
             0 if residual is None else residual.stride(0), out.data_ptr(), out.stride(0), b, top_k,
             self.N, w.k, expert_base, w.experts, self._recv, self._ctr, self.rank, self.world,
@@ -195,6 +202,10 @@ class PeerComm:
         rc = _lib.cuda().rmlx_tp_barrier(self._recv, self._ctr_barrier, self.rank, self.world, 0,
                                          self._barrier_epoch, _lib.stream_ptr())
         _lib.check(rc, "tp_barrier")
+
+    def stream_launches(self) -> int:
+        """Fused projections of this process that ran on the weight-streaming kernel."""
+        return int(_lib.cuda().rmlx_tp_stream_launches())
 
     def status(self) -> int:
         """0, or the code of a device-side wait that gave up since the last call."""

@@ -94,6 +94,8 @@ def _worker(rank, world, port, quant, comm_kind, dense_first, max_batch, use_gra
         torch.cuda.synchronize()
         assert comm.status() == 0
         assert torch.isfinite(eng.logits[:nseq, :v_local]).all()
+        if comm_kind == "fused":   # the streaming form ran unless it was switched off
+            assert (comm.stream_launches() > 0) == (os.environ.get("RMLX_TP_STREAM", "1") != "0")
 
         if rank == 0:
             full = TransformerModel(from_state_dict(cfg, sd, device=dev, quant=quant))
@@ -128,6 +130,7 @@ CASES = [
     (None, "nccl", 0, 2, False), ("q4", "nccl", 0, 2, False),
     ("q4", "fused", 1, 2, False), ("q4", "fused", 1, 2, True),
     (None, "fused", 0, 8, False), (None, "fused", 0, 8, True),
+    ("q8", "fused", 1, 2, True), ("q4", "fused", 1, 8, True),
 ]
 
 
@@ -151,3 +154,10 @@ def test_tp_decode_matches_single_gpu(quant, comm_kind, dense_first, max_batch, 
     assert err <= 5e-2 * mag + 2e-2, (err, mag)
     assert tok_tp == tok_1 or err > 0, (tok_tp, tok_1)
     assert tuple(shape) == (2 if max_batch <= 2 else 5, 5)
+
+
+@pytest.mark.parametrize("quant,max_batch", [("q4", 2), (None, 8)])
+def test_tp_decode_per_row_kernels(monkeypatch, quant, max_batch):
+    """The per-row fused kernels (shapes the streaming kernel does not take) keep working."""
+    monkeypatch.setenv("RMLX_TP_STREAM", "0")
+    test_tp_decode_matches_single_gpu(quant, "fused", 1, max_batch, True)
