@@ -166,11 +166,25 @@ def build_ours(c: Ctx, weights: str, total_steps: int):
     cfg = moe_a22b_config(a.layers, max_seq_len=ctx + 2 * total_steps + 64)
     quant = None if weights == "bf16" else "q4"
     w = random_on_device(cfg, c.dev, quant, ParallelLayout(c.rank, c.world), seed=0)
-    model = TransformerModel(w)
     comm = None
     if c.world > 1:
+        import torch.distributed as dist
+
+        def allreduce(t):
+            t = t.contiguous()
+            dist.all_reduce(t)
+            return t
+
+        def allgather(t):
+            parts = [torch.empty_like(t) for _ in range(c.world)]
+            dist.all_gather(parts, t.contiguous())
+            return torch.cat(parts, -1)
+
+        model = TransformerModel(w, allreduce, allgather)
         from rmlx_b200.parallel.comm import make_comm
-        comm = make_comm("fused", model, max_batch=B)
+        comm = make_comm("fused", model, max_batch=min(B, 4))
+    else:
+        model = TransformerModel(w)
     bps = (cfg.max_seq_len + 15) // 16
     cache = model.new_cache(1 + B * bps, max_seqs=B, max_blocks_per_seq=bps)
     for s in range(B):      # synthetic context: K/V ~ N(0,1) for `ctx` tokens per sequence
@@ -184,8 +198,11 @@ def build_ours(c: Ctx, weights: str, total_steps: int):
         eng = CachedDecode(model, cache, max_batch=B, use_graph=not a.no_graph, pdl=not a.no_pdl, comm=comm)
     else:   # more rows than one mat-vec launch takes: the tensor-core decode step
         from rmlx_b200.models.prefill import BatchedDecode, enable_native_prefill
-        if c.world > 1:
-            raise SystemExit("bench.py: --batch > 4 runs on one GPU")
+        if c.world > 1:      # row-parallel GEMMs fused with their all-reduce over NVLink
+            from rmlx_b200.parallel.tp_gemm import make_gemm_comm
+            i_local = max([l.w_gate_up.n // 2 for l in w.layers if l.w_gate_up is not None] + [64])
+            model.gemm_comm = make_gemm_comm("fused", B, cfg.hidden_size,
+                                             max(model.hq * cfg.head_dim, i_local), device=c.dev)
         enable_native_prefill(model)
         eng = BatchedDecode(model, cache, max_batch=B, use_graph=not a.no_graph)
     eng.bind(list(range(B)), [1] * B)
@@ -333,6 +350,8 @@ def main():
         nonlocal cfg, weights, model, comm, cache, eng
         if comm is not None:
             comm.close()
+        if getattr(model, "gemm_comm", None) is not None:
+            model.gemm_comm.close()
         cfg = weights = model = comm = cache = eng = None
         c.free()
 

@@ -1,12 +1,19 @@
 #!/usr/bin/env python
-"""Serving-shaped numbers for the MoE-A22B-shaped model on one GPU: time to first token for a
-2048-token prompt through the native prefill path, and decode throughput at batch 1 / 8 / 64 (batch
-1 through the graph-captured mat-vec engine, larger batches through the graph-captured tensor-core
-path). The counterpart of the reference's e2e_prefill_bench / pipeline_bench
-(crates/rmlx-nn/benches/e2e_prefill_bench.rs, pipeline_bench.rs).
+"""Serving-shaped numbers for the MoE-A22B-shaped model: time to first token for a 2048-token
+prompt through the native prefill path, and decode throughput at batch 1 / 8 / 64 (batch 1 through
+the graph-captured mat-vec engine, larger batches through the tensor-core path). The counterpart
+of the reference's e2e_prefill_bench / pipeline_bench / distributed_bench
+(crates/rmlx-nn/benches/e2e_prefill_bench.rs, pipeline_bench.rs, distributed_bench.rs:45-54).
 
     python benchmarks/bench_model_serving.py [--layers 12] [--weights q4|bf16] [--prompt 2048]
         [--batches 1,8,64] [--steps 16]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        benchmarks/bench_model_serving.py ...          # tensor parallel over N GPUs
+
+Under a multi-rank launch the weights are sharded (heads, FFN columns, experts, vocabulary), the
+row-parallel GEMMs of the tensor-core path run fused with their all-reduce over NVLink
+(``--tp-gemm fused``, default) or as GEMM + NCCL (``--tp-gemm nccl``), and the mat-vec engine uses the
+fused mat-vec + all-reduce kernels. Times are the maximum over ranks.
 
 ``--layers`` defaults to 12 so that the run fits a short GPU slot; every figure is printed per layer
 and, labelled as such, scaled to the 60 layers of the full model (layers are identical, the LM head
@@ -26,10 +33,17 @@ from rmlx_b200.config import moe_a22b_config  # noqa: E402
 from rmlx_b200.models.decode_engine import CachedDecode  # noqa: E402
 from rmlx_b200.models.prefill import BatchedDecode, enable_native_prefill  # noqa: E402
 from rmlx_b200.models.transformer import TransformerModel  # noqa: E402
-from rmlx_b200.models.weights import random_on_device  # noqa: E402
+from rmlx_b200.models.weights import ParallelLayout, random_on_device  # noqa: E402
+
+
+WORLD = int(os.environ.get("WORLD_SIZE", "1"))
+RANK = int(os.environ.get("RANK", "0"))
 
 
 def ev_time(fn, iters=1):
+    """Device time per call (CUDA events), maximum over ranks."""
+    if WORLD > 1:
+        torch.distributed.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -37,7 +51,17 @@ def ev_time(fn, iters=1):
         fn()
     e1.record()
     torch.cuda.synchronize()
-    return e0.elapsed_time(e1) / iters
+    ms = e0.elapsed_time(e1) / iters
+    if WORLD > 1:
+        t = torch.tensor([ms], device="cuda")
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+    return ms
+
+
+def say(*a):
+    if RANK == 0:
+        print(*a, flush=True)
 
 
 def main():
@@ -47,14 +71,45 @@ def main():
     ap.add_argument("--prompt", type=int, default=2048)
     ap.add_argument("--batches", default="1,8,64")
     ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--tp-gemm", default="fused", choices=["fused", "nccl"])
     a = ap.parse_args()
-    dev = torch.device("cuda:0")
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     batches = [int(v) for v in a.batches.split(",")]
     cfg = moe_a22b_config(a.layers, max_seq_len=a.prompt + 4 * a.steps + 64)
-    model = TransformerModel(random_on_device(cfg, dev, None if a.weights == "bf16" else "q4"))
+    quant = None if a.weights == "bf16" else "q4"
+    comm = None
+    if WORLD > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+        def allreduce(t):
+            t = t.contiguous()
+            dist.all_reduce(t)
+            return t
+
+        def allgather(t):
+            parts = [torch.empty_like(t) for _ in range(WORLD)]
+            dist.all_gather(parts, t.contiguous())
+            return torch.cat(parts, -1)
+
+        model = TransformerModel(random_on_device(cfg, dev, quant, ParallelLayout(RANK, WORLD), seed=0),
+                                 allreduce, allgather)
+        from rmlx_b200.parallel.comm import make_comm
+        from rmlx_b200.parallel.tp_gemm import make_gemm_comm
+        rows = max(a.prompt, max(batches))
+        attn_local = model.hq * cfg.head_dim
+        i_local = max([l.w_gate_up.n // 2 for l in model.w.layers if l.w_gate_up is not None] + [0])
+        model.gemm_comm = make_gemm_comm(a.tp_gemm, rows, cfg.hidden_size, max(attn_local, i_local, 64),
+                                         device=dev)
+        comm = make_comm("fused", model, max_batch=4)
+    else:
+        model = TransformerModel(random_on_device(cfg, dev, quant))
     assert enable_native_prefill(model)
     L = a.layers
-    print(f"# moe-a22b-shaped, {L} layers resident, weights={a.weights}, prompt={a.prompt}")
+    say(f"# moe-a22b-shaped, {L} layers resident, weights={a.weights}, prompt={a.prompt}, "
+        f"tensor parallel {WORLD}" + (f" (row-parallel GEMMs: {a.tp_gemm})" if WORLD > 1 else ""))
 
     # ---- prefill: time to first token
     blocks_per_seq = (cfg.max_seq_len + 15) // 16
@@ -70,7 +125,7 @@ def main():
     ttft = min(times[2:])
     head_ms = ev_time(lambda: model._native_prefill.layers.logits(torch.zeros(1, cfg.hidden_size, dtype=torch.bfloat16, device=dev)), 5)
     per_layer = (ttft - head_ms) / L
-    print(f"prefill {a.prompt} tokens: {ttft:8.2f} ms ({L} layers)  {per_layer * 1e3:8.1f} us/layer  "
+    say(f"prefill {a.prompt} tokens: {ttft:8.2f} ms ({L} layers)  {per_layer * 1e3:8.1f} us/layer  "
           f"{a.prompt / ttft * 1e3:9.0f} tok/s;  scaled to 60 layers: {per_layer * 60 + head_ms:8.2f} ms TTFT")
 
     # ---- decode at several batch sizes, context = the prompt
@@ -82,7 +137,7 @@ def main():
             cache.commit(s, a.prompt)          # context content is irrelevant to timing (zeros)
         last = [1] * b
         if b <= 4:
-            eng = CachedDecode(model, cache, max_batch=b)
+            eng = CachedDecode(model, cache, max_batch=b, comm=comm)
         else:
             eng = BatchedDecode(model, cache, max_batch=b)
         eng.bind(seqs, last)
@@ -90,10 +145,18 @@ def main():
         eng.reserve(a.steps + 2)
         ms = ev_time(lambda: eng.step(), a.steps)
         tok_s = b / ms * 1e3
-        print(f"decode batch {b:3d} ctx {a.prompt}: {ms:8.3f} ms/step ({L} layers)  {ms / L * 1e3:7.1f} us/layer  "
+        say(f"decode batch {b:3d} ctx {a.prompt}: {ms:8.3f} ms/step ({L} layers)  {ms / L * 1e3:7.1f} us/layer  "
               f"{tok_s:9.0f} tok/s;  scaled to 60 layers: {b / (ms / L * 60) * 1e3:9.0f} tok/s")
         for s in seqs:
             cache.free_sequence(s)
+    if WORLD > 1:
+        torch.cuda.synchronize()
+        torch.distributed.barrier()
+        st = (comm.status(), model.gemm_comm.status())
+        say(f"# status words (mat-vec all-reduce, GEMM collective): {st}")
+        comm.close()
+        model.gemm_comm.close()
+        torch.distributed.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -24,6 +24,9 @@ OBJ = ROOT / "build"
 LIB = ROOT / "lib"
 
 CUDA_LIB = LIB / "librmlx_b200_cuda.so"
+# The same sources compiled with -DRMLX_BOUNDS: device-side index checks that record the first
+# offender and skip the access (build(kinds=("cuda_bounds",)); loaded when RMLX_BOUNDS=1).
+CUDA_BOUNDS_LIB = LIB / "librmlx_b200_cuda_bounds.so"
 HOST_LIB = LIB / "librmlx_b200_host.so"
 
 NVCC_FLAGS = [
@@ -71,7 +74,7 @@ def _compile_one(args) -> tuple[Path, bool, str]:
 
 
 def _sources(kind: str) -> list[Path]:
-    if kind == "cuda":
+    if kind in ("cuda", "cuda_bounds"):
         return sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
     return sorted((CSRC / "host").glob("*.cpp"))
 
@@ -84,14 +87,14 @@ def build(kinds=("host", "cuda"), verbose: bool = False, force: bool = False) ->
     out: dict[str, Path] = {}
     for kind in kinds:
         srcs = _sources(kind)
-        lib = CUDA_LIB if kind == "cuda" else HOST_LIB
+        lib = {"cuda": CUDA_LIB, "cuda_bounds": CUDA_BOUNDS_LIB}.get(kind, HOST_LIB)
         if not srcs:
             continue
-        if kind == "cuda":
+        if kind in ("cuda", "cuda_bounds"):
             nvcc = _nvcc()
             if nvcc is None:
                 raise RuntimeError("nvcc not found; cannot build the CUDA library")
-            flags = NVCC_FLAGS
+            flags = NVCC_FLAGS + (["-DRMLX_BOUNDS"] if kind == "cuda_bounds" else [])
             mk = lambda s, o: [nvcc, *flags, "-I", str(CSRC), "-c", str(s), "-o", str(o)]
         else:
             cxx = shutil.which("g++") or "g++"
@@ -117,7 +120,7 @@ def build(kinds=("host", "cuda"), verbose: bool = False, force: bool = False) ->
         if rebuilt or not lib.exists() or not link_stamp.exists() or \
                 link_stamp.read_text() != link_digest:
             objs = [str(r[0]) for r in results]
-            if kind == "cuda":
+            if kind in ("cuda", "cuda_bounds"):
                 cmd = [_nvcc(), "-shared", "-o", str(lib), *objs, "-lpthread", "-ldl"]
             else:
                 cmd = [shutil.which("g++") or "g++", "-shared", "-o", str(lib), *objs, "-pthread"]

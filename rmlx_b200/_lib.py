@@ -13,6 +13,7 @@ compiled kernels.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_float, c_int, c_longlong, c_void_p
 from typing import Any, Dict, Optional
@@ -90,12 +91,30 @@ def cuda() -> ctypes.CDLL:
     if _cuda_lib is None:
         with _lock:
             if _cuda_lib is None:
-                if not _build.CUDA_LIB.exists():
-                    _build.build(kinds=("cuda",))
-                lib = ctypes.CDLL(str(_build.CUDA_LIB))
+                # RMLX_BOUNDS=1: the bounds-checked build of the same kernels
+                bounds = os.environ.get("RMLX_BOUNDS", "0") == "1"
+                path = _build.CUDA_BOUNDS_LIB if bounds else _build.CUDA_LIB
+                if not path.exists():
+                    _build.build(kinds=("cuda_bounds" if bounds else "cuda",))
+                lib = ctypes.CDLL(str(path))
                 _bind(lib, _CUDA_SIGS)
+                _register_status_words(lib)
                 _cuda_lib = lib
     return _cuda_lib
+
+
+def _register_status_words(lib: ctypes.CDLL) -> None:
+    """The kernels' status words (set by a bounded wait that ran out) become sources of the
+    process-wide error store; ``ERRORS.collect()`` reads and clears them."""
+    from .runtime.streams import ERRORS
+    for title, sym in (("weight-streaming mat-vec", "rmlx_sg_status"),
+                       ("tensor-core mat-vec", "rmlx_qmv_status"),
+                       ("tensor-parallel decode", "rmlx_tp_status"),
+                       ("decode step kernel", "rmlx_decode_step_status")):
+        fn = getattr(lib, sym, None)
+        if fn is not None:
+            fn.restype = c_int
+            ERRORS.register(title, lambda fn=fn: int(fn()) & 0xff if torch.cuda.is_available() else 0)
 
 
 def host() -> ctypes.CDLL:
@@ -118,6 +137,28 @@ def stream_ptr(stream: Optional[torch.cuda.Stream] = None) -> int:
 
 
 _launch_count = 0
+# RMLX_DEBUG_SERIALIZE=1: every launch is followed by a device synchronisation and a read of the
+# kernels' status words, so a fault or an expired wait is reported with the name of the launch that
+# caused it (the stand-in for a race / memory checker on boxes where none can run). Launches made
+# during stream capture are left alone; the engines run un-captured in this mode.
+_debug_serialize = os.environ.get("RMLX_DEBUG_SERIALIZE", "0") == "1"
+_serial_trace: list = []
+
+
+def set_debug_serialize(on: bool) -> None:
+    global _debug_serialize
+    _debug_serialize = bool(on)
+
+
+def debug_serialize() -> bool:
+    return _debug_serialize
+
+
+def serial_trace() -> list:
+    """Names of the launches checked one by one since the last call (debug-serialize mode)."""
+    out = list(_serial_trace)
+    _serial_trace.clear()
+    return out
 
 
 def launch_count() -> int:
@@ -129,11 +170,43 @@ def check(rc: int, what: str) -> None:
     global _launch_count
     _launch_count += 1
     if rc == 0:
+        if _debug_serialize and torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+            _check_serialized(what)
         return
     if rc == -2:
         raise NativeError(f"{what}: invalid argument or unsupported shape")
     msg = cuda().rmlx_error_string(rc)
     raise NativeError(f"{what}: CUDA error {rc}: {msg.decode() if msg else '?'}")
+
+
+def bounds_status():
+    """Bounds-checked build only: the first out-of-range index a kernel recorded since the last
+    call, as (source file, source line, index, limit), or None. Raises on a normal build."""
+    lib = cuda()
+    lib.rmlx_bounds_status.argtypes = [c_void_p, ctypes.c_char_p, c_int]
+    lib.rmlx_bounds_status.restype = c_int
+    rec = (c_int * 4)()
+    name = ctypes.create_string_buffer(64)
+    rc = lib.rmlx_bounds_status(ctypes.cast(rec, c_void_p), name, 64)
+    if rc == -3:
+        raise NativeError("not a bounds-checked build (set RMLX_BOUNDS=1 before the first kernel)")
+    if rc < 0:
+        raise NativeError("bounds status could not be read")
+    return (name.value.decode(), rec[1], rec[2], rec[3]) if rc == 1 else None
+
+
+def _check_serialized(what: str) -> None:
+    try:
+        torch.cuda.synchronize()
+    except RuntimeError as e:                      # a sticky CUDA error: name the launch
+        raise NativeError(f"{what}: {e}") from e
+    from .runtime.streams import ERRORS
+    from .runtime.graph import HAZARDS
+    HAZARDS.retire_all()                           # everything before this point has completed
+    _serial_trace.append(what)
+    new = ERRORS.collect()
+    if new:
+        raise NativeError(f"{what}: device status " + ", ".join(f"{n}={c} ({m})" for n, c, m in new))
 
 
 def require_cuda_tensor(*ts: Any) -> None:

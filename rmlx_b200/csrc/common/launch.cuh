@@ -5,7 +5,27 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#ifdef RMLX_BOUNDS
+#include <vector>
+#endif
+
 namespace rb {
+
+// Bounds-checked build: every source file that uses RB_BOUNDS registers a reader of its own
+// record (RB_BOUNDS_REGISTER at file scope); rmlx_bounds_status() walks the list.
+#ifdef RMLX_BOUNDS
+struct BoundsSource { const char* file; int (*read)(int* out4, int clear); };
+inline std::vector<BoundsSource>& bounds_sources() { static std::vector<BoundsSource> v; return v; }
+#define RB_BOUNDS_REGISTER(name)                                                                   \
+  static int rb_bounds_read(int* out4, int clear) {                                                \
+    if (cudaMemcpyFromSymbol(out4, ::rb::g_rb_bounds, 16) != cudaSuccess) return -1;               \
+    if (clear && out4[0]) { const int z[4] = {0, 0, 0, 0}; (void)cudaMemcpyToSymbol(::rb::g_rb_bounds, z, 16); } \
+    return 0;                                                                                      \
+  }                                                                                                \
+  static const bool rb_bounds_registered = (::rb::bounds_sources().push_back({name, rb_bounds_read}), true);
+#else
+#define RB_BOUNDS_REGISTER(name)
+#endif
 
 #define RB_CHECK(expr)                                   \
   do {                                                   \

@@ -22,6 +22,27 @@ enum StatusCode : int {
   kStatusBadArgument = 3,    // device-side argument check failed (debug builds)
 };
 
+// Bounds-checked build (-DRMLX_BOUNDS, a second library beside the normal one): RB_BOUNDS(i, n)
+// is true when 0 <= i < n; otherwise it records the first offender of this source file (code,
+// source line, index, limit) in a device word the host reads with rmlx_bounds_status(), and the
+// caller skips or redirects the access. In the normal build it is the constant true and costs
+// nothing. This is the stand-in for a memory checker on boxes where none can run.
+#ifdef RMLX_BOUNDS
+static __device__ int g_rb_bounds[4];
+__device__ __forceinline__ bool rb_in_bounds(long long i, long long n, int line) {
+  if (i >= 0 && i < n) return true;
+  if (atomicCAS(&g_rb_bounds[0], 0, int(kStatusBadArgument)) == 0) {
+    g_rb_bounds[1] = line;
+    g_rb_bounds[2] = int(i);
+    g_rb_bounds[3] = int(n);
+  }
+  return false;
+}
+#define RB_BOUNDS(i, n) ::rb::rb_in_bounds((long long)(i), (long long)(n), __LINE__)
+#else
+#define RB_BOUNDS(i, n) true
+#endif
+
 // Poll budgets. One poll of try_wait blocks for up to ~1-2 us in hardware, so 2^22 polls is a few
 // seconds at worst; the peer-flag budget is counted in polls with a nanosleep between them.
 constexpr uint32_t kMbarPollLimit = 1u << 22;

@@ -110,13 +110,17 @@ rms_qkv_rope_kernel(QkvMatrix<WT> W, const __nv_bfloat16* __restrict__ x, int x_
         dst = a.q_out + (size_t(b) * a.Hq + head) * a.HD;
       } else {
         const int seq = a.row_seq ? a.row_seq[b] : b;
-        const int blk = a.block_table[size_t(seq) * a.max_blocks + pos / a.page];
+        const bool inb = RB_BOUNDS(pos / a.page, a.max_blocks);   // bounds-checked build: skip the append
+        const int blk = inb ? a.block_table[size_t(seq) * a.max_blocks + pos / a.page] : 0;
         const bool is_k = head < a.Hq + a.Hkv;
         const int kvh = is_k ? head - a.Hq : head - a.Hq - a.Hkv;
-        dst = (is_k ? a.k_cache : a.v_cache) + ((size_t(blk) * a.Hkv + kvh) * a.page + pos % a.page) * a.HD;
+        dst = inb ? (is_k ? a.k_cache : a.v_cache) + ((size_t(blk) * a.Hkv + kvh) * a.page + pos % a.page) * a.HD
+                  : nullptr;
       }
-      dst[d_lo] = __float2bfloat16_rn(mylo);
-      dst[d_hi] = __float2bfloat16_rn(myhi);
+      if (dst) {
+        dst[d_lo] = __float2bfloat16_rn(mylo);
+        dst[d_hi] = __float2bfloat16_rn(myhi);
+      }
     }
   }
   pdl_launch_dependents();
@@ -152,6 +156,8 @@ static int launch_qkv_rope(const void* w, const void* sc, const void* bi, const 
 }  // namespace rb
 
 using namespace rb;
+RB_BOUNDS_REGISTER("decode_qkv_rope.cu")
+
 
 // x [B, K] bf16 -> Q rotated into q_out [B, Hq, HD]; K rotated and V copied into their page slots.
 // w: merged QKV weight [(Hq + 2*Hkv) * HD, K] (w_kind 0 bf16, 1 MLX-affine Q4). B <= 4.

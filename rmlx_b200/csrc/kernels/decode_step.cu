@@ -198,7 +198,7 @@ __device__ __forceinline__ bool step_fd_produce(const StepParams& p, const StepL
     uint32_t bytes = 0;
     const int j = lane >> 1, kv = lane & 1;
     if (lane < 2 * kStFdWarps && pg + j < f.pg1) {
-      const int blk = __ldcg(p.block_table + pg + j);
+      const int blk = RB_BOUNDS(pg + j, p.max_blocks) ? __ldcg(p.block_table + pg + j) : 0;   // page 0 is reserved
       const char* src = reinterpret_cast<const char*>(kv ? L.v_cache : L.k_cache) +
                         (size_t(blk) * p.Hkv + f.kvh) * page_bytes;
       bulk_g2s(stage + (size_t(j) * 2 + kv) * page_bytes, src, page_bytes, t.sm.c->full + s);
@@ -612,6 +612,8 @@ __global__ void __launch_bounds__(kSgThreads, 1) decode_step_kernel(StepParams p
 }  // namespace rb
 
 using namespace rb;
+RB_BOUNDS_REGISTER("decode_step.cu")
+
 
 // ---- host interface -----------------------------------------------------------------------------
 // The caller fills a plain-int description of the model and the per-layer pointers; the plans and

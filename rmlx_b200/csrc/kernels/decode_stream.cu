@@ -107,6 +107,8 @@ static int run_moe_down(const void* w, const void* sc, const void* bi, const voi
 }  // namespace rb
 
 using namespace rb;
+RB_BOUNDS_REGISTER("decode_stream.cu")
+
 
 #define SG_DISPATCH_B(B_, ...)                       \
   switch (B_) {                                      \

@@ -117,7 +117,7 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
 
   const int* bt = p.block_table + size_t(b) * p.max_blocks;
   auto issue = [&](int pg, int stage) {
-    const int blk = bt[pg];
+    const int blk = RB_BOUNDS(pg, p.max_blocks) ? bt[pg] : 0;   // page 0 is the reserved page
     const char* ksrc = reinterpret_cast<const char*>(p.k_cache) +
                        (size_t(blk) * p.Hkv + kvh) * PAGE_BYTES;
     const char* vsrc = reinterpret_cast<const char*>(p.v_cache) +
@@ -311,6 +311,8 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
 }  // namespace rb
 
 using namespace rb;
+RB_BOUNDS_REGISTER("flash_decode.cu")
+
 
 // Scratch sizes for a launch with the given shape (floats / uint32 counts).
 extern "C" int rmlx_flash_decode_gtiles(int Hq, int Hkv) { return ((Hq / Hkv) + 15) / 16; }

@@ -126,7 +126,7 @@ __global__ void __launch_bounds__(kFcThreads) flash_decode_cluster_kernel(FcPara
 
   const int* bt = p.block_table + size_t(b) * p.max_blocks;
   auto issue = [&](int pg, int stage) {
-    const int blk = bt[pg];
+    const int blk = RB_BOUNDS(pg, p.max_blocks) ? bt[pg] : 0;   // page 0 is the reserved page
     const char* ksrc = reinterpret_cast<const char*>(p.k_cache) + (size_t(blk) * p.Hkv + kvh) * PAGE_BYTES;
     const char* vsrc = reinterpret_cast<const char*>(p.v_cache) + (size_t(blk) * p.Hkv + kvh) * PAGE_BYTES;
     char* kd = wsm + stage * 2 * PAGE_BYTES;
@@ -350,6 +350,8 @@ static int fc_launch(Kern kern, int cl, dim3 grid, size_t smem, cudaStream_t st,
 }  // namespace rb
 
 using namespace rb;
+RB_BOUNDS_REGISTER("flash_decode_cluster.cu")
+
 
 static size_t fc_smem(int HD) { return size_t(kFcWarps) * 2 * 2 * kFcPage * HD * 2 + (16 * HD + 32) * 4; }
 

@@ -17,6 +17,7 @@ __global__ void embedding_kernel(const __nv_bfloat16* __restrict__ table,
   pdl_launch_dependents();   // let the next kernel start its weight prefetch now; its own wait covers our completion
   pdl_wait();
   int id = ids[blockIdx.x];
+  (void)RB_BOUNDS(id, vocab);               // bounds-checked build: record it; the clamp keeps the read safe
   id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
   const uint4* src = reinterpret_cast<const uint4*>(table + size_t(id) * D);
   uint4* dst = reinterpret_cast<uint4*>(out + size_t(blockIdx.x) * D);
@@ -181,6 +182,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ next, int* __restr
 }  // namespace rb
 
 using namespace rb;
+RB_BOUNDS_REGISTER("misc.cu")
+
 
 extern "C" int rmlx_decode_advance(const int* next, int* tokens, int* positions, int* seq_lens,
                                    const int* active, int B, int pdl, cudaStream_t st) {
@@ -287,4 +290,39 @@ extern "C" int rmlx_fp8_dequant_rows(const void* q, const float* scales, void* o
   fp8_dequant_rows_kernel<<<T, 256, 0, st>>>(static_cast<const __nv_fp8_storage_t*>(q), scales,
                                              static_cast<__nv_bfloat16*>(out), D);
   return static_cast<int>(cudaGetLastError());
+}
+
+// ---- bounds-checked build ---------------------------------------------------------------------
+// 1 when this library was compiled with -DRMLX_BOUNDS.
+extern "C" int rmlx_bounds_build() {
+#ifdef RMLX_BOUNDS
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+// Reads (and clears) the first recorded out-of-range index: out4 = {status code, source line,
+// index, limit}, `file` the source file that recorded it. Returns 1 when a record was found, 0 when
+// none, -1 on a runtime error, -3 when this is not a bounds-checked build.
+extern "C" int rmlx_bounds_status(int* out4, char* file, int file_len) {
+#ifdef RMLX_BOUNDS
+  for (const auto& src : bounds_sources()) {
+    int rec[4] = {0, 0, 0, 0};
+    if (src.read(rec, 1) != 0) return -1;
+    if (rec[0]) {
+      for (int i = 0; i < 4; ++i) out4[i] = rec[i];
+      if (file && file_len > 0) {
+        int i = 0;
+        for (; src.file[i] && i < file_len - 1; ++i) file[i] = src.file[i];
+        file[i] = 0;
+      }
+      return 1;
+    }
+  }
+  return 0;
+#else
+  (void)out4; (void)file; (void)file_len;
+  return -3;
+#endif
 }

@@ -42,6 +42,7 @@ __global__ void rope_kv_write_kernel(const __nv_bfloat16* __restrict__ qkv,
       dst = q_out + (size_t(tkn) * Hq + head) * HD;
     } else {
       const int seq = token_seq ? token_seq[tkn] : tkn;
+      if (!RB_BOUNDS(pos / page, max_blocks)) continue;
       const int blk = block_table[size_t(seq) * max_blocks + pos / page];
       const bool is_k = head < Hq + Hkv;
       const int kvh = is_k ? head - Hq : head - Hq - Hkv;
@@ -74,6 +75,8 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
 }  // namespace rb
 
 using namespace rb;
+RB_BOUNDS_REGISTER("rope_kv.cu")
+
 
 extern "C" int rmlx_rope_kv_write(const void* qkv, void* q_out, void* k_cache, void* v_cache,
                                   const int* block_table, const int* positions, const int* token_seq,

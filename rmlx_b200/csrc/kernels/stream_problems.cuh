@@ -118,7 +118,8 @@ struct SgQkvRope {
         int* pi = reinterpret_cast<int*>(cs + a.HD);
         const int seq = a.row_seq ? a.row_seq[b] : b;
         pi[0] = pos;
-        pi[1] = a.block_table[size_t(seq) * a.max_blocks + pos / a.page];
+        pi[1] = RB_BOUNDS(pos / a.page, a.max_blocks)
+                    ? a.block_table[size_t(seq) * a.max_blocks + pos / a.page] : -1;
       }
     }
     sg_stage_plain<WK, B>(sm, x, x_stride, norm_w, eps, K);
@@ -152,6 +153,7 @@ struct SgQkvRope {
         dst = a.q_out + (size_t(b) * a.Hq + head) * a.HD;
       } else {
         const int blk = pi[1];
+        if (blk < 0) continue;              // bounds-checked build: position beyond the block table
         const bool is_k = head < a.Hq + a.Hkv;
         const int kvh = is_k ? head - a.Hq : head - a.Hq - a.Hkv;
         dst = (is_k ? a.k_cache : a.v_cache) + ((size_t(blk) * a.Hkv + kvh) * a.page + pos % a.page) * a.HD;

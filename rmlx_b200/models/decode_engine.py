@@ -28,6 +28,7 @@ import torch
 
 from .. import _lib
 from ..kv.paged import PagedKvCache
+from ..runtime.graph import GraphCache, bucket_for
 from ..ops import decode as D
 from .transformer import TransformerModel
 
@@ -67,8 +68,15 @@ class CachedDecode:
         self.logits = torch.zeros(B, cfg.vocab_size, dtype=torch.float32, device=dev)
         lib = _lib.cuda()
         gt = lib.rmlx_flash_decode_gtiles(hq, hkv)
+        # One captured graph per batch bucket (1, 2, 4, ... max_batch): a step runs the smallest
+        # bucket that holds the bound rows, so a serving engine sized for 8 rows does not pay for
+        # 8 when one sequence is left. Split counts and attention scratch are planned per bucket.
+        self.buckets = tuple(b for b in (1, 2, 4, 8, 16, 32, 64) if b < B) + (B,)
+        self.graphs = GraphCache(max_entries=len(self.buckets))
+        self._splits_arg = splits
+        self._fd = {}
         self.splits = splits or D.default_splits(B, hkv, gt, cfg.max_seq_len)
-        self.fd_scratch = D.FlashDecodeScratch(B, hq, hkv, hd, self.splits, dev, max_len=cfg.max_seq_len)
+        self.fd_scratch = self._fd_plan(B)[1]
         moe = cfg.ff_type.moe
         if moe is not None:
             k = moe.num_experts_per_token
@@ -82,8 +90,8 @@ class CachedDecode:
             self.dense_act = torch.zeros(B, max(dense_i), **bf)
         self.argmax_scratch = D.ArgmaxScratch(B, dev)
         self.seq_ids: List[int] = []
-        self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._launches_per_step = 0
+        self.serialize = os.environ.get("RMLX_DEBUG_SERIALIZE", "0") == "1"
         # batch 1 on one GPU: the whole step is one persistent kernel when the model fits it
         self.step_kernel = None
         from .step_kernel import DecodeStepKernel
@@ -93,6 +101,20 @@ class CachedDecode:
                 self.step_kernel = sk
         if step_kernel and self.step_kernel is None:
             raise _lib.NativeError("the persistent step kernel does not take this model / batch")
+
+    def _fd_plan(self, nb: int):
+        """(splits, scratch) of the attention kernel for a step of ``nb`` rows."""
+        if nb not in self._fd:
+            m, cfg = self.model, self.cfg
+            gt = _lib.cuda().rmlx_flash_decode_gtiles(m.hq, m.hkv)
+            sp = self._splits_arg or D.default_splits(nb, m.hkv, gt, cfg.max_seq_len)
+            self._fd[nb] = (sp, D.FlashDecodeScratch(nb, m.hq, m.hkv, cfg.head_dim, sp, m.device,
+                                                     max_len=cfg.max_seq_len))
+        return self._fd[nb]
+
+    def bucket(self) -> int:
+        """Rows the next step runs: the smallest bucket that holds the bound sequences."""
+        return bucket_for(max(1, len(self.seq_ids)), self.buckets)
 
     # ------------------------------------------------------------------ binding
     def bind(self, seq_ids: Sequence[int], last_tokens: Sequence[int]) -> None:
@@ -122,50 +144,56 @@ class CachedDecode:
         self.refresh_tables()
 
     # ------------------------------------------------------------------ the step
-    def _run_step(self) -> None:
+    def _run_step(self, nb: Optional[int] = None) -> None:
         m, cfg, w = self.model, self.cfg, self.model.w
         eps, pdl = cfg.rms_norm_eps, self.pdl
         tp = self.comm is not None and m.layout.world > 1
         n0 = _lib.launch_count()
+        nb = self.B if nb is None else nb
         if self.step_kernel is not None:
             self.step_kernel.launch()
-            self._finish_step(pdl=False, n0=n0)
+            self._finish_step(pdl=False, n0=n0, nb=nb)
             return
-        D.embedding(w.embed, self.tokens, out=self.h, pdl=False)
-        h, h2 = self.h, self.h2
+        splits, fd_scratch = self._fd_plan(nb)
+        tokens, positions, seq_lens = self.tokens[:nb], self.positions[:nb], self.seq_lens[:nb]
+        block_table, q, attn = self.block_table[:nb], self.q[:nb], self.attn[:nb]
+        D.embedding(w.embed, tokens, out=self.h[:nb], pdl=False)
+        h, h2 = self.h[:nb], self.h2[:nb]
         for li, lw in enumerate(w.layers):
             if self.fuse_rope:
-                D.rms_qkv_rope(h, lw.wqkv, lw.norm1, eps, self.q, self.cache.k[li], self.cache.v[li],
-                               self.block_table, self.positions, m.cos, m.sin, m.hq, m.hkv,
+                D.rms_qkv_rope(h, lw.wqkv, lw.norm1, eps, q, self.cache.k[li], self.cache.v[li],
+                               block_table, positions, m.cos, m.sin, m.hq, m.hkv,
                                traditional=cfg.rope_traditional, pdl=pdl)
             else:
-                D.rms_gemv(h, lw.wqkv, lw.norm1, eps, out=self.qkv, pdl=pdl)
-                D.rope_kv_write(self.qkv, self.q, self.cache.k[li], self.cache.v[li], self.block_table,
-                                self.positions, m.cos, m.sin, m.hq, m.hkv,
+                D.rms_gemv(h, lw.wqkv, lw.norm1, eps, out=self.qkv[:nb], pdl=pdl)
+                D.rope_kv_write(self.qkv[:nb], q, self.cache.k[li], self.cache.v[li], block_table,
+                                positions, m.cos, m.sin, m.hq, m.hkv,
                                 traditional=cfg.rope_traditional, pdl=pdl)
-            D.flash_decode_paged(self.q, self.cache.k[li], self.cache.v[li], self.block_table,
-                                 self.seq_lens, m.scale, self.splits, self.fd_scratch,
-                                 cfg.sliding_window, out=self.attn, pdl=pdl)
-            a2 = self.attn.view(self.B, -1)
+            D.flash_decode_paged(q, self.cache.k[li], self.cache.v[li], block_table,
+                                 seq_lens, m.scale, splits, fd_scratch,
+                                 cfg.sliding_window, out=attn, pdl=pdl)
+            a2 = attn.view(nb, -1)
             if tp:
                 self.comm.gemv_allreduce(a2, lw.wo, residual=h, out=h2, pdl=pdl)
             else:
                 D.rms_gemv(a2, lw.wo, None, eps, residual=h, out=h2, pdl=pdl)
             if lw.router is not None:
                 moe = cfg.ff_type.moe
-                D.moe_router(h2, lw.router, lw.norm2, eps, moe.num_experts_per_token, lw.expert_bias,
-                             self.router_scratch, self.idx, self.wts, pdl=pdl)
-                D.moe_gate_up(h2, lw.experts_gate_up, lw.norm2, eps, self.idx, out=self.act,
+                k = moe.num_experts_per_token
+                idx, wts, act = self.idx[:nb], self.wts[:nb], self.act[:nb * k]
+                D.moe_router(h2, lw.router, lw.norm2, eps, k, lw.expert_bias,
+                             self.router_scratch, idx, wts, pdl=pdl)
+                D.moe_gate_up(h2, lw.experts_gate_up, lw.norm2, eps, idx, out=act,
                               expert_base=lw.expert_base, pdl=pdl)
                 if tp:
-                    self.comm.moe_down_allreduce(self.act, lw.experts_down, self.idx, self.wts,
+                    self.comm.moe_down_allreduce(act, lw.experts_down, idx, wts,
                                                  residual=h2, out=h, expert_base=lw.expert_base,
                                                  pdl=pdl)
                 else:
-                    D.moe_down(self.act, lw.experts_down, self.idx, self.wts, residual=h2, out=h,
+                    D.moe_down(act, lw.experts_down, idx, wts, residual=h2, out=h,
                                expert_base=lw.expert_base, pdl=pdl)
             else:
-                act = self.dense_act[:, :lw.w_gate_up.n // 2]
+                act = self.dense_act[:nb, :lw.w_gate_up.n // 2]
                 D.rms_gate_up_swiglu(h2, lw.w_gate_up, lw.norm2, eps, out=act, pdl=pdl)
                 if tp:
                     self.comm.gemv_allreduce(act, lw.w_down, residual=h2, out=h, pdl=pdl)
@@ -173,56 +201,54 @@ class CachedDecode:
                     D.rms_gemv(act, lw.w_down, None, eps, residual=h2, out=h, pdl=pdl)
         sharded_vocab = tp and self.vocab_local != cfg.vocab_size
         # vocabulary-parallel LM head: this rank's logits occupy the first vocab_local columns
-        logits = self.logits[:, :self.vocab_local] if sharded_vocab else self.logits
+        logits = self.logits[:nb, :self.vocab_local] if sharded_vocab else self.logits[:nb]
         D.rms_gemv(h, w.lm_head, w.final_norm, eps, out=logits, pdl=pdl)
-        self._finish_step(pdl=pdl, n0=n0, logits=logits, sharded_vocab=sharded_vocab)
+        self._finish_step(pdl=pdl, n0=n0, logits=logits, sharded_vocab=sharded_vocab, nb=nb)
 
-    def _finish_step(self, pdl: bool, n0: int, logits=None, sharded_vocab: bool = False) -> None:
+    def _finish_step(self, pdl: bool, n0: int, logits=None, sharded_vocab: bool = False,
+                     nb: Optional[int] = None) -> None:
         """Greedy sampling and the advance kernel that feeds the token back."""
         w = self.model.w
+        nb = self.B if nb is None else nb
         if logits is None:
-            logits = self.logits
+            logits = self.logits[:nb]
         if self.greedy:
+            nxt = self.next_tokens[:nb]
             if sharded_vocab:
-                self.comm.argmax(logits, w.vocab_base, self.next_tokens, pdl=pdl)
+                self.comm.argmax(logits, w.vocab_base, nxt, pdl=pdl)
             else:
-                D.argmax(self.logits, out=self.next_tokens, scratch=self.argmax_scratch, pdl=pdl)
-            rc = _lib.cuda().rmlx_decode_advance(self.next_tokens.data_ptr(), self.tokens.data_ptr(),
+                D.argmax(logits, out=nxt, scratch=self.argmax_scratch, pdl=pdl)
+            rc = _lib.cuda().rmlx_decode_advance(nxt.data_ptr(), self.tokens.data_ptr(),
                                                  self.positions.data_ptr(), self.seq_lens.data_ptr(),
-                                                 self.active.data_ptr(), self.B, int(pdl),
+                                                 self.active.data_ptr(), nb, int(pdl),
                                                  _lib.stream_ptr())
             _lib.check(rc, "decode_advance")
         self._launches_per_step = _lib.launch_count() - n0
 
-    def capture(self) -> None:
-        """Warm up once eagerly (sets kernel attributes), then capture the step."""
-        saved = [t.clone() for t in (self.tokens, self.positions, self.seq_lens)]
-        s = torch.cuda.Stream(device=self.model.device)
-        s.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(s):
-            self._run_step()
-        torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize()
-        for t, sv in zip((self.tokens, self.positions, self.seq_lens), saved):
-            t.copy_(sv)
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=s):
-            self._run_step()
-        for t, sv in zip((self.tokens, self.positions, self.seq_lens), saved):
-            t.copy_(sv)
-        torch.cuda.synchronize()
-        self._graph = g
+    def capture(self, nb: Optional[int] = None):
+        """The captured step of bucket ``nb`` (default: the bucket of the bound rows), captured on
+        first use: one eager warm-up run (sets kernel attributes), then the capture; the state
+        the runs advance is put back after each."""
+        nb = self.bucket() if nb is None else nb
+        state = (self.tokens, self.positions, self.seq_lens)
+        saved = [t.clone() for t in state]
+
+        def restore():
+            for t, sv in zip(state, saved):
+                t.copy_(sv)
+
+        return self.graphs.get_or_capture(("decode", nb), lambda: self._run_step(nb), warmup=1,
+                                          restore=restore, device=self.model.device)
 
     def step(self) -> torch.Tensor:
         """Run one decode step for every bound row. Returns the device tensor of sampled tokens
         (greedy) — reading it is the caller's only synchronisation. KV blocks for the step must
-        have been reserved."""
-        if self.use_graph:
-            if self._graph is None:
-                self.capture()
-            self._graph.replay()
+        have been reserved. ``RMLX_DEBUG_SERIALIZE=1`` runs the step launch by launch instead
+        (each launch followed by a device synchronisation and a read of the status words)."""
+        if self.use_graph and not self.serialize:
+            self.capture().replay()
         else:
-            self._run_step()
+            self._run_step(self.bucket())
         for s in self.seq_ids:
             self.cache.commit(s, 1)
         return self.next_tokens

@@ -23,6 +23,7 @@ import torch
 from .. import _lib
 from ..kv.paged import PagedKvCache
 from ..ops import decode as D
+from ..runtime.graph import GraphCache, bucket_for
 from ..ops.attention import flash_prefill_paged
 from ..ops.gemm import GemmStatus, gemm_bf16
 from ..ops.grouped import moe_prefill_ffn
@@ -61,9 +62,6 @@ def _check_model(model) -> None:
         raise ImportError("the native forward covers head_dim 64 and 128")
     if model.w.embed.dtype != torch.bfloat16:
         raise ImportError("the native forward needs bf16 activations")
-    for lw in model.w.layers:
-        if lw.experts_gate_up is not None and lw.expert_base != 0:
-            raise ImportError("expert-parallel shards go through the exchange path")
 
 
 class _Layers:
@@ -100,7 +98,7 @@ class _Layers:
                 idx, wts, _, offsets = D.topk_route(logits, moe.num_experts_per_token, lw.expert_bias)
                 single = m.layout.world == 1 and lw.shared_gate_up is None
                 y = moe_prefill_ffn(xn, idx, wts, offsets, lw.experts_gate_up, lw.experts_down,
-                                    residual=h if single else None)
+                                    residual=h if single else None, expert_base=lw.expert_base)
                 if lw.shared_gate_up is not None:
                     y = y + _mm(_gate_up_act(xn, lw.shared_gate_up), lw.shared_down)
                 h = y if single else h + m._sum(y)
@@ -118,14 +116,21 @@ class _Layers:
             out = D.rms_gemv(rows.contiguous(), w.lm_head, w.final_norm, cfg.rms_norm_eps,
                              out=torch.empty(r, w.lm_head.n, dtype=torch.float32, device=m.device))
         else:
-            out = _mm(D.rms_norm(rows.contiguous(), w.final_norm, cfg.rms_norm_eps), w.lm_head).float()
+            xn = D.rms_norm(rows.contiguous(), w.final_norm, cfg.rms_norm_eps)
+            if w.lm_head.kind == W_BF16 and w.lm_head.k % 8 == 0:
+                from ..ops.gemm import gemm_bf16_f32       # accumulator stored unrounded
+                out = gemm_bf16_f32(xn, w.lm_head.w)
+            else:
+                out = _mm(xn, w.lm_head).float()
         if m.allgather_logits is not None and m.layout.world > 1 and w.lm_head.n != cfg.vocab_size:
             out = m.allgather_logits(out)
         return out
 
 
 class NativePrefill:
-    """Callable ``(token_ids, cache, seq_id) -> last-token logits [1, vocab]`` (fp32)."""
+    """Callable ``(token_ids, cache, seq_id) -> last-token logits [1, vocab]`` (fp32); with
+    ``all_logits=True`` the logits of every position of the call, ``[T, vocab]`` (what speculative
+    verification needs: crates/rmlx-nn/src/sampler.rs verify helpers read one row per proposal)."""
 
     def __init__(self, model, chunk: int = 8192):
         self.m = model
@@ -133,13 +138,14 @@ class NativePrefill:
         self.layers = _Layers(model)
 
     @torch.no_grad()
-    def __call__(self, token_ids: torch.Tensor, cache: PagedKvCache, seq_id: int) -> torch.Tensor:
-        logits = None
+    def __call__(self, token_ids: torch.Tensor, cache: PagedKvCache, seq_id: int,
+                 all_logits: bool = False) -> torch.Tensor:
+        parts = []
         for s in range(0, token_ids.numel(), self.chunk):
-            logits = self._chunk(token_ids[s:s + self.chunk], cache, seq_id)
-        return logits
+            parts.append(self._chunk(token_ids[s:s + self.chunk], cache, seq_id, all_logits))
+        return torch.cat(parts, 0) if all_logits else parts[-1]
 
-    def _chunk(self, token_ids, cache, seq_id):
+    def _chunk(self, token_ids, cache, seq_id, all_logits=False):
         m = self.m
         cfg = m.cfg
         t = token_ids.numel()
@@ -160,7 +166,7 @@ class NativePrefill:
         h = self.layers.run(D.embedding(m.w.embed, token_ids.to(torch.int32)), attend)
         cache.commit(seq_id, t)
         GemmStatus.check(m.device)
-        return self.layers.logits(h[t - 1:t])
+        return self.layers.logits(h if all_logits else h[t - 1:t])
 
 
 class BatchedDecode:
@@ -181,16 +187,31 @@ class BatchedDecode:
         self.table = torch.zeros(b, cache.max_blocks_per_seq, dtype=torch.int32, device=dev)
         self.q = torch.empty(b, model.hq, cfg.head_dim, dtype=torch.bfloat16, device=dev)
         self.next_tokens = torch.zeros(b, dtype=torch.int32, device=dev)
-        self.logits: Optional[torch.Tensor] = None
-        lib = _lib.cuda()
-        self.splits = splits or D.default_splits(b, model.hkv, lib.rmlx_flash_decode_gtiles(model.hq, model.hkv),
-                                                 cache.max_blocks_per_seq * 16)
-        self.fd = D.FlashDecodeScratch(b, model.hq, model.hkv, cfg.head_dim, self.splits, dev)
+        # one captured graph per batch bucket: a step runs the smallest bucket that holds the
+        # bound rows (crates/rmlx-metal/src/icb.rs:357, a replay cache keyed by shape)
+        self.buckets = tuple(x for x in (1, 2, 4, 8, 16, 32, 64) if x < b) + (b,)
+        self.graphs = GraphCache(max_entries=len(self.buckets))
+        self._splits_arg = splits
+        self._fd = {}
+        self.splits, self.fd = self._fd_plan(b)
         self.argmax_scratch = D.ArgmaxScratch(b, dev)
         self.seq_ids: List[int] = []
         self.launches_per_step = 0           # launches of this package's kernels in one step
-        self.use_graph = use_graph and model.layout.world == 1
-        self._graph: Optional[torch.cuda.CUDAGraph] = None
+        self.use_graph = use_graph and model.layout.world == 1 and not _lib.debug_serialize()
+        self._logits = {}
+        self._last_bucket = b
+
+    def _fd_plan(self, nb: int):
+        if nb not in self._fd:
+            m, cfg = self.m, self.m.cfg
+            sp = self._splits_arg or D.default_splits(
+                nb, m.hkv, _lib.cuda().rmlx_flash_decode_gtiles(m.hq, m.hkv),
+                self.cache.max_blocks_per_seq * 16)
+            self._fd[nb] = (sp, D.FlashDecodeScratch(nb, m.hq, m.hkv, cfg.head_dim, sp, m.device))
+        return self._fd[nb]
+
+    def bucket(self) -> int:
+        return bucket_for(max(1, len(self.seq_ids)), self.buckets)
 
     def bind(self, seq_ids: Sequence[int], last_tokens: Sequence[int]) -> None:
         assert len(seq_ids) <= self.B
@@ -216,43 +237,48 @@ class BatchedDecode:
             self.cache.reserve(s, steps)
         self.refresh_tables()
 
-    def _body(self) -> None:
+    def _body(self, nb: Optional[int] = None) -> None:
         m, cfg, cache = self.m, self.m.cfg, self.cache
+        nb = self.B if nb is None else nb
+        splits, fd = self._fd_plan(nb)
+        tokens, positions, seq_lens = self.tokens[:nb], self.positions[:nb], self.seq_lens[:nb]
+        table, q, rows, live = self.table[:nb], self.q[:nb], self.rows[:nb], self.live[:nb]
 
         def attend(li, qkv):
-            D.rope_kv_write(qkv, self.q, cache.k[li], cache.v[li], self.table, self.positions, m.cos,
-                            m.sin, m.hq, m.hkv, token_seq=self.rows, traditional=cfg.rope_traditional)
-            return D.flash_decode_paged(self.q, cache.k[li], cache.v[li], self.table, self.seq_lens,
-                                        m.scale, self.splits, self.fd, cfg.sliding_window or 0)
+            D.rope_kv_write(qkv, q, cache.k[li], cache.v[li], table, positions, m.cos,
+                            m.sin, m.hq, m.hkv, token_seq=rows, traditional=cfg.rope_traditional)
+            return D.flash_decode_paged(q, cache.k[li], cache.v[li], table, seq_lens,
+                                        m.scale, splits, fd, cfg.sliding_window or 0)
 
-        h = self.layers.run(D.embedding(m.w.embed, self.tokens), attend)
-        self.logits = self.layers.logits(h)
-        D.argmax(self.logits, self.next_tokens, self.argmax_scratch)
+        h = self.layers.run(D.embedding(m.w.embed, tokens), attend)
+        self._logits[nb] = self.layers.logits(h)
+        D.argmax(self._logits[nb], self.next_tokens[:nb], self.argmax_scratch)
         # feed the tokens back and advance the bound rows (idle rows stay at length 0 on page 0)
-        self.tokens.copy_(self.next_tokens * self.live)
-        self.positions.add_(self.live)
-        self.seq_lens.add_(self.live)
+        tokens.copy_(self.next_tokens[:nb] * live)
+        positions.add_(live)
+        seq_lens.add_(live)
+
+    @property
+    def logits(self) -> Optional[torch.Tensor]:
+        """Logits of the last step: [bucket rows, vocab] (rows beyond the bound sequences are idle)."""
+        return self._logits.get(self._last_bucket)
 
     @torch.no_grad()
     def step(self) -> torch.Tensor:
         """Run one step for every bound sequence; returns the next-token ids (device, int32)."""
+        nb = self._last_bucket = self.bucket()
         if not self.use_graph:
             n0 = _lib.launch_count()
-            self._body()
+            self._body(nb)
             self.launches_per_step = _lib.launch_count() - n0
         else:
-            if self._graph is None:
+            def body():
                 n0 = _lib.launch_count()
-                self._body()                         # warm-up outside capture (lazy initialisations)
+                self._body(nb)
                 self.launches_per_step = _lib.launch_count() - n0
-                self._rewind()
-                torch.cuda.synchronize()
-                g = torch.cuda.CUDAGraph()
-                with torch.cuda.graph(g):
-                    self._body()
-                self._graph = g
-                self._rewind()                       # capture ran nothing, but keep the invariant explicit
-            self._graph.replay()
+            # one warm-up run outside capture (lazy initialisations), state rewound after each
+            self.graphs.get_or_capture(("batched", nb), body, warmup=1, restore=self._rewind,
+                                       device=self.m.device).replay()
         for s in self.seq_ids:
             self.cache.commit(s, 1)
         return self.next_tokens

@@ -151,10 +151,12 @@ class TransformerModel:
 
     # ------------------------------------------------------------------ prefill
     @torch.no_grad()
-    def prefill(self, token_ids: torch.Tensor, cache: PagedKvCache, seq_id: int) -> torch.Tensor:
+    def prefill(self, token_ids: torch.Tensor, cache: PagedKvCache, seq_id: int,
+                all_logits: bool = False) -> torch.Tensor:
         """Run a prompt (or a chunk of one) for ``seq_id``, filling its KV pages. Returns the
-        logits of the last token, ``[1, vocab]``. On CUDA this takes the native tensor-core path
-        when it is available for the model's weights, else the library-kernel forward."""
+        logits of the last token, ``[1, vocab]``, or with ``all_logits`` those of every position,
+        ``[T, vocab]``. On CUDA this takes the native tensor-core path when it is available for
+        the model's weights, else the library-kernel forward."""
         if token_ids.is_cuda:
             if not hasattr(self, "_native_prefill"):
                 # first prompt on a GPU: attach the tensor-core path when the model's shapes and
@@ -164,8 +166,8 @@ class TransformerModel:
                     from .prefill import enable_native_prefill
                     enable_native_prefill(self)
             if self._native_prefill is not None:
-                return self._native_prefill(token_ids, cache, seq_id)
-        return self.forward(token_ids, cache, [seq_id], last_only=True)
+                return self._native_prefill(token_ids, cache, seq_id, all_logits=all_logits)
+        return self.forward(token_ids, cache, [seq_id], last_only=not all_logits)
 
     # ------------------------------------------------------------------ greedy generation (oracle)
     @torch.no_grad()

@@ -106,6 +106,10 @@ class MoeLayer:
         self.expert_bias: Optional[torch.Tensor] = None
         self.shared: Optional[Tuple[LinearWeight, LinearWeight]] = None
         self.exchange = None
+        self.policy = None                        # parallel.moe_policy.MoePolicy
+        self.exchanges = {}                       # MoeBackend -> exchange (dispatch / combine)
+        self.overlap: Optional[str] = None        # None | "sbo" | "tbo"
+        self._pipeline = None
         self.metrics = MoeForwardMetrics()
         self.last_counts: Optional[torch.Tensor] = None
 
@@ -121,6 +125,39 @@ class MoeLayer:
     def with_exchange(self, exchange) -> "MoeLayer":
         self.exchange = exchange
         return self
+
+    def with_policy(self, policy, exchanges) -> "MoeLayer":
+        """Choose the exchange per call from the token count: ``exchanges`` maps a
+        ``MoeBackend`` to an object with ``dispatch`` / ``combine`` (the device-side exchange for
+        FUSED, the library all-to-all for NCCL); a backend without an entry falls back to the one
+        set by ``with_exchange`` (crates/rmlx-distributed/src/moe_policy.rs:85-423)."""
+        self.policy, self.exchanges = policy, dict(exchanges)
+        return self
+
+    def with_overlap(self, mode: Optional[str]) -> "MoeLayer":
+        """``"sbo"``: the shared expert runs on a side stream beside the routed experts;
+        ``"tbo"``: two token micro-batches alternate between two streams
+        (crates/rmlx-nn/src/moe_pipeline.rs:45-500)."""
+        if mode not in (None, "sbo", "tbo"):
+            raise ValueError(f"unknown overlap mode {mode}")
+        self.overlap = mode
+        return self
+
+    def forward_overlapped(self, x: torch.Tensor) -> torch.Tensor:
+        """``forward`` under the schedule chosen by ``with_overlap`` (plain ``forward`` if none)."""
+        if self.overlap is None:
+            return self.forward(x)
+        if self._pipeline is None:
+            from .moe_pipeline import MoePipeline
+            self._pipeline = MoePipeline(self)
+        return self._pipeline.forward_sbo(x) if self.overlap == "sbo" else self._pipeline.forward_tbo(x)
+
+    def _exchange_for(self, x: torch.Tensor):
+        if self.policy is None:
+            return self.exchange
+        backend = self.policy.select(x.shape[0], x.numel() * x.element_size())
+        self.metrics_backend = backend
+        return self.exchanges.get(backend, self.exchange)
 
     def with_expert_bias(self, bias: torch.Tensor) -> "MoeLayer":
         self.expert_bias = bias
@@ -142,10 +179,11 @@ class MoeLayer:
         idx, wts, counts, _ = self.route(x)
         self.last_counts = counts
         self.metrics = MoeForwardMetrics(t, int(counts.max()), int((counts == 0).sum()))
-        if self.exchange is not None:
-            rows, layout = self.exchange.dispatch(x, idx)
+        exchange = self._exchange_for(x)
+        if exchange is not None:
+            rows, layout = exchange.dispatch(x, idx)
             y = self.experts.grouped_rows(rows, layout.offsets)
-            out = self.exchange.combine(y, wts, layout)
+            out = exchange.combine(y, wts, layout)
         elif self.strategy == MoeStrategy.PER_EXPERT:
             out = ref.moe_ffn(x, idx, wts, self.experts._dense("gate_up", x.dtype),
                               self.experts._dense("down", x.dtype))

@@ -27,17 +27,22 @@ class OverlapStats:
 
 
 class MoePipeline:
-    def __init__(self, layer: MoeLayer, side_stream: Optional["torch.cuda.Stream"] = None):
+    """The two streams come from a ``StreamManager``; every piece of work is submitted with the
+    tensors it reads and writes, and the manager's hazard tracker inserts the event waits (so
+    ``RMLX_DEBUG_SERIALIZE=1`` serialises the schedule without touching this code)."""
+
+    def __init__(self, layer: MoeLayer, streams=None):
         self.layer = layer
-        self._side = side_stream
+        self._streams = streams
         self.stats = OverlapStats()
 
-    def _side_stream(self, x: torch.Tensor):
+    def _manager(self, x: torch.Tensor):
         if not x.is_cuda:
             return None
-        if self._side is None:
-            self._side = torch.cuda.Stream(x.device)
-        return self._side
+        if self._streams is None:
+            from ..runtime.streams import StreamManager
+            self._streams = StreamManager(x.device)
+        return self._streams
 
     def _shared(self, x: torch.Tensor) -> torch.Tensor:
         gu, dn = self.layer.shared
@@ -56,18 +61,19 @@ class MoePipeline:
         """Shared expert on the side stream, routed experts on the current stream, one join."""
         if self.layer.shared is None:
             return self.layer.forward(x)
-        side = self._side_stream(x)
-        self.stats = OverlapStats(1, side is not None, x.shape[0], x.shape[0])
-        if side is None:
+        sm = self._manager(x)
+        self.stats = OverlapStats(1, sm is not None, x.shape[0], x.shape[0])
+        if sm is None:
             return (self._routed(x) + self._shared(x)).to(x.dtype)
-        main = torch.cuda.current_stream(x.device)
-        side.wait_stream(main)                    # x is ready
-        with torch.cuda.stream(side):
-            s = self._shared(x)
-        r = self._routed(x)
-        main.wait_stream(side)                    # join: the sum needs both
-        s.record_stream(main)
-        return (r + s).to(x.dtype)
+        from ..runtime.streams import STREAM_COPY, STREAM_DEFAULT
+        _, x = sm.submit(STREAM_DEFAULT, lambda: x, writes=[x])          # x is produced on the main stream
+        _, s = sm.submit(STREAM_COPY, lambda: self._shared(x), reads=[x])
+        _, r = sm.submit(STREAM_DEFAULT, lambda: self._routed(x), reads=[x])
+        s.record_stream(sm.get(STREAM_DEFAULT))
+        # the sum reads what the side stream wrote: the tracker makes the main stream wait for it
+        _, out = sm.submit(STREAM_DEFAULT, lambda: (r + s).to(x.dtype), reads=[r, s])
+        sm.reap()
+        return out
 
     # ------------------------------------------------------------------ TBO
     def forward_tbo(self, x: torch.Tensor, micro_batches: int = 2) -> torch.Tensor:
@@ -77,23 +83,22 @@ class MoePipeline:
         t = x.shape[0]
         n = max(1, min(micro_batches, t))
         bounds = [t * i // n for i in range(n + 1)]
-        side = self._side_stream(x)
-        self.stats = OverlapStats(n, side is not None and n > 1, t if self.layer.shared else 0, t)
+        sm = self._manager(x)
+        self.stats = OverlapStats(n, sm is not None and n > 1, t if self.layer.shared else 0, t)
         outs = []
-        if side is None or n == 1:
+        if sm is None or n == 1:
             for i in range(n):
                 outs.append(self.layer.forward(x[bounds[i]:bounds[i + 1]]))
             return torch.cat(outs, 0)
-        main = torch.cuda.current_stream(x.device)
-        side.wait_stream(main)
+        from ..runtime.streams import STREAM_COPY, STREAM_DEFAULT
+        _, x = sm.submit(STREAM_DEFAULT, lambda: x, writes=[x])
         for i in range(n):
             chunk = x[bounds[i]:bounds[i + 1]]
-            if i % 2 == 0:
-                outs.append(self.layer.forward(chunk))
-            else:
-                with torch.cuda.stream(side):
-                    o = self.layer.forward(chunk)
-                o.record_stream(main)
-                outs.append(o)
-        main.wait_stream(side)
-        return torch.cat(outs, 0)
+            name = STREAM_DEFAULT if i % 2 == 0 else STREAM_COPY
+            _, o = sm.submit(name, lambda c=chunk: self.layer.forward(c), reads=[chunk])
+            if name != STREAM_DEFAULT:
+                o.record_stream(sm.get(STREAM_DEFAULT))
+            outs.append(o)
+        _, out = sm.submit(STREAM_DEFAULT, lambda: torch.cat(outs, 0), reads=outs)
+        sm.reap()
+        return out

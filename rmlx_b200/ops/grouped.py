@@ -20,8 +20,11 @@ def _grouped_ok(w: LinearWeight) -> bool:
 
 
 def grouped_expert_ffn(x_sorted: torch.Tensor, offsets: torch.Tensor, gate_up: LinearWeight,
-                       down: LinearWeight) -> torch.Tensor:
-    """x_sorted [R, D] bf16 (rows grouped by expert), offsets [E+1] -> [R, D]."""
+                       down: LinearWeight, zero_rest: bool = False) -> torch.Tensor:
+    """x_sorted [R, D] bf16 (rows grouped by expert), offsets [E+1] -> [R, D]. The offsets are
+    absolute row numbers of ``x_sorted``, so a rank that holds a slice of the experts passes the
+    matching slice of the global offsets; ``zero_rest`` then returns zeros in the rows of the
+    experts it does not hold."""
     if gate_up.kind == W_Q8 or gate_up.scales_f16:   # expanded to bf16 for the grouped tensor-core GEMM
         gate_up = LinearWeight(W_BF16, gate_up.dense_bf16())
     if down.kind == W_Q8 or down.scales_f16:
@@ -30,16 +33,22 @@ def grouped_expert_ffn(x_sorted: torch.Tensor, offsets: torch.Tensor, gate_up: L
         raise ImportError("shape not covered by the grouped tensor-core kernel")
     off = offsets.to(torch.int32)
     act = xgemm(x_sorted.contiguous(), gate_up, offsets=off, swiglu=True)   # SwiGLU in the epilogue
-    return xgemm(act, down, offsets=off)
+    out = None
+    if zero_rest:
+        out = torch.zeros(x_sorted.shape[0], down.n, dtype=torch.bfloat16, device=x_sorted.device)
+    return xgemm(act, down, offsets=off, out=out)
 
 
 def moe_prefill_ffn(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, offsets: torch.Tensor,
                     gate_up: LinearWeight, down: LinearWeight,
-                    residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """x [T, D] bf16, idx/wts [T, k] from the router, offsets [E+1] int32 (device)."""
+                    residual: Optional[torch.Tensor] = None, expert_base: int = 0) -> torch.Tensor:
+    """x [T, D] bf16, idx/wts [T, k] from the router, offsets [E+1] int32 (device) over ALL
+    experts. ``gate_up`` / ``down`` hold experts ``expert_base .. expert_base + E_local``; pairs
+    routed elsewhere contribute zero (the caller sums the ranks' results)."""
     t, d = x.shape
     k = idx.shape[1]
-    e = gate_up.experts
+    e = offsets.numel() - 1
+    e_local = gate_up.experts
     lib, st = _lib.cuda(), _lib.stream_ptr()
     xs = torch.empty(t * k, d, dtype=torch.bfloat16, device=x.device)
     row_of_pair = torch.empty(t * k, dtype=torch.int32, device=x.device)
@@ -47,7 +56,11 @@ def moe_prefill_ffn(x: torch.Tensor, idx: torch.Tensor, wts: torch.Tensor, offse
     _lib.check(lib.rmlx_moe_scatter_rows(x.data_ptr(), x.stride(0), idx.data_ptr(), offsets.data_ptr(),
                                          cursors.data_ptr(), xs.data_ptr(), row_of_pair.data_ptr(),
                                          t, k, d, e, st), "moe_scatter_rows")
-    y = grouped_expert_ffn(xs, offsets, gate_up, down)
+    if e_local == e:
+        y = grouped_expert_ffn(xs, offsets, gate_up, down)
+    else:
+        y = grouped_expert_ffn(xs, offsets[expert_base:expert_base + e_local + 1], gate_up, down,
+                               zero_rest=True)
     out = torch.empty(t, d, dtype=torch.bfloat16, device=x.device)
     _lib.check(lib.rmlx_moe_combine(y.data_ptr(), row_of_pair.data_ptr(), wts.data_ptr(),
                                     _lib.ptr(residual), 0 if residual is None else residual.stride(0),

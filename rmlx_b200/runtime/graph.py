@@ -31,34 +31,45 @@ class GraphCache:
     def __len__(self) -> int:
         return len(self._g)
 
-    def get_or_capture(self, key: Hashable, fn: Callable[[], None], warmup: int = 1):
-        """Returns a replayable object for ``fn`` (a CUDA graph; on CPU, ``fn`` itself)."""
+    def get_or_capture(self, key: Hashable, fn: Callable[[], None], warmup: int = 1,
+                       restore: Optional[Callable[[], None]] = None, device=None):
+        """Returns a replayable object for ``fn`` (a CUDA graph; on CPU, ``fn`` itself).
+        ``restore`` is called after the warm-up runs and after the capture: it puts back whatever
+        state ``fn`` advances (a decode step moves its own positions), so that capturing leaves no
+        trace."""
         g = self._g.get(key)
         if g is not None:
             self._g.move_to_end(key)
             self.hits += 1
             return g
         self.misses += 1
-        g = self._capture(fn, warmup)
+        g = self._capture(fn, warmup, restore, device)
         self._g[key] = g
         if len(self._g) > self.max_entries:
             self._g.popitem(last=False)
         return g
 
-    def _capture(self, fn, warmup):
+    def _capture(self, fn, warmup, restore=None, device=None):
         self.captures += 1
         if not torch.cuda.is_available():
             return _HostReplay(fn)
-        s = torch.cuda.Stream()
-        s.wait_stream(torch.cuda.current_stream())
+        from ..utils.metrics import PERF
+        PERF.add("graph_captures")
+        s = torch.cuda.Stream(device=device)
+        s.wait_stream(torch.cuda.current_stream(device))
         with torch.cuda.stream(s):
             for _ in range(warmup):
                 fn()
-        torch.cuda.current_stream().wait_stream(s)
-        torch.cuda.synchronize()
+        torch.cuda.current_stream(device).wait_stream(s)
+        torch.cuda.synchronize(device)
+        if restore is not None:
+            restore()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=s):
             fn()
+        if restore is not None:
+            restore()
+        torch.cuda.synchronize(device)
         return g
 
     def invalidate(self, key: Optional[Hashable] = None) -> None:
@@ -126,11 +137,31 @@ class HazardTracker:
         self._inflight.append(op)
         return deps
 
+    def add_writes(self, op_id: int, writes) -> None:
+        """Ranges an in-flight operation turned out to write (its freshly allocated results)."""
+        for o in self._inflight:
+            if o.op_id == op_id:
+                o.writes.extend(writes)
+
+    def last_id(self) -> int:
+        """Id of the operation submitted last."""
+        return self._next - 1
+
     def retire(self, op_id: int) -> None:
         self._inflight = [o for o in self._inflight if o.op_id != op_id]
 
     def retire_stream(self, stream: str) -> None:
         self._inflight = [o for o in self._inflight if o.stream != stream]
 
+    def retire_all(self) -> None:
+        """Everything submitted so far has completed (a device synchronisation)."""
+        self._inflight = []
+
     def in_flight(self) -> int:
         return len(self._inflight)
+
+
+# Process-wide tracker: the multi-stream schedules (runtime.streams.StreamManager.submit) register
+# their operations here; RMLX_DEBUG_SERIALIZE=1 makes every dependency check answer "wait".
+import os as _os
+HAZARDS = HazardTracker(serialize=_os.environ.get("RMLX_DEBUG_SERIALIZE", "0") == "1")

@@ -85,6 +85,8 @@ class GpuFence:
 class StreamManager:
     def __init__(self, device=None, names=(STREAM_DEFAULT, STREAM_COMPUTE, STREAM_COPY)):
         self._cuda = torch.cuda.is_available()
+        self._events: Dict[int, "torch.cuda.Event"] = {}
+        self.waits_inserted = 0
         self.streams: Dict[str, Optional[torch.cuda.Stream]] = {}
         for n in names:
             if not self._cuda:
@@ -96,6 +98,57 @@ class StreamManager:
 
     def get(self, name: str):
         return self.streams[name]
+
+    def submit(self, name: str, fn, reads=(), writes=(), temporaries=()):
+        """Run ``fn`` on stream ``name`` after the operations still in flight on OTHER streams
+        that it depends on: ``reads`` / ``writes`` are the tensors (or (address, end) ranges) it
+        touches, and the process-wide hazard tracker (runtime.graph.HAZARDS) names the RAW / WAW /
+        WAR predecessors whose completion events the stream then waits for. Work on one stream
+        needs no event. With RMLX_DEBUG_SERIALIZE=1 the tracker reports every in-flight operation
+        as a dependency, which serialises the schedule (crates/rmlx-metal/src/command.rs:130-311,
+        the ``tracked_hazards`` switch of device.rs:23-32). Returns (op id, fn's result)."""
+        from .graph import HAZARDS
+
+        def ranges(items):
+            out = []
+            for t in items:
+                if isinstance(t, torch.Tensor):
+                    a = t.data_ptr()
+                    out.append((a, a + max(1, t.numel() * t.element_size())))
+                else:
+                    out.append((int(t[0]), int(t[1])))
+            return out
+
+        deps = HAZARDS.submit(name, ranges(reads), ranges(writes), ranges(temporaries))
+        op_id = HAZARDS.last_id()
+        stream = self.streams[name]
+        for dep, _kind in deps:
+            ev = self._events.get(dep)
+            if ev is not None and self._cuda:
+                stream.wait_event(ev)
+        self.waits_inserted += len(deps)
+        if self._cuda:
+            with torch.cuda.stream(stream):
+                result = fn()
+            ev = torch.cuda.Event()
+            ev.record(stream)
+            self._events[op_id] = ev
+            # tensors the operation returns are its writes too (they did not exist before it ran)
+            outs = [result] if isinstance(result, torch.Tensor) else \
+                [r for r in result if isinstance(r, torch.Tensor)] if isinstance(result, (list, tuple)) else []
+            HAZARDS.add_writes(op_id, ranges(outs))
+        else:
+            result = fn()
+            HAZARDS.retire(op_id)      # host execution is synchronous
+        return op_id, result
+
+    def reap(self) -> int:
+        """Retire the submitted operations whose events have completed; returns how many remain."""
+        from .graph import HAZARDS
+        for op_id in [k for k, ev in self._events.items() if ev.query()]:
+            HAZARDS.retire(op_id)
+            del self._events[op_id]
+        return len(self._events)
 
     def order(self, before: str, after: str) -> GpuFence:
         """Everything queued on ``before`` happens before later work on ``after``."""

@@ -82,14 +82,15 @@ class SpeculativeDecoder:
             dprobs = []
             feed = unfed
             for _ in range(k):
-                dl = drf.forward(torch.tensor(feed, device=drf.device), dc, [0], last_only=True)
+                dl = drf.prefill(torch.tensor(feed, device=drf.device), dc, 0)
                 tok, probs = self._pick(dl[0].float(), out + proposals)
                 proposals.append(tok)
                 dprobs.append(probs)
                 feed = [tok]
             # the draft cache now holds everything up to proposals[k-2]; proposals[k-1] is unfed
             # ---- target: one forward over the pending token and the k proposals
-            tl = tgt.forward(torch.tensor([pending] + proposals, device=tgt.device), tc, [0]).float().cpu()
+            tl = tgt.prefill(torch.tensor([pending] + proposals, device=tgt.device), tc, 0,
+                             all_logits=True).float().cpu()
             if self.greedy:
                 res = Sampler.greedy_verify(proposals, tl)
             else:

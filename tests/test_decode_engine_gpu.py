@@ -197,3 +197,86 @@ def test_step_kernel_matches_oracle(dev, quant, use_graph, ctx):
             assert err <= 5e-2 * mag + 2e-2, f"step {i}: err {err} mag {mag}"
         assert (outs[0] - outs[1]).abs().max().item() <= 3e-2 * mag + 1e-2
     assert engines[0].cache.seq_len(0) == ctx + steps
+
+
+def test_one_graph_per_batch_bucket(dev):
+    """An engine sized for 8 rows runs the smallest bucket that holds the bound rows, keeps one
+    captured graph per bucket, and gives the same tokens whichever bucket ran."""
+    cfg = tiny_moe_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant="q4"))
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g) for n in (9, 14, 5)]
+
+    def run(max_batch, seqs):
+        cache = model.new_cache(8 * max(2, len(prompts)), max_seqs=4)
+        last = []
+        for s in seqs:
+            cache.add_sequence(s)
+            last.append(int(model.forward(prompts[s].to(dev), cache, [s], last_only=True)[0].argmax()))
+        eng = CachedDecode(model, cache, max_batch=max_batch)
+        eng.bind(seqs, last)
+        return eng, eng.generate(4)
+
+    eng1, t1 = run(1, [0])
+    eng8, t8 = run(8, [0])
+    assert eng8.buckets == (1, 2, 4, 8) and eng8.bucket() == 1
+    assert torch.equal(t1, t8)
+    assert len(eng8.graphs) == 1 and eng8.graphs.captures == 1 and eng8.graphs.hits >= 3
+    # three rows: the 4-row bucket; a second graph appears, the first stays
+    eng8b, t3 = run(8, [0, 1, 2])
+    assert eng8b.bucket() == 4 and torch.equal(t3[0], t1[0])
+    eng8b.bind([1], [int(t3[1, -1])])
+    eng8b.reserve(2)
+    eng8b.step()
+    assert len(eng8b.graphs) == 2
+
+
+def test_debug_serialize_runs_launch_by_launch(dev):
+    """Debug-serialize mode: the step runs un-captured, every launch is followed by a device
+    synchronisation and a read of the status words, and the result is unchanged."""
+    from rmlx_b200 import _lib
+    cfg = tiny_moe_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant=None))
+    prompt = torch.randint(0, cfg.vocab_size, (11,), generator=torch.Generator().manual_seed(1))
+
+    def run(serialize):
+        cache = model.new_cache(8, max_seqs=1)
+        cache.add_sequence(0)
+        last = int(model.forward(prompt.to(dev), cache, [0], last_only=True)[0].argmax())
+        eng = CachedDecode(model, cache, max_batch=1)
+        eng.serialize = serialize
+        eng.bind([0], [last])
+        return eng, eng.generate(3)
+
+    _, want = run(False)
+    _lib.set_debug_serialize(True)
+    try:
+        _lib.serial_trace()
+        eng, got = run(True)
+        trace = _lib.serial_trace()
+    finally:
+        _lib.set_debug_serialize(False)
+    assert torch.equal(got, want)
+    assert len(eng.graphs) == 0
+    assert len(trace) >= 3 * eng.launches_per_step and "decode_advance" in trace
+
+
+def test_moe_overlap_schedules_on_two_streams(dev):
+    """Shared-expert and token-batch overlap on real streams: the hazard tracker inserts the event
+    waits, the result equals the plain forward."""
+    from rmlx_b200.config import MoeConfig
+    from rmlx_b200.nn.moe import ExpertGroup, MoeLayer
+    from rmlx_b200.ops.weights import LinearWeight
+    torch.manual_seed(0)
+    mc = MoeConfig(num_experts=4, num_experts_per_token=2, hidden_dim=64, intermediate_dim=128)
+    mk = lambda *s: LinearWeight.from_dense(torch.randn(*s) * 0.1, None, dtype=torch.bfloat16, device=dev)
+    layer = MoeLayer(mc, (torch.randn(4, 64) * 0.3).to(dev), ExpertGroup(mk(4, 256, 64), mk(4, 64, 128)))
+    layer.with_shared_expert(mk(256, 64), mk(64, 128))
+    x = torch.randn(48, 64, device=dev, dtype=torch.bfloat16)
+    want = layer.forward(x).float()
+    for mode in ("sbo", "tbo"):
+        got = layer.with_overlap(mode).forward_overlapped(x).float()
+        torch.cuda.synchronize()
+        assert (got - want).abs().max() <= 2e-2 * want.abs().max()
+        sm = layer._pipeline._streams
+        assert sm.waits_inserted >= 2            # x -> side stream, side stream -> sum

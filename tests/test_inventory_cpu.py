@@ -156,3 +156,46 @@ def test_ncu_summary_parses_raw_csv():
     assert b.stalls[0] == (3.25, "wait")
     assert "top stalls" in a.render() and "regs/thread: 131" in a.render()
     assert parse_raw_csv("") == []
+
+
+def test_moe_layer_picks_its_exchange_through_the_policy_and_overlap_mode():
+    from rmlx_b200.parallel.moe_policy import MoeBackend, MoePolicy, ThresholdCalibration
+
+    class Loopback:
+        """Single-rank exchange: sorts the (token, slot) pairs by expert, as the real ones do."""
+        def __init__(self, n_experts):
+            self.e, self.calls = n_experts, 0
+
+        def dispatch(self, x, idx):
+            self.calls += 1
+            k = idx.shape[1]
+            flat = idx.reshape(-1).long()
+            order = torch.argsort(flat, stable=True)
+            offsets = torch.zeros(self.e + 1, dtype=torch.int64)
+            offsets[1:] = torch.cumsum(torch.bincount(flat, minlength=self.e), 0)
+            lay = type("L", (), {})()
+            lay.offsets, lay.order, lay.k, lay.t = offsets, order, k, x.shape[0]
+            return x[order // k], lay
+
+        def combine(self, y, wts, lay):
+            out = torch.zeros(lay.t, y.shape[-1])
+            out.index_add_(0, lay.order // lay.k, y.float() * wts.reshape(-1)[lay.order].float()[:, None])
+            return out
+
+    layer = _moe_layer()
+    x_small, x_large = torch.randn(4, 32), torch.randn(40, 32)
+    want_small, want_large = layer.forward(x_small), layer.forward(x_large)
+    fused, lib = Loopback(4), Loopback(4)
+    pol = MoePolicy(ThresholdCalibration(small_n_max=8, large_n_min=32), hysteresis=0, cooldown_s=0.0,
+                    cooldown_calls=0, env={})
+    layer.with_policy(pol, {MoeBackend.FUSED: fused, MoeBackend.LOCAL: None})
+    assert torch.allclose(layer.forward(x_small), want_small, atol=1e-5) and fused.calls == 0
+    assert torch.allclose(layer.forward(x_large), want_large, atol=1e-5) and fused.calls == 1
+    pol.force_backend(MoeBackend.NCCL)
+    layer.exchanges[MoeBackend.NCCL] = lib
+    assert torch.allclose(layer.forward(x_small), want_small, atol=1e-5) and lib.calls == 1
+    layer.with_policy(None, {})
+    for mode in ("sbo", "tbo", None):
+        assert torch.allclose(layer.with_overlap(mode).forward_overlapped(x_large), want_large, atol=1e-5)
+    with pytest.raises(ValueError):
+        layer.with_overlap("both")

@@ -147,6 +147,40 @@ def test_native_prefill_matches_oracle(dev, cfg_fn, quant):
     assert int(out[0, 0]) in top5
 
 
+def test_native_prefill_all_positions_and_speculative_verify(dev):
+    """Every position's logits from the tensor-core forward (what speculative verification
+    reads), and the draft-and-verify runner on that path reproduces the target's greedy output."""
+    from rmlx_b200.serve.speculative import SpeculativeDecoder
+    cfg = _moe_cfg()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant=None))
+    assert enable_native_prefill(model, chunk=64)
+    oracle = _oracle_from(model)
+    prompt = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(4))
+    oc = oracle.new_cache(8, max_seqs=1)
+    oc.add_sequence(0)
+    want = oracle.forward(prompt, oc, [0])
+    cache = model.new_cache(8, max_seqs=1)
+    cache.add_sequence(0)
+    got = model.prefill(prompt.to(dev), cache, 0, all_logits=True).float().cpu()
+    assert got.shape == want.shape == (70, cfg.vocab_size)
+    assert (got - want).abs().max().item() / want.abs().max().item() < 4e-2
+    rel_fro = ((got - want).norm() / want.norm()).item()
+    assert rel_fro < 2e-2, rel_fro
+    # a draft equal to the target: every proposal is accepted, output = the target's greedy tokens
+    dec = SpeculativeDecoder(model, model, k=3)
+    out = dec.generate(prompt[:20].tolist(), 8)
+    c2 = model.new_cache(8, max_seqs=1)
+    c2.add_sequence(0)
+    lg = model.prefill(prompt[:20].to(dev), c2, 0)
+    ref_toks = []
+    for _ in range(8):
+        tok = int(lg[0].argmax())
+        ref_toks.append(tok)
+        lg = model.prefill(torch.tensor([tok], device=dev), c2, 0)
+    assert out == ref_toks
+    assert dec.stats.accepted == dec.stats.proposed
+
+
 @pytest.mark.parametrize("cfg_fn", [_dense_cfg, _moe_cfg])
 @pytest.mark.parametrize("use_graph", [False, True])
 def test_batched_decode_matches_oracle(dev, cfg_fn, use_graph):

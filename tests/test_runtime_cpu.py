@@ -95,3 +95,23 @@ def test_logging_metrics_guard_shutdown():
     assert g.check(peaked) in (GuardAction.WARN, GuardAction.FALLBACK)
     s = ShutdownSignal(); h = s.handle()
     assert not h.is_shutdown(); s.trigger(); assert h.is_shutdown() and h.wait(0.01)
+
+
+def test_stream_manager_submit_tracks_hazards_on_the_host():
+    graph.HAZARDS.retire_all()
+    sm = streams.StreamManager()
+    a = torch.zeros(8)
+    op0, _ = sm.submit("compute", lambda: a.add_(1), writes=[a])
+    op1, r = sm.submit("copy", lambda: a * 2, reads=[a])
+    assert op1 == op0 + 1 and float(r[0]) == 2.0
+    # host execution is synchronous: nothing stays in flight, no event wait was needed
+    assert graph.HAZARDS.in_flight() == 0 and sm.reap() == 0
+
+
+def test_hazard_tracker_learns_the_results_of_an_operation():
+    h = graph.HazardTracker()
+    h.submit("copy", reads=[(0, 10)])
+    h.add_writes(h.last_id(), [(100, 140)])
+    assert h.submit("compute", reads=[(120, 130)]) == [(0, "RAW")]
+    h.retire_all()
+    assert h.in_flight() == 0
