@@ -31,6 +31,10 @@ extern "C" {
 //
 // * The first call on each device resolves the scratch array's device address (once per device,
 //   with that device current). Make that first call outside any stream capture.
+// * The device that owns `stream` must be the current device of the calling thread: the scratch
+//   address is looked up for the current device, not for the stream's. The first-call lookup is
+//   not synchronised between host threads (concurrent first calls on one device all store the
+//   same address, which is harmless, but do not rely on it for ordering).
 // * All calls share the one scratch array, and it keeps whatever the previous call left in it
 //   (the part that must start at zero, the per-tile tickets, is cleared on the stream by every
 //   call). Two calls that overlap on the GPU, e.g. on different streams, race on it: serialise them.

@@ -91,11 +91,14 @@ class BlockManager:
         (src_block, dst_block) pairs for a shared last block that is about to be written."""
         if seq_id not in self.tables:
             self.add_sequence(seq_id)
-        if not self.can_allocate(seq_id, new_tokens):
-            raise OutOfBlocks(f"need {self.blocks_needed(seq_id, new_tokens)} blocks, "
-                              f"{len(self.free)} free")
-        copies = []
         table, cur = self.tables[seq_id], self.lengths[seq_id]
+        # a shared partial last block is copied before it is written: count that block too, so
+        # that the request fails before anything has changed
+        cow = bool(new_tokens > 0 and table and cur % self.block_size != 0 and self.ref[table[-1]] > 1)
+        need = self.blocks_needed(seq_id, new_tokens) + (1 if cow else 0)
+        if need > len(self.free):
+            raise OutOfBlocks(f"need {need} blocks, {len(self.free)} free")
+        copies = []
         if new_tokens > 0 and table and cur % self.block_size != 0:
             last = table[-1]
             if self.ref[last] > 1:                       # shared partial block: copy before write
@@ -189,6 +192,10 @@ class PagedKvCache:
                                        pin_memory=self.device.type == "cuda")
         self.slot_of: Dict[int, int] = {}
         self._free_slots = list(range(max_seqs - 1, -1, -1))
+        # the pinned row of a slot is the source of an asynchronous copy: the event recorded after
+        # the copy is waited for before the row is written again (by a later update of the same
+        # sequence, or by the next sequence that takes the slot)
+        self._row_copied: Dict[int, "torch.cuda.Event"] = {}
 
     # -------------------------------------------------------------- sequences
     def add_sequence(self, seq_id: int) -> int:
@@ -200,6 +207,7 @@ class PagedKvCache:
     def free_sequence(self, seq_id: int) -> None:
         self.manager.free_sequence(seq_id)
         slot = self.slot_of.pop(seq_id)
+        self._row_idle(slot)
         self._host_table[slot].zero_()
         self._free_slots.append(slot)
 
@@ -218,14 +226,25 @@ class PagedKvCache:
     def seq_len(self, seq_id: int) -> int:
         return self.manager.seq_len(seq_id)
 
+    def _row_idle(self, slot: int) -> None:
+        """Wait until the last queued copy out of the slot's pinned row has run."""
+        ev = self._row_copied.pop(slot, None)
+        if ev is not None:
+            ev.synchronize()
+
     def _sync_slot(self, seq_id: int) -> None:
         slot = self.slot_of[seq_id]
         table = self.manager.block_table(seq_id)
         if len(table) > self.max_blocks_per_seq:
             raise OutOfBlocks("sequence exceeds max_blocks_per_seq")
+        self._row_idle(slot)
         row = self._host_table[slot]
         row[:len(table)] = torch.tensor(table, dtype=torch.int32)
         self.block_table[slot].copy_(row, non_blocking=True)
+        if self.device.type == "cuda":
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(self.device))
+            self._row_copied[slot] = ev
 
     def reserve(self, seq_id: int, new_tokens: int) -> None:
         """Ensure blocks exist for ``new_tokens`` more tokens (doing any copy-on-write) and push

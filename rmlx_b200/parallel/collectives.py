@@ -8,6 +8,8 @@ Counterpart of the reference's ``Group`` algorithms executed on the CPU over RDM
 """
 from __future__ import annotations
 
+import ctypes
+
 from typing import Optional
 
 import torch
@@ -20,6 +22,9 @@ from .comm import SymmetricRegion
 _lib.register_cuda_sigs({
     "rmlx_coll": ("ppiiiippqqiipp", "i"),
     "rmlx_coll_area_bytes": ("iq", "q"),
+    "rmlx_nvls_allreduce": ("pqipiiip", "i"),
+    "rmlx_nvls_flag_bytes": ("", "i"),
+    "rmlx_nvls_status": ("", "i"),
 })
 
 ALL_GATHER, ALL_TO_ALL, REDUCE_SCATTER, ALL_REDUCE, BROADCAST = range(5)
@@ -40,6 +45,14 @@ class PeerCollectives:
         self.region = SymmetricRegion(area + 256, group)
         self._buf = self.region.peer_array(0)
         self._ctl = self.region.peer_array(area)
+        # in-switch all-reduce: an operand buffer and a flag area in the symmetric heap, usable
+        # when the heap is bound to NVLink multicast objects (RMLX_SYMM_MULTICAST=1)
+        self._nvls = None
+        if getattr(self.region, "mc", 0):
+            self.nvls_cap = self.cap * self.world
+            flag_bytes = int(_lib.cuda().rmlx_nvls_flag_bytes())
+            self._nvls = SymmetricRegion(self.nvls_cap + 256 + flag_bytes, group)
+            self._nvls_flags = self._nvls.peer_array(self.nvls_cap + 256)
 
     def _run(self, op: int, src: torch.Tensor, dst: torch.Tensor, chunk_bytes: int, root: int = 0) -> torch.Tensor:
         assert src.is_contiguous() and dst.is_contiguous() and src.is_cuda and dst.is_cuda
@@ -80,13 +93,59 @@ class PeerCollectives:
         out = out if out is not None else torch.empty_like(x)
         return self._run(ALL_REDUCE, x, out, x.numel() * x.element_size() // self.world)
 
+    @property
+    def nvls_available(self) -> bool:
+        return self._nvls is not None
+
+    def nvls_buffer(self, dtype: torch.dtype, numel: int) -> torch.Tensor:
+        """View of this rank's copy of the in-switch all-reduce operand: a producer that writes
+        its partial result here saves the staging copy of ``all_reduce_nvls``."""
+        from .tp_gemm import _RawCuda
+        nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        if nbytes > self.nvls_cap:
+            raise ValueError(f"{nbytes} bytes exceed the operand buffer of {self.nvls_cap}")
+        raw = torch.as_tensor(_RawCuda(self._nvls.local, nbytes), device=self.device)
+        return raw.view(dtype)
+
+    def all_reduce_nvls(self, x: Optional[torch.Tensor] = None, numel: Optional[int] = None,
+                        dtype: Optional[torch.dtype] = None, out: Optional[torch.Tensor] = None):
+        """Sum over ranks done by the NVLink switch (``multimem.ld_reduce`` + ``multimem.st``,
+        csrc/comm/nvls.cu). With ``x`` the operand is staged into the heap buffer first; without it
+        the buffer (``nvls_buffer(dtype, numel)``) is reduced in place and returned as a view."""
+        if self._nvls is None:
+            raise _lib.NativeError("the symmetric heap is not bound to NVLink multicast "
+                                   "(RMLX_SYMM_MULTICAST=1 on a box that supports it)")
+        if x is not None:
+            x = x.contiguous()
+            numel, dtype = x.numel(), x.dtype
+        if dtype not in (torch.bfloat16, torch.float32):
+            raise ValueError("sums are implemented for bf16 and fp32")
+        buf = self.nvls_buffer(dtype, numel)
+        nbytes = buf.numel() * buf.element_size()
+        if nbytes % 16:
+            raise ValueError("the operand must be a whole number of 16-byte vectors")
+        if x is not None:
+            buf.copy_(x.view(-1))
+        rc = _lib.cuda().rmlx_nvls_allreduce(ctypes.c_void_p(self._nvls.mc), nbytes,
+                                             int(dtype == torch.bfloat16), self._nvls_flags, self.rank,
+                                             self.world, 0, _lib.stream_ptr())
+        _lib.check(rc, "nvls_allreduce")
+        if x is None:
+            return buf
+        out = out if out is not None else torch.empty_like(x)
+        out.view(-1).copy_(buf)
+        return out
+
     def broadcast(self, x: torch.Tensor, root: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         x = x.contiguous()
         out = out if out is not None else torch.empty_like(x)
         return self._run(BROADCAST, x, out, x.numel() * x.element_size(), root)
 
     def status(self) -> int:
-        return int(GemmStatus.get(self.device).item())
+        return int(GemmStatus.get(self.device).item()) or int(_lib.cuda().rmlx_nvls_status())
 
     def close(self) -> None:
+        if self._nvls is not None:
+            self._nvls.close()
+            self._nvls = None
         self.region.close()

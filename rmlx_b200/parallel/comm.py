@@ -42,9 +42,21 @@ _lib.register_cuda_sigs({
 })
 
 
-class SymmetricRegion:
-    """One device allocation per rank, of the same size, with every peer's copy mapped locally.
-    ``ptrs[r]`` is the address, valid in this process, of rank r's region."""
+def SymmetricRegion(nbytes: int, group=None):
+    """Peer-mapped memory of ``nbytes`` per rank, zero-initialised, at the same offset of every
+    rank's symmetric heap (``parallel.symm_heap``): ``local`` is this rank's address, ``ptrs[r]``
+    the address, valid in this process, of rank r's copy. Falls back to one inter-process mapped
+    allocation per call where the heap is unavailable or switched off (``RMLX_SYMM_HEAP=0``)."""
+    from .symm_heap import default_heap
+    heap = default_heap(group)
+    if heap is not None:
+        return heap.alloc(nbytes)
+    return IpcRegion(nbytes, group)
+
+
+class IpcRegion:
+    """One device allocation per rank, of the same size, with every peer's copy mapped locally
+    through the legacy inter-process memory handles."""
 
     def __init__(self, nbytes: int, group=None):
         lib = _lib.cuda()

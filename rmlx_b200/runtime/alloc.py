@@ -4,7 +4,7 @@
 (crates/rmlx-alloc/src/allocator.rs:131-512): ``alloc`` / ``free`` / ``set_memory_limit`` /
 ``set_cache_limit`` / ``set_gc_limit`` / ``reset_peak_memory`` / ``clear_cache`` / ``stats`` /
 ``leak_detector``. ``BfcArena`` is the sub-allocator over one region
-(crates/rmlx-alloc/src/bfc.rs); ``SymmetricHeap`` runs a ``BfcArena`` over a peer-mapped region so
+(crates/rmlx-alloc/src/bfc.rs); the peer-mapped heap (``parallel.symm_heap.SymmetricHeap``) keeps its own growable arena so
 that every rank, performing the same allocation sequence, gets the same offsets in every peer's
 memory. The backing store defaults to host memory (tests run without a GPU); ``device=True``
 backs it with cudaMalloc.
@@ -222,28 +222,6 @@ class BfcArena:
             self.close()
         except Exception:
             pass
-
-
-class SymmetricHeap:
-    """A BFC arena over a peer-mapped region (see ``parallel.comm.SymmetricRegion``): ``alloc``
-    returns an offset that is valid on every rank; ``peer_ptr(rank, offset)`` is the address of
-    that rank's copy in this process."""
-
-    def __init__(self, region, alignment: int = 256):
-        self.region = region
-        self.arena = BfcArena(region.nbytes, alignment)
-
-    def alloc(self, nbytes: int) -> int:
-        return self.arena.alloc(nbytes)
-
-    def free(self, offset: int) -> None:
-        self.arena.free(offset)
-
-    def peer_ptr(self, rank: int, offset: int) -> int:
-        return self.region.ptrs[rank] + offset
-
-    def local_ptr(self, offset: int) -> int:
-        return self.region.local + offset
 
 
 def crc32(data: bytes, seed: int = 0) -> int:

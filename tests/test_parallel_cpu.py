@@ -303,3 +303,24 @@ def test_rank_leaves_between_steps_and_the_rest_re_rendezvous():
         assert res[r][0] == [6.0, 6.0, 6.0]
     assert res[2][1] is None
     assert res[0][1] == (0, 2, [3.0, 3.0, 3.0]) and res[1][1] == (1, 2, [3.0, 3.0, 3.0])
+
+
+def test_symmetric_heap_offset_arena_is_deterministic_and_coalesces():
+    from rmlx_b200.parallel.symm_heap import OffsetArena
+    a, b = OffsetArena(), OffsetArena()
+    for ar in (a, b):
+        assert ar.take(16) is None
+        ar.grow(1000)
+    seq = [256, 256, 256]
+    offs_a = [a.take(n) for n in seq]
+    offs_b = [b.take(n) for n in seq]
+    assert offs_a == offs_b == [0, 256, 512]
+    a.give(256, 256)
+    assert a.take(300) is None              # 256 in the middle, 232 at the end: neither fits
+    a.grow(1000)                            # the new segment merges with the free tail
+    assert a.take(300) == 768
+    a.give(0, 256)
+    assert a.free[0] == (0, 512)            # coalesced with its free neighbour
+    with pytest.raises(ValueError):
+        a.give(100, 50)                     # a range that is already free
+    assert a.free_bytes() + 256 + 300 == a.capacity
