@@ -54,8 +54,10 @@ __device__ __forceinline__ void mma_bf16_16816(float (&d)[4], const uint32_t (&a
 
 struct FdParams {
   const __nv_bfloat16* q;        // [B, Hq, HD]
-  const __nv_bfloat16* k_cache;  // [blocks, Hkv, 16, HD]
+  const __nv_bfloat16* k_cache;  // [blocks, Hkv, 16, HD]  (8-bit cache: uint8 of the same shape)
   const __nv_bfloat16* v_cache;
+  const char* k_sb;              // 8-bit cache: [blocks, Hkv, 16, HD/64] (scale, bias) bf16 pairs
+  const char* v_sb;
   const int* block_table;        // [B, max_blocks]
   const int* seq_lens;           // [B] tokens in the cache including the current one
   __nv_bfloat16* out;            // [B, Hq, HD]
@@ -66,15 +68,26 @@ struct FdParams {
   float scale_log2;              // softmax scale * log2(e)
 };
 
-template <int HD, int NST>
+// KVQ: the cache holds 8-bit affine values (x = q * scale + bias per token and group of 64 along
+// the head dimension; crates/rmlx-nn/src/attention.rs:4438-4680 keeps the same format on the host).
+// A stage then holds the raw pages and their (scale, bias) pairs, and the warp expands a page into
+// its own bf16 tile (same swizzled layout) right before it multiplies: half the DRAM bytes per
+// token, the tensor-core part unchanged.
+template <int HD, int NST, bool KVQ = false>
 __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
   constexpr int CH = HD / 8;             // 16-byte chunks per row
   constexpr int KS = HD / 16;            // k-steps of the QK^T product
   constexpr int NT = HD / 8;             // n-tiles of the PV product
   constexpr int PAGE_BYTES = kPage * HD * 2;
+  constexpr int G64 = HD / 64;                    // quantisation groups per row
+  constexpr int RAW_PAGE = kPage * HD;            // bytes of an 8-bit page
+  constexpr int SB_PAGE = kPage * G64 * 4;        // bytes of a page's (scale, bias) pairs
+  constexpr int STAGE_BYTES = KVQ ? 2 * RAW_PAGE + 2 * SB_PAGE : 2 * PAGE_BYTES;
+  constexpr int WARP_BYTES = NST * STAGE_BYTES + (KVQ ? 2 * PAGE_BYTES : 0);
   extern __shared__ __align__(128) char smem[];
-  // per warp: NST stages x (K page, V page); reused afterwards for the cross-warp merge
-  char* wsm = smem + (threadIdx.x >> 5) * (NST * 2 * PAGE_BYTES);
+  // per warp: NST stages x (K page, V page) (+ one expanded K/V tile for the 8-bit cache); reused
+  // afterwards for the cross-warp merge
+  char* wsm = smem + (threadIdx.x >> 5) * WARP_BYTES;
   __shared__ float s_m[kFdWarps][16], s_l[kFdWarps][16];
   __shared__ unsigned int s_last;
 
@@ -118,6 +131,24 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
   const int* bt = p.block_table + size_t(b) * p.max_blocks;
   auto issue = [&](int pg, int stage) {
     const int blk = RB_BOUNDS(pg, p.max_blocks) ? bt[pg] : 0;   // page 0 is the reserved page
+    if (KVQ) {
+      const size_t pgi = size_t(blk) * p.Hkv + kvh;
+      const char* ksrc = reinterpret_cast<const char*>(p.k_cache) + pgi * RAW_PAGE;
+      const char* vsrc = reinterpret_cast<const char*>(p.v_cache) + pgi * RAW_PAGE;
+      char* kd = wsm + stage * STAGE_BYTES;
+      char* vd = kd + RAW_PAGE;
+#pragma unroll
+      for (int i = 0; i < (RAW_PAGE / 16) / 32; ++i) {
+        const int idx = i * 32 + lane;
+        cp_async16(kd + idx * 16, ksrc + idx * 16);
+        cp_async16(vd + idx * 16, vsrc + idx * 16);
+      }
+      if (lane < SB_PAGE / 16) {
+        cp_async16(vd + RAW_PAGE + lane * 16, p.k_sb + pgi * SB_PAGE + lane * 16);
+        cp_async16(vd + RAW_PAGE + SB_PAGE + lane * 16, p.v_sb + pgi * SB_PAGE + lane * 16);
+      }
+      return;
+    }
     const char* ksrc = reinterpret_cast<const char*>(p.k_cache) +
                        (size_t(blk) * p.Hkv + kvh) * PAGE_BYTES;
     const char* vsrc = reinterpret_cast<const char*>(p.v_cache) +
@@ -134,6 +165,38 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
     }
   };
 
+  // 8-bit cache: expand stage `stage` (raw K and V pages) into the warp's bf16 tile pair.
+  auto expand = [&](int stage) {
+    const char* raw = wsm + stage * STAGE_BYTES;
+    char* tile = wsm + NST * STAGE_BYTES;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const char* src = raw + which * RAW_PAGE;
+      const char* sb = raw + 2 * RAW_PAGE + which * SB_PAGE;
+      char* dst = tile + which * PAGE_BYTES;
+#pragma unroll
+      for (int i = 0; i < (RAW_PAGE / 16) / 32; ++i) {
+        const int idx = i * 32 + lane;
+        const int r = idx / (HD / 16), k = idx % (HD / 16);     // token, 16-value piece
+        const uint4 w = *reinterpret_cast<const uint4*>(src + idx * 16);
+        const uint32_t sbv = *reinterpret_cast<const uint32_t*>(sb + (r * G64 + (k >> 2)) * 4);
+        const float sc = __uint_as_float(sbv << 16), bi = __uint_as_float(sbv & 0xffff0000u);
+        const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float f0 = fmaf(float(ww[j] & 0xffu), sc, bi), f1 = fmaf(float((ww[j] >> 8) & 0xffu), sc, bi);
+          const float f2 = fmaf(float((ww[j] >> 16) & 0xffu), sc, bi), f3 = fmaf(float(ww[j] >> 24), sc, bi);
+          o[2 * j] = pack_bf16(f0, f1);
+          o[2 * j + 1] = pack_bf16(f2, f3);
+        }
+        char* row = dst + r * (HD * 2);
+        *reinterpret_cast<uint4*>(row + (((2 * k) ^ (r & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(row + (((2 * k + 1) ^ (r & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+    }
+  };
+
   // Ring of NST stages per warp: the first NST pages are requested up front, so their DRAM
   // latencies overlap instead of adding up; a stage is refilled as soon as it has been consumed.
   int pg = pg0 + warp;
@@ -146,7 +209,8 @@ __global__ void __launch_bounds__(kFdThreads) flash_decode_kernel(FdParams p) {
   for (; pg < pg1; pg += kFdWarps) {
     cp_async_wait<NST - 1>();
     __syncwarp();
-    const uint32_t kbase = smem_u32(wsm + stage * 2 * PAGE_BYTES);
+    if (KVQ) { expand(stage); __syncwarp(); }
+    const uint32_t kbase = smem_u32(KVQ ? wsm + NST * STAGE_BYTES : wsm + stage * 2 * PAGE_BYTES);
     const uint32_t vbase = kbase + PAGE_BYTES;
 
     // S = Q K^T for 16 tokens: two n-tiles of 8 tokens.
@@ -329,17 +393,19 @@ extern "C" long long rmlx_flash_decode_ticket_elems(int B, int Hq, int Hkv) {
 // `splits` in [1, 64]: how many blocks share one sequence's context. `tickets` must be zero on the
 // first call; the kernel leaves it zero. `window` > 0 restricts attention to the last `window`
 // tokens (sliding-window models). head_dim 64 or 128, page size 16.
-extern "C" int rmlx_flash_decode_paged(const void* q, const void* k_cache, const void* v_cache,
-                                       const int* block_table, const int* seq_lens, void* out,
-                                       float* part_o, float* part_ml, unsigned int* tickets, int B,
-                                       int Hq, int Hkv, int HD, int max_blocks, int splits,
-                                       int window, float scale, int pdl, cudaStream_t st) {
+static int fd_launch(const void* q, const void* k_cache, const void* v_cache, const void* k_sb,
+                     const void* v_sb, const int* block_table, const int* seq_lens, void* out,
+                     float* part_o, float* part_ml, unsigned int* tickets, int B, int Hq, int Hkv,
+                     int HD, int max_blocks, int splits, int window, float scale, int pdl,
+                     cudaStream_t st) {
   if (B < 1 || Hq % Hkv || splits < 1 || splits > kFdMaxSplits) return -2;
   if (splits > 1 && (!part_o || !part_ml || !tickets)) return -2;
+  const bool kvq = k_sb != nullptr;
   FdParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
   p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.k_sb = static_cast<const char*>(k_sb); p.v_sb = static_cast<const char*>(v_sb);
   p.block_table = block_table; p.seq_lens = seq_lens;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.part_o = part_o; p.part_ml = part_ml; p.tickets = tickets;
@@ -351,17 +417,45 @@ extern "C" int rmlx_flash_decode_paged(const void* q, const void* k_cache, const
   // several blocks share an SM. Either way the staging area (>= 32 KB at HD 128, 16 KB at HD 64)
   // covers the cross-warp merge buffer and the split-merge tables.
   const bool deep = size_t(splits) * Hkv * p.gtiles * B <= size_t(2 * sm_count());
-#define RB_FD(HD_, NST_)                                                          \
-  {                                                                               \
-    const size_t smem = size_t(kFdWarps) * NST_ * 2 * kPage * HD_ * 2;            \
-    auto kern = flash_decode_kernel<HD_, NST_>;                                   \
-    RB_CHECK(set_max_smem(kern, smem));                                           \
-    return launch(kern, grid, dim3(kFdThreads), smem, st, pdl != 0, p);           \
+#define RB_FD(HD_, NST_, KVQ_)                                                                    \
+  {                                                                                               \
+    const size_t stage = KVQ_ ? 2 * kPage * HD_ + 2 * kPage * (HD_ / 64) * 4 : 2 * kPage * HD_ * 2; \
+    const size_t smem = size_t(kFdWarps) * (NST_ * stage + (KVQ_ ? 2 * kPage * HD_ * 2 : 0));     \
+    auto kern = flash_decode_kernel<HD_, NST_, KVQ_>;                                             \
+    RB_CHECK(set_max_smem(kern, smem));                                                           \
+    return launch(kern, grid, dim3(kFdThreads), smem, st, pdl != 0, p);                           \
   }
-  if (HD == 128) { if (deep) RB_FD(128, 4) else RB_FD(128, 2) }
-  if (HD == 64) { if (deep) RB_FD(64, 4) else RB_FD(64, 2) }
+  if (kvq) {
+    if (HD == 128) { if (deep) RB_FD(128, 4, true) else RB_FD(128, 2, true) }
+    if (HD == 64) { if (deep) RB_FD(64, 4, true) else RB_FD(64, 2, true) }
+    return -2;
+  }
+  if (HD == 128) { if (deep) RB_FD(128, 4, false) else RB_FD(128, 2, false) }
+  if (HD == 64) { if (deep) RB_FD(64, 4, false) else RB_FD(64, 2, false) }
 #undef RB_FD
   return -2;
+}
+
+extern "C" int rmlx_flash_decode_paged(const void* q, const void* k_cache, const void* v_cache,
+                                       const int* block_table, const int* seq_lens, void* out,
+                                       float* part_o, float* part_ml, unsigned int* tickets, int B,
+                                       int Hq, int Hkv, int HD, int max_blocks, int splits,
+                                       int window, float scale, int pdl, cudaStream_t st) {
+  return fd_launch(q, k_cache, v_cache, nullptr, nullptr, block_table, seq_lens, out, part_o, part_ml,
+                   tickets, B, Hq, Hkv, HD, max_blocks, splits, window, scale, pdl, st);
+}
+
+// The same attention over an 8-bit cache: k_q / v_q uint8 [blocks, Hkv, 16, HD], k_sb / v_sb bf16
+// [blocks, Hkv, 16, HD/64, 2] (scale, bias), as written by rmlx_rope_kv_write_q8 (kv_q8.cu).
+extern "C" int rmlx_flash_decode_paged_q8(const void* q, const void* k_q, const void* k_sb,
+                                          const void* v_q, const void* v_sb, const int* block_table,
+                                          const int* seq_lens, void* out, float* part_o,
+                                          float* part_ml, unsigned int* tickets, int B, int Hq,
+                                          int Hkv, int HD, int max_blocks, int splits, int window,
+                                          float scale, int pdl, cudaStream_t st) {
+  if (!k_sb || !v_sb) return -2;
+  return fd_launch(q, k_q, v_q, k_sb, v_sb, block_table, seq_lens, out, part_o, part_ml, tickets, B,
+                   Hq, Hkv, HD, max_blocks, splits, window, scale, pdl, st);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -171,19 +171,68 @@ def make_block_manager(num_blocks: int, block_size: int = PAGE, reserved: int = 
     return BlockManager(num_blocks, block_size, reserved)
 
 
+def quantize_kv_rows(x: torch.Tensor):
+    """x [..., D] (D a multiple of 64) -> (codes uint8 [..., D], sb bf16 [..., D/64, 2]): 8-bit affine
+    per group of 64. The bias is the group minimum rounded DOWN to bf16 and the scale is
+    (max - stored bias) / 255 rounded UP to bf16, so neither end of the range clips; the codes are
+    computed against the stored pair, as the device kernel does (csrc/kernels/kv_q8.cu)."""
+    d = x.shape[-1]
+    g = x.float().reshape(*x.shape[:-1], d // 64, 64)
+    mn, mx = g.amin(-1), g.amax(-1)
+    bits = mn.contiguous().view(torch.int32)
+    # towards minus infinity: truncate a positive value's low bits, grow a negative one's magnitude
+    down = torch.where(mn >= 0, bits & ~0xFFFF, (bits + 0xFFFF) & ~0xFFFF).view(torch.float32)
+    bias = down.to(torch.bfloat16)
+    span = (mx - bias.float()).clamp_min(0.0) / 255.0
+    span = torch.where(span > 0, span, torch.ones_like(span))
+    up = ((span.contiguous().view(torch.int32) + 0xFFFF) & ~0xFFFF).view(torch.float32)   # next bf16 at or above
+    scale = up.to(torch.bfloat16)
+    q = torch.round((g - bias.float()[..., None]) * (1.0 / scale.float()[..., None])).clamp_(0, 255)
+    return q.to(torch.uint8).reshape(x.shape), torch.stack([scale, bias], -1)
+
+
+def dequantize_kv_rows(q: torch.Tensor, sb: torch.Tensor) -> torch.Tensor:
+    """Inverse of ``quantize_kv_rows``: fp32 [..., D]."""
+    d = q.shape[-1]
+    g = q.float().reshape(*q.shape[:-1], d // 64, 64)
+    return (g * sb[..., 0].float()[..., None] + sb[..., 1].float()[..., None]).reshape(q.shape)
+
+
 class PagedKvCache:
-    """Device K/V pools for every layer plus the manager and a device mirror of block tables."""
+    """Device K/V pools for every layer plus the manager and a device mirror of block tables.
+
+    ``kv_quant="q8"`` keeps the pools in the 8-bit affine format (codes uint8
+    ``[blocks, Hkv, page, D]`` in ``k`` / ``v`` plus ``k_sb`` / ``v_sb`` bf16
+    ``[blocks, Hkv, page, D/64, 2]`` of (scale, bias) per token and group of 64): half the bytes
+    per token. The device kernels quantise on append and expand inside attention
+    (csrc/kernels/kv_q8.cu, flash_decode.cu); the counterpart of the reference's host-side
+    QuantizedKvCache (crates/rmlx-nn/src/attention.rs:4438-4680)."""
 
     def __init__(self, num_blocks: int, num_layers: int, kv_heads: int, head_dim: int,
                  dtype=torch.bfloat16, device="cpu", max_seqs: int = 64,
-                 max_blocks_per_seq: int = 512, block_size: int = PAGE):
+                 max_blocks_per_seq: int = 512, block_size: int = PAGE,
+                 kv_quant: Optional[str] = None):
         self.manager = make_block_manager(num_blocks, block_size, reserved=1)
         self.num_layers, self.kv_heads, self.head_dim = num_layers, kv_heads, head_dim
         self.block_size = block_size
-        self.k = [torch.zeros(num_blocks, kv_heads, block_size, head_dim, dtype=dtype, device=device)
-                  for _ in range(num_layers)]
-        self.v = [torch.zeros(num_blocks, kv_heads, block_size, head_dim, dtype=dtype, device=device)
-                  for _ in range(num_layers)]
+        if kv_quant not in (None, "q8"):
+            raise ValueError(f"unsupported KV quantisation {kv_quant}")
+        self.quantized = kv_quant == "q8"
+        self.dtype = dtype
+        if self.quantized:
+            if head_dim % 64:
+                raise ValueError("the 8-bit cache needs head_dim to be a multiple of 64")
+            shape, sbs = (num_blocks, kv_heads, block_size, head_dim), (num_blocks, kv_heads, block_size, head_dim // 64, 2)
+            self.k = [torch.zeros(shape, dtype=torch.uint8, device=device) for _ in range(num_layers)]
+            self.v = [torch.zeros(shape, dtype=torch.uint8, device=device) for _ in range(num_layers)]
+            self.k_sb = [torch.zeros(sbs, dtype=torch.bfloat16, device=device) for _ in range(num_layers)]
+            self.v_sb = [torch.zeros(sbs, dtype=torch.bfloat16, device=device) for _ in range(num_layers)]
+        else:
+            self.k = [torch.zeros(num_blocks, kv_heads, block_size, head_dim, dtype=dtype, device=device)
+                      for _ in range(num_layers)]
+            self.v = [torch.zeros(num_blocks, kv_heads, block_size, head_dim, dtype=dtype, device=device)
+                      for _ in range(num_layers)]
+            self.k_sb = self.v_sb = None
         self.device = torch.device(device)
         self.max_blocks_per_seq = max_blocks_per_seq
         # row r of the device table belongs to the sequence bound to slot r
@@ -255,6 +304,9 @@ class PagedKvCache:
             for l in range(self.num_layers):
                 self.k[l][dst].copy_(self.k[l][src])
                 self.v[l][dst].copy_(self.v[l][src])
+                if self.quantized:
+                    self.k_sb[l][dst].copy_(self.k_sb[l][src])
+                    self.v_sb[l][dst].copy_(self.v_sb[l][src])
         if copies or len(self.manager.block_table(seq_id)) != before:
             self._sync_slot(seq_id)
 
@@ -273,15 +325,39 @@ class PagedKvCache:
         bs = self.block_size
         pos = torch.arange(start, start + k.shape[0], device=self.device)
         blk, off = table[pos // bs], pos % bs
+        if self.quantized:
+            kq, ksb = quantize_kv_rows(k)
+            vq, vsb = quantize_kv_rows(v)
+            self.k[layer][blk, :, off], self.k_sb[layer][blk, :, off] = kq, ksb
+            self.v[layer][blk, :, off], self.v_sb[layer][blk, :, off] = vq, vsb
+            return
         self.k[layer][blk, :, off] = k.to(self.k[layer].dtype)
         self.v[layer][blk, :, off] = v.to(self.v[layer].dtype)
 
-    def get_keys(self, layer: int, seq_id: int, length: Optional[int] = None) -> torch.Tensor:
+    def _gather(self, pool, sb, seq_id: int, length: Optional[int]) -> torch.Tensor:
         length = self.manager.seq_len(seq_id) if length is None else length
         row = torch.tensor(self.manager.block_table(seq_id), dtype=torch.int64, device=self.device)
-        return ref.gather_paged(self.k[layer], row, length)
+        if not self.quantized:
+            return ref.gather_paged(pool, row, length)
+        nblk = (length + self.block_size - 1) // self.block_size
+        idx = row[:nblk]
+        full = dequantize_kv_rows(pool[idx], sb[idx]).to(self.dtype)      # [nblk, Hkv, page, D]
+        return full.permute(0, 2, 1, 3).reshape(nblk * self.block_size, self.kv_heads, self.head_dim)[:length]
+
+    def get_keys(self, layer: int, seq_id: int, length: Optional[int] = None) -> torch.Tensor:
+        return self._gather(self.k[layer], None if self.k_sb is None else self.k_sb[layer], seq_id, length)
 
     def get_values(self, layer: int, seq_id: int, length: Optional[int] = None) -> torch.Tensor:
-        length = self.manager.seq_len(seq_id) if length is None else length
-        row = torch.tensor(self.manager.block_table(seq_id), dtype=torch.int64, device=self.device)
-        return ref.gather_paged(self.v[layer], row, length)
+        return self._gather(self.v[layer], None if self.v_sb is None else self.v_sb[layer], seq_id, length)
+
+    def sb(self, layer: int) -> dict:
+        """Keyword arguments that tell the kernels about the 8-bit format (empty for bf16)."""
+        if not self.quantized:
+            return {}
+        return {"k_sb": self.k_sb[layer], "v_sb": self.v_sb[layer]}
+
+    def bytes_per_token(self) -> int:
+        """Cache bytes one token occupies over all layers (K and V)."""
+        per = self.head_dim + (self.head_dim // 64) * 4 if self.quantized else \
+            self.head_dim * torch.empty(0, dtype=self.dtype).element_size()
+        return 2 * self.num_layers * self.kv_heads * per

@@ -47,7 +47,7 @@ class CachedDecode:
         self.use_graph = use_graph
         self.greedy = greedy
         # RoPE and the KV append run in the QKV projection's epilogue unless switched off
-        self.fuse_rope = os.environ.get("RMLX_FUSE_ROPE", "1") != "0"
+        self.fuse_rope = os.environ.get("RMLX_FUSE_ROPE", "1") != "0" and not cache.quantized
         dev = model.device
         B, D_ = max_batch, cfg.hidden_size
         hq, hkv, hd = model.hq, model.hkv, cfg.head_dim
@@ -95,7 +95,8 @@ class CachedDecode:
         # batch 1 on one GPU: the whole step is one persistent kernel when the model fits it
         self.step_kernel = None
         from .step_kernel import DecodeStepKernel
-        if step_kernel is not False and DecodeStepKernel.supported(model, max_batch, comm, force=bool(step_kernel)):
+        if step_kernel is not False and not cache.quantized and \
+                DecodeStepKernel.supported(model, max_batch, comm, force=bool(step_kernel)):
             sk = DecodeStepKernel(self)
             if sk.ok:
                 self.step_kernel = sk
@@ -168,10 +169,10 @@ class CachedDecode:
                 D.rms_gemv(h, lw.wqkv, lw.norm1, eps, out=self.qkv[:nb], pdl=pdl)
                 D.rope_kv_write(self.qkv[:nb], q, self.cache.k[li], self.cache.v[li], block_table,
                                 positions, m.cos, m.sin, m.hq, m.hkv,
-                                traditional=cfg.rope_traditional, pdl=pdl)
+                                traditional=cfg.rope_traditional, pdl=pdl, **self.cache.sb(li))
             D.flash_decode_paged(q, self.cache.k[li], self.cache.v[li], block_table,
                                  seq_lens, m.scale, splits, fd_scratch,
-                                 cfg.sliding_window, out=attn, pdl=pdl)
+                                 cfg.sliding_window, out=attn, pdl=pdl, **self.cache.sb(li))
             a2 = attn.view(nb, -1)
             if tp:
                 self.comm.gemv_allreduce(a2, lw.wo, residual=h, out=h2, pdl=pdl)

@@ -157,9 +157,18 @@ class NativePrefill:
         seq = torch.zeros(t, dtype=torch.int32, device=m.device)
         q = torch.empty(t, hq, hd, dtype=torch.bfloat16, device=m.device)
 
+        npages = (pos0 + t + cache.block_size - 1) // cache.block_size
+        ident = torch.arange(npages, dtype=torch.int32, device=m.device) if cache.quantized else None
+
         def attend(li, qkv):
             D.rope_kv_write(qkv, q, cache.k[li], cache.v[li], row.view(1, -1), pos, m.cos, m.sin,
-                            hq, hkv, token_seq=seq, traditional=cfg.rope_traditional)
+                            hq, hkv, token_seq=seq, traditional=cfg.rope_traditional, **cache.sb(li))
+            if cache.quantized:
+                # prompt attention over an 8-bit cache: the sequence's pages are expanded once per
+                # layer into contiguous bf16 pages (amortised over the chunk's tokens)
+                kk = D.kv_dequant_pages(cache.k[li], cache.k_sb[li], row, npages)
+                vv = D.kv_dequant_pages(cache.v[li], cache.v_sb[li], row, npages)
+                return flash_prefill_paged(q, kk, vv, ident, pos0, m.scale, cfg.sliding_window or 0)
             return flash_prefill_paged(q, cache.k[li], cache.v[li], row, pos0, m.scale,
                                        cfg.sliding_window or 0)
 
@@ -246,9 +255,10 @@ class BatchedDecode:
 
         def attend(li, qkv):
             D.rope_kv_write(qkv, q, cache.k[li], cache.v[li], table, positions, m.cos,
-                            m.sin, m.hq, m.hkv, token_seq=rows, traditional=cfg.rope_traditional)
+                            m.sin, m.hq, m.hkv, token_seq=rows, traditional=cfg.rope_traditional,
+                            **cache.sb(li))
             return D.flash_decode_paged(q, cache.k[li], cache.v[li], table, seq_lens,
-                                        m.scale, splits, fd, cfg.sliding_window or 0)
+                                        m.scale, splits, fd, cfg.sliding_window or 0, **cache.sb(li))
 
         h = self.layers.run(D.embedding(m.w.embed, tokens), attend)
         self._logits[nb] = self.layers.logits(h)

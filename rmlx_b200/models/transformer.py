@@ -50,12 +50,13 @@ class TransformerModel:
 
     # ------------------------------------------------------------------ helpers
     def new_cache(self, num_blocks: int, max_seqs: int = 64, max_blocks_per_seq: Optional[int] = None,
-                  dtype=None) -> PagedKvCache:
+                  dtype=None, kv_quant: Optional[str] = None) -> PagedKvCache:
+        """``kv_quant="q8"``: the cache is kept in the 8-bit affine format (half the bytes)."""
         cfg = self.cfg
         mb = max_blocks_per_seq or (cfg.max_seq_len + 15) // 16
         return PagedKvCache(num_blocks, cfg.num_layers, self.hkv, cfg.head_dim,
                             dtype=dtype or self.w.embed.dtype, device=self.device,
-                            max_seqs=max_seqs, max_blocks_per_seq=mb)
+                            max_seqs=max_seqs, max_blocks_per_seq=mb, kv_quant=kv_quant)
 
     def _deq(self, lw, name: str, dtype):
         """Dense [.., N, K] view of a (possibly quantised) weight in the compute dtype, cached."""

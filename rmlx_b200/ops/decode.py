@@ -348,9 +348,13 @@ def flash_decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
                        block_table: torch.Tensor, seq_lens: torch.Tensor,
                        scale: Optional[float] = None, splits: Optional[int] = None,
                        scratch: Optional[FlashDecodeScratch] = None, window: int = 0,
-                       out: Optional[torch.Tensor] = None, pdl: bool = False) -> torch.Tensor:
+                       out: Optional[torch.Tensor] = None, pdl: bool = False,
+                       k_sb: Optional[torch.Tensor] = None,
+                       v_sb: Optional[torch.Tensor] = None) -> torch.Tensor:
     """q [B, Hq, D] bf16; caches [blocks, Hkv, 16, D] bf16; block_table int32 [B, max_blocks];
-    seq_lens int32 [B] (context length including the current token)."""
+    seq_lens int32 [B] (context length including the current token). With ``k_sb`` / ``v_sb``
+    (bf16 [blocks, Hkv, 16, D/64, 2]) the caches are the uint8 codes of the 8-bit format and the
+    kernel expands pages in shared memory."""
     _lib.require_cuda_tensor(q, k_cache, v_cache, block_table, seq_lens)
     b, hq, d = q.shape
     hkv, page = k_cache.shape[1], k_cache.shape[2]
@@ -366,6 +370,17 @@ def flash_decode_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Te
         scratch = FlashDecodeScratch(b, hq, hkv, d, splits, q.device)
     if out is None:
         out = torch.empty_like(q)
+    if k_sb is not None:
+        assert k_cache.dtype == torch.uint8 and v_sb is not None and k_sb.dtype == torch.bfloat16
+        rc = lib.rmlx_flash_decode_paged_q8(
+            q.data_ptr(), k_cache.data_ptr(), k_sb.data_ptr(), v_cache.data_ptr(), v_sb.data_ptr(),
+            block_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(),
+            None if scratch is None else scratch.part_o.data_ptr(),
+            None if scratch is None else scratch.part_ml.data_ptr(),
+            None if scratch is None else scratch.tickets.data_ptr(),
+            b, hq, hkv, d, block_table.stride(0), splits, window, scale, int(pdl), _lib.stream_ptr())
+        _lib.check(rc, "flash_decode_paged_q8")
+        return out
     if scratch is not None and scratch.clusters > 0 and (splits is None or splits == scratch.splits):
         nc = scratch.clusters & 0xff
         rc = lib.rmlx_flash_decode_cluster(
@@ -393,13 +408,25 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
                   v_cache: torch.Tensor, block_table: torch.Tensor, positions: torch.Tensor,
                   cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int,
                   token_seq: Optional[torch.Tensor] = None, traditional: bool = False,
-                  pdl: bool = False) -> torch.Tensor:
-    """RoPE(Q) -> q_out, RoPE(K) and V -> their page slots. qkv [T, (Hq+2Hkv)*D] bf16."""
+                  pdl: bool = False, k_sb: Optional[torch.Tensor] = None,
+                  v_sb: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """RoPE(Q) -> q_out, RoPE(K) and V -> their page slots. qkv [T, (Hq+2Hkv)*D] bf16. With
+    ``k_sb`` / ``v_sb`` the caches are in the 8-bit format: K and V are quantised as they are
+    written."""
     _lib.require_cuda_tensor(qkv, q_out, k_cache, v_cache, block_table, positions, cos, sin)
     t = qkv.shape[0]
     d = k_cache.shape[3]
     assert qkv.is_contiguous() and qkv.shape[1] == (hq + 2 * hkv) * d
     assert positions.dtype == torch.int32 and cos.dtype == torch.float32
+    if k_sb is not None:
+        assert k_cache.dtype == torch.uint8 and v_sb is not None
+        rc = _lib.cuda().rmlx_rope_kv_write_q8(
+            qkv.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), k_sb.data_ptr(), v_cache.data_ptr(),
+            v_sb.data_ptr(), block_table.data_ptr(), positions.data_ptr(), _lib.ptr(token_seq),
+            cos.data_ptr(), sin.data_ptr(), t, hq, hkv, d, block_table.stride(0), k_cache.shape[2],
+            int(traditional), int(pdl), _lib.stream_ptr())
+        _lib.check(rc, "rope_kv_write_q8")
+        return q_out
     rc = _lib.cuda().rmlx_rope_kv_write(
         qkv.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
         block_table.data_ptr(), positions.data_ptr(), _lib.ptr(token_seq), cos.data_ptr(),
@@ -411,7 +438,25 @@ def rope_kv_write(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor,
 
 _lib.register_cuda_sigs({
     "rmlx_rms_qkv_rope": ("ippppipfppppppppiiiiiiiiip", "i"),
+    "rmlx_flash_decode_paged_q8": ("pppppppppppiiiiiiifip", "i"),
+    "rmlx_rope_kv_write_q8": ("pppppppppppiiiiiiiip", "i"),
+    "rmlx_kv_dequant_pages": ("ppppiiiip", "i"),
 })
+
+
+def kv_dequant_pages(codes: torch.Tensor, sb: torch.Tensor, table_row: torch.Tensor, n_pages: int,
+                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Expand the first ``n_pages`` pages of one sequence (``table_row`` int32) of an 8-bit cache
+    into contiguous bf16 pages [n_pages, Hkv, page, D] (page i of the result is page
+    ``table_row[i]`` of the cache)."""
+    _lib.require_cuda_tensor(codes, sb, table_row)
+    _, hkv, page, d = codes.shape
+    if out is None:
+        out = torch.empty(n_pages, hkv, page, d, dtype=torch.bfloat16, device=codes.device)
+    rc = _lib.cuda().rmlx_kv_dequant_pages(codes.data_ptr(), sb.data_ptr(), table_row.data_ptr(),
+                                           out.data_ptr(), n_pages, hkv, page, d, _lib.stream_ptr())
+    _lib.check(rc, "kv_dequant_pages")
+    return out
 
 
 def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor], eps: float,

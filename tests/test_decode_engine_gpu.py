@@ -280,3 +280,42 @@ def test_moe_overlap_schedules_on_two_streams(dev):
         assert (got - want).abs().max() <= 2e-2 * want.abs().max()
         sm = layer._pipeline._streams
         assert sm.waits_inserted >= 2            # x -> side stream, side stream -> sum
+
+
+@pytest.mark.parametrize("use_graph", [False, True])
+def test_decode_with_8bit_kv_cache(dev, use_graph):
+    """The decode engine over an 8-bit cache (quantising append + in-kernel page expansion) against
+    the fp32 forward over a cache quantised the same way; prompt through the native prefill."""
+    cfg = tiny_moe_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant=None))
+    oracle = _oracle_from(model)
+    prompt = torch.randint(0, cfg.vocab_size, (40,), generator=torch.Generator().manual_seed(6))
+    steps = 6
+    oc = oracle.new_cache(8, max_seqs=1, kv_quant="q8")
+    oc.add_sequence(0)
+    lg = oracle.forward(prompt, oc, [0], last_only=True)
+    want_logits, toks = [], []
+    tok = int(lg[0].argmax())
+    for _ in range(steps):
+        toks.append(tok)
+        lg = oracle.forward(torch.tensor([tok]), oc, [0], last_only=True)
+        want_logits.append(lg[0].clone())
+        tok = int(lg[0].argmax())
+    cache = model.new_cache(8, max_seqs=2, kv_quant="q8")
+    assert cache.quantized and cache.k[0].dtype == torch.uint8
+    cache.add_sequence(0)
+    model.prefill(prompt.to(dev), cache, 0)
+    # what the prompt path wrote decodes to what the oracle cached
+    assert (cache.get_keys(1, 0).float().cpu() - oc.get_keys(1, 0).float()).abs().max() < 0.25
+    eng = CachedDecode(model, cache, max_batch=2, use_graph=use_graph)
+    assert not eng.fuse_rope and eng.step_kernel is None
+    eng.bind([0], [toks[0]])
+    eng.reserve(steps + 1)
+    for i in range(steps):
+        eng.step()
+        torch.cuda.synchronize()
+        got = eng.logits[0].float().cpu()
+        rel = (got - want_logits[i]).abs().max().item() / want_logits[i].abs().max().item()
+        assert rel < 6e-2, (i, rel)
+        if i + 1 < steps:
+            eng.set_next_tokens([toks[i + 1]])

@@ -259,6 +259,72 @@ def test_rope_kv_write(dev, traditional):
     _close(back, q, atol=2e-2)
 
 
+@pytest.mark.parametrize("traditional", [False, True])
+@pytest.mark.parametrize("hd", [64, 128])
+def test_q8_kv_write_and_attention(dev, hd, traditional, q4_path):
+    """8-bit cache: the append kernel's codes and (scale, bias) pairs against the host quantiser
+    applied to the rotated rows, the page expansion kernel, and attention over the 8-bit pages
+    against fp32 attention over the dequantised cache."""
+    if q4_path != "stream":
+        pytest.skip("one run is enough: the kernels do not depend on the mat-vec path")
+    from rmlx_b200.kv.paged import dequantize_kv_rows, quantize_kv_rows
+    torch.manual_seed(21)
+    hq, hkv, t = 8, 2, 6
+    cos, sin = ref.rope_tables(hd, 512, 1e6, device=dev)
+    qkv = (torch.randn(t, (hq + 2 * hkv) * hd, device=dev) * 2).to(torch.bfloat16)
+    pos = torch.tensor([0, 17, 31, 32, 200, 201], dtype=torch.int32, device=dev)
+    nblk = 100
+    kq = torch.zeros(nblk, hkv, 16, hd, dtype=torch.uint8, device=dev)
+    vq = torch.zeros_like(kq)
+    ksb = torch.zeros(nblk, hkv, 16, hd // 64, 2, dtype=torch.bfloat16, device=dev)
+    vsb = torch.zeros_like(ksb)
+    bt = (torch.randperm(nblk - 1, device=dev)[:t * 16].view(t, 16) + 1).to(torch.int32)   # disjoint pages
+    qo = torch.empty(t, hq, hd, dtype=torch.bfloat16, device=dev)
+    D.rope_kv_write(qkv, qo, kq, vq, bt, pos, cos, sin, hq, hkv, traditional=traditional, k_sb=ksb, v_sb=vsb)
+    q = qkv[:, :hq * hd].view(t, hq, hd)
+    k = qkv[:, hq * hd:(hq + hkv) * hd].view(t, hkv, hd)
+    v = qkv[:, (hq + hkv) * hd:].view(t, hkv, hd)
+    _close(qo, ref.apply_rope(q.float(), pos.long(), cos, sin, traditional), atol=1e-2)
+    kr = ref.apply_rope(k.float(), pos.long(), cos, sin, traditional)
+    for i in range(t):
+        p = int(pos[i])
+        blk = int(bt[i, p // 16])
+        for want, codes, sb in ((kr[i], kq, ksb), (v[i].float(), vq, vsb)):
+            wq, wsb = quantize_kv_rows(want)
+            got_sb = sb[blk, :, p % 16]
+            # the rotation's fp32 rounding can move a minimum or maximum by an ulp of bf16
+            assert (got_sb.float() - wsb.float()).abs().max() <= 2e-2 * wsb.float().abs().max()
+            back = dequantize_kv_rows(codes[blk, :, p % 16], got_sb)
+            step = got_sb[..., 0].float().repeat_interleave(64, -1).reshape(want.shape)
+            assert ((back - want).abs() <= 0.55 * step + 1e-3).all()
+            assert (codes[blk, :, p % 16].int() - wq.int()).abs().max() <= 2
+    # page expansion
+    row = bt[1].contiguous()
+    pages = D.kv_dequant_pages(kq, ksb, row, 3)
+    want_pages = dequantize_kv_rows(kq[row[:3].long()], ksb[row[:3].long()])
+    _close(pages, want_pages, atol=1e-2)
+
+    # attention over 8-bit pages (several lengths, splits, a window)
+    lens = [1, 37, 300, 1024]
+    b = len(lens)
+    kc, vc, bt2 = _paged_setup(dev, b, hkv, hd, lens, seed=5)
+    kq2, ksb2 = quantize_kv_rows(kc.float())
+    vq2, vsb2 = quantize_kv_rows(vc.float())
+    kd, vd = dequantize_kv_rows(kq2, ksb2), dequantize_kv_rows(vq2, vsb2)
+    qq = torch.randn(b, hq, hd, device=dev).to(torch.bfloat16)
+    sl = torch.tensor(lens, dtype=torch.int32, device=dev)
+    scale = 1 / math.sqrt(hd)
+    for splits in (1, 4):
+        for window in (0, 100):
+            got = D.flash_decode_paged(qq, kq2, vq2, bt2, sl, scale, splits=splits, window=window,
+                                       k_sb=ksb2, v_sb=vsb2)
+            for i, l in enumerate(lens):
+                kk = ref.gather_paged(kd, bt2[i].long(), l)
+                vv = ref.gather_paged(vd, bt2[i].long(), l)
+                want = ref.sdpa(qq[i:i + 1].float(), kk, vv, scale, l - 1, window)
+                _close(got[i:i + 1], want, atol=3e-2)
+
+
 def test_small_kernels(dev):
     torch.manual_seed(12)
     table = torch.randn(1000, 256, device=dev).to(torch.bfloat16)

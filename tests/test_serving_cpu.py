@@ -1,5 +1,6 @@
 """Scheduler, sampler, prefix cache and the serving loop on CPU (the logic tests of
 crates/rmlx-nn/src/scheduler.rs, sampler.rs:543-640 and prefix_cache.rs)."""
+import pytest
 import torch
 
 from rmlx_b200.config import SamplerConfig, SchedulerConfig, tiny_dense_config
@@ -243,3 +244,42 @@ def test_sampler_batch_matches_per_row():
     # the same seed gives the same draws
     a, b = Sampler(SamplerConfig(temperature=1.0, seed=11)), Sampler(SamplerConfig(temperature=1.0, seed=11))
     assert [a.sample_batch(logits) for _ in range(3)] == [b.sample_batch(logits) for _ in range(3)]
+
+
+def test_q8_kv_cache_on_the_host_path():
+    """The 8-bit paged cache through the host-driven append / gather: error within half a code
+    step per group, copy-on-write carries the scales, and a tiny model generates the same tokens
+    as with the bf16 cache."""
+    from rmlx_b200.kv.paged import PagedKvCache, dequantize_kv_rows, quantize_kv_rows
+    torch.manual_seed(0)
+    x = torch.randn(5, 2, 128) * 3
+    q, sb = quantize_kv_rows(x)
+    assert q.dtype == torch.uint8 and sb.shape == (5, 2, 2, 2)
+    back = dequantize_kv_rows(q, sb)
+    step = sb[..., 0].float().repeat_interleave(64, -1).reshape(x.shape)
+    assert ((back - x).abs() <= 0.51 * step + 1e-6).all()
+
+    c = PagedKvCache(8, 1, 2, 128, dtype=torch.float32, max_seqs=4, max_blocks_per_seq=4, kv_quant="q8")
+    assert c.quantized and c.bytes_per_token() == 2 * 2 * (128 + 8)
+    c.add_sequence(0)
+    c.reserve(0, 20)
+    k, v = torch.randn(20, 2, 128), torch.randn(20, 2, 128)
+    c.append(0, 0, k, v, 0)
+    c.commit(0, 20)
+    assert (c.get_keys(0, 0) - k).abs().max() < 0.03 and (c.get_values(0, 0) - v).abs().max() < 0.03
+    c.fork(0, 1)
+    c.reserve(1, 1)                            # shared partial last block: copied with its scales
+    assert c.manager.block_table(1)[-1] != c.manager.block_table(0)[-1]
+    assert torch.equal(c.get_keys(0, 1, 20), c.get_keys(0, 0, 20))
+    with pytest.raises(ValueError):
+        PagedKvCache(4, 1, 2, 96, kv_quant="q8")
+
+    from rmlx_b200.config import tiny_dense_config
+    from rmlx_b200.models.transformer import TransformerModel
+    from rmlx_b200.models.weights import from_state_dict, random_state_dict
+    cfg = tiny_dense_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    prompt = torch.randint(0, cfg.vocab_size, (12,), generator=torch.Generator().manual_seed(2))
+    plain = model.generate_greedy(prompt, 6)
+    cq = model.new_cache(4, max_seqs=1, kv_quant="q8")
+    assert model.generate_greedy(prompt, 6, cache=cq) == plain
