@@ -20,8 +20,10 @@ namespace rb {
 constexpr int kNvlsMaxWorld = 8;
 constexpr int kNvlsMaxBlocks = 64;
 // flag area (u32 words): [0, 64) input-ready counters, [64, 128) done counters, 128 call number,
-// 129 exit ticket
-constexpr int kNvlsFlagWords = 2 * kNvlsMaxBlocks + 2;
+// 129 exit ticket, 130 grid size of the first call. Block b counts on word b, so every call on one
+// flag area must use the same number of blocks (a block index that sat out a call would fall
+// behind the call number); the kernel checks it and refuses a different grid.
+constexpr int kNvlsFlagWords = 2 * kNvlsMaxBlocks + 3;
 
 __device__ int g_nvls_status = 0;
 
@@ -53,6 +55,11 @@ template <bool BF16>
 __global__ void __launch_bounds__(512)
 nvls_allreduce_kernel(char* mc, long long nvec, NvlsPeers P) {
   uint32_t* mine = P.flags[P.rank];
+  const uint32_t g0 = atomicCAS(mine + 2 * kNvlsMaxBlocks + 2, 0u, gridDim.x);
+  if (g0 != 0u && g0 != gridDim.x) {         // uniform over the grid: every block sees the same word
+    if (threadIdx.x == 0) atomicExch(&g_nvls_status, kStatusBadArgument);
+    return;
+  }
   const uint32_t call = *reinterpret_cast<volatile uint32_t*>(mine + 2 * kNvlsMaxBlocks) + 1u;
   const int b = blockIdx.x;
   // this rank's input is complete (it was written by earlier work on this stream)
@@ -105,7 +112,8 @@ extern "C" int rmlx_nvls_status() {
 }
 
 // mc: multicast address of the operand; bytes: multiple of 16; flags: host array of `world` device
-// pointers to the ranks' flag areas (zero-initialised, rmlx_nvls_flag_bytes() each).
+// pointers to the ranks' flag areas (zero-initialised, rmlx_nvls_flag_bytes() each); blocks: grid
+// size, the same on every call that uses these flag areas (1..64).
 extern "C" int rmlx_nvls_allreduce(void* mc, long long bytes, int bf16, void* const* flags, int rank,
                                    int world, int blocks, cudaStream_t st) {
   if (!mc || bytes < 16 || bytes % 16 || (reinterpret_cast<uintptr_t>(mc) & 15u) || world < 1 ||
@@ -115,12 +123,7 @@ extern "C" int rmlx_nvls_allreduce(void* mc, long long bytes, int bf16, void* co
   for (int i = 0; i < kNvlsMaxWorld; ++i) P.flags[i] = i < world ? static_cast<uint32_t*>(flags[i]) : nullptr;
   P.rank = rank; P.world = world;
   const long long nvec = bytes / 16;
-  if (blocks < 1) {
-    const long long per_rank = (nvec + world - 1) / world;
-    blocks = int((per_rank + 2047) / 2048);        // four vectors per thread
-  }
-  if (blocks < 1) blocks = 1;
-  if (blocks > kNvlsMaxBlocks) blocks = kNvlsMaxBlocks;
+  if (blocks < 1 || blocks > kNvlsMaxBlocks) return -2;
   if (bf16) nvls_allreduce_kernel<true><<<blocks, 512, 0, st>>>(static_cast<char*>(mc), nvec, P);
   else nvls_allreduce_kernel<false><<<blocks, 512, 0, st>>>(static_cast<char*>(mc), nvec, P);
   return static_cast<int>(cudaGetLastError());

@@ -306,7 +306,7 @@ def test_decode_with_8bit_kv_cache(dev, use_graph):
     cache.add_sequence(0)
     model.prefill(prompt.to(dev), cache, 0)
     # what the prompt path wrote decodes to what the oracle cached
-    assert (cache.get_keys(1, 0).float().cpu() - oc.get_keys(1, 0).float()).abs().max() < 0.25
+    assert (cache.get_keys(1, 0).float().cpu() - oc.get_keys(1, 0, 40).float()).abs().max() < 0.25
     eng = CachedDecode(model, cache, max_batch=2, use_graph=use_graph)
     assert not eng.fuse_rope and eng.step_kernel is None
     eng.bind([0], [toks[0]])
