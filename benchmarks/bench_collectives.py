@@ -5,6 +5,10 @@ form is in bench.py's fused path), all-gather, reduce-scatter and all-to-all, 8 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port 29513 benchmarks/bench_collectives.py [--sizes 8192,...] [--iters 20]
 
+With RMLX_SYMM_MULTICAST=1 (symmetric heap bound to NVLink multicast objects) two more rows per
+size time the in-switch all-reduce (multimem.ld_reduce + multimem.st): staged from an ordinary
+tensor, and in place on the heap buffer.
+
 CUDA-event time per call, max over ranks, after warm-up. Bus bandwidth uses the usual factors
 (all-reduce 2(N-1)/N, the others (N-1)/N of the full buffer). The counterpart of the reference's
 rdma_allreduce_bench / distributed_bench (crates/rmlx-distributed/benches).
@@ -63,6 +67,12 @@ def main():
             ("all_gather", lambda: pc.all_gather(piece, out), lambda: dist.all_gather_into_tensor(out, piece), (world - 1) / world),
             ("all_to_all", lambda: pc.all_to_all(x, out), lambda: dist.all_to_all_single(out, x), (world - 1) / world),
         ]
+        if pc.nvls_available and nbytes <= pc.nvls_cap:
+            pc.nvls_buffer(torch.bfloat16, n).copy_(x)
+            ops += [
+                ("all_reduce nvls", lambda: pc.all_reduce_nvls(x, out=out), lambda: dist.all_reduce(out), 2.0 * (world - 1) / world),
+                ("  in place", lambda: pc.all_reduce_nvls(numel=n, dtype=torch.bfloat16), lambda: dist.all_reduce(out), 2.0 * (world - 1) / world),
+            ]
         for name, ours, lib, factor in ops:
             to, tl = timed(ours, a.iters), timed(lib, a.iters)
             rows.append((name, nbytes, to, tl, nbytes * factor / to / 1e3))
@@ -74,6 +84,8 @@ def main():
             print(f"{name:16s} {nb:10d} {to:9.1f} {tl:9.1f} {tl / to:10.2f} {bw:16.1f}")
     dist.barrier()
     pc.close()
+    from rmlx_b200.parallel.symm_heap import close_heaps
+    close_heaps()
     dist.destroy_process_group()
 
 

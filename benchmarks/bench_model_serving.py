@@ -72,6 +72,9 @@ def main():
     ap.add_argument("--batches", default="1,8,64")
     ap.add_argument("--steps", type=int, default=16)
     ap.add_argument("--tp-gemm", default="fused", choices=["fused", "nccl"])
+    ap.add_argument("--matvec-max-batch", type=int, default=8,
+                    help="largest batch that runs on the mat-vec engine (rows beyond four are chunked)")
+    ap.add_argument("--kv-quant", default=None, choices=[None, "q8"])
     a = ap.parse_args()
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
@@ -94,7 +97,10 @@ def main():
             dist.all_gather(parts, t.contiguous())
             return torch.cat(parts, -1)
 
-        model = TransformerModel(random_on_device(cfg, dev, quant, ParallelLayout(RANK, WORLD), seed=0),
+        # whole experts per rank (the grouped tensor-core GEMM then keeps its full inner dimension);
+        # attention, the dense projections and the vocabulary are sliced
+        model = TransformerModel(random_on_device(cfg, dev, quant,
+                                                  ParallelLayout(RANK, WORLD, expert_parallel=True), seed=0),
                                  allreduce, allgather)
         from rmlx_b200.parallel.comm import make_comm
         from rmlx_b200.parallel.tp_gemm import make_gemm_comm
@@ -103,7 +109,7 @@ def main():
         i_local = max([l.w_gate_up.n // 2 for l in model.w.layers if l.w_gate_up is not None] + [0])
         model.gemm_comm = make_gemm_comm(a.tp_gemm, rows, cfg.hidden_size, max(attn_local, i_local, 64),
                                          device=dev)
-        comm = make_comm("fused", model, max_batch=4)
+        comm = make_comm("fused", model, max_batch=max(4, a.matvec_max_batch))
     else:
         model = TransformerModel(random_on_device(cfg, dev, quant))
     assert enable_native_prefill(model)
@@ -114,7 +120,7 @@ def main():
     # ---- prefill: time to first token
     blocks_per_seq = (cfg.max_seq_len + 15) // 16
     cache = model.new_cache(blocks_per_seq * (max(batches) + 3) + 2, max_seqs=max(batches) + 4,
-                            max_blocks_per_seq=blocks_per_seq)
+                            max_blocks_per_seq=blocks_per_seq, kv_quant=a.kv_quant)
     g = torch.Generator().manual_seed(0)
     prompt = torch.randint(0, cfg.vocab_size, (a.prompt,), generator=g).to(dev)
     times = []
@@ -136,7 +142,7 @@ def main():
             cache.reserve(s, a.prompt)
             cache.commit(s, a.prompt)          # context content is irrelevant to timing (zeros)
         last = [1] * b
-        if b <= 4:
+        if b <= a.matvec_max_batch:
             eng = CachedDecode(model, cache, max_batch=b, comm=comm)
         else:
             eng = BatchedDecode(model, cache, max_batch=b)

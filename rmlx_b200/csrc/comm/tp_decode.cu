@@ -617,7 +617,9 @@ extern "C" int rmlx_tp_gemv_allreduce(int w_kind, const void* w, const void* sca
       world > kMaxWorld)
     return -2;
   const TpPeers P = make_peers(recv, ctr, rank, world, bmax);
-  if (tp_stream_on() && N % 4 == 0 && w_kind >= 0 && w_kind <= 2 &&
+  // 8-bit weights and fp16 scales exist only in the streaming kernels
+  const bool stream_only = w_kind == 2 || (kind_bits & 0x100);
+  if ((tp_stream_on() || stream_only) && N % 4 == 0 && w_kind >= 0 && w_kind <= 2 &&
       sg_weights_ok(w_kind, w, scales, biases, K)) {
     const SgTpTail T = make_tail(P, residual, res_stride, out, out_stride, N);
     int rc = -2;
@@ -632,7 +634,7 @@ extern "C" int rmlx_tp_gemv_allreduce(int w_kind, const void* w, const void* sca
 #undef RB_TPS
     if (rc != -2) { tp_stream_launches() += rc == 0; return rc; }
   }
-  if (kind_bits & 0x100) return -2;
+  if (stream_only) return -2;
   const int grid = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
 #define RB_TPG(WT, BB)                                                                            \
   {                                                                                               \
@@ -669,7 +671,8 @@ extern "C" int rmlx_tp_moe_down_allreduce(int w_kind, const void* w, const void*
       world < 1 || world > kMaxWorld)
     return -2;
   const TpPeers P = make_peers(recv, ctr, rank, world, bmax);
-  if (tp_stream_on() && N % 4 == 0 && w_kind >= 0 && w_kind <= 2 && experts_local <= 256 &&
+  const bool stream_only = w_kind == 2 || (kind_bits & 0x100);
+  if ((tp_stream_on() || stream_only) && N % 4 == 0 && w_kind >= 0 && w_kind <= 2 && experts_local <= 256 &&
       sg_weights_ok(w_kind, w, scales, biases, I) && !(w_kind == 0 && I % 32)) {
     const SgTpTail T = make_tail(P, residual, res_stride, out, out_stride, N);
     int rc = -2;
@@ -681,7 +684,7 @@ extern "C" int rmlx_tp_moe_down_allreduce(int w_kind, const void* w, const void*
 #undef RB_TPS
     if (rc != -2) { tp_stream_launches() += rc == 0; return rc; }
   }
-  if (kind_bits & 0x100) return -2;
+  if (stream_only) return -2;
   const int gx = (N + kTpRowsPerCta - 1) / kTpRowsPerCta;
 #define RB_TPD(WT, MK)                                                                            \
   {                                                                                               \

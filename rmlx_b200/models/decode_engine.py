@@ -160,8 +160,11 @@ class CachedDecode:
         block_table, q, attn = self.block_table[:nb], self.q[:nb], self.attn[:nb]
         D.embedding(w.embed, tokens, out=self.h[:nb], pdl=False)
         h, h2 = self.h[:nb], self.h2[:nb]
+        # several rows on 4-bit weights: the projection runs on the tensor-core mat-vec (eight rows
+        # per pass) and RoPE + the KV append follow as their own small kernel
+        fuse_rope = self.fuse_rope and not (nb >= 2 and w.layers[0].wqkv.kind == 1)
         for li, lw in enumerate(w.layers):
-            if self.fuse_rope:
+            if fuse_rope:
                 D.rms_qkv_rope(h, lw.wqkv, lw.norm1, eps, q, self.cache.k[li], self.cache.v[li],
                                block_table, positions, m.cos, m.sin, m.hq, m.hkv,
                                traditional=cfg.rope_traditional, pdl=pdl)

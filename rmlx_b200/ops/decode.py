@@ -80,7 +80,13 @@ def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = 
     if out is None:
         out = torch.empty(b, n, dtype=out_dtype, device=x.device)
     lib, st = _lib.cuda(), _lib.stream_ptr()
-    if _STREAM:
+    # Several rows against 4-bit weights: the tensor-core mat-vec carries up to eight rows in the
+    # MMA's columns for the price of one, while the CUDA-core kernels pay their unpacking FMAs per
+    # row (measured on B200, 9216x4096: four rows 29.5 us streaming; the weights are read once
+    # either way).
+    mma_rows = (w.kind == W_Q4 and not w.scales_f16 and b >= 2 and q4_path() != "scalar" and
+                bool(lib.rmlx_qmv_mma_supported(k, min(8, b), 16)))
+    if _STREAM and not mma_rows:
         done = True
         for b0 in range(0, b, _MAXB):
             bb = min(_MAXB, b - b0)
@@ -96,7 +102,8 @@ def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = 
             _lib.check(rc, "sg_rms_gemv")
         if done:
             return out
-    if w.kind == W_Q4 and q4_path() == "mma" and lib.rmlx_qmv_mma_supported(k, min(8, b), 16):
+    if mma_rows or (w.kind == W_Q4 and not w.scales_f16 and q4_path() == "mma" and
+                    lib.rmlx_qmv_mma_supported(k, min(8, b), 16)):
         for b0 in range(0, b, 8):
             bb = min(8, b - b0)
             xs, os_ = x[b0:b0 + bb], out[b0:b0 + bb]

@@ -19,16 +19,27 @@ def _grouped_ok(w: LinearWeight) -> bool:
     return w.n % 128 == 0 and (w.kind != W_Q4 or bool(_lib.cuda().rmlx_qgemm_supported(w.k)))
 
 
+def _expanded_if_needed(w: LinearWeight) -> LinearWeight:
+    if w.kind == W_BF16:
+        return w
+    if w.kind == W_Q4 and not w.scales_f16 and bool(_lib.cuda().rmlx_qgemm_supported(w.k)):
+        return w
+    dense = getattr(w, "_dense_bf16_cache", None)
+    if dense is None:
+        dense = LinearWeight(W_BF16, w.dense_bf16())
+        w._dense_bf16_cache = dense
+    return dense
+
+
 def grouped_expert_ffn(x_sorted: torch.Tensor, offsets: torch.Tensor, gate_up: LinearWeight,
                        down: LinearWeight, zero_rest: bool = False) -> torch.Tensor:
     """x_sorted [R, D] bf16 (rows grouped by expert), offsets [E+1] -> [R, D]. The offsets are
     absolute row numbers of ``x_sorted``, so a rank that holds a slice of the experts passes the
     matching slice of the global offsets; ``zero_rest`` then returns zeros in the rows of the
     experts it does not hold."""
-    if gate_up.kind == W_Q8 or gate_up.scales_f16:   # expanded to bf16 for the grouped tensor-core GEMM
-        gate_up = LinearWeight(W_BF16, gate_up.dense_bf16())
-    if down.kind == W_Q8 or down.scales_f16:
-        down = LinearWeight(W_BF16, down.dense_bf16())
+    # 8-bit weights, fp16 scales and 4-bit shapes the fused kernel does not take (K not a multiple
+    # of 512, e.g. experts sliced along their inner dimension) are expanded to bf16 once and kept
+    gate_up, down = _expanded_if_needed(gate_up), _expanded_if_needed(down)
     if not (_grouped_ok(gate_up) and _grouped_ok(down)):
         raise ImportError("shape not covered by the grouped tensor-core kernel")
     off = offsets.to(torch.int32)

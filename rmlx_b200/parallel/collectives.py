@@ -53,8 +53,6 @@ class PeerCollectives:
             flag_bytes = int(_lib.cuda().rmlx_nvls_flag_bytes())
             self._nvls = SymmetricRegion(self.nvls_cap + 256 + flag_bytes, group)
             self._nvls_flags = self._nvls.peer_array(self.nvls_cap + 256)
-            # the grid is fixed per flag area (block b counts on flag word b)
-            self.nvls_blocks = max(1, min(32, self.nvls_cap // self.world // (512 * 16 * 4)))
 
     def _run(self, op: int, src: torch.Tensor, dst: torch.Tensor, chunk_bytes: int, root: int = 0) -> torch.Tensor:
         assert src.is_contiguous() and dst.is_contiguous() and src.is_cuda and dst.is_cuda
@@ -130,7 +128,7 @@ class PeerCollectives:
             buf.copy_(x.view(-1))
         rc = _lib.cuda().rmlx_nvls_allreduce(ctypes.c_void_p(self._nvls.mc), nbytes,
                                              int(dtype == torch.bfloat16), self._nvls_flags, self.rank,
-                                             self.world, self.nvls_blocks, _lib.stream_ptr())
+                                             self.world, 0, _lib.stream_ptr())
         _lib.check(rc, "nvls_allreduce")
         if x is None:
             return buf

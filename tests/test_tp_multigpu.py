@@ -95,7 +95,7 @@ def _worker(rank, world, port, quant, comm_kind, dense_first, max_batch, use_gra
         assert comm.status() == 0
         assert torch.isfinite(eng.logits[:nseq, :v_local]).all()
         if comm_kind == "fused":   # the streaming form ran unless it was switched off
-            assert (comm.stream_launches() > 0) == (os.environ.get("RMLX_TP_STREAM", "1") != "0")
+            assert (comm.stream_launches() > 0) == (comm.stream or quant == "q8")
 
         if rank == 0:
             full = TransformerModel(from_state_dict(cfg, sd, device=dev, quant=quant))
@@ -157,7 +157,8 @@ def test_tp_decode_matches_single_gpu(quant, comm_kind, dense_first, max_batch, 
 
 
 @pytest.mark.parametrize("quant,max_batch", [("q4", 2), (None, 8)])
-def test_tp_decode_per_row_kernels(monkeypatch, quant, max_batch):
-    """The per-row fused kernels (shapes the streaming kernel does not take) keep working."""
-    monkeypatch.setenv("RMLX_TP_STREAM", "0")
+@pytest.mark.parametrize("stream", ["0", "1"])
+def test_tp_decode_both_kernel_families(monkeypatch, quant, max_batch, stream):
+    """The per-row and the weight-streaming fused kernels, whichever the rank count would pick."""
+    monkeypatch.setenv("RMLX_TP_STREAM", stream)
     test_tp_decode_matches_single_gpu(quant, "fused", 1, max_batch, True)
