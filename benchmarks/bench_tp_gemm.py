@@ -74,6 +74,19 @@ def main():
         tf = timed(lambda: fused.gemm_allreduce(x, w, residual=res), a.iters)
         tn = timed(lambda: nccl.gemm_allreduce(x, w, residual=res), a.iters)
         rows.append((f"gemm+allreduce m={m} k/rank={kl}", tf, tn, floor))
+        if m % (128 * world) == 0:
+            # reduce-scatter: the partial tiles cross NVLink once, nothing comes back
+            link_rs = m * hidden * 2 * (world - 1) / world
+            floor_rs = max(flops / (peak * 1e6), link_rs / 770e3)
+
+            def nccl_rs():
+                y = nccl._mm(x, w)
+                o = torch.empty(m // world, hidden, dtype=y.dtype, device=dev)
+                dist.reduce_scatter_tensor(o, y)
+                return o
+            tf = timed(lambda: fused.gemm_reduce_scatter(x, w, residual=res), a.iters)
+            tn = timed(nccl_rs, a.iters)
+            rows.append((f"gemm+reduce_scatter m={m} k/rank={kl}", tf, tn, floor_rs))
         if a.trace:
             fused.enable_trace()
             fused.gemm_allreduce(x, w, residual=res)

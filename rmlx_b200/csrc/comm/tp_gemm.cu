@@ -50,7 +50,12 @@ extern "C" int rmlx_tp_gemm_allreduce(int w_kind, const void* A, const void* W, 
                                       const void* biases, const void* residual, void* const* stage,
                                       void* const* tile_flags, void* const* out, void* const* done,
                                       void* epoch, int rank, int world, int M, int N, int K, int lda,
-                                      int ldc, int bn, int* status, void* trace, cudaStream_t st) {
+                                      int ldc, int bn, int scatter, int* status, void* trace,
+                                      cudaStream_t st) {
+  // scatter != 0: GEMM + reduce-scatter. The owner of a tile (tile index modulo world; with a
+  // whole number of 128-row blocks per rank that is row block b -> rank b % world, for every
+  // column) keeps the reduced tile in its own output and nothing is broadcast; the ranks still
+  // leave together, so the staging slabs are free for the next call.
   if (world < 1 || world > kXMaxRanks || rank < 0 || rank >= world) return -2;
   if (M < 1 || N < 8 || N % 8 || ldc % 8 || K < 8 || K % 8 || lda % 8) return -2;
   if (w_kind == 1 && K % 512) return -2;
@@ -67,6 +72,7 @@ extern "C" int rmlx_tp_gemm_allreduce(int w_kind, const void* A, const void* W, 
   cm.trace = static_cast<unsigned long long*>(trace);   // optional [grid][8] phase timestamps
   const int tiles = ((M + kXBM - 1) / kXBM) * ((N + bn - 1) / bn);
   cm.tiles_owned_max = (tiles + world - 1) / world;
+  cm.scatter = scatter != 0;
   for (int p = 0; p < world; ++p) {
     cm.stage[p] = static_cast<__nv_bfloat16*>(stage[p]);
     cm.tile_flags[p] = static_cast<uint32_t*>(tile_flags[p]);

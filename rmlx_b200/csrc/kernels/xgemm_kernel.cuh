@@ -43,6 +43,7 @@ struct XComm {
   __nv_bfloat16* out[kXMaxRanks] = {};       // rank p's output matrix [M, ldc]
   uint32_t* done[kXMaxRanks] = {};           // rank p's count of finished tiles
   int tiles_owned_max = 0;
+  int scatter = 0;                           // 1: reduce-scatter (the owner keeps the finished tile, no broadcast)
   // gather
   const __nv_bfloat16* a_shard = nullptr;    // this rank's rows [shard_rows, lda_shard]
   int lda_shard = 0, shard_rows = 0;
@@ -169,9 +170,13 @@ __device__ __forceinline__ void x_reduce_tile(const XComm& cm, const __nv_bfloat
         uint4 o;
         o.x = pack_bf16(f[0], f[1]); o.y = pack_bf16(f[2], f[3]);
         o.z = pack_bf16(f[4], f[5]); o.w = pack_bf16(f[6], f[7]);
-        for (int pi = 0; pi < cm.world; ++pi) {
-          int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
-          *reinterpret_cast<uint4*>(cm.out[p] + off[u]) = o;
+        if (cm.scatter) {
+          *reinterpret_cast<uint4*>(cm.out[cm.rank] + off[u]) = o;
+        } else {
+          for (int pi = 0; pi < cm.world; ++pi) {
+            int p = cm.rank + pi; if (p >= cm.world) p -= cm.world;
+            *reinterpret_cast<uint4*>(cm.out[p] + off[u]) = o;
+          }
         }
       }
     }

@@ -23,7 +23,7 @@ from .comm import SymmetricRegion
 
 _lib.register_cuda_sigs({
     "rmlx_tp_gemm_stage_bytes": ("iiii", "q"),
-    "rmlx_tp_gemm_allreduce": ("ippppppppppiiiiiiiippp", "i"),
+    "rmlx_tp_gemm_allreduce": ("ippppppppppiiiiiiiiippp", "i"),
     "rmlx_tp_allgather_gemm": ("ipiippppppppiiiiiippp", "i"),
 })
 
@@ -85,8 +85,27 @@ class FusedGemmComm:
         return off
 
     # ------------------------------------------------------------------ row-parallel: GEMM + all-reduce
+    def gemm_reduce_scatter(self, x: torch.Tensor, w: LinearWeight,
+                            residual: Optional[torch.Tensor] = None, bn: int = 0) -> torch.Tensor:
+        """x [M, K_local] bf16, w [N, K_local] -> this rank's share of sum over ranks (+ residual):
+        the 128-row blocks b with b % world == rank, in order, as [M / world, N] (a strided view of a
+        peer-mapped buffer, valid until the call after next). Nothing is broadcast: a finished tile
+        stays with the rank that reduced it. M must be a whole number of 128-row blocks per rank.
+        ``owned_rows(M)`` lists the row indices (crates/rmlx-distributed/src/group.rs:728,
+        reduce_scatter)."""
+        m = x.shape[0]
+        if m % (128 * self.world):
+            raise ValueError("reduce-scatter needs M to be a multiple of 128 x world")
+        full = self.gemm_allreduce(x, w, residual, bn, _scatter=True)
+        return full.view(m // 128, 128, w.n)[self.rank::self.world].reshape(m // self.world, w.n)
+
+    def owned_rows(self, m: int) -> torch.Tensor:
+        """Row indices of the [M, N] result that ``gemm_reduce_scatter`` leaves on this rank."""
+        blocks = torch.arange(self.rank, m // 128, self.world)
+        return (blocks[:, None] * 128 + torch.arange(128)[None, :]).reshape(-1)
+
     def gemm_allreduce(self, x: torch.Tensor, w: LinearWeight, residual: Optional[torch.Tensor] = None,
-                       bn: int = 0) -> torch.Tensor:
+                       bn: int = 0, _scatter: bool = False) -> torch.Tensor:
         """x [M, K_local] bf16, w [N, K_local] -> sum over ranks (+ residual) as [M, N], complete on
         every rank. The result is a view of one of two peer-mapped buffers, valid until the call
         after next."""
@@ -97,7 +116,7 @@ class FusedGemmComm:
         tiles = ((m + 127) // 128) * ((n + bn - 1) // bn)
         owned = (tiles + self.world - 1) // self.world
         # block: [0] epoch, [1] ticket, [2] done, [4..] per-tile arrival counters
-        off = self._site(("ar", m, n, bn), 4 + owned)
+        off = self._site(("rs" if _scatter else "ar", m, n, bn), 4 + owned)
         self._flip ^= 1
         out = self._out_views[self._flip][: m * n * 2].view(torch.bfloat16).view(m, n)
         if residual is not None:
@@ -107,7 +126,8 @@ class FusedGemmComm:
             w.kind, x.data_ptr(), w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases),
             _lib.ptr(residual), self._stage, rg.peer_array(off + 16), rg.peer_array(self.off_out[self._flip]),
             rg.peer_array(off + 8), ctypes.c_void_p(rg.local + off), self.rank, self.world, m, n, k,
-            x.stride(0), n, bn, GemmStatus.get(self.device).data_ptr(), _lib.ptr(self.trace), _lib.stream_ptr())
+            x.stride(0), n, bn, int(_scatter), GemmStatus.get(self.device).data_ptr(), _lib.ptr(self.trace),
+            _lib.stream_ptr())
         _lib.check(rc, "tp_gemm_allreduce")
         return out
 
@@ -173,6 +193,15 @@ class NcclGemmComm:
         y = self._mm(x, w)
         dist.all_reduce(y, group=self.group)
         return y if residual is None else y + residual
+
+    def gemm_reduce_scatter(self, x, w, residual=None, bn=0):
+        m = x.shape[0]
+        y = self.gemm_allreduce(x, w, residual, bn)
+        return y.view(m // 128, 128, w.n)[self.rank::self.world].reshape(m // self.world, w.n)
+
+    def owned_rows(self, m: int) -> torch.Tensor:
+        blocks = torch.arange(self.rank, m // 128, self.world)
+        return (blocks[:, None] * 128 + torch.arange(128)[None, :]).reshape(-1)
 
     def allgather_gemm(self, x_shard, w, residual=None, out=None, bn=0):
         full = torch.empty(x_shard.shape[0] * self.world, x_shard.shape[1], dtype=x_shard.dtype,

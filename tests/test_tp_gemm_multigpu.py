@@ -50,6 +50,16 @@ def _worker(rank, world, port, ret):
                     errs.append(((got.float() - want).abs().max() / want.abs().max()).item())
                 b = base.gemm_allreduce(xs, w, residual=res.to(dev))
                 errs.append(((b.float() - want).abs().max() / want.abs().max()).item())
+                if m % (128 * world) == 0:
+                    # GEMM + reduce-scatter: the owner keeps its 128-row blocks, nothing is broadcast
+                    rows = comm.owned_rows(m).to(dev)
+                    for it in range(2):
+                        mine = comm.gemm_reduce_scatter(xs, w, residual=res.to(dev))
+                        torch.cuda.synchronize()
+                        assert mine.shape == (m // world, n)
+                        errs.append(((mine.float() - want[rows]).abs().max() / want.abs().max()).item())
+                    bm = base.gemm_reduce_scatter(xs, w, residual=res.to(dev))
+                    errs.append(((bm.float() - want[rows]).abs().max() / want.abs().max()).item())
             # all-gather + GEMM: rows sharded, weight columns sharded
             for (ms, n, k) in ((128, 512, 1024), (256, 1024, 512)):
                 m = ms * world
