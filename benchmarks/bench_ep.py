@@ -108,15 +108,19 @@ def main():
                 y = grouped_expert_ffn(got, layout.offsets, gu, dn)
                 return lib.combine(y, wts, layout)
 
+            def layer_captured():
+                return moe.forward_captured(x, router, k)
+
             fa, fb = layer_fused().float(), layer_lib()
             err = (fa - fb).abs().max().item() / max(fb.abs().max().item(), 1e-6)
-            layer_rows.append((t, timed(layer_fused, a.iters), timed(layer_lib, a.iters), err))
+            layer_rows.append((t, timed(layer_fused, a.iters), timed(layer_lib, a.iters), err,
+                               timed(layer_captured, a.iters)))
     st = fused.status()
     if rank == 0 and layer_rows:
         print(f"# expert-parallel MoE layer end to end (router + exchange + grouped FFN + combine), weights={a.weights}")
-        print(f"{'tokens/rank':>11s} {'fused us':>9s} {'nccl us':>9s} {'speedup':>8s} {'max rel diff':>12s}")
-        for t, tf, tn, err in layer_rows:
-            print(f"{t:11d} {tf:9.1f} {tn:9.1f} {tn / tf:8.2f} {err:12.1e}")
+        print(f"{'tokens/rank':>11s} {'fused us':>9s} {'captured us':>11s} {'nccl us':>9s} {'nccl/captured':>13s} {'max rel diff':>12s}")
+        for t, tf, tn, err, tc in layer_rows:
+            print(f"{t:11d} {tf:9.1f} {tc:11.1f} {tn:9.1f} {tn / tc:13.2f} {err:12.1e}")
     if rank == 0:
         print(f"# world={world} hidden={hidden} experts={E} top_k={k}; NVLink 770 GB/s/dir; status={st}")
         print(f"{'tokens/rank':>11s} {'fused us':>9s} {'nccl us':>9s} {'speedup':>8s} {'floor us':>9s} {'floor/fused':>11s} {'max rel diff':>12s}")

@@ -147,10 +147,19 @@ ep_dispatch_kernel(EpPeers pp, const __nv_bfloat16* __restrict__ x, int x_stride
       int e = 0, pos = 0;
       if (lane == 0) {
         e = idx[p];
-        pos = s_myoff[e] + int(atomicAdd(cursors + e, 1u));
+        // an expert id outside the table, or a row beyond the slab (ids that do not match the
+        // counts), is reported and skipped: nothing is written through a bad index
+        if (e < 0 || e >= E) {
+          e = -1;
+          ep_fail(status, kStatusBadArgument);
+        } else {
+          pos = s_myoff[e] + int(atomicAdd(cursors + e, 1u));
+          if (pos < 0 || pos >= capacity_rows) { e = -1; ep_fail(status, kEpStatusOverflow); }
+        }
       }
       e = __shfl_sync(0xffffffffu, e, 0);
       pos = __shfl_sync(0xffffffffu, pos, 0);
+      if (e < 0) continue;
       const int dest = e / e_local;
       ep_copy_row(reinterpret_cast<uint4*>(pp.slab[dest] + size_t(pos) * D),
                   reinterpret_cast<const uint4*>(x + size_t(p / top_k) * x_stride), D / 8, lane);

@@ -112,6 +112,9 @@ class FusedEpMoe:
     def __init__(self, exchange: FusedEpExchange, gate_up: LinearWeight, down: LinearWeight):
         assert gate_up.experts == exchange.e_local
         self.ex, self.gate_up, self.down = exchange, gate_up, down
+        from ..runtime.graph import GraphCache
+        self.graphs = GraphCache(max_entries=16)
+        self._static = {}
 
     @torch.no_grad()
     def forward(self, x: torch.Tensor, router_w: torch.Tensor, top_k: int,
@@ -124,3 +127,40 @@ class FusedEpMoe:
         rows = int(self.ex.capacity)            # the grouped kernel only touches rows below offsets[-1]
         y = grouped_expert_ffn(slab[:rows], offsets, self.gate_up, self.down)
         return self.ex.combine(y, wts, x.shape[0], residual)
+
+    @torch.no_grad()
+    def forward_captured(self, x: torch.Tensor, router_w: torch.Tensor, top_k: int,
+                         expert_bias: Optional[torch.Tensor] = None,
+                         residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``forward`` as ONE CUDA-graph replay per token count: router, dispatch, grouped expert
+        FFN and combine are captured together (the exchange keeps its epochs on the device, so a
+        replay needs nothing from the host), which removes the launches and allocations from
+        Python between the phases. Collective: every rank calls it with the same token count, the
+        first call per count captures (one eager warm-up run, then the capture). The result is a
+        buffer owned by the graph, valid until the next call with the same token count.
+        Counterpart of the reference's asynchronous exchange-and-compute chain
+        (crates/rmlx-nn/src/moe.rs:786-1008)."""
+        t = x.shape[0]
+        key = (t, top_k, residual is not None)
+        st = self._static.get(key)
+        if st is None:
+            # everything the graph reads lives in buffers the graph's owner keeps: activations and
+            # residual are copied in per call; the router matrix and the bias are kept by reference
+            # when the caller passes the same tensors again (model parameters) and copied otherwise
+            st = {"x": torch.empty_like(x), "res": None if residual is None else torch.empty_like(residual),
+                  "out": torch.empty(t, self.ex.D, dtype=torch.bfloat16, device=x.device),
+                  "router": router_w, "bias": expert_bias}
+            self._static[key] = st
+
+        def body():
+            st["out"].copy_(self.forward(st["x"], st["router"], top_k, st["bias"], st["res"]))
+
+        st["x"].copy_(x)
+        if residual is not None:
+            st["res"].copy_(residual)
+        if router_w is not st["router"]:
+            st["router"].copy_(router_w)
+        if expert_bias is not None and expert_bias is not st["bias"]:
+            st["bias"].copy_(expert_bias)
+        self.graphs.get_or_capture(key, body, warmup=1, device=x.device).replay()
+        return st["out"]

@@ -54,6 +54,21 @@ def _worker(rank, world, port, ret):
                 idx, wts, _ = ref.topk_route(logits, k)
                 want = ref.moe_ffn(x, idx, wts, gu_all, dn_all) + res.float()
                 errs.append(((got.float() - want).abs().max() / want.abs().max()).item())
+            # the whole layer as one CUDA-graph replay per token count (two replays each)
+            rw = router.to(dev).to(torch.bfloat16)
+            for it, t in enumerate((8, 64 + 8 * rank, 8)):
+                for rep in range(2):
+                    gx = torch.Generator().manual_seed(7000 + 100 * it + 10 * rep + rank)
+                    x = torch.randn(t, d, generator=gx).to(torch.bfloat16).to(dev)
+                    res = torch.randn(t, d, generator=gx).to(torch.bfloat16).to(dev)
+                    # the same parameter tensor, or (second replay) a copy that the layer takes over
+                    got = moe.forward_captured(x, rw if rep == 0 else rw.clone(), k, residual=res)
+                    torch.cuda.synchronize()
+                    logits = x.float() @ router.to(dev).to(torch.bfloat16).float().t()
+                    idx, wts, _ = ref.topk_route(logits, k)
+                    want = ref.moe_ffn(x, idx, wts, gu_all, dn_all) + res.float()
+                    errs.append(((got.float() - want).abs().max() / want.abs().max()).item())
+            assert moe.graphs.captures == 2 and moe.graphs.hits == 4
             status = ex.status()
             dist.barrier()
             ex.close()
