@@ -13,6 +13,8 @@ The hot paths do not go through this class: decode uses the fused peer-memory ke
 """
 from __future__ import annotations
 
+import os
+
 from enum import Enum
 from typing import List, Optional, Sequence
 
@@ -34,10 +36,22 @@ _OPS = {ReduceOp.SUM: dist.ReduceOp.SUM, ReduceOp.MAX: dist.ReduceOp.MAX, Reduce
 
 
 class Group:
+    """Collectives of one process group. CUDA tensors go through this package's peer-memory
+    kernels (``parallel.collectives.PeerCollectives`` over the symmetric heap: all-reduce,
+    all-gather, reduce-scatter, all-to-all, broadcast) whenever the call fits them (sum, bf16 or
+    fp32, pieces of whole 16-byte vectors); everything else, and every CPU tensor, goes to
+    ``torch.distributed`` (NCCL / gloo), the last resort. ``RMLX_GROUP_NATIVE=0`` switches the
+    native path off; ``native_calls`` / ``library_calls`` count which way calls went.
+    Reference: crates/rmlx-distributed/src/group.rs:348-964 (ring / tree / mesh algorithms over
+    RDMA selected by size)."""
+
     def __init__(self, pg=None, ranks: Optional[List[int]] = None):
         """``pg``: a torch process group (None = the default group when initialised, else a
         single-rank group)."""
         self._pg = pg
+        self._pc = None
+        self.native_calls = 0
+        self.library_calls = 0
         if dist.is_available() and dist.is_initialized():
             self.local_rank = dist.get_rank(pg)
             self.world_size = dist.get_world_size(pg)
@@ -61,10 +75,44 @@ class Group:
             return t.float(), t.dtype
         return t, None
 
+    # ------------------------------------------------------------------ native path
+    def _native(self, t: torch.Tensor, piece_bytes: int, summed: bool = False):
+        """The peer-memory collectives for a call that moves pieces of ``piece_bytes`` per rank,
+        or None when the call has to go to the library. Creating (or growing) the communicator is
+        collective; every rank takes the same decision because it depends on shapes only."""
+        if (self.single or not t.is_cuda or piece_bytes <= 0 or piece_bytes % 16 or
+                os.environ.get("RMLX_GROUP_NATIVE", "1") == "0"):
+            return None
+        if summed and t.dtype not in (torch.bfloat16, torch.float32):
+            return None
+        if piece_bytes > (64 << 20):            # large transfers: the library's pipelined rings
+            return None
+        if self._pc is None or piece_bytes > self._pc.cap:
+            from .collectives import PeerCollectives
+            if self._pc is not None:
+                self._pc.close()
+            cap = 1 << 20
+            while cap < piece_bytes:
+                cap <<= 1
+            self._pc = PeerCollectives(cap, group=self._pg, device=t.device)
+        self.native_calls += 1
+        return self._pc
+
+    def close(self) -> None:
+        """Release the native communicator (collective)."""
+        if self._pc is not None:
+            self._pc.close()
+            self._pc = None
+
     # ------------------------------------------------------------------ collectives
     def allreduce(self, t: torch.Tensor, op: ReduceOp = ReduceOp.SUM) -> torch.Tensor:
         if self.single:
             return t.clone()
+        if op == ReduceOp.SUM and t.numel() % self.world_size == 0:
+            pc = self._native(t, t.numel() * t.element_size() // self.world_size, summed=True)
+            if pc is not None:
+                return pc.all_reduce(t.contiguous()).view(t.shape)
+        self.library_calls += 1
         w, narrow = self._widen(t.contiguous())
         w = w.clone()
         dist.all_reduce(w, op=_OPS[op], group=self._pg)
@@ -85,6 +133,11 @@ class Group:
     def allgather(self, t: torch.Tensor, dim: int = 0) -> torch.Tensor:
         if self.single:
             return t.clone()
+        if dim == 0 and t.dim() >= 1:
+            pc = self._native(t, t.numel() * t.element_size())
+            if pc is not None:
+                return pc.all_gather(t.contiguous())
+        self.library_calls += 1
         parts = [torch.empty_like(t) for _ in range(self.world_size)]
         dist.all_gather(parts, t.contiguous(), group=self._pg)
         return torch.cat(parts, dim)
@@ -92,6 +145,12 @@ class Group:
     def broadcast(self, t: torch.Tensor, root: int = 0) -> torch.Tensor:
         if self.single:
             return t
+        if t.is_contiguous():
+            pc = self._native(t, t.numel() * t.element_size())
+            if pc is not None:
+                t.copy_(pc.broadcast(t, root=root))
+                return t
+        self.library_calls += 1
         dist.broadcast(t, src=self._global(root), group=self._pg)
         return t
 
@@ -101,6 +160,11 @@ class Group:
             return t.clone()
         if t.shape[0] % self.world_size:
             raise DistributedError("reduce_scatter: leading dim must divide by the world size")
+        if op == ReduceOp.SUM:
+            pc = self._native(t, t.numel() * t.element_size() // self.world_size, summed=True)
+            if pc is not None:
+                return pc.reduce_scatter(t.contiguous())
+        self.library_calls += 1
         w, narrow = self._widen(t.contiguous())
         n = t.shape[0] // self.world_size
         if w.is_cuda:
@@ -121,6 +185,9 @@ class Group:
         if send_counts is None:
             if t.shape[0] % self.world_size:
                 raise DistributedError("all_to_all: rows must divide by the world size")
+            pc = self._native(t, t.numel() * t.element_size() // self.world_size)
+            if pc is not None:
+                return pc.all_to_all(t)
             send_counts = recv_counts = [t.shape[0] // self.world_size] * self.world_size
         elif recv_counts is None:
             sc = torch.tensor(list(send_counts), dtype=torch.int64, device=t.device)

@@ -58,6 +58,34 @@ def _worker(rank, world, port, ret):
                 want_b = x.clone(); dist.broadcast(want_b, world - 1)
                 if not torch.equal(pc.broadcast(x, root=world - 1), want_b):
                     bad.append(("broadcast", rnd, str(dtype)))
+        # the Group API takes the same kernels for CUDA tensors that fit them, the library otherwise
+        from rmlx_b200.parallel.group import Group
+        grp = Group()
+        x = torch.randn(world * 512, 16, device=dev, generator=g).to(torch.bfloat16)
+        want = x.clone(); dist.all_reduce(want)
+        if not torch.allclose(grp.allreduce(x).float(), want.float(), rtol=2e-2, atol=2e-2):
+            bad.append(("group.allreduce",))
+        want_ag = torch.empty(world * x.shape[0], 16, device=dev, dtype=x.dtype)
+        dist.all_gather_into_tensor(want_ag, x)
+        if not torch.equal(grp.allgather(x), want_ag):
+            bad.append(("group.allgather",))
+        want_rs = torch.empty(512, 16, device=dev, dtype=x.dtype)
+        dist.reduce_scatter_tensor(want_rs, x)
+        if not torch.allclose(grp.reduce_scatter(x).float(), want_rs.float(), rtol=2e-2, atol=2e-2):
+            bad.append(("group.reduce_scatter",))
+        want_a2a = torch.empty_like(x); dist.all_to_all_single(want_a2a, x)
+        if not torch.equal(grp.all_to_all(x), want_a2a):
+            bad.append(("group.all_to_all",))
+        y = x.clone(); want_b = x.clone(); dist.broadcast(want_b, 0)
+        if not torch.equal(grp.broadcast(y, 0), want_b):
+            bad.append(("group.broadcast",))
+        if grp.native_calls != 5 or grp.library_calls != 0:
+            bad.append(("group routing", grp.native_calls, grp.library_calls))
+        odd = torch.randn(7, device=dev)                     # 28 bytes: not whole 16-byte vectors
+        want_odd = odd.clone(); dist.all_reduce(want_odd)
+        if not torch.allclose(grp.allreduce(odd), want_odd) or grp.library_calls != 1:
+            bad.append(("group fallback", grp.library_calls))
+        grp.close()
         torch.cuda.synchronize()
         status = pc.status()
         dist.barrier()
