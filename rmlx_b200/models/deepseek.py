@@ -2,9 +2,11 @@
 dense feed-forward in the first layers (crates/rmlx-nn/src/models/deepseek.rs:30-490). The preset
 ``deepseek_v3()`` is the published shape (hidden 7168, 128 heads, 61 layers, 256 experts top-8 of
 width 2048, kv_lora 512, q_lora 1536, rope head 64, v head 128, one shared expert, first layer
-dense). The forward here is the library-kernel path (PyTorch ops) with a latent KV cache; the
+dense). ``forward`` is the library-kernel path (PyTorch ops) with a contiguous latent cache; the
 routed experts run through ``MoeLayer`` and therefore through this package's grouped kernels on
-CUDA."""
+CUDA. ``new_paged_cache`` / ``prefill_paged`` / ``decode_paged`` keep the latents in pages and run
+the decode attention in the absorbed form on the latent-attention kernel
+(csrc/kernels/mla_decode.cu) for several sequences per step."""
 from __future__ import annotations
 
 from dataclasses import dataclass
@@ -13,7 +15,7 @@ from typing import List, Optional
 import torch
 
 from ..config import MlaConfig, MoeConfig
-from ..nn.mla import MlaAttention, MlaKvCache, random_mla_weights
+from ..nn.mla import MlaAttention, MlaKvCache, MlaPagedCache, mla_decode_paged, random_mla_weights
 from ..nn.moe import ExpertGroup, MoeLayer, MoeStrategy
 from ..ops.weights import LinearWeight
 from ..reference import ops as ref
@@ -122,4 +124,40 @@ class DeepSeekV3Model:
                 h = h + b.moe.forward(xn)
             else:
                 h = h + ref.swiglu(xn @ b.dense_gate_up.t()) @ b.dense_down.t()
+        return (ref.rms_norm(h, self.final_norm, eps) @ self.lm_head.t()).float()
+
+    # ------------------------------------------------------------------ paged latent cache
+    def new_paged_cache(self, num_blocks: int, max_seqs: int = 8, dtype=None) -> List[MlaPagedCache]:
+        return [MlaPagedCache(self.cfg.mla(), num_blocks, max_seqs, dtype=dtype or self.embed.dtype,
+                              device=self.embed.device) for _ in self.blocks]
+
+    def _ffn(self, b: DeepSeekBlock, h: torch.Tensor) -> torch.Tensor:
+        xn = ref.rms_norm(h, b.norm2, self.cfg.rms_norm_eps)
+        if b.moe is not None:
+            return h + b.moe.forward(xn)
+        return h + ref.swiglu(xn @ b.dense_gate_up.t()) @ b.dense_down.t()
+
+    @torch.no_grad()
+    def prefill_paged(self, token_ids: torch.Tensor, cache: List[MlaPagedCache], seq_id: int) -> torch.Tensor:
+        """Run a prompt for ``seq_id`` (added to every layer's cache here), filling its latent
+        pages. Returns the last token's logits [1, vocab]."""
+        eps = self.cfg.rms_norm_eps
+        h = self.embed[token_ids.long()]
+        n = token_ids.numel()
+        for i, b in enumerate(self.blocks):
+            xn = ref.rms_norm(h, b.norm1, eps)
+            cache[i].add_sequence(seq_id)
+            cache[i].append(seq_id, *b.attn.compress(xn, torch.arange(n, device=h.device)))
+            h = self._ffn(b, h + b.attn(xn, None))          # causal attention over the prompt itself
+        return (ref.rms_norm(h[-1:], self.final_norm, eps) @ self.lm_head.t()).float()
+
+    @torch.no_grad()
+    def decode_paged(self, token_ids: torch.Tensor, cache: List[MlaPagedCache], seq_ids) -> torch.Tensor:
+        """One token per sequence: token_ids [B] (row b continues sequence seq_ids[b]).
+        Returns logits [B, vocab]."""
+        eps = self.cfg.rms_norm_eps
+        h = self.embed[token_ids.long()]
+        for i, b in enumerate(self.blocks):
+            h = h + mla_decode_paged(b.attn, ref.rms_norm(h, b.norm1, eps), cache[i], list(seq_ids))
+            h = self._ffn(b, h)
         return (ref.rms_norm(h, self.final_norm, eps) @ self.lm_head.t()).float()

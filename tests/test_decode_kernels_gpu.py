@@ -393,3 +393,33 @@ def test_fp16_scales_and_dequant_kernel(dev, quant, q4_path):
     dense = w16.dense_bf16()
     assert dense.dtype == torch.bfloat16 and torch.equal(dense.float(), wd.to(torch.bfloat16).float())
     assert torch.equal(w.dense_bf16().float(), w.dequantized().to(torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("lat,heads", [(128, 20), (512, 128), (512, 16)])
+def test_mla_decode_over_paged_latent_cache(dev, lat, heads, q4_path):
+    """Latent-attention decode kernel (absorbed queries, paged latent cache, KV splits + merge)
+    against fp32 attention over the gathered latents."""
+    if q4_path != "stream":
+        pytest.skip("one run is enough: the kernel does not depend on the mat-vec path")
+    from rmlx_b200.config import MlaConfig
+    from rmlx_b200.nn.mla import MlaPagedCache, _mla_decode_kernel
+    rope = 64
+    cfg = MlaConfig(hidden_size=256, num_heads=heads, head_dim=64, v_head_dim=64, kv_lora_rank=lat,
+                    rope_head_dim=rope, q_lora_rank=0, max_seq_len=2048)
+    torch.manual_seed(31)
+    lens = [1, 37, 700, 1500]
+    cache = MlaPagedCache(cfg, 1 + sum((l + 15) // 16 for l in lens) + 4, max_seqs=4, device=dev)
+    for s, l in enumerate(lens):
+        cache.add_sequence(s)
+        cache.append(s, torch.randn(l, lat, device=dev), torch.randn(l, rope, device=dev))
+    q = (torch.randn(len(lens), heads, lat + rope, device=dev) * 0.5).to(torch.bfloat16)
+    slots = torch.tensor([cache.slot_of(s) for s in range(len(lens))], dtype=torch.int32, device=dev)
+    scale = 1.0 / math.sqrt(64 + rope)
+    for splits in (1, 5, 0):
+        got = _mla_decode_kernel(q, cache, slots, scale, splits).float()
+        for s in range(len(lens)):
+            ck, kr = cache.gather(s)
+            keys = torch.cat([ck, kr], -1).float()
+            sc = (q[s].float() @ keys.t()) * scale
+            want = torch.softmax(sc, -1) @ ck.float()
+            _close(got[s], want, atol=3e-2)

@@ -168,3 +168,36 @@ def test_model_presets():
     cache = ds.new_cache()
     inc = torch.cat([ds.forward(ids[:5], cache), ds.forward(ids[5:], cache)])
     assert full.shape == (9, 256) and torch.allclose(inc, full, atol=1e-4)
+
+
+def test_mla_absorbed_decode_over_paged_latent_cache():
+    """The absorbed decode step over the paged latent cache equals the reference forward with the
+    contiguous cache (prompt of 20 tokens, then three single-token steps, two sequences)."""
+    from rmlx_b200.config import MlaConfig
+    from rmlx_b200.nn.mla import (MlaAttention, MlaKvCache, MlaPagedCache, mla_decode_paged,
+                                  random_mla_weights)
+    cfg = MlaConfig(hidden_size=256, num_heads=4, head_dim=32, v_head_dim=32, kv_lora_rank=128,
+                    rope_head_dim=64, q_lora_rank=0, max_seq_len=128)
+    attn = MlaAttention(cfg, random_mla_weights(cfg, 0, std=0.05))
+    torch.manual_seed(0)
+    xs = {3: torch.randn(24, 256), 9: torch.randn(12, 256)}
+    prompts = {3: 20, 9: 5}
+    refs = {s: MlaKvCache(cfg, dtype=torch.float32) for s in xs}
+    pc = MlaPagedCache(cfg, 16, dtype=torch.float32)
+    for s, x in xs.items():
+        n = prompts[s]
+        attn.forward(x[:n], refs[s])
+        pc.add_sequence(s)
+        pc.append(s, *attn.compress(x[:n], torch.arange(n)))
+    for step in range(3):
+        rows = torch.stack([xs[s][prompts[s] + step] for s in (3, 9)])
+        want = torch.cat([attn.forward(xs[s][prompts[s] + step][None], refs[s]) for s in (3, 9)])
+        got = mla_decode_paged(attn, rows, pc, [3, 9])
+        assert (got - want).abs().max() < 1e-5
+    assert pc.seq_len(3) == 23 and pc.seq_len(9) == 8 and pc.bytes_per_token() == (128 + 64) * 4
+    ck, kr = pc.gather(9)
+    assert torch.allclose(ck, refs[9].c_kv[:8]) and torch.allclose(kr, refs[9].k_rope[:8])
+    pc.free_sequence(3)
+    pc.add_sequence(11)                         # the slot and the pages are reusable
+    pc.append(11, *attn.compress(xs[9][:3], torch.arange(3)))
+    assert pc.seq_len(11) == 3

@@ -103,3 +103,28 @@ def test_tensor_parallel_gloo_world2_matches_single(kind, ep):
         p.join(timeout=60)
         assert p.exitcode == 0
     assert got == want
+
+
+def test_deepseek_paged_latent_decode_matches_the_contiguous_cache():
+    """Batched decode over paged latent caches (absorbed attention) generates the same tokens as
+    the per-sequence forward with contiguous latent caches."""
+    from rmlx_b200.models.deepseek import DeepSeekV3Model, deepseek_tiny
+    m = DeepSeekV3Model(deepseek_tiny(), seed=1)
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 256, (9,), generator=g), torch.randint(0, 256, (5,), generator=g)]
+    want = []
+    for p in prompts:
+        c = m.new_cache()
+        lg = m.forward(p, c)
+        toks = []
+        for _ in range(4):
+            toks.append(int(lg[-1].argmax()))
+            lg = m.forward(torch.tensor([toks[-1]]), c)
+        want.append(toks)
+    pc = m.new_paged_cache(16)
+    t = torch.tensor([int(m.prefill_paged(p, pc, s)[0].argmax()) for s, p in enumerate(prompts)])
+    got = [[], []]
+    for _ in range(4):
+        got[0].append(int(t[0])); got[1].append(int(t[1]))
+        t = m.decode_paged(t, pc, [0, 1]).argmax(-1)
+    assert got == want
