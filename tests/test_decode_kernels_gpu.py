@@ -416,7 +416,7 @@ def test_mla_decode_over_paged_latent_cache(dev, lat, heads, q4_path):
     slots = torch.tensor([cache.slot_of(s) for s in range(len(lens))], dtype=torch.int32, device=dev)
     scale = 1.0 / math.sqrt(64 + rope)
     for splits in (1, 5, 0):
-        got = _mla_decode_kernel(q, cache, slots, scale, splits).float()
+        got = _mla_decode_kernel(q, cache, slots, scale, splits)      # bf16 out: the bf16 bounds apply
         for s in range(len(lens)):
             ck, kr = cache.gather(s)
             keys = torch.cat([ck, kr], -1).float()

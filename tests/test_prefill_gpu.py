@@ -219,15 +219,19 @@ def test_batched_decode_matches_oracle(dev, cfg_fn, use_graph):
 
 
 def test_serving_engine_large_batch_uses_tensor_core_decode(dev):
-    """Six requests with max_batch 8 (beyond the mat-vec kernels' 4 rows): prompts go through the
-    native prefill, decode through the batched tensor-core step; first tokens match the oracle."""
+    """Six requests with max_batch 16 (beyond the 8 rows the mat-vec engine takes): prompts go
+    through the native prefill, decode through the batched tensor-core step; first tokens match the
+    oracle. With max_batch 8 the mat-vec engine is chosen."""
     from rmlx_b200.config import SchedulerConfig
     from rmlx_b200.models.prefill import BatchedDecode
     from rmlx_b200.serve.engine import ServingEngine
     cfg = _moe_cfg()
     model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant="q4"))
     oracle = _oracle_from(model)
-    eng = ServingEngine(model, num_blocks=96, scheduler_cfg=SchedulerConfig(max_batch_size=8, max_prefill_chunk=64))
+    from rmlx_b200.models.decode_engine import CachedDecode
+    small = ServingEngine(model, num_blocks=32, scheduler_cfg=SchedulerConfig(max_batch_size=8, max_prefill_chunk=64))
+    assert isinstance(small._engine, CachedDecode)
+    eng = ServingEngine(model, num_blocks=160, scheduler_cfg=SchedulerConfig(max_batch_size=16, max_prefill_chunk=64))
     assert isinstance(eng._engine, BatchedDecode)
     g = torch.Generator().manual_seed(11)
     prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (12, 30, 7, 21, 16, 9)]
