@@ -142,6 +142,12 @@ def from_state_dict(cfg: TransformerConfig, sd: Dict[str, torch.Tensor], device=
     hq, q0, hkv, kv0 = layout.heads(cfg)
     hd, d = cfg.head_dim, cfg.hidden_size
     w, r = layout.world, layout.rank
+    # Towards a GPU the layers go through the compute / transfer pipeline: layer i's slicing,
+    # packing and quantisation run on the host while layer i-1's tensors cross to the device on a
+    # second stream (parallel.pipeline.LayerPipeline; pinned staging makes the copies asynchronous).
+    final_device = torch.device(device)
+    piped = final_device.type == "cuda"
+    device = "cpu" if piped else device
 
     def lin(t: torch.Tensor) -> LinearWeight:
         return LinearWeight.from_dense(t, quant, dtype, device)
@@ -149,8 +155,20 @@ def from_state_dict(cfg: TransformerConfig, sd: Dict[str, torch.Tensor], device=
     def vec(t: torch.Tensor) -> torch.Tensor:
         return t.to(dtype).to(device).contiguous()
 
-    layers = []
-    for i in range(cfg.num_layers):
+    def ship(t):
+        """Host tensor (or weight container) -> the target device, asynchronously."""
+        if t is None or isinstance(t, int):
+            return t
+        if isinstance(t, LinearWeight):
+            return LinearWeight(t.kind, ship(t.w), ship(t.scales), ship(t.biases))
+        return t.pin_memory().to(final_device, non_blocking=True)
+
+    def ship_layer(_i: int, lw: "LayerWeights") -> "LayerWeights":
+        for f in lw.__dataclass_fields__:
+            setattr(lw, f, ship(getattr(lw, f)))
+        return lw
+
+    def host_layer(i: int) -> "LayerWeights":
         p = f"model.layers.{i}."
         q = sd[p + "self_attn.q_proj.weight"][q0 * hd:(q0 + hq) * hd]
         k = sd[p + "self_attn.k_proj.weight"][kv0 * hd:(kv0 + hkv) * hd]
@@ -189,12 +207,23 @@ def from_state_dict(cfg: TransformerConfig, sd: Dict[str, torch.Tensor], device=
             lw.w_gate_up = lin(torch.cat([sd[p + "mlp.gate_proj.weight"][i0:i1],
                                           sd[p + "mlp.up_proj.weight"][i0:i1]], 0))
             lw.w_down = lin(sd[p + "mlp.down_proj.weight"][:, i0:i1].contiguous())
-        layers.append(lw)
+        return lw
+
+    if piped:
+        from ..parallel.pipeline import LayerPipeline, PipelineConfig
+        pipe = LayerPipeline(PipelineConfig(num_layers=cfg.num_layers), device=final_device)
+        layers = pipe.run(host_layer, ship_layer)
+    else:
+        layers = [host_layer(i) for i in range(cfg.num_layers)]
     head = sd["model.embed_tokens.weight"] if cfg.tie_embeddings else sd["lm_head.weight"]
     v0, v1 = _split(cfg.vocab_size, w, r) if (shard_lm_head and w > 1) else (0, cfg.vocab_size)
-    return ModelWeights(cfg=cfg, layout=layout, embed=vec(sd["model.embed_tokens.weight"]),
-                        layers=layers, final_norm=vec(sd["model.norm.weight"]),
-                        lm_head=lin(head[v0:v1].contiguous()), vocab_base=v0)
+    fin = ship if piped else (lambda t: t)
+    out = ModelWeights(cfg=cfg, layout=layout, embed=fin(vec(sd["model.embed_tokens.weight"])),
+                       layers=layers, final_norm=fin(vec(sd["model.norm.weight"])),
+                       lm_head=fin(lin(head[v0:v1].contiguous())), vocab_base=v0)
+    if piped:
+        torch.cuda.synchronize(final_device)
+    return out
 
 
 def random_on_device(cfg: TransformerConfig, device, quant: Optional[str] = None,
