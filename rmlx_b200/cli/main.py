@@ -77,15 +77,17 @@ def launch(cmd: Sequence[str], nproc: int, backend: str = "auto", addr: str = "1
 
 def launch_hosts(cmd: Sequence[str], hosts: Sequence[str], per_host: int, backend: str = "nccl",
                  port: int = 18520, extra_env: Optional[Dict[str, str]] = None, cwd: Optional[str] = None,
-                 sink=None, poll_s: float = 0.05, dry_run: bool = False) -> int:
-    """One rank per GPU on every host, spawned through ssh; the first host is the coordinator.
+                 sink=None, poll_s: float = 0.05, dry_run: bool = False,
+                 coordinator: Optional[str] = None) -> int:
+    """One rank per GPU on every host, spawned through ssh; the first host is the coordinator
+    (``coordinator``: the address the ranks rendezvous at, default the first host's name).
     ``dry_run`` prints the ssh command lines instead of running them
     (crates/rmlx-cli/src/launch.rs:95-120: hosts list, per-rank environment, fail-fast)."""
     from . import ssh
     sink = sink or sys.stdout
     plan = ssh.plan_ranks(hosts, per_host)
     world = len(plan)
-    addr = hosts[0].split("@")[-1]
+    addr = coordinator or hosts[0].split("@")[-1]
     specs = []
     for host, rank, slot in plan:
         env = build_env(rank, world, backend, addr, port, extra_env, device_map=None)
@@ -153,6 +155,9 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     sub = ap.add_subparsers(dest="cmd", required=True)
     c = sub.add_parser("config", help="probe GPUs and NVLink topology")
     c.add_argument("--output", "-o", default=None)
+    c.add_argument("--hostfile", default=None,
+                   help="also write a one-entry hostfile for this machine (ssh target = --ssh)")
+    c.add_argument("--ssh", default="localhost", help="ssh target recorded in the hostfile")
     l = sub.add_parser("launch", help="run a command as one rank per GPU")
     l.add_argument("--nproc", "-n", type=int, default=0, help="ranks (default: all GPUs)")
     l.add_argument("--backend", default="auto")
@@ -160,21 +165,33 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     l.add_argument("--port", type=int, default=18520)
     l.add_argument("--env", action="append", default=[])
     l.add_argument("--hosts", default="", help="comma-separated [user@]host list: spawn over ssh, --nproc ranks per host")
+    l.add_argument("--hostfile", default=None, help="JSON hostfile (see cli/hostfile.py) instead of --hosts")
     l.add_argument("--cwd", default=None, help="working directory on the remote hosts")
     l.add_argument("--dry-run", action="store_true", help="with --hosts: print the ssh commands only")
     l.add_argument("command", nargs=argparse.REMAINDER)
     a = ap.parse_args(argv)
     if a.cmd == "config":
-        print(json.dumps(config(a.output), indent=1))
+        doc = config(a.output)
+        if a.hostfile:
+            from .hostfile import HostEntry, save_host_entries
+            save_host_entries(a.hostfile, [HostEntry(a.ssh, [], len(doc["gpus"]) or None,
+                                                     bool(doc["fully_connected"]))])
+        print(json.dumps(doc, indent=1))
         return 0
     cmd = a.command[1:] if a.command and a.command[0] == "--" else a.command
     if not cmd:
         ap.error("launch needs a command after --")
-    if a.hosts:
-        hosts = [h for h in a.hosts.split(",") if h]
+    if a.hosts or a.hostfile:
+        from .hostfile import resolve_hosts
+        try:
+            entries = resolve_hosts(a.hosts or None, a.hostfile)
+        except ValueError as e:
+            ap.error(str(e))
+        per_host = a.nproc or min((e.gpus for e in entries if e.gpus), default=8)
         backend = "nccl" if a.backend == "auto" else resolve_backend(a.backend, True)
-        return launch_hosts(cmd, hosts, a.nproc or 8, backend, a.port, parse_env_args(a.env), a.cwd,
-                            dry_run=a.dry_run)
+        return launch_hosts(cmd, [e.ssh for e in entries], per_host, backend, a.port,
+                            parse_env_args(a.env), a.cwd, dry_run=a.dry_run,
+                            coordinator=entries[0].address())
     import torch
     n = a.nproc or max(1, torch.cuda.device_count())
     backend = resolve_backend(a.backend, torch.cuda.is_available())

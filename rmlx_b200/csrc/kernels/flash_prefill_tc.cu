@@ -1,5 +1,6 @@
 // Paged causal flash attention for prompt processing on the 5th-generation tensor cores
-// (head_dim 128, no sliding window; other shapes use the mma.sync kernel in flash_prefill.cu).
+// (head_dim 128, optional sliding window; other head dimensions use the mma.sync kernel in
+// flash_prefill.cu).
 //
 // A CTA owns LANES (1 or 2) tiles of 128 query tokens of one query head and walks the keys 64 at a
 // time; the K and V tiles of a step serve every lane. A kernel that allocates tensor memory gets one
@@ -63,6 +64,7 @@ struct TcParams {
   const int* block_table;   // this sequence's pages
   __nv_bfloat16* out;       // [T, Hq, 128]
   int T, Hq, Hkv, pos0, n_qt;
+  int window;               // > 0: a query sees only its last `window` keys
   float scale_log2;
   int* status;
 };
@@ -103,14 +105,17 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
   const int qt = p.n_qt - 1 - int(blockIdx.x) / p.Hq, h = int(blockIdx.x) % p.Hq;
   const int kvh = h / (p.Hq / p.Hkv);
   const int q0 = qt * (kTcRows * LANES);
-  // steps of lane L: it sees keys [0, kv_end_L); a lane that starts past the last token is idle
+  // steps of lane L: it sees keys [0, kv_end_L); a lane that starts past the last token is idle.
+  // With a sliding window the block's steps start at j0, the step that holds the first key its
+  // first row can see (later rows mask what lies before their own window).
+  const int j0 = p.window > 0 ? max(0, p.pos0 + q0 - p.window + 1) / kTcKeys : 0;
   int n_steps[LANES];
   int n_max = 0, kv_end_max = 1;
 #pragma unroll
   for (int L = 0; L < LANES; ++L) {
     const int first = q0 + L * kTcRows;
     const int kv_end = p.pos0 + min(first + kTcRows - 1, p.T - 1) + 1;
-    n_steps[L] = first < p.T ? (kv_end + kTcKeys - 1) / kTcKeys : 0;
+    n_steps[L] = first < p.T ? (kv_end + kTcKeys - 1) / kTcKeys - j0 : 0;
     if (n_steps[L] > 0) { n_max = max(n_max, n_steps[L]); kv_end_max = max(kv_end_max, kv_end); }
   }
   const int last_page = (kv_end_max - 1) / kTcPage;
@@ -171,7 +176,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
         for (int pg = 0; pg < kTcPages; ++pg) {
           // pages past the last one this CTA can see repeat it (their keys are masked)
-          const int page = min(j * kTcPages + pg, last_page);
+          const int page = min((j + j0) * kTcPages + pg, last_page);
           y[pg] = (p.block_table[page] * p.Hkv + kvh) * kTcPage;
         }
         if (!mbar_wait(k_free + s, par, abort_flag)) break;
@@ -301,7 +306,7 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free + sb);         // the issuer may overwrite this S now
 
-      const int k0 = j * kTcKeys;
+      const int k0 = (j + j0) * kTcKeys;
       if (k0 + kTcKeys - 1 > p.pos0 + lane_q0) {       // the step touches the diagonal
         const int vis = pos - k0;                      // keys k0 .. k0+vis are visible to this row
 #pragma unroll
@@ -309,6 +314,14 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q,
 #pragma unroll
           for (int i = 0; i < 32; ++i)
             if (c * 32 + i > vis) r[c][i] = 0xff800000u;   // -inf
+      }
+      if (p.window > 0 && pos - p.window + 1 > k0) {   // keys before this row's window
+        const int lo = pos - p.window + 1 - k0;        // keys k0 .. k0+lo-1 are out of the window
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < lo) r[c][i] = 0xff800000u;
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -421,20 +434,21 @@ static int launch_prefill_tc(const CUtensorMap& tq, const CUtensorMap& tk, const
 
 using namespace rb;
 
-// 1 when the tensor-core kernel covers the shape (head_dim 128, no sliding window).
+// 1 when the tensor-core kernel covers the shape (head_dim 128; any sliding window).
 extern "C" int rmlx_flash_prefill_tc_supported(int HD, int window) {
-  return HD == kTcHd && window <= 0;
+  (void)window;
+  return HD == kTcHd;
 }
 
 // q, out: [T, Hq, 128] bf16; caches [num_blocks, Hkv, 16, 128] bf16; block_table: the sequence's
 // pages (int32, device); queries sit at positions pos0 .. pos0+T-1 and the cache already holds keys
-// 0 .. pos0+T-1. lanes: query tiles per CTA, 1 or 2 (0 = choose; one tile measured at least as
+// 0 .. pos0+T-1. window > 0: sliding-window attention over the last `window` keys. lanes: query tiles per CTA, 1 or 2 (0 = choose; one tile measured at least as
 // fast as two at every length tried, so that is the choice). status: optional device int set
 // non-zero if a pipeline wait gave up.
 extern "C" int rmlx_flash_prefill_tc(const void* q, const void* k_cache, const void* v_cache,
                                      const int* block_table, void* out, int T, int Hq, int Hkv,
-                                     int HD, int num_blocks, int pos0, float scale, int lanes,
-                                     int* status, int pdl, cudaStream_t st) {
+                                     int HD, int num_blocks, int pos0, int window, float scale,
+                                     int lanes, int* status, int pdl, cudaStream_t st) {
   if (T < 1 || HD != kTcHd || Hkv < 1 || Hq % Hkv || pos0 < 0 || num_blocks < 1) return -2;
   if (lanes == 0) lanes = 1;
   if (lanes != 1 && lanes != 2) return -2;
@@ -455,6 +469,7 @@ extern "C" int rmlx_flash_prefill_tc(const void* q, const void* k_cache, const v
   p.out = static_cast<__nv_bfloat16*>(out);
   p.T = T; p.Hq = Hq; p.Hkv = Hkv; p.pos0 = pos0;
   p.n_qt = 0;
+  p.window = window > 0 ? window : 0;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   return lanes == 2 ? launch_prefill_tc<2>(tq, tk, tv, p, pdl, st)

@@ -1,5 +1,5 @@
 """Prompt-phase attention over the paged KV cache. Two kernels: the tcgen05 one
-(csrc/kernels/flash_prefill_tc.cu; head_dim 128, no sliding window) and the mma.sync one
+(csrc/kernels/flash_prefill_tc.cu; head_dim 128, optional sliding window) and the mma.sync one
 (csrc/kernels/flash_prefill.cu; every other shape). The decode-phase kernel is
 ``ops.decode.flash_decode_paged``. Counterpart of the reference's sdpa prefill kernels
 (crates/rmlx-core/src/ops/sdpa.rs:1873-2855), reading pages in place."""
@@ -17,7 +17,7 @@ from .gemm import GemmStatus
 _lib.register_cuda_sigs({
     "rmlx_flash_prefill_paged": ("pppppiiiiiifip", "i"),
     "rmlx_flash_prefill_tc_supported": ("ii", "i"),
-    "rmlx_flash_prefill_tc": ("pppppiiiiiifipip", "i"),
+    "rmlx_flash_prefill_tc": ("pppppiiiiiiifipip", "i"),
 })
 
 
@@ -56,7 +56,7 @@ def flash_prefill_paged(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     else:
         rc = _lib.cuda().rmlx_flash_prefill_tc(
             q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_row.data_ptr(),
-            out.data_ptr(), t, hq, k_cache.shape[1], d, k_cache.shape[0], pos0, scale,
+            out.data_ptr(), t, hq, k_cache.shape[1], d, k_cache.shape[0], pos0, int(window or 0), scale,
             int(os.environ.get("RMLX_FLASH_PREFILL_LANES", "0")),     # query tiles per CTA: 1, 2, 0 = choose
             GemmStatus.get(q.device).data_ptr(), int(pdl), _lib.stream_ptr())
     _lib.check(rc, "flash_prefill_paged")

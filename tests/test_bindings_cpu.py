@@ -120,7 +120,7 @@ def test_prefill_kernel_choice_is_a_host_decision(monkeypatch):
     lib = _cuda_lib()
     monkeypatch.delenv("RMLX_FLASH_PREFILL", raising=False)
     assert prefill_kernel_choice(128, 0) == "tc"
-    assert prefill_kernel_choice(64, 0) == "mma" and prefill_kernel_choice(128, 4096) == "mma"
+    assert prefill_kernel_choice(64, 0) == "mma" and prefill_kernel_choice(128, 4096) == "tc"
     monkeypatch.setenv("RMLX_FLASH_PREFILL", "mma")
     assert prefill_kernel_choice(128, 0) == "mma"
     assert lib.rmlx_qgemm_supported(4096) == 1 and lib.rmlx_qgemm_supported(4096 + 64) == 0

@@ -37,3 +37,37 @@ def test_launch_prefixes_output_and_fails_fast():
     rc = launch([sys.executable, "-c", prog], 3, backend="gloo", port=18998, sink=out)
     assert rc == 1 and time.time() - t0 < 20
     assert "rank 1 exited with 3" in out.getvalue()
+
+
+def test_hostfile_schema_round_trip_and_launch_plan(tmp_path):
+    import io
+    import json
+    from rmlx_b200.cli import main as cli
+    from rmlx_b200.cli.hostfile import (HostEntry, load_host_entries, resolve_hosts,
+                                        save_host_entries)
+    path = str(tmp_path / "hosts.json")
+    save_host_entries(path, [HostEntry("user@node0", ["10.0.0.1"], 2, True), HostEntry("node1")])
+    entries = load_host_entries(path)
+    assert [e.ssh for e in entries] == ["user@node0", "node1"]
+    assert entries[0].address() == "10.0.0.1" and entries[1].address() == "node1"
+    assert entries[0].gpus == 2 and entries[1].gpus is None
+    assert [e.ssh for e in resolve_hosts("a,b", None)] == ["a", "b"]
+    for bad in ([], [{"ips": []}], [{"ssh": "-oProxyCommand=x"}], [{"ssh": "n", "gpus": 0}],
+                [{"ssh": "n", "rdma": []}]):
+        with open(path, "w") as f:
+            json.dump(bad, f)
+        with pytest.raises(ValueError):
+            load_host_entries(path)
+    with pytest.raises(ValueError):
+        resolve_hosts("a", path)
+    with pytest.raises(ValueError):
+        resolve_hosts(None, None)
+    # the launcher takes the ranks per host and the coordinator address from the file
+    save_host_entries(path, [HostEntry("user@node0", ["10.0.0.1"], 2), HostEntry("node1", [], 2)])
+    buf = io.StringIO()
+    entries = load_host_entries(path)
+    rc = cli.launch_hosts(["python", "x.py"], [e.ssh for e in entries], 2, sink=buf, dry_run=True,
+                          coordinator=entries[0].address())
+    lines = buf.getvalue().strip().splitlines()
+    assert rc == 0 and len(lines) == 4
+    assert all("MASTER_ADDR=10.0.0.1" in ln for ln in lines) and "node1" in lines[2]

@@ -22,13 +22,15 @@ pytestmark = pytest.mark.gpu
 @pytest.mark.parametrize("kernel", ["tc", "mma"])
 @pytest.mark.parametrize("hd", [64, 128])
 @pytest.mark.parametrize("t,pos0,window", [(200, 0, 0), (64, 0, 0), (77, 37, 0), (300, 19, 50), (1, 130, 0),
-                                           (640, 100, 0), (1500, 0, 0)])
+                                           (640, 100, 0), (1500, 0, 0), (1500, 0, 200), (640, 100, 64),
+                                           (700, 333, 129)])
 def test_flash_prefill_matches_reference(dev, hd, t, pos0, window, kernel, monkeypatch):
-    """Both kernels against fp32 softmax(QK^T)V: the tcgen05 one covers head_dim 128 without a
-    window (several 128-key steps, partial pages, a tile that starts off the diagonal), the
-    mma.sync one everything else and, forced, the same shapes."""
+    """Both kernels against fp32 softmax(QK^T)V: the tcgen05 one covers head_dim 128 (several
+    key steps, partial pages, a tile that starts off the diagonal, sliding windows shorter and
+    longer than a step, rows whose first steps are entirely outside their window), the mma.sync
+    one everything else and, forced, the same shapes."""
     monkeypatch.setenv("RMLX_FLASH_PREFILL", kernel)
-    expect = "tc" if (kernel == "tc" and hd == 128 and window == 0) else "mma"
+    expect = "tc" if (kernel == "tc" and hd == 128) else "mma"
     assert prefill_kernel_choice(hd, window) == expect
     if kernel == "tc" and expect == "mma":
         pytest.skip("shape not covered by the tcgen05 kernel; the mma.sync case runs it")
