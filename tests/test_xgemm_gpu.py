@@ -20,7 +20,11 @@ def _w(n, k, quant, experts=0, seed=0):
     return LinearWeight.from_dense(torch.randn(*shape, generator=g) * 0.05, quant, device=DEV)
 
 
-def _rel(got, want):
+def _rel(got, want, fro_bound=5e-3):
+    """Maximum error over the reference's maximum; also asserts the relative Frobenius error (an
+    error confined to a few columns or one K block would pass a bound scaled by the global maximum)."""
+    fro = ((got.float() - want).norm() / want.norm().clamp_min(1e-12)).item()
+    assert fro <= fro_bound, f"relative Frobenius error {fro} > {fro_bound}"
     return (got.float() - want).abs().max().item() / max(want.abs().max().item(), 1e-6)
 
 
