@@ -19,6 +19,13 @@ from .weights import LinearWeight, W_Q4
 _MAXB = 4
 _Q4_PATH = os.environ.get("RMLX_Q4_PATH", "auto")
 _STREAM = os.environ.get("RMLX_DECODE_STREAM", "1") != "0"
+# which operations take the streaming kernels when streaming is on: any of qkv, gemv (O projection,
+# dense down projection, LM head), gate_up, moe_gate_up, moe_down (default: all)
+_STREAM_OPS = set(os.environ.get("RMLX_DECODE_STREAM_OPS", "qkv,gemv,gate_up,moe_gate_up,moe_down").split(","))
+
+
+def _stream(op: str) -> bool:
+    return _STREAM and op in _STREAM_OPS
 
 _lib.register_cuda_sigs({
     "rmlx_sg_status": ("", "i"),
@@ -86,7 +93,7 @@ def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = 
     # either way).
     mma_rows = (w.kind == W_Q4 and not w.scales_f16 and b >= 2 and q4_path() != "scalar" and
                 bool(lib.rmlx_qmv_mma_supported(k, min(8, b), 16)))
-    if _STREAM and not mma_rows:
+    if _stream("gemv") and not mma_rows:
         done = True
         for b0 in range(0, b, _MAXB):
             bb = min(_MAXB, b - b0)
@@ -135,7 +142,7 @@ def rms_gate_up_swiglu(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.
     if out is None:
         out = torch.empty(b, i, dtype=torch.bfloat16, device=x.device)
     lib, st = _lib.cuda(), _lib.stream_ptr()
-    if _STREAM:
+    if _stream("gate_up"):
         done = True
         for b0 in range(0, b, _MAXB):
             bb = min(_MAXB, b - b0)
@@ -242,7 +249,7 @@ def moe_gate_up(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor]
     i = w.n // 2
     if out is None:
         out = torch.zeros(b * top_k, i, dtype=torch.bfloat16, device=x.device)
-    if _STREAM:
+    if _stream("moe_gate_up"):
         rc = _lib.cuda().rmlx_sg_moe_gate_up(*_wargs(w), x.data_ptr(), x.stride(0), _lib.ptr(norm_w),
                                              eps, idx.data_ptr(), out.data_ptr(), out.stride(0), b,
                                              top_k, i, k, expert_base, w.experts, int(pdl),
@@ -273,7 +280,7 @@ def moe_down(act: torch.Tensor, w: LinearWeight, idx: torch.Tensor, wts: torch.T
     n, i = w.n, w.k
     if out is None:
         out = torch.empty(b, n, dtype=out_dtype, device=act.device)
-    if _STREAM:
+    if _stream("moe_down"):
         rc = _lib.cuda().rmlx_sg_moe_down(*_wargs(w), act.data_ptr(), act.stride(0), idx.data_ptr(),
                                           wts.data_ptr(), _lib.ptr(residual),
                                           0 if residual is None else residual.stride(0),
@@ -484,7 +491,7 @@ def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor
         # without an explicit map, row r of this launch is sequence b0 + r: shift the table instead
         bt = block_table if row_seq is not None else block_table[b0:]
         rs = None if row_seq is None else row_seq[b0:]
-        fn = _lib.cuda().rmlx_sg_rms_qkv_rope if _STREAM else None
+        fn = _lib.cuda().rmlx_sg_rms_qkv_rope if _stream("qkv") else None
         if fn is not None:
             rc = fn(w.kernel_kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
                     xs.stride(0), _lib.ptr(norm_w), eps, qs.data_ptr(), k_cache.data_ptr(),
