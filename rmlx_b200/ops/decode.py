@@ -19,13 +19,20 @@ from .weights import LinearWeight, W_Q4
 _MAXB = 4
 _Q4_PATH = os.environ.get("RMLX_Q4_PATH", "auto")
 _STREAM = os.environ.get("RMLX_DECODE_STREAM", "1") != "0"
-# which operations take the streaming kernels when streaming is on: any of qkv, gemv (O projection,
-# dense down projection, LM head), gate_up, moe_gate_up, moe_down (default: all)
-_STREAM_OPS = set(os.environ.get("RMLX_DECODE_STREAM_OPS", "qkv,gemv,gate_up,moe_gate_up,moe_down").split(","))
+# Which operations take the streaming kernels when streaming is on: any of qkv, gemv (O projection,
+# dense down projection, LM head), gate_up, moe_gate_up, moe_down. Measured inside the captured
+# step of the 60-layer model (4-bit weights, one GPU, us per layer; per-row kernels everywhere:
+# 82.6): streaming the expert down projection saves 3.2, the expert gate/up 3.2, while streaming
+# the merged QKV costs 1.3 and the O projection / LM head 2.7 (their per-row kernels request the
+# first rows before the dependency wait and have less to set up). Hence the default below; 8-bit
+# weights and fp16 scales exist only in the streaming kernels and always take them.
+_STREAM_OPS = set(os.environ.get("RMLX_DECODE_STREAM_OPS", "gate_up,moe_gate_up,moe_down").split(","))
 
 
-def _stream(op: str) -> bool:
-    return _STREAM and op in _STREAM_OPS
+def _stream(op: str, w: Optional[LinearWeight] = None) -> bool:
+    if not _STREAM:
+        return False
+    return op in _STREAM_OPS or (w is not None and (w.kind == 2 or w.scales_f16))
 
 _lib.register_cuda_sigs({
     "rmlx_sg_status": ("", "i"),
@@ -45,9 +52,21 @@ def stream_enabled() -> bool:
     return _STREAM
 
 
-def set_stream(on: bool) -> None:
-    global _STREAM
+ALL_STREAM_OPS = ("qkv", "gemv", "gate_up", "moe_gate_up", "moe_down")
+_DEFAULT_STREAM_OPS = set(_STREAM_OPS)
+
+
+def set_stream(on: bool, ops=None) -> None:
+    """Switch the streaming kernels on or off; ``ops``: which operations take them ("all", an
+    iterable of names from ``ALL_STREAM_OPS``, or None for the default selection)."""
+    global _STREAM, _STREAM_OPS
     _STREAM = bool(on)
+    if ops == "all":
+        _STREAM_OPS = set(ALL_STREAM_OPS)
+    elif ops is None:
+        _STREAM_OPS = set(_DEFAULT_STREAM_OPS)
+    else:
+        _STREAM_OPS = set(ops)
 
 
 def stream_status() -> int:
@@ -93,7 +112,7 @@ def rms_gemv(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor] = 
     # either way).
     mma_rows = (w.kind == W_Q4 and not w.scales_f16 and b >= 2 and q4_path() != "scalar" and
                 bool(lib.rmlx_qmv_mma_supported(k, min(8, b), 16)))
-    if _stream("gemv") and not mma_rows:
+    if _stream("gemv", w) and not mma_rows:
         done = True
         for b0 in range(0, b, _MAXB):
             bb = min(_MAXB, b - b0)
@@ -142,7 +161,7 @@ def rms_gate_up_swiglu(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.
     if out is None:
         out = torch.empty(b, i, dtype=torch.bfloat16, device=x.device)
     lib, st = _lib.cuda(), _lib.stream_ptr()
-    if _stream("gate_up"):
+    if _stream("gate_up", w):
         done = True
         for b0 in range(0, b, _MAXB):
             bb = min(_MAXB, b - b0)
@@ -249,7 +268,7 @@ def moe_gate_up(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor]
     i = w.n // 2
     if out is None:
         out = torch.zeros(b * top_k, i, dtype=torch.bfloat16, device=x.device)
-    if _stream("moe_gate_up"):
+    if _stream("moe_gate_up", w):
         rc = _lib.cuda().rmlx_sg_moe_gate_up(*_wargs(w), x.data_ptr(), x.stride(0), _lib.ptr(norm_w),
                                              eps, idx.data_ptr(), out.data_ptr(), out.stride(0), b,
                                              top_k, i, k, expert_base, w.experts, int(pdl),
@@ -280,7 +299,7 @@ def moe_down(act: torch.Tensor, w: LinearWeight, idx: torch.Tensor, wts: torch.T
     n, i = w.n, w.k
     if out is None:
         out = torch.empty(b, n, dtype=out_dtype, device=act.device)
-    if _stream("moe_down"):
+    if _stream("moe_down", w):
         rc = _lib.cuda().rmlx_sg_moe_down(*_wargs(w), act.data_ptr(), act.stride(0), idx.data_ptr(),
                                           wts.data_ptr(), _lib.ptr(residual),
                                           0 if residual is None else residual.stride(0),
@@ -491,7 +510,7 @@ def rms_qkv_rope(x: torch.Tensor, w: LinearWeight, norm_w: Optional[torch.Tensor
         # without an explicit map, row r of this launch is sequence b0 + r: shift the table instead
         bt = block_table if row_seq is not None else block_table[b0:]
         rs = None if row_seq is None else row_seq[b0:]
-        fn = _lib.cuda().rmlx_sg_rms_qkv_rope if _stream("qkv") else None
+        fn = _lib.cuda().rmlx_sg_rms_qkv_rope if _stream("qkv", w) else None
         if fn is not None:
             rc = fn(w.kernel_kind, w.w.data_ptr(), _lib.ptr(w.scales), _lib.ptr(w.biases), xs.data_ptr(),
                     xs.stride(0), _lib.ptr(norm_w), eps, qs.data_ptr(), k_cache.data_ptr(),

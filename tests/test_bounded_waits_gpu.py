@@ -22,7 +22,7 @@ def test_dropped_ring_stage_expires_and_next_launch_is_clean(dev, quant):
     n, k = 4096, 1024
     w = LinearWeight.from_dense(torch.randn(n, k) * 0.02, quant, device=dev)
     x = torch.randn(1, k, device=dev).to(torch.bfloat16)
-    D.set_stream(True)
+    D.set_stream(True, ops="all")
     want = x.float() @ w.dequantized().t()
     assert D.stream_status() == 0
     _lib.cuda().rmlx_sg_debug_drop_stage(0)           # block 0 never receives its first stage
@@ -35,6 +35,7 @@ def test_dropped_ring_stage_expires_and_next_launch_is_clean(dev, quant):
     torch.cuda.synchronize()
     assert D.stream_status() == 0
     assert (got.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item()
+    D.set_stream(True)                                # back to the default selection of operations
 
 
 def test_peer_word_that_is_never_written_expires(dev):

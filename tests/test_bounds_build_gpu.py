@@ -32,6 +32,7 @@ q = torch.empty(1, hq, hd, dtype=torch.bfloat16, device=dev)
 pos_ok = torch.tensor([5], dtype=torch.int32, device=dev)
 pos_bad = torch.tensor([70], dtype=torch.int32, device=dev)      # block column 4 of a 4-column table
 
+D.set_stream(True, ops="all")
 assert _lib.cuda().rmlx_bounds_build() == 1
 assert _lib.bounds_status() is None
 
@@ -52,7 +53,7 @@ qkv(pos_bad)
 rec = _lib.bounds_status()
 assert rec is not None and rec[0] == "decode_qkv_rope.cu" and rec[2:] == (4, 4), rec
 assert float(kc.abs().sum()) == 0
-D.set_stream(True)
+D.set_stream(True, ops="all")
 
 flat = torch.randn(1, (hq + 2 * hkv) * hd, device=dev, generator=g).to(torch.bfloat16)
 D.rope_kv_write(flat, q, kc, vc, bt, pos_bad, cos, sin, hq, hkv)

@@ -16,7 +16,7 @@ pytestmark = pytest.mark.gpu
 @pytest.fixture(autouse=True, params=["stream", "mma", "scalar"])
 def q4_path(request):
     """Every test runs on the weight-streaming kernels and on both per-row Q4 implementations."""
-    D.set_stream(request.param == "stream")
+    D.set_stream(request.param == "stream", ops="all")     # every projection on the streaming kernels
     D.set_q4_path("auto" if request.param == "stream" else request.param)
     yield request.param
     D.set_q4_path("auto")
