@@ -50,6 +50,7 @@ class Group:
         single-rank group)."""
         self._pg = pg
         self._pc = None
+        self._chan = None
         self.native_calls = 0
         self.library_calls = 0
         if dist.is_available() and dist.is_initialized():
@@ -98,11 +99,29 @@ class Group:
         self.native_calls += 1
         return self._pc
 
+    def enable_native_p2p(self, slot_bytes: int, device=None) -> None:
+        """Collective: create the mailboxes that let ``send`` / ``recv`` / ``sendrecv`` of CUDA
+        tensors up to ``slot_bytes`` run as peer stores plus counters (``parallel.p2p.PeerChannel``)
+        instead of library point-to-point calls."""
+        if self.single or self._chan is not None:
+            return
+        from .p2p import PeerChannel
+        self._chan = PeerChannel(slot_bytes, group=self._pg, device=device)
+
+    def _p2p(self, t: torch.Tensor):
+        if self._chan is None or not t.is_cuda or t.numel() * t.element_size() > self._chan.slot_bytes:
+            return None
+        self.native_calls += 1
+        return self._chan
+
     def close(self) -> None:
-        """Release the native communicator (collective)."""
+        """Release the native communicators (collective)."""
         if self._pc is not None:
             self._pc.close()
             self._pc = None
+        if self._chan is not None:
+            self._chan.close()
+            self._chan = None
 
     # ------------------------------------------------------------------ collectives
     def allreduce(self, t: torch.Tensor, op: ReduceOp = ReduceOp.SUM) -> torch.Tensor:
@@ -201,17 +220,29 @@ class Group:
     def send(self, t: torch.Tensor, dst: int) -> None:
         if self.single:
             raise DistributedError("send on a single-rank group")
+        ch = self._p2p(t)
+        if ch is not None:
+            return ch.send(t, dst)
+        self.library_calls += 1
         dist.send(t.contiguous(), dst=self._global(dst), group=self._pg)
 
     def recv(self, t: torch.Tensor, src: int) -> torch.Tensor:
         if self.single:
             raise DistributedError("recv on a single-rank group")
+        ch = self._p2p(t)
+        if ch is not None and t.is_contiguous():
+            return ch.recv(t, src)
+        self.library_calls += 1
         dist.recv(t, src=self._global(src), group=self._pg)
         return t
 
     def sendrecv(self, send: torch.Tensor, recv: torch.Tensor, peer: int) -> torch.Tensor:
         if self.single:
             raise DistributedError("sendrecv on a single-rank group")
+        ch = self._p2p(send)
+        if ch is not None and recv.is_contiguous() and self._p2p(recv) is not None:
+            return ch.sendrecv(send, recv, peer)
+        self.library_calls += 1
         ops = [dist.P2POp(dist.isend, send.contiguous(), self._global(peer), self._pg),
                dist.P2POp(dist.irecv, recv, self._global(peer), self._pg)]
         for r in dist.batch_isend_irecv(ops):

@@ -85,6 +85,32 @@ def _worker(rank, world, port, ret):
         want_odd = odd.clone(); dist.all_reduce(want_odd)
         if not torch.allclose(grp.allreduce(odd), want_odd) or grp.library_calls != 1:
             bad.append(("group fallback", grp.library_calls))
+        # point-to-point over the heap: a ring of messages, three rounds (slots and counters recycle)
+        grp.enable_native_p2p(1 << 16)
+        nxt, prv = (rank + 1) % world, (rank - 1) % world
+        before = grp.native_calls
+        for rnd in range(3):
+            msg = torch.full((1000,), float(100 * rnd + rank), device=dev)
+            got = grp.sendrecv(msg, torch.empty_like(msg), nxt) if world == 2 else None
+            if world == 2:
+                if not torch.all(got == float(100 * rnd + prv)):
+                    bad.append(("group.sendrecv", rnd))
+            else:
+                grp.send(msg, nxt)
+                got = grp.recv(torch.empty_like(msg), prv)
+                if not torch.all(got == float(100 * rnd + prv)):
+                    bad.append(("group.send/recv", rnd))
+        if grp.native_calls == before:
+            bad.append(("p2p went to the library",))
+        ch = grp._chan
+        ch.put(nxt, torch.full((64,), float(rank + 7), device=dev), slot=rank)   # one-sided
+        torch.cuda.synchronize()
+        dist.barrier()
+        peek = ch.get(rank, torch.empty(64, device=dev), slot=prv)
+        if not torch.all(peek == float(prv + 7)):
+            bad.append(("put/get",))
+        if ch.status():
+            bad.append(("p2p status", ch.status()))
         grp.close()
         torch.cuda.synchronize()
         status = pc.status()
