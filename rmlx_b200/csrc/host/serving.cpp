@@ -33,7 +33,7 @@ constexpr int kOk = 0, kNoSeq = -1, kBad = -2, kOutOfBlocks = -3;
 class BlockManager {
  public:
   BlockManager(int num_blocks, int block_size, int reserved)
-      : block_size_(block_size), ref_(num_blocks, 0) {
+      : block_size_(block_size), reserved_(reserved), ref_(num_blocks, 0) {
     // hand out low block ids first (the free list is a stack with the lowest id on top)
     for (int b = num_blocks - 1; b >= reserved; --b) free_.push_back(b);
   }
@@ -133,6 +133,22 @@ class BlockManager {
     s.len = nl;
     return kOk;
   }
+  // Sliding-window sequences: release the pages that lie entirely before the last keep_tokens
+  // tokens. Their table entries become 0, the reserved page (attention with a window never reads
+  // them; positions keep indexing the table by pos / block_size). Returns the number released,
+  // or a negative code. Needs a reserved page.
+  int drop_front(int64_t seq, int keep_tokens) {
+    auto it = seqs_.find(seq);
+    if (it == seqs_.end()) return kNoSeq;
+    if (reserved_ < 1 || keep_tokens < 0) return kBad;
+    Seq& s = it->second;
+    const int first_needed = std::max(0, s.len - keep_tokens) / block_size_;
+    int n = 0;
+    for (int i = 0; i < first_needed && i < static_cast<int>(s.table.size()); ++i) {
+      if (s.table[i] >= reserved_) { drop(s.table[i]); s.table[i] = 0; ++n; }
+    }
+    return n;
+  }
   int free_sequence(int64_t seq) {
     auto it = seqs_.find(seq);
     if (it == seqs_.end()) return kOk;       // freeing an unknown sequence is a no-op
@@ -156,9 +172,11 @@ class BlockManager {
     return b;
   }
   void drop(int b) {
+    if (b < reserved_) return;               // a released front page (entry 0) holds no reference
     if (--ref_[b] == 0) free_.push_back(b);
   }
   int block_size_;
+  int reserved_;
   std::vector<int> ref_;
   std::vector<int> free_;
   std::unordered_map<int64_t, Seq> seqs_;
@@ -443,6 +461,7 @@ int rmlx_bm_adopt(void* h, int64_t seq, const int* blocks, int n, int tokens) {
 int rmlx_bm_retain(void* h, int block) { return BM(h)->retain(block); }
 int rmlx_bm_release(void* h, int block) { return BM(h)->release(block); }
 int rmlx_bm_trim(void* h, int64_t seq, int n) { return BM(h)->trim(seq, n); }
+int rmlx_bm_drop_front(void* h, int64_t seq, int keep) { return BM(h)->drop_front(seq, keep); }
 int rmlx_bm_free_sequence(void* h, int64_t seq) { return BM(h)->free_sequence(seq); }
 int rmlx_bm_ref_count(void* h, int block) { return BM(h)->ref_count(block); }
 // Block table of seq into out (at most cap entries); returns its full length, -1 if unknown.

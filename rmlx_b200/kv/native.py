@@ -42,6 +42,7 @@ def _host():
             "rmlx_bm_retain": (c_int, [c_void_p, c_int]),
             "rmlx_bm_release": (c_int, [c_void_p, c_int]),
             "rmlx_bm_trim": (c_int, [c_void_p, c_int64, c_int]),
+            "rmlx_bm_drop_front": (c_int, [c_void_p, c_int64, c_int]),
             "rmlx_bm_free_sequence": (c_int, [c_void_p, c_int64]),
             "rmlx_bm_ref_count": (c_int, [c_void_p, c_int]),
             "rmlx_bm_table": (c_int, [c_void_p, c_int64, _IP, c_int]),
@@ -183,6 +184,14 @@ class NativeBlockManager:
     def trim(self, seq_id: int, num_tokens: int) -> None:
         if self._lib.rmlx_bm_trim(self._h, seq_id, num_tokens) != 0:
             raise KeyError(seq_id)
+
+    def drop_front(self, seq_id: int, keep_tokens: int) -> int:
+        n = self._lib.rmlx_bm_drop_front(self._h, seq_id, keep_tokens)
+        if n == -1:
+            raise KeyError(seq_id)
+        if n < 0:
+            raise ValueError("drop_front needs a reserved page and keep_tokens >= 0")
+        return n
 
     def free_sequence(self, seq_id: int) -> None:
         self._lib.rmlx_bm_free_sequence(self._h, seq_id)

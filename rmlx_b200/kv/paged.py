@@ -32,6 +32,7 @@ class BlockManager:
         target of idle batch rows in a shape-stable decode graph)."""
         self.num_blocks = num_blocks
         self.block_size = block_size
+        self.reserved = reserved
         self.free: List[int] = list(range(num_blocks - 1, reserved - 1, -1))
         self.ref = [0] * num_blocks
         self.tables: Dict[int, List[int]] = {}
@@ -74,6 +75,8 @@ class BlockManager:
         return b
 
     def _drop(self, b: int) -> None:
+        if b < self.reserved:                # a released front page (entry 0) holds no reference
+            return
         self.ref[b] -= 1
         if self.ref[b] == 0:
             self.free.append(b)
@@ -155,6 +158,25 @@ class BlockManager:
         while len(table) > keep:
             self._drop(table.pop())
         self.lengths[seq_id] = new
+
+    def drop_front(self, seq_id: int, keep_tokens: int) -> int:
+        """Sliding-window sequences: release the pages that lie entirely before the last
+        ``keep_tokens`` tokens; their table entries become 0, the reserved page. Returns how many
+        pages were released (the rotating cache of crates/rmlx-nn/src/attention.rs:970, as a page
+        policy)."""
+        if seq_id not in self.tables:
+            raise KeyError(seq_id)
+        if self.reserved < 1 or keep_tokens < 0:
+            raise ValueError("drop_front needs a reserved page and keep_tokens >= 0")
+        table = self.tables[seq_id]
+        first_needed = max(0, self.lengths[seq_id] - keep_tokens) // self.block_size
+        n = 0
+        for i in range(min(first_needed, len(table))):
+            if table[i] >= self.reserved:
+                self._drop(table[i])
+                table[i] = 0
+                n += 1
+        return n
 
     def free_sequence(self, seq_id: int) -> None:
         for b in self.tables.pop(seq_id, []):
@@ -316,6 +338,15 @@ class PagedKvCache:
     def trim(self, seq_id: int, num_tokens: int) -> None:
         self.manager.trim(seq_id, num_tokens)
         self._sync_slot(seq_id)
+
+    def drop_front(self, seq_id: int, window: int) -> int:
+        """A model with a sliding window of ``window`` tokens never reads older keys: give the
+        pages that lie entirely before the window back to the pool (the device table points at the
+        reserved zero page instead). Call it between steps; returns the pages released."""
+        n = self.manager.drop_front(seq_id, window)
+        if n:
+            self._sync_slot(seq_id)
+        return n
 
     # -------------------------------------------------------------- reference-style access
     def append(self, layer: int, seq_id: int, k: torch.Tensor, v: torch.Tensor, start: int) -> None:

@@ -50,6 +50,7 @@ class ServingEngine:
         self.prefix = prefix_cls(self.cache.block_size) if use_prefix_cache else None
         self._prompts: Dict[int, List[int]] = {}
         self.prefill_tokens = 0               # prompt tokens actually run (cached prefixes excluded)
+        self.released_pages = 0               # sliding-window models: pages returned to the pool
         self._engine = None
         self._bound: List[int] = []
         if model.device.type == "cuda":
@@ -157,8 +158,21 @@ class ServingEngine:
         return self.outputs
 
     # ------------------------------------------------------------------ decode back-ends
+    def _release_outside_window(self, ids: List[int]) -> None:
+        """Sliding-window models: pages that lie entirely before the window go back to the pool
+        (checked when a sequence crosses a page boundary). Prefix-cached pages keep their own
+        reference, so only this sequence's hold on them is dropped."""
+        window = self.model.cfg.sliding_window or 0
+        if window <= 0:
+            return
+        bs = self.cache.block_size
+        for s in ids:
+            if self.cache.seq_len(s) % bs == 0 and self.cache.seq_len(s) > window + bs:
+                self.released_pages += self.cache.drop_front(s, window)
+
     def _decode(self, ids: List[int]) -> List[int]:
         dev = self.model.device
+        self._release_outside_window(ids)
         # the device engines compute full-vocabulary logits unless the LM head is sharded
         on_device = self._engine is not None and (self.greedy or self.model.layout.world == 1)
         if on_device:

@@ -205,3 +205,38 @@ def test_paged_cache_uses_native_manager_by_default():
     assert cache.seq_len(3) == 10 and cache.manager.num_free_blocks() == 6
     cache.free_sequence(3)
     assert cache.manager.num_free_blocks() == 7
+
+
+def test_drop_front_releases_pages_before_the_window_in_both_managers():
+    """Sliding-window sequences give back the pages that lie entirely before the window; both block
+    managers agree on tables, free counts and what freeing the sequence returns."""
+    from rmlx_b200.kv import native
+    from rmlx_b200.kv.paged import BlockManager
+    mgrs = [BlockManager(12, 16, reserved=1)]
+    if native.available():
+        mgrs.append(native.NativeBlockManager(12, 16, 1))
+    states = []
+    for m in mgrs:
+        m.add_sequence(5)
+        m.reserve(5, 100)
+        m.commit(5, 100)                       # 7 pages
+        assert m.num_free_blocks() == 11 - 7
+        assert m.drop_front(5, 200) == 0       # the window still covers everything
+        n = m.drop_front(5, 40)                # tokens 60..99 stay: pages 0..2 go (3*16 = 48 <= 60)
+        table = list(m.block_table(5))
+        assert n == 3 and table[:3] == [0, 0, 0] and all(b > 0 for b in table[3:])
+        assert m.num_free_blocks() == 11 - 4
+        assert m.drop_front(5, 40) == 0        # idempotent
+        m.fork(5, 6)                           # shared pages: released entries carry no reference
+        m.free_sequence(5)
+        assert m.num_free_blocks() == 11 - 4
+        m.free_sequence(6)
+        assert m.num_free_blocks() == 11
+        states.append(table)
+        with pytest.raises(KeyError):
+            m.drop_front(99, 1)
+    assert all(s == states[0] for s in states)
+    unreserved = BlockManager(4, 16, reserved=0)
+    unreserved.add_sequence(0)
+    with pytest.raises(ValueError):
+        unreserved.drop_front(0, 1)

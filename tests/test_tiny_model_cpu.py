@@ -128,3 +128,31 @@ def test_deepseek_paged_latent_decode_matches_the_contiguous_cache():
         got[0].append(int(t[0])); got[1].append(int(t[1]))
         t = m.decode_paged(t, pc, [0, 1]).argmax(-1)
     assert got == want
+
+
+def test_sliding_window_model_keeps_generating_after_old_pages_are_released():
+    """A model with a sliding window never reads keys before the window, so releasing their pages
+    between steps (the rotating cache as a page policy) changes nothing."""
+    from rmlx_b200.config import tiny_dense_config
+    from rmlx_b200.models.transformer import TransformerModel
+    from rmlx_b200.models.weights import from_state_dict, random_state_dict
+    cfg = tiny_dense_config().replace(sliding_window=24)
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    prompt = torch.randint(0, cfg.vocab_size, (70,), generator=torch.Generator().manual_seed(3))
+
+    def run(release):
+        cache = model.new_cache(12, max_seqs=1)
+        cache.add_sequence(0)
+        lg = model.forward(prompt, cache, [0], last_only=True)
+        toks, freed = [], 0
+        for _ in range(10):
+            toks.append(int(lg[0].argmax()))
+            if release:
+                freed += cache.drop_front(0, cfg.sliding_window)
+            lg = model.forward(torch.tensor([toks[-1]]), cache, [0], last_only=True)
+        return toks, freed, cache.manager.num_free_blocks()
+
+    plain, _, free_plain = run(False)
+    rotated, freed, free_rot = run(True)
+    assert rotated == plain
+    assert freed >= 2 and free_rot == free_plain + freed
