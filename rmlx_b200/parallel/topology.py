@@ -49,6 +49,30 @@ class Topology:
         return json.dumps({"gpus": [g.__dict__ for g in self.gpus], "peer": self.peer,
                            "link": self.link})
 
+    # The device-matrix file: what rank i uses to reach rank j, written once by ``config`` and read
+    # by every rank at start-up instead of probing again (the reference keeps a rank x rank table
+    # of RDMA device names, crates/rmlx-rdma/src/device_file.rs:1-150; here an entry is the link
+    # label between two GPUs and whether peer mapping works).
+    def save(self, path: str) -> None:
+        with open(path, "w") as f:
+            f.write(self.to_json())
+
+    @staticmethod
+    def load(path: str) -> "Topology":
+        with open(path) as f:
+            doc = json.load(f)
+        n = len(doc.get("gpus", []))
+        peer, link = doc.get("peer", []), doc.get("link", [])
+        if len(peer) != n or any(len(r) != n for r in peer) or (link and (len(link) != n or any(len(r) != n for r in link))):
+            raise ValueError("device matrix file: peer / link tables must be rank x rank")
+        if any(peer[i][i] is not True for i in range(n)):
+            raise ValueError("device matrix file: a device must reach itself")
+        return Topology([GpuInfo(**g) for g in doc["gpus"]], [[bool(v) for v in r] for r in peer],
+                        [[str(v) for v in r] for r in link])
+
+    def reachable(self, i: int, j: int) -> bool:
+        return bool(self.peer[i][j])
+
 
 def parse_topo_matrix(text: str) -> List[List[str]]:
     """Rows ``GPUi  X  NV18 ...`` of ``nvidia-smi topo -m`` -> matrix of link labels."""

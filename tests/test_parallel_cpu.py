@@ -324,3 +324,21 @@ def test_symmetric_heap_offset_arena_is_deterministic_and_coalesces():
     with pytest.raises(ValueError):
         a.give(100, 50)                     # a range that is already free
     assert a.free_bytes() + 256 + 300 == a.capacity
+
+
+def test_device_matrix_file_round_trip(tmp_path):
+    from rmlx_b200.parallel.topology import GpuInfo, Topology
+    t = Topology([GpuInfo(0, "B200", 1 << 30, 18), GpuInfo(1, "B200", 1 << 30, 18)],
+                 [[True, True], [True, True]], [["X", "NV18"], ["NV18", "X"]])
+    path = str(tmp_path / "devices.json")
+    t.save(path)
+    back = Topology.load(path)
+    assert back.num_gpus == 2 and back.fully_connected() and back.all_nvlink() and back.reachable(0, 1)
+    assert back.gpus[1].nvlink_links == 18 and back.link == t.link
+    import json
+    doc = json.loads(t.to_json())
+    doc["peer"] = [[True, True]]
+    with open(path, "w") as f:
+        json.dump(doc, f)
+    with pytest.raises(ValueError):
+        Topology.load(path)
