@@ -326,3 +326,77 @@ extern "C" int rmlx_bounds_status(int* out4, char* file, int file_len) {
   return -3;
 #endif
 }
+
+// ---- AWQ / GPTQ 4-bit checkpoints -> fp32 [out, in] (exact: a small integer times an fp16) ------
+// AWQ: qweight int32 [in, out/8], qzeros int32 [in/g, out/8], scales fp16 [in/g, out]; logical
+// output j of a word is nibble {0, 4, 1, 5, 2, 6, 3, 7}[j]; w = (q - z) * s
+// (crates/rmlx-core/src/ops/quantized.rs:707, awq_dequant_f32).
+// GPTQ: qweight int32 [in/8, out] (nibble j of a word is input 8*iw + j), qzeros int32
+// [groups, out/8] (stored zero + 1 is the zero point), scales fp16 [groups, out], g_idx [in] (or
+// null: consecutive groups); w = (q - (z + 1)) * s (quantized.rs:749, gptq_dequant_f32).
+namespace rb {
+
+__global__ void __launch_bounds__(256)
+awq_dequant_kernel(const uint32_t* __restrict__ qweight, const uint32_t* __restrict__ qzeros,
+                   const __half* __restrict__ scales, float* __restrict__ out, int in_f,
+                   int out_f, int group) {
+  const int out8 = out_f >> 3;
+  const long long idx = blockIdx.x * 256LL + threadIdx.x;      // (ob, i): i fastest -> coalesced stores
+  if (idx >= 1LL * in_f * out8) return;
+  const int i = int(idx % in_f), ob = int(idx / in_f);
+  const int g = i / group;
+  const uint32_t w = qweight[size_t(i) * out8 + ob], z = qzeros[size_t(g) * out8 + ob];
+  const int order[8] = {0, 4, 1, 5, 2, 6, 3, 7};
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int q = int((w >> (4 * order[j])) & 0xFu) - int((z >> (4 * order[j])) & 0xFu);
+    const float s = __half2float(scales[size_t(g) * out_f + ob * 8 + j]);
+    out[size_t(ob * 8 + j) * in_f + i] = float(q) * s;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+gptq_dequant_kernel(const uint32_t* __restrict__ qweight, const uint32_t* __restrict__ qzeros,
+                    const __half* __restrict__ scales, const int* __restrict__ g_idx,
+                    float* __restrict__ out, int in_f, int out_f, int groups) {
+  const int in8 = in_f >> 3, out8 = out_f >> 3;
+  const long long idx = blockIdx.x * 256LL + threadIdx.x;      // (iw, o): o fastest -> coalesced loads
+  if (idx >= 1LL * in8 * out_f) return;
+  const int o = int(idx % out_f), iw = int(idx / out_f);
+  const uint32_t w = qweight[size_t(iw) * out_f + o];
+  const int per_group = in_f / groups;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int i = iw * 8 + j;
+    const int g = g_idx ? g_idx[i] : i / per_group;
+    const int z = int((qzeros[size_t(g) * out8 + (o >> 3)] >> (4 * (o & 7))) & 0xFu) + 1;
+    v[j] = float(int((w >> (4 * j)) & 0xFu) - z) * __half2float(scales[size_t(g) * out_f + o]);
+  }
+  float4* dst = reinterpret_cast<float4*>(out + size_t(o) * in_f + iw * 8);
+  dst[0] = make_float4(v[0], v[1], v[2], v[3]);
+  dst[1] = make_float4(v[4], v[5], v[6], v[7]);
+}
+
+}  // namespace rb
+
+extern "C" int rmlx_awq_dequant(const void* qweight, const void* qzeros, const void* scales, void* out,
+                                int in_f, int out_f, int group, cudaStream_t st) {
+  if (in_f < 1 || out_f < 8 || out_f % 8 || group < 1 || in_f % group) return -2;
+  const long long n = 1LL * in_f * (out_f / 8);
+  rb::awq_dequant_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(
+      static_cast<const uint32_t*>(qweight), static_cast<const uint32_t*>(qzeros),
+      static_cast<const __half*>(scales), static_cast<float*>(out), in_f, out_f, group);
+  return static_cast<int>(cudaGetLastError());
+}
+
+extern "C" int rmlx_gptq_dequant(const void* qweight, const void* qzeros, const void* scales,
+                                 const int* g_idx, void* out, int in_f, int out_f, int groups,
+                                 cudaStream_t st) {
+  if (in_f < 8 || in_f % 8 || out_f < 8 || out_f % 8 || groups < 1 || in_f % groups) return -2;
+  const long long n = 1LL * (in_f / 8) * out_f;
+  rb::gptq_dequant_kernel<<<unsigned((n + 255) / 256), 256, 0, st>>>(
+      static_cast<const uint32_t*>(qweight), static_cast<const uint32_t*>(qzeros),
+      static_cast<const __half*>(scales), g_idx, static_cast<float*>(out), in_f, out_f, groups);
+  return static_cast<int>(cudaGetLastError());
+}

@@ -94,8 +94,39 @@ def _unpack_int32_nibbles(t: torch.Tensor) -> torch.Tensor:
     return (w[..., None] >> (torch.arange(8, dtype=torch.int64, device=t.device) * 4)) & 0xF
 
 
+def _native_4bit_dequant(kind: str, qweight, qzeros, scales, group_size=None, g_idx=None):
+    """fp32 [out, in] on the device kernels (csrc/kernels/misc.cu) for CUDA checkpoints with fp16
+    scales; None when the inputs do not qualify (the torch formulas below are the oracle)."""
+    if not (qweight.is_cuda and scales.dtype == torch.float16 and qweight.dtype == torch.int32
+            and qzeros.dtype == torch.int32):
+        return None
+    from .. import _lib
+    _lib.register_cuda_sigs({"rmlx_awq_dequant": ("ppppiiip", "i"),
+                             "rmlx_gptq_dequant": ("pppppiiip", "i")})
+    lib, st = _lib.cuda(), _lib.stream_ptr()
+    qweight, qzeros, scales = qweight.contiguous(), qzeros.contiguous(), scales.contiguous()
+    if kind == "awq":
+        in_f, out_f = qweight.shape[0], qweight.shape[1] * 8
+        out = torch.empty(out_f, in_f, dtype=torch.float32, device=qweight.device)
+        rc = lib.rmlx_awq_dequant(qweight.data_ptr(), qzeros.data_ptr(), scales.data_ptr(), out.data_ptr(),
+                                  in_f, out_f, group_size, st)
+    else:
+        in_f, out_f = qweight.shape[0] * 8, qweight.shape[1]
+        out = torch.empty(out_f, in_f, dtype=torch.float32, device=qweight.device)
+        gi = None if g_idx is None else g_idx.to(torch.int32).contiguous()
+        rc = lib.rmlx_gptq_dequant(qweight.data_ptr(), qzeros.data_ptr(), scales.data_ptr(), _lib.ptr(gi),
+                                   out.data_ptr(), in_f, out_f, scales.shape[0], st)
+    if rc == -2:
+        return None
+    _lib.check(rc, f"{kind}_dequant")
+    return out
+
+
 def awq_dequantize(qweight, qzeros, scales, group_size: int = 128) -> torch.Tensor:
     """-> fp32 [out, in] (crates/rmlx-core/src/ops/quantized.rs:707 awq_dequant_f32)."""
+    native = _native_4bit_dequant("awq", qweight, qzeros, scales, group_size=group_size)
+    if native is not None:
+        return native
     order = _AWQ_ORDER.to(qweight.device)
     q = _unpack_int32_nibbles(qweight)[..., order].flatten(-2)        # [in, out]
     z = _unpack_int32_nibbles(qzeros)[..., order].flatten(-2)         # [in/g, out]
@@ -106,6 +137,9 @@ def awq_dequantize(qweight, qzeros, scales, group_size: int = 128) -> torch.Tens
 
 def gptq_dequantize(qweight, qzeros, scales, g_idx=None) -> torch.Tensor:
     """-> fp32 [out, in] (crates/rmlx-core/src/ops/quantized.rs:749 gptq_dequant_f32)."""
+    native = _native_4bit_dequant("gptq", qweight, qzeros, scales, g_idx=g_idx)
+    if native is not None:
+        return native
     q = _unpack_int32_nibbles(qweight.t().contiguous()).flatten(-2).t()  # [in, out]
     z = _unpack_int32_nibbles(qzeros).flatten(-2) + 1                     # [groups, out]
     n_in = q.shape[0]

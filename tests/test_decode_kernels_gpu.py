@@ -423,3 +423,26 @@ def test_mla_decode_over_paged_latent_cache(dev, lat, heads, q4_path):
             sc = (q[s].float() @ keys.t()) * scale
             want = torch.softmax(sc, -1) @ ck.float()
             _close(got[s], want, atol=3e-2)
+
+
+def test_awq_and_gptq_dequant_kernels_are_exact(dev, q4_path):
+    """AWQ / GPTQ checkpoints expanded on the device equal the torch formulas bit for bit (a small
+    integer times an fp16 scale is exact in fp32); act-order group indices included."""
+    if q4_path != "stream":
+        pytest.skip("one run is enough")
+    from rmlx_b200.nn import layers as L
+    g = torch.Generator().manual_seed(5)
+    in_f, out_f, group = 256, 64, 128
+    qw = torch.randint(-2**31, 2**31 - 1, (in_f, out_f // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    qz = torch.randint(-2**31, 2**31 - 1, (in_f // group, out_f // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    sc = (torch.rand(in_f // group, out_f, generator=g) * 0.02 + 0.001).to(torch.float16)
+    want = L.awq_dequantize(qw, qz, sc, group)                       # CPU tensors: the torch formula
+    got = L.awq_dequantize(qw.to(dev), qz.to(dev), sc.to(dev), group)
+    assert got.is_cuda and got.dtype == torch.float32 and torch.equal(got.cpu(), want)
+    qw2 = torch.randint(-2**31, 2**31 - 1, (in_f // 8, out_f), generator=g, dtype=torch.int64).to(torch.int32)
+    qz2 = torch.randint(-2**31, 2**31 - 1, (2, out_f // 8), generator=g, dtype=torch.int64).to(torch.int32)
+    sc2 = (torch.rand(2, out_f, generator=g) * 0.02 + 0.001).to(torch.float16)
+    for g_idx in (None, torch.randint(0, 2, (in_f,), generator=g)):
+        want = L.gptq_dequantize(qw2, qz2, sc2, g_idx)
+        got = L.gptq_dequantize(qw2.to(dev), qz2.to(dev), sc2.to(dev), None if g_idx is None else g_idx.to(dev))
+        assert got.is_cuda and torch.equal(got.cpu(), want)
