@@ -323,10 +323,24 @@ class BatchedDecode:
         return out
 
 
-def enable_native_prefill(model, chunk: int = 8192) -> bool:
+def plan_chunk(model, scratch_limit_bytes: int = 4 << 30, longest: int = 8192) -> int:
+    """Largest prompt chunk (a multiple of 128, at most ``longest``) whose per-layer intermediates
+    stay within ``scratch_limit_bytes`` according to the layer's static plan
+    (``models.prefill_plan.PrefillPlan``: every launch of a layer with its output size)."""
+    from .prefill_plan import PrefillPlan
+    chunk = longest
+    while chunk > 128 and PrefillPlan(model.cfg, chunk, model.layout).scratch_bytes > scratch_limit_bytes:
+        chunk -= 128
+    return chunk
+
+
+def enable_native_prefill(model, chunk: Optional[int] = None, scratch_limit_bytes: int = 4 << 30) -> bool:
     """Attach the native path to ``model.prefill``; False (and the library-kernel path stays) when the
-    model's shapes are outside what the kernels cover."""
+    model's shapes are outside what the kernels cover. ``chunk`` None: the longest chunk whose
+    intermediates fit ``scratch_limit_bytes`` (``plan_chunk``)."""
     try:
+        if chunk is None:
+            chunk = plan_chunk(model, scratch_limit_bytes)
         model._native_prefill = NativePrefill(model, chunk)
         return True
     except ImportError:

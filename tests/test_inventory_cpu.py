@@ -199,3 +199,21 @@ def test_moe_layer_picks_its_exchange_through_the_policy_and_overlap_mode():
         assert torch.allclose(layer.with_overlap(mode).forward_overlapped(x_large), want_large, atol=1e-5)
     with pytest.raises(ValueError):
         layer.with_overlap("both")
+
+
+def test_prefill_chunk_comes_from_the_static_plan():
+    """The prompt chunk of the native forward is the longest one whose per-layer intermediates fit a
+    scratch limit according to the layer's static plan."""
+    from rmlx_b200.config import moe_a22b_config
+    from rmlx_b200.models.prefill import plan_chunk
+    from rmlx_b200.models.prefill_plan import PrefillPlan
+    from rmlx_b200.models.weights import ParallelLayout
+
+    class _M:
+        cfg, layout = moe_a22b_config(2), ParallelLayout()
+
+    assert plan_chunk(_M) == 8192
+    small = plan_chunk(_M, 512 << 20)
+    assert small % 128 == 0 and 128 <= small < 8192
+    assert PrefillPlan(_M.cfg, small, _M.layout).scratch_bytes <= 512 << 20
+    assert PrefillPlan(_M.cfg, small + 128, _M.layout).scratch_bytes > 512 << 20
