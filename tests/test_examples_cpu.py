@@ -13,7 +13,7 @@ def examples_on_path():
     sys.path.insert(0, EX)
     yield
     sys.path.remove(EX)
-    for m in ("generate", "serve_requests", "speculative"):
+    for m in ("generate", "serve_requests", "speculative", "deepseek_paged"):
         sys.modules.pop(m, None)
 
 
@@ -31,3 +31,8 @@ def test_serve_requests_example(examples_on_path):
 def test_speculative_example(examples_on_path):
     out = importlib.import_module("speculative").main(["--k", "3", "--steps", "9"])
     assert len(out) == 9
+
+
+def test_deepseek_paged_example(examples_on_path):
+    out = importlib.import_module("deepseek_paged").main(["--steps", "4"])
+    assert len(out) == 2 and all(len(o) == 4 for o in out)
