@@ -148,6 +148,35 @@ def main():
     add(f"flash_decode ctx{ctx} splits{splits}",
         [(lambda i=i: D.flash_decode_paged(q, kcs[i], vcs[i], bt, sl, None, splits, fsc, out=ao))
          for i in range(ncp)], B * ctx * HKV * HD * 2 * 2)
+    # the same attention over an 8-bit cache (codes + (scale, bias) per token and group of 64)
+    if not args.only or "q8kv" in args.only or "flash_decode" in args.only:
+        from rmlx_b200.kv.paged import quantize_kv_rows
+        kq, vq = [], []
+        for i in range(ncp):
+            kq.append(quantize_kv_rows(kcs[i].float()))
+            vq.append(quantize_kv_rows(vcs[i].float()))
+        add(f"flash_decode ctx{ctx} splits{splits}, 8-bit KV (q8kv)",
+            [(lambda i=i: D.flash_decode_paged(q, kq[i][0], vq[i][0], bt, sl, None, splits, fsc, out=ao,
+                                               k_sb=kq[i][1], v_sb=vq[i][1])) for i in range(ncp)],
+            B * ctx * HKV * (HD + 4 * HD // 64) * 2)
+    # latent attention (DeepSeek-V3 widths: 128 heads, latent 512 + rope 64) over a paged latent cache
+    if not args.only or "mla" in args.only:
+        from rmlx_b200.config import MlaConfig
+        from rmlx_b200.nn.mla import MlaPagedCache, _mla_decode_kernel
+        mcfg = MlaConfig(num_heads=128, head_dim=128, v_head_dim=128, hidden_size=7168, kv_lora_rank=512,
+                         q_lora_rank=0, rope_head_dim=64, max_seq_len=ctx + 16)
+        caches = []
+        for i in range(30):                      # 30 x 4.7 MB of latents: more than the L2
+            c = MlaPagedCache(mcfg, B * ((ctx + 15) // 16) + 1, max_seqs=B, device=dev)
+            for s_ in range(B):
+                c.add_sequence(s_)
+                c.append(s_, torch.randn(ctx, 512, device=dev), torch.randn(ctx, 64, device=dev))
+            caches.append(c)
+        qa = (torch.randn(B, 128, 576, device=dev) * 0.3).to(torch.bfloat16)
+        slots = torch.arange(B, dtype=torch.int32, device=dev)
+        add(f"mla decode ctx{ctx} 128 heads, latent 512+64" + (f", splits{args.splits}" if args.splits else ""),
+            [(lambda c=c: _mla_decode_kernel(qa, c, slots, 1.0 / math.sqrt(192.0), args.splits)) for c in caches],
+            B * ctx * 576 * 2)
     cos, sin = ref.rope_tables(HD, ctx + 8, 1e6, device=dev)
     qkv = torch.randn(B, (HQ + 2 * HKV) * HD, device=dev).to(torch.bfloat16)
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)

@@ -110,7 +110,8 @@ def _register_status_words(lib: ctypes.CDLL) -> None:
     for title, sym in (("weight-streaming mat-vec", "rmlx_sg_status"),
                        ("tensor-core mat-vec", "rmlx_qmv_status"),
                        ("tensor-parallel decode", "rmlx_tp_status"),
-                       ("decode step kernel", "rmlx_decode_step_status")):
+                       ("decode step kernel", "rmlx_decode_step_status"),
+                       ("latent-attention decode", "rmlx_mla_status")):
         fn = getattr(lib, sym, None)
         if fn is not None:
             fn.restype = c_int

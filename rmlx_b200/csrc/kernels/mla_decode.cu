@@ -10,26 +10,31 @@
 // shared by every query head; the value up-projection follows outside. Nothing is expanded per
 // head in memory: a cached token costs (LAT + ROPE) * 2 bytes whatever the number of heads.
 //
-// One block = (KV split, tile of 16 query heads, sequence). The block's four warps all walk the
-// same pages (a block-wide ring of cp.async stages); each computes the 16 x 16 score tile with
-// mma.sync (queries from shared memory, keys straight from the staged page) and owns a quarter of
-// the LAT output columns for the P V product. Splits are merged by a second small kernel.
+// One block = (KV split, tile of 16 query heads, sequence); eight warps. The block walks its share
+// of the sequence in steps of four pages (64 tokens), double-buffered: one warp issues a bulk copy
+// (cp.async.bulk, completing on an mbarrier) per cached row, into shared-memory rows padded by 16
+// bytes so that ldmatrix is conflict-free without a swizzle. Within a step warp w computes the
+// 16 heads x 8 tokens score tile of tokens 8w .. 8w+7 with mma.sync (queries from shared memory,
+// keys straight from the staged page), the warps agree on the step's row maxima through shared
+// memory, every warp writes its probabilities (bf16) into a shared 16 x 64 tile, and then each
+// warp runs the P V product over all 64 tokens for its eighth of the LAT output columns. No score
+// is computed twice. Splits are merged by a second kernel.
 #include "../common/ptx.cuh"
 #include "../common/launch.cuh"
 
 namespace rb {
 
 constexpr int kMlaPage = 16;
-constexpr int kMlaWarps = 4;
-constexpr int kMlaThreads = kMlaWarps * 32;
-constexpr int kMlaStages = 3;
+constexpr int kMlaStages = 2;
 
-__device__ __forceinline__ void mla_cp_async16(void* smem_dst, const void* gsrc) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gsrc) : "memory");
+__device__ int g_mla_status = 0;          // kStatusMbarTimeout once a wait for staged pages gave up
+
+__device__ __forceinline__ void mla_bulk_g2s(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
 }
-__device__ __forceinline__ void mla_cp_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void mla_cp_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void mla_ldm_x4(uint32_t (&r)[4], uint32_t addr) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -49,8 +54,9 @@ __device__ __forceinline__ void mla_mma(float (&d)[4], const uint32_t (&a)[4], u
 struct MlaParams {
   const __nv_bfloat16* q;        // [B, H, LAT + ROPE]  absorbed query: q_lat then q_rope
   const __nv_bfloat16* cache;    // [blocks, 16, LAT + ROPE]
-  const int* block_table;        // [B, max_blocks]
-  const int* seq_lens;           // [B] tokens in the cache including the current one
+  const int* block_table;        // [slots, max_blocks]
+  const int* seq_lens;           // [slots] tokens in the cache including the current one
+  const int* slots;              // [B] cache slot of each query row (null: row b uses slot b)
   __nv_bfloat16* out;            // [B, H, LAT]
   float* part_o;                 // [B, HT, S, 16, LAT]
   float* part_ml;                // [B, HT, S, 16, 2]
@@ -58,39 +64,79 @@ struct MlaParams {
   float scale_log2;
 };
 
-// Row layout in shared memory (queries and pages alike): row r is (LAT + ROPE) * 2 bytes, its
-// 16-byte chunk c sits at chunk position c ^ (r & 7), which keeps ldmatrix conflict-free.
-template <int LAT, int ROPE>
-__global__ void __launch_bounds__(kMlaThreads) mla_decode_kernel(MlaParams p) {
+// Shared memory: rows of queries and staged pages are (LAT + ROPE) * 2 + 16 bytes apart (eight
+// consecutive rows start in eight different 16-byte bank groups). The probability tile is 16 rows
+// of 64 bf16 whose 16-byte chunk c sits at position c ^ (row & 7).
+// WARPS = 8: steps of 64 tokens, one block per SM (the choice while the grid fits the SMs once).
+// WARPS = 4: steps of 32 tokens at half the shared memory, so two blocks share an SM and one
+// block's exchange / softmax phases overlap the other's tensor-core phases.
+template <int LAT, int ROPE, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) mla_decode_kernel(MlaParams p) {
+  constexpr int kMlaWarps = WARPS, kMlaThreads = WARPS * 32;
+  constexpr int kMlaStepPages = WARPS / 2;   // eight tokens per warp in the score product
   constexpr int W = LAT + ROPE;            // values per row
   constexpr int CH = W / 8;                // 16-byte chunks per row
   constexpr int KS = W / 16;               // k-steps of the score product
   constexpr int NTW = LAT / kMlaWarps / 8; // output n-tiles per warp
   constexpr int ROW_BYTES = W * 2;
-  constexpr int PAGE_BYTES = kMlaPage * ROW_BYTES;
-  static_assert(CH % 8 == 0 && LAT % (kMlaWarps * 16) == 0, "widths: multiples of 64 / 64");
+  constexpr int ROW_PAD = ROW_BYTES + 16;
+  constexpr int PAGE_SM = kMlaPage * ROW_PAD;
+  constexpr int STEP_SM = kMlaStepPages * PAGE_SM;
+  constexpr int STEP_ROWS = kMlaStepPages * kMlaPage;
+  static_assert(KS % 4 == 0 && NTW % 2 == 0 && NTW >= 2, "widths: LAT a multiple of 128, LAT + ROPE of 64");
+  static_assert(STEP_ROWS == 8 * kMlaWarps && STEP_ROWS % 32 == 0, "eight tokens per warp, whole rows per copying lane");
+  static_assert(PAGE_SM % 128 == 0, "tiles stay 128-byte aligned");
   extern __shared__ __align__(128) char smem[];
-  char* qs = smem;                              // 16 query rows
-  char* ring = smem + PAGE_BYTES;               // kMlaStages pages
+  char* qs = smem;                                        // 16 query rows
+  char* ring = smem + PAGE_SM;                            // kMlaStages steps of four pages
+  char* ps = ring + kMlaStages * STEP_SM;                 // probabilities [16][<= 64] bf16, 128-byte rows
+  float* red = reinterpret_cast<float*>(ps + 16 * 128);   // [warps][16] row maxima / row sums
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + kMlaWarps * 16);   // one per stage
 
   const int split = blockIdx.x, ht = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, t = lane & 3;
+  if (threadIdx.x == 0) {
+    mbar_init(bars, 1);
+    mbar_init(bars + 1, 1);
+    fence_mbar_init();
+  }
   pdl_launch_dependents();
   pdl_wait();
-  const int len = p.seq_lens[b];
+  const int slot = p.slots ? p.slots[b] : b;
+  const int len = p.seq_lens[slot];
   const int pg_total = (len + kMlaPage - 1) / kMlaPage;
-  const int per = (pg_total + p.S - 1) / p.S;
+  const int per = ((pg_total + p.S - 1) / p.S + kMlaStepPages - 1) / kMlaStepPages * kMlaStepPages;
   const int pg0 = split * per, pg1 = min(pg0 + per, pg_total);
-  const int* bt = p.block_table + size_t(b) * p.max_blocks;
+  const int steps = pg1 > pg0 ? (pg1 - pg0 + kMlaStepPages - 1) / kMlaStepPages : 0;
+  const int* bt = p.block_table + size_t(slot) * p.max_blocks;
 
-  auto issue = [&](int pg, int stage) {
-    const int blk = RB_BOUNDS(pg, p.max_blocks) ? bt[pg] : 0;
-    const char* src = reinterpret_cast<const char*>(p.cache) + size_t(blk) * PAGE_BYTES;
-    char* dst = ring + stage * PAGE_BYTES;
-    for (int idx = threadIdx.x; idx < kMlaPage * CH; idx += kMlaThreads) {
-      const int r = idx / CH, c = idx - r * CH;
-      mla_cp_async16(dst + r * ROW_BYTES + (((c & ~7) | ((c ^ r) & 7)) << 4), src + idx * 16);
+  // Warp 0 stages the four pages of step `st`: one bulk copy per cached row, two rows per lane. A
+  // page past the split's end is filled with zeros so that its (zero-probability) rows cannot
+  // bring a NaN into the P V product. The block ids of a step are read from the block table one
+  // step before they are needed (`load_ids`), which keeps that read off the copy's critical path.
+  auto load_ids = [&](int st, int (&ids)[STEP_ROWS / 32]) {
+#pragma unroll
+    for (int i = 0; i < STEP_ROWS / 32; ++i) {
+      const int pg = pg0 + st * kMlaStepPages + ((lane + 32 * i) >> 4);
+      ids[i] = (pg < pg1 && RB_BOUNDS(pg, p.max_blocks)) ? bt[pg] : 0;
+    }
+  };
+  auto issue = [&](int st, int stage, const int (&ids)[STEP_ROWS / 32]) {
+    const int first = pg0 + st * kMlaStepPages;
+    if (lane == 0)
+      mbar_arrive_expect_tx(bars + stage, uint32_t(min(kMlaStepPages, pg1 - first)) * kMlaPage * ROW_BYTES);
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < STEP_ROWS / 32; ++i) {
+      const int R = lane + 32 * i, pg = first + (R >> 4), r = R & 15;
+      char* dst = ring + stage * STEP_SM + R * ROW_PAD;
+      if (pg < pg1) {
+        mla_bulk_g2s(smem_u32(dst), reinterpret_cast<const char*>(p.cache) + (size_t(ids[i]) * kMlaPage + r) * ROW_BYTES,
+                     ROW_BYTES, bars + stage);
+      } else {
+        for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0u, 0u, 0u, 0u);
+      }
     }
   };
   // queries of this head tile (rows beyond H are zero)
@@ -99,85 +145,117 @@ __global__ void __launch_bounds__(kMlaThreads) mla_decode_kernel(MlaParams p) {
     const int h = ht * 16 + r;
     uint4 v = make_uint4(0u, 0u, 0u, 0u);
     if (h < p.H) v = *reinterpret_cast<const uint4*>(p.q + (size_t(b) * p.H + h) * W + c * 8);
-    *reinterpret_cast<uint4*>(qs + r * ROW_BYTES + (((c & ~7) | ((c ^ r) & 7)) << 4)) = v;
+    *reinterpret_cast<uint4*>(qs + r * ROW_PAD + c * 16) = v;
   }
-#pragma unroll
-  for (int s = 0; s < kMlaStages; ++s) {
-    if (pg0 + s < pg1) issue(pg0 + s, s);
-    mla_cp_commit();
+  __syncthreads();              // the barriers are initialised, the queries staged
+  int ids_next[STEP_ROWS / 32] = {};      // warp 0: block ids of the step that is issued next
+  if (warp == 0 && steps > 0) {
+    int ids0[STEP_ROWS / 32];
+    load_ids(0, ids0);
+    load_ids(1, ids_next);
+    issue(0, 0, ids0);
   }
 
   float o[NTW][4];
 #pragma unroll
   for (int j = 0; j < NTW; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
-  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-  const uint32_t qbase = smem_u32(qs);
-  int stage = 0;
-  for (int pg = pg0; pg < pg1; ++pg) {
-    mla_cp_wait<kMlaStages - 1>();
-    __syncthreads();                         // the page (and, first time, the queries) are visible
-    const uint32_t kbase = smem_u32(ring + stage * PAGE_BYTES);
-    float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-    for (int ks = 0; ks < KS; ++ks) {
-      const int mi = lane >> 3, r = lane & 7;
-      uint32_t qa[4], kb[4];
-      {   // A: rows = heads; matrices (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi), (rows 8-15, k hi)
-        const int row = (mi & 1) * 8 + r, c = 2 * ks + (mi >> 1);
-        mla_ldm_x4(qa, qbase + row * ROW_BYTES + (((c & ~7) | ((c ^ row) & 7)) << 4));
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // l: this warp's tokens only
+  const int mi = lane >> 3, r8 = lane & 7;
+  // per-lane ldmatrix bases; everything added to them below is a compile-time constant
+  const uint32_t q_lane = smem_u32(qs) + ((mi & 1) * 8 + r8) * ROW_PAD + (mi >> 1) * 16;
+  const uint32_t k_lane = ((warp & 1) * 8 + r8) * ROW_PAD + mi * 16 + (warp >> 1) * PAGE_SM;
+  const uint32_t v_lane = ((mi & 1) * 8 + r8) * ROW_PAD + (warp * NTW + (mi >> 1)) * 16;
+  const uint32_t p_lane = smem_u32(ps) + ((mi & 1) * 8 + r8) * 128;
+  const uint32_t p_x = uint32_t((mi >> 1) ^ r8);          // chunk (2 kk + mi>>1) ^ r8 = (2 kk) ^ p_x
+  bool timed_out = false;
+  for (int st = 0; st < steps; ++st) {
+    const int stage = st & 1;
+    {   // bounded wait for the staged step; each thread observes the completed phase itself
+      bool ok = false;
+      for (uint32_t i = 0; i < kMbarPollLimit; ++i) {
+        if (mbar_try_wait(bars + stage, uint32_t(st >> 1) & 1u)) { ok = true; break; }
       }
-      {   // B: rows = tokens; matrices (tok 0-7, k lo), (tok 0-7, k hi), (tok 8-15, k lo), (tok 8-15, k hi)
-        const int tok = (mi >> 1) * 8 + r, c = 2 * ks + (mi & 1);
-        mla_ldm_x4(kb, kbase + tok * ROW_BYTES + (((c & ~7) | ((c ^ tok) & 7)) << 4));
-      }
-      mla_mma(s0, qa, kb[0], kb[1]);
-      mla_mma(s1, qa, kb[2], kb[3]);
+      timed_out |= !ok;
     }
-    const int tok0 = pg * kMlaPage + t * 2;
-    float sv[8] = {s0[0], s0[1], s1[0], s1[1], s0[2], s0[3], s1[2], s1[3]};
-    const int tk[4] = {tok0, tok0 + 1, tok0 + 8, tok0 + 9};
+    __syncthreads();            // every warp has left step st - 1: its stage may be refilled
+    if (warp == 0 && st + 1 < steps) {
+      issue(st + 1, stage ^ 1, ids_next);
+      load_ids(st + 2, ids_next);
+    }
+    const uint32_t sbase = smem_u32(ring + stage * STEP_SM);
+    // scores of this warp's eight tokens: four independent accumulator chains
+    float s[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KS; ks += 4) {
+      uint32_t kb[2][4], qa[4];
+      mla_ldm_x4(kb[0], sbase + k_lane + ks * 32);          // (k lo, k hi) of ks, then of ks + 1
+      mla_ldm_x4(kb[1], sbase + k_lane + (ks + 2) * 32);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        // A: rows = heads; matrices (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi), (rows 8-15, k hi)
+        mla_ldm_x4(qa, q_lane + (ks + i) * 32);
+        mla_mma(s[i], qa, kb[i >> 1][(i & 1) * 2], kb[i >> 1][(i & 1) * 2 + 1]);
+      }
+    }
+    const int pg = pg0 + st * kMlaStepPages + (warp >> 1);
+    const int tok0 = pg * kMlaPage + (warp & 1) * 8 + t * 2;
+    float sv[4];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const bool ok = tk[i] < len;
-      sv[i] = ok ? sv[i] * p.scale_log2 : -INFINITY;
-      sv[4 + i] = ok ? sv[4 + i] * p.scale_log2 : -INFINITY;
+      const bool ok = pg < pg1 && tok0 + (i & 1) < len;
+      sv[i] = ok ? (s[0][i] + s[1][i] + s[2][i] + s[3][i]) * p.scale_log2 : -INFINITY;
     }
-    float mx0 = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
-    float mx1 = fmaxf(fmaxf(sv[4], sv[5]), fmaxf(sv[6], sv[7]));
+    float mx0 = fmaxf(sv[0], sv[1]), mx1 = fmaxf(sv[2], sv[3]);   // rows g and g + 8
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);   // finite: a page holds a visible token
+    if (t == 0) { red[warp * 16 + g] = mx0; red[warp * 16 + g + 8] = mx1; }
+    __syncthreads();            // the eight warps' row maxima
+#pragma unroll
+    for (int w = 0; w < kMlaWarps; ++w) {
+      mx0 = fmaxf(mx0, red[w * 16 + g]);
+      mx1 = fmaxf(mx1, red[w * 16 + g + 8]);
+    }
+    // finite: the step's first page holds a visible token
+    const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
     const float c0 = exp2f(m0 - nm0), c1 = exp2f(m1 - nm1);
     m0 = nm0; m1 = nm1;
-    float pr[8];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) { pr[i] = exp2f(sv[i] - m0); pr[4 + i] = exp2f(sv[4 + i] - m1); }
-    l0 = l0 * c0 + (pr[0] + pr[1] + pr[2] + pr[3]);
-    l1 = l1 * c1 + (pr[4] + pr[5] + pr[6] + pr[7]);
-    const uint32_t pa[4] = {pack_bf16(pr[0], pr[1]), pack_bf16(pr[4], pr[5]), pack_bf16(pr[2], pr[3]),
-                            pack_bf16(pr[6], pr[7])};
+    const float p0 = exp2f(sv[0] - m0), p1 = exp2f(sv[1] - m0), p2 = exp2f(sv[2] - m1), p3 = exp2f(sv[3] - m1);
+    l0 = l0 * c0 + (p0 + p1);
+    l1 = l1 * c1 + (p2 + p3);
+    // this warp's eight columns of the probability tile are chunk `warp` of each row
+    *reinterpret_cast<uint32_t*>(ps + g * 128 + ((warp ^ g) << 4) + 4 * t) = pack_bf16(p0, p1);
+    *reinterpret_cast<uint32_t*>(ps + (g + 8) * 128 + ((warp ^ g) << 4) + 4 * t) = pack_bf16(p2, p3);
 #pragma unroll
     for (int j = 0; j < NTW; ++j) { o[j][0] *= c0; o[j][1] *= c0; o[j][2] *= c1; o[j][3] *= c1; }
-    // O += P V over this warp's quarter of the latent columns
+    __syncthreads();            // the probability tile is complete
+    // O += P V over the step's 64 tokens and this warp's share of the latent columns
 #pragma unroll
-    for (int j = 0; j < NTW; j += 2) {
-      const int mi = lane >> 3, r = lane & 7;
-      const int tok = (mi & 1) * 8 + r, c = warp * NTW + j + (mi >> 1);
-      uint32_t vb[4];
-      mla_ldm_x4_trans(vb, kbase + tok * ROW_BYTES + (((c & ~7) | ((c ^ tok) & 7)) << 4));
-      mla_mma(o[j], pa, vb[0], vb[1]);
-      mla_mma(o[j + 1], pa, vb[2], vb[3]);
+    for (int kk = 0; kk < kMlaStepPages; ++kk) {
+      uint32_t pa[4];
+      mla_ldm_x4(pa, p_lane + ((uint32_t(2 * kk) ^ p_x) << 4));
+#pragma unroll
+      for (int j = 0; j < NTW; j += 2) {
+        uint32_t vb[4];
+        mla_ldm_x4_trans(vb, sbase + v_lane + kk * PAGE_SM + j * 16);
+        mla_mma(o[j], pa, vb[0], vb[1]);
+        mla_mma(o[j + 1], pa, vb[2], vb[3]);
+      }
     }
-    __syncthreads();                         // every warp is done with this stage
-    if (pg + kMlaStages < pg1) issue(pg + kMlaStages, stage);
-    mla_cp_commit();
-    stage = (stage + 1 == kMlaStages) ? 0 : stage + 1;
   }
-  mla_cp_wait<0>();
+  if (timed_out) atomicExch(&g_mla_status, int(kStatusMbarTimeout));
+  // row sums: over the quad, then over the warps (all share the same running maximum)
   l0 += __shfl_xor_sync(0xffffffffu, l0, 1); l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
   l1 += __shfl_xor_sync(0xffffffffu, l1, 1); l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  __syncthreads();              // the last step's reads of `red` are over
+  if (t == 0) { red[warp * 16 + g] = l0; red[warp * 16 + g + 8] = l1; }
+  __syncthreads();
+  l0 = l1 = 0.f;
+#pragma unroll
+  for (int w = 0; w < kMlaWarps; ++w) { l0 += red[w * 16 + g]; l1 += red[w * 16 + g + 8]; }
 
   const size_t tile = (size_t(b) * p.HT + ht) * p.S + split;
 #pragma unroll
@@ -204,36 +282,57 @@ __global__ void __launch_bounds__(kMlaThreads) mla_decode_kernel(MlaParams p) {
   pdl_launch_dependents();
 }
 
-// One block per (sequence, head tile): weights exp2(m_s - M) / L per split and row, then the sum.
+// One block per (sequence, head tile, 64 output columns). Weights exp2(m_s - M) / L per split and
+// row first (16 lanes per row, up to four splits per lane), then the weighted sum of the partials.
 template <int LAT>
 __global__ void __launch_bounds__(256) mla_merge_kernel(MlaParams p) {
   __shared__ float wgt[64 * 16];
-  const int ht = blockIdx.x, b = blockIdx.y;
+  const int ht = blockIdx.x, b = blockIdx.y, cz = blockIdx.z;
   pdl_launch_dependents();
   pdl_wait();
   const size_t tile0 = (size_t(b) * p.HT + ht) * p.S;
-  if (threadIdx.x < 16) {
-    const int row = threadIdx.x;
-    float M = -INFINITY;
-    for (int s = 0; s < p.S; ++s) M = fmaxf(M, p.part_ml[((tile0 + s) * 16 + row) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < p.S; ++s) {
-      const float ms = p.part_ml[((tile0 + s) * 16 + row) * 2];
-      const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
-      wgt[s * 16 + row] = f;
-      L += p.part_ml[((tile0 + s) * 16 + row) * 2 + 1] * f;
+  {
+    const int row = threadIdx.x >> 4, ls = threadIdx.x & 15;
+    float ms[4], lsum[4], M = -INFINITY;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int s = ls + 16 * k;
+      ms[k] = -INFINITY; lsum[k] = 0.f;
+      if (s < p.S) {
+        const float2 ml = *reinterpret_cast<const float2*>(p.part_ml + ((tile0 + s) * 16 + row) * 2);
+        ms[k] = ml.x; lsum[k] = ml.y;
+      }
+      M = fmaxf(M, ms[k]);
     }
+#pragma unroll
+    for (int off = 8; off; off >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, off));
+    float f[4], L = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      f[k] = (ms[k] == -INFINITY) ? 0.f : exp2f(ms[k] - M);
+      L += lsum[k] * f[k];
+    }
+#pragma unroll
+    for (int off = 8; off; off >>= 1) L += __shfl_xor_sync(0xffffffffu, L, off);
     const float inv = L > 0.f ? 1.f / L : 0.f;
-    for (int s = 0; s < p.S; ++s) wgt[s * 16 + row] *= inv;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int s = ls + 16 * k;
+      if (s < p.S) wgt[s * 16 + row] = f[k] * inv;
+    }
   }
   __syncthreads();
-  for (int idx = threadIdx.x; idx < 16 * (LAT / 2); idx += 256) {
-    const int row = idx / (LAT / 2), d = (idx - row * (LAT / 2)) * 2;
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int idx = threadIdx.x + 256 * i;              // 16 rows x 32 column pairs
+    const int row = idx >> 5, d = cz * 64 + (idx & 31) * 2;
     const int h = ht * 16 + row;
     if (h >= p.H) continue;
+    const float* src = p.part_o + (tile0 * 16 + row) * LAT + d;
     float a0 = 0.f, a1 = 0.f;
+#pragma unroll 8
     for (int s = 0; s < p.S; ++s) {
-      const float2 v = *reinterpret_cast<const float2*>(p.part_o + ((tile0 + s) * 16 + row) * LAT + d);
+      const float2 v = *reinterpret_cast<const float2*>(src + size_t(s) * 16 * LAT);
       const float w = wgt[s * 16 + row];
       a0 = fmaf(v.x, w, a0); a1 = fmaf(v.y, w, a1);
     }
@@ -253,10 +352,19 @@ extern "C" long long rmlx_mla_decode_part_ml_elems(int B, int H, int S) {
   return 1LL * B * ((H + 15) / 16) * S * 16 * 2;
 }
 
+// 0 while every wait for staged pages completed; kStatusMbarTimeout otherwise. Reading resets it.
+extern "C" int rmlx_mla_status() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_mla_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_mla_status, &zero, sizeof(int));
+  return v;
+}
+
 // q [B, H, LAT + ROPE] bf16 (absorbed), cache [blocks, 16, LAT + ROPE] bf16, out [B, H, LAT] bf16.
+// block_table / seq_lens are the cache's own tables, indexed by slots[b] (by b when slots is null).
 // (LAT, ROPE) in {(512, 64), (128, 64)}; splits in [1, 64]; part_* needed when splits > 1.
 extern "C" int rmlx_mla_decode_paged(const void* q, const void* cache, const int* block_table,
-                                     const int* seq_lens, void* out, float* part_o, float* part_ml,
+                                     const int* seq_lens, const int* slots, void* out, float* part_o, float* part_ml,
                                      int B, int H, int LAT, int ROPE, int max_blocks, int splits,
                                      float scale, int pdl, cudaStream_t st) {
   if (B < 1 || H < 1 || splits < 1 || splits > 64) return -2;
@@ -264,20 +372,23 @@ extern "C" int rmlx_mla_decode_paged(const void* q, const void* cache, const int
   MlaParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
   p.cache = static_cast<const __nv_bfloat16*>(cache);
-  p.block_table = block_table; p.seq_lens = seq_lens;
+  p.block_table = block_table; p.seq_lens = seq_lens; p.slots = slots;
   p.out = static_cast<__nv_bfloat16*>(out);
   p.part_o = part_o; p.part_ml = part_ml;
   p.max_blocks = max_blocks; p.H = H; p.HT = (H + 15) / 16; p.S = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
   const dim3 grid(splits, p.HT, B);
+  const bool narrow = 1LL * splits * p.HT * B > 148;   // more blocks than SMs: two narrow blocks per SM
 #define RB_MLA(LAT_, ROPE_)                                                                   \
   {                                                                                           \
-    const size_t smem = size_t(1 + kMlaStages) * kMlaPage * (LAT_ + ROPE_) * 2;               \
-    auto kern = mla_decode_kernel<LAT_, ROPE_>;                                               \
+    const int warps = narrow ? 4 : 8;                                                         \
+    const size_t smem = size_t(1 + kMlaStages * (warps / 2)) * kMlaPage * ((LAT_ + ROPE_) * 2 + 16) \
+                        + 16 * 128 + warps * 16 * sizeof(float) + kMlaStages * 8;             \
+    auto kern = narrow ? mla_decode_kernel<LAT_, ROPE_, 4> : mla_decode_kernel<LAT_, ROPE_, 8>; \
     RB_CHECK(set_max_smem(kern, smem));                                                       \
-    int rc = launch(kern, grid, dim3(kMlaThreads), smem, st, pdl != 0, p);                    \
+    int rc = launch(kern, grid, dim3(warps * 32), smem, st, pdl != 0, p);                     \
     if (rc || splits == 1) return rc;                                                         \
-    return launch(mla_merge_kernel<LAT_>, dim3(p.HT, B), dim3(256), 0, st, pdl != 0, p);      \
+    return launch(mla_merge_kernel<LAT_>, dim3(p.HT, B, LAT_ / 64), dim3(256), 0, st, pdl != 0, p); \
   }
   if (LAT == 512 && ROPE == 64) RB_MLA(512, 64)
   if (LAT == 128 && ROPE == 64) RB_MLA(128, 64)

@@ -190,19 +190,23 @@ def _mla_decode_kernel(q_abs: torch.Tensor, cache: MlaPagedCache, slots: torch.T
     kernel; row b attends to the sequence in cache slot ``slots[b]``."""
     from .. import _lib
     _lib.register_cuda_sigs({
-        "rmlx_mla_decode_paged": ("pppppppiiiiiifip", "i"),
+        "rmlx_mla_decode_paged": ("ppppppppiiiiiifip", "i"),
         "rmlx_mla_decode_part_o_elems": ("iiii", "q"),
         "rmlx_mla_decode_part_ml_elems": ("iii", "q"),
     })
     lib = _lib.cuda()
     b, h, w = q_abs.shape
     lat = cache.cfg.kv_lora_rank
-    table = cache.block_table.index_select(0, slots.long()).contiguous()
-    lens = cache.seq_lens.index_select(0, slots.long()).contiguous()
-    if splits <= 0:     # about one block per SM, at least 8 pages per split
+    table, lens = cache.block_table, cache.seq_lens      # the kernel indexes both by slots[b]
+    slots = slots.to(torch.int32)
+    if splits <= 0:
+        # Up to 16 head tiles: wide blocks (eight warps, one per SM), one wave of 148. More: narrow
+        # blocks (four warps, two per SM; the launcher picks them once the grid exceeds the SMs),
+        # one wave of 296. At least 8 pages per split.
         tiles = b * ((h + 15) // 16)
         longest = int(table.shape[1]) * MlaPagedCache.PAGE
-        splits = max(1, min(64, (148 + tiles - 1) // tiles, longest // 128))
+        slots_per_wave = 148 if tiles <= 16 else 296
+        splits = max(1, min(64, slots_per_wave // tiles, longest // 128))
     out = torch.empty(b, h, lat, dtype=torch.bfloat16, device=q_abs.device)
     part_o = part_ml = None
     if splits > 1:
@@ -211,7 +215,7 @@ def _mla_decode_kernel(q_abs: torch.Tensor, cache: MlaPagedCache, slots: torch.T
         part_ml = torch.empty(lib.rmlx_mla_decode_part_ml_elems(b, h, splits), dtype=torch.float32,
                               device=q_abs.device)
     rc = lib.rmlx_mla_decode_paged(q_abs.data_ptr(), cache.pages.data_ptr(), table.data_ptr(),
-                                   lens.data_ptr(), out.data_ptr(), _lib.ptr(part_o), _lib.ptr(part_ml),
+                                   lens.data_ptr(), slots.data_ptr(), out.data_ptr(), _lib.ptr(part_o), _lib.ptr(part_ml),
                                    b, h, lat, w - lat, table.shape[1], splits, scale, 0,
                                    _lib.stream_ptr())
     _lib.check(rc, "mla_decode_paged")

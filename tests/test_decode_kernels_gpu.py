@@ -423,6 +423,9 @@ def test_mla_decode_over_paged_latent_cache(dev, lat, heads, q4_path):
             sc = (q[s].float() @ keys.t()) * scale
             want = torch.softmax(sc, -1) @ ck.float()
             _close(got[s], want, atol=3e-2)
+    from rmlx_b200 import _lib
+    torch.cuda.synchronize()
+    assert _lib.cuda().rmlx_mla_status() == 0          # no wait for staged pages ran out
 
 
 def test_awq_and_gptq_dequant_kernels_are_exact(dev, q4_path):
