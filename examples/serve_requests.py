@@ -18,6 +18,7 @@ from rmlx_b200.config import SamplerConfig, SchedulerConfig  # noqa: E402
 from rmlx_b200.models.transformer import TransformerModel  # noqa: E402
 from rmlx_b200.models.weights import from_state_dict, random_state_dict  # noqa: E402
 from rmlx_b200.serve.engine import ServingEngine  # noqa: E402
+from rmlx_b200.utils.precision_guard import PrecisionGuard  # noqa: E402
 
 from generate import small_moe  # noqa: E402
 
@@ -39,7 +40,9 @@ def main(argv=None) -> dict:
     eng = ServingEngine(model, num_blocks=128,
                         scheduler_cfg=SchedulerConfig(max_batch_size=a.max_batch, max_prefill_chunk=64),
                         sampler_cfg=SamplerConfig(temperature=a.temperature, top_k=40, seed=0),
-                        use_prefix_cache=True)
+                        use_prefix_cache=True, precision_guard=PrecisionGuard(), guard_every=4)
+    warm = eng.warm_up()        # kernels loaded, one graph per batch bucket captured, pages given back
+    print(f"warm-up: {warm.kernels_s * 1e3:.0f} ms")
     g = torch.Generator().manual_seed(0)
     system = torch.randint(0, cfg.vocab_size, (48,), generator=g).tolist()
     ids = [eng.submit(system + torch.randint(0, cfg.vocab_size, (5 + i,), generator=g).tolist(), a.max_new)
@@ -48,7 +51,8 @@ def main(argv=None) -> dict:
     for i in ids:
         print(f"request {i}: {outs[i]}")
     print(f"prompt tokens run: {eng.prefill_tokens} (prefix cache hits: {eng.prefix.hits}, "
-          f"pages kept: {len(eng.prefix)})")
+          f"pages kept: {len(eng.prefix)}); logit monitor: {eng.guard.checks} checks, "
+          f"{eng.guard_warnings} warnings, {eng.guard_fallbacks} fallback verdicts")
     return outs
 
 

@@ -14,7 +14,9 @@ import torch
 
 from ..config import SamplerConfig, SchedulerConfig
 from ..models.transformer import TransformerModel
+from ..parallel.warmup import Warmup, WarmupResult
 from ..utils.metrics import PERF
+from ..utils.precision_guard import GuardAction, PrecisionGuard
 from .prefix_cache import PrefixCache
 from .sampler import Sampler
 from .scheduler import GenerationRequest, Scheduler
@@ -25,10 +27,14 @@ class ServingEngine:
                  scheduler_cfg: Optional[SchedulerConfig] = None,
                  sampler_cfg: Optional[SamplerConfig] = None, comm=None,
                  use_prefix_cache: bool = False, sample_on_device: bool = False,
-                 kv_quant: Optional[str] = None):
+                 kv_quant: Optional[str] = None, precision_guard: Optional[PrecisionGuard] = None,
+                 guard_every: int = 16):
         """``sample_on_device``: run the sampler's tensor ops where the logits are (only the chosen
         token ids come back) instead of on a host copy of the logits. ``kv_quant="q8"``: the KV
-        cache is kept in the 8-bit format (half the bytes per cached token)."""
+        cache is kept in the 8-bit format (half the bytes per cached token). ``precision_guard``:
+        every ``guard_every``-th decode step (and every completed prompt) hands its logits to the
+        guard; its verdicts are counted in ``guard_warnings`` / ``guard_fallbacks`` and the steps
+        they came from listed in ``guard_events``."""
         self.model = model
         scfg = scheduler_cfg or SchedulerConfig()
         self.cache = model.new_cache(num_blocks, max_seqs=scfg.max_batch_size, kv_quant=kv_quant)
@@ -53,6 +59,14 @@ class ServingEngine:
         self.released_pages = 0               # sliding-window models: pages returned to the pool
         self._engine = None
         self._bound: List[int] = []
+        self.guard = precision_guard
+        self.guard_every = max(1, guard_every)
+        self.guard_warnings = 0
+        self.guard_fallbacks = 0
+        self.guard_events: List[tuple] = []   # (decode step, GuardAction) of every verdict but OK
+        self._decode_steps = 0
+        self._comm = comm
+        self._warmup = Warmup()
         if model.device.type == "cuda":
             # prompts through the tensor-core path; decode through the mat-vec engine for small
             # batches and through the tensor-core path (batch = GEMM rows) for larger ones
@@ -109,6 +123,47 @@ class ServingEngine:
             self.cache.manager.release(b)
         return len(victims)
 
+    # ------------------------------------------------------------------ warm-up and logit monitor
+    def warm_up(self, prompt_len: int = 8, new_tokens: int = 3) -> WarmupResult:
+        """Run the communication path and every kernel once before the first real request: a
+        barrier over the tensor-parallel group, then throw-away requests that fill each batch
+        bucket of the decode engine in turn (prompt path, graph capture per bucket, sampler).
+        Their pages, outputs and counters are dropped afterwards. A second call does nothing and
+        returns the first call's timings (crates/rmlx-distributed/src/warmup.rs:20-150)."""
+        def comm_fn():
+            if self._comm is not None and hasattr(self._comm, "barrier"):
+                self._comm.barrier()
+
+        def kernel_fn():
+            buckets = getattr(self._engine, "buckets", None) or (self.sched.cfg.max_batch_size,)
+            guard, self.guard = self.guard, None          # throw-away logits stay out of the statistics
+            try:
+                for nb in buckets:
+                    ids = [self.submit([1 + (i % 7)] * prompt_len, new_tokens) for i in range(nb)]
+                    self.run_until_done()
+                    for sid in ids:
+                        self.outputs.pop(sid, None)
+                        self.last_token.pop(sid, None)
+            finally:
+                self.guard = guard
+            if self.prefix is not None:                   # the throw-away prompts leave no cached pages
+                self.reclaim(1 << 30)
+            self.prefill_tokens = 0
+            self.released_pages = 0
+            self._decode_steps = 0
+
+        return self._warmup.run(comm_fn=comm_fn, kernel_fn=kernel_fn)
+
+    def _guard_check(self, logits: torch.Tensor) -> None:
+        action = self.guard.check(logits)
+        if action is GuardAction.OK:
+            return
+        if action is GuardAction.WARN:
+            self.guard_warnings += 1
+        else:
+            self.guard_fallbacks += 1
+        self.guard_events.append((self._decode_steps, action))
+
     # ------------------------------------------------------------------ public API
     def submit(self, prompt_tokens: List[int], max_output_len: int) -> int:
         sid = next(self._ids)
@@ -136,6 +191,8 @@ class ServingEngine:
             logits = self.model.prefill(chunk, self.cache, meta.seq_id)
             self.prefill_tokens += hi - lo
             if hi >= meta.prompt_len:      # prompt complete: its last logits give the first token
+                if self.guard is not None:
+                    self._guard_check(logits[:1])
                 tok = self.sampler.sample_token(logits[0].float().cpu(), self.outputs[meta.seq_id])
                 produced[meta.seq_id] = tok
         ids = [m.seq_id for m in plan.decode_seqs]
@@ -173,6 +230,8 @@ class ServingEngine:
     def _decode(self, ids: List[int]) -> List[int]:
         dev = self.model.device
         self._release_outside_window(ids)
+        self._decode_steps += 1
+        guarded = self.guard is not None and self._decode_steps % self.guard_every == 0
         # the device engines compute full-vocabulary logits unless the LM head is sharded
         on_device = self._engine is not None and (self.greedy or self.model.layout.world == 1)
         if on_device:
@@ -181,6 +240,8 @@ class ServingEngine:
                 self._bound = list(ids)
             self._engine.reserve(1)
             nxt = self._engine.step()
+            if guarded:
+                self._guard_check(self._engine.logits[:len(ids)])
             if self.greedy:
                 PERF.record_d2h(nxt[:len(ids)])
                 return [int(t) for t in nxt[:len(ids)].cpu()]
@@ -194,6 +255,8 @@ class ServingEngine:
             return toks
         toks = torch.tensor([self.last_token[s] for s in ids], device=dev)
         logits = self.model.forward(toks, self.cache, ids, last_only=True)
+        if guarded:
+            self._guard_check(logits)
         if not self.sample_on_device:
             logits = logits.float().cpu()
         return self.sampler.sample_batch(logits, [self.outputs[s] for s in ids])

@@ -283,3 +283,54 @@ def test_q8_kv_cache_on_the_host_path():
     plain = model.generate_greedy(prompt, 6)
     cq = model.new_cache(4, max_seqs=1, kv_quant="q8")
     assert model.generate_greedy(prompt, 6, cache=cq) == plain
+
+
+def test_serving_engine_warm_up_leaves_no_trace_and_runs_once():
+    """``warm_up`` runs throw-away requests through the prompt and decode paths, gives every page
+    back, keeps its tokens out of the outputs and counters, and does nothing the second time."""
+    cfg = tiny_dense_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    eng = ServingEngine(model, num_blocks=24, use_prefix_cache=True,
+                        scheduler_cfg=SchedulerConfig(max_batch_size=2, max_prefill_chunk=8))
+    first = eng.warm_up()
+    assert first.ran and first.kernels_s > 0
+    assert eng.outputs == {} and eng.prefill_tokens == 0 and len(eng.prefix) == 0
+    assert eng.cache.manager.num_free_blocks() == 23
+    again = eng.warm_up()
+    assert not again.ran and again.kernels_s == first.kernels_s
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    sid = eng.submit(prompt, 4)
+    assert eng.run_until_done()[sid][:4] == model.generate_greedy(torch.tensor(prompt), 4)
+
+
+def test_serving_engine_precision_guard_counts_bad_logits():
+    """The logit monitor sees every ``guard_every``-th decode step and each completed prompt; a
+    non-finite row is counted as a fallback verdict with the step it came from."""
+    from rmlx_b200.utils.precision_guard import GuardAction, PrecisionGuard
+    cfg = tiny_dense_config()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), dtype=torch.float32))
+    guard = PrecisionGuard()
+    eng = ServingEngine(model, num_blocks=24, precision_guard=guard, guard_every=2,
+                        scheduler_cfg=SchedulerConfig(max_batch_size=2, max_prefill_chunk=8))
+    sid = eng.submit([5, 6, 7], 9)
+    eng.run_until_done()
+    # one prompt + decode steps 2, 4, 6, 8 (the first of the 9 tokens came from the prompt)
+    assert guard.checks == 5 and eng.guard_fallbacks == 0 and guard.nan_events == 0
+    assert len(eng.outputs[sid]) == 9
+
+    real = model.forward
+    def poisoned(*a, **k):
+        out = real(*a, **k).clone()
+        out[0, 0] = float("nan")
+        return out
+    model.forward = poisoned
+    try:
+        eng2 = ServingEngine(model, num_blocks=24, precision_guard=PrecisionGuard(), guard_every=1,
+                             scheduler_cfg=SchedulerConfig(max_batch_size=2, max_prefill_chunk=8))
+        eng2.submit([5, 6, 7], 3)
+        eng2.run_until_done()
+    finally:
+        model.forward = real
+    # the prompt's logits (decode step 0: the library prompt path runs the same forward) and both decode steps
+    assert eng2.guard_fallbacks == 3 and eng2.guard.nan_events == 3
+    assert eng2.guard_events == [(s, GuardAction.FALLBACK) for s in (0, 1, 2)]
