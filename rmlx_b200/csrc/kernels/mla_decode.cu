@@ -1,7 +1,7 @@
 // Decode attention for multi-head latent attention over a PAGED LATENT cache.
 //
 // The cache holds, per token, the compressed latent c_kv (LAT values) followed by the decoupled
-// RoPE key (ROPE values): one row of LAT + ROPE bf16 shared by all heads
+// RoPE key (ROPE values) and 8 values of padding: one row of LAT + ROPE + 8 bf16 shared by all heads
 // (crates/rmlx-nn/src/mla.rs:111-250, MlaKvCache). With the key up-projection absorbed into the
 // query (q_lat = q_nope W_uk per head) the attention of one new token is
 //     score[h, t] = scale * (q_lat[h] . c_kv[t] + q_rope[h] . k_rope[t])
@@ -11,9 +11,11 @@
 // head in memory: a cached token costs (LAT + ROPE) * 2 bytes whatever the number of heads.
 //
 // One block = (KV split, tile of 16 query heads, sequence); eight warps. The block walks its share
-// of the sequence in steps of four pages (64 tokens), double-buffered: one warp issues a bulk copy
-// (cp.async.bulk, completing on an mbarrier) per cached row, into shared-memory rows padded by 16
-// bytes so that ldmatrix is conflict-free without a swizzle. Within a step warp w computes the
+// of the sequence in steps of four pages (64 tokens), double-buffered: one warp issues ONE bulk copy
+// (cp.async.bulk, completing on an mbarrier) per page. A bulk copy occupies the copy engine for
+// about as long whatever its size, so a page of 18 KB must not be fetched row by row; the 16 bytes
+// of padding that keep ldmatrix conflict-free without a swizzle are therefore part of the cache's
+// row in global memory, and a page lands in shared memory as it is. Within a step warp w computes the
 // 16 heads x 8 tokens score tile of tokens 8w .. 8w+7 with mma.sync (queries from shared memory,
 // keys straight from the staged page), the warps agree on the step's row maxima through shared
 // memory, every warp writes its probabilities (bf16) into a shared 16 x 64 tile, and then each
@@ -53,7 +55,7 @@ __device__ __forceinline__ void mla_mma(float (&d)[4], const uint32_t (&a)[4], u
 
 struct MlaParams {
   const __nv_bfloat16* q;        // [B, H, LAT + ROPE]  absorbed query: q_lat then q_rope
-  const __nv_bfloat16* cache;    // [blocks, 16, LAT + ROPE]
+  const __nv_bfloat16* cache;    // [blocks, 16, LAT + ROPE + 8]
   const int* block_table;        // [slots, max_blocks]
   const int* seq_lens;           // [slots] tokens in the cache including the current one
   const int* slots;              // [B] cache slot of each query row (null: row b uses slot b)
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) mla_decode_ker
   constexpr int STEP_SM = kMlaStepPages * PAGE_SM;
   constexpr int STEP_ROWS = kMlaStepPages * kMlaPage;
   static_assert(KS % 4 == 0 && NTW % 2 == 0 && NTW >= 2, "widths: LAT a multiple of 128, LAT + ROPE of 64");
-  static_assert(STEP_ROWS == 8 * kMlaWarps && STEP_ROWS % 32 == 0, "eight tokens per warp, whole rows per copying lane");
+  static_assert(STEP_ROWS == 8 * kMlaWarps, "eight tokens per warp");
   static_assert(PAGE_SM % 128 == 0, "tiles stay 128-byte aligned");
   extern __shared__ __align__(128) char smem[];
   char* qs = smem;                                        // 16 query rows
@@ -111,33 +113,25 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) mla_decode_ker
   const int steps = pg1 > pg0 ? (pg1 - pg0 + kMlaStepPages - 1) / kMlaStepPages : 0;
   const int* bt = p.block_table + size_t(slot) * p.max_blocks;
 
-  // Warp 0 stages the four pages of step `st`: one bulk copy per cached row, two rows per lane. A
-  // page past the split's end is filled with zeros so that its (zero-probability) rows cannot
-  // bring a NaN into the P V product. The block ids of a step are read from the block table one
-  // step before they are needed (`load_ids`), which keeps that read off the copy's critical path.
-  auto load_ids = [&](int st, int (&ids)[STEP_ROWS / 32]) {
-#pragma unroll
-    for (int i = 0; i < STEP_ROWS / 32; ++i) {
-      const int pg = pg0 + st * kMlaStepPages + ((lane + 32 * i) >> 4);
-      ids[i] = (pg < pg1 && RB_BOUNDS(pg, p.max_blocks)) ? bt[pg] : 0;
-    }
+  // Warp 0 stages the pages of step `st`: lane i copies page i whole. A page past the split's end
+  // is filled with zeros so that its (zero-probability) rows cannot bring a NaN into the P V
+  // product. The block ids of a step are read from the block table one step before they are
+  // needed (`load_id`), which keeps that read off the copy's critical path.
+  auto load_id = [&](int st) -> int {
+    const int pg = pg0 + st * kMlaStepPages + lane;
+    return (lane < kMlaStepPages && pg < pg1 && RB_BOUNDS(pg, p.max_blocks)) ? bt[pg] : 0;
   };
-  auto issue = [&](int st, int stage, const int (&ids)[STEP_ROWS / 32]) {
+  auto issue = [&](int st, int stage, int id) {
     const int first = pg0 + st * kMlaStepPages;
-    if (lane == 0)
-      mbar_arrive_expect_tx(bars + stage, uint32_t(min(kMlaStepPages, pg1 - first)) * kMlaPage * ROW_BYTES);
+    const int valid = min(kMlaStepPages, pg1 - first);
+    if (lane == 0) mbar_arrive_expect_tx(bars + stage, uint32_t(valid) * PAGE_SM);
     __syncwarp();
-#pragma unroll
-    for (int i = 0; i < STEP_ROWS / 32; ++i) {
-      const int R = lane + 32 * i, pg = first + (R >> 4), r = R & 15;
-      char* dst = ring + stage * STEP_SM + R * ROW_PAD;
-      if (pg < pg1) {
-        mla_bulk_g2s(smem_u32(dst), reinterpret_cast<const char*>(p.cache) + (size_t(ids[i]) * kMlaPage + r) * ROW_BYTES,
-                     ROW_BYTES, bars + stage);
-      } else {
-        for (int c = 0; c < CH; ++c) *reinterpret_cast<uint4*>(dst + c * 16) = make_uint4(0u, 0u, 0u, 0u);
-      }
-    }
+    char* dst = ring + stage * STEP_SM;
+    if (lane < valid)
+      mla_bulk_g2s(smem_u32(dst + lane * PAGE_SM), reinterpret_cast<const char*>(p.cache) + size_t(id) * PAGE_SM,
+                   PAGE_SM, bars + stage);
+    for (int idx = valid * (PAGE_SM / 16) + lane; idx < kMlaStepPages * (PAGE_SM / 16); idx += 32)
+      *reinterpret_cast<uint4*>(dst + idx * 16) = make_uint4(0u, 0u, 0u, 0u);
   };
   // queries of this head tile (rows beyond H are zero)
   for (int idx = threadIdx.x; idx < 16 * CH; idx += kMlaThreads) {
@@ -148,12 +142,11 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) mla_decode_ker
     *reinterpret_cast<uint4*>(qs + r * ROW_PAD + c * 16) = v;
   }
   __syncthreads();              // the barriers are initialised, the queries staged
-  int ids_next[STEP_ROWS / 32] = {};      // warp 0: block ids of the step that is issued next
+  int id_next = 0;                        // warp 0, lane i: block id of page i of the step issued next
   if (warp == 0 && steps > 0) {
-    int ids0[STEP_ROWS / 32];
-    load_ids(0, ids0);
-    load_ids(1, ids_next);
-    issue(0, 0, ids0);
+    const int id0 = load_id(0);
+    id_next = load_id(1);
+    issue(0, 0, id0);
   }
 
   float o[NTW][4];
@@ -179,8 +172,8 @@ __global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 2 : 1) mla_decode_ker
     }
     __syncthreads();            // every warp has left step st - 1: its stage may be refilled
     if (warp == 0 && st + 1 < steps) {
-      issue(st + 1, stage ^ 1, ids_next);
-      load_ids(st + 2, ids_next);
+      issue(st + 1, stage ^ 1, id_next);
+      id_next = load_id(st + 2);
     }
     const uint32_t sbase = smem_u32(ring + stage * STEP_SM);
     // scores of this warp's eight tokens: four independent accumulator chains
@@ -360,14 +353,16 @@ extern "C" int rmlx_mla_status() {
   return v;
 }
 
-// q [B, H, LAT + ROPE] bf16 (absorbed), cache [blocks, 16, LAT + ROPE] bf16, out [B, H, LAT] bf16.
+// q [B, H, LAT + ROPE] bf16 (absorbed), cache [blocks, 16, row_elems = LAT + ROPE + 8] bf16 (the
+// last 8 values of a row are padding), out [B, H, LAT] bf16.
 // block_table / seq_lens are the cache's own tables, indexed by slots[b] (by b when slots is null).
 // (LAT, ROPE) in {(512, 64), (128, 64)}; splits in [1, 64]; part_* needed when splits > 1.
 extern "C" int rmlx_mla_decode_paged(const void* q, const void* cache, const int* block_table,
                                      const int* seq_lens, const int* slots, void* out, float* part_o, float* part_ml,
-                                     int B, int H, int LAT, int ROPE, int max_blocks, int splits,
-                                     float scale, int pdl, cudaStream_t st) {
+                                     int B, int H, int LAT, int ROPE, int row_elems, int max_blocks,
+                                     int splits, float scale, int pdl, cudaStream_t st) {
   if (B < 1 || H < 1 || splits < 1 || splits > 64) return -2;
+  if (row_elems != LAT + ROPE + 8) return -2;     // the padded row layout is part of the contract
   if (splits > 1 && (!part_o || !part_ml)) return -2;
   MlaParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);

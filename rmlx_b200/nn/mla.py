@@ -118,15 +118,20 @@ class MlaPagedCache:
     """Paged latent cache for several sequences: one row of ``kv_lora_rank + rope_head_dim`` values
     per token (latent, then the RoPE key), pages of 16 tokens, page 0 reserved; block tables and
     lengths live on the device so the decode kernel (csrc/kernels/mla_decode.cu) is shape-stable.
+    A row is stored with ``ROW_PAD`` unused values behind it (``pages`` is a view without them):
+    the kernel copies whole pages into shared memory, where the 16 bytes keep rows on different
+    banks.
     The paged counterpart of ``MlaKvCache`` (crates/rmlx-nn/src/mla.rs:111-250)."""
 
     PAGE = 16
+    ROW_PAD = 8
 
     def __init__(self, cfg: MlaConfig, num_blocks: int, max_seqs: int = 8, max_blocks_per_seq: Optional[int] = None,
                  dtype=torch.bfloat16, device="cpu"):
         self.cfg = cfg
         self.width = cfg.kv_lora_rank + cfg.rope_head_dim
-        self.pages = torch.zeros(num_blocks, self.PAGE, self.width, dtype=dtype, device=device)
+        self.store = torch.zeros(num_blocks, self.PAGE, self.width + self.ROW_PAD, dtype=dtype, device=device)
+        self.pages = self.store[..., :self.width]
         mb = max_blocks_per_seq or (cfg.max_seq_len + self.PAGE - 1) // self.PAGE
         self.block_table = torch.zeros(max_seqs, mb, dtype=torch.int32, device=device)
         self.seq_lens = torch.zeros(max_seqs, dtype=torch.int32, device=device)
@@ -181,7 +186,7 @@ class MlaPagedCache:
         return flat[:, :self.cfg.kv_lora_rank], flat[:, self.cfg.kv_lora_rank:]
 
     def bytes_per_token(self) -> int:
-        return self.width * self.pages.element_size()
+        return (self.width + self.ROW_PAD) * self.pages.element_size()
 
 
 def _mla_decode_kernel(q_abs: torch.Tensor, cache: MlaPagedCache, slots: torch.Tensor,
@@ -190,7 +195,7 @@ def _mla_decode_kernel(q_abs: torch.Tensor, cache: MlaPagedCache, slots: torch.T
     kernel; row b attends to the sequence in cache slot ``slots[b]``."""
     from .. import _lib
     _lib.register_cuda_sigs({
-        "rmlx_mla_decode_paged": ("ppppppppiiiiiifip", "i"),
+        "rmlx_mla_decode_paged": ("ppppppppiiiiiiifip", "i"),
         "rmlx_mla_decode_part_o_elems": ("iiii", "q"),
         "rmlx_mla_decode_part_ml_elems": ("iii", "q"),
     })
@@ -214,9 +219,9 @@ def _mla_decode_kernel(q_abs: torch.Tensor, cache: MlaPagedCache, slots: torch.T
                              device=q_abs.device)
         part_ml = torch.empty(lib.rmlx_mla_decode_part_ml_elems(b, h, splits), dtype=torch.float32,
                               device=q_abs.device)
-    rc = lib.rmlx_mla_decode_paged(q_abs.data_ptr(), cache.pages.data_ptr(), table.data_ptr(),
+    rc = lib.rmlx_mla_decode_paged(q_abs.data_ptr(), cache.store.data_ptr(), table.data_ptr(),
                                    lens.data_ptr(), slots.data_ptr(), out.data_ptr(), _lib.ptr(part_o), _lib.ptr(part_ml),
-                                   b, h, lat, w - lat, table.shape[1], splits, scale, 0,
+                                   b, h, lat, w - lat, cache.store.shape[2], table.shape[1], splits, scale, 0,
                                    _lib.stream_ptr())
     _lib.check(rc, "mla_decode_paged")
     return out

@@ -194,7 +194,7 @@ def test_mla_absorbed_decode_over_paged_latent_cache():
         want = torch.cat([attn.forward(xs[s][prompts[s] + step][None], refs[s]) for s in (3, 9)])
         got = mla_decode_paged(attn, rows, pc, [3, 9])
         assert (got - want).abs().max() < 1e-5
-    assert pc.seq_len(3) == 23 and pc.seq_len(9) == 8 and pc.bytes_per_token() == (128 + 64) * 4
+    assert pc.seq_len(3) == 23 and pc.seq_len(9) == 8 and pc.bytes_per_token() == (128 + 64 + 8) * 4
     ck, kr = pc.gather(9)
     assert torch.allclose(ck, refs[9].c_kv[:8]) and torch.allclose(kr, refs[9].k_rope[:8])
     pc.free_sequence(3)
