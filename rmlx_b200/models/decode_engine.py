@@ -143,6 +143,10 @@ class CachedDecode:
     def refresh_tables(self) -> None:
         for b, s in enumerate(self.seq_ids):
             self.block_table[b].copy_(self.cache.block_table[self.cache.slot_of[s]])
+        # Idle rows still run and append their key/value at position 0 of whatever page their row
+        # names: it must be the reserved page 0, never a page left over from an earlier binding
+        # (such a page may belong to a live sequence by now).
+        self.block_table[len(self.seq_ids):].zero_()
 
     def reserve(self, steps: int) -> None:
         """Allocate KV blocks for the next ``steps`` tokens of every bound sequence."""

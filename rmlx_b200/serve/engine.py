@@ -139,7 +139,9 @@ class ServingEngine:
             guard, self.guard = self.guard, None          # throw-away logits stay out of the statistics
             try:
                 for nb in buckets:
-                    ids = [self.submit([1 + (i % 7)] * prompt_len, new_tokens) for i in range(nb)]
+                    # prompts are admitted one per step: the first request must still be decoding
+                    # when the last one joins, or the bucket's batch never forms
+                    ids = [self.submit([1 + (i % 7)] * prompt_len, max(new_tokens, nb + 2)) for i in range(nb)]
                     self.run_until_done()
                     for sid in ids:
                         self.outputs.pop(sid, None)

@@ -266,3 +266,34 @@ def test_serving_engine_samples_through_the_device_engines(dev, max_batch):
         outs.append([res[i] for i in ids])
         GemmStatus.check(dev)
     assert outs[0] == outs[1]
+
+
+def test_serving_engine_warm_up_and_logit_monitor_on_device(dev):
+    """``warm_up`` captures every batch bucket with throw-away requests and leaves pages, outputs
+    and counters as they were; the requests served afterwards match an engine that was not warmed
+    up, and the logit monitor reads the device engine's logits without a verdict."""
+    from rmlx_b200.config import SchedulerConfig
+    from rmlx_b200.serve.engine import ServingEngine
+    from rmlx_b200.utils.precision_guard import PrecisionGuard
+    cfg = _moe_cfg()
+    model = TransformerModel(from_state_dict(cfg, random_state_dict(cfg, 0), device=dev, quant="q4"))
+    g = torch.Generator().manual_seed(13)
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in (12, 30, 7)]
+    scfg = SchedulerConfig(max_batch_size=4, max_prefill_chunk=64)
+    cold = ServingEngine(model, num_blocks=64, scheduler_cfg=scfg)
+    ids = [cold.submit(p, 6) for p in prompts]
+    want = cold.run_until_done()
+    eng = ServingEngine(model, num_blocks=64, scheduler_cfg=scfg, precision_guard=PrecisionGuard(), guard_every=2)
+    free = eng.cache.manager.num_free_blocks()
+    res = eng.warm_up()
+    assert res.ran and len(eng._engine.graphs) == len(eng._engine.buckets)      # one graph per bucket
+    assert eng.outputs == {} and eng.cache.manager.num_free_blocks() == free and eng.guard.checks == 0
+    assert not eng.warm_up().ran
+    ids2 = [eng.submit(p, 6) for p in prompts]
+    got = eng.run_until_done()
+    # (the warmed-up engine's rows were bound to other sequences before: an idle row whose block
+    # table still named one of their pages would write into a page that a live sequence owns now)
+    assert [got[i] for i in ids2] == [want[i] for i in ids]
+    assert int(eng._engine.block_table[len(eng._engine.seq_ids):].abs().sum()) == 0
+    assert eng.guard.checks >= 3 and eng.guard_fallbacks == 0 and eng.guard.nan_events == 0
+    GemmStatus.check(dev)
