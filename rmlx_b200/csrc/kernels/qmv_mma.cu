@@ -461,6 +461,102 @@ moe_down_q4_mma_kernel(const uint32_t* __restrict__ w, const __nv_bfloat16* __re
   pdl_launch_dependents();
 }
 
+// ------------------------------------------------------------------------------------------------
+// Grouped narrow-M expert projections: activation rows sorted by expert (rows offsets[e] ..
+// offsets[e+1] of x belong to local expert e), a handful of rows per expert (decode batches of
+// 16-64 tokens spread over a hundred experts). Block (row tile, expert) brings its weight rows
+// into shared memory ONCE and multiplies them with all of the expert's rows, NCOLS at a time; an
+// expert without rows costs an early exit. A 128-row tensor-core tile per expert would spend the
+// same dequantisation work per weight on rows that do not exist.
+//   SWIGLU: weights [E, 2 I, K] (gate rows, then up rows), out[r, i] = silu(gate) * up, N = I;
+//           tile tl holds gate rows i0 + 8 tl + [0, 8) in image rows 16 tl + [0, 8) and the
+//           matching up rows in 16 tl + [8, 16).
+//   else:   weights [E, N, K], out[r, n] = W[e][n, :] . x[r, :].
+// grid = (row tiles, local experts).
+// ------------------------------------------------------------------------------------------------
+template <int NCOLS, int TILES, bool SWIGLU>
+__global__ void __launch_bounds__(kQThreads)
+grouped_qmv_mma_kernel(const uint32_t* __restrict__ w, const __nv_bfloat16* __restrict__ scales,
+                       const __nv_bfloat16* __restrict__ biases, const __nv_bfloat16* __restrict__ x,
+                       int x_stride, const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out,
+                       int out_stride, int N, int K) {
+  constexpr int ROWS = 16 * TILES;
+  extern __shared__ __align__(128) char smem[];
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ float part[kQWarps][TILES][16][8];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int e = blockIdx.y;
+  const WTile wt{K};
+  char* wimg = smem;
+  char* xst = smem + ((wt.bytes(ROWS) + 127) & ~size_t(127));
+  const size_t cstride = QStage::col_bytes(K);
+  const int first = blockIdx.x * (SWIGLU ? 8 * TILES : ROWS);   // first output row / first gate row
+  pdl_launch_dependents();
+  pdl_wait();                       // the offsets come from the routing kernel
+  const int r0 = offsets[e], r1 = offsets[e + 1];
+  if (r1 <= r0) return;             // nothing routed to this expert (block-uniform)
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_init(&bar, 1);
+      fence_mbar_init();
+      mbar_arrive_expect_tx(&bar, uint32_t(ROWS) * (wt.wbytes() + 2 * wt.sbytes()));
+    }
+    __syncwarp();
+    for (int r = lane; r < ROWS; r += 32) {
+      size_t grow;
+      if (SWIGLU) {
+        const int tl = r >> 4, rr = r & 15;
+        const int i = min(first + tl * 8 + (rr & 7), N - 1);
+        grow = size_t(e) * 2 * N + (rr < 8 ? i : N + i);
+      } else {
+        grow = size_t(e) * N + min(first + r, N - 1);
+      }
+      wt.issue_row(wimg, ROWS, r, w, scales, biases, grow, &bar);
+    }
+  }
+  int G0, G1;
+  warp_group_range(K >> 6, warp, G0, G1);
+  for (int c0 = r0; c0 < r1; c0 += NCOLS) {
+    const int nc = min(NCOLS, r1 - c0);
+    // columns beyond nc keep whatever they held: MMA columns are independent and theirs are not stored
+#pragma unroll
+    for (int b = 0; b < NCOLS; ++b)
+      if (b < nc) QStage::stage(xst + b * cstride, x + size_t(c0 + b) * x_stride, nullptr, K, nullptr);
+    __syncthreads();
+    if (c0 == r0) wait_weights(&bar, 0);
+#pragma unroll
+    for (int tl = 0; tl < TILES; ++tl) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      qmv_tile_groups<NCOLS>(wt, wimg, ROWS, tl * 16 + g, tl * 16 + g + 8, xst, cstride, G0, G1, acc);
+      part[warp][tl][g][2 * t] = acc[0]; part[warp][tl][g][2 * t + 1] = acc[1];
+      part[warp][tl][g + 8][2 * t] = acc[2]; part[warp][tl][g + 8][2 * t + 1] = acc[3];
+    }
+    __syncthreads();
+    if (SWIGLU) {
+      for (int idx = threadIdx.x; idx < TILES * 8 * NCOLS; idx += kQThreads) {
+        const int col = idx / (TILES * 8), rem = idx - col * (TILES * 8);
+        const int tl = rem >> 3, gg = rem & 7, i = first + tl * 8 + gg;
+        if (col >= nc || i >= N) continue;
+        float gt = 0.f, up = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < kQWarps; ++wv) { gt += part[wv][tl][gg][col]; up += part[wv][tl][gg + 8][col]; }
+        out[size_t(c0 + col) * out_stride + i] = __float2bfloat16_rn(gt / (1.f + __expf(-gt)) * up);
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < ROWS * NCOLS; idx += kQThreads) {
+        const int col = idx / ROWS, rr = idx - col * ROWS, n = first + rr;
+        if (col >= nc || n >= N) continue;
+        float v = 0.f;
+#pragma unroll
+        for (int wv = 0; wv < kQWarps; ++wv) v += part[wv][rr >> 4][rr & 15][col];
+        out[size_t(c0 + col) * out_stride + n] = __float2bfloat16_rn(v);
+      }
+    }
+    __syncthreads();                // the next chunk overwrites the staged columns and the partials
+  }
+  pdl_launch_dependents();
+}
+
 }  // namespace rb
 
 using namespace rb;
@@ -571,4 +667,45 @@ extern "C" int rmlx_moe_down_q4_mma(const void* w, const void* scales, const voi
   }
   if (out_f32) RB_QDOWN(true) else RB_QDOWN(false)
 #undef RB_QDOWN
+}
+
+// Shapes the grouped narrow-M kernels take: K a multiple of 512 and the block's image within
+// shared memory for the chosen variant (0: 8 columns x 16 rows; 1: 4 columns x 32 rows).
+extern "C" int rmlx_moe_grouped_q4_mma_supported(int K, int variant) {
+  if (K % 512 || variant < 0 || variant > 1) return 0;
+  const WTile wt{K};
+  const size_t smem = ((wt.bytes(variant ? 32 : 16) + 127) & ~size_t(127)) + QStage::col_bytes(K) * (variant ? 4 : 8);
+  return smem <= 200 * 1024;
+}
+
+template <int NCOLS, int TILES, bool SWIGLU>
+static int launch_grouped_qmv(const void* w, const void* sc, const void* bi, const void* x, int x_stride,
+                              const int* offsets, void* out, int out_stride, int experts, int N, int K,
+                              int pdl, cudaStream_t st) {
+  const WTile wt{K};
+  const size_t smem = ((wt.bytes(16 * TILES) + 127) & ~size_t(127)) + QStage::col_bytes(K) * NCOLS;
+  auto kern = grouped_qmv_mma_kernel<NCOLS, TILES, SWIGLU>;
+  RB_CHECK(set_max_smem(kern, smem));
+  const int per = SWIGLU ? 8 * TILES : 16 * TILES;
+  return launch(kern, dim3((N + per - 1) / per, experts), dim3(kQThreads), smem, st, pdl != 0,
+                static_cast<const uint32_t*>(w), static_cast<const __nv_bfloat16*>(sc),
+                static_cast<const __nv_bfloat16*>(bi), static_cast<const __nv_bfloat16*>(x), x_stride,
+                offsets, static_cast<__nv_bfloat16*>(out), out_stride, N, K);
+}
+
+// x [R, K] bf16, rows grouped by expert: rows offsets[e] .. offsets[e+1] belong to local expert e
+// (offsets: experts + 1 ints on the device, absolute row numbers). swiglu != 0: w [experts, 2 N, K]
+// -> out[r, 0..N) = silu(gate) * up; else w [experts, N, K] -> out[r, 0..N). Rows of x outside
+// every local expert's range leave their rows of out untouched.
+extern "C" int rmlx_moe_grouped_q4_mma(const void* w, const void* scales, const void* biases,
+                                       const void* x, int x_stride, const int* offsets, void* out,
+                                       int out_stride, int experts, int N, int K, int swiglu,
+                                       int variant, int pdl, cudaStream_t st) {
+  if (experts < 1 || experts > 65535 || N < 1 || !rmlx_moe_grouped_q4_mma_supported(K, variant)) return -2;
+#define RB_GQ(NC, TL)                                                                               \
+  return swiglu ? launch_grouped_qmv<NC, TL, true>(w, scales, biases, x, x_stride, offsets, out, out_stride, experts, N, K, pdl, st) \
+                : launch_grouped_qmv<NC, TL, false>(w, scales, biases, x, x_stride, offsets, out, out_stride, experts, N, K, pdl, st);
+  if (variant == 0) { RB_GQ(8, 1) }
+  RB_GQ(4, 2)
+#undef RB_GQ
 }
