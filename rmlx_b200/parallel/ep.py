@@ -38,8 +38,45 @@ class DispatchLayout:
     top_k: int
 
 
+def fp8_quant_rows(x: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor]:
+    """[n, d] -> (E4M3 codes as uint8 [n, d], fp32 scale [n]): scale = max|row| / 448, the wire
+    format of the reference's FP8 exchange (crates/rmlx-distributed/src/fp8_exchange.rs:85-160).
+    bf16 rows on a GPU go through this package's kernel, everything else through torch."""
+    n, d = x.shape
+    if x.is_cuda and x.dtype == torch.bfloat16 and n > 0:
+        from .. import _lib
+        q = torch.empty(n, d, dtype=torch.uint8, device=x.device)
+        scale = torch.empty(n, dtype=torch.float32, device=x.device)
+        xc = x.contiguous()
+        _lib.check(_lib.cuda().rmlx_fp8_quant_rows(xc.data_ptr(), q.data_ptr(), scale.data_ptr(), n, d,
+                                                   _lib.stream_ptr()), "fp8_quant_rows")
+        return q, scale
+    xf = x.float()
+    amax = xf.abs().amax(-1, keepdim=True) if n else xf.new_zeros(0, 1)
+    scale = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    return (xf / scale).to(torch.float8_e4m3fn).view(torch.uint8), scale.squeeze(-1)
+
+
+def fp8_dequant_rows(q: torch.Tensor, scale: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    n, d = q.shape
+    if q.is_cuda and dtype == torch.bfloat16 and n > 0:
+        from .. import _lib
+        out = torch.empty(n, d, dtype=torch.bfloat16, device=q.device)
+        _lib.check(_lib.cuda().rmlx_fp8_dequant_rows(q.contiguous().data_ptr(), scale.contiguous().data_ptr(),
+                                                     out.data_ptr(), n, d, _lib.stream_ptr()), "fp8_dequant_rows")
+        return out
+    return (q.view(torch.float8_e4m3fn).float() * scale[:, None]).to(dtype)
+
+
 class EpExchange:
-    def __init__(self, group: Group, num_experts: int):
+    """``payload="fp8"``: rows cross the wire as E4M3 codes plus one fp32 scale per row (d + 4
+    bytes instead of 2 d), in both directions; ``wire_bytes`` counts what was sent either way."""
+
+    def __init__(self, group: Group, num_experts: int, payload: str = "bf16"):
+        if payload not in ("bf16", "fp8"):
+            raise ValueError("payload is 'bf16' (rows as they are) or 'fp8'")
+        self.payload = payload
+        self.wire_bytes = 0
         self.group = group
         self.world, self.rank = group.world_size, group.local_rank
         if num_experts % self.world:
@@ -58,7 +95,7 @@ class EpExchange:
         recv_counts = self.group.all_to_all(
             torch.tensor(send_counts, dtype=torch.int64, device=x.device)).tolist() \
             if self.world > 1 else list(send_counts)
-        got = self.group.all_to_all(rows, send_counts, recv_counts)
+        got = self._rows_all_to_all(rows, send_counts, recv_counts)
         got_e = self.group.all_to_all(meta, send_counts, recv_counts)
         perm = torch.argsort(got_e, stable=True)             # group by local expert
         counts = torch.bincount(got_e, minlength=self.e_local)
@@ -67,11 +104,21 @@ class EpExchange:
         layout = DispatchLayout(order, send_counts, recv_counts, got_e[perm], perm, offsets, t, k)
         return got[perm], layout
 
+    def _rows_all_to_all(self, rows: torch.Tensor, send_counts: List[int], recv_counts: List[int]) -> torch.Tensor:
+        if self.payload == "bf16":
+            self.wire_bytes += rows.numel() * rows.element_size()
+            return self.group.all_to_all(rows, send_counts, recv_counts)
+        q, scale = fp8_quant_rows(rows)
+        self.wire_bytes += q.numel() + 4 * scale.numel()
+        got_q = self.group.all_to_all(q, send_counts, recv_counts)
+        got_s = self.group.all_to_all(scale, send_counts, recv_counts)
+        return fp8_dequant_rows(got_q, got_s, rows.dtype)
+
     def combine(self, y: torch.Tensor, wts: torch.Tensor, layout: DispatchLayout) -> torch.Tensor:
         """y: expert outputs for the grouped rows. Returns sum_k w[t,k] * y(t,k) as fp32 [T, D]."""
         arrival = torch.empty_like(y)
         arrival[layout.recv_perm] = y                        # back to arrival order
-        back = self.group.all_to_all(arrival, layout.recv_counts, layout.send_counts)
+        back = self._rows_all_to_all(arrival, layout.recv_counts, layout.send_counts)
         out = torch.zeros(layout.num_tokens, y.shape[-1], dtype=torch.float32, device=y.device)
         pair = layout.order
         w = wts.reshape(-1)[pair].float()

@@ -98,6 +98,19 @@ def _group_worker(rank, world, port, q):
         ok &= torch.allclose(got, want, atol=1e-5)
         grouped = full.with_strategy(MoeStrategy.GROUPED).forward(x)
         ok &= torch.allclose(grouped, want, atol=1e-5)
+        # the same exchange with FP8 rows on the wire: E4M3 codes + one scale per row, both ways
+        ex8 = ep.EpExchange(g, E, payload="fp8")
+        got8 = MoeLayer(cfg, router, ExpertGroup.from_experts(mine, dtype=torch.float32)).with_exchange(ex8).forward(x)
+        rel = float((got8 - want).norm() / want.norm())
+        ok &= 1e-4 < rel < 6e-2                           # E4M3: 3 mantissa bits, twice
+        # every pair crosses once out and once back: summed over the ranks, 2 x world x T x K rows
+        total = float(g.allreduce(torch.tensor([float(ex8.wire_bytes)])))
+        ok &= total == 2 * world * (T * K) * (D_ + 4)
+        rows = torch.randn(5, D_) * 3
+        qr, sr = ep.fp8_quant_rows(rows)
+        back = ep.fp8_dequant_rows(qr, sr, torch.float32)
+        ok &= qr.dtype == torch.uint8 and float((back - rows).abs().max() / rows.abs().max()) < 0.07
+        ok &= torch.allclose(back.abs().amax(-1), rows.abs().amax(-1), rtol=1e-6)   # the row maximum is exact
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
