@@ -1,4 +1,4 @@
-"""In-tree native build: every ``.cu`` under ``csrc/kernels`` and ``csrc/comm`` is compiled for
+"""In-tree native build: every ``.cu`` under ``csrc/kernels``, ``csrc/comm`` and ``csrc/runtime`` is compiled for
 sm_100a and linked into ``lib/librmlx_b200_cuda.so``; every ``.cpp`` under ``csrc/host`` goes into
 ``lib/librmlx_b200_host.so`` (pure C++, loadable without a GPU).
 
@@ -75,7 +75,8 @@ def _compile_one(args) -> tuple[Path, bool, str]:
 
 def _sources(kind: str) -> list[Path]:
     if kind in ("cuda", "cuda_bounds"):
-        return sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu"))
+        return sorted((CSRC / "kernels").glob("*.cu")) + sorted((CSRC / "comm").glob("*.cu")) + \
+            sorted((CSRC / "runtime").glob("*.cu"))
     return sorted((CSRC / "host").glob("*.cpp"))
 
 

@@ -22,7 +22,7 @@ import torch
 
 from . import _build
 
-_CODES = {"p": c_void_p, "i": c_int, "f": c_float, "q": c_longlong}
+_CODES = {"p": c_void_p, "i": c_int, "f": c_float, "q": c_longlong, "Q": ctypes.c_ulonglong, None: None}
 
 # name -> (argument codes, restype code)
 _CUDA_SIGS: Dict[str, tuple] = {

@@ -78,11 +78,17 @@ class CachedDecode:
         # bucket that holds the bound rows, so a serving engine sized for 8 rows does not pay for
         # 8 when one sequence is left. Split counts and attention scratch are planned per bucket.
         self.buckets = tuple(b for b in (1, 2, 4, 8, 16, 32, 64) if b < B) + (B,)
-        self.graphs = GraphCache(max_entries=len(self.buckets))
+        # The steps are recorded and replayed by the native graph store (csrc/runtime/graph_exec.cu)
+        # on one GPU; tensor-parallel engines keep torch's graphs unless RMLX_NATIVE_GRAPHS=1
+        # (RMLX_NATIVE_GRAPHS=0 switches the native store off everywhere).
+        native = os.environ.get("RMLX_NATIVE_GRAPHS", "1" if model.layout.world == 1 else "0") == "1"
+        self.graphs = GraphCache(max_entries=len(self.buckets), native=native)
         self._splits_arg = splits
         self._fd = {}
         self.splits = splits or D.default_splits(B, hkv, gt, cfg.max_seq_len)
         self.fd_scratch = self._fd_plan(B)[1]
+        for nb in self.buckets:       # planned up front: a step that allocates nothing can be recorded natively
+            self._fd_plan(nb)
         moe = cfg.ff_type.moe
         if moe is not None:
             k = moe.num_experts_per_token

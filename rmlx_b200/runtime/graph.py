@@ -21,12 +21,24 @@ import torch
 
 
 class GraphCache:
-    def __init__(self, max_entries: int = 64):
+    """``native=True``: graphs are recorded, kept and replayed by the native store
+    (csrc/runtime/graph_exec.cu through ``runtime.native_graph.NativeGraphStore``) instead of
+    ``torch.cuda.CUDAGraph``. A natively recorded function must not allocate; the warm-up run is
+    watched, and a function whose warm-up asked torch's allocator for memory is captured through
+    torch instead (``native_refused`` counts those)."""
+
+    def __init__(self, max_entries: int = 64, native: bool = False):
         self.max_entries = max_entries
         self._g: "OrderedDict[Hashable, object]" = OrderedDict()
         self.hits = 0
         self.misses = 0
         self.captures = 0
+        self.native = native
+        self.native_captures = 0
+        self.native_refused = 0
+        self.capture_failures = 0      # recordings that were invalidated and tried again
+        self.eager_fallbacks = 0       # keys that run launch by launch because recording kept failing
+        self._store = None
 
     def __len__(self) -> int:
         return len(self._g)
@@ -43,13 +55,15 @@ class GraphCache:
             self.hits += 1
             return g
         self.misses += 1
-        g = self._capture(fn, warmup, restore, device)
+        g = self._capture(fn, warmup, restore, device, key)
         self._g[key] = g
         if len(self._g) > self.max_entries:
-            self._g.popitem(last=False)
+            _, old = self._g.popitem(last=False)
+            if isinstance(old, _NativeReplay):
+                old.drop()
         return g
 
-    def _capture(self, fn, warmup, restore=None, device=None):
+    def _capture(self, fn, warmup, restore=None, device=None, key=None):
         self.captures += 1
         if not torch.cuda.is_available():
             return _HostReplay(fn)
@@ -57,26 +71,90 @@ class GraphCache:
         PERF.add("graph_captures")
         s = torch.cuda.Stream(device=device)
         s.wait_stream(torch.cuda.current_stream(device))
+        allocs0 = torch.cuda.memory_stats(device).get("allocation.all.allocated", 0)
         with torch.cuda.stream(s):
-            for _ in range(warmup):
+            for _ in range(max(warmup, 1) if self.native else warmup):
                 fn()
+        allocated = torch.cuda.memory_stats(device).get("allocation.all.allocated", 0) - allocs0
         torch.cuda.current_stream(device).wait_stream(s)
         torch.cuda.synchronize(device)
         if restore is not None:
             restore()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=s):
-            fn()
+        if self.native:
+            if allocated == 0:
+                g = self._capture_native(fn, restore, device, key)
+                if g is not None:
+                    return g
+            else:
+                self.native_refused += 1
+        # A recording can be invalidated from outside (another thread's call, a stream left in an
+        # odd state): try once more on another stream, then run launch by launch rather than fail.
+        for _ in range(2):
+            g = torch.cuda.CUDAGraph()
+            try:
+                with torch.cuda.graph(g, stream=s):
+                    fn()
+            except Exception as e:                       # noqa: BLE001
+                if "captur" not in str(e).lower():
+                    raise
+                self.capture_failures += 1
+                del g
+                torch.cuda.synchronize(device)
+                if restore is not None:
+                    restore()
+                s = torch.cuda.Stream(device=device)
+                continue
+            if restore is not None:
+                restore()
+            torch.cuda.synchronize(device)
+            return g
+        self.eager_fallbacks += 1
+        return _HostReplay(fn)
+
+    def _capture_native(self, fn, restore, device, key):
+        from .. import _lib
+        from .native_graph import NativeGraphStore
+        if self._store is None:
+            # the store's own bound is one above this cache's: eviction is decided here
+            self._store = NativeGraphStore(self.max_entries + 1)
+        try:
+            self._store.capture(key, fn)
+        except _lib.NativeError as e:
+            if "captur" not in str(e).lower():
+                raise
+            self.capture_failures += 1
+            torch.cuda.synchronize(device)
+            if restore is not None:
+                restore()
+            return None
         if restore is not None:
             restore()
         torch.cuda.synchronize(device)
-        return g
+        self.native_captures += 1
+        return _NativeReplay(self._store, key)
 
     def invalidate(self, key: Optional[Hashable] = None) -> None:
+        dropped = list(self._g.values()) if key is None else [self._g.get(key)]
+        for g in dropped:
+            if isinstance(g, _NativeReplay):
+                g.drop()
         if key is None:
             self._g.clear()
         else:
             self._g.pop(key, None)
+
+
+class _NativeReplay:
+    """Replays a graph of the native store on the current stream."""
+
+    def __init__(self, store, key):
+        self._store, self._key = store, key
+
+    def replay(self):
+        self._store.launch(self._key)
+
+    def drop(self):
+        self._store.invalidate(self._key)
 
 
 class _HostReplay:

@@ -449,42 +449,3 @@ def test_awq_and_gptq_dequant_kernels_are_exact(dev, q4_path):
         want = L.gptq_dequantize(qw2, qz2, sc2, g_idx)
         got = L.gptq_dequantize(qw2.to(dev), qz2.to(dev), sc2.to(dev), None if g_idx is None else g_idx.to(dev))
         assert got.is_cuda and torch.equal(got.cpu(), want)
-
-
-@pytest.mark.parametrize("variant", [0, 1])
-def test_narrow_grouped_expert_ffn(dev, variant, q4_path):
-    """The narrow-M grouped expert kernels (a few sorted rows per expert, 4-bit weights) against
-    fp32: experts without rows, one row, and more rows than one pass holds; a rank holding a slice
-    of the experts leaves the other experts' rows zero."""
-    if q4_path != "stream":
-        pytest.skip("one run is enough: the kernel does not depend on the mat-vec path")
-    from rmlx_b200.ops.grouped import narrow_expert_ffn, narrow_supported
-    e, d, i = 6, 1024, 512
-    wgu = _w(2 * i, d, "q4", dev, experts=e, seed=18)
-    wdn = _w(d, i, "q4", dev, experts=e, seed=19)
-    counts = [3, 0, 1, 11, 0, 8]
-    off = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=dev)
-    r = sum(counts)
-    assert narrow_supported(wgu, wdn, variant)
-    torch.manual_seed(20)
-    xs = torch.randn(r, d, device=dev).to(torch.bfloat16)
-    gu_d, dn_d = wgu.dequantized(), wdn.dequantized()
-    want = torch.zeros(r, d, device=dev)
-    want_act = torch.zeros(r, i, device=dev)
-    for ex in range(e):
-        lo, hi = int(off[ex]), int(off[ex + 1])
-        h = xs[lo:hi].float() @ gu_d[ex].t()
-        a = (torch.nn.functional.silu(h[:, :i]) * h[:, i:]).to(torch.bfloat16).float()
-        want_act[lo:hi] = a
-        want[lo:hi] = a @ dn_d[ex].t()
-    got = narrow_expert_ffn(xs, off, wgu, wdn, variant=variant)
-    _close(got, want)
-    # experts 2..4 only (a rank's slice): rows of the other experts stay zero
-    sl_gu, sl_dn = wgu.experts_slice(2, 5), wdn.experts_slice(2, 5)
-    part = narrow_expert_ffn(xs, off[2:6], sl_gu, sl_dn, zero_rest=True, variant=variant)
-    lo, hi = int(off[2]), int(off[5])
-    _close(part[lo:hi], want[lo:hi])
-    assert float(part[:lo].abs().sum()) == 0.0 and float(part[hi:].abs().sum()) == 0.0
-    torch.cuda.synchronize()
-    from rmlx_b200 import _lib
-    assert _lib.cuda().rmlx_qmv_status() == 0

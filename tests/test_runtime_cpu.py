@@ -115,3 +115,23 @@ def test_hazard_tracker_learns_the_results_of_an_operation():
     assert h.submit("compute", reads=[(120, 130)]) == [(0, "RAW")]
     h.retire_all()
     assert h.in_flight() == 0
+
+
+def test_native_graph_store_bookkeeping_without_a_gpu():
+    """The keyed store's host side: misses are counted, an unknown key cannot be launched, nothing
+    to drop. (Recording and replaying need a GPU.)"""
+    from rmlx_b200 import _lib
+    try:
+        _lib.cuda()
+    except Exception as e:                          # noqa: BLE001
+        pytest.skip(f"CUDA library not available: {e}")
+    from rmlx_b200.runtime.native_graph import NativeGraphStore
+    store = NativeGraphStore(max_entries=3)
+    assert not store.has(("decode", 4)) and not store.has("x")
+    with pytest.raises(KeyError):
+        store.launch(("decode", 4))
+    assert store.invalidate(("decode", 4)) == 0 and store.invalidate() == 0
+    st = store.stats()
+    assert st["entries"] == 0 and st["misses"] == 2 and st["hits"] == 0 and st["captures"] == 0
+    store.close()
+    store.close()                                   # idempotent
