@@ -1,6 +1,7 @@
 """nn layers and model presets on CPU (the shape of crates/rmlx-nn/tests/nn_tests.rs): linears and
 their quantised imports, tensor-parallel linears, the KV cache family, sliding windows, latent
 attention, LoRA with a numerical-gradient check, model presets."""
+import pytest
 import torch
 
 from rmlx_b200.config import AttentionConfig
@@ -162,6 +163,21 @@ def test_model_presets():
         toks = model.generate_greedy(torch.arange(12) % cfg.vocab_size, 5)
         full = model.forward(torch.cat([torch.arange(12) % cfg.vocab_size, torch.tensor(toks[:-1])]))
         assert [int(full[11 + i].argmax()) for i in range(5)] == toks
+    # the architecture classes: constructors check the architecture, accessors as in the reference
+    qm = qwen.Qwen2Model.from_config()
+    assert qm.num_layers() == 2 and qm.config() is qm.cfg and qm.inner() is qm
+    assert qm.generate_greedy(torch.arange(6), 3) == TransformerModel(qm.w).generate_greedy(torch.arange(6), 3)
+    with pytest.raises(ValueError):
+        qwen.Qwen2Model.from_config(mixtral.mixtral_tiny())
+    mm = mixtral.MixtralModel.from_config()
+    assert mm.sliding_window_size() == 8 and mm.config().num_experts == 4 and mm.layer(1) is mm.w.layers[1]
+    assert mm.layer(2) is None and mm.num_layers() == 2
+    full = mixtral.mixtral_8x7b_full()
+    assert (full.sliding_window_size, full.num_experts, full.num_experts_per_token) == (4096, 8, 2)
+    with pytest.raises(ValueError):
+        mixtral.MixtralConfig(full.base, 4096, 8, 3).validate()       # disagrees with the base config
+    with pytest.raises(ValueError):
+        mixtral.MixtralModel.from_config(qwen.qwen2_tiny())
     ds = deepseek.DeepSeekV3Model(deepseek.deepseek_tiny(), std=0.1)
     ids = torch.arange(9) % 256
     full = ds.forward(ids)
