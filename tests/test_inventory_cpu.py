@@ -74,17 +74,50 @@ def test_prefill_plan_and_pool():
     assert [s.name for s in PrefillPlan(dense, 8).steps][-2:] == ["gate_up", "down"]
 
 
-def test_conv_wrappers_match_torch():
+def test_conv_layers_against_the_tap_by_tap_definition():
+    """Channels-first layers (the reference's layout) and the channels-last option against the
+    explicit definition; weight validation; a layer that waits for its weights."""
+    from rmlx_b200.nn.conv import (Conv1dConfig, Conv2dConfig, conv1d_direct, conv2d_direct, conv_out_len)
     torch.manual_seed(1)
-    x = torch.randn(2, 10, 3)
-    w = torch.randn(5, 3, 3)
-    y = Conv1d(w, torch.zeros(5), padding=1)(x)
-    ref = torch.nn.functional.conv1d(x.transpose(1, 2), w.permute(0, 2, 1), None, padding=1).transpose(1, 2)
-    assert y.shape == (2, 10, 5) and torch.allclose(y, ref, atol=1e-5)
-    x2 = torch.randn(1, 6, 6, 4)
-    w2 = torch.randn(8, 3, 3, 2)
-    y2 = Conv2d(w2, stride=2, padding=1, groups=2)(x2)
-    assert y2.shape == (1, 3, 3, 8)
+    x = torch.randn(2, 6, 19)
+    w = torch.randn(8, 3, 4)                                    # groups = 2: 6 / 2 input channels per group
+    b = torch.randn(8)
+    layer = Conv1d(w, b, stride=2, padding=3, dilation=2, groups=2)
+    y = layer(x)
+    assert y.shape == (2, 8, layer.out_len(19)) and layer.out_len(19) == conv_out_len(19, 4, 2, 3, 2) == 10
+    assert torch.allclose(y, conv1d_direct(x, w, b, 2, 3, 2, 2), atol=1e-4)
+    cl = Conv1d(w.permute(0, 2, 1).contiguous(), b, stride=2, padding=3, dilation=2, groups=2, channels_last=True)
+    assert torch.allclose(cl(x.transpose(1, 2)), y.transpose(1, 2), atol=1e-5)
+
+    lazy = Conv1d(Conv1dConfig(6, 8, 4, groups=2, has_bias=True))
+    assert not lazy.has_weights() and lazy.weight() is None
+    with pytest.raises(ValueError):
+        lazy(x)                                                 # weights not loaded
+    with pytest.raises(ValueError):
+        lazy.load_weights(torch.randn(8, 6, 4), b)              # wrong C_in / groups
+    with pytest.raises(ValueError):
+        lazy.load_weights(w)                                    # the config asks for a bias
+    lazy.load_weights(w, b)
+    assert lazy.has_weights() and lazy.config().groups == 2 and lazy.bias() is b
+    with pytest.raises(ValueError):
+        lazy(torch.randn(2, 5, 19))                             # wrong channel count
+    with pytest.raises(ValueError):
+        Conv1dConfig(6, 8, 3, groups=4).validate()
+
+    x2 = torch.randn(1, 4, 9, 7)
+    w2 = torch.randn(6, 2, 3, 2)
+    conv = Conv2d(w2, None, stride=(2, 1), padding=(1, 0), dilation=(1, 2), groups=2)
+    y2 = conv(x2)
+    assert y2.shape == (1, 6, *conv.out_size(9, 7)) and conv.out_size(9, 7) == (5, 5)
+    assert torch.allclose(y2, conv2d_direct(x2, w2, None, (2, 1), (1, 0), (1, 2), 2), atol=1e-4)
+    nhwc = Conv2d(w2.permute(0, 2, 3, 1).contiguous(), stride=(2, 1), padding=(1, 0), dilation=(1, 2), groups=2,
+                  channels_last=True)
+    assert torch.allclose(nhwc(x2.permute(0, 2, 3, 1)), y2.permute(0, 2, 3, 1), atol=1e-5)
+    lazy2 = Conv2d(Conv2dConfig(4, 6, (3, 2), groups=2))
+    with pytest.raises(ValueError):
+        lazy2.load_weights(torch.randn(6, 2, 2, 3))
+    lazy2.load_weights(w2)
+    assert lazy2.has_weights()
 
 
 def test_dtype_table():
