@@ -13,11 +13,29 @@ wait is required. ``serialize=True`` turns every dependency check into "always w
 used to bisect suspected races (the reference's ``tracked_hazards`` feature)."""
 from __future__ import annotations
 
+import gc
 from collections import OrderedDict
+from contextlib import contextmanager
 from dataclasses import dataclass
 from typing import Callable, Hashable, List, Optional, Tuple
 
 import torch
+
+
+@contextmanager
+def _no_cyclic_gc():
+    """No automatic garbage collection while a stream is recording: a collection that happens to
+    run inside the recording may finalise an object whose destructor makes a CUDA call that is not
+    allowed during stream capture (another engine's graph being destroyed, a mapped region being
+    released), which invalidates the recording. Garbage is collected first, outside it."""
+    was_enabled = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 class GraphCache:
@@ -87,12 +105,12 @@ class GraphCache:
                     return g
             else:
                 self.native_refused += 1
-        # A recording can be invalidated from outside (another thread's call, a stream left in an
-        # odd state): try once more on another stream, then run launch by launch rather than fail.
+        # A recording can still be invalidated from outside (another thread's call): try once more
+        # on another stream, then run launch by launch rather than fail.
         for _ in range(2):
             g = torch.cuda.CUDAGraph()
             try:
-                with torch.cuda.graph(g, stream=s):
+                with _no_cyclic_gc(), torch.cuda.graph(g, stream=s):
                     fn()
             except Exception as e:                       # noqa: BLE001
                 if "captur" not in str(e).lower():
@@ -118,7 +136,8 @@ class GraphCache:
             # the store's own bound is one above this cache's: eviction is decided here
             self._store = NativeGraphStore(self.max_entries + 1)
         try:
-            self._store.capture(key, fn)
+            with _no_cyclic_gc():
+                self._store.capture(key, fn)
         except _lib.NativeError as e:
             if "captur" not in str(e).lower():
                 raise

@@ -135,3 +135,66 @@ def test_native_graph_store_bookkeeping_without_a_gpu():
     assert st["entries"] == 0 and st["misses"] == 2 and st["hits"] == 0 and st["captures"] == 0
     store.close()
     store.close()                                   # idempotent
+
+
+def test_recordings_run_without_cyclic_gc_and_fall_back_when_invalidated(monkeypatch):
+    """The graph cache's handling of a recording that gets invalidated, against a stand-in for
+    torch.cuda: garbage collection is off inside the recording, a failed recording is tried once
+    more, a second failure turns the key into launch-by-launch replay, other errors pass through."""
+    import contextlib
+    import gc
+    import types
+
+    with graph._no_cyclic_gc():
+        assert not gc.isenabled()
+    assert gc.isenabled()
+    gc.disable()
+    try:
+        with graph._no_cyclic_gc():
+            pass
+        assert not gc.isenabled()                      # a caller's own setting is kept
+    finally:
+        gc.enable()
+
+    class _S:
+        def wait_stream(self, other):
+            pass
+
+    fail = {"left": 0, "msg": "CUDA error: operation failed due to a previous error during capture", "gc": []}
+
+    @contextlib.contextmanager
+    def fake_graph(g, stream=None):
+        fail["gc"].append(gc.isenabled())
+        yield
+        if fail["left"] > 0:
+            fail["left"] -= 1
+            raise RuntimeError(fail["msg"])
+
+    cuda = types.SimpleNamespace(
+        is_available=lambda: True, Stream=lambda device=None: _S(), current_stream=lambda device=None: _S(),
+        memory_stats=lambda device=None: {"allocation.all.allocated": 0},
+        stream=lambda s: contextlib.nullcontext(), synchronize=lambda device=None: None,
+        CUDAGraph=lambda: types.SimpleNamespace(replay=lambda: calls.append("replay")), graph=fake_graph)
+    monkeypatch.setattr(graph, "torch", types.SimpleNamespace(cuda=cuda))
+    calls, restored = [], []
+    fn, restore = (lambda: calls.append("fn")), (lambda: restored.append(1))
+
+    cache = graph.GraphCache()
+    fail["left"] = 1
+    g = cache.get_or_capture("a", fn, warmup=1, restore=restore)
+    assert cache.capture_failures == 1 and cache.eager_fallbacks == 0 and calls == ["fn"] * 3
+    assert fail["gc"] == [False, False] and gc.isenabled()       # no collection inside either attempt
+    g.replay()
+    assert calls[-1] == "replay" and len(restored) == 3          # after warm-up, after the failure, after the capture
+
+    fail["left"] = 2
+    g2 = cache.get_or_capture("b", fn, warmup=1, restore=restore)
+    assert cache.capture_failures == 3 and cache.eager_fallbacks == 1
+    n = len(calls)
+    g2.replay()
+    assert calls[n:] == ["fn"]                                   # launch by launch
+    assert cache.get_or_capture("b", fn) is g2 and len(cache) == 2
+
+    fail["left"], fail["msg"] = 1, "invalid argument"
+    with pytest.raises(RuntimeError):
+        cache.get_or_capture("c", fn, warmup=0)
