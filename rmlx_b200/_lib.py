@@ -97,6 +97,9 @@ def cuda() -> ctypes.CDLL:
                 if not path.exists():
                     _build.build(kinds=("cuda_bounds" if bounds else "cuda",))
                 lib = ctypes.CDLL(str(path))
+                lib.rmlx_bounds_build.restype = c_int
+                if bool(lib.rmlx_bounds_build()) != bounds:
+                    raise NativeError(f"{path.name} is {'not ' if bounds else ''}a bounds-checked build")
                 _bind(lib, _CUDA_SIGS)
                 _register_status_words(lib)
                 _cuda_lib = lib
@@ -178,6 +181,11 @@ def check(rc: int, what: str) -> None:
         raise NativeError(f"{what}: invalid argument or unsupported shape")
     msg = cuda().rmlx_error_string(rc)
     raise NativeError(f"{what}: CUDA error {rc}: {msg.decode() if msg else '?'}")
+
+
+def is_bounds_build() -> bool:
+    """Whether the loaded kernels are the bounds-checked build (RMLX_BOUNDS=1)."""
+    return bool(cuda().rmlx_bounds_build())
 
 
 def bounds_status():
