@@ -138,6 +138,31 @@ def bench_dequant(repeat):
               f"({64 * 4 / 1024 / t_nat:.1f} GB/s of fp32 out, {t_np / t_nat:.1f}x)")
 
 
+def bench_sampler(repeat):
+    """Host-side sampling of one token per row from 151936 logits: the torch-op sampler against the
+    native one (same distribution; each draws from its own seeded generator)."""
+    import torch
+    from rmlx_b200.config import SamplerConfig
+    from rmlx_b200.serve.native import NativeSampler
+    from rmlx_b200.serve.sampler import Sampler
+    torch.manual_seed(0)
+    for rows in (1, 8):
+        logits = torch.randn(rows, 151936)
+        hist = [list(range(0, 400, 3)) for _ in range(rows)]
+        for name, cfg in (("top-k 40, top-p 0.9, penalty 1.1",
+                           SamplerConfig(temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.1, seed=0)),
+                          ("temperature only", SamplerConfig(temperature=0.8, seed=0)),
+                          ("top-p 0.9 only (flat logits: 60 % of the vocabulary is the nucleus)",
+                           SamplerConfig(temperature=0.8, top_p=0.9, seed=0))):
+            t = []
+            for cls in (Sampler, NativeSampler):
+                smp = cls(cfg)
+                smp.sample_batch(logits, hist)
+                t.append(best(lambda: [smp.sample_batch(logits, hist) for _ in range(5)], repeat)[0] / 5)
+            print(f"sampler, {rows} row(s), {name}: torch ops {t[0] * 1e3:6.2f} ms   native {t[1] * 1e3:6.2f} ms "
+                  f"({t[0] / t[1]:.1f}x)")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--requests", type=int, default=256)
@@ -149,6 +174,7 @@ def main():
     bench_prefix_cache(a.repeat)
     bench_loader(a.file_mb, a.repeat)
     bench_dequant(a.repeat)
+    bench_sampler(a.repeat)
 
 
 if __name__ == "__main__":

@@ -45,7 +45,8 @@ class ServingEngine:
         sched_cls = native.NativeScheduler if self.native else Scheduler
         self.sched = sched_cls(scfg, manage_blocks=False, on_admit=self._on_admit,
                                on_evict=self._on_evict, tables_in_meta=False)
-        self.sampler = Sampler(sampler_cfg)
+        # host-side sampling (logits read back to the CPU) runs in the native library as well
+        self.sampler = (native.NativeSampler if self.native else Sampler)(sampler_cfg)
         self.sample_on_device = sample_on_device
         self.greedy = self.sampler.cfg.temperature == 0.0 and self.sampler.cfg.repetition_penalty == 1.0
         self.outputs: Dict[int, List[int]] = {}

@@ -210,3 +210,120 @@ class NativeScheduler:
         self._lib.rmlx_sched_info(self._h, sid, info)
         table = bm.block_table(sid) if bm.has_sequence(sid) else []
         return SeqMeta(sid, int(info[0]), bm.seq_len(sid), table, int(info[1]))
+
+
+# ------------------------------------------------------------------------------------------------
+# sampler
+# ------------------------------------------------------------------------------------------------
+import ctypes as _ct                                                    # noqa: E402
+import os as _os                                                        # noqa: E402
+
+import torch as _torch                                                  # noqa: E402
+
+from .sampler import Sampler, SpecDecodeResult                          # noqa: E402
+
+_FP = _ct.POINTER(_ct.c_float)
+_sampler_bound = False
+
+
+def _sampler_lib():
+    global _sampler_bound
+    lib = _host()
+    if not _sampler_bound:
+        ip = _ct.POINTER(_ct.c_int)
+        sig = {
+            "rmlx_sampler_create": (_ct.c_void_p, [_ct.c_float, _ct.c_int, _ct.c_float, _ct.c_float, _ct.c_uint64]),
+            "rmlx_sampler_destroy": (None, [_ct.c_void_p]),
+            "rmlx_sampler_probabilities": (_ct.c_int, [_ct.c_void_p, _ct.c_void_p, _ct.c_int, ip, _ct.c_int, _ct.c_void_p]),
+            "rmlx_sampler_sample": (_ct.c_int, [_ct.c_void_p, _ct.c_void_p, _ct.c_int, _ct.c_int, ip, ip, ip]),
+            "rmlx_sampler_uniform": (_ct.c_double, [_ct.c_void_p]),
+            "rmlx_sampler_multinomial": (_ct.c_int, [_ct.c_void_p, _ct.c_void_p, _ct.c_int]),
+            "rmlx_spec_greedy_verify": (_ct.c_int, [ip, _ct.c_int, _ct.c_void_p, _ct.c_int, _ct.c_int, ip]),
+            "rmlx_spec_rejection_sample": (_ct.c_int, [_ct.c_void_p, ip, _ct.c_int, _ct.c_void_p, _ct.c_void_p,
+                                                       _ct.c_int, _ct.c_int, ip]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _sampler_bound = True
+    return lib
+
+
+def _f32(t: "_torch.Tensor") -> "_torch.Tensor":
+    return t.detach().to(_torch.float32).contiguous()
+
+
+class NativeSampler(Sampler):
+    """``serve.sampler.Sampler`` whose host-side work (logits or probabilities already on the CPU)
+    runs in the native library (csrc/host/sampler.cpp): distribution shaping, the multinomial draw
+    from the sampler's own seeded generator, and both speculative acceptance rules. Logits that
+    live on a GPU keep the tensor-op path of the base class (only token ids leave the device).
+    The distribution is the base class's to rounding; the random stream is its own, so a seed
+    reproduces a run of this class, not the tokens of the other."""
+
+    def __init__(self, config=None):
+        super().__init__(config)
+        self._lib = _sampler_lib()
+        c = self.cfg
+        seed = c.seed if c.seed is not None else int.from_bytes(_os.urandom(8), "little")
+        self._h = self._lib.rmlx_sampler_create(c.temperature, c.top_k, c.top_p, c.repetition_penalty,
+                                                seed & 0xFFFFFFFFFFFFFFFF)
+        if not self._h:
+            raise ValueError("bad sampler configuration")
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.rmlx_sampler_destroy(h)
+
+    def probabilities(self, logits, history=()):
+        if logits.is_cuda:
+            return super().probabilities(logits, history)
+        l = _f32(logits)
+        out = _torch.empty_like(l)
+        hist = _ints([int(t) for t in history])
+        self._lib.rmlx_sampler_probabilities(self._h, l.data_ptr(), l.numel(), hist, len(history), out.data_ptr())
+        return out
+
+    def sample_token(self, logits, history=()):
+        if logits.is_cuda:
+            return super().sample_token(logits, history)
+        return self.sample_batch(logits.reshape(1, -1), [list(history)])[0]
+
+    def sample_batch(self, logits, histories=None):
+        if logits.is_cuda:
+            return super().sample_batch(logits, histories)
+        l = _f32(logits)
+        rows, vocab = l.shape
+        out = (_ct.c_int * max(1, rows))()
+        hist = off = None
+        if histories is not None and self.cfg.repetition_penalty != 1.0:
+            flat, offs = [], [0]
+            for h in histories:
+                flat += [int(t) for t in h]
+                offs.append(len(flat))
+            hist, off = _ints(flat), _ints(offs)
+        self._lib.rmlx_sampler_sample(self._h, l.data_ptr(), rows, vocab, hist, off, out)
+        return list(out[:rows])
+
+    def greedy_verify(self, draft_tokens, target_logits):          # an instance method here: same call shape
+        if target_logits.is_cuda:
+            return Sampler.greedy_verify(draft_tokens, target_logits)
+        l = _f32(target_logits)
+        nxt = _ct.c_int(-1)
+        draft = [int(t) for t in draft_tokens]
+        n = self._lib.rmlx_spec_greedy_verify(_ints(draft), len(draft), l.data_ptr(), l.shape[0], l.shape[1],
+                                              _ct.byref(nxt))
+        return SpecDecodeResult(n, draft[:n], None if nxt.value < 0 else nxt.value)
+
+    def rejection_sample(self, draft_tokens, draft_probs, target_probs):
+        if draft_probs.is_cuda or target_probs.is_cuda:
+            return super().rejection_sample(draft_tokens, draft_probs, target_probs)
+        pd, pt = _f32(draft_probs), _f32(target_probs)
+        nxt = _ct.c_int(-1)
+        draft = [int(t) for t in draft_tokens]
+        n = self._lib.rmlx_spec_rejection_sample(self._h, _ints(draft), len(draft), pd.data_ptr(), pt.data_ptr(),
+                                                 pt.shape[0], pt.shape[1], _ct.byref(nxt))
+        if n < 0:
+            raise ValueError("draft token outside the vocabulary")
+        return SpecDecodeResult(n, draft[:n], None if nxt.value < 0 else nxt.value)

@@ -240,3 +240,63 @@ def test_drop_front_releases_pages_before_the_window_in_both_managers():
     unreserved.add_sequence(0)
     with pytest.raises(ValueError):
         unreserved.drop_front(0, 1)
+
+
+def test_native_sampler_matches_the_python_sampler():
+    """Distribution shaping (penalty, temperature, top-k, top-p) agrees with the Python class to
+    rounding; draws follow the distribution and are reproducible from the seed; the speculative
+    acceptance rules agree on deterministic cases and keep the target distribution."""
+    import torch
+    from rmlx_b200.config import SamplerConfig
+    from rmlx_b200.serve.native import NativeSampler
+    from rmlx_b200.serve.sampler import Sampler
+    g = torch.Generator().manual_seed(3)
+    logits = torch.randn(4, 97, generator=g) * 2
+    hist = [[1, 5, 5, 60], [], [96, 0], [3]]
+    for cfg in (SamplerConfig(temperature=0.7, top_k=5, top_p=0.9, repetition_penalty=1.3, seed=1),
+                SamplerConfig(temperature=1.0, seed=1), SamplerConfig(temperature=1.5, top_p=0.5, seed=1),
+                SamplerConfig(temperature=0.9, top_k=200, seed=1), SamplerConfig(repetition_penalty=2.0)):
+        py, nat = Sampler(cfg), NativeSampler(cfg)
+        for r in range(4):
+            want, got = py.probabilities(logits[r], hist[r]), nat.probabilities(logits[r], hist[r])
+            assert torch.allclose(got, want, atol=1e-6), cfg
+            assert abs(float(got.sum()) - 1.0) < 1e-5
+        if cfg.temperature == 0.0:
+            assert nat.sample_batch(logits, hist) == py.sample_batch(logits, hist)
+            assert nat.sample_token(logits[0], hist[0]) == py.sample_token(logits[0], hist[0])
+
+    cfg = SamplerConfig(temperature=1.0, seed=11)
+    small = torch.tensor([[2.0, 1.0, 0.0, -1.0, -30.0]])
+    a, b, c = NativeSampler(cfg), NativeSampler(cfg), NativeSampler(SamplerConfig(temperature=1.0, seed=12))
+    draws = [a.sample_batch(small)[0] for _ in range(4000)]
+    assert draws == [b.sample_batch(small)[0] for _ in range(4000)]
+    assert draws != [c.sample_batch(small)[0] for _ in range(4000)]
+    freq = torch.bincount(torch.tensor(draws), minlength=5).float() / len(draws)
+    assert torch.allclose(freq, torch.softmax(small[0], -1), atol=0.03) and freq[4] == 0
+
+    tl = torch.tensor([[0.0, 3.0, 1.0], [5.0, 0.0, 1.0], [0.0, 0.0, 9.0]])
+    for draft in ([1, 0], [1, 2], [2], [1, 0, 2]):
+        want = Sampler.greedy_verify(draft, tl)
+        got = a.greedy_verify(draft, tl)
+        assert (got.num_accepted, got.accepted_tokens, got.correction_token) == (
+            want.num_accepted, want.accepted_tokens, want.correction_token), draft
+
+    pt = torch.tensor([[0.5, 0.3, 0.2, 0.0], [0.1, 0.1, 0.1, 0.7]])
+    same = a.rejection_sample([0], pt[:1], pt)                       # equal distributions: always accepted
+    assert same.num_accepted == 1 and same.accepted_tokens == [0] and same.correction_token in (0, 1, 2, 3)
+    pd = torch.tensor([[0.0, 0.0, 0.0, 1.0]])                        # the target gives the draft token no mass
+    rej = a.rejection_sample([3], pd, pt[:1])
+    assert rej.num_accepted == 0 and rej.correction_token in (0, 1, 2)
+    # the accepted-or-corrected token follows the target distribution whatever the draft distribution
+    pdraft = torch.tensor([[0.1, 0.6, 0.2, 0.1]])
+    out = []
+    for _ in range(6000):
+        d = int(a._lib.rmlx_sampler_multinomial(a._h, pdraft.data_ptr(), 4))
+        r = a.rejection_sample([d], pdraft, pt[:1])
+        out.append(d if r.num_accepted == 1 else r.correction_token)
+    freq = torch.bincount(torch.tensor(out), minlength=4).float() / len(out)
+    assert torch.allclose(freq, pt[0], atol=0.03)
+    with pytest.raises(ValueError):
+        a.rejection_sample([9], pdraft, pt[:1])
+    assert not a._lib.rmlx_sampler_create(1.0, -1, 0.5, 1.0, 0)      # a negative top-k is refused
+    assert not a._lib.rmlx_sampler_create(1.0, 0, 0.0, 1.0, 0)       # so is top-p = 0
