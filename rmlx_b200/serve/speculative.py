@@ -48,7 +48,9 @@ class SpeculativeDecoder:
         if target.cfg.vocab_size != draft.cfg.vocab_size:
             raise ValueError("draft and target must share a vocabulary")
         self.target, self.draft, self.k = target, draft, k
-        self.sampler = Sampler(sampler_cfg)
+        from . import native
+        # host-side shaping, draws and acceptance rules run in the native library when it is there
+        self.sampler = (native.NativeSampler if native.enabled() else Sampler)(sampler_cfg)
         self.greedy = self.sampler.cfg.temperature == 0.0
         self.eos = eos_token_id
         self.stats = SpecStats()
@@ -92,7 +94,7 @@ class SpeculativeDecoder:
             tl = tgt.prefill(torch.tensor([pending] + proposals, device=tgt.device), tc, 0,
                              all_logits=True).float().cpu()
             if self.greedy:
-                res = Sampler.greedy_verify(proposals, tl)
+                res = self.sampler.greedy_verify(proposals, tl)
             else:
                 tp = torch.stack([self.sampler.probabilities(tl[i], out + proposals[:i])
                                   for i in range(k + 1)])
