@@ -177,3 +177,58 @@ def combine_with_layout(expert_out: List[torch.Tensor], idx: torch.Tensor, wts: 
             le, pos = slot // (world * capacity), slot % (world * capacity)
             out[ti] += float(wts[ti, s]) * expert_out[r][le, pos].float()
     return out
+
+
+class GuardedCapacityRouter:
+    """Capacity-limited routing with the overflow guard in the loop, as the reference wires it
+    (crates/rmlx-distributed/src/moe_exchange.rs:556-576 with sparse_guard.rs:80-129): every
+    dispatch reports its dropped pairs to a ``SparseGuard``; when the windowed overflow ratio
+    crosses the guard's first threshold the capacity factor grows (x1.5, bounded), past the second
+    the router stops dropping (capacity = every pair, the dense fallback), and a window below both
+    puts the configured factor back. The capacity-free exchange of this framework never drops;
+    this class is for callers that want the reference's fixed-shape buffers."""
+
+    def __init__(self, num_experts: int, world: int, src_rank: int, capacity_factor: float = 1.0,
+                 guard=None, max_factor: float = 8.0):
+        from .moe_policy import SparseGuard
+        if num_experts % world:
+            raise ValueError("num_experts must divide by the expert-parallel size")
+        self.E, self.world, self.src_rank = num_experts, world, src_rank
+        self.base_factor = self.factor = float(capacity_factor)
+        self.max_factor = float(max_factor)
+        self.guard = guard or SparseGuard()
+        self.dense = False
+        self.total_overflow = 0
+        self.increases = self.dense_fallbacks = self.resets = 0
+
+    def capacity(self, num_tokens: int, top_k: int) -> int:
+        if self.dense:
+            return num_tokens * top_k                    # room for every pair on one expert
+        return expert_capacity(num_tokens, top_k, self.E, self.factor)
+
+    def dispatch(self, x: torch.Tensor, idx: torch.Tensor):
+        """(buffers, route_indices, overflow, capacity) of this step; then the guard's verdict on
+        the step adjusts the capacity of the next ones."""
+        from .moe_policy import GuardAction
+        t, k = idx.shape
+        cap = self.capacity(t, k)
+        factor = cap * self.E / max(1, t * k)            # the factor that yields exactly this capacity
+        bufs, route, overflow = dispatch_with_capacity(x, idx, self.E, self.world, self.src_rank, factor)
+        assert bufs[0].shape[1] == cap
+        self.total_overflow += overflow
+        action = self.guard.record_step(overflow, t * k)
+        if action is GuardAction.INCREASE_CAPACITY and not self.dense:
+            self.factor = min(self.max_factor, self.factor * 1.5)
+            self.increases += 1
+        elif action is GuardAction.DENSE_FALLBACK:
+            if not self.dense:
+                self.dense_fallbacks += 1
+            self.dense = True
+        elif action is GuardAction.RESET:
+            self.factor, self.dense = self.base_factor, False
+            self.resets += 1
+        return bufs, route, overflow, cap
+
+    def combine(self, expert_out: List[torch.Tensor], idx: torch.Tensor, wts: torch.Tensor,
+                route: torch.Tensor, capacity: int) -> torch.Tensor:
+        return combine_with_layout(expert_out, idx, wts, route, self.E, self.world, self.src_rank, capacity)

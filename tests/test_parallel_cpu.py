@@ -227,6 +227,41 @@ def test_capacity_limited_dispatch_matches_reference_semantics():
     assert torch.allclose(y[:4], 2.0 * x[:4]) and y[4:].abs().sum() == 0
 
 
+def test_capacity_router_reacts_to_overflow():
+    """The overflow guard in the loop: a skewed routing raises the capacity factor, a heavily
+    skewed one stops the dropping (every pair fits), balanced steps put the configured factor back;
+    the result with room for every pair equals the unrestricted combination."""
+    torch.manual_seed(0)
+    T, K, E, W, D_ = 16, 2, 8, 2, 4
+    x = torch.randn(T, D_)
+    wts = torch.full((T, K), 0.5)
+    skew = torch.zeros(T, K, dtype=torch.int64); skew[:, 1] = 1          # every token to experts 0 and 1
+    even = torch.stack([torch.arange(T) % E, (torch.arange(T) + 4) % E], 1)
+    r = ep.GuardedCapacityRouter(E, W, src_rank=0, capacity_factor=1.0, guard=SparseGuard(window=4))
+    assert r.capacity(T, K) == 4
+    drops = []
+    for _ in range(4):                                                  # window 1: ratio 0.75 > 0.20
+        _, route, overflow, cap = r.dispatch(x, skew)
+        drops.append(overflow)
+    assert drops == [24] * 4 and cap == 4 and r.dense and r.dense_fallbacks == 1
+    bufs, route, overflow, cap = r.dispatch(x, skew)                    # now nothing is dropped
+    assert overflow == 0 and cap == T * K and (route >= 0).all()
+    outs = [torch.zeros(E // W, W * cap, D_) for _ in range(W)]
+    outs[0][:, :cap] = bufs[0] * 3.0                                    # "experts": y = 3 x (src rank 0's stripe)
+    y = r.combine(outs, skew, wts, route, cap)
+    assert torch.allclose(y, 3.0 * x, atol=1e-6)
+    for _ in range(140):                                                # balanced traffic: the averaged ratio decays
+        r.dispatch(x, even)
+    assert not r.dense and r.factor == 1.0 and r.resets >= 1
+    # a mild skew (a few drops per step) only grows the factor
+    mild = even.clone(); mild[:6, 0] = 0
+    r2 = ep.GuardedCapacityRouter(E, W, src_rank=0, capacity_factor=1.0, guard=SparseGuard(window=4))
+    for _ in range(4):
+        _, _, overflow, _ = r2.dispatch(x, mild)
+    assert 0 < overflow < 0.2 * T * K and r2.factor == 1.5 and not r2.dense and r2.increases == 1
+    assert r2.capacity(T, K) == 6
+
+
 def test_topology_matrix_parser():
     txt = """\tGPU0\tGPU1\tGPU2\tCPU Affinity
 GPU0\t X \tNV18\tNV18\t0-55

@@ -32,6 +32,8 @@ WIRED = {
     "NativePrefixCache": ["serve/engine.py"],
     "drop_front": ["serve/engine.py"],
     "fp8_quant_rows": ["parallel/ep.py"],
+    "SparseGuard": ["parallel/ep.py"],
+    "NativeSampler": ["serve/engine.py", "serve/speculative.py"],
     "narrow_expert_ffn": ["ops/grouped.py"],
 }
 
