@@ -342,6 +342,9 @@ def main():
     status = comm.status() if comm is not None else 0
     launches = eng.launches_per_step
     use_graph = bool(getattr(eng, "use_graph", False))
+    graphs = getattr(eng, "graphs", None)
+    graph_store = "none" if not use_graph else \
+        "native store (csrc/runtime/graph_exec.cu)" if getattr(graphs, "native_captures", 0) else "torch.cuda.CUDAGraph"
     nbytes = weights.nbytes()
     nlayers = cfg.num_layers
     extra = {}
@@ -397,7 +400,7 @@ def main():
                        "weights": "q4 group-64 affine (bf16 activations, fp32 accumulate)"
                        if args.weights == "q4" else "bf16",
                        "global_batch": B, "seq_len": args.ctx, "kv": "paged (page 16), ~N(0,1) context",
-                       "parallelism": f"tp{world}", "cuda_graph": use_graph,
+                       "parallelism": f"tp{world}", "cuda_graph": use_graph, "graph_store": graph_store,
                        "tp_reduction": "fused" if world > 1 else "none",
                        "l2": "no flush needed: each step streams the active weights of "
                              f"{nlayers} layers (>> 126 MB L2) so nothing is reused across steps",
