@@ -229,3 +229,30 @@ extern "C" int rmlx_sg_moe_down(int w_kind, const void* w, const void* scales, c
 #undef SG_DOWN
   return -2;
 }
+
+// The plan the streaming kernels would run a projection with (host arithmetic only: no launch, no
+// device needed), for tests of the planner and for tools. `op`: 0 dense mat-vec of N rows, 1 gate/up
+// with SwiGLU (N = intermediate size: quads are two row pairs), 2 expert down projection (rows
+// chained over `top_k` routed slots of K weights each). `ctas`: blocks to spread over (0: the
+// device's SM count). out[0..15] = LW, qpt, TR, SQ, QS, units, spl, KP, nseg, seg_rows, stage_bytes,
+// ns, qpc, grid, shared memory of a block, supported (grid > 0 and the block fits the launch helper's bound).
+extern "C" int rmlx_sg_plan_query(int w_kind, int op, int B, int N, int K, int top_k, int ctas, int* out) {
+  if (w_kind < 0 || w_kind > 2 || op < 0 || op > 2 || B < 1 || N < 1 || K < 8 || !out) return -2;
+  const int units = w_kind == 1 ? K >> 5 : w_kind == 2 ? K >> 4 : K >> 3;
+  if (ctas <= 0) ctas = sm_count();
+  SgPlan p;
+  if (op == 0) {
+    p = sg_make_plan(w_kind, units, 1, false, (N + 3) / 4, ctas, 1 << 20, sg_x_bytes(w_kind, K, B), 0, B);
+  } else if (op == 1) {
+    p = sg_make_plan(w_kind, units, 1, true, N / 2, ctas, 1 << 20, sg_x_bytes(w_kind, K, B), 0, B);
+  } else {
+    if (top_k < 1 || top_k > kSgMaxTopK) return -2;
+    const int per_token = ctas / B > 0 ? ctas / B : 1;            // as the launcher: the blocks are shared out over the tokens
+    p = sg_make_plan(w_kind, units, top_k, false, (N + 3) / 4, per_token, 1 << 20, sg_x_bytes(w_kind, K * top_k, 1), 64, 1);
+  }
+  const size_t smem = p.grid > 0 ? sg_smem_bytes(p, op == 2 ? 1 : B) : 0;
+  const int v[16] = {p.LW, p.qpt, p.TR, p.SQ, p.QS, p.units, p.spl, p.KP, p.nseg, p.seg_rows, p.stage_bytes,
+                     p.ns, p.qpc, p.grid, int(smem), p.grid > 0 && smem <= 200 * 1024 ? 1 : 0};   // the launch helper's own bound
+  for (int i = 0; i < 16; ++i) out[i] = v[i];
+  return 0;
+}

@@ -69,6 +69,24 @@ def set_stream(on: bool, ops=None) -> None:
         _STREAM_OPS = set(ops)
 
 
+def stream_plan(w_kind: int, op: int, batch: int, n: int, k: int, top_k: int = 1, ctas: int = 0) -> dict:
+    """The plan the streaming kernels would use for a projection (host arithmetic only, no device
+    needed): ``op`` 0 dense mat-vec of ``n`` rows, 1 gate/up with SwiGLU (``n`` = intermediate
+    size), 2 expert down projection over ``top_k`` routed slots of ``k`` weights. ``ok`` is False
+    when the launch would be refused (the caller then runs another kernel family)."""
+    import ctypes
+    lib = _lib.cuda()
+    lib.rmlx_sg_plan_query.argtypes = [ctypes.c_int] * 7 + [ctypes.POINTER(ctypes.c_int)]
+    lib.rmlx_sg_plan_query.restype = ctypes.c_int
+    out = (ctypes.c_int * 16)()
+    if lib.rmlx_sg_plan_query(w_kind, op, batch, n, k, top_k, ctas, out) != 0:
+        raise ValueError("bad planner query")
+    names = "LW qpt TR SQ QS units spl KP nseg seg_rows stage_bytes ns qpc grid smem ok".split()
+    plan = dict(zip(names, out))
+    plan["ok"] = bool(plan["ok"])
+    return plan
+
+
 def stream_status() -> int:
     """0, or the code of a bounded wait that expired inside a streaming kernel since the last call."""
     return int(_lib.cuda().rmlx_sg_status())
