@@ -93,3 +93,16 @@ def test_planner_refuses_what_it_cannot_run(query):
     assert query(1, MOE_DOWN, 1, 4096, 1536, 9)[0] == -2                        # more slots than a stage has segments
     rc, p = query(0, MOE_DOWN, 1, 4096, 1536, 8)                                # bf16 experts this wide: two stages do not fit
     assert rc == 0 and p["ok"] == 0                                             # the caller falls back to the per-row kernel
+
+
+def test_flash_decode_split_heuristic():
+    """About one block per SM, never more than 16 splits, never fewer than 8 pages per split."""
+    from rmlx_b200.ops.decode import default_splits
+    assert default_splits(1, 4, 1, 4096) == 16                   # 4 tiles: as many splits as allowed
+    assert default_splits(1, 4, 1, 1024) == 8                    # 64 pages: 8 pages per split
+    assert default_splits(1, 4, 1, 100) == 1 and default_splits(64, 4, 1, 8192) == 1
+    assert default_splits(8, 4, 1, 8192) == 5                    # 32 tiles -> ceil(148 / 32)
+    for b, hkv, ctx in itertools.product((1, 2, 8, 32), (1, 4, 8), (128, 2048, 32768)):
+        s = default_splits(b, hkv, 1, ctx)
+        assert 1 <= s <= 16 and (s == 1 or ctx // s >= 128)
+        assert s == 1 or (s - 1) * b * hkv < 148                 # one split fewer would leave SMs idle
