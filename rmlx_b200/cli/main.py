@@ -158,6 +158,8 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     c.add_argument("--hostfile", default=None,
                    help="also write a one-entry hostfile for this machine (ssh target = --ssh)")
     c.add_argument("--ssh", default="localhost", help="ssh target recorded in the hostfile")
+    sub.add_parser("plan", add_help=False,
+                   help="memory and decode plans of a model on B200s (see `rmlx_b200 plan --help`)")
     l = sub.add_parser("launch", help="run a command as one rank per GPU")
     l.add_argument("--nproc", "-n", type=int, default=0, help="ranks (default: all GPUs)")
     l.add_argument("--backend", default="auto")
@@ -169,6 +171,10 @@ def main(argv: Optional[Sequence[str]] = None) -> int:
     l.add_argument("--cwd", default=None, help="working directory on the remote hosts")
     l.add_argument("--dry-run", action="store_true", help="with --hosts: print the ssh commands only")
     l.add_argument("command", nargs=argparse.REMAINDER)
+    args = list(sys.argv[1:] if argv is None else argv)
+    if args and args[0] == "plan":                  # the planner owns its own options
+        from .plan import main as plan_main
+        return plan_main(args[1:])
     a = ap.parse_args(argv)
     if a.cmd == "config":
         doc = config(a.output)

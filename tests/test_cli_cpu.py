@@ -71,3 +71,37 @@ def test_hostfile_schema_round_trip_and_launch_plan(tmp_path):
     lines = buf.getvalue().strip().splitlines()
     assert rc == 0 and len(lines) == 4
     assert all("MASTER_ADDR=10.0.0.1" in ln for ln in lines) and "node1" in lines[2]
+
+
+def test_plan_matches_the_loaders_sharding_and_the_real_weights():
+    """``rmlx plan``: the analytic weight bytes equal what the loader builds for a small model at
+    TP 1 and 2 (sliced and partitioned experts, 4-bit and bf16); the 60-layer model's headline
+    facts (bf16 does not fit one GPU, 4-bit does; KV bytes per token) and the CLI exit codes."""
+    import torch
+    from rmlx_b200.cli import plan as P
+    from rmlx_b200.cli.main import main as cli_main
+    from rmlx_b200.config import FeedForwardType, MoeConfig, TransformerConfig
+    from rmlx_b200.models.weights import ParallelLayout, from_state_dict, random_state_dict
+    moe = MoeConfig(num_experts=4, num_experts_per_token=2, hidden_dim=128, intermediate_dim=128)
+    cfg = TransformerConfig(hidden_size=128, num_heads=4, num_kv_heads=2, head_dim=32, num_layers=2,
+                            vocab_size=512, max_seq_len=128, ff_type=FeedForwardType.moe_(moe), name="tiny").validate()
+    sd = random_state_dict(cfg, 0)
+    for quant, fmt in ((None, "bf16"), ("q4", "q4")):
+        for tp, ep in ((1, False), (2, False), (2, True)):
+            w = from_state_dict(cfg, sd, dtype=torch.bfloat16, quant=quant, layout=ParallelLayout(0, tp, ep))
+            parts = P.weight_bytes_per_gpu(cfg, fmt, tp, ep)
+            # ModelWeights.nbytes counts the projections, embedding and LM head (not norms / router)
+            want = parts["total"] - parts["norms"] - cfg.num_layers * moe.num_experts * cfg.hidden_size * 2
+            assert w.nbytes() == want, (fmt, tp, ep, w.nbytes(), want)
+    big = P.plan("moe-a22b", "bf16", tp=1)
+    assert not big["fits"] and 295e9 < big["weight_bytes_per_gpu"]["total"] < 305e9
+    q4 = P.plan("moe-a22b", "q4", tp=1, batch=1, ctx=4096)
+    assert q4["fits"] and q4["kv_bytes_per_token_per_gpu"] == 60 * 2 * 4 * 128 * 2
+    assert q4["kv_tokens_that_fit"] > 500_000
+    assert P.plan("moe-a22b", "q4", tp=8)["kv_bytes_per_token_per_gpu"] == 60 * 2 * 1 * 128 * 2   # kv heads replicated
+    assert P.kv_bytes_per_token_per_gpu(P.presets()["moe-a22b"], 1, "q8") == int(60 * 2 * 4 * 128 * (1 + 4 / 64))
+    if q4["decode_stream_plans"]:                                    # the library is there: plans are filled in
+        assert q4["decode_stream_plans"]["qkv"]["supported"] and q4["decode_stream_plans"]["qkv"]["blocks"] <= 148
+    assert P.plan("moe-a22b", "q4", batch=64)["decode_stream_plans"] == {}
+    assert "DOES NOT FIT" in P.render(big) and "fits" in P.render(q4)
+    assert cli_main(["plan", "--weights", "q4"]) == 0 and cli_main(["plan", "--weights", "bf16"]) == 1
