@@ -104,9 +104,56 @@ def decode_stream_plans(cfg: TransformerConfig, weights: str, tp: int, batch: in
     return out
 
 
+def plan_deepseek(weights: str = "q4", ranks: int = 8, batch: int = 1, ctx: int = 4096,
+                  budget_fraction: float = 0.90, cfg=None) -> dict:
+    """DeepSeek-V3 (latent attention, 256 routed experts + a shared one, first layer dense): the
+    routed experts are partitioned over ``ranks`` GPUs, attention, the shared expert and the dense
+    layer are replicated (how ``models/deepseek.py`` with an expert-parallel exchange lays it out).
+    The cache holds one latent row of kv_lora_rank + rope_head_dim (+ 8 padding) values per token
+    and layer, whatever the number of heads."""
+    from ..models.deepseek import deepseek_v3
+    c = cfg or deepseek_v3()
+    bits = BITS[weights]
+    lin = lambda n, k: int(n * k * bits / 8)                         # noqa: E731
+    d, h = c.hidden_size, c.num_heads
+    qk = c.head_dim + c.rope_head_dim
+    q = lin(c.q_lora_rank, d) + lin(h * qk, c.q_lora_rank) if c.q_lora_rank else lin(h * qk, d)
+    attn = q + lin(c.kv_lora_rank + c.rope_head_dim, d) + lin(h * (c.head_dim + c.v_head_dim), c.kv_lora_rank) \
+        + lin(d, h * c.v_head_dim)
+    expert = lin(2 * c.moe_intermediate, d) + lin(d, c.moe_intermediate)
+    moe_layers = c.num_layers - c.first_dense_layers
+    dense = c.first_dense_layers * (lin(2 * c.dense_intermediate, d) + lin(d, c.dense_intermediate))
+    parts = {
+        "attention": c.num_layers * attn,
+        "routed_experts": moe_layers * (c.num_experts // ranks) * expert,
+        "shared_experts_and_router": moe_layers * (c.num_shared_experts * expert + c.num_experts * d * 2),
+        "dense_layers": dense,
+        "norms": c.num_layers * (2 * d + c.kv_lora_rank + c.q_lora_rank) * 2,
+        "embedding": c.vocab_size * d * 2,
+        "lm_head": lin(c.vocab_size, d),
+    }
+    parts["total"] = sum(parts.values())
+    latent_row = (c.kv_lora_rank + c.rope_head_dim + 8) * 2
+    kv_tok = c.num_layers * latent_row
+    full_kv_tok = c.num_layers * h * (qk + c.v_head_dim) * 2
+    budget = int(HBM_BYTES * budget_fraction)
+    need = batch * ctx * kv_tok
+    return {
+        "model": "deepseek-v3", "weights": weights, "tp": ranks, "expert_parallel": True, "batch": batch,
+        "ctx": ctx, "kv_quant": "latent bf16", "weight_bytes_per_gpu": parts,
+        "kv_bytes_per_token_per_gpu": kv_tok, "uncompressed_kv_bytes_per_token": full_kv_tok,
+        "kv_compression": round(full_kv_tok / kv_tok, 1),
+        "prefill_chunk": 0, "prefill_scratch_bytes": 0, "budget_bytes_per_gpu": budget,
+        "kv_bytes_needed": need, "kv_tokens_that_fit": max(0, (budget - parts["total"]) // kv_tok),
+        "fits": parts["total"] + need <= budget, "decode_stream_plans": {},
+    }
+
+
 def plan(model: str = "moe-a22b", weights: str = "q4", tp: int = 1, batch: int = 1, ctx: int = 4096,
          kv_quant: Optional[str] = None, expert_parallel: bool = False, prefill_chunk: int = 2048,
          budget_fraction: float = 0.90, cfg: Optional[TransformerConfig] = None) -> dict:
+    if model == "deepseek-v3" and cfg is None:
+        return plan_deepseek(weights, tp, batch, ctx, budget_fraction)
     cfg = cfg or presets()[model]
     w = weight_bytes_per_gpu(cfg, weights, tp, expert_parallel)
     kv_tok = kv_bytes_per_token_per_gpu(cfg, tp, kv_quant)
@@ -135,6 +182,16 @@ def _gb(n: int) -> str:
 
 def render(p: dict) -> str:
     w = p["weight_bytes_per_gpu"]
+    if p["model"] == "deepseek-v3":
+        return "\n".join([
+            f"deepseek-v3: {p['weights']} weights, routed experts over {p['tp']} GPUs, batch {p['batch']}, context {p['ctx']}",
+            f"  weights per GPU      {_gb(w['total'])}  (routed experts {_gb(w['routed_experts']).strip()}, attention "
+            f"{_gb(w['attention']).strip()}, shared experts + router {_gb(w['shared_experts_and_router']).strip()}, "
+            f"dense layer {_gb(w['dense_layers']).strip()}, embedding {_gb(w['embedding']).strip()}, LM head {_gb(w['lm_head']).strip()})",
+            f"  latent cache per token {p['kv_bytes_per_token_per_gpu']} B ({p['kv_compression']}x smaller than per-head keys and values: "
+            f"{p['uncompressed_kv_bytes_per_token']} B); needed {_gb(p['kv_bytes_needed']).strip()}",
+            f"  budget per GPU       {_gb(p['budget_bytes_per_gpu'])}  -> {'fits' if p['fits'] else 'DOES NOT FIT'}; "
+            f"room for {p['kv_tokens_that_fit']:,} cached tokens per GPU"])
     lines = [f"{p['model']}: {p['weights']} weights, TP={p['tp']}"
              f"{' (experts partitioned)' if p['expert_parallel'] else ''}, batch {p['batch']}, context {p['ctx']}, "
              f"KV {p['kv_quant']}",
@@ -154,7 +211,7 @@ def render(p: dict) -> str:
 
 def main(argv: Optional[Sequence[str]] = None) -> int:
     ap = argparse.ArgumentParser(prog="rmlx plan", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--model", default="moe-a22b", choices=sorted(presets()))
+    ap.add_argument("--model", default="moe-a22b", choices=sorted(presets()) + ["deepseek-v3"])
     ap.add_argument("--weights", default="q4", choices=sorted(BITS))
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--expert-parallel", action="store_true")

@@ -105,3 +105,9 @@ def test_plan_matches_the_loaders_sharding_and_the_real_weights():
     assert P.plan("moe-a22b", "q4", batch=64)["decode_stream_plans"] == {}
     assert "DOES NOT FIT" in P.render(big) and "fits" in P.render(q4)
     assert cli_main(["plan", "--weights", "q4"]) == 0 and cli_main(["plan", "--weights", "bf16"]) == 1
+    ds8, ds2 = P.plan("deepseek-v3", "q4", tp=8, batch=8, ctx=32768), P.plan("deepseek-v3", "q4", tp=2)
+    assert ds8["fits"] and not ds2["fits"] and ds8["kv_compression"] > 50
+    total = 8 * ds8["weight_bytes_per_gpu"]["routed_experts"] + ds8["weight_bytes_per_gpu"]["total"] \
+        - ds8["weight_bytes_per_gpu"]["routed_experts"]
+    assert 660e9 < total / (4.5 / 8) < 690e9                          # the 671 B parameters of the model
+    assert ds8["kv_bytes_per_token_per_gpu"] == 61 * (512 + 64 + 8) * 2 and "latent cache" in P.render(ds8)
