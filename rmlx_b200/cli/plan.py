@@ -74,6 +74,37 @@ def kv_bytes_per_token_per_gpu(cfg: TransformerConfig, tp: int, kv_quant: Option
     return int(cfg.num_layers * 2 * hkv * cfg.head_dim * per_value)
 
 
+def decode_roofline(cfg: TransformerConfig, weights: str, tp: int, ctx: int, batch: int = 1,
+                    hbm_gbs: Optional[float] = None) -> Dict[str, float]:
+    """Bytes one decode step must read per GPU (each active weight once, the cached keys and
+    values of ``ctx`` tokens per sequence, the LM head) over the copy bandwidth: the floor the
+    measured step time is reported against. ``hbm_gbs`` defaults to the pool's measured figure
+    (``MEASURED_PEAKS.json`` beside the package) or 6650 GB/s."""
+    if hbm_gbs is None:
+        import os
+        path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                            "MEASURED_PEAKS.json")
+        hbm_gbs = json.load(open(path))["hbm_gbs"] if os.path.exists(path) else 6650.0
+    layout = ParallelLayout(0, tp)
+    hq, _, hkv, _ = layout.heads(cfg)
+    d, hd, bits = cfg.hidden_size, cfg.head_dim, BITS[weights]
+    lin = lambda n, k: n * k * bits / 8                              # noqa: E731
+    layer = lin((hq + 2 * hkv) * hd, d) + lin(d, hq * hd) + batch * ctx * 2 * hkv * hd * 2
+    if cfg.ff_type.kind == "moe":
+        m = cfg.ff_type.moe
+        inter = m.intermediate_dim // tp
+        active = min(m.num_experts, batch * m.num_experts_per_token)   # distinct experts at most
+        layer += active * (lin(2 * inter, d) + lin(d, inter)) + m.num_experts * d * 2
+    else:
+        inter = cfg.ff_type.intermediate_dim // tp
+        layer += lin(2 * inter, d) + lin(d, inter)
+    head = lin(cfg.vocab_size // tp, d)
+    step = cfg.num_layers * layer + head
+    us = step / (hbm_gbs * 1e3)
+    return {"bytes_per_layer": layer, "us_per_layer": layer / (hbm_gbs * 1e3), "us_per_step": us,
+            "tokens_per_s": batch * 1e6 / us, "hbm_gbs": hbm_gbs}
+
+
 def decode_stream_plans(cfg: TransformerConfig, weights: str, tp: int, batch: int = 1) -> Dict[str, dict]:
     """Blocks and shared memory of the decode projections on the streaming kernels (None where
     the library cannot be loaded)."""
@@ -171,6 +202,7 @@ def plan(model: str = "moe-a22b", weights: str = "q4", tp: int = 1, batch: int =
         "kv_bytes_needed": kv_needed,
         "kv_tokens_that_fit": max(0, free_for_kv // kv_tok),
         "fits": w["total"] + scratch + kv_needed <= budget,
+        "decode_roofline": decode_roofline(cfg, weights, tp, ctx, batch),
         # batches above 8 rows decode on the tensor-core path, not on the streaming mat-vecs
         "decode_stream_plans": decode_stream_plans(cfg, weights, tp, batch) if batch <= 8 else {},
     }
@@ -201,6 +233,9 @@ def render(p: dict) -> str:
              f"  prompt chunk {p['prefill_chunk']}: scratch {_gb(p['prefill_scratch_bytes']).strip()}",
              f"  budget per GPU       {_gb(p['budget_bytes_per_gpu'])}  -> {'fits' if p['fits'] else 'DOES NOT FIT'}; "
              f"room for {p['kv_tokens_that_fit']:,} cached tokens per GPU"]
+    r = p["decode_roofline"]
+    lines.append(f"  decode floor (bytes over {r['hbm_gbs']:.0f} GB/s): {r['bytes_per_layer'] / 1e6:.1f} MB and "
+                 f"{r['us_per_layer']:.1f} us per layer, {r['tokens_per_s']:.0f} tokens/s")
     if p["batch"] > 8:
         lines.append("  decode: batches above 8 rows run on the tensor-core path (GEMM tiles), no streaming plan")
     for name, sp in p["decode_stream_plans"].items():

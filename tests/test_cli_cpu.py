@@ -103,6 +103,9 @@ def test_plan_matches_the_loaders_sharding_and_the_real_weights():
     if q4["decode_stream_plans"]:                                    # the library is there: plans are filled in
         assert q4["decode_stream_plans"]["qkv"]["supported"] and q4["decode_stream_plans"]["qkv"]["blocks"] <= 148
     assert P.plan("moe-a22b", "q4", batch=64)["decode_stream_plans"] == {}
+    roof = P.decode_roofline(P.presets()["moe-a22b"], "q4", 1, 4096, hbm_gbs=6533.0)
+    assert 20.0 < roof["us_per_layer"] < 21.0 and 750 < roof["tokens_per_s"] < 810     # the 20.6 us of bytes per layer
+    assert P.decode_roofline(P.presets()["moe-a22b"], "q4", 8, 4096, hbm_gbs=6533.0)["us_per_layer"] < 0.2 * roof["us_per_layer"]
     assert "DOES NOT FIT" in P.render(big) and "fits" in P.render(q4)
     assert cli_main(["plan", "--weights", "q4"]) == 0 and cli_main(["plan", "--weights", "bf16"]) == 1
     ds8, ds2 = P.plan("deepseek-v3", "q4", tp=8, batch=8, ctx=32768), P.plan("deepseek-v3", "q4", tp=2)
