@@ -249,6 +249,23 @@ class Group:
             r.wait()
         return recv
 
+    def shift(self, send: torch.Tensor, recv: torch.Tensor, dst: int, src: int) -> torch.Tensor:
+        """Send ``send`` to ``dst`` while receiving ``recv`` from ``src`` (the step of a ring: two
+        different peers, both transfers in flight together, so no ordering between ranks can
+        deadlock)."""
+        if self.single:
+            raise DistributedError("shift on a single-rank group")
+        ch = self._p2p(send)
+        if ch is not None and recv.is_contiguous() and self._p2p(recv) is not None:
+            ch.send(send, dst)                      # a put plus a signal: does not wait for the receiver
+            return ch.recv(recv, src)
+        self.library_calls += 1
+        ops = [dist.P2POp(dist.isend, send.contiguous(), self._global(dst), self._pg),
+               dist.P2POp(dist.irecv, recv, self._global(src), self._pg)]
+        for r in dist.batch_isend_irecv(ops):
+            r.wait()
+        return recv
+
     def barrier(self) -> None:
         if not self.single:
             dist.barrier(group=self._pg)

@@ -116,6 +116,61 @@ def _group_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def _algo_worker(rank, world, port, q):
+    import torch.distributed as dist
+    from rmlx_b200.parallel import algorithms as A
+    from rmlx_b200.parallel.group import Group
+    dist.init_process_group("gloo", init_method=f"tcp://127.0.0.1:{port}", rank=rank, world_size=world)
+    try:
+        g = Group()
+        ok = True
+        for n, dtype in ((1, torch.float32), (7, torch.float32), (1000, torch.float32), (2, torch.bfloat16),
+                         (513, torch.bfloat16)):
+            gen = torch.Generator().manual_seed(100 * n + rank)
+            x = torch.randint(-8, 9, (n,), generator=gen).to(dtype)           # small integers: sums are exact
+            want = sum(torch.randint(-8, 9, (n,), generator=torch.Generator().manual_seed(100 * n + r)).float()
+                       for r in range(world)).to(dtype)
+            for fn in (A.tree_allreduce, A.ring_allreduce, A.mesh_allreduce):
+                got = fn(g, x)
+                ok &= got.dtype == dtype and got.shape == x.shape and torch.equal(got, want)
+        y = torch.randn(3, 5, generator=torch.Generator().manual_seed(rank))
+        ref = g.allreduce(y)
+        for fn in (A.tree_allreduce, A.ring_allreduce, A.mesh_allreduce):
+            ok &= torch.allclose(fn(g, y), ref, atol=1e-5)
+        out, algo = A.allreduce_auto(g, y)
+        ok &= algo is A.AllreduceAlgorithm.TREE and torch.allclose(out, ref, atol=1e-5)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [3, 4])
+def test_tree_ring_and_mesh_allreduce_over_point_to_point(world):
+    """The three algorithms on gloo ranks (an odd and an even group): exact sums on integer data of
+    sizes that do not divide by the group, fp32 and bf16, and agreement with the library."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_algo_worker, args=(r, world, port, q)) for r in range(world)]
+    [p.start() for p in ps]
+    res = dict(q.get(timeout=120) for _ in range(world))
+    for p in ps:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res == {r: True for r in range(world)}
+
+
+def test_allreduce_algorithm_choice_and_chunks():
+    from rmlx_b200.parallel import algorithms as A
+    assert A.chunk_bounds(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    assert A.chunk_bounds(2, 4) == [(0, 1), (1, 2), (2, 2), (2, 2)] and A.chunk_bounds(0, 3) == [(0, 0)] * 3
+    T, R, M = A.AllreduceAlgorithm.TREE, A.AllreduceAlgorithm.RING, A.AllreduceAlgorithm.MESH
+    assert A.choose_algorithm(4096, 8) is T and A.choose_algorithm(2 << 20, 8) is M
+    assert A.choose_algorithm(16 << 20, 8) is R and A.choose_algorithm(16 << 20, 2) is M    # two ranks never ring
+    assert A.choose_algorithm(256 << 10, 4, half=True) is R and A.choose_algorithm(256 << 10, 4) is T
+    assert A.choose_algorithm(4096, 8, tree_threshold=1024) is M
+
+
 def test_group_collectives_split_and_ep_exchange_on_gloo():
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
