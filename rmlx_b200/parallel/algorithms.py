@@ -98,6 +98,55 @@ def ring_allreduce(group: Group, t: torch.Tensor) -> torch.Tensor:
     return acc.to(t.dtype).reshape(t.shape)
 
 
+def ring_reduce_scatter(group: Group, t: torch.Tensor) -> torch.Tensor:
+    """The first half of the ring: returns this rank's chunk (``chunk_bounds(numel, N)[rank]``)
+    of the sum over ranks, flat, in the input's dtype."""
+    n, r = group.world_size, group.local_rank
+    acc = _acc(t)
+    bounds = chunk_bounds(acc.numel(), n)
+    if n > 1:
+        right, left = (r + 1) % n, (r - 1) % n
+        buf = torch.empty(max(hi - lo for lo, hi in bounds), dtype=acc.dtype, device=acc.device)
+        for s in range(n - 1):                        # chunks start one place earlier, so r ends with chunk r
+            lo, hi = bounds[(r - s - 1) % n]
+            rlo, rhi = bounds[(r - s - 2) % n]
+            got = group.shift(acc[lo:hi].contiguous(), buf[:rhi - rlo], right, left)
+            acc[rlo:rhi] += got
+    lo, hi = bounds[r]
+    return acc[lo:hi].to(t.dtype)
+
+
+def ring_allgather(group: Group, shard: torch.Tensor) -> torch.Tensor:
+    """Shards of equal shape from every rank, concatenated along a new leading axis in rank
+    order: N - 1 steps, each passing on the shard received in the step before."""
+    n, r = group.world_size, group.local_rank
+    out = torch.empty((n, *shard.shape), dtype=shard.dtype, device=shard.device)
+    out[r] = shard
+    right, left = (r + 1) % n, (r - 1) % n
+    for s in range(n - 1):
+        src = (r - s - 1) % n
+        group.shift(out[(r - s) % n].contiguous(), out[src], right, left)
+    return out
+
+
+def tree_broadcast(group: Group, t: torch.Tensor, root: int = 0) -> torch.Tensor:
+    """``root``'s tensor to every rank in ceil(log2 N) steps (ranks renumbered so that the root is
+    0; in step k every rank that already holds the data passes it to the rank 2^k away)."""
+    n, r = group.world_size, group.local_rank
+    if n == 1:
+        return t
+    v = (r - root) % n                                # position in the tree rooted at `root`
+    buf = t.contiguous() if v == 0 else torch.empty_like(t)
+    step = 1
+    while step < n:
+        if v < step and v + step < n:
+            group.send(buf, (v + step + root) % n)
+        elif step <= v < 2 * step:
+            group.recv(buf, (v - step + root) % n)
+        step *= 2
+    return buf
+
+
 def mesh_allreduce(group: Group, t: torch.Tensor) -> torch.Tensor:
     """Every rank exchanges its whole tensor with every other rank (N - 1 pairwise exchanges, a
     round-robin schedule so that each round is a perfect matching) and sums in rank order."""

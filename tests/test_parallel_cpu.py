@@ -139,6 +139,15 @@ def _algo_worker(rank, world, port, q):
             ok &= torch.allclose(fn(g, y), ref, atol=1e-5)
         out, algo = A.allreduce_auto(g, y)
         ok &= algo is A.AllreduceAlgorithm.TREE and torch.allclose(out, ref, atol=1e-5)
+        # the halves of the ring on their own, and the tree broadcast from a root that is not rank 0
+        z = torch.arange(11.0) * (rank + 1)
+        lo, hi = A.chunk_bounds(11, world)[rank]
+        ok &= torch.equal(A.ring_reduce_scatter(g, z), (torch.arange(11.0) * sum(range(1, world + 1)))[lo:hi])
+        gathered = A.ring_allgather(g, torch.full((2, 3), float(rank)))
+        ok &= gathered.shape == (world, 2, 3) and all(float(gathered[i].mean()) == i for i in range(world))
+        root = world - 1
+        b = A.tree_broadcast(g, torch.arange(5.0) + 10 * rank, root=root)
+        ok &= torch.equal(b, torch.arange(5.0) + 10 * root)
         q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
