@@ -27,7 +27,9 @@ CUDA_LIB = LIB / "librmlx_b200_cuda.so"
 # The same sources compiled with -DRMLX_BOUNDS: device-side index checks that record the first
 # offender and skip the access (build(kinds=("cuda_bounds",)); loaded when RMLX_BOUNDS=1).
 CUDA_BOUNDS_LIB = LIB / "librmlx_b200_cuda_bounds.so"
-HOST_LIB = LIB / "librmlx_b200_host.so"
+# RMLX_HOST_LIB=<file>: load that build of the host runtime instead (a sanitizer build, say: the
+# sources compile on their own, `g++ -shared -fPIC -pthread -fsanitize=address,undefined csrc/host/*.cpp`)
+HOST_LIB = Path(os.environ["RMLX_HOST_LIB"]) if os.environ.get("RMLX_HOST_LIB") else LIB / "librmlx_b200_host.so"
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
