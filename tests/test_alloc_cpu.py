@@ -96,3 +96,82 @@ def test_limits_and_gc():
 def test_crc32_matches_zlib():
     for data in (b"", b"a", b"hello world" * 100):
         assert crc32(data) == zlib.crc32(data)
+
+
+def _run_ops(arena_alloc, arena_free, ops, align):
+    """Replay (kind, value) operations; returns the live {offset: size} map after checking that no
+    two live blocks overlap and that every offset is aligned."""
+    live = {}
+    order = []
+    for kind, v in ops:
+        if kind == "a":
+            off = arena_alloc(v)
+            if off is None:
+                continue
+            assert off % align == 0
+            for o, n in live.items():
+                assert off + v <= o or o + n <= off, "overlapping blocks"
+            live[off] = v
+            order.append(off)
+        elif order:
+            off = order.pop(v % len(order))
+            arena_free(off, live.pop(off))
+    return live, order
+
+
+def test_arenas_never_overlap_and_coalesce_back_to_one_block():
+    """Random allocate / free sequences (hypothesis) on the native BFC arena and on the symmetric
+    heap's offset arena: blocks never overlap, offsets are aligned, two arenas fed the same sequence
+    agree (ranks must derive the same offsets), and after freeing everything the whole range is one
+    free block again."""
+    from hypothesis import given, settings, strategies as st
+    from rmlx_b200.parallel.symm_heap import OffsetArena
+    from rmlx_b200.runtime.alloc import AllocError, BfcArena
+
+    ops_st = st.lists(st.one_of(st.tuples(st.just("a"), st.integers(1, 5000)),
+                                st.tuples(st.just("f"), st.integers(0, 1000))), max_size=60)
+
+    @settings(max_examples=60, deadline=None)
+    @given(ops_st)
+    def bfc(ops):
+        size = 64 * 1024
+        arenas = [BfcArena(size, alignment=256), BfcArena(size, alignment=256)]
+
+        def alloc_on(a):
+            def f(n):
+                try:
+                    return a.alloc(n)
+                except AllocError:
+                    return None
+            return f
+        results = [_run_ops(alloc_on(a), lambda off, _n, a=a: a.free(off), ops, 256) for a in arenas]
+        assert results[0] == results[1]                      # deterministic across instances
+        live, order = results[0]
+        a = arenas[0]
+        for off in list(order):
+            a.free(off)
+        assert a.in_use() == 0 and a.largest_free() == size  # everything coalesced
+        for x in arenas:
+            x.close()
+
+    @settings(max_examples=60, deadline=None)
+    @given(ops_st)
+    def offsets(ops):
+        def fresh():
+            a = OffsetArena()
+            a.grow(32 * 1024)
+            return a
+        arenas = [fresh(), fresh()]
+        results = [_run_ops(lambda n, a=a: a.take((n + 255) // 256 * 256),
+                            lambda off, n, a=a: a.give(off, (n + 255) // 256 * 256), ops, 256) for a in arenas]
+        assert results[0] == results[1]
+        live, order = results[0]
+        a = arenas[0]
+        for off in list(order):
+            a.give(off, (live[off] + 255) // 256 * 256)
+        assert a.free == [(0, 32 * 1024)] and a.free_bytes() == 32 * 1024
+        a.grow(1024)                                          # growth extends the last free range
+        assert a.free == [(0, 33 * 1024)]
+
+    bfc()
+    offsets()
