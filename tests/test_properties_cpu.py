@@ -92,3 +92,27 @@ def test_fp8_row_payload_keeps_the_row_maximum_and_three_bits(n, d, seed):
     # E4M3: 3 mantissa bits -> relative error at most 2^-4 of the value, plus the subnormal step of the scaled range
     assert bool(((back - x).abs() <= x.abs() / 16 + (amax / 448 * 2**-9)[:, None] + 1e-7).all())
     assert wire.fp8_unpack_tokens(wire.fp8_pack_tokens(x), n, d).shape == (n, d)
+
+
+@settings(max_examples=60, deadline=None)
+@given(st.integers(2, 300), st.floats(0.05, 3.0), st.integers(0, 64), st.floats(0.05, 1.0), st.floats(0.5, 2.5),
+       st.integers(0, 2**31 - 1), st.lists(st.integers(0, 299), max_size=8))
+def test_native_sampler_distribution_properties(vocab, temperature, top_k, top_p, penalty, seed, history):
+    """For any configuration: the native distribution equals the torch-op one, sums to one, keeps at
+    most top-k tokens (ties aside), and its kept mass reaches top-p of the shaped distribution."""
+    from rmlx_b200.config import SamplerConfig
+    from rmlx_b200.serve import native
+    from rmlx_b200.serve.sampler import Sampler
+    if not native.available():
+        pytest.skip("host library not available")
+    cfg = SamplerConfig(temperature=temperature, top_k=top_k, top_p=top_p, repetition_penalty=penalty, seed=1)
+    logits = torch.randn(vocab, generator=torch.Generator().manual_seed(seed)) * 3
+    hist = [h for h in history if h < vocab]
+    want = Sampler(cfg).probabilities(logits, hist)
+    got = native.NativeSampler(cfg).probabilities(logits, hist)
+    assert torch.allclose(got, want, atol=2e-6)
+    assert abs(float(got.sum()) - 1.0) < 1e-4 and bool((got >= 0).all())
+    kept = int((got > 0).sum())
+    if 0 < top_k < vocab:
+        assert kept <= top_k
+    assert kept >= 1 and int(got.argmax()) == int(want.argmax())
