@@ -131,7 +131,7 @@ def test_arenas_never_overlap_and_coalesce_back_to_one_block():
     ops_st = st.lists(st.one_of(st.tuples(st.just("a"), st.integers(1, 5000)),
                                 st.tuples(st.just("f"), st.integers(0, 1000))), max_size=60)
 
-    @settings(max_examples=60, deadline=None)
+    @settings(max_examples=60, deadline=None, derandomize=True)
     @given(ops_st)
     def bfc(ops):
         size = 64 * 1024
@@ -154,7 +154,7 @@ def test_arenas_never_overlap_and_coalesce_back_to_one_block():
         for x in arenas:
             x.close()
 
-    @settings(max_examples=60, deadline=None)
+    @settings(max_examples=60, deadline=None, derandomize=True)
     @given(ops_st)
     def offsets(ops):
         def fresh():

@@ -10,7 +10,7 @@ from rmlx_b200.parallel.algorithms import chunk_bounds
 from rmlx_b200.reference import ops as ref
 
 
-@settings(max_examples=80, deadline=None)
+@settings(max_examples=80, deadline=None, derandomize=True)
 @given(st.integers(0, 5000), st.integers(1, 17))
 def test_chunk_bounds_partition_the_range(n, parts):
     b = chunk_bounds(n, parts)
@@ -20,7 +20,7 @@ def test_chunk_bounds_partition_the_range(n, parts):
     assert max(sizes) - min(sizes) <= 1 and sorted(sizes, reverse=True) == sizes
 
 
-@settings(max_examples=80, deadline=None)
+@settings(max_examples=80, deadline=None, derandomize=True)
 @given(st.integers(0, (1 << 40) - 1), st.integers(0, 255), st.integers(0, 255), st.integers(0, 255))
 def test_exchange_tag_round_trip(seq, tag, slot, peer):
     word = wire.pack_exchange_tag(seq, tag, slot, peer)
@@ -33,7 +33,7 @@ def test_exchange_tag_rejects_out_of_range_fields():
             wire.pack_exchange_tag(*bad)
 
 
-@settings(max_examples=50, deadline=None)
+@settings(max_examples=50, deadline=None, derandomize=True)
 @given(st.lists(st.tuples(st.integers(0, 65535), st.integers(0, 65535)), max_size=12), st.integers(1, 24),
        st.integers(0, 2**32 - 1))
 def test_v3_wire_format_round_trip_and_truncation(meta, stride, seed):
@@ -56,7 +56,7 @@ def test_v3_wire_format_round_trip_and_truncation(meta, stride, seed):
             wire.crc_verify(bytes(broken))
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(st.integers(1, 6), st.sampled_from([64, 128, 192]), st.sampled_from([4, 8]), st.integers(0, 2**31 - 1),
        st.floats(1e-3, 50.0))
 def test_affine_quantiser_error_is_bounded_by_half_a_step(n, k, bits, seed, spread):
@@ -70,7 +70,7 @@ def test_affine_quantiser_error_is_bounded_by_half_a_step(n, k, bits, seed, spre
     s = scales.float().repeat_interleave(64, dim=1)
     lo = w.view(n, k // 64, 64).amin(-1)
     # the stored bias is the group minimum rounded to bf16: allow that rounding on top of half a step
-    slack = (biases.float() - lo).abs().repeat_interleave(64, dim=1) + 1e-6
+    slack = (biases.float() - lo).abs().repeat_interleave(64, dim=1) + 1e-5 * (w.abs() + 1)   # fp32 arithmetic
     levels = (1 << bits) - 1
     inside = (w - biases.float().repeat_interleave(64, dim=1)) / s
     clipped = (inside < -0.5) | (inside > levels + 0.5)            # beyond the representable range after rounding
@@ -80,7 +80,7 @@ def test_affine_quantiser_error_is_bounded_by_half_a_step(n, k, bits, seed, spre
     assert torch.allclose(ref.dequantize_affine(*again, bits=bits, group_size=64), back, atol=float(s.max()) * 1.01)
 
 
-@settings(max_examples=40, deadline=None)
+@settings(max_examples=40, deadline=None, derandomize=True)
 @given(st.integers(1, 5), st.integers(1, 40), st.integers(0, 2**31 - 1))
 def test_fp8_row_payload_keeps_the_row_maximum_and_three_bits(n, d, seed):
     from rmlx_b200.parallel.ep import fp8_dequant_rows, fp8_quant_rows
@@ -94,7 +94,7 @@ def test_fp8_row_payload_keeps_the_row_maximum_and_three_bits(n, d, seed):
     assert wire.fp8_unpack_tokens(wire.fp8_pack_tokens(x), n, d).shape == (n, d)
 
 
-@settings(max_examples=60, deadline=None)
+@settings(max_examples=60, deadline=None, derandomize=True)
 @given(st.integers(2, 300), st.floats(0.05, 3.0), st.integers(0, 64), st.floats(0.05, 1.0), st.floats(0.5, 2.5),
        st.integers(0, 2**31 - 1), st.lists(st.integers(0, 299), max_size=8))
 def test_native_sampler_distribution_properties(vocab, temperature, top_k, top_p, penalty, seed, history):
