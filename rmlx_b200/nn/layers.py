@@ -149,6 +149,62 @@ def gptq_dequantize(qweight, qzeros, scales, g_idx=None) -> torch.Tensor:
     return ((q - z[g]).float() * scales.float()[g]).t().contiguous()
 
 
+class AwqLinear:
+    """A linear layer kept in the AutoAWQ checkpoint layout (crates/rmlx-nn/src/quantized_linear.rs:350-540):
+    ``forward`` multiplies with the expanded weight (expanded once, on the checkpoint's device, by the
+    kernel of csrc/kernels/misc.cu for CUDA fp16 checkpoints); ``to_quantized`` re-encodes it in the
+    framework's own 4-bit format, which is what the decode and prompt kernels consume."""
+
+    def __init__(self, qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor,
+                 group_size: int = 128, bias: Optional[torch.Tensor] = None):
+        if qweight.shape[1] * 8 != scales.shape[1] or qzeros.shape != (scales.shape[0], qweight.shape[1]):
+            raise ValueError("AwqLinear: qweight [in, out/8], qzeros [in/g, out/8], scales [in/g, out]")
+        if qweight.shape[0] != scales.shape[0] * group_size:
+            raise ValueError("AwqLinear: group_size does not match the scales")
+        self.qweight, self.qzeros, self.scales, self.group_size, self.bias = qweight, qzeros, scales, group_size, bias
+        self.in_features, self.out_features = qweight.shape[0], scales.shape[1]
+        self._dense: Optional[torch.Tensor] = None
+
+    def _expand(self) -> torch.Tensor:
+        return awq_dequantize(self.qweight, self.qzeros, self.scales, self.group_size)
+
+    def dense_weight(self) -> torch.Tensor:
+        """fp32 [out, in], expanded on first use."""
+        if self._dense is None:
+            self._dense = self._expand()
+        return self._dense
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = x.float() @ self.dense_weight().t()
+        if self.bias is not None:
+            y = y + self.bias.float()
+        return y.to(x.dtype)
+
+    __call__ = forward
+
+    def to_quantized(self, device=None) -> "QuantizedLinear":
+        return QuantizedLinear(LinearWeight.from_dense(self.dense_weight(), "q4", device=device))
+
+
+class GptqLinear(AwqLinear):
+    """The same for the GPTQ layout (qweight [in/8, out], qzeros stored minus one, optional
+    activation-order index ``g_idx``)."""
+
+    def __init__(self, qweight: torch.Tensor, qzeros: torch.Tensor, scales: torch.Tensor,
+                 g_idx: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None):
+        if qweight.shape[1] != scales.shape[1] or qzeros.shape != (scales.shape[0], scales.shape[1] // 8):
+            raise ValueError("GptqLinear: qweight [in/8, out], qzeros [groups, out/8], scales [groups, out]")
+        if g_idx is not None and g_idx.numel() != qweight.shape[0] * 8:
+            raise ValueError("GptqLinear: g_idx has one entry per input feature")
+        self.qweight, self.qzeros, self.scales, self.g_idx, self.bias = qweight, qzeros, scales, g_idx, bias
+        self.in_features, self.out_features = qweight.shape[0] * 8, scales.shape[1]
+        self.group_size = self.in_features // scales.shape[0]
+        self._dense = None
+
+    def _expand(self) -> torch.Tensor:
+        return gptq_dequantize(self.qweight, self.qzeros, self.scales, self.g_idx)
+
+
 class Embedding:
     def __init__(self, table: torch.Tensor):
         self.table = table
@@ -176,6 +232,9 @@ class RMSNorm:
         return ref.rms_norm(x, self.weight, self.eps)
 
     __call__ = forward
+
+
+RmsNorm = RMSNorm          # the reference's spelling
 
 
 class LayerNorm:

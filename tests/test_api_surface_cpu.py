@@ -60,6 +60,21 @@ def test_awq_and_gptq_imports_round_trip():
     got = gptq_dequantize(qw, qz, s, perm)
     assert torch.allclose(got, ((q - (((z - 1) % 16) + 1)[perm]).float() * s[perm]).t())
     assert QuantizedLinear.from_gptq(qw, qz, s).weight.n == n_out
+    # the layer classes that keep the checkpoint layout: exact product with the expanded weight
+    from rmlx_b200.nn.layers import AwqLinear, GptqLinear, RmsNorm, RMSNorm
+    import pytest
+    bias = torch.randn(n_out, generator=g)
+    awq = AwqLinear(_pack_nibbles(q, awq_pos), _pack_nibbles(z, awq_pos), s, gs, bias=bias)
+    assert (awq.in_features, awq.out_features) == (n_in, n_out)
+    assert torch.allclose(awq(x), x @ want.t() + bias, atol=1e-4)
+    assert awq.to_quantized().weight.n == n_out
+    gptq = GptqLinear(qw, qz, s, perm)
+    assert gptq.group_size == gs and torch.allclose(gptq(x), x @ gptq.dense_weight().t(), atol=1e-4)
+    with pytest.raises(ValueError):
+        AwqLinear(_pack_nibbles(q, awq_pos), _pack_nibbles(z, awq_pos), s, gs * 2)      # wrong group size
+    with pytest.raises(ValueError):
+        GptqLinear(qw, qz, s, perm[:-1])
+    assert RmsNorm is RMSNorm
 
 
 def test_moe_expert_bias_builders_and_update():
