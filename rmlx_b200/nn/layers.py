@@ -279,6 +279,7 @@ ACTIVATIONS: Dict[str, Callable[[torch.Tensor], torch.Tensor]] = {
     "silu": torch.nn.functional.silu, "swish": torch.nn.functional.silu, "mish": torch.nn.functional.mish,
     "sigmoid": torch.sigmoid, "tanh": torch.tanh, "softplus": torch.nn.functional.softplus,
     "softsign": torch.nn.functional.softsign, "hardswish": torch.nn.functional.hardswish,
+    "hardsigmoid": torch.nn.functional.hardsigmoid, "quick_gelu": lambda x: x * torch.sigmoid(1.702 * x),
     "glu": lambda x: torch.nn.functional.glu(x, -1), "swiglu": ref.swiglu,
 }
 

@@ -341,3 +341,27 @@ def test_logical_topology_striping_and_failover():
     assert fo.report(1, False) == "active" and fo.report(1, False) == "failed" and fo.usable() == [0]
     assert fo.report(1, True) == "recovering" and fo.report(1, False) == "failed"
     assert fo.report(1, True) == "recovering" and fo.report(1, True) == "active" and fo.usable() == [0, 1]
+
+
+def test_every_activation_of_the_reference_has_a_closed_form_here():
+    """SiLU, GELU (exact / tanh / fast), sigmoid, tanh, ReLU, leaky ReLU, ELU, SELU, Mish, QuickGELU,
+    hard swish, hard sigmoid, softplus, softsign, GLU (crates/rmlx-nn/src/activations.rs:1188-1205)."""
+    from rmlx_b200.nn.layers import ACTIVATIONS, activation
+    x = torch.linspace(-4, 4, 33)
+    sig = torch.sigmoid
+    forms = {
+        "silu": x * sig(x), "sigmoid": sig(x), "tanh": torch.tanh(x), "relu": x.clamp_min(0),
+        "leaky_relu": torch.where(x > 0, x, 0.01 * x), "elu": torch.where(x > 0, x, torch.expm1(x)),
+        "selu": 1.0507009873554805 * torch.where(x > 0, x, 1.6732632423543772 * torch.expm1(x)),
+        "mish": x * torch.tanh(torch.log1p(torch.exp(x))), "quick_gelu": x * sig(1.702 * x),
+        "hardswish": x * (x + 3).clamp(0, 6) / 6, "hardsigmoid": (x + 3).clamp(0, 6) / 6,
+        "softplus": torch.log1p(torch.exp(x)), "softsign": x / (1 + x.abs()),
+        "gelu": 0.5 * x * (1 + torch.erf(x / 2 ** 0.5)),
+        "gelu_approx": 0.5 * x * (1 + torch.tanh(0.7978845608 * (x + 0.044715 * x ** 3))),
+    }
+    for name, want in forms.items():
+        assert torch.allclose(activation(name)(x), want, atol=1e-5), name
+    assert torch.allclose(activation("gelu_fast")(x), forms["gelu"], atol=3e-2)
+    pair = torch.randn(3, 8)
+    assert torch.allclose(activation("glu")(pair), pair[:, :4] * sig(pair[:, 4:]))
+    assert len(ACTIVATIONS) >= 17
