@@ -117,3 +117,37 @@ class PrefillPool:
     @property
     def available(self) -> int:
         return len(self._free)
+
+
+class DynamicExecContext:
+    """``count`` intermediates of [max_seq_len, hidden] allocated once; a step of any length up to
+    the maximum takes views of their first rows, so a varying sequence length never allocates
+    (crates/rmlx-nn/src/dynamic.rs:16-104)."""
+
+    def __init__(self, max_seq_len: int, hidden_dim: int, dtype=torch.bfloat16, num_intermediates: int = 4,
+                 device="cpu"):
+        if max_seq_len < 1 or hidden_dim < 1 or num_intermediates < 1:
+            raise ValueError("DynamicExecContext: sizes must be positive")
+        self._max, self._hidden, self.dtype = max_seq_len, hidden_dim, dtype
+        self._bufs = [torch.zeros(max_seq_len, hidden_dim, dtype=dtype, device=device)
+                      for _ in range(num_intermediates)]
+
+    def max_seq_len(self) -> int:
+        return self._max
+
+    def hidden_dim(self) -> int:
+        return self._hidden
+
+    def num_intermediates(self) -> int:
+        return len(self._bufs)
+
+    def allocated_bytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs)
+
+    def get_intermediate(self, idx: int, actual_seq_len: int) -> torch.Tensor:
+        """A view of the first ``actual_seq_len`` rows of intermediate ``idx`` (no copy)."""
+        if not 0 <= idx < len(self._bufs):
+            raise ValueError(f"DynamicExecContext: intermediate index {idx} >= count {len(self._bufs)}")
+        if not 0 <= actual_seq_len <= self._max:
+            raise ValueError(f"DynamicExecContext: actual_seq_len {actual_seq_len} > max_seq_len {self._max}")
+        return self._bufs[idx][:actual_seq_len]

@@ -16,6 +16,7 @@ Sliding-window masks: crates/rmlx-nn/src/sliding_window.rs:25-160.
 from __future__ import annotations
 
 import math
+from dataclasses import dataclass
 from typing import List, Sequence
 
 import torch
@@ -207,3 +208,53 @@ class Attention:
         return self.o(out.reshape(t, hq * hd))
 
     __call__ = forward
+
+
+@dataclass
+class SlidingWindowAttentionConfig:
+    """An attention config plus the window (crates/rmlx-nn/src/sliding_window.rs:25-36)."""
+    base: AttentionConfig
+    window_size: int
+
+    def validate(self) -> "SlidingWindowAttentionConfig":
+        self.base.validate()
+        if self.window_size <= 0:
+            raise ValueError("SlidingWindowAttention: window_size must be positive")
+        return self
+
+
+class SlidingWindowAttention(Attention):
+    """Mistral-style attention: query i sees the keys of positions i - window + 1 .. i
+    (crates/rmlx-nn/src/sliding_window.rs:37-160). With a ``RotatingKvCache`` of the window's size
+    the cache never grows beyond it. On the device the same window is applied inside the flash
+    kernels (``TransformerConfig.sliding_window``); this class is the layer-level form."""
+
+    def __init__(self, config: SlidingWindowAttentionConfig, wqkv: LinearWeight, wo: LinearWeight,
+                 traditional_rope: bool = False, device=None):
+        self.sw_config = config.validate()
+        super().__init__(config.base, wqkv, wo, window=config.window_size,
+                         traditional_rope=traditional_rope, device=device)
+
+    @classmethod
+    def from_projections(cls, config: SlidingWindowAttentionConfig, wq: torch.Tensor, wk: torch.Tensor,
+                         wv: torch.Tensor, wo: torch.Tensor, device=None) -> "SlidingWindowAttention":
+        """Separate q / k / v / o projection matrices ([out, in]) stacked into the merged form."""
+        wqkv = LinearWeight.from_dense(torch.cat([wq, wk, wv], 0), None, device=device)
+        return cls(config, wqkv, LinearWeight.from_dense(wo, None, device=device), device=device)
+
+    def window_size(self) -> int:
+        return self.sw_config.window_size
+
+    def base_config(self) -> AttentionConfig:
+        return self.sw_config.base
+
+    def build_sliding_window_mask(self, q_len: int, kv_len: int, offset: int = 0, device=None) -> torch.Tensor:
+        return sliding_window_mask(q_len, kv_len, self.window, offset, device)
+
+    def new_cache(self, chunk: int = 1, device="cpu", dtype=torch.float32) -> "RotatingKvCache":
+        """A ring that holds what the layer needs when it is fed at most ``chunk`` tokens per call:
+        window + chunk - 1 positions (the first query of a chunk still needs the window before it
+        after the chunk's own keys have been appended)."""
+        c = self.cfg
+        return RotatingKvCache(c.num_kv_heads, c.head_dim, self.window + max(1, chunk) - 1, dtype=dtype,
+                               device=device)

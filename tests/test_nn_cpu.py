@@ -217,3 +217,47 @@ def test_mla_absorbed_decode_over_paged_latent_cache():
     pc.add_sequence(11)                         # the slot and the pages are reusable
     pc.append(11, *attn.compress(xs[9][:3], torch.arange(3)))
     assert pc.seq_len(11) == 3
+
+
+def test_sliding_window_attention_layer_and_dynamic_context():
+    """The layer-level sliding-window attention: same result as the plain layer with that window,
+    incremental decoding over a rotating cache of the window's size equals the full pass, config
+    checks; the pre-allocated intermediates hand out views, never copies."""
+    from rmlx_b200.models.prefill_plan import DynamicExecContext
+    from rmlx_b200.nn.attention import SlidingWindowAttention, SlidingWindowAttentionConfig, sliding_window_mask
+    from rmlx_b200.ops.weights import LinearWeight
+    g = torch.Generator().manual_seed(4)
+    base = AttentionConfig(num_heads=4, num_kv_heads=2, head_dim=8, max_seq_len=64)
+    d = 32
+    wq, wk, wv = torch.randn(32, d, generator=g) * 0.2, torch.randn(16, d, generator=g) * 0.2, torch.randn(16, d, generator=g) * 0.2
+    wo = torch.randn(d, 32, generator=g) * 0.2
+    cfg = SlidingWindowAttentionConfig(base, window_size=5)
+    layer = SlidingWindowAttention.from_projections(cfg, wq, wk, wv, wo)
+    assert layer.window_size() == 5 and layer.base_config() is base
+    plain = Attention(base, LinearWeight.from_dense(torch.cat([wq, wk, wv], 0), None, dtype=torch.float32),
+                      LinearWeight.from_dense(wo, None, dtype=torch.float32), window=5)
+    layer.qkv, layer.o = plain.qkv, plain.o                      # same fp32 weights for an exact comparison
+    x = torch.randn(12, d, generator=g)
+    full = layer(x)
+    assert torch.allclose(full, plain(x), atol=1e-6)
+    cache = layer.new_cache()
+    assert cache.max_size == 5                                   # token by token: exactly the window
+    inc = torch.cat([layer(x[i:i + 1], cache) for i in range(12)])
+    assert torch.allclose(inc, full, atol=1e-5)
+    cache4 = layer.new_cache(chunk=4)
+    assert cache4.max_size == 8                                  # chunks of up to four tokens
+    inc4 = torch.cat([layer(x[:4], cache4), layer(x[4:5], cache4), layer(x[5:9], cache4), layer(x[9:], cache4)])
+    assert torch.allclose(inc4, full, atol=1e-5)
+    m = layer.build_sliding_window_mask(3, 6, offset=3)
+    assert torch.equal(m, sliding_window_mask(3, 6, 5, 3)) and float(m[0, 3]) == 0.0 and m[2, 0] == float("-inf")
+    with pytest.raises(ValueError):
+        SlidingWindowAttentionConfig(base, 0).validate()
+
+    ctx = DynamicExecContext(16, 8, dtype=torch.float32, num_intermediates=2)
+    a = ctx.get_intermediate(1, 5)
+    a.fill_(3.0)
+    assert a.shape == (5, 8) and float(ctx.get_intermediate(1, 16)[:5].mean()) == 3.0      # a view, not a copy
+    assert (ctx.max_seq_len(), ctx.hidden_dim(), ctx.num_intermediates(), ctx.allocated_bytes()) == (16, 8, 2, 2 * 16 * 8 * 4)
+    for bad in ((2, 4), (0, 17)):
+        with pytest.raises(ValueError):
+            ctx.get_intermediate(*bad)
