@@ -365,3 +365,27 @@ def test_every_activation_of_the_reference_has_a_closed_form_here():
     pair = torch.randn(3, 8)
     assert torch.allclose(activation("glu")(pair), pair[:, :4] * sig(pair[:, 4:]))
     assert len(ACTIVATIONS) >= 17
+
+
+def test_top_level_exports_resolve_lazily():
+    """``import rmlx_b200`` is cheap (no model code, no CUDA library) and every exported name
+    resolves to the object of its home module."""
+    import importlib
+    import subprocess
+    import sys
+    import rmlx_b200
+    for name in rmlx_b200.__all__:
+        if name == "__version__":
+            continue
+        obj = getattr(rmlx_b200, name)
+        home = importlib.import_module("rmlx_b200." + rmlx_b200._EXPORTS[name])
+        assert obj is getattr(home, name), name
+    assert "TransformerModel" in dir(rmlx_b200)
+    try:
+        rmlx_b200.no_such_name
+        raise AssertionError("expected AttributeError")
+    except AttributeError:
+        pass
+    code = ("import sys, rmlx_b200; "
+            "assert not [m for m in sys.modules if m.startswith('rmlx_b200.')], 'submodules loaded at import'")
+    assert subprocess.run([sys.executable, "-c", code], capture_output=True).returncode == 0
