@@ -401,6 +401,8 @@ def main():
                        if args.weights == "q4" else "bf16",
                        "global_batch": B, "seq_len": args.ctx, "kv": "paged (page 16), ~N(0,1) context",
                        "parallelism": f"tp{world}", "cuda_graph": use_graph, "graph_store": graph_store,
+                       "graph_recordings_retried": int(getattr(graphs, "capture_failures", 0)),
+                       "graph_keys_run_launch_by_launch": int(getattr(graphs, "eager_fallbacks", 0)),
                        "tp_reduction": "fused" if world > 1 else "none",
                        "l2": "no flush needed: each step streams the active weights of "
                              f"{nlayers} layers (>> 126 MB L2) so nothing is reused across steps",
