@@ -345,6 +345,9 @@ def main():
     graphs = getattr(eng, "graphs", None)
     graph_store = "none" if not use_graph else \
         "native store (csrc/runtime/graph_exec.cu)" if getattr(graphs, "native_captures", 0) else "torch.cuda.CUDAGraph"
+    graph_retries = int(getattr(graphs, "capture_failures", 0))
+    graph_eager = int(getattr(graphs, "eager_fallbacks", 0))
+    del graphs                       # plain numbers only from here on: the cache must die with the engine
     nbytes = weights.nbytes()
     nlayers = cfg.num_layers
     extra = {}
@@ -401,8 +404,8 @@ def main():
                        if args.weights == "q4" else "bf16",
                        "global_batch": B, "seq_len": args.ctx, "kv": "paged (page 16), ~N(0,1) context",
                        "parallelism": f"tp{world}", "cuda_graph": use_graph, "graph_store": graph_store,
-                       "graph_recordings_retried": int(getattr(graphs, "capture_failures", 0)),
-                       "graph_keys_run_launch_by_launch": int(getattr(graphs, "eager_fallbacks", 0)),
+                       "graph_recordings_retried": graph_retries,
+                       "graph_keys_run_launch_by_launch": graph_eager,
                        "tp_reduction": "fused" if world > 1 else "none",
                        "l2": "no flush needed: each step streams the active weights of "
                              f"{nlayers} layers (>> 126 MB L2) so nothing is reused across steps",
