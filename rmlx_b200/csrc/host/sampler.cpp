@@ -223,6 +223,7 @@ int rmlx_sampler_multinomial(void* h, const float* p, int n) {
 // from row n when rows > n, else -1.
 int rmlx_spec_greedy_verify(const int* draft, int n, const float* target_logits, int rows, int vocab, int* next) {
   *next = -1;
+  if (n < 0 || rows < 0 || vocab < 1) return -1;
   for (int i = 0; i < n && i < rows; ++i) {
     const int best = Sampler::argmax(target_logits + size_t(i) * vocab, vocab);
     if (best != draft[i]) { *next = best; return i; }
@@ -238,6 +239,7 @@ int rmlx_spec_rejection_sample(void* h, const int* draft, int n, const float* dr
                                const float* target_probs, int rows, int vocab, int* next) {
   Sampler* s = static_cast<Sampler*>(h);
   *next = -1;
+  if (!h || n < 0 || rows < n || vocab < 1) return -1;      // a target row per draft token at least
   std::vector<float> resid(vocab);
   for (int i = 0; i < n; ++i) {
     const float* pt = target_probs + size_t(i) * vocab;

@@ -325,5 +325,5 @@ class NativeSampler(Sampler):
         n = self._lib.rmlx_spec_rejection_sample(self._h, _ints(draft), len(draft), pd.data_ptr(), pt.data_ptr(),
                                                  pt.shape[0], pt.shape[1], _ct.byref(nxt))
         if n < 0:
-            raise ValueError("draft token outside the vocabulary")
+            raise ValueError("rejection_sample: a draft token outside the vocabulary, or fewer target rows than draft tokens")
         return SpecDecodeResult(n, draft[:n], None if nxt.value < 0 else nxt.value)

@@ -298,5 +298,7 @@ def test_native_sampler_matches_the_python_sampler():
     assert torch.allclose(freq, pt[0], atol=0.03)
     with pytest.raises(ValueError):
         a.rejection_sample([9], pdraft, pt[:1])
+    with pytest.raises(ValueError):
+        a.rejection_sample([0, 1], torch.cat([pdraft, pdraft]), pt[:1])     # two draft tokens, one target row
     assert not a._lib.rmlx_sampler_create(1.0, -1, 0.5, 1.0, 0)      # a negative top-k is refused
     assert not a._lib.rmlx_sampler_create(1.0, 0, 0.0, 1.0, 0)       # so is top-p = 0
